@@ -1,0 +1,393 @@
+/*
+ * metallic_cuda.h -- C ABI of the B200 (sm_100a) KV-cache hot path for
+ * metallic-foundry: fused RoPE + K/V append, flash-decode attention with
+ * grouped-query heads (contiguous and paged caches, split-KV + log-sum-exp
+ * merge) and causal chunked prefill.
+ *
+ * The reference project (cchance27/test-burn, crate metallic-foundry) has no C
+ * ABI: its operators are Rust `Step`/`CompiledStep` impls that bind Metal
+ * buffers.  Each entry point below names the reference item it replaces; paths
+ * are relative to crates/metallic-foundry/.  The Rust side binds these symbols
+ * with a plain `extern "C"` block.
+ *
+ * Conventions
+ *  - All pointers inside MfTensor / the cache descriptors are DEVICE pointers
+ *    valid on the context's device unless a parameter says "host".
+ *  - The caller owns every buffer.  The library keeps no reference after a call
+ *    returns, except for the context-owned scratch arena.
+ *  - Every op is enqueued on the context's stream and returns without waiting.
+ *  - A context is not thread-safe: one context per host thread per GPU.
+ *  - Contract violations are rejected on the host before any launch (the Metal
+ *    kernels silently return instead: flash_decode.metal:165-170).
+ *  - There is no CPU fallback: if no CUDA device is present every call fails.
+ */
+#ifndef METALLIC_CUDA_H
+#define METALLIC_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define MF_API __declspec(dllexport)
+#else
+#define MF_API __attribute__((visibility("default")))
+#endif
+
+/* ------------------------------------------------------------------ status ---
+ * Mirrors the MetalError variants this path can raise (src/error.rs:22-75). */
+typedef int32_t mf_status;
+enum {
+    MF_OK = 0,
+    MF_ERR_OPERATION_NOT_SUPPORTED = 1, /* MetalError::OperationNotSupported */
+    MF_ERR_INVALID_SHAPE = 2,           /* MetalError::InvalidShape */
+    MF_ERR_INVALID_OPERATION = 3,       /* MetalError::InvalidOperation */
+    MF_ERR_INPUT_NOT_FOUND = 4,         /* MetalError::InputNotFound (null tensor) */
+    MF_ERR_UNSUPPORTED_DTYPE = 5,       /* MetalError::UnsupportedDtype */
+    MF_ERR_OUT_OF_MEMORY = 6,           /* MetalError::OutOfMemory */
+    MF_ERR_CUDA = 7,                    /* a CUDA runtime/driver call failed */
+    MF_ERR_NCCL = 8,                    /* a collective failed */
+    MF_ERR_TIMEOUT = 9                  /* a bounded device-side wait ran out */
+};
+
+/* ---------------------------------------------------------------- tensors ---
+ * Replaces TensorArg (src/types/mod.rs:341-347): buffer + byte offset + dtype +
+ * dims + element strides. */
+enum { MF_DTYPE_F16 = 0, MF_DTYPE_F32 = 1, MF_DTYPE_U32 = 2 };
+
+typedef struct MfTensor {
+    void *dev_ptr;
+    uint64_t offset_bytes;
+    uint32_t dtype;
+    uint32_t rank;
+    uint64_t dims[4];
+    uint64_t strides[4]; /* in elements */
+} MfTensor;
+
+/* ----------------------------------------------------------- param structs ---
+ * Byte-for-byte the reference's #[repr(C)] structs (all fields 4 bytes). */
+
+/* KvPrepFusedParamsResolved (src/metals/kv_prep/mod.rs:79-114). */
+typedef struct KvPrepFusedParamsResolved {
+    uint32_t d_model;
+    uint32_t kv_dim;
+    uint32_t head_dim;
+    uint32_t n_heads;
+    uint32_t n_kv_heads;
+    uint32_t group_size;
+    uint32_t seq_len;
+    uint32_t position_offset;
+    uint32_t max_seq_len;
+    uint32_t total_elements;
+    uint32_t rope_mode; /* 0 = neox (half-split), 1 = normal (adjacent pairs) */
+    uint32_t layer_idx;
+    uint32_t no_rope_layer_step;
+} KvPrepFusedParamsResolved;
+enum { MF_ROPE_MODE_NEOX = 0, MF_ROPE_MODE_NORMAL = 1 };
+
+/* RopeParamsResolved (src/metals/rope/mod.rs:11-22). */
+typedef struct RopeParamsResolved {
+    uint32_t dim;
+    uint32_t seq_len;
+    uint32_t position_offset;
+    uint32_t total_elements;
+} RopeParamsResolved;
+
+/* KvCacheWriteParamsResolved (src/metals/kv_cache_write/mod.rs:61-78). */
+typedef struct KvCacheWriteParamsResolved {
+    uint32_t n_kv_heads;
+    uint32_t head_dim;
+    uint32_t input_seq_len;
+    uint32_t position_offset;
+    uint32_t max_seq_len;
+    uint32_t total_elements;
+    uint32_t layer_idx;
+} KvCacheWriteParamsResolved;
+
+/* KvCacheWriteRepeatKvHeadsParamsResolved (src/metals/kv_cache_write/mod.rs:13-35). */
+typedef struct KvCacheWriteRepeatKvHeadsParamsResolved {
+    uint32_t n_kv_heads;
+    uint32_t n_heads;
+    uint32_t group_size;
+    uint32_t head_dim;
+    uint32_t input_seq_len;
+    uint32_t position_offset;
+    uint32_t max_seq_len;
+    uint32_t total_elements;
+    uint32_t layer_idx;
+} KvCacheWriteRepeatKvHeadsParamsResolved;
+
+/* SdpaParams (src/metals/flashattention/stages.rs:456-464). */
+typedef struct SdpaParams {
+    uint32_t kv_len;
+    uint32_t head_dim;
+    float scale;
+    uint32_t stride_k_s;
+    uint32_t stride_v_s;
+} SdpaParams;
+
+/* SdpaPrefillParams (src/metals/flashattention/stages.rs:240-270). */
+typedef struct SdpaPrefillParams {
+    uint32_t kv_len;
+    uint32_t head_dim;
+    float scale;
+    uint32_t stride_k_s;
+    uint32_t stride_v_s;
+    uint32_t query_offset;
+    uint32_t q_stride_b;
+    uint32_t q_stride_h;
+    uint32_t k_stride_b;
+    uint32_t k_stride_h;
+    uint32_t v_stride_b;
+    uint32_t v_stride_h;
+    uint32_t out_stride_b;
+    uint32_t out_stride_h;
+    uint32_t q_stride_m;
+    uint32_t out_stride_m;
+    uint32_t group_size;
+    uint32_t q_len;
+} SdpaPrefillParams;
+
+/* SdpaPrefillSplitKParams (src/metals/flashattention/stages.rs:272-306). */
+typedef struct SdpaPrefillSplitKParams {
+    SdpaPrefillParams base;
+    uint32_t n_heads;
+    uint32_t split_k;
+} SdpaPrefillSplitKParams;
+
+/* Strides of one decode dispatch: FlashDecodeArgs minus the tensors
+ * (src/metals/flashattention/step.rs:404-424). */
+typedef struct MfFlashDecodeStrides {
+    uint32_t q_stride_b, q_stride_h;
+    uint32_t k_stride_b, k_stride_h;
+    uint32_t v_stride_b, v_stride_h;
+    uint32_t out_stride_b, out_stride_h;
+} MfFlashDecodeStrides;
+
+/* Fields of FlashAttentionStep after DynamicValue resolution
+ * (src/metals/sdpa/step.rs:21-38). */
+typedef struct MfFlashAttentionArgs {
+    uint32_t causal;        /* bool */
+    uint32_t query_offset;
+    uint32_t n_heads;
+    uint32_t head_dim;
+    uint32_t kv_seq_len;
+    uint32_t m;             /* 0 is treated as 1, like the reference */
+    uint32_t kv_head_major; /* bool; must be 1 (sdpa/step.rs:193-197) */
+} MfFlashAttentionArgs;
+
+/* Which route the dispatcher took (for tests and logging). */
+enum { MF_ROUTE_DECODE = 1, MF_ROUTE_PREFILL = 2, MF_ROUTE_PREFILL_SPLITK = 3 };
+
+/* ----------------------------------------------------------- paged KV cache ---
+ * Not in the reference (its cache is contiguous only).  Pool layout per layer,
+ * for K and for V: [n_pages, n_kv_heads, page_size, head_dim] f16.  Token t of
+ * sequence b lives in page page_table[b*page_table_stride + t/page_size], row
+ * t % page_size.  kv_lens[b] counts the tokens visible to the query AFTER the
+ * append of this step (so the token appended by this step sits at kv_lens[b]-1). */
+typedef struct MfPagedKv {
+    void *k_pool;                /* device, f16 */
+    void *v_pool;                /* device, f16 */
+    const uint32_t *page_table;  /* device, [batch, page_table_stride] */
+    const uint32_t *kv_lens;     /* device, [batch] */
+    uint32_t n_pages;
+    uint32_t n_kv_heads;
+    uint32_t page_size;          /* 16, 32 or 64 */
+    uint32_t head_dim;           /* 64 or 128 */
+    uint32_t page_table_stride;
+    uint32_t batch;
+} MfPagedKv;
+
+/* Inputs of one batched decode step over a paged cache: one new token per
+ * sequence.  q is [batch, n_heads*head_dim], k and v are [batch, n_kv_heads*head_dim],
+ * out is [batch, n_heads*head_dim]; cos/sin are [max_pos, head_dim/2] f16 tables. */
+typedef struct MfPagedDecodeArgs {
+    const void *q, *k, *v; /* device f16; k/v may be NULL when append == 0 */
+    void *q_rot;           /* device f16 or NULL: optional copy of the roped q */
+    void *out;             /* device f16 */
+    const void *cos, *sin; /* device f16; may be NULL when rope == 0 */
+    uint32_t n_heads;
+    uint32_t rope;         /* 1: q (and appended k) are roped at position kv_lens[b]-1 */
+    uint32_t rope_mode;    /* MF_ROPE_MODE_* */
+    uint32_t append;       /* 1: write the new k,v row into the pool before attending */
+    float scale;           /* 1/sqrt(head_dim), computed by the caller (step.rs:1042) */
+} MfPagedDecodeArgs;
+
+typedef struct MfContext MfContext;
+typedef struct MfDecodePlan MfDecodePlan;
+
+/* ------------------------------------------------------------------ context ---
+ * Replaces Foundry (src/lib.rs:57-353): device + in-order stream + scratch. */
+MF_API mf_status mf_context_create(int32_t device, void *cuda_stream, MfContext **out);
+MF_API void mf_context_destroy(MfContext *ctx);
+MF_API mf_status mf_context_set_stream(MfContext *ctx, void *cuda_stream);
+MF_API mf_status mf_synchronize(MfContext *ctx); /* Foundry::synchronize (lib.rs:170-188) */
+MF_API const char *mf_last_error(const MfContext *ctx);
+MF_API const char *mf_status_name(mf_status s);
+MF_API uint32_t mf_abi_version(void);
+/* Number of kernels this context has launched since creation (instrumentation,
+ * stands in for the per-dispatch metric events of lib.rs:225-233). */
+MF_API uint64_t mf_launch_count(const MfContext *ctx);
+/* Caller-provided scratch (device); when absent the context allocates its own
+ * arena on first use and grows it on demand (pooled scratch of step.rs:927-929). */
+MF_API mf_status mf_context_set_scratch(MfContext *ctx, void *dev_ptr, uint64_t bytes);
+
+/* ------------------------------------------------------- host-side builders ---
+ * RoPE cos/sin tables (src/model/executor.rs:1980-2007), written to HOST f16
+ * buffers of n_pos*head_dim/2 elements covering positions
+ * [first_pos, first_pos+n_pos).  freq_factors may be NULL. */
+MF_API mf_status mf_rope_tables_host(float rope_base, uint32_t head_dim, uint32_t first_pos,
+                                     uint32_t n_pos, const float *freq_factors,
+                                     uint16_t *cos_out, uint16_t *sin_out);
+
+/* ContextConfig::align_capacity (src/model/context.rs:213-219). */
+MF_API uint64_t mf_align_capacity(uint64_t capacity);
+/* Growth rule of ensure_kv_capacity (src/model/executor.rs:2332-2396):
+ * max(2*current, required) clamped to max_context_len, aligned to 128; returns 0
+ * when required > max_context_len (the reference raises InvalidOperation). */
+MF_API uint64_t mf_grown_capacity(uint64_t current, uint64_t required, uint64_t max_context_len);
+/* KvGeometry::per_token_bytes_f16 (src/model/kv_geometry.rs:82-89). */
+MF_API uint64_t mf_kv_per_token_bytes_f16(uint32_t n_layers, uint32_t cache_heads, uint32_t head_dim);
+/* ContextConfig::estimate_kv_memory (src/model/context.rs:222-243), total bytes. */
+MF_API uint64_t mf_estimate_kv_memory(uint32_t n_layers, uint32_t cache_heads, uint32_t head_dim,
+                                      uint64_t context_len);
+/* Prefill split-K heuristic (src/metals/flashattention/step.rs:849-866). */
+MF_API uint32_t mf_prefill_split_k(uint32_t kv_seq_len, uint32_t q_seq_len);
+
+/* ---------------------------------------------------------------- operators --- */
+
+/* "KvPrepFused" (src/metals/kv_prep/step.rs:93-132, kv_prep_fused.metal:26-123):
+ * q [M, Hq*D], k,v [M, Hkv*D] row-major -> q_rot [Hq, M, D] packed from element 0,
+ * caches [cache_heads, max_seq_len, D] written at rows position_offset..+M.
+ * The cache layout is taken from k_cache->dims[0]: Hkv = compact, Hq = expanded
+ * (KvCacheLayout, src/model/kv_geometry.rs:6-12). */
+MF_API mf_status mf_kv_prep_fused(MfContext *ctx, const MfTensor *q, const MfTensor *k,
+                                  const MfTensor *v, const MfTensor *q_rot,
+                                  const MfTensor *k_cache, const MfTensor *v_cache,
+                                  const MfTensor *cos, const MfTensor *sin,
+                                  const KvPrepFusedParamsResolved *params);
+
+/* "Rope" (src/metals/rope/mod.rs, rope.metal:28-75): NeoX RoPE over rows of `dim`. */
+MF_API mf_status mf_rope(MfContext *ctx, const MfTensor *input, const MfTensor *output,
+                         const MfTensor *cos, const MfTensor *sin,
+                         const RopeParamsResolved *params);
+
+/* "KvCacheWrite" (kv_cache_write.metal:6-30): input [Hkv, M, D] -> rows
+ * position_offset..+M of a compact cache [Hkv, cap, D]. */
+MF_API mf_status mf_kv_cache_write(MfContext *ctx, const MfTensor *input, const MfTensor *cache,
+                                   const KvCacheWriteParamsResolved *params);
+
+/* "KvCacheWriteRepeatKvHeads" (kv_cache_write_repeat.metal:9-40): same input,
+ * each KV head written to its group_size heads of an expanded cache [Hq, cap, D]. */
+MF_API mf_status mf_kv_cache_write_repeat_kv_heads(MfContext *ctx, const MfTensor *input,
+                                                   const MfTensor *cache,
+                                                   const KvCacheWriteRepeatKvHeadsParamsResolved *params);
+
+/* "KvCacheRead" (kv_cache_read.metal:7-29): cache [H, cap, D] -> [H, seq_len, D]. */
+MF_API mf_status mf_kv_cache_read(MfContext *ctx, const MfTensor *cache, const MfTensor *output,
+                                  uint32_t seq_len);
+
+/* "FlashAttention" (src/metals/sdpa/step.rs:160-503): the dispatcher.  m == 1
+ * routes to decode, m > 1 (causal, query_offset + m == kv_seq_len) to prefill;
+ * anything else returns MF_ERR_OPERATION_NOT_SUPPORTED (the reference falls back
+ * to its materialised path there).  route_out may be NULL. */
+MF_API mf_status mf_flash_attention(MfContext *ctx, const MfTensor *q, const MfTensor *k,
+                                    const MfTensor *v, const MfTensor *output,
+                                    const MfFlashAttentionArgs *args, uint32_t *route_out);
+
+/* run_flash_decode (src/metals/flashattention/step.rs:558-585): decode when
+ * q_seq_len == 1, prefill otherwise; strides inferred from the tensors exactly as
+ * the reference does (q_rot head-major packed over the true M, cache capacity
+ * from k->dims[1]). */
+MF_API mf_status mf_run_flash_decode(MfContext *ctx, const MfTensor *q, const MfTensor *k,
+                                     const MfTensor *v, const MfTensor *output, uint32_t n_heads,
+                                     uint32_t head_dim, uint32_t kv_seq_len, uint32_t q_seq_len,
+                                     uint32_t kv_head_major);
+
+/* "FlashDecode" with explicit strides (src/metals/flashattention/step.rs:340-402;
+ * kernels flash_decode.metal:146-490).  grid (1, n_heads, batch) in the reference;
+ * here one CTA per (kv head, KV split, batch).  n_splits == 0 lets the library
+ * choose. */
+MF_API mf_status mf_flash_decode(MfContext *ctx, const void *q, const void *k, const void *v,
+                                 void *output, const MfFlashDecodeStrides *strides,
+                                 const SdpaParams *params, uint32_t n_heads, uint32_t batch,
+                                 uint32_t n_splits);
+
+/* RopeFlashDecodeStep (src/metals/flashattention/step.rs:54-306): NeoX RoPE of q
+ * at rope->position_offset fused in front of decode.  q is un-roped [batch, Hq, D]. */
+MF_API mf_status mf_rope_flash_decode(MfContext *ctx, const void *q, const void *k, const void *v,
+                                      const void *cos, const void *sin, void *output,
+                                      const RopeParamsResolved *rope, const SdpaParams *params,
+                                      const MfFlashDecodeStrides *strides, uint32_t n_heads,
+                                      uint32_t batch);
+
+/* Causal prefill with explicit params (flash_prefill.metal:94-446 and the
+ * split-K pair :460-983).  split_k <= 1 runs the single kernel. */
+MF_API mf_status mf_flash_prefill(MfContext *ctx, const void *q, const void *k, const void *v,
+                                  void *output, const SdpaPrefillSplitKParams *params);
+
+/* Split merge (flash_prefill.metal:806-983), also the merge that follows the
+ * cross-GPU all-gather: acc [n_splits, rows, D] f32, m,l [n_splits, rows] f32
+ * -> out [rows, D] f16. */
+MF_API mf_status mf_merge_partials(MfContext *ctx, const float *acc, const float *m,
+                                   const float *l, uint32_t n_splits, uint32_t rows,
+                                   uint32_t head_dim, void *out);
+
+/* ------------------------------------------------------ paged batched decode ---
+ * No counterpart in the reference (contiguous cache, batch 1).  A plan cuts the
+ * step's KV tiles into equal spans, one per resident CTA; it depends only on
+ * kv_lens (host copy), geometry and the device, and is reused by every layer of
+ * the step. */
+MF_API mf_status mf_decode_plan_create(MfContext *ctx, const uint32_t *kv_lens_host, uint32_t batch,
+                                       uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,
+                                       uint32_t page_size, uint32_t max_ctas, MfDecodePlan **out);
+/* Re-plan in place for new lengths (same batch and geometry); no allocation when
+ * the work list fits the plan's capacity. */
+MF_API mf_status mf_decode_plan_update(MfContext *ctx, MfDecodePlan *plan,
+                                       const uint32_t *kv_lens_host);
+MF_API void mf_decode_plan_destroy(MfContext *ctx, MfDecodePlan *plan);
+/* The planner alone, on the host (no device needed): fills items_out (8 uint32 per
+ * item: seq, kvh, tile_begin, tile_end, slot, unit, n_parts, first_slot) and
+ * cta_begin_out (n_ctas+1 entries); returns the number of items, or the number
+ * needed when item_capacity is too small.  n_ctas_out receives the CTA count. */
+MF_API uint32_t mf_decode_plan_build_host(const uint32_t *kv_lens_host, uint32_t batch, uint32_t n_kv_heads,
+                                          uint32_t max_ctas, uint32_t *items_out, uint32_t item_capacity,
+                                          uint32_t *cta_begin_out, uint32_t *n_ctas_out);
+MF_API uint32_t mf_decode_plan_ctas(const MfDecodePlan *plan);
+MF_API uint32_t mf_decode_plan_items(const MfDecodePlan *plan);
+MF_API uint64_t mf_decode_plan_tiles(const MfDecodePlan *plan);
+
+/* Append (optional) + RoPE (optional) + GQA flash-decode over a paged cache, one
+ * launch per layer. */
+MF_API mf_status mf_paged_decode(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv *cache,
+                                 const MfPagedDecodeArgs *args);
+
+/* Stand-alone paged append (RoPE + K/V slot write, q_rot out) for M new tokens of
+ * sequence `seq` starting at position_offset (chunked prefill into a paged cache),
+ * or with seq == UINT32_MAX one token per sequence at kv_lens[b]-1. */
+MF_API mf_status mf_paged_kv_append(MfContext *ctx, const MfPagedKv *cache, const void *q,
+                                    const void *k, const void *v, void *q_rot, const void *cos,
+                                    const void *sin, uint32_t n_heads, uint32_t rope_mode,
+                                    uint32_t apply_rope, uint32_t seq, uint32_t position_offset,
+                                    uint32_t seq_len);
+
+/* Debug/oracle gather: first `len` tokens of sequence `seq` -> [Hkv, len, D]. */
+MF_API mf_status mf_paged_gather(MfContext *ctx, const MfPagedKv *cache, uint32_t use_v,
+                                 uint32_t seq, uint32_t len, void *out);
+
+/* Sequence-sharded decode: this shard attends over its own keys only and emits
+ * unnormalised f32 partials (acc [batch, Hq, D], m and l [batch, Hq]) for the
+ * all-gather + mf_merge_partials step.  kv_lens in `cache` are the shard-local
+ * lengths; positions for RoPE come from rope_positions (device, [batch]). */
+MF_API mf_status mf_paged_decode_partial(MfContext *ctx, const MfDecodePlan *plan,
+                                         const MfPagedKv *cache, const MfPagedDecodeArgs *args,
+                                         const uint32_t *rope_positions, float *acc, float *m,
+                                         float *l);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* METALLIC_CUDA_H */

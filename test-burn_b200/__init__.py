@@ -1,0 +1,400 @@
+"""Python host binding of libmetallic_cuda.so (the C ABI in include/metallic_cuda.h).
+
+The names follow the metallic-foundry operator layer this library stands in for
+(crates/metallic-foundry/src/metals/{kv_prep,sdpa,flashattention,rope,kv_cache_write}):
+`Foundry` (context), `KvPrepFused`, `FlashAttentionStep`, `run_flash_decode`,
+`RopeFlashDecodeStep`, `KvCacheWrite`, `KvCacheRead`, `Rope`, plus the paged
+batched-decode entry points, which the reference does not have.
+
+There is no fallback path: importing works without a GPU (so that the symbol table
+can be checked), but creating a `Foundry` raises `MetalError` when no sm_100
+device is present, and a missing shared library raises at import.
+
+PyTorch appears here only as the owner of device buffers and streams; the shared
+library itself does not link it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from pathlib import Path
+
+_HERE = Path(__file__).resolve().parent
+_SO = _HERE / "libmetallic_cuda.so"
+if not _SO.exists():
+    raise ImportError(f"{_SO} is missing: build it with `python {_HERE / 'build.py'}` (no CPU fallback exists)")
+lib = C.CDLL(str(_SO))
+
+u32 = C.c_uint32
+u64 = C.c_uint64
+vp = C.c_void_p
+
+MF_OK = 0
+STATUS_NAMES = {0: "Ok", 1: "OperationNotSupported", 2: "InvalidShape", 3: "InvalidOperation", 4: "InputNotFound",
+                5: "UnsupportedDtype", 6: "OutOfMemory", 7: "CudaError", 8: "NcclError", 9: "Timeout"}
+ROPE_MODE_NEOX, ROPE_MODE_NORMAL = 0, 1
+ROUTE_DECODE, ROUTE_PREFILL, ROUTE_PREFILL_SPLITK = 1, 2, 3
+DTYPE_F16, DTYPE_F32, DTYPE_U32 = 0, 1, 2
+ALL_SEQUENCES = 0xFFFFFFFF
+
+
+class MetalError(RuntimeError):
+    """Raised for any non-zero mf_status; `.kind` is the MetalError variant name."""
+
+    def __init__(self, status: int, message: str):
+        self.status = status
+        self.kind = STATUS_NAMES.get(status, "Unknown")
+        super().__init__(f"{self.kind}: {message}")
+
+
+class MfTensor(C.Structure):
+    _fields_ = [("dev_ptr", vp), ("offset_bytes", u64), ("dtype", u32), ("rank", u32), ("dims", u64 * 4),
+                ("strides", u64 * 4)]
+
+
+def _u32_struct(name, fields):
+    return type(name, (C.Structure,), {"_fields_": [(f, u32) for f in fields]})
+
+
+KvPrepFusedParamsResolved = _u32_struct("KvPrepFusedParamsResolved", (
+    "d_model", "kv_dim", "head_dim", "n_heads", "n_kv_heads", "group_size", "seq_len", "position_offset",
+    "max_seq_len", "total_elements", "rope_mode", "layer_idx", "no_rope_layer_step"))
+RopeParamsResolved = _u32_struct("RopeParamsResolved", ("dim", "seq_len", "position_offset", "total_elements"))
+KvCacheWriteParamsResolved = _u32_struct("KvCacheWriteParamsResolved", (
+    "n_kv_heads", "head_dim", "input_seq_len", "position_offset", "max_seq_len", "total_elements", "layer_idx"))
+KvCacheWriteRepeatKvHeadsParamsResolved = _u32_struct("KvCacheWriteRepeatKvHeadsParamsResolved", (
+    "n_kv_heads", "n_heads", "group_size", "head_dim", "input_seq_len", "position_offset", "max_seq_len",
+    "total_elements", "layer_idx"))
+MfFlashDecodeStrides = _u32_struct("MfFlashDecodeStrides", (
+    "q_stride_b", "q_stride_h", "k_stride_b", "k_stride_h", "v_stride_b", "v_stride_h", "out_stride_b",
+    "out_stride_h"))
+MfFlashAttentionArgs = _u32_struct("MfFlashAttentionArgs", (
+    "causal", "query_offset", "n_heads", "head_dim", "kv_seq_len", "m", "kv_head_major"))
+
+
+class SdpaParams(C.Structure):
+    _fields_ = [("kv_len", u32), ("head_dim", u32), ("scale", C.c_float), ("stride_k_s", u32), ("stride_v_s", u32)]
+
+
+class SdpaPrefillParams(C.Structure):
+    _fields_ = [("kv_len", u32), ("head_dim", u32), ("scale", C.c_float)] + [(f, u32) for f in (
+        "stride_k_s", "stride_v_s", "query_offset", "q_stride_b", "q_stride_h", "k_stride_b", "k_stride_h",
+        "v_stride_b", "v_stride_h", "out_stride_b", "out_stride_h", "q_stride_m", "out_stride_m", "group_size",
+        "q_len")]
+
+
+class SdpaPrefillSplitKParams(C.Structure):
+    _fields_ = [("base", SdpaPrefillParams), ("n_heads", u32), ("split_k", u32)]
+
+
+class MfPagedKv(C.Structure):
+    _fields_ = [("k_pool", vp), ("v_pool", vp), ("page_table", vp), ("kv_lens", vp), ("n_pages", u32),
+                ("n_kv_heads", u32), ("page_size", u32), ("head_dim", u32), ("page_table_stride", u32),
+                ("batch", u32)]
+
+
+class MfPagedDecodeArgs(C.Structure):
+    _fields_ = [("q", vp), ("k", vp), ("v", vp), ("q_rot", vp), ("out", vp), ("cos", vp), ("sin", vp),
+                ("n_heads", u32), ("rope", u32), ("rope_mode", u32), ("append", u32), ("scale", C.c_float)]
+
+
+# Every symbol declared in include/metallic_cuda.h, with its signature.
+_SIGNATURES = {
+    "mf_context_create": (C.c_int32, [C.c_int32, vp, C.POINTER(vp)]),
+    "mf_context_destroy": (None, [vp]),
+    "mf_context_set_stream": (C.c_int32, [vp, vp]),
+    "mf_synchronize": (C.c_int32, [vp]),
+    "mf_last_error": (C.c_char_p, [vp]),
+    "mf_status_name": (C.c_char_p, [C.c_int32]),
+    "mf_abi_version": (u32, []),
+    "mf_launch_count": (u64, [vp]),
+    "mf_context_set_scratch": (C.c_int32, [vp, vp, u64]),
+    "mf_rope_tables_host": (C.c_int32, [C.c_float, u32, u32, u32, vp, vp, vp]),
+    "mf_align_capacity": (u64, [u64]),
+    "mf_grown_capacity": (u64, [u64, u64, u64]),
+    "mf_kv_per_token_bytes_f16": (u64, [u32, u32, u32]),
+    "mf_estimate_kv_memory": (u64, [u32, u32, u32, u64]),
+    "mf_prefill_split_k": (u32, [u32, u32]),
+    "mf_kv_prep_fused": (C.c_int32, [vp] + [C.POINTER(MfTensor)] * 8 + [C.POINTER(KvPrepFusedParamsResolved)]),
+    "mf_rope": (C.c_int32, [vp] + [C.POINTER(MfTensor)] * 4 + [C.POINTER(RopeParamsResolved)]),
+    "mf_kv_cache_write": (C.c_int32, [vp, C.POINTER(MfTensor), C.POINTER(MfTensor),
+                                      C.POINTER(KvCacheWriteParamsResolved)]),
+    "mf_kv_cache_write_repeat_kv_heads": (C.c_int32, [vp, C.POINTER(MfTensor), C.POINTER(MfTensor),
+                                                      C.POINTER(KvCacheWriteRepeatKvHeadsParamsResolved)]),
+    "mf_kv_cache_read": (C.c_int32, [vp, C.POINTER(MfTensor), C.POINTER(MfTensor), u32]),
+    "mf_flash_attention": (C.c_int32, [vp] + [C.POINTER(MfTensor)] * 4 + [C.POINTER(MfFlashAttentionArgs),
+                                                                         C.POINTER(u32)]),
+    "mf_run_flash_decode": (C.c_int32, [vp] + [C.POINTER(MfTensor)] * 4 + [u32] * 5),
+    "mf_flash_decode": (C.c_int32, [vp, vp, vp, vp, vp, C.POINTER(MfFlashDecodeStrides), C.POINTER(SdpaParams),
+                                    u32, u32, u32]),
+    "mf_rope_flash_decode": (C.c_int32, [vp, vp, vp, vp, vp, vp, vp, C.POINTER(RopeParamsResolved),
+                                         C.POINTER(SdpaParams), C.POINTER(MfFlashDecodeStrides), u32, u32]),
+    "mf_flash_prefill": (C.c_int32, [vp, vp, vp, vp, vp, C.POINTER(SdpaPrefillSplitKParams)]),
+    "mf_merge_partials": (C.c_int32, [vp, vp, vp, vp, u32, u32, u32, vp]),
+    "mf_decode_plan_create": (C.c_int32, [vp, vp, u32, u32, u32, u32, u32, u32, C.POINTER(vp)]),
+    "mf_decode_plan_update": (C.c_int32, [vp, vp, vp]),
+    "mf_decode_plan_destroy": (None, [vp, vp]),
+    "mf_decode_plan_build_host": (u32, [vp, u32, u32, u32, vp, u32, vp, C.POINTER(u32)]),
+    "mf_decode_plan_ctas": (u32, [vp]),
+    "mf_decode_plan_items": (u32, [vp]),
+    "mf_decode_plan_tiles": (u64, [vp]),
+    "mf_paged_decode": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv), C.POINTER(MfPagedDecodeArgs)]),
+    "mf_paged_kv_append": (C.c_int32, [vp, C.POINTER(MfPagedKv), vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32,
+                                       u32]),
+    "mf_paged_gather": (C.c_int32, [vp, C.POINTER(MfPagedKv), u32, u32, u32, vp]),
+    "mf_paged_decode_partial": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv), C.POINTER(MfPagedDecodeArgs), vp, vp, vp,
+                                            vp]),
+}
+for _name, (_res, _args) in _SIGNATURES.items():
+    _fn = getattr(lib, _name)  # AttributeError here means the library does not export a declared symbol
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+EXPORTED_SYMBOLS = tuple(_SIGNATURES)
+
+
+def tensor_arg(t, dims=None, strides=None) -> MfTensor:
+    """TensorArg::from_tensor for a torch tensor (dims/strides may be overridden to
+    describe metadata that differs from the buffer's true layout, as the reference does
+    for q_rot)."""
+    import torch
+
+    dt = {torch.float16: DTYPE_F16, torch.float32: DTYPE_F32, torch.int32: DTYPE_U32, torch.uint32: DTYPE_U32}
+    if t.dtype not in dt:
+        code = 99
+    else:
+        code = dt[t.dtype]
+    dims = list(t.shape) if dims is None else list(dims)
+    strides = list(t.stride()) if strides is None else list(strides)
+    m = MfTensor()
+    m.dev_ptr = t.data_ptr()
+    m.offset_bytes = 0
+    m.dtype = code
+    m.rank = len(dims)
+    for i, (d, s) in enumerate(zip(dims, strides)):
+        m.dims[i] = d
+        m.strides[i] = s
+    return m
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+class Foundry:
+    """Device + in-order stream + scratch (Foundry, src/lib.rs:57-353)."""
+
+    def __init__(self, device: int = 0, stream=None):
+        h = vp()
+        stream_ptr = None if stream is None else int(stream)
+        st = lib.mf_context_create(device, stream_ptr, C.byref(h))
+        if st != MF_OK:
+            raise MetalError(st, "mf_context_create failed (no sm_100 CUDA device? there is no CPU fallback)")
+        self._h = h
+        self.device = device
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib.mf_context_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def check(self, st: int):
+        if st != MF_OK:
+            raise MetalError(st, (lib.mf_last_error(self._h) or b"").decode())
+
+    def set_stream(self, stream):
+        self.check(lib.mf_context_set_stream(self._h, None if stream is None else int(stream)))
+
+    def synchronize(self):
+        self.check(lib.mf_synchronize(self._h))
+
+    @property
+    def launch_count(self) -> int:
+        return int(lib.mf_launch_count(self._h))
+
+    # -- operators -------------------------------------------------------------------------
+
+    def kv_prep_fused(self, q, k, v, q_rot, k_cache, v_cache, cos, sin, params: KvPrepFusedParamsResolved):
+        """foundry.run(&KvPrepFused{..}) (src/metals/kv_prep/mod.rs:157-182)."""
+        ts = [tensor_arg(x) for x in (q, k, v, q_rot, k_cache, v_cache, cos, sin)]
+        self.check(lib.mf_kv_prep_fused(self._h, *[C.byref(t) for t in ts], C.byref(params)))
+
+    def rope(self, x, out, cos, sin, params: RopeParamsResolved):
+        ts = [tensor_arg(t) for t in (x, out, cos, sin)]
+        self.check(lib.mf_rope(self._h, *[C.byref(t) for t in ts], C.byref(params)))
+
+    def kv_cache_write(self, x, cache, params):
+        a, b = tensor_arg(x), tensor_arg(cache)
+        fn = lib.mf_kv_cache_write if isinstance(params, KvCacheWriteParamsResolved) \
+            else lib.mf_kv_cache_write_repeat_kv_heads
+        self.check(fn(self._h, C.byref(a), C.byref(b), C.byref(params)))
+
+    def kv_cache_read(self, cache, out, seq_len: int):
+        a, b = tensor_arg(cache), tensor_arg(out)
+        self.check(lib.mf_kv_cache_read(self._h, C.byref(a), C.byref(b), seq_len))
+
+    def flash_attention(self, q, k, v, output, *, causal, query_offset, n_heads, head_dim, kv_seq_len, m=1,
+                        kv_head_major=True, q_meta=None, out_meta=None) -> int:
+        """FlashAttentionStep::execute (src/metals/sdpa/step.rs:160-503).  Returns the route."""
+        args = MfFlashAttentionArgs(int(causal), query_offset, n_heads, head_dim, kv_seq_len, m, int(kv_head_major))
+        tq = tensor_arg(q, *(q_meta or (None, None)))
+        to = tensor_arg(output, *(out_meta or (None, None)))
+        tk, tv = tensor_arg(k), tensor_arg(v)
+        route = u32(0)
+        self.check(lib.mf_flash_attention(self._h, C.byref(tq), C.byref(tk), C.byref(tv), C.byref(to), C.byref(args),
+                                          C.byref(route)))
+        return route.value
+
+    def run_flash_decode(self, q, k, v, output, n_heads, head_dim, kv_seq_len, q_seq_len=1, kv_head_major=True,
+                         q_meta=None, out_meta=None):
+        tq = tensor_arg(q, *(q_meta or (None, None)))
+        to = tensor_arg(output, *(out_meta or (None, None)))
+        tk, tv = tensor_arg(k), tensor_arg(v)
+        self.check(lib.mf_run_flash_decode(self._h, C.byref(tq), C.byref(tk), C.byref(tv), C.byref(to), n_heads,
+                                           head_dim, kv_seq_len, q_seq_len, int(kv_head_major)))
+
+    def flash_decode(self, q, k, v, output, strides: MfFlashDecodeStrides, params: SdpaParams, n_heads, batch=1,
+                     n_splits=0):
+        self.check(lib.mf_flash_decode(self._h, _ptr(q), _ptr(k), _ptr(v), _ptr(output), C.byref(strides),
+                                       C.byref(params), n_heads, batch, n_splits))
+
+    def rope_flash_decode(self, q, k, v, cos, sin, output, rope: RopeParamsResolved, params: SdpaParams,
+                          strides: MfFlashDecodeStrides, n_heads, batch=1):
+        """RopeFlashDecodeStep (src/metals/flashattention/step.rs:54-306)."""
+        self.check(lib.mf_rope_flash_decode(self._h, _ptr(q), _ptr(k), _ptr(v), _ptr(cos), _ptr(sin), _ptr(output),
+                                            C.byref(rope), C.byref(params), C.byref(strides), n_heads, batch))
+
+    def flash_prefill(self, q, k, v, output, params: SdpaPrefillSplitKParams):
+        self.check(lib.mf_flash_prefill(self._h, _ptr(q), _ptr(k), _ptr(v), _ptr(output), C.byref(params)))
+
+    def merge_partials(self, acc, m, l, out):
+        n_splits, rows, d = acc.shape
+        self.check(lib.mf_merge_partials(self._h, _ptr(acc), _ptr(m), _ptr(l), n_splits, rows, d, _ptr(out)))
+
+    # -- paged cache -----------------------------------------------------------------------
+
+    def decode_plan(self, kv_lens_host, *, n_heads, n_kv_heads, head_dim, page_size, max_ctas=0) -> "DecodePlan":
+        return DecodePlan(self, kv_lens_host, n_heads, n_kv_heads, head_dim, page_size, max_ctas)
+
+    def paged_decode(self, plan: "DecodePlan", cache: MfPagedKv, q, out, *, n_heads, scale=None, k=None, v=None,
+                     cos=None, sin=None, rope=False, rope_mode=ROPE_MODE_NEOX, append=False, q_rot=None):
+        scale = 1.0 / math.sqrt(cache.head_dim) if scale is None else scale
+        a = MfPagedDecodeArgs(_ptr(q), _ptr(k), _ptr(v), _ptr(q_rot), _ptr(out), _ptr(cos), _ptr(sin), n_heads,
+                              int(rope), rope_mode, int(append), scale)
+        self.check(lib.mf_paged_decode(self._h, plan._h, C.byref(cache), C.byref(a)))
+
+    def paged_decode_partial(self, plan, cache, q, acc, m, l, *, n_heads, rope_positions=None, scale=None, k=None,
+                             v=None, cos=None, sin=None, rope=False, rope_mode=ROPE_MODE_NEOX, append=False):
+        scale = 1.0 / math.sqrt(cache.head_dim) if scale is None else scale
+        a = MfPagedDecodeArgs(_ptr(q), _ptr(k), _ptr(v), None, None, _ptr(cos), _ptr(sin), n_heads, int(rope),
+                              rope_mode, int(append), scale)
+        self.check(lib.mf_paged_decode_partial(self._h, plan._h, C.byref(cache), C.byref(a), _ptr(rope_positions),
+                                               _ptr(acc), _ptr(m), _ptr(l)))
+
+    def paged_kv_append(self, cache: MfPagedKv, q, k, v, q_rot, cos, sin, *, n_heads, rope_mode=ROPE_MODE_NEOX,
+                        apply_rope=True, seq=ALL_SEQUENCES, position_offset=0, seq_len=0):
+        self.check(lib.mf_paged_kv_append(self._h, C.byref(cache), _ptr(q), _ptr(k), _ptr(v), _ptr(q_rot), _ptr(cos),
+                                          _ptr(sin), n_heads, rope_mode, int(apply_rope), seq, position_offset,
+                                          seq_len))
+
+    def paged_gather(self, cache: MfPagedKv, use_v: bool, seq: int, length: int, out):
+        self.check(lib.mf_paged_gather(self._h, C.byref(cache), int(use_v), seq, length, _ptr(out)))
+
+
+class DecodePlan:
+    """Equal-span work list of one batched decode step (see mf_decode_plan_create)."""
+
+    def __init__(self, foundry: Foundry, kv_lens_host, n_heads, n_kv_heads, head_dim, page_size, max_ctas=0):
+        import numpy as np
+
+        self._f = foundry
+        lens = np.ascontiguousarray(kv_lens_host, dtype=np.uint32)
+        self.batch = int(lens.shape[0])
+        h = vp()
+        foundry.check(lib.mf_decode_plan_create(foundry._h, lens.ctypes.data, self.batch, n_heads, n_kv_heads, head_dim,
+                                                page_size, max_ctas, C.byref(h)))
+        self._h = h
+
+    def update(self, kv_lens_host):
+        import numpy as np
+
+        lens = np.ascontiguousarray(kv_lens_host, dtype=np.uint32)
+        assert lens.shape[0] == self.batch
+        self._f.check(lib.mf_decode_plan_update(self._f._h, self._h, lens.ctypes.data))
+
+    @property
+    def ctas(self):
+        return int(lib.mf_decode_plan_ctas(self._h))
+
+    @property
+    def items(self):
+        return int(lib.mf_decode_plan_items(self._h))
+
+    @property
+    def tiles(self):
+        return int(lib.mf_decode_plan_tiles(self._h))
+
+    def close(self):
+        if getattr(self, "_h", None) and getattr(self._f, "_h", None):
+            lib.mf_decode_plan_destroy(self._f._h, self._h)
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def paged_kv(k_pool, v_pool, page_table, kv_lens, *, n_kv_heads, page_size, head_dim) -> MfPagedKv:
+    """Describe torch-owned pools [n_pages, Hkv, P, D] and a [batch, stride] page table."""
+    n_pages = k_pool.shape[0]
+    return MfPagedKv(k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(), kv_lens.data_ptr(), n_pages,
+                     n_kv_heads, page_size, head_dim, page_table.shape[1], page_table.shape[0])
+
+
+def rope_tables(rope_base: float, head_dim: int, n_pos: int, first_pos: int = 0, freq_factors=None):
+    """Host RoPE cos/sin tables as numpy uint16 (f16 bits) arrays [n_pos, head_dim/2]."""
+    import numpy as np
+
+    half = head_dim // 2
+    cos = np.empty((n_pos, half), np.uint16)
+    sin = np.empty((n_pos, half), np.uint16)
+    ff = None if freq_factors is None else np.ascontiguousarray(freq_factors, np.float32)
+    st = lib.mf_rope_tables_host(rope_base, head_dim, first_pos, n_pos, None if ff is None else ff.ctypes.data,
+                                 cos.ctypes.data, sin.ctypes.data)
+    if st != MF_OK:
+        raise MetalError(st, "mf_rope_tables_host")
+    return cos, sin
+
+
+def build_decode_plan_host(kv_lens, n_kv_heads: int, max_ctas: int):
+    """Run the step planner on the host.  Returns (items [n, 8] uint32, cta_begin [n_ctas+1])."""
+    import numpy as np
+
+    lens = np.ascontiguousarray(kv_lens, dtype=np.uint32)
+    cap = lens.shape[0] * n_kv_heads + max_ctas
+    items = np.zeros((cap, 8), np.uint32)
+    cta_begin = np.zeros(max_ctas + 1, np.uint32)
+    n_ctas = u32(0)
+    n = lib.mf_decode_plan_build_host(lens.ctypes.data, lens.shape[0], n_kv_heads, max_ctas, items.ctypes.data, cap,
+                                      cta_begin.ctypes.data, C.byref(n_ctas))
+    return items[:n].copy(), cta_begin[:n_ctas.value + 1].copy()
+
+
+def align_capacity(n: int) -> int:
+    return int(lib.mf_align_capacity(n))
+
+
+def grown_capacity(current: int, required: int, max_context_len: int) -> int:
+    return int(lib.mf_grown_capacity(current, required, max_context_len))
+
+
+def prefill_split_k(kv_seq_len: int, q_seq_len: int) -> int:
+    return int(lib.mf_prefill_split_k(kv_seq_len, q_seq_len))

@@ -1,0 +1,555 @@
+// Host side of the attention operators: argument validation, stride inference
+// and routing, mirroring FlashAttentionStep / run_flash_decode of the reference
+// (src/metals/sdpa/step.rs:160-503, src/metals/flashattention/step.rs:558-1086),
+// plus the paged batched-decode entry points and the partial-merge kernel.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+#include "internal.hpp"
+
+namespace mf {
+
+mf_status launch_prefill(MfContext *ctx, const void *q, const void *k, const void *v, void *out,
+                         const SdpaPrefillSplitKParams &p);
+
+namespace {
+
+// acc [S, rows, D] f32, m/l [S, rows] -> out [rows, D] f16 (flash_prefill.metal:843-888).
+__global__ void __launch_bounds__(128)
+merge_partials_kernel(const float *__restrict__ acc, const float *__restrict__ m, const float *__restrict__ l,
+                      uint32_t n_splits, uint32_t rows, uint32_t head_dim, __half *__restrict__ out)
+{
+    const uint32_t row = blockIdx.x;
+    float mx = -1e30f;
+    for (uint32_t s = 0; s < n_splits; ++s) mx = fmaxf(mx, m[(size_t)s * rows + row]);
+    float lt = 0.f;
+    for (uint32_t s = 0; s < n_splits; ++s) {
+        const float ls = l[(size_t)s * rows + row];
+        if (ls > 0.f) lt += ls * __expf(m[(size_t)s * rows + row] - mx);
+    }
+    const float inv = ((fabsf(lt) <= 3.0e38f) && fabsf(lt) > 1e-6f) ? 1.0f / lt : 0.f;
+    for (uint32_t d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float a = 0.f;
+        for (uint32_t s = 0; s < n_splits; ++s)
+            a += acc[((size_t)s * rows + row) * head_dim + d] * __expf(m[(size_t)s * rows + row] - mx);
+        out[(size_t)row * head_dim + d] = __float2half_rn(a * inv);
+    }
+}
+
+uint32_t heads_padded(uint32_t group) { return 8 * ((group + 7) / 8); }
+
+uint64_t partial_slot_bytes(uint32_t group, uint32_t head_dim)
+{
+    return (uint64_t)heads_padded(group) * (head_dim + 2) * 4;
+}
+
+// Contiguous-cache decode through the shared kernel with an arithmetic plan.
+mf_status decode_contiguous(MfContext *ctx, const void *q, const void *k, const void *v, void *output,
+                            const MfFlashDecodeStrides *s, const SdpaParams *sp, uint32_t n_heads, uint32_t batch,
+                            uint32_t n_splits, const void *cos, const void *sin, const RopeParamsResolved *rope)
+{
+    if (!q || !k || !v || !output) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "FlashDecode: null tensor");
+    if (!s || !sp) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "FlashDecode: params");
+    const uint32_t D = sp->head_dim;
+    if (D != 64 && D != 128)
+        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "Flash Decode only supports head_dim=64 or 128, got %u", D);
+    // The Metal kernels return without writing when the row stride differs from
+    // head_dim (flash_decode.metal:165-167, 343-351); reject it instead.
+    if (sp->stride_k_s != D || sp->stride_v_s != D)
+        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "FlashDecode: K/V row stride must equal head_dim");
+    if (sp->kv_len == 0 || batch == 0 || n_heads == 0) return MF_OK;  // nothing is written (flash_decode.metal:168)
+    if (s->q_stride_h == 0 || s->k_stride_h == 0 || s->v_stride_h == 0)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "FlashDecode: zero head stride");
+    // Head mapping of run_flash_head_layout_stage (flash_decode.metal:128-132).
+    const uint32_t q_heads = std::max(1u, s->q_stride_b / s->q_stride_h);
+    const uint32_t k_heads = std::max(1u, s->k_stride_b / s->k_stride_h);
+    const uint32_t group = std::max(1u, q_heads / k_heads);
+    if (q_heads != n_heads) return fail(ctx, MF_ERR_INVALID_SHAPE, "FlashDecode: q strides imply %u heads, n_heads=%u", q_heads, n_heads);
+    if (n_heads % group != 0) return fail(ctx, MF_ERR_INVALID_SHAPE, "FlashDecode: n_heads %u not a multiple of group %u", n_heads, group);
+    const uint32_t cache_heads = n_heads / group;
+    if (s->k_stride_h % D || s->k_stride_b % D || s->v_stride_h % D || s->v_stride_b % D)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "FlashDecode: K/V strides must be multiples of head_dim");
+    if ((uint64_t)sp->kv_len * D > s->k_stride_h || (uint64_t)sp->kv_len * D > s->v_stride_h)
+        return fail(ctx, MF_ERR_INVALID_OPERATION, "FlashDecode: kv_len %u exceeds the cache capacity", sp->kv_len);
+
+    const uint32_t T = (sp->kv_len + kTileKeys - 1) / kTileKeys;
+    const uint32_t U = batch * cache_heads;
+    if (U > kMaxUniformUnits) return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "FlashDecode: %u (batch x kv head) units", U);
+    const uint64_t total = (uint64_t)U * T;
+    if (total > 0xFFFFFFFFull) return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "FlashDecode: too many tiles");
+    uint32_t span;
+    if (n_splits > 0) {
+        span = (T + n_splits - 1) / n_splits;
+    } else {
+        const uint32_t want = (uint32_t)std::min<uint64_t>(total, (uint64_t)ctx->sm_count);
+        span = (uint32_t)((total + want - 1) / want);
+    }
+    span = std::max(1u, span);
+    const uint32_t n_ctas = (uint32_t)((total + span - 1) / span);
+
+    const uint64_t slot_bytes = partial_slot_bytes(group, D);
+    const uint64_t need = kCounterRegionBytes + (uint64_t)(U + n_ctas) * slot_bytes;
+    mf_status st = ensure_scratch(ctx, need);
+    if (st != MF_OK) return st;
+
+    DecodeParams p{};
+    p.q = static_cast<const __half *>(q);
+    p.out = static_cast<__half *>(output);
+    p.k_base = const_cast<__half *>(static_cast<const __half *>(k));
+    p.v_base = const_cast<__half *>(static_cast<const __half *>(v));
+    p.counters = static_cast<uint32_t *>(ctx->scratch);
+    char *parts = static_cast<char *>(ctx->scratch) + kCounterRegionBytes;
+    const uint32_t HP = heads_padded(group);
+    p.part_acc = reinterpret_cast<float *>(parts);
+    p.part_ml = reinterpret_cast<float *>(parts + (uint64_t)(U + n_ctas) * HP * D * 4);
+    p.status = ctx->d_status;
+    p.n_heads = n_heads;
+    p.n_kv_heads = cache_heads;
+    p.group = group;
+    p.batch = batch;
+    p.k_rows_b = s->k_stride_b / D;
+    p.k_rows_h = s->k_stride_h / D;
+    p.v_rows_b = s->v_stride_b / D;
+    p.v_rows_h = s->v_stride_h / D;
+    p.uniform_kv_len = sp->kv_len;
+    p.uniform_tiles = T;
+    p.uniform_span = span;
+    p.uniform_total = (uint32_t)total;
+    p.q_stride_b = s->q_stride_b;
+    p.q_stride_h = s->q_stride_h;
+    p.out_stride_b = s->out_stride_b;
+    p.out_stride_h = s->out_stride_h;
+    p.scale_log2 = sp->scale * 1.4426950408889634f;
+    p.rope_mode = MF_ROPE_MODE_NEOX;
+    if (rope) {
+        if (!cos || !sin) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "RopeFlashDecode: cos/sin");
+        if (rope->dim != D) return fail(ctx, MF_ERR_INVALID_SHAPE, "RopeFlashDecode: rope dim %u != head_dim %u", rope->dim, D);
+        p.rope = 1;
+        p.rope_position = rope->position_offset;
+        p.cos_t = static_cast<const __half *>(cos);
+        p.sin_t = static_cast<const __half *>(sin);
+    }
+    // The tensor maps cover every row any (batch, head) can address.
+    const uint64_t k_rows = (uint64_t)(batch - 1) * p.k_rows_b + (uint64_t)(cache_heads - 1) * p.k_rows_h + p.k_rows_h;
+    const uint64_t v_rows = (uint64_t)(batch - 1) * p.v_rows_b + (uint64_t)(cache_heads - 1) * p.v_rows_h + p.v_rows_h;
+    CUtensorMap tm_k, tm_v;
+    if ((st = get_tensor_map(ctx, k, k_rows, D, kTileKeys, 64, &tm_k)) != MF_OK) return st;
+    if ((st = get_tensor_map(ctx, v, v_rows, D, kTileKeys, 64, &tm_v)) != MF_OK) return st;
+    return launch_decode(ctx, tm_k, tm_v, p, D, n_ctas);
+}
+
+struct QLayout {
+    uint32_t stride_b, stride_h, stride_m;
+};
+
+}  // namespace
+}  // namespace mf
+
+using namespace mf;
+
+extern "C" {
+
+mf_status mf_merge_partials(MfContext *ctx, const float *acc, const float *m, const float *l, uint32_t n_splits,
+                            uint32_t rows, uint32_t head_dim, void *out)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!acc || !m || !l || !out) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "merge: null input");
+    if (n_splits == 0 || rows == 0 || head_dim == 0) return MF_OK;
+    merge_partials_kernel<<<rows, 128, 0, ctx->stream>>>(acc, m, l, n_splits, rows, head_dim, static_cast<__half *>(out));
+    return check_launch(ctx, "merge_partials_kernel");
+}
+
+mf_status mf_flash_decode(MfContext *ctx, const void *q, const void *k, const void *v, void *output,
+                          const MfFlashDecodeStrides *strides, const SdpaParams *params, uint32_t n_heads,
+                          uint32_t batch, uint32_t n_splits)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    return decode_contiguous(ctx, q, k, v, output, strides, params, n_heads, batch, n_splits, nullptr, nullptr, nullptr);
+}
+
+mf_status mf_rope_flash_decode(MfContext *ctx, const void *q, const void *k, const void *v, const void *cos,
+                               const void *sin, void *output, const RopeParamsResolved *rope, const SdpaParams *params,
+                               const MfFlashDecodeStrides *strides, uint32_t n_heads, uint32_t batch)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!rope) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "RopeFlashDecode: rope params");
+    return decode_contiguous(ctx, q, k, v, output, strides, params, n_heads, batch, 0, cos, sin, rope);
+}
+
+mf_status mf_flash_prefill(MfContext *ctx, const void *q, const void *k, const void *v, void *output,
+                           const SdpaPrefillSplitKParams *params)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!q || !k || !v || !output) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "FlashPrefill: null tensor");
+    if (!params) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "FlashPrefill: params");
+    return launch_prefill(ctx, q, k, v, output, *params);
+}
+
+// run_flash_decode (src/metals/flashattention/step.rs:558-1086).
+mf_status mf_run_flash_decode(MfContext *ctx, const MfTensor *q, const MfTensor *k, const MfTensor *v,
+                              const MfTensor *output, uint32_t n_heads, uint32_t head_dim, uint32_t kv_seq_len,
+                              uint32_t q_seq_len, uint32_t kv_head_major)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    mf_status st;
+    if ((st = need_tensor(ctx, q, "q")) != MF_OK) return st;
+    if ((st = need_tensor(ctx, k, "k")) != MF_OK) return st;
+    if ((st = need_tensor(ctx, v, "v")) != MF_OK) return st;
+    if ((st = need_tensor(ctx, output, "output")) != MF_OK) return st;
+    if (!kv_head_major)
+        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "FlashAttention only supports kv_head_major=true for now");
+    const uint32_t D = head_dim;
+    auto last_contig = [&](const MfTensor *t, const char *name) -> mf_status {
+        if (t->strides[t->rank - 1] != 1)
+            return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "requires contiguous last dim for %s", name);
+        return MF_OK;
+    };
+    // n_kv_heads from the cache tensor (step.rs:430-446).
+    const uint32_t n_kv_heads = std::max<uint32_t>(1, (uint32_t)(k->rank == 3 ? k->dims[0] : k->dims[1]));
+
+    if (q_seq_len > 1) {
+        if (D != 64 && D != 128)
+            return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "Prefill only supports head_dim=64 or 128, got %u", D);
+        if ((st = last_contig(q, "q")) != MF_OK) return st;
+        if ((st = last_contig(k, "k")) != MF_OK) return st;
+        if ((st = last_contig(v, "v")) != MF_OK) return st;
+        if ((st = last_contig(output, "output")) != MF_OK) return st;
+        const uint64_t dm = (uint64_t)n_heads * D, M = q_seq_len;
+        // Q layout inference (step.rs:658-720).  A [1, M_cap, d_model] tensor is read as
+        // head-major packed over the true M, the order KvPrepFused writes.
+        QLayout ql{};
+        const uint64_t *qd = q->dims, *qs = q->strides;
+        if (q->rank == 3 && qd[0] == 1 && qd[2] == dm) {
+            ql = {n_heads * q_seq_len * D, q_seq_len * D, D};
+        } else if (q->rank == 3 && qd[0] == n_heads && qd[1] >= M && qd[2] == D) {
+            ql = {0, (uint32_t)qs[0], (uint32_t)qs[1]};
+        } else if (q->rank == 4 && qd[1] == n_heads && qd[2] >= M && qd[3] == D) {
+            ql = {(uint32_t)qs[0], (uint32_t)qs[1], (uint32_t)qs[2]};
+        } else if (q->rank == 2 && qd[0] >= M && qd[1] == dm) {
+            ql = {0, D, (uint32_t)qs[0]};
+        } else if (q->rank == 3 && qd[1] >= M && qd[2] == dm) {
+            ql = {(uint32_t)qs[0], D, (uint32_t)qs[1]};
+        } else if (q->rank == 3 && qd[0] >= M && qd[1] == n_heads && qd[2] == D) {
+            ql = {0, (uint32_t)qs[1], (uint32_t)qs[0]};
+        } else if (q->rank == 4 && qd[1] >= M && qd[2] == n_heads && qd[3] == D) {
+            ql = {(uint32_t)qs[0], (uint32_t)qs[2], (uint32_t)qs[1]};
+        } else {
+            return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "Prefill Q layout unsupported");
+        }
+        // Output layout (step.rs:722-756).
+        QLayout ol{};
+        const uint64_t *od = output->dims, *os = output->strides;
+        if (output->rank == 2 && od[0] >= M && od[1] == dm) {
+            ol = {0, D, (uint32_t)os[0]};
+        } else if (output->rank == 3 && od[1] >= M && od[2] == dm) {
+            ol = {(uint32_t)os[0], D, (uint32_t)os[1]};
+        } else if (output->rank == 3 && od[0] >= M && od[1] == n_heads && od[2] == D) {
+            ol = {0, (uint32_t)os[1], (uint32_t)os[0]};
+        } else if (output->rank == 4 && od[1] >= M && od[2] == n_heads && od[3] == D) {
+            ol = {(uint32_t)os[0], (uint32_t)os[2], (uint32_t)os[1]};
+        } else if (output->rank == 3 && od[0] == n_heads && od[1] >= M && od[2] == D) {
+            ol = {0, (uint32_t)os[0], (uint32_t)os[1]};
+        } else if (output->rank == 4 && od[1] == n_heads && od[2] >= M && od[3] == D) {
+            ol = {(uint32_t)os[0], (uint32_t)os[1], (uint32_t)os[2]};
+        } else {
+            return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "Prefill output layout unsupported");
+        }
+        SdpaPrefillSplitKParams pp{};
+        SdpaPrefillParams &b = pp.base;
+        b.kv_len = kv_seq_len;
+        b.head_dim = D;
+        b.scale = 1.0f / sqrtf((float)D);
+        if (k->rank == 4) {
+            b.k_stride_b = (uint32_t)k->strides[0];
+            b.k_stride_h = (uint32_t)k->strides[1];
+            b.stride_k_s = (uint32_t)k->strides[2];
+        } else {
+            b.k_stride_b = 0;
+            b.k_stride_h = (uint32_t)k->strides[0];
+            b.stride_k_s = (uint32_t)k->strides[1];
+        }
+        if (v->rank == 4) {
+            b.v_stride_b = (uint32_t)v->strides[0];
+            b.v_stride_h = (uint32_t)v->strides[1];
+            b.stride_v_s = (uint32_t)v->strides[2];
+        } else {
+            b.v_stride_b = 0;
+            b.v_stride_h = (uint32_t)v->strides[0];
+            b.stride_v_s = (uint32_t)v->strides[1];
+        }
+        b.query_offset = kv_seq_len > q_seq_len ? kv_seq_len - q_seq_len : 0;
+        b.q_stride_b = ql.stride_b;
+        b.q_stride_h = ql.stride_h;
+        b.q_stride_m = ql.stride_m;
+        b.out_stride_b = ol.stride_b;
+        b.out_stride_h = ol.stride_h;
+        b.out_stride_m = ol.stride_m;
+        b.group_size = std::max(1u, n_heads / n_kv_heads);
+        b.q_len = q_seq_len;
+        pp.n_heads = n_heads;
+        pp.split_k = mf_prefill_split_k(kv_seq_len, q_seq_len);
+        return launch_prefill(ctx, tensor_ptr(q), tensor_ptr(k), tensor_ptr(v), tensor_ptr(output), pp);
+    }
+
+    // Decode: strides from the resolved sizes, not from the q tensor's metadata
+    // (step.rs:995-1040).
+    if (D != 64 && D != 128)
+        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "Flash Decode only supports head_dim=64 or 128, got %u", D);
+    const uint32_t capacity = k->rank >= 2 ? (uint32_t)k->dims[1] : kv_seq_len;
+    MfFlashDecodeStrides s{};
+    s.q_stride_b = n_heads * D;
+    s.q_stride_h = D;
+    s.k_stride_b = n_kv_heads * capacity * D;
+    s.k_stride_h = capacity * D;
+    s.v_stride_b = s.k_stride_b;
+    s.v_stride_h = s.k_stride_h;
+    s.out_stride_b = n_heads * D;
+    s.out_stride_h = D;
+    SdpaParams sp{kv_seq_len, D, 1.0f / sqrtf((float)D), D, D};
+    return decode_contiguous(ctx, tensor_ptr(q), tensor_ptr(k), tensor_ptr(v), tensor_ptr(output), &s, &sp, n_heads, 1,
+                             0, nullptr, nullptr, nullptr);
+}
+
+// FlashAttentionStep dispatcher (src/metals/sdpa/step.rs:160-503).
+mf_status mf_flash_attention(MfContext *ctx, const MfTensor *q, const MfTensor *k, const MfTensor *v,
+                             const MfTensor *output, const MfFlashAttentionArgs *a, uint32_t *route_out)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!a) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "FlashAttention: args");
+    if (route_out) *route_out = 0;
+    mf_status st;
+    if ((st = need_tensor(ctx, q, "q")) != MF_OK) return st;
+    if ((st = need_tensor(ctx, k, "k")) != MF_OK) return st;
+    if ((st = need_tensor(ctx, v, "v")) != MF_OK) return st;
+    if ((st = need_tensor(ctx, output, "output")) != MF_OK) return st;
+    const uint32_t m = std::max(1u, a->m);
+    if (!a->kv_head_major)
+        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "FlashAttention only supports kv_head_major=true for now");
+    if (m == 1) {
+        // Online path only when nothing has to be masked (sdpa/step.rs:271).
+        if (a->causal && a->query_offset + 1 != a->kv_seq_len)
+            return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED,
+                        "FlashAttention m=1 but causal offset mismatch (query_offset %u, kv_seq_len %u): the reference "
+                        "takes its materialised path here, which this library does not provide",
+                        a->query_offset, a->kv_seq_len);
+        // Token-major row check (sdpa/step.rs:305-349).
+        const uint64_t dm = (uint64_t)a->n_heads * a->head_dim;
+        auto row_ok = [&](const MfTensor *t) {
+            if (t->rank == 1) return t->dims[0] == dm;
+            const uint32_t r = t->rank;
+            if (r == 2 && t->dims[0] == 1 && t->dims[1] == dm) return true;
+            return t->dims[r - 1] == dm && t->strides[r - 1] == 1 && t->strides[r - 2] == dm;
+        };
+        if (!row_ok(q) || !row_ok(output))
+            return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "FlashAttention requested but tensor layout unsupported");
+        if (route_out) *route_out = MF_ROUTE_DECODE;
+        return mf_run_flash_decode(ctx, q, k, v, output, a->n_heads, a->head_dim, a->kv_seq_len, 1, a->kv_head_major);
+    }
+    if (!a->causal)
+        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "FlashAttention prefill non-causal: materialised path not provided");
+    if (a->query_offset + m != a->kv_seq_len)
+        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "FlashAttention prefill causal offset mismatch (query_offset %u + m %u != kv_seq_len %u)",
+                    a->query_offset, m, a->kv_seq_len);
+    if (route_out) *route_out = mf_prefill_split_k(a->kv_seq_len, m) > 1 ? MF_ROUTE_PREFILL_SPLITK : MF_ROUTE_PREFILL;
+    return mf_run_flash_decode(ctx, q, k, v, output, a->n_heads, a->head_dim, a->kv_seq_len, m, a->kv_head_major);
+}
+
+// ------------------------------------------------------------------ paged ---
+
+static mf_status plan_upload(MfContext *ctx, MfDecodePlan *pl)
+{
+    pl->n_items = (uint32_t)pl->h_items.size();
+    pl->n_ctas = (uint32_t)pl->h_cta_begin.size() - 1;
+    if (pl->n_items > pl->item_capacity)
+        return fail(ctx, MF_ERR_INVALID_OPERATION, "decode plan: %u items exceed capacity %u", pl->n_items, pl->item_capacity);
+    if (pl->n_items == 0) return MF_OK;
+    std::memcpy(pl->pinned_items, pl->h_items.data(), sizeof(WorkItem) * pl->n_items);
+    std::memcpy(pl->pinned_cta_begin, pl->h_cta_begin.data(), 4 * (pl->n_ctas + 1));
+    mf_status st = check_cuda(ctx, cudaMemcpyAsync(pl->d_items, pl->pinned_items, sizeof(WorkItem) * pl->n_items,
+                                                   cudaMemcpyHostToDevice, ctx->stream), "plan upload");
+    if (st != MF_OK) return st;
+    return check_cuda(ctx, cudaMemcpyAsync(pl->d_cta_begin, pl->pinned_cta_begin, 4 * (pl->n_ctas + 1),
+                                           cudaMemcpyHostToDevice, ctx->stream), "plan upload");
+}
+
+mf_status mf_decode_plan_create(MfContext *ctx, const uint32_t *kv_lens_host, uint32_t batch, uint32_t n_heads,
+                                uint32_t n_kv_heads, uint32_t head_dim, uint32_t page_size, uint32_t max_ctas,
+                                MfDecodePlan **out)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!kv_lens_host || !out) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "decode plan: null input");
+    *out = nullptr;
+    if (batch == 0 || n_kv_heads == 0 || n_heads % n_kv_heads != 0)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "decode plan: batch %u, n_heads %u, n_kv_heads %u", batch, n_heads, n_kv_heads);
+    if (head_dim != 64 && head_dim != 128)
+        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "Flash Decode only supports head_dim=64 or 128, got %u", head_dim);
+    if (n_heads / n_kv_heads > 16)
+        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "decode plan: group size %u > 16", n_heads / n_kv_heads);
+    if (max_ctas == 0) max_ctas = (uint32_t)ctx->sm_count;
+    MfDecodePlan *pl = new MfDecodePlan();
+    pl->batch = batch;
+    pl->n_heads = n_heads;
+    pl->n_kv_heads = n_kv_heads;
+    pl->head_dim = head_dim;
+    pl->page_size = page_size;
+    pl->max_ctas = max_ctas;
+    pl->n_units = batch * n_kv_heads;
+    pl->item_capacity = pl->n_units + max_ctas;
+    pl->heads_padded = heads_padded(n_heads / n_kv_heads);
+    cudaError_t e = cudaSuccess;
+    auto ok = [&](cudaError_t r) {
+        if (e == cudaSuccess) e = r;
+    };
+    ok(cudaMallocHost(reinterpret_cast<void **>(&pl->pinned_items), sizeof(WorkItem) * pl->item_capacity));
+    ok(cudaMallocHost(reinterpret_cast<void **>(&pl->pinned_cta_begin), 4 * (max_ctas + 1)));
+    ok(cudaMalloc(reinterpret_cast<void **>(&pl->d_items), sizeof(WorkItem) * pl->item_capacity));
+    ok(cudaMalloc(reinterpret_cast<void **>(&pl->d_cta_begin), 4 * (max_ctas + 1)));
+    ok(cudaMalloc(reinterpret_cast<void **>(&pl->d_part_acc), (size_t)pl->item_capacity * pl->heads_padded * head_dim * 4));
+    ok(cudaMalloc(reinterpret_cast<void **>(&pl->d_part_ml), (size_t)pl->item_capacity * pl->heads_padded * 2 * 4));
+    ok(cudaMalloc(reinterpret_cast<void **>(&pl->d_counters), 4 * (size_t)pl->n_units));
+    if (e == cudaSuccess) ok(cudaMemsetAsync(pl->d_counters, 0, 4 * (size_t)pl->n_units, ctx->stream));
+    if (e != cudaSuccess) {
+        mf_decode_plan_destroy(ctx, pl);
+        return check_cuda(ctx, e, "decode plan allocation");
+    }
+    mf_status st = mf_decode_plan_update(ctx, pl, kv_lens_host);
+    if (st != MF_OK) {
+        mf_decode_plan_destroy(ctx, pl);
+        return st;
+    }
+    *out = pl;
+    return MF_OK;
+}
+
+mf_status mf_decode_plan_update(MfContext *ctx, MfDecodePlan *pl, const uint32_t *kv_lens_host)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!pl || !kv_lens_host) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "decode plan: null input");
+    // The pinned staging buffers may still be read by a copy queued earlier.
+    mf_status st = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+    if (st != MF_OK) return st;
+    build_decode_plan(kv_lens_host, pl->batch, pl->n_kv_heads, pl->max_ctas, pl->h_items, pl->h_cta_begin, &pl->n_units,
+                      &pl->total_tiles);
+    return plan_upload(ctx, pl);
+}
+
+void mf_decode_plan_destroy(MfContext *ctx, MfDecodePlan *pl)
+{
+    if (!pl) return;
+    if (ctx && ctx->stream) cudaStreamSynchronize(ctx->stream);
+    if (pl->pinned_items) cudaFreeHost(pl->pinned_items);
+    if (pl->pinned_cta_begin) cudaFreeHost(pl->pinned_cta_begin);
+    if (pl->d_items) cudaFree(pl->d_items);
+    if (pl->d_cta_begin) cudaFree(pl->d_cta_begin);
+    if (pl->d_part_acc) cudaFree(pl->d_part_acc);
+    if (pl->d_part_ml) cudaFree(pl->d_part_ml);
+    if (pl->d_counters) cudaFree(pl->d_counters);
+    delete pl;
+}
+
+uint32_t mf_decode_plan_build_host(const uint32_t *kv_lens_host, uint32_t batch, uint32_t n_kv_heads, uint32_t max_ctas,
+                                   uint32_t *items_out, uint32_t item_capacity, uint32_t *cta_begin_out,
+                                   uint32_t *n_ctas_out)
+{
+    if (!kv_lens_host || max_ctas == 0 || n_kv_heads == 0) return 0;
+    std::vector<WorkItem> items;
+    std::vector<uint32_t> cta_begin;
+    uint32_t n_units = 0;
+    uint64_t total = 0;
+    build_decode_plan(kv_lens_host, batch, n_kv_heads, max_ctas, items, cta_begin, &n_units, &total);
+    if (n_ctas_out) *n_ctas_out = (uint32_t)cta_begin.size() - 1;
+    if (items.size() <= item_capacity && items_out && cta_begin_out) {
+        static_assert(sizeof(WorkItem) == 32, "WorkItem is 8 x uint32");
+        if (!items.empty()) std::memcpy(items_out, items.data(), items.size() * sizeof(WorkItem));
+        std::memcpy(cta_begin_out, cta_begin.data(), cta_begin.size() * 4);
+    }
+    return (uint32_t)items.size();
+}
+
+uint32_t mf_decode_plan_ctas(const MfDecodePlan *pl) { return pl ? pl->n_ctas : 0; }
+uint32_t mf_decode_plan_items(const MfDecodePlan *pl) { return pl ? pl->n_items : 0; }
+uint64_t mf_decode_plan_tiles(const MfDecodePlan *pl) { return pl ? pl->total_tiles : 0; }
+
+static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, const MfPagedKv *c,
+                                     const MfPagedDecodeArgs *a, const uint32_t *rope_positions, float *acc, float *m,
+                                     float *l)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!pl || !c || !a) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode: null argument");
+    if (!c->k_pool || !c->v_pool || !c->page_table || !c->kv_lens || !a->q)
+        return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode: null tensor");
+    if (!acc && !a->out) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode: output");
+    if (a->append && (!a->k || !a->v)) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode: k/v of the new token");
+    if (a->rope && (!a->cos || !a->sin)) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode: cos/sin");
+    if (a->rope_mode > 1) return fail(ctx, MF_ERR_INVALID_OPERATION, "paged decode: rope_mode %u", a->rope_mode);
+    if (c->batch != pl->batch || c->n_kv_heads != pl->n_kv_heads || c->head_dim != pl->head_dim ||
+        a->n_heads != pl->n_heads || c->page_size != pl->page_size)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "paged decode: cache geometry differs from the plan");
+    const uint32_t P = c->page_size;
+    if (P < 8 || P > 256 || (P & (P - 1)) != 0)
+        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "paged decode: page_size %u (power of two in 8..256)", P);
+    if ((uint64_t)c->n_pages * c->n_kv_heads * P > 0x7FFFFFFFull)
+        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "paged decode: pool has too many rows");
+    if (pl->n_items == 0) return MF_OK;
+    const uint32_t D = c->head_dim;
+    DecodeParams p{};
+    p.q = static_cast<const __half *>(a->q);
+    p.k_new = static_cast<const __half *>(a->k);
+    p.v_new = static_cast<const __half *>(a->v);
+    p.q_rot = static_cast<__half *>(a->q_rot);
+    p.out = static_cast<__half *>(a->out);
+    p.cos_t = static_cast<const __half *>(a->cos);
+    p.sin_t = static_cast<const __half *>(a->sin);
+    p.k_base = static_cast<__half *>(c->k_pool);
+    p.v_base = static_cast<__half *>(c->v_pool);
+    p.page_table = c->page_table;
+    p.kv_lens = c->kv_lens;
+    p.rope_positions = rope_positions;
+    p.items = pl->d_items;
+    p.cta_item_begin = pl->d_cta_begin;
+    p.part_acc = pl->d_part_acc;
+    p.part_ml = pl->d_part_ml;
+    p.counters = pl->d_counters;
+    p.out_acc = acc;
+    p.out_m = m;
+    p.out_l = l;
+    p.status = ctx->d_status;
+    p.n_heads = a->n_heads;
+    p.n_kv_heads = c->n_kv_heads;
+    p.group = a->n_heads / c->n_kv_heads;
+    p.page_size = P;
+    p.pt_stride = c->page_table_stride;
+    p.batch = c->batch;
+    p.rope = a->rope;
+    p.rope_mode = a->rope_mode;
+    p.append = a->append;
+    p.q_stride_b = a->n_heads * D;
+    p.q_stride_h = D;
+    p.out_stride_b = a->n_heads * D;
+    p.out_stride_h = D;
+    p.knew_stride_b = c->n_kv_heads * D;
+    p.scale_log2 = a->scale * 1.4426950408889634f;
+    CUtensorMap tm_k, tm_v;
+    const uint64_t rows = (uint64_t)c->n_pages * c->n_kv_heads * P;
+    const uint32_t box_rows = std::min(P, kTileKeys);
+    mf_status st;
+    if ((st = get_tensor_map(ctx, c->k_pool, rows, D, box_rows, 64, &tm_k)) != MF_OK) return st;
+    if ((st = get_tensor_map(ctx, c->v_pool, rows, D, box_rows, 64, &tm_v)) != MF_OK) return st;
+    return launch_decode(ctx, tm_k, tm_v, p, D, pl->n_ctas);
+}
+
+mf_status mf_paged_decode(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv *cache, const MfPagedDecodeArgs *args)
+{
+    return paged_decode_common(ctx, plan, cache, args, nullptr, nullptr, nullptr, nullptr);
+}
+
+mf_status mf_paged_decode_partial(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv *cache,
+                                  const MfPagedDecodeArgs *args, const uint32_t *rope_positions, float *acc, float *m,
+                                  float *l)
+{
+    if (ctx && (!acc || !m || !l)) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode partial: acc/m/l");
+    return paged_decode_common(ctx, plan, cache, args, rope_positions, acc, m, l);
+}
+
+}  // extern "C"

@@ -1,0 +1,669 @@
+// GQA flash-decode over a contiguous or paged F16 KV cache for sm_100a, with the
+// append of the step's new token and the RoPE of q fused in.
+//
+// Replaces flash_decode_warp_tiled_m1_half2/half4 (flash_decode.metal:146-490),
+// run_flash_head_layout_stage (:107-144) and, when rope/append are set, RopeStage
+// (rope_common.metal:27-63) and the K/V part of kv_prep_fused_kernel_f16
+// (kv_prep_fused.metal:89-122).  The arithmetic contract kept from those kernels:
+// q and the appended k are rounded to f16 after RoPE, scores are f16 x f16
+// products accumulated in f32 and multiplied by `scale`, the running max starts
+// at -1e30, non-finite scores count as -1e30, accumulation is f32, and the result
+// is acc/l (acc when |l| <= 1e-6), non-finite -> 0, one rounding to f16.
+//
+// Shape of the kernel (not the reference's): the reference runs one threadgroup
+// per query head and walks all keys serially, so K/V are read once per QUERY
+// head.  Here one CTA processes spans of 64-key tiles of one (sequence, kv head)
+// unit for all G query heads of the group at once, so K/V cross HBM once per KV
+// head.  A producer warp streams K/V tiles into a multi-stage shared-memory ring
+// with TMA tensor loads (one box per page and 64-column half, 128-byte swizzle)
+// signalled through mbarriers; four consumer warps take 16 keys each, compute
+// S^T = K Q^T and O^T += V^T P^T on mma.sync m16n8k16 (keys / dims on the M side,
+// the query group on the 8-wide N side), keep online-softmax state in registers
+// (row max by warp shuffles) and combine at the end of the span.  Spans that do
+// not cover a whole unit write unnormalised f32 partials; the CTA that finishes a
+// unit last (an atomic ticket, no waiting) merges them with the log-sum-exp rule
+// of flash_prefill.metal:843-888.
+#include "internal.hpp"
+#include "ptx.cuh"
+
+namespace mf {
+
+namespace {
+
+constexpr uint32_t kConsumerWarps = 4;
+constexpr uint32_t kConsumerThreads = kConsumerWarps * 32;
+constexpr uint32_t kThreads = kConsumerThreads + 32;
+constexpr float kNegSentinel = -1e30f;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per barrier wait
+constexpr float kLn2 = 0.6931471805599453f;
+
+template <int D, int NT, int STAGES>
+struct Smem {
+    static constexpr uint32_t kHP = 8 * NT;                    // padded heads per group
+    static constexpr uint32_t kTileBytes = kTileKeys * D * 2;  // one K or V tile
+    static constexpr uint32_t kStageBytes = 2 * kTileBytes;
+    static constexpr uint32_t kHalfBytes = kTileKeys * 128;  // one 64-column half of a tile
+    static constexpr uint32_t kCombStride = D + 4;           // floats per head row
+    static constexpr uint32_t kQStride = D + 8;              // halves per head row
+    static constexpr uint32_t kOffComb = STAGES * kStageBytes;
+    static constexpr uint32_t kCombBytes = kConsumerWarps * kHP * kCombStride * 4;
+    static constexpr uint32_t kOffQ = kOffComb + kCombBytes;
+    static constexpr uint32_t kQBytes = kHP * kQStride * 2;
+    static constexpr uint32_t kOffMl = kOffQ + kQBytes;
+    static constexpr uint32_t kMlBytes = kConsumerWarps * kHP * 2 * 4;
+    static constexpr uint32_t kOffMerge = kOffMl + kMlBytes;
+    static constexpr uint32_t kMergeBytes = kHP * 2 * 4;
+    static constexpr uint32_t kOffBar = kOffMerge + kMergeBytes;
+    static constexpr uint32_t kBarBytes = 2 * STAGES * 8;
+    static constexpr uint32_t kOffFlags = kOffBar + kBarBytes;
+    static constexpr uint32_t kTotal = kOffFlags + 16;
+    static constexpr uint32_t kDynamic = kTotal + 1024;  // slack for 1024-byte alignment
+};
+
+// Iterates the work items of one CTA, from the explicit plan or, for uniform
+// lengths, computed from the CTA index.
+struct ItemCursor {
+    const DecodeParams &p;
+    uint32_t idx, end;       // explicit mode
+    uint32_t flat, flat_end; // uniform mode
+    __device__ ItemCursor(const DecodeParams &pp, uint32_t cta) : p(pp)
+    {
+        if (p.items) {
+            idx = p.cta_item_begin[cta];
+            end = p.cta_item_begin[cta + 1];
+            flat = flat_end = 0;
+        } else {
+            idx = end = 0;
+            flat = cta * p.uniform_span;
+            flat_end = min(p.uniform_total, flat + p.uniform_span);
+        }
+    }
+    __device__ bool next(WorkItem &it)
+    {
+        if (p.items) {
+            if (idx >= end) return false;
+            it = p.items[idx++];
+            return true;
+        }
+        if (flat >= flat_end) return false;
+        const uint32_t T = p.uniform_tiles;
+        const uint32_t u = flat / T;
+        const uint32_t tb = flat - u * T;
+        const uint32_t te = min(T, tb + (flat_end - flat));
+        const uint32_t c_first = (u * T) / p.uniform_span;
+        const uint32_t c_last = ((u + 1) * T - 1) / p.uniform_span;
+        it.seq = u / p.n_kv_heads;
+        it.kvh = u - it.seq * p.n_kv_heads;
+        it.tile_begin = tb;
+        it.tile_end = te;
+        it.unit = u;
+        it.n_parts = c_last - c_first + 1;
+        it.first_slot = u + c_first;
+        it.slot = u + flat / p.uniform_span;
+        flat += te - tb;
+        return true;
+    }
+};
+
+__device__ __forceinline__ uint32_t kv_len_of(const DecodeParams &p, uint32_t seq)
+{
+    return p.kv_lens ? p.kv_lens[seq] : p.uniform_kv_len;
+}
+
+// Byte offset of (row, 16-byte chunk `c16` of the D*2-byte row) inside a K or V
+// tile laid out [half][64 rows][128 B] with the TMA 128-byte swizzle.
+__device__ __forceinline__ uint32_t tile_off(uint32_t row, uint32_t c16)
+{
+    return (c16 >> 3) * (kTileKeys * 128) + row * 128 + (((c16 & 7) ^ (row & 7)) << 4);
+}
+
+// One RoPE'd element pair, rounded to f16 exactly as kv_prep_fused.metal:74-82.
+__device__ __forceinline__ void rope_pair(float xi, float xj, float c, float s, __half &oi,
+                                          __half &oj)
+{
+    oi = __float2half_rn(__fsub_rn(__fmul_rn(xi, c), __fmul_rn(xj, s)));
+    oj = __float2half_rn(__fadd_rn(__fmul_rn(xj, c), __fmul_rn(xi, s)));
+}
+
+template <int D, int NT, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+              const DecodeParams p)
+{
+    using S = Smem<D, NT, STAGES>;
+    constexpr uint32_t HP = S::kHP;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    const uint32_t tid = threadIdx.x;
+    const uint32_t warp = tid >> 5;
+    const uint32_t lane = tid & 31;
+    const uint32_t bar_full = smem_base + S::kOffBar;
+    const uint32_t bar_empty = bar_full + STAGES * 8;
+    volatile uint32_t *flags = reinterpret_cast<volatile uint32_t *>(smem + S::kOffFlags);
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + s * 8, 1);
+            mbar_init(bar_empty + s * 8, kConsumerWarps);
+        }
+        flags[0] = 0;  // abort
+        flags[1] = 0;  // merge ticket broadcast
+        mbar_fence_init();
+        fence_proxy_async();
+    }
+    __syncthreads();
+
+    const uint32_t rows_per_box = p.page_table ? min(p.page_size, kTileKeys) : kTileKeys;
+    const uint32_t boxes_per_tile = kTileKeys / rows_per_box;
+
+    if (warp == kConsumerWarps) {
+        // ------------------------------------------------------------ producer ---
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_k);
+            tma_prefetch_desc(&tm_v);
+        }
+        const uint64_t policy = l2_policy_evict_first();
+        ItemCursor cur(p, blockIdx.x);
+        WorkItem it;
+        uint32_t stage = 0, phase = 0, issued = 0;
+        while (cur.next(it)) {
+            const uint32_t L = kv_len_of(p, it.seq);
+            // Row of this lane's box inside the K / V tensor for a given tile.
+            auto box_rows = [&](uint32_t tile, int32_t &rk, int32_t &rv) -> bool {
+                const uint32_t tok = tile * kTileKeys + lane * rows_per_box;
+                if (lane >= boxes_per_tile) return false;
+                if (p.page_table) {
+                    if (tok >= L) return false;
+                    const uint32_t page = __ldg(p.page_table + (size_t)it.seq * p.pt_stride + tok / p.page_size);
+                    const uint32_t row = (page * p.n_kv_heads + it.kvh) * p.page_size + tok % p.page_size;
+                    rk = rv = static_cast<int32_t>(row);
+                } else {
+                    rk = static_cast<int32_t>(it.seq * p.k_rows_b + it.kvh * p.k_rows_h + tok);
+                    rv = static_cast<int32_t>(it.seq * p.v_rows_b + it.kvh * p.v_rows_h + tok);
+                }
+                return true;
+            };
+            int32_t rk = 0, rv = 0, nrk = 0, nrv = 0;
+            bool valid = box_rows(it.tile_begin, rk, rv), nvalid = false;
+            for (uint32_t t = it.tile_begin; t < it.tile_end; ++t) {
+                // Look the next tile's page up before blocking on the ring.
+                if (t + 1 < it.tile_end) nvalid = box_rows(t + 1, nrk, nrv);
+                if (!flags[0] && !mbar_wait_bounded(bar_empty + stage * 8, phase ^ 1, kWaitLimitNs)) {
+                    flags[0] = 1;
+                    atomicOr(p.status, 1u);
+                }
+                const uint32_t n_valid = __popc(__ballot_sync(0xffffffffu, valid));
+                const uint32_t full = bar_full + stage * 8;
+                if (lane == 0) mbar_arrive_expect_tx(full, n_valid * rows_per_box * D * 4);
+                __syncwarp();
+                if (valid) {
+                    const uint32_t dst_k = smem_base + stage * S::kStageBytes + lane * rows_per_box * 128;
+                    const uint32_t dst_v = dst_k + S::kTileBytes;
+#pragma unroll
+                    for (int h = 0; h < D / 64; ++h) {
+                        tma_load_2d_hint(dst_k + h * S::kHalfBytes, &tm_k, h * 64, rk, full, policy);
+                        tma_load_2d_hint(dst_v + h * S::kHalfBytes, &tm_v, h * 64, rv, full, policy);
+                    }
+                }
+                ++issued;
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+                valid = nvalid;
+                rk = nrk;
+                rv = nrv;
+            }
+        }
+        // After an abort the consumers no longer wait for the ring: make sure our
+        // own copies have landed before the CTA gives its shared memory back.
+        if (flags[0]) {
+            const uint32_t n = issued < (uint32_t)STAGES ? issued : (uint32_t)STAGES;
+            for (uint32_t i = 0; i < n; ++i) {
+                const uint32_t s = (stage + STAGES - 1 - i) % STAGES;
+                const uint32_t ph = (s < stage) ? phase : (phase ^ 1);
+                (void)mbar_wait_bounded(bar_full + s * 8, ph, kWaitLimitNs);
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers ---
+    float *comb = reinterpret_cast<float *>(smem + S::kOffComb);
+    __half *q_s = reinterpret_cast<__half *>(smem + S::kOffQ);
+    float *ml_s = reinterpret_cast<float *>(smem + S::kOffMl);
+    float *merge_s = reinterpret_cast<float *>(smem + S::kOffMerge);
+    const uint32_t G = p.group;
+    const uint32_t half_d = D / 2;
+
+    ItemCursor cur(p, blockIdx.x);
+    WorkItem it;
+    uint32_t stage = 0, phase = 0;
+    while (cur.next(it)) {
+        const uint32_t L = kv_len_of(p, it.seq);
+        const uint32_t n_tiles = (L + kTileKeys - 1) / kTileKeys;
+        const uint32_t pos = p.rope_positions ? p.rope_positions[it.seq]
+                                              : (p.kv_lens ? L - 1 : p.rope_position);
+        const __half *cos_row = p.cos_t + (size_t)pos * half_d;
+        const __half *sin_row = p.sin_t + (size_t)pos * half_d;
+
+        // ---- q (optionally roped, rounded to f16) -> shared memory -----------------
+        named_bar_sync(1, kConsumerThreads);  // previous item is done with q_s / comb
+        for (uint32_t e = tid; e < HP * half_d; e += kConsumerThreads) {
+            const uint32_t g = e / half_d;
+            const uint32_t pr = e - g * half_d;
+            uint32_t di, dj;
+            if (p.rope_mode == MF_ROPE_MODE_NORMAL) {
+                di = 2 * pr;
+                dj = di + 1;
+            } else {
+                di = pr;
+                dj = pr + half_d;
+            }
+            __half oi = __float2half_rn(0.f), oj = oi;
+            if (g < G) {
+                const uint32_t h = it.kvh * G + g;
+                const __half *src = p.q + (size_t)it.seq * p.q_stride_b + (size_t)h * p.q_stride_h;
+                oi = src[di];
+                oj = src[dj];
+                if (p.rope) {
+                    rope_pair(__half2float(oi), __half2float(oj), __half2float(cos_row[pr]),
+                              __half2float(sin_row[pr]), oi, oj);
+                }
+                if (p.q_rot && it.tile_begin == 0) {
+                    __half *dst = p.q_rot + (size_t)it.seq * p.q_stride_b + (size_t)h * p.q_stride_h;
+                    dst[di] = oi;
+                    dst[dj] = oj;
+                }
+            }
+            q_s[g * S::kQStride + di] = oi;
+            q_s[g * S::kQStride + dj] = oj;
+        }
+        named_bar_sync(1, kConsumerThreads);
+
+        // B fragments of Q^T: [k = 16 dims][n = 8 heads] per k-step and n-tile.
+        uint32_t bq[NT][D / 16][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const __half *row = q_s + (nt * 8 + (lane >> 2)) * S::kQStride + 2 * (lane & 3);
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                bq[nt][ks][0] = *reinterpret_cast<const uint32_t *>(row + ks * 16);
+                bq[nt][ks][1] = *reinterpret_cast<const uint32_t *>(row + ks * 16 + 8);
+            }
+        }
+
+        float m_run[NT][2], l_run[NT][2];
+        float o[NT][D / 16][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            m_run[nt][0] = m_run[nt][1] = kNegSentinel;
+            l_run[nt][0] = l_run[nt][1] = 0.f;
+#pragma unroll
+            for (int mt = 0; mt < D / 16; ++mt) o[nt][mt][0] = o[nt][mt][1] = o[nt][mt][2] = o[nt][mt][3] = 0.f;
+        }
+
+        for (uint32_t t = it.tile_begin; t < it.tile_end; ++t) {
+            if (!flags[0] && !mbar_wait_bounded(bar_full + stage * 8, phase, kWaitLimitNs)) {
+                flags[0] = 1;
+                atomicOr(p.status, 2u);
+            }
+            uint8_t *k_tile = smem + stage * S::kStageBytes;
+            uint8_t *v_tile = k_tile + S::kTileBytes;
+            const uint32_t k_addr = smem_base + stage * S::kStageBytes;
+            const uint32_t v_addr = k_addr + S::kTileBytes;
+            const uint32_t key0 = t * kTileKeys;
+            const bool last_tile = (t + 1 == n_tiles);
+
+            if (last_tile) {
+                // The tile that holds position L-1: splice in the token appended by
+                // this step (and store it to the cache), then clear V rows past L so
+                // that stale or never-written rows cannot leak NaNs through 0 * NaN.
+                const uint32_t r_new = (L - 1) - key0;
+                if (p.append) {
+                    size_t krow, vrow;
+                    if (p.page_table) {
+                        const uint32_t page = p.page_table[(size_t)it.seq * p.pt_stride + (L - 1) / p.page_size];
+                        krow = vrow = ((size_t)page * p.n_kv_heads + it.kvh) * p.page_size + (L - 1) % p.page_size;
+                    } else {
+                        krow = (size_t)it.seq * p.k_rows_b + (size_t)it.kvh * p.k_rows_h + (L - 1);
+                        vrow = (size_t)it.seq * p.v_rows_b + (size_t)it.kvh * p.v_rows_h + (L - 1);
+                    }
+                    const __half *ks = p.k_new + (size_t)it.seq * p.knew_stride_b + (size_t)it.kvh * D;
+                    const __half *vs = p.v_new + (size_t)it.seq * p.knew_stride_b + (size_t)it.kvh * D;
+                    for (uint32_t pr = tid; pr < half_d; pr += kConsumerThreads) {
+                        uint32_t di, dj;
+                        if (p.rope_mode == MF_ROPE_MODE_NORMAL) {
+                            di = 2 * pr;
+                            dj = di + 1;
+                        } else {
+                            di = pr;
+                            dj = pr + half_d;
+                        }
+                        __half oi = ks[di], oj = ks[dj];
+                        if (p.rope) {
+                            rope_pair(__half2float(oi), __half2float(oj), __half2float(cos_row[pr]),
+                                      __half2float(sin_row[pr]), oi, oj);
+                        }
+                        p.k_base[krow * D + di] = oi;
+                        p.k_base[krow * D + dj] = oj;
+                        *reinterpret_cast<__half *>(k_tile + tile_off(r_new, di >> 3) + (di & 7) * 2) = oi;
+                        *reinterpret_cast<__half *>(k_tile + tile_off(r_new, dj >> 3) + (dj & 7) * 2) = oj;
+                    }
+                    for (uint32_t d = tid; d < (uint32_t)D; d += kConsumerThreads) {
+                        const __half x = vs[d];
+                        p.v_base[vrow * D + d] = x;
+                        *reinterpret_cast<__half *>(v_tile + tile_off(r_new, d >> 3) + (d & 7) * 2) = x;
+                    }
+                }
+                const uint32_t first_dead = L - key0;  // 1..64
+                const uint32_t n_chunks = (kTileKeys - first_dead) * (D / 8);
+                for (uint32_t c = tid; c < n_chunks; c += kConsumerThreads) {
+                    const uint32_t row = first_dead + c / (D / 8);
+                    const uint32_t c16 = c % (D / 8);
+                    *reinterpret_cast<uint4 *>(v_tile + tile_off(row, c16)) = make_uint4(0, 0, 0, 0);
+                }
+                fence_proxy_async();  // order these writes before the ring's next TMA refill
+                named_bar_sync(2, kConsumerThreads);
+            }
+
+            const uint32_t wkey0 = key0 + warp * 16;
+            if (wkey0 < L) {
+                // ---- S^T (16 keys x 8*NT heads) = K_tile Q^T ---------------------------
+                float c[NT][4];
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.f;
+                {
+                    const uint32_t row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+                    for (int ks = 0; ks < D / 16; ++ks) {
+                        uint32_t a[4];
+                        ldmatrix_x4(a, k_addr + tile_off(row, 2 * ks + (lane >> 4)));
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) mma_m16n8k16(c[nt], a, bq[nt][ks][0], bq[nt][ks][1]);
+                    }
+                }
+                // ---- online softmax over this warp's 16 keys ---------------------------
+                const uint32_t kr0 = wkey0 + (lane >> 2);
+                const bool dead0 = kr0 >= L, dead1 = kr0 + 8 >= L;
+                uint32_t bp[NT][2];
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    float s0 = c[nt][0] * p.scale_log2, s1 = c[nt][1] * p.scale_log2;
+                    float s2 = c[nt][2] * p.scale_log2, s3 = c[nt][3] * p.scale_log2;
+                    if (dead0 || !(fabsf(s0) <= 3.0e38f)) s0 = kNegSentinel;
+                    if (dead0 || !(fabsf(s1) <= 3.0e38f)) s1 = kNegSentinel;
+                    if (dead1 || !(fabsf(s2) <= 3.0e38f)) s2 = kNegSentinel;
+                    if (dead1 || !(fabsf(s3) <= 3.0e38f)) s3 = kNegSentinel;
+                    float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
+#pragma unroll
+                    for (int off = 4; off <= 16; off <<= 1) {
+                        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+                        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+                    }
+                    const float mn0 = fmaxf(m_run[nt][0], mx0), mn1 = fmaxf(m_run[nt][1], mx1);
+                    const float a0 = fast_exp2(m_run[nt][0] - mn0), a1 = fast_exp2(m_run[nt][1] - mn1);
+                    m_run[nt][0] = mn0;
+                    m_run[nt][1] = mn1;
+                    // Masked keys get weight 0 even when the whole row so far is masked
+                    // (then s - m would be 0, not -inf).
+                    const float p0 = dead0 ? 0.f : fast_exp2(s0 - mn0);
+                    const float p1 = dead0 ? 0.f : fast_exp2(s1 - mn1);
+                    const float p2 = dead1 ? 0.f : fast_exp2(s2 - mn0);
+                    const float p3 = dead1 ? 0.f : fast_exp2(s3 - mn1);
+                    l_run[nt][0] = l_run[nt][0] * a0 + (p0 + p2);
+                    l_run[nt][1] = l_run[nt][1] * a1 + (p1 + p3);
+#pragma unroll
+                    for (int mt = 0; mt < D / 16; ++mt) {
+                        o[nt][mt][0] *= a0;
+                        o[nt][mt][1] *= a1;
+                        o[nt][mt][2] *= a0;
+                        o[nt][mt][3] *= a1;
+                    }
+                    bp[nt][0] = movmatrix_trans(pack_f16x2(p0, p1));
+                    bp[nt][1] = movmatrix_trans(pack_f16x2(p2, p3));
+                }
+                // ---- O^T (D dims x heads) += V_tile^T P^T ------------------------------
+                {
+                    const uint32_t row = warp * 16 + (lane & 7) + (lane >> 4) * 8;
+#pragma unroll
+                    for (int mt = 0; mt < D / 16; ++mt) {
+                        uint32_t a[4];
+                        ldmatrix_x4_trans(a, v_addr + tile_off(row, 2 * mt + ((lane >> 3) & 1)));
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) mma_m16n8k16(o[nt][mt], a, bp[nt][0], bp[nt][1]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + stage * 8);
+            if (++stage == STAGES) {
+                stage = 0;
+                phase ^= 1;
+            }
+        }
+
+        // ---- combine the four warps' states ------------------------------------------
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+            for (int off = 4; off <= 16; off <<= 1) {
+                l_run[nt][0] += __shfl_xor_sync(0xffffffffu, l_run[nt][0], off);
+                l_run[nt][1] += __shfl_xor_sync(0xffffffffu, l_run[nt][1], off);
+            }
+            if (lane < 4) {
+                float *dst = ml_s + ((warp * HP) + nt * 8 + 2 * lane) * 2;
+                dst[0] = m_run[nt][0];
+                dst[1] = l_run[nt][0];
+                dst[2] = m_run[nt][1];
+                dst[3] = l_run[nt][1];
+            }
+        }
+        named_bar_sync(1, kConsumerThreads);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const uint32_t h0 = nt * 8 + 2 * (lane & 3);
+            float ma0 = kNegSentinel, ma1 = kNegSentinel;
+#pragma unroll
+            for (uint32_t w = 0; w < kConsumerWarps; ++w) {
+                ma0 = fmaxf(ma0, ml_s[(w * HP + h0) * 2]);
+                ma1 = fmaxf(ma1, ml_s[(w * HP + h0 + 1) * 2]);
+            }
+            const float f0 = fast_exp2(m_run[nt][0] - ma0), f1 = fast_exp2(m_run[nt][1] - ma1);
+            float *c0 = comb + (warp * HP + h0) * S::kCombStride;
+            float *c1 = c0 + S::kCombStride;
+#pragma unroll
+            for (int mt = 0; mt < D / 16; ++mt) {
+                const uint32_t d0 = mt * 16 + (lane >> 2);
+                c0[d0] = o[nt][mt][0] * f0;
+                c1[d0] = o[nt][mt][1] * f1;
+                c0[d0 + 8] = o[nt][mt][2] * f0;
+                c1[d0 + 8] = o[nt][mt][3] * f1;
+            }
+        }
+        named_bar_sync(2, kConsumerThreads);
+
+        const bool direct = (it.n_parts == 1);
+        const bool partial_out = (p.out_acc != nullptr);
+        for (uint32_t e = tid; e < HP * D; e += kConsumerThreads) {
+            const uint32_t g = e / D, d = e - g * D;
+            float m_all = kNegSentinel;
+#pragma unroll
+            for (uint32_t w = 0; w < kConsumerWarps; ++w) m_all = fmaxf(m_all, ml_s[(w * HP + g) * 2]);
+            float l_all = 0.f, acc = 0.f;
+#pragma unroll
+            for (uint32_t w = 0; w < kConsumerWarps; ++w) {
+                l_all += ml_s[(w * HP + g) * 2 + 1] * fast_exp2(ml_s[(w * HP + g) * 2] - m_all);
+                acc += comb[(w * HP + g) * S::kCombStride + d];
+            }
+            const uint32_t h = it.kvh * G + g;
+            if (!direct) {
+                p.part_acc[((size_t)it.slot * HP + g) * D + d] = acc;
+                if (d == 0) {
+                    p.part_ml[((size_t)it.slot * HP + g) * 2] = m_all * kLn2;
+                    p.part_ml[((size_t)it.slot * HP + g) * 2 + 1] = l_all;
+                }
+            } else if (g < G) {
+                if (partial_out) {
+                    p.out_acc[((size_t)it.seq * p.n_heads + h) * D + d] = acc;
+                    if (d == 0) {
+                        p.out_m[(size_t)it.seq * p.n_heads + h] = m_all * kLn2;
+                        p.out_l[(size_t)it.seq * p.n_heads + h] = l_all;
+                    }
+                } else {
+                    const bool ok = (fabsf(l_all) <= 3.0e38f) && fabsf(l_all) > 1e-6f;
+                    float r = ok ? acc / l_all : acc;
+                    if (!(fabsf(r) <= 3.0e38f)) r = 0.f;
+                    p.out[(size_t)it.seq * p.out_stride_b + (size_t)h * p.out_stride_h + d] = __float2half_rn(r);
+                }
+            }
+        }
+        if (direct) continue;
+
+        // ---- ticket: the CTA that completes the unit merges its partials ---------------
+        __threadfence();
+        named_bar_sync(1, kConsumerThreads);
+        if (tid == 0) {
+            const uint32_t old = atomicAdd(p.counters + it.unit, 1u);
+            const uint32_t last = (old + 1 == it.n_parts) ? 1u : 0u;
+            if (last) p.counters[it.unit] = 0;  // ready for the next launch
+            flags[1] = last;
+        }
+        named_bar_sync(2, kConsumerThreads);
+        if (!flags[1]) continue;
+        __threadfence();
+        if (tid < HP) {
+            float mx = kNegSentinel;
+            for (uint32_t s = 0; s < it.n_parts; ++s)
+                mx = fmaxf(mx, __ldcg(p.part_ml + ((size_t)(it.first_slot + s) * HP + tid) * 2));
+            float lt = 0.f;
+            for (uint32_t s = 0; s < it.n_parts; ++s) {
+                const float ms = __ldcg(p.part_ml + ((size_t)(it.first_slot + s) * HP + tid) * 2);
+                const float ls = __ldcg(p.part_ml + ((size_t)(it.first_slot + s) * HP + tid) * 2 + 1);
+                if (ls > 0.f) lt += ls * __expf(ms - mx);
+            }
+            merge_s[tid * 2] = mx;
+            merge_s[tid * 2 + 1] = lt;
+        }
+        named_bar_sync(1, kConsumerThreads);
+        for (uint32_t e = tid; e < HP * D; e += kConsumerThreads) {
+            const uint32_t g = e / D, d = e - g * D;
+            if (g >= G) continue;
+            const float mx = merge_s[g * 2], lt = merge_s[g * 2 + 1];
+            float acc = 0.f;
+            for (uint32_t s = 0; s < it.n_parts; ++s) {
+                const size_t sl = it.first_slot + s;
+                const float ms = __ldcg(p.part_ml + (sl * HP + g) * 2);
+                acc += __ldcg(p.part_acc + (sl * HP + g) * D + d) * __expf(ms - mx);
+            }
+            const uint32_t h = it.kvh * G + g;
+            if (partial_out) {
+                p.out_acc[((size_t)it.seq * p.n_heads + h) * D + d] = acc;
+                if (d == 0) {
+                    p.out_m[(size_t)it.seq * p.n_heads + h] = mx;
+                    p.out_l[(size_t)it.seq * p.n_heads + h] = lt;
+                }
+            } else {
+                const bool ok = (fabsf(lt) <= 3.0e38f) && fabsf(lt) > 1e-6f;
+                float r = ok ? acc / lt : 0.f;  // merge rule: flash_prefill.metal:861
+                if (!(fabsf(r) <= 3.0e38f)) r = 0.f;
+                p.out[(size_t)it.seq * p.out_stride_b + (size_t)h * p.out_stride_h + d] = __float2half_rn(r);
+            }
+        }
+    }
+}
+
+template <int D, int NT, int STAGES>
+mf_status launch_one(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap &tm_v,
+                     const DecodeParams &p, uint32_t n_ctas)
+{
+    using S = Smem<D, NT, STAGES>;
+    static bool configured[64] = {};
+    auto kern = decode_kernel<D, NT, STAGES>;
+    if (ctx->device < 64 && !configured[ctx->device]) {
+        mf_status st = check_cuda(
+            ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic),
+            "cudaFuncSetAttribute(decode)");
+        if (st != MF_OK) return st;
+        configured[ctx->device] = true;
+    }
+    kern<<<n_ctas, kThreads, S::kDynamic, ctx->stream>>>(tm_k, tm_v, p);
+    return check_launch(ctx, "decode_kernel");
+}
+
+}  // namespace
+
+mf_status launch_decode(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap &tm_v,
+                        const DecodeParams &p, uint32_t head_dim, uint32_t n_ctas)
+{
+    const uint32_t nt = (p.group + 7) / 8;
+    if (nt > 2) return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "decode: group size %u > 16", p.group);
+    if (head_dim == 128) {
+        return nt == 1 ? launch_one<128, 1, 6>(ctx, tm_k, tm_v, p, n_ctas)
+                       : launch_one<128, 2, 5>(ctx, tm_k, tm_v, p, n_ctas);
+    }
+    if (head_dim == 64) {
+        return nt == 1 ? launch_one<64, 1, 8>(ctx, tm_k, tm_v, p, n_ctas)
+                       : launch_one<64, 2, 8>(ctx, tm_k, tm_v, p, n_ctas);
+    }
+    return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "Flash Decode only supports head_dim=64 or 128, got %u",
+                head_dim);
+}
+
+void build_decode_plan(const uint32_t *kv_lens, uint32_t batch, uint32_t n_kv_heads,
+                       uint32_t max_ctas, std::vector<WorkItem> &items,
+                       std::vector<uint32_t> &cta_begin, uint32_t *n_units, uint64_t *total_tiles)
+{
+    items.clear();
+    cta_begin.clear();
+    uint64_t total = 0;
+    for (uint32_t b = 0; b < batch; ++b) total += (uint64_t)((kv_lens[b] + kTileKeys - 1) / kTileKeys) * n_kv_heads;
+    *total_tiles = total;
+    *n_units = batch * n_kv_heads;
+    if (total == 0) {
+        cta_begin.push_back(0);
+        return;
+    }
+    const uint32_t n_ctas = (uint32_t)(total < max_ctas ? total : max_ctas);
+    const uint64_t base = total / n_ctas, rem = total % n_ctas;
+    uint32_t cta = 0;
+    uint64_t room = base + (0 < rem ? 1 : 0);  // tiles the current CTA can still take
+    uint32_t slot = 0;
+    cta_begin.push_back(0);
+    for (uint32_t b = 0; b < batch; ++b) {
+        const uint32_t tiles = (kv_lens[b] + kTileKeys - 1) / kTileKeys;
+        if (tiles == 0) continue;
+        for (uint32_t kh = 0; kh < n_kv_heads; ++kh) {
+            const uint32_t unit = b * n_kv_heads + kh;
+            const uint32_t first_slot = slot;
+            const size_t first_item = items.size();
+            uint32_t t = 0;
+            while (t < tiles) {
+                if (room == 0) {
+                    ++cta;
+                    cta_begin.push_back((uint32_t)items.size());
+                    room = base + (cta < rem ? 1 : 0);
+                }
+                const uint32_t take = (uint32_t)((uint64_t)(tiles - t) < room ? (tiles - t) : room);
+                WorkItem it{};
+                it.seq = b;
+                it.kvh = kh;
+                it.tile_begin = t;
+                it.tile_end = t + take;
+                it.slot = slot++;
+                it.unit = unit;
+                it.first_slot = first_slot;
+                items.push_back(it);
+                t += take;
+                room -= take;
+            }
+            const uint32_t parts = (uint32_t)(items.size() - first_item);
+            for (size_t i = first_item; i < items.size(); ++i) items[i].n_parts = parts;
+        }
+    }
+    while (cta_begin.size() < (size_t)n_ctas + 1) cta_begin.push_back((uint32_t)items.size());
+}
+
+}  // namespace mf

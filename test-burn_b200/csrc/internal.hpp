@@ -1,0 +1,152 @@
+// Internal declarations shared by the translation units of libmetallic_cuda.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/metallic_cuda.h"
+
+namespace mf {
+
+constexpr uint32_t kTileKeys = 64;          // keys per pipeline stage
+constexpr uint32_t kCounterRegionBytes = 64 * 1024;  // head of a scratch arena: unit counters
+constexpr uint32_t kMaxUniformUnits = kCounterRegionBytes / 4;
+
+// One span of KV tiles of one (sequence, kv head) unit, processed by one CTA.
+struct WorkItem {
+    uint32_t seq;
+    uint32_t kvh;
+    uint32_t tile_begin;
+    uint32_t tile_end;
+    uint32_t slot;        // partial slot written when the unit has several parts
+    uint32_t unit;        // counter index
+    uint32_t n_parts;     // number of items the unit was cut into
+    uint32_t first_slot;  // slot of the unit's first part (parts are consecutive)
+};
+
+struct DecodeParams {
+    const __half *q;
+    const __half *k_new;
+    const __half *v_new;
+    __half *q_rot;
+    __half *out;
+    const __half *cos_t;
+    const __half *sin_t;
+    __half *k_base;
+    __half *v_base;
+    const uint32_t *page_table;
+    const uint32_t *kv_lens;
+    const uint32_t *rope_positions;
+    const WorkItem *items;
+    const uint32_t *cta_item_begin;
+    float *part_acc;
+    float *part_ml;
+    uint32_t *counters;
+    float *out_acc;
+    float *out_m;
+    float *out_l;
+    uint32_t *status;
+    uint32_t n_heads, n_kv_heads, group, page_size, pt_stride, batch;
+    uint32_t k_rows_b, k_rows_h, v_rows_b, v_rows_h;  // contiguous: row strides
+    uint32_t uniform_kv_len, uniform_tiles, uniform_span, uniform_total;
+    uint32_t rope, rope_mode, append;
+    uint32_t rope_position;  // contiguous mode: position of the query token
+    uint32_t q_stride_b, q_stride_h, out_stride_b, out_stride_h;
+    uint32_t knew_stride_b;  // elements between sequences in k_new / v_new
+    float scale_log2;
+};
+
+struct TensorMapKey {
+    const void *base;
+    uint64_t rows;
+    uint32_t cols;
+    uint32_t box_rows;
+    uint32_t box_cols;
+    bool operator==(const TensorMapKey &o) const
+    {
+        return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows &&
+               box_cols == o.box_cols;
+    }
+};
+struct TensorMapKeyHash {
+    size_t operator()(const TensorMapKey &k) const
+    {
+        uint64_t h = reinterpret_cast<uint64_t>(k.base) * 0x9E3779B97F4A7C15ull;
+        h ^= k.rows + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+        h ^= (uint64_t(k.cols) << 32 | k.box_rows) + (h << 6) + (h >> 2);
+        h ^= k.box_cols + (h << 6) + (h >> 2);
+        return static_cast<size_t>(h);
+    }
+};
+
+}  // namespace mf
+
+struct MfContext {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    int sm_count = 0;
+    std::string last_error;
+    void *scratch = nullptr;
+    uint64_t scratch_bytes = 0;
+    bool scratch_owned = false;
+    uint32_t *d_status = nullptr;
+    uint64_t launches = 0;
+    std::unordered_map<mf::TensorMapKey, CUtensorMap, mf::TensorMapKeyHash> tmaps;
+    void *encode_fn = nullptr;
+};
+
+struct MfDecodePlan {
+    uint32_t batch = 0, n_heads = 0, n_kv_heads = 0, head_dim = 0, page_size = 0;
+    uint32_t max_ctas = 0, n_ctas = 0, n_items = 0, n_units = 0;
+    uint64_t total_tiles = 0;
+    uint32_t item_capacity = 0;
+    std::vector<mf::WorkItem> h_items;
+    std::vector<uint32_t> h_cta_begin;
+    mf::WorkItem *pinned_items = nullptr;
+    uint32_t *pinned_cta_begin = nullptr;
+    mf::WorkItem *d_items = nullptr;
+    uint32_t *d_cta_begin = nullptr;
+    float *d_part_acc = nullptr;
+    float *d_part_ml = nullptr;
+    uint32_t *d_counters = nullptr;
+    uint32_t heads_padded = 0;
+};
+
+namespace mf {
+
+mf_status fail(MfContext *ctx, mf_status code, const char *fmt, ...);
+mf_status check_cuda(MfContext *ctx, cudaError_t e, const char *what);
+mf_status check_launch(MfContext *ctx, const char *what);
+
+// f16 tensor checks used by the operator entry points.
+mf_status need_tensor(MfContext *ctx, const MfTensor *t, const char *name);
+inline __half *tensor_ptr(const MfTensor *t)
+{
+    return reinterpret_cast<__half *>(static_cast<char *>(t->dev_ptr) + t->offset_bytes);
+}
+
+// Cached 2-D f16 tensor map over [rows, cols] with a [box_rows, box_cols] box and
+// the 128-byte swizzle.
+mf_status get_tensor_map(MfContext *ctx, const void *base, uint64_t rows, uint32_t cols,
+                         uint32_t box_rows, uint32_t box_cols, CUtensorMap *out);
+
+mf_status ensure_scratch(MfContext *ctx, uint64_t bytes);
+
+// Host planner: cut the tiles of all (sequence, kv head) units into n_ctas equal spans.
+void build_decode_plan(const uint32_t *kv_lens, uint32_t batch, uint32_t n_kv_heads,
+                       uint32_t max_ctas, std::vector<WorkItem> &items,
+                       std::vector<uint32_t> &cta_begin, uint32_t *n_units,
+                       uint64_t *total_tiles);
+
+// Launchers (decode.cu, prefill.cu, kv_append.cu).
+mf_status launch_decode(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap &tm_v,
+                        const DecodeParams &p, uint32_t head_dim, uint32_t n_ctas);
+
+}  // namespace mf

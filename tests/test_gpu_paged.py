@@ -1,0 +1,234 @@
+"""GPU parity: batched paged decode (fused RoPE + append + GQA flash-decode) through the C ABI.
+
+The paged layout, batch > 1 and split-KV decode are not in the reference; they are pinned by
+identities against the restated oracle: pool contents after the append are bit-exact, the
+gathered pages equal the contiguous cache bit-exact, and attention matches the contiguous
+oracle (f32 online softmax and fp64 gold) within max-abs 2e-3.
+"""
+import numpy as np
+import pytest
+
+import oracle
+from kvcases import PagedCase, dev, dev_u32, host, max_abs
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+class DeviceCase:
+    def __init__(self, mfk, case):
+        self.k_pool, self.v_pool = dev(case.k_pool), dev(case.v_pool)
+        self.page_table = dev_u32(case.page_table)
+        self.kv_lens = dev_u32(case.kv_lens)
+        self.q, self.k, self.v = dev(case.q), dev(case.k), dev(case.v)
+        self.cos, self.sin = dev(case.cos), dev(case.sin)
+        self.desc = mfk.paged_kv(self.k_pool, self.v_pool, self.page_table, self.kv_lens, n_kv_heads=case.Hkv,
+                                 page_size=case.P, head_dim=case.D)
+
+
+def run_fused(mfk, foundry, case, max_ctas=0, repeats=1):
+    import torch
+
+    dc = DeviceCase(mfk, case)
+    plan = foundry.decode_plan(case.kv_lens, n_heads=case.Hq, n_kv_heads=case.Hkv, head_dim=case.D,
+                               page_size=case.P, max_ctas=max_ctas)
+    out = torch.full((case.B, case.Hq * case.D), float("nan"), dtype=torch.float16, device="cuda")
+    q_rot = torch.full_like(out, float("nan"))
+    for _ in range(repeats):
+        foundry.paged_decode(plan, dc.desc, dc.q, out, n_heads=case.Hq, k=dc.k, v=dc.v, cos=dc.cos, sin=dc.sin,
+                             rope=True, rope_mode=case.rope_mode, append=True, q_rot=q_rot, scale=float(case.scale))
+    foundry.synchronize()
+    res = host(out), host(q_rot), host(dc.k_pool), host(dc.v_pool)
+    plan.close()
+    return res
+
+
+def check(case, got, ref):
+    out, q_rot, kp, vp = got
+    q_ref, kp_ref, vp_ref, out_ref, gold = ref
+    assert np.array_equal(q_rot, q_ref)
+    assert np.array_equal(kp, kp_ref)  # the appended rows, bit-exact, and nothing else touched
+    assert np.array_equal(vp, vp_ref)
+    assert max_abs(out, out_ref) <= TOL
+    assert max_abs(out, gold.ravel()) <= TOL
+
+
+CASES = [
+    # batch, Hq, Hkv, D, P, cached lengths
+    dict(batch=6, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[0, 14, 15, 16, 63, 64]),
+    dict(batch=5, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[511, 1000, 2049, 3, 4095]),
+    dict(batch=4, n_heads=24, n_kv_heads=8, head_dim=128, page_size=64, cached=[0, 63, 64, 1337]),
+    dict(batch=3, n_heads=14, n_kv_heads=2, head_dim=64, page_size=16, cached=[511, 31, 32]),
+    dict(batch=3, n_heads=32, n_kv_heads=2, head_dim=64, page_size=32, cached=[200, 7, 95]),
+    dict(batch=2, n_heads=4, n_kv_heads=4, head_dim=128, page_size=8, cached=[77, 130]),
+    dict(batch=2, n_heads=8, n_kv_heads=1, head_dim=128, page_size=128, cached=[300, 127]),
+]
+
+
+@pytest.mark.parametrize("cfg", CASES)
+@pytest.mark.parametrize("rope_mode", [0, 1])
+def test_fused_append_decode(mfk, foundry, cfg, rope_mode):
+    case = PagedCase(rope_mode=rope_mode, **cfg)
+    check(case, run_fused(mfk, foundry, case), case.oracle_step())
+
+
+@pytest.mark.parametrize("max_ctas", [1, 3, 40, 1000])
+def test_any_cta_count_gives_the_same_answer(mfk, foundry, max_ctas):
+    """Span boundaries move with the CTA count; parity must not."""
+    case = PagedCase(batch=5, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[511, 1000, 2049, 3, 4095])
+    check(case, run_fused(mfk, foundry, case, max_ctas=max_ctas), case.oracle_step())
+
+
+def test_fused_step_is_idempotent(mfk, foundry):
+    """Running the same step again rewrites the same row and gives the same output."""
+    case = PagedCase(batch=4, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[100, 2000, 17, 900])
+    a = run_fused(mfk, foundry, case, repeats=1)
+    b = run_fused(mfk, foundry, case, repeats=4)
+    for x, y in zip(a, b):
+        assert np.array_equal(x, y)
+
+
+def test_separate_append_then_decode(mfk, foundry):
+    """mf_paged_kv_append + decode without fusion equals the fused launch bit for bit."""
+    import torch
+
+    case = PagedCase(batch=4, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[5, 700, 64, 2047])
+    fused = run_fused(mfk, foundry, case)
+    dc = DeviceCase(mfk, case)
+    q_rot = torch.empty((case.B, case.Hq * case.D), dtype=torch.float16, device="cuda")
+    foundry.paged_kv_append(dc.desc, dc.q, dc.k, dc.v, q_rot, dc.cos, dc.sin, n_heads=case.Hq,
+                            rope_mode=case.rope_mode)
+    plan = foundry.decode_plan(case.kv_lens, n_heads=case.Hq, n_kv_heads=case.Hkv, head_dim=case.D, page_size=case.P)
+    out = torch.empty_like(q_rot)
+    foundry.paged_decode(plan, dc.desc, q_rot, out, n_heads=case.Hq, scale=float(case.scale))
+    foundry.synchronize()
+    assert np.array_equal(host(q_rot), fused[1])
+    assert np.array_equal(host(dc.k_pool), fused[2])
+    assert np.array_equal(host(dc.v_pool), fused[3])
+    assert np.array_equal(host(out), fused[0])
+    plan.close()
+
+
+def test_paged_gather_equals_contiguous(mfk, foundry):
+    """Pages gathered in logical order are the contiguous [Hkv, L, D] cache, bit-exact."""
+    import torch
+
+    case = PagedCase(batch=3, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[33, 500, 16],
+                     poison=False)
+    dc = DeviceCase(mfk, case)
+    for b in range(case.B):
+        n = int(case.cached[b])
+        for use_v, pool in ((False, case.k_pool), (True, case.v_pool)):
+            out = torch.empty((case.Hkv, n, case.D), dtype=torch.float16, device="cuda")
+            foundry.paged_gather(dc.desc, use_v, b, n, out)
+            foundry.synchronize()
+            ref = np.empty((case.Hkv, n, case.D), np.uint16)
+            oracle.lib().mfo_paged_gather(pool, case.page_table[b], n, case.Hkv, case.P, case.D, ref)
+            assert np.array_equal(host(out), ref)
+
+
+def test_plan_update_follows_growing_sequences(mfk, foundry):
+    """Three decode steps in a row: lengths grow by one, the plan is updated in place."""
+    import torch
+
+    cached = np.array([14, 62, 300], np.uint32)
+    case = PagedCase(batch=3, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=cached + 3, poison=False)
+    # start three tokens earlier and replay the appends with the oracle and the GPU side by side
+    k_pool, v_pool = case.k_pool.copy(), case.v_pool.copy()
+    dk, dv = dev(k_pool), dev(v_pool)
+    pt = dev_u32(case.page_table)
+    cos, sin = dev(case.cos), dev(case.sin)
+    plan = None
+    L = oracle.lib()
+    for step in range(3):
+        lens = cached + step + 1
+        q = oracle.normal_fill(77, 10 + step, case.B * case.Hq * case.D).reshape(case.B, -1)
+        k = oracle.normal_fill(77, 20 + step, case.B * case.Hkv * case.D).reshape(case.B, -1)
+        v = oracle.normal_fill(77, 30 + step, case.B * case.Hkv * case.D).reshape(case.B, -1)
+        q_rot = np.empty_like(q)
+        L.mfo_paged_kv_append(q, k, v, q_rot, k_pool, v_pool, case.cos, case.sin, case.page_table, case.pt_stride,
+                              (lens - 1).astype(np.uint32), case.B, case.Hq, case.Hkv, case.D, case.P, 0, 1)
+        ref = np.empty((case.B, case.Hq * case.D), np.uint16)
+        for b in range(case.B):
+            n = int(lens[b])
+            kc = np.empty((case.Hkv, n, case.D), np.uint16)
+            vc = np.empty((case.Hkv, n, case.D), np.uint16)
+            L.mfo_paged_gather(k_pool, case.page_table[b], n, case.Hkv, case.P, case.D, kc)
+            L.mfo_paged_gather(v_pool, case.page_table[b], n, case.Hkv, case.P, case.D, vc)
+            ref[b] = oracle.decode_online(q_rot[b], kc, vc, n_heads=case.Hq, cache_heads=case.Hkv, head_dim=case.D,
+                                          capacity=n, kv_len=n, scale=case.scale)
+        dl = dev_u32(lens)
+        desc = mfk.paged_kv(dk, dv, pt, dl, n_kv_heads=case.Hkv, page_size=case.P, head_dim=case.D)
+        if plan is None:
+            plan = foundry.decode_plan(lens, n_heads=case.Hq, n_kv_heads=case.Hkv, head_dim=case.D, page_size=case.P)
+        else:
+            plan.update(lens)
+        out = torch.empty((case.B, case.Hq * case.D), dtype=torch.float16, device="cuda")
+        foundry.paged_decode(plan, desc, dev(q), out, n_heads=case.Hq, k=dev(k), v=dev(v), cos=cos, sin=sin,
+                             rope=True, append=True, scale=float(case.scale))
+        foundry.synchronize()
+        assert max_abs(host(out), ref) <= TOL
+        assert np.array_equal(host(dk), k_pool)
+    plan.close()
+
+
+def test_partials_and_merge_equal_full_decode(mfk, foundry):
+    """Sequence-sharded decode on one GPU: two shards of one long sequence emit (acc, m, l);
+    mf_merge_partials over the gathered partials equals the unsharded result."""
+    import torch
+
+    Hq, Hkv, D, P, L = 24, 8, 128, 64, 4096 + 17
+    full = PagedCase(batch=1, n_heads=Hq, n_kv_heads=Hkv, head_dim=D, page_size=P, cached=[L - 1], poison=False)
+    q_ref, kp, vp, out_ref, gold = full.oracle_step()
+    dk, dv = dev(kp), dev(vp)  # pools after the append
+    q_rot = dev(q_ref)
+    n_pages = full.page_table.shape[1]
+    cut = (n_pages // 2)
+    shards = [(0, cut), (cut, n_pages)]
+    accs, ms, ls = [], [], []
+    for (p0, p1) in shards:
+        pt = np.ascontiguousarray(full.page_table[:, p0:p1])
+        lens = np.array([min(L, p1 * P) - p0 * P], np.uint32)
+        d_pt, d_len = dev_u32(pt), dev_u32(lens)
+        desc = mfk.paged_kv(dk, dv, d_pt, d_len, n_kv_heads=Hkv, page_size=P, head_dim=D)
+        plan = foundry.decode_plan(lens, n_heads=Hq, n_kv_heads=Hkv, head_dim=D, page_size=P)
+        acc = torch.zeros((1, Hq, D), dtype=torch.float32, device="cuda")
+        m = torch.full((1, Hq), -1e30, dtype=torch.float32, device="cuda")
+        l = torch.zeros((1, Hq), dtype=torch.float32, device="cuda")
+        foundry.paged_decode_partial(plan, desc, q_rot, acc, m, l, n_heads=Hq, scale=float(full.scale))
+        foundry.synchronize()
+        plan.close()
+        accs.append(acc.view(Hq, D))
+        ms.append(m.view(Hq))
+        ls.append(l.view(Hq))
+    acc = torch.stack(accs).contiguous()
+    m = torch.stack(ms).contiguous()
+    l = torch.stack(ls).contiguous()
+    out = torch.empty((Hq, D), dtype=torch.float16, device="cuda")
+    foundry.merge_partials(acc, m, l, out)
+    foundry.synchronize()
+    assert max_abs(host(out), out_ref) <= TOL
+    assert max_abs(host(out), gold.ravel()) <= TOL
+    # the merge kernel itself against the oracle's merge, same partials
+    ref_merge = oracle.merge_partials(acc.cpu().numpy(), m.cpu().numpy(), l.cpu().numpy())
+    assert max_abs(host(out), ref_merge) <= 1e-3
+
+
+def test_paged_decode_rejects_bad_arguments(mfk, foundry):
+    import torch
+
+    case = PagedCase(batch=2, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[5, 70], poison=False)
+    dc = DeviceCase(mfk, case)
+    plan = foundry.decode_plan(case.kv_lens, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16)
+    out = torch.empty((2, 16 * 128), dtype=torch.float16, device="cuda")
+    with pytest.raises(mfk.MetalError) as e:  # append without k/v
+        foundry.paged_decode(plan, dc.desc, dc.q, out, n_heads=16, append=True)
+    assert e.value.kind == "InputNotFound"
+    with pytest.raises(mfk.MetalError) as e:  # geometry differs from the plan
+        foundry.paged_decode(plan, dc.desc, dc.q, out, n_heads=8)
+    assert e.value.kind == "InvalidShape"
+    with pytest.raises(mfk.MetalError) as e:
+        foundry.decode_plan(case.kv_lens, n_heads=16, n_kv_heads=2, head_dim=96, page_size=16)
+    assert e.value.kind == "OperationNotSupported"
+    plan.close()
+    foundry.synchronize()
