@@ -1,0 +1,410 @@
+#!/usr/bin/env python
+"""Benchmark of the KV-cache hot path: fused RoPE + K/V append + paged GQA flash-decode.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3|c2|c3-small]
+
+Workload (default `c3`, the batched paged-decode configuration the headline metric is quoted on):
+Qwen2.5-3B shape, 36 layers, 16 q heads / 2 kv heads, head_dim 128, batch 64, per-sequence
+context lengths uniform in [512, 16384] from the seed, page size 16, page table a seeded random
+permutation of a shared f16 page pool (one K and one V pool per layer).  A step appends one
+token per sequence in every layer and attends over the whole context: 36 launches of the fused
+kernel.  Inputs are synthetic N(0,1) f16; no model weights are involved.
+
+With N > 1 (launched by torchrun, one rank per GPU) every rank owns its own batch of 64
+sequences (seed + rank) and its own pools: sequences are independent, so there is no data-path
+collective and the scaling is weak.  torch.distributed (NCCL) is used for the barrier and the
+max-over-ranks of the device time only.
+
+`--impl reference` times the CPU restatement of the reference's math (the oracle; the reference
+itself is Rust + Metal and cannot run here) on the host cores, one layer per step, and scales
+to the full step.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: layers, Hq, Hkv, D, batch, len_lo, len_hi, page_size, theta, rope_mode
+    "c3": dict(layers=36, n_heads=16, n_kv_heads=2, head_dim=128, batch=64, lo=512, hi=16384, page_size=16,
+               theta=1e6, rope_mode=0,
+               name="batched paged decode, Qwen2.5-3B shape: 36 layers, 16q/2kv heads, D128, batch 64, "
+                    "ctx U[512,16384], page 16, fused rope+append+decode"),
+    "c3-small": dict(layers=4, n_heads=16, n_kv_heads=2, head_dim=128, batch=64, lo=512, hi=16384, page_size=16,
+                     theta=1e6, rope_mode=0, name="c3 with 4 layers (profiling case)"),
+    "c2": dict(layers=28, n_heads=24, n_kv_heads=8, head_dim=128, batch=1, lo=8191, hi=8191, page_size=64,
+               theta=5e5, rope_mode=1,
+               name="Llama-3.2-3B shape decode step: 28 layers, 24q/8kv heads, D128, batch 1, ctx 8192, "
+                    "cache as 64-token pages in order"),
+}
+SEED = 0x5EED
+METRIC = "kv_append_decode_attn_tokens_per_s"
+# DRAM bytes moved by the decode kernel per algorithmic byte, from the ncu capture summarised in
+# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the same launch).
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = None
+
+
+def measured_peak_gbs():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def make_lengths(w, seed):
+    rng = np.random.default_rng(seed)
+    cached = rng.integers(w["lo"], w["hi"] + 1, size=w["batch"]).astype(np.uint32)
+    return cached, cached + 1  # cached tokens, kv_len after the append
+
+
+def make_page_table(w, kv_lens, seed):
+    P = w["page_size"]
+    pages = (kv_lens + P - 1) // P
+    n_pages = int(pages.sum())
+    rng = np.random.default_rng(seed + 1)
+    perm = rng.permutation(n_pages).astype(np.uint32) if w["batch"] > 1 else np.arange(n_pages, dtype=np.uint32)
+    stride = int(pages.max())
+    table = np.zeros((w["batch"], stride), np.uint32)
+    o = 0
+    for b in range(w["batch"]):
+        n = int(pages[b])
+        table[b, :n] = perm[o:o + n]
+        o += n
+    return table, n_pages
+
+
+def algorithmic_bytes_per_layer(w, kv_lens):
+    """K and V read once per KV head (incl. the new row) + new k,v read + cache row write + q read,
+    out write + cos/sin row + page ids."""
+    hq, hkv, d, P = w["n_heads"], w["n_kv_heads"], w["head_dim"], w["page_size"]
+    total = 0
+    for L in kv_lens.astype(np.int64):
+        total += 2 * hkv * L * d * 2 + 2 * hkv * d * 2 + 2 * hkv * d * 2 + 2 * hq * d * 2 + 2 * (d // 2) * 2
+        total += 4 * ((L + P - 1) // P)
+    return int(total)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [l for (t, l) in self.lines if t0 <= t <= t1 + 0.2] or [l for (_, l) in self.lines]
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            f = [x.strip() for x in r.split(",")]
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- ours ---
+
+def run_ours(args, w):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    mfk = importlib.import_module("test-burn_b200")  # raises if the CUDA library is missing
+
+    layers, hq, hkv, d, B, P = w["layers"], w["n_heads"], w["n_kv_heads"], w["head_dim"], w["batch"], w["page_size"]
+    seed = SEED + rank
+    cached, kv_lens = make_lengths(w, seed)
+    table, n_pages = make_page_table(w, kv_lens, seed)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+    pool_elems = n_pages * hkv * P * d
+    k_pools = [torch.empty(pool_elems, dtype=torch.float16, device=dev).normal_(generator=gen) for _ in range(layers)]
+    v_pools = [torch.empty(pool_elems, dtype=torch.float16, device=dev).normal_(generator=gen) for _ in range(layers)]
+    d_table = torch.from_numpy(table.view(np.int32)).to(dev)
+    d_lens = torch.from_numpy(kv_lens.view(np.int32)).to(dev)
+    cos_np, sin_np = mfk.rope_tables(w["theta"], d, int(kv_lens.max()))
+    d_cos = torch.from_numpy(cos_np.view(np.float16)).to(dev)
+    d_sin = torch.from_numpy(sin_np.view(np.float16)).to(dev)
+    # per-layer step inputs: host (pinned) and device copies
+    cpu_gen = torch.Generator().manual_seed(seed)
+    h_q = torch.randn((layers, B, hq * d), generator=cpu_gen).half().pin_memory()
+    h_k = torch.randn((layers, B, hkv * d), generator=cpu_gen).half().pin_memory()
+    h_v = torch.randn((layers, B, hkv * d), generator=cpu_gen).half().pin_memory()
+    h_out = torch.empty((layers, B, hq * d), dtype=torch.float16).pin_memory()
+    h_table = torch.from_numpy(table.view(np.int32)).pin_memory()
+    h_lens = torch.from_numpy(kv_lens.view(np.int32)).pin_memory()
+    d_q, d_k, d_v = h_q.to(dev), h_k.to(dev), h_v.to(dev)
+    d_out = torch.empty((layers, B, hq * d), dtype=torch.float16, device=dev)
+
+    stream = torch.cuda.Stream(device=dev)
+    copy_in, copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    f = mfk.Foundry(dev.index, stream.cuda_stream)
+    plan = f.decode_plan(kv_lens, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P)
+    descs = [mfk.paged_kv(k_pools[i].view(n_pages, hkv, P, d), v_pools[i].view(n_pages, hkv, P, d), d_table, d_lens,
+                          n_kv_heads=hkv, page_size=P, head_dim=d) for i in range(layers)]
+    scale = 1.0 / math.sqrt(d)
+
+    def device_step():
+        for i in range(layers):
+            f.paged_decode(plan, descs[i], d_q[i], d_out[i], n_heads=hq, k=d_k[i], v=d_v[i], cos=d_cos, sin=d_sin,
+                           rope=True, rope_mode=w["rope_mode"], append=True, scale=scale)
+
+    # End-to-end step: host inputs -> device -> host results, through the same C-ABI calls.  The page
+    # table, lengths and work plan are rebuilt from host state each step as a serving loop would; per
+    # layer the q/k/v rows go up and the attention output comes back; the KV pools are cache state
+    # and stay resident.  Uploads and downloads run on copy streams, ordered by events.
+    e2e_q = torch.empty((2, B, hq * d), dtype=torch.float16, device=dev)
+    e2e_k = torch.empty((2, B, hkv * d), dtype=torch.float16, device=dev)
+    e2e_v = torch.empty((2, B, hkv * d), dtype=torch.float16, device=dev)
+    e2e_out = torch.empty((2, B, hq * d), dtype=torch.float16, device=dev)
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_free = [torch.cuda.Event() for _ in range(2)]
+    ev_done = [torch.cuda.Event() for _ in range(2)]
+    ev_out_free = [torch.cuda.Event() for _ in range(2)]
+
+    def e2e_step():
+        with torch.cuda.stream(stream):
+            d_table.copy_(h_table, non_blocking=True)
+            d_lens.copy_(h_lens, non_blocking=True)
+        plan.update(kv_lens)
+        for i in range(layers):
+            s = i & 1
+            with torch.cuda.stream(copy_in):
+                copy_in.wait_event(ev_free[s])
+                e2e_q[s].copy_(h_q[i], non_blocking=True)
+                e2e_k[s].copy_(h_k[i], non_blocking=True)
+                e2e_v[s].copy_(h_v[i], non_blocking=True)
+                ev_in[s].record(copy_in)
+            stream.wait_event(ev_in[s])
+            stream.wait_event(ev_out_free[s])
+            f.paged_decode(plan, descs[i], e2e_q[s], e2e_out[s], n_heads=hq, k=e2e_k[s], v=e2e_v[s], cos=d_cos,
+                           sin=d_sin, rope=True, rope_mode=w["rope_mode"], append=True, scale=scale)
+            ev_free[s].record(stream)
+            ev_done[s].record(stream)
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(ev_done[s])
+                h_out[i].copy_(e2e_out[s], non_blocking=True)
+                ev_out_free[s].record(copy_out)
+        stream.wait_stream(copy_out)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        """Returns (device ms for all steps, wall seconds window)."""
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        t0 = time.time()
+        start.record(stream)
+        for _ in range(steps):
+            fn()
+        stop.record(stream)
+        barrier()
+        t1 = time.time()
+        ms = start.elapsed_time(stop)
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, t0, t1
+
+    for _ in range(max(args.warmup, 3)):
+        device_step()
+    f.synchronize()
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    time.sleep(0.3)
+    launches0 = f.launch_count
+    ms, t0, t1 = timed(device_step, args.steps)
+    launches = f.launch_count - launches0
+    f.synchronize()  # also reads the device status word: a timed-out barrier wait would raise here
+    for _ in range(2):
+        e2e_step()
+    ms_e2e, _, t1 = timed(e2e_step, args.steps)
+    f.synchronize()
+    clocks = sampler.stop(t0, t1)
+
+    ms_step = ms / args.steps
+    tokens_per_s = B * world / (ms_step * 1e-3)
+    ms_step_e2e = ms_e2e / args.steps
+    bytes_layer = algorithmic_bytes_per_layer(w, kv_lens)
+    launch_us = ms_step * 1e3 / layers
+    achieved = bytes_layer / (launch_us * 1e-6) / 1e9
+    peak, peak_kind = measured_peak_gbs()
+    if world > 1:
+        t = torch.tensor([launches], dtype=torch.float64, device=dev)
+        dist.all_reduce(t)
+        launches = int(t.item())
+    h2d = layers * B * (hq + 2 * hkv) * d * 2 + h_table.numel() * 4 + h_lens.numel() * 4 + plan.items * 32
+    d2h = layers * B * hq * d * 2
+    result = {
+        "metric": METRIC, "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "us_per_step": ms_step * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": w["name"], "layers": layers, "batch_per_gpu": B, "tokens_cached_per_gpu": int(cached.sum()),
+                   "pages_per_layer": n_pages, "seed": SEED, "l2": "inputs larger than L2 (KV pools %.1f GB per GPU)"
+                   % (2 * layers * pool_elems * 2 / 1e9), "ctas": plan.ctas, "work_items": plan.items},
+        "hbm_tb_s": achieved / 1e3,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": peak_kind, "kernel": "decode_kernel<128,1,6>", "launch_us": launch_us,
+                     "algorithmic_bytes_per_launch": bytes_layer,
+                     "traffic": (bytes_layer * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE
+                                 if NCU_TRAFFIC_PER_ALGORITHMIC_BYTE else None)},
+        "e2e": {"value": B * world / (ms_step_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_step_e2e,
+                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        result["cpu_baseline"] = cpu_baseline(w, steps=1)
+    # Sanity on the timed buffers: the last layer's output is finite and the end-to-end output equals it.
+    torch.cuda.synchronize()
+    ok = bool(torch.isfinite(d_out[-1].float()).all()) and bool(torch.equal(h_out[-1].to(dev), d_out[-1]))
+    result["self_check"] = "ok" if ok else "FAILED"
+    plan.close()
+    f.close()
+    if world > 1:
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(result))
+    return 0 if ok else 1
+
+
+# ---------------------------------------------------------------------- CPU arms ---
+
+def cpu_layer_inputs(w, seed):
+    """Host-side inputs of ONE layer of the workload (pools tiled from a random block)."""
+    hq, hkv, d, B, P = w["n_heads"], w["n_kv_heads"], w["head_dim"], w["batch"], w["page_size"]
+    cached, kv_lens = make_lengths(w, seed)
+    table, n_pages = make_page_table(w, kv_lens, seed)
+    rng = np.random.default_rng(seed)
+    block = rng.standard_normal(1 << 22, dtype=np.float32).astype(np.float16).view(np.uint16)
+    n = n_pages * hkv * P * d
+    k_pool = np.resize(block, n)
+    v_pool = np.resize(block[::-1], n)
+    q = rng.standard_normal(B * hq * d, dtype=np.float32).astype(np.float16).view(np.uint16)
+    k = rng.standard_normal(B * hkv * d, dtype=np.float32).astype(np.float16).view(np.uint16)
+    v = rng.standard_normal(B * hkv * d, dtype=np.float32).astype(np.float16).view(np.uint16)
+    return cached, kv_lens, table, k_pool, v_pool, q, k, v
+
+
+def cpu_time_layer(w, repeats):
+    import oracle
+
+    L = oracle.lib()
+    hq, hkv, d, B, P = w["n_heads"], w["n_kv_heads"], w["head_dim"], w["batch"], w["page_size"]
+    cached, kv_lens, table, k_pool, v_pool, q, k, v = cpu_layer_inputs(w, SEED)
+    cos, sin = oracle.rope_tables(w["theta"], d, int(kv_lens.max()))
+    out = np.empty(B * hq * d, np.uint16)
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        L.mfo_paged_decode_layer(q, k, v, k_pool, v_pool, cos, sin, table, table.shape[1], kv_lens, B, hq, hkv, d, P,
+                                 w["rope_mode"], 1.0 / math.sqrt(d), out)
+        times.append(time.perf_counter() - t0)
+    return times, int(L.mfo_num_threads())
+
+
+def cpu_baseline(w, steps=1):
+    times, threads = cpu_time_layer(w, steps)
+    t_layer = float(np.median(times))
+    return {"value": w["batch"] / (t_layer * w["layers"]), "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": "1 of %d layers, all %d sequences, timed %d time(s) (%.2f s per layer), scaled by the layer count; "
+                      "scalar C restatement of the reference math with OpenMP over (sequence, kv head)"
+                      % (w["layers"], w["batch"], steps, t_layer)}
+
+
+def run_reference(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    n = int(os.environ.get("WORLD_SIZE", "1"))
+    times, threads = cpu_time_layer(w, max(1, args.steps + min(args.warmup, 1)))
+    times = times[min(args.warmup, 1):] or times
+    t_layer = float(np.mean(times))
+    ms_step = t_layer * w["layers"] * 1e3
+    value = w["batch"] / (ms_step * 1e-3)
+    sample = ("each step = 1 of %d layers on all %d sequences (%.2f s), scaled by the layer count; CPU restatement of "
+              "the reference math (the reference is Rust + Metal and cannot run on this host)" % (w["layers"], w["batch"], t_layer))
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": n, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16 storage, f32 accumulate", "data": "synthetic", "config": {"workload": w["name"]},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        return run_reference(args, w)
+    return run_ours(args, w)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

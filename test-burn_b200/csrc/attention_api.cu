@@ -364,13 +364,20 @@ static mf_status plan_upload(MfContext *ctx, MfDecodePlan *pl)
     if (pl->n_items > pl->item_capacity)
         return fail(ctx, MF_ERR_INVALID_OPERATION, "decode plan: %u items exceed capacity %u", pl->n_items, pl->item_capacity);
     if (pl->n_items == 0) return MF_OK;
-    std::memcpy(pl->pinned_items, pl->h_items.data(), sizeof(WorkItem) * pl->n_items);
-    std::memcpy(pl->pinned_cta_begin, pl->h_cta_begin.data(), 4 * (pl->n_ctas + 1));
-    mf_status st = check_cuda(ctx, cudaMemcpyAsync(pl->d_items, pl->pinned_items, sizeof(WorkItem) * pl->n_items,
-                                                   cudaMemcpyHostToDevice, ctx->stream), "plan upload");
+    const uint32_t s = pl->next_stage;
+    pl->next_stage ^= 1;
+    // The copy that last read this staging set must have finished.
+    mf_status st = check_cuda(ctx, cudaEventSynchronize(pl->staged[s]), "cudaEventSynchronize(plan staging)");
     if (st != MF_OK) return st;
-    return check_cuda(ctx, cudaMemcpyAsync(pl->d_cta_begin, pl->pinned_cta_begin, 4 * (pl->n_ctas + 1),
-                                           cudaMemcpyHostToDevice, ctx->stream), "plan upload");
+    std::memcpy(pl->pinned_items[s], pl->h_items.data(), sizeof(WorkItem) * pl->n_items);
+    std::memcpy(pl->pinned_cta_begin[s], pl->h_cta_begin.data(), 4 * (pl->n_ctas + 1));
+    st = check_cuda(ctx, cudaMemcpyAsync(pl->d_items, pl->pinned_items[s], sizeof(WorkItem) * pl->n_items,
+                                         cudaMemcpyHostToDevice, ctx->stream), "plan upload");
+    if (st != MF_OK) return st;
+    st = check_cuda(ctx, cudaMemcpyAsync(pl->d_cta_begin, pl->pinned_cta_begin[s], 4 * (pl->n_ctas + 1),
+                                         cudaMemcpyHostToDevice, ctx->stream), "plan upload");
+    if (st != MF_OK) return st;
+    return check_cuda(ctx, cudaEventRecord(pl->staged[s], ctx->stream), "cudaEventRecord(plan staging)");
 }
 
 mf_status mf_decode_plan_create(MfContext *ctx, const uint32_t *kv_lens_host, uint32_t batch, uint32_t n_heads,
@@ -401,8 +408,11 @@ mf_status mf_decode_plan_create(MfContext *ctx, const uint32_t *kv_lens_host, ui
     auto ok = [&](cudaError_t r) {
         if (e == cudaSuccess) e = r;
     };
-    ok(cudaMallocHost(reinterpret_cast<void **>(&pl->pinned_items), sizeof(WorkItem) * pl->item_capacity));
-    ok(cudaMallocHost(reinterpret_cast<void **>(&pl->pinned_cta_begin), 4 * (max_ctas + 1)));
+    for (int i = 0; i < 2; ++i) {
+        ok(cudaMallocHost(reinterpret_cast<void **>(&pl->pinned_items[i]), sizeof(WorkItem) * pl->item_capacity));
+        ok(cudaMallocHost(reinterpret_cast<void **>(&pl->pinned_cta_begin[i]), 4 * (max_ctas + 1)));
+        ok(cudaEventCreateWithFlags(&pl->staged[i], cudaEventDisableTiming));
+    }
     ok(cudaMalloc(reinterpret_cast<void **>(&pl->d_items), sizeof(WorkItem) * pl->item_capacity));
     ok(cudaMalloc(reinterpret_cast<void **>(&pl->d_cta_begin), 4 * (max_ctas + 1)));
     ok(cudaMalloc(reinterpret_cast<void **>(&pl->d_part_acc), (size_t)pl->item_capacity * pl->heads_padded * head_dim * 4));
@@ -426,9 +436,6 @@ mf_status mf_decode_plan_update(MfContext *ctx, MfDecodePlan *pl, const uint32_t
 {
     if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
     if (!pl || !kv_lens_host) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "decode plan: null input");
-    // The pinned staging buffers may still be read by a copy queued earlier.
-    mf_status st = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
-    if (st != MF_OK) return st;
     build_decode_plan(kv_lens_host, pl->batch, pl->n_kv_heads, pl->max_ctas, pl->h_items, pl->h_cta_begin, &pl->n_units,
                       &pl->total_tiles);
     return plan_upload(ctx, pl);
@@ -438,8 +445,11 @@ void mf_decode_plan_destroy(MfContext *ctx, MfDecodePlan *pl)
 {
     if (!pl) return;
     if (ctx && ctx->stream) cudaStreamSynchronize(ctx->stream);
-    if (pl->pinned_items) cudaFreeHost(pl->pinned_items);
-    if (pl->pinned_cta_begin) cudaFreeHost(pl->pinned_cta_begin);
+    for (int i = 0; i < 2; ++i) {
+        if (pl->pinned_items[i]) cudaFreeHost(pl->pinned_items[i]);
+        if (pl->pinned_cta_begin[i]) cudaFreeHost(pl->pinned_cta_begin[i]);
+        if (pl->staged[i]) cudaEventDestroy(pl->staged[i]);
+    }
     if (pl->d_items) cudaFree(pl->d_items);
     if (pl->d_cta_begin) cudaFree(pl->d_cta_begin);
     if (pl->d_part_acc) cudaFree(pl->d_part_acc);

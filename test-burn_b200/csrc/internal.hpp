@@ -109,8 +109,12 @@ struct MfDecodePlan {
     uint32_t item_capacity = 0;
     std::vector<mf::WorkItem> h_items;
     std::vector<uint32_t> h_cta_begin;
-    mf::WorkItem *pinned_items = nullptr;
-    uint32_t *pinned_cta_begin = nullptr;
+    // Two pinned staging sets used alternately, each guarded by the event recorded
+    // after its upload, so that re-planning never has to drain the stream.
+    mf::WorkItem *pinned_items[2] = {nullptr, nullptr};
+    uint32_t *pinned_cta_begin[2] = {nullptr, nullptr};
+    cudaEvent_t staged[2] = {nullptr, nullptr};
+    uint32_t next_stage = 0;
     mf::WorkItem *d_items = nullptr;
     uint32_t *d_cta_begin = nullptr;
     float *d_part_acc = nullptr;
