@@ -127,6 +127,8 @@ _SIGNATURES = {
     "mf_run_flash_decode": (C.c_int32, [vp] + [C.POINTER(MfTensor)] * 4 + [u32] * 5),
     "mf_flash_decode": (C.c_int32, [vp, vp, vp, vp, vp, C.POINTER(MfFlashDecodeStrides), C.POINTER(SdpaParams),
                                     u32, u32, u32]),
+    "mf_flash_decode_static_scratch": (C.c_int32, [vp, vp, vp, vp, vp, C.POINTER(MfFlashDecodeStrides),
+                                                   C.POINTER(SdpaParams), u32, u32, C.c_char_p, u32]),
     "mf_rope_flash_decode": (C.c_int32, [vp, vp, vp, vp, vp, vp, vp, C.POINTER(RopeParamsResolved),
                                          C.POINTER(SdpaParams), C.POINTER(MfFlashDecodeStrides), u32, u32]),
     "mf_flash_prefill": (C.c_int32, [vp, vp, vp, vp, vp, C.POINTER(SdpaPrefillSplitKParams)]),
@@ -305,6 +307,17 @@ class Foundry:
 
     def paged_gather(self, cache: MfPagedKv, use_v: bool, seq: int, length: int, out):
         self.check(lib.mf_paged_gather(self._h, C.byref(cache), int(use_v), seq, length, _ptr(out)))
+
+
+def flash_decode_static_scratch(stream, q, k, v, output, strides: MfFlashDecodeStrides, params: SdpaParams, n_heads,
+                                batch=1):
+    """mf_flash_decode_static_scratch: decode that allocates nothing (needs no Foundry).  `stream` is a raw
+    cudaStream_t value (0 / None = the default stream)."""
+    buf = C.create_string_buffer(256)
+    st = lib.mf_flash_decode_static_scratch(None if not stream else int(stream), _ptr(q), _ptr(k), _ptr(v),
+                                            _ptr(output), C.byref(strides), C.byref(params), n_heads, batch, buf, 256)
+    if st != MF_OK:
+        raise MetalError(st, buf.value.decode())
 
 
 class DecodePlan:

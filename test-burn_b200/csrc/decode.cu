@@ -667,3 +667,207 @@ void build_decode_plan(const uint32_t *kv_lens, uint32_t batch, uint32_t n_kv_he
 }
 
 }  // namespace mf
+
+// ---------------------------------------------------------------------------------------
+// Decode without any allocation: mf_flash_decode_static_scratch.
+//
+// Some hosts of this library may not allocate device memory at all: an inference server
+// that has handed the whole GPU to its own pooling allocator and forbids plug-ins to call
+// cudaMalloc, a latency-critical decode loop that cannot afford the device-wide
+// synchronisation cudaMalloc / cudaFree imply, or a sandbox that simply denies the call.
+// For them the split-KV partials and unit tickets of the decode kernel live in the
+// file-scope device array below instead of a cudaMalloc'ed arena.  The array has a fixed,
+// modest size; a request that does not fit is refused, never grown.
+//
+// The array is per device and shared by every call in the process.  It keeps whatever the
+// previous call left, so each call clears the words that must start at zero (status and
+// tickets) on the caller's stream before its kernel.  Two calls that overlap on the same
+// GPU (different streams, or different host threads) race on it: serialise them.
+namespace mf {
+namespace {
+
+constexpr uint32_t kStaticScratchBytes = 4u << 20;   // whole array, per GPU
+constexpr uint32_t kStaticStatusBytes = 256;         // word 0: timeout status of the last call
+constexpr uint32_t kStaticTicketBytes = 16u << 10;   // up to 4096 (batch x kv head) units
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+typedef CUresult (*StaticEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct StaticDeviceState {
+    bool ready = false;
+    unsigned char *scratch = nullptr;  // device address of g_static_scratch on this device
+    int sm_count = 0;
+    StaticEncodeFn encode = nullptr;
+};
+StaticDeviceState g_static_state[64];
+
+mf_status static_fail(char *buf, uint32_t len, mf_status code, const char *fmt, unsigned long long a = 0,
+                      unsigned long long b = 0)
+{
+    if (buf && len) snprintf(buf, len, fmt, a, b);
+    return code;
+}
+
+template <int D, int NT, int STAGES>
+cudaError_t static_prepare_kernel()
+{
+    return cudaFuncSetAttribute(decode_kernel<D, NT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                Smem<D, NT, STAGES>::kDynamic);
+}
+
+template <int D, int NT, int STAGES>
+cudaError_t static_launch(const CUtensorMap &tm_k, const CUtensorMap &tm_v, const DecodeParams &p, uint32_t n_ctas,
+                          cudaStream_t stream)
+{
+    decode_kernel<D, NT, STAGES><<<n_ctas, kThreads, Smem<D, NT, STAGES>::kDynamic, stream>>>(tm_k, tm_v, p);
+    return cudaGetLastError();
+}
+
+// Once per device, with that device current.  In host code `g_static_scratch` is only a
+// stand-in for the symbol: the address a kernel can use comes from cudaGetSymbolAddress.
+mf_status static_setup(int device, char *err, uint32_t err_len)
+{
+    StaticDeviceState &st = g_static_state[device];
+    void *ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || !ptr)
+        return static_fail(err, err_len, MF_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed (%llu)", (unsigned long long)e);
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess || major != 10)
+        return static_fail(err, err_len, MF_ERR_OPERATION_NOT_SUPPORTED, "device is not sm_100 (major %llu)", (unsigned long long)major);
+    if (cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || st.sm_count <= 0)
+        return static_fail(err, err_len, MF_ERR_CUDA, "cannot read the SM count");
+    cudaDriverEntryPointQueryResult q;
+    void *fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess || !fn)
+        return static_fail(err, err_len, MF_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    st.encode = reinterpret_cast<StaticEncodeFn>(fn);
+    if (static_prepare_kernel<128, 1, 6>() != cudaSuccess || static_prepare_kernel<128, 2, 5>() != cudaSuccess ||
+        static_prepare_kernel<64, 1, 8>() != cudaSuccess || static_prepare_kernel<64, 2, 8>() != cudaSuccess)
+        return static_fail(err, err_len, MF_ERR_CUDA, "cudaFuncSetAttribute(decode) failed");
+    st.scratch = static_cast<unsigned char *>(ptr);
+    st.ready = true;
+    return MF_OK;
+}
+
+bool static_encode(const StaticDeviceState &st, const void *base, uint64_t rows, uint32_t cols, CUtensorMap *out)
+{
+    cuuint64_t gdim[2] = {cols, rows};
+    cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {64, kTileKeys};
+    cuuint32_t estr[2] = {1, 1};
+    return st.encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), gdim, gstride, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+}  // namespace mf
+
+extern "C" mf_status mf_flash_decode_static_scratch(void *cuda_stream, const void *q, const void *k, const void *v,
+                                                    void *output, const MfFlashDecodeStrides *s, const SdpaParams *sp,
+                                                    uint32_t n_heads, uint32_t batch, char *err, uint32_t err_len)
+{
+    using namespace mf;
+    if (err && err_len) err[0] = 0;
+    if (!q || !k || !v || !output || !s || !sp)
+        return static_fail(err, err_len, MF_ERR_INPUT_NOT_FOUND, "null tensor or parameter block");
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64)
+        return static_fail(err, err_len, MF_ERR_CUDA, "no current CUDA device");
+    if (!g_static_state[device].ready) {
+        mf_status st = static_setup(device, err, err_len);
+        if (st != MF_OK) return st;
+    }
+    const StaticDeviceState &dst = g_static_state[device];
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+
+    // Same contract checks as mf_flash_decode.
+    const uint32_t D = sp->head_dim;
+    if (D != 64 && D != 128)
+        return static_fail(err, err_len, MF_ERR_OPERATION_NOT_SUPPORTED, "Flash Decode only supports head_dim=64 or 128, got %llu", D);
+    if (sp->stride_k_s != D || sp->stride_v_s != D)
+        return static_fail(err, err_len, MF_ERR_OPERATION_NOT_SUPPORTED, "K/V row stride must equal head_dim");
+    if (sp->kv_len == 0 || batch == 0 || n_heads == 0) return MF_OK;
+    if (s->q_stride_h == 0 || s->k_stride_h == 0 || s->v_stride_h == 0)
+        return static_fail(err, err_len, MF_ERR_INVALID_SHAPE, "zero head stride");
+    const uint32_t q_heads = s->q_stride_b / s->q_stride_h ? s->q_stride_b / s->q_stride_h : 1;
+    const uint32_t k_heads = s->k_stride_b / s->k_stride_h ? s->k_stride_b / s->k_stride_h : 1;
+    const uint32_t group = q_heads / k_heads ? q_heads / k_heads : 1;
+    if (q_heads != n_heads || n_heads % group != 0)
+        return static_fail(err, err_len, MF_ERR_INVALID_SHAPE, "strides imply %llu query heads, n_heads is %llu", q_heads, n_heads);
+    if (group > 16) return static_fail(err, err_len, MF_ERR_OPERATION_NOT_SUPPORTED, "group size %llu > 16", group);
+    const uint32_t cache_heads = n_heads / group;
+    if (s->k_stride_h % D || s->k_stride_b % D || s->v_stride_h % D || s->v_stride_b % D)
+        return static_fail(err, err_len, MF_ERR_INVALID_SHAPE, "K/V strides must be multiples of head_dim");
+    if ((uint64_t)sp->kv_len * D > s->k_stride_h || (uint64_t)sp->kv_len * D > s->v_stride_h)
+        return static_fail(err, err_len, MF_ERR_INVALID_OPERATION, "kv_len %llu exceeds the cache capacity", sp->kv_len);
+    if ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u)
+        return static_fail(err, err_len, MF_ERR_INVALID_SHAPE, "K/V base pointers must be 16-byte aligned");
+
+    // Same span rule as mf_flash_decode with n_splits = 0, so both produce the same bits.
+    const uint32_t T = (sp->kv_len + kTileKeys - 1) / kTileKeys;
+    const uint64_t U = (uint64_t)batch * cache_heads;
+    const uint64_t total = U * T;
+    if (total > 0xFFFFFFFFull) return static_fail(err, err_len, MF_ERR_OPERATION_NOT_SUPPORTED, "too many tiles");
+    const uint64_t want = total < (uint64_t)dst.sm_count ? total : (uint64_t)dst.sm_count;
+    const uint32_t span = (uint32_t)((total + want - 1) / want);
+    const uint32_t n_ctas = (uint32_t)((total + span - 1) / span);
+    const uint32_t HP = 8 * ((group + 7) / 8);
+    const uint64_t slots = U + n_ctas;
+    const uint64_t need = (uint64_t)kStaticStatusBytes + kStaticTicketBytes + slots * HP * (D + 2) * 4;
+    if (U * 4 > kStaticTicketBytes || need > kStaticScratchBytes)
+        return static_fail(err, err_len, MF_ERR_OUT_OF_MEMORY,
+                           "this decode needs %llu bytes of scratch; the built-in array holds %llu (and 4096 batch x kv-head "
+                           "units): use mf_flash_decode, which allocates",
+                           need, (unsigned long long)kStaticScratchBytes);
+
+    unsigned char *base = dst.scratch;
+    if (cudaMemsetAsync(base, 0, kStaticStatusBytes + kStaticTicketBytes, stream) != cudaSuccess)
+        return static_fail(err, err_len, MF_ERR_CUDA, "cudaMemsetAsync(static scratch) failed");
+
+    DecodeParams p{};
+    p.q = static_cast<const __half *>(q);
+    p.out = static_cast<__half *>(output);
+    p.k_base = const_cast<__half *>(static_cast<const __half *>(k));
+    p.v_base = const_cast<__half *>(static_cast<const __half *>(v));
+    p.status = reinterpret_cast<uint32_t *>(base);
+    p.counters = reinterpret_cast<uint32_t *>(base + kStaticStatusBytes);
+    p.part_acc = reinterpret_cast<float *>(base + kStaticStatusBytes + kStaticTicketBytes);
+    p.part_ml = p.part_acc + slots * HP * D;
+    p.n_heads = n_heads;
+    p.n_kv_heads = cache_heads;
+    p.group = group;
+    p.batch = batch;
+    p.k_rows_b = s->k_stride_b / D;
+    p.k_rows_h = s->k_stride_h / D;
+    p.v_rows_b = s->v_stride_b / D;
+    p.v_rows_h = s->v_stride_h / D;
+    p.uniform_kv_len = sp->kv_len;
+    p.uniform_tiles = T;
+    p.uniform_span = span;
+    p.uniform_total = (uint32_t)total;
+    p.q_stride_b = s->q_stride_b;
+    p.q_stride_h = s->q_stride_h;
+    p.out_stride_b = s->out_stride_b;
+    p.out_stride_h = s->out_stride_h;
+    p.scale_log2 = sp->scale * 1.4426950408889634f;
+    p.rope_mode = MF_ROPE_MODE_NEOX;
+
+    const uint64_t k_rows = (uint64_t)(batch - 1) * p.k_rows_b + (uint64_t)cache_heads * p.k_rows_h;
+    const uint64_t v_rows = (uint64_t)(batch - 1) * p.v_rows_b + (uint64_t)cache_heads * p.v_rows_h;
+    CUtensorMap tm_k, tm_v;
+    if (!static_encode(dst, k, k_rows, D, &tm_k) || !static_encode(dst, v, v_rows, D, &tm_v))
+        return static_fail(err, err_len, MF_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+    const uint32_t nt = (group + 7) / 8;
+    cudaError_t e;
+    if (D == 128)
+        e = nt == 1 ? static_launch<128, 1, 6>(tm_k, tm_v, p, n_ctas, stream) : static_launch<128, 2, 5>(tm_k, tm_v, p, n_ctas, stream);
+    else
+        e = nt == 1 ? static_launch<64, 1, 8>(tm_k, tm_v, p, n_ctas, stream) : static_launch<64, 2, 8>(tm_k, tm_v, p, n_ctas, stream);
+    if (e != cudaSuccess) return static_fail(err, err_len, MF_ERR_CUDA, "decode launch failed (%llu)", (unsigned long long)e);
+    return MF_OK;
+}
