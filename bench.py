@@ -79,7 +79,8 @@ def make_page_table(w, kv_lens, seed):
     pages = (kv_lens + P - 1) // P
     n_pages = int(pages.sum())
     rng = np.random.default_rng(seed + 1)
-    perm = rng.permutation(n_pages).astype(np.uint32) if w["batch"] > 1 else np.arange(n_pages, dtype=np.uint32)
+    shuffle = w["batch"] > 1 and not w.get("sequential")
+    perm = rng.permutation(n_pages).astype(np.uint32) if shuffle else np.arange(n_pages, dtype=np.uint32)
     stride = int(pages.max())
     table = np.zeros((w["batch"], stride), np.uint32)
     o = 0
@@ -191,6 +192,8 @@ def run_ours(args, w):
     stream = torch.cuda.Stream(device=dev)
     copy_in, copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
     f = mfk.Foundry(dev.index, stream.cuda_stream)
+    if not args.no_overlap:
+        f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 1)
     plan = f.decode_plan(kv_lens, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P)
     descs = [mfk.paged_kv(k_pools[i].view(n_pages, hkv, P, d), v_pools[i].view(n_pages, hkv, P, d), d_table, d_lens,
                           n_kv_heads=hkv, page_size=P, head_dim=d) for i in range(layers)]
@@ -399,8 +402,17 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-overlap", action="store_true", help="plain launches instead of programmatic dependent launch")
+    ap.add_argument("--page-size", type=int, default=0, help="override the workload's page size (experiments)")
+    ap.add_argument("--sequential-pages", action="store_true", help="identity page table (experiments)")
     args = ap.parse_args()
-    w = WORKLOADS[args.workload]
+    w = dict(WORKLOADS[args.workload])
+    if args.page_size:
+        w["page_size"] = args.page_size
+        w["name"] += " [page size %d]" % args.page_size
+    if args.sequential_pages:
+        w["sequential"] = True
+        w["name"] += " [sequential pages]"
     if args.impl == "reference":
         return run_reference(args, w)
     return run_ours(args, w)

@@ -231,6 +231,15 @@ MF_API uint32_t mf_abi_version(void);
 /* Number of kernels this context has launched since creation (instrumentation,
  * stands in for the per-dispatch metric events of lib.rs:225-233). */
 MF_API uint64_t mf_launch_count(const MfContext *ctx);
+/* Tuning knobs (the reference's are environment variables, docs/FLASH.md:204-225).
+ * MF_OPTION_OVERLAP_LAUNCHES = 1: decode launches use programmatic dependent launch, so
+ * the next launch's CTAs are scheduled while the previous grid drains.  A fused
+ * append+decode launch then starts streaming K/V pages before the previous kernel in the
+ * stream has finished; the caller promises that this previous kernel does not write the
+ * pools, page table or lengths the launch reads (consecutive layers of a decode step never
+ * do).  Everything else a launch reads or writes still waits for the previous kernel. */
+enum { MF_OPTION_OVERLAP_LAUNCHES = 1 };
+MF_API mf_status mf_context_set_option(MfContext *ctx, uint32_t option, uint32_t value);
 /* Caller-provided scratch (device); when absent the context allocates its own
  * arena on first use and grows it on demand (pooled scratch of step.rs:927-929). */
 MF_API mf_status mf_context_set_scratch(MfContext *ctx, void *dev_ptr, uint64_t bytes);

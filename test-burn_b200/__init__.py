@@ -36,6 +36,7 @@ ROPE_MODE_NEOX, ROPE_MODE_NORMAL = 0, 1
 ROUTE_DECODE, ROUTE_PREFILL, ROUTE_PREFILL_SPLITK = 1, 2, 3
 DTYPE_F16, DTYPE_F32, DTYPE_U32 = 0, 1, 2
 ALL_SEQUENCES = 0xFFFFFFFF
+OPTION_OVERLAP_LAUNCHES = 1
 
 
 class MetalError(RuntimeError):
@@ -109,6 +110,7 @@ _SIGNATURES = {
     "mf_abi_version": (u32, []),
     "mf_launch_count": (u64, [vp]),
     "mf_context_set_scratch": (C.c_int32, [vp, vp, u64]),
+    "mf_context_set_option": (C.c_int32, [vp, u32, u32]),
     "mf_rope_tables_host": (C.c_int32, [C.c_float, u32, u32, u32, vp, vp, vp]),
     "mf_align_capacity": (u64, [u64]),
     "mf_grown_capacity": (u64, [u64, u64, u64]),
@@ -215,6 +217,9 @@ class Foundry:
 
     def synchronize(self):
         self.check(lib.mf_synchronize(self._h))
+
+    def set_option(self, option: int, value: int):
+        self.check(lib.mf_context_set_option(self._h, option, value))
 
     @property
     def launch_count(self) -> int:

@@ -134,8 +134,16 @@ mf_status decode_contiguous(MfContext *ctx, const void *q, const void *k, const 
     const uint64_t k_rows = (uint64_t)(batch - 1) * p.k_rows_b + (uint64_t)(cache_heads - 1) * p.k_rows_h + p.k_rows_h;
     const uint64_t v_rows = (uint64_t)(batch - 1) * p.v_rows_b + (uint64_t)(cache_heads - 1) * p.v_rows_h + p.v_rows_h;
     CUtensorMap tm_k, tm_v;
-    if ((st = get_tensor_map(ctx, k, k_rows, D, kTileKeys, 64, &tm_k)) != MF_OK) return st;
-    if ((st = get_tensor_map(ctx, v, v_rows, D, kTileKeys, 64, &tm_v)) != MF_OK) return st;
+    // D = 128: one copy per 64-row box brings whole rows; fall back to one copy per 64-column
+    // half if the driver refuses that map.
+    p.whole_rows = (D == 128);
+    if (p.whole_rows && (get_tensor_map(ctx, k, k_rows, D, kTileKeys, 64, &tm_k, 1) != MF_OK ||
+                         get_tensor_map(ctx, v, v_rows, D, kTileKeys, 64, &tm_v, 1) != MF_OK))
+        p.whole_rows = 0;
+    if (!p.whole_rows) {
+        if ((st = get_tensor_map(ctx, k, k_rows, D, kTileKeys, 64, &tm_k)) != MF_OK) return st;
+        if ((st = get_tensor_map(ctx, v, v_rows, D, kTileKeys, 64, &tm_v)) != MF_OK) return st;
+    }
     return launch_decode(ctx, tm_k, tm_v, p, D, n_ctas);
 }
 
@@ -540,12 +548,21 @@ static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, con
     p.out_stride_h = D;
     p.knew_stride_b = c->n_kv_heads * D;
     p.scale_log2 = a->scale * 1.4426950408889634f;
+    // With overlapped launches the tile stream may start early only when this launch does the
+    // append itself: then no kernel right before it can have written the pages it reads.
+    p.early_stream = (ctx->overlap_launches && a->append) ? 1u : 0u;
     CUtensorMap tm_k, tm_v;
     const uint64_t rows = (uint64_t)c->n_pages * c->n_kv_heads * P;
     const uint32_t box_rows = std::min(P, kTileKeys);
     mf_status st;
-    if ((st = get_tensor_map(ctx, c->k_pool, rows, D, box_rows, 64, &tm_k)) != MF_OK) return st;
-    if ((st = get_tensor_map(ctx, c->v_pool, rows, D, box_rows, 64, &tm_v)) != MF_OK) return st;
+    p.whole_rows = (D == 128);
+    if (p.whole_rows && (get_tensor_map(ctx, c->k_pool, rows, D, box_rows, 64, &tm_k, 1) != MF_OK ||
+                         get_tensor_map(ctx, c->v_pool, rows, D, box_rows, 64, &tm_v, 1) != MF_OK))
+        p.whole_rows = 0;
+    if (!p.whole_rows) {
+        if ((st = get_tensor_map(ctx, c->k_pool, rows, D, box_rows, 64, &tm_k)) != MF_OK) return st;
+        if ((st = get_tensor_map(ctx, c->v_pool, rows, D, box_rows, 64, &tm_v)) != MF_OK) return st;
+    }
     return launch_decode(ctx, tm_k, tm_v, p, D, pl->n_ctas);
 }
 

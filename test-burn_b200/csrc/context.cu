@@ -54,9 +54,9 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapFloatOOBfill);
 
 mf_status get_tensor_map(MfContext *ctx, const void *base, uint64_t rows, uint32_t cols, uint32_t box_rows,
-                         uint32_t box_cols, CUtensorMap *out)
+                         uint32_t box_cols, CUtensorMap *out, uint32_t whole_rows)
 {
-    TensorMapKey key{base, rows, cols, box_rows, box_cols};
+    TensorMapKey key{base, rows, cols, box_rows, box_cols, whole_rows};
     auto it = ctx->tmaps.find(key);
     if (it != ctx->tmaps.end()) {
         *out = it->second;
@@ -74,15 +74,31 @@ mf_status get_tensor_map(MfContext *ctx, const void *base, uint64_t rows, uint32
         return fail(ctx, MF_ERR_INVALID_SHAPE, "K/V base pointer must be 16-byte aligned");
     if (box_cols * 2 != 128 || cols % box_cols != 0 || box_rows == 0 || box_rows > 256)
         return fail(ctx, MF_ERR_INVALID_SHAPE, "tensor-map box [%u x %u] unsupported", box_rows, box_cols);
-    cuuint64_t gdim[2] = {cols, rows};
-    cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {box_cols, box_rows};
-    cuuint32_t estr[2] = {1, 1};
     CUtensorMap tm;
-    CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_fn)(
-        &tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), gdim, gstride, box, estr,
-        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r;
+    if (whole_rows) {
+        if (cols != 128) return fail(ctx, MF_ERR_INVALID_SHAPE, "whole-row tensor map needs 128 columns");
+        // (64 cols, rows, 2 halves): the half index is the OUTER box dimension so that shared
+        // memory receives [half][rows][128 B]; its global stride (128 B) is smaller than the row
+        // stride (256 B), which the address arithmetic of a tiled copy does not mind.
+        cuuint64_t gdim[3] = {64, rows, 2};
+        cuuint64_t gstride[2] = {256, 128};
+        cuuint32_t box[3] = {64, box_rows, 2};
+        cuuint32_t estr[3] = {1, 1, 1};
+        r = reinterpret_cast<EncodeTiledFn>(ctx->encode_fn)(
+            &tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base), gdim, gstride, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        cuuint64_t gdim[2] = {cols, rows};
+        cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
+        cuuint32_t box[2] = {box_cols, box_rows};
+        cuuint32_t estr[2] = {1, 1};
+        r = reinterpret_cast<EncodeTiledFn>(ctx->encode_fn)(
+            &tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), gdim, gstride, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
     if (r != CUDA_SUCCESS) return fail(ctx, MF_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
     if (ctx->tmaps.size() > 4096) ctx->tmaps.clear();
     ctx->tmaps.emplace(key, tm);
@@ -210,6 +226,15 @@ mf_status mf_context_set_scratch(MfContext *ctx, void *dev_ptr, uint64_t bytes)
         return check_cuda(ctx, cudaMemsetAsync(dev_ptr, 0, kCounterRegionBytes, ctx->stream),
                           "cudaMemsetAsync(scratch counters)");
     return MF_OK;
+}
+
+mf_status mf_context_set_option(MfContext *ctx, uint32_t option, uint32_t value)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    switch (option) {
+        case MF_OPTION_OVERLAP_LAUNCHES: ctx->overlap_launches = value ? 1u : 0u; return MF_OK;
+        default: return fail(ctx, MF_ERR_INVALID_OPERATION, "unknown option %u", option);
+    }
 }
 
 mf_status mf_synchronize(MfContext *ctx)

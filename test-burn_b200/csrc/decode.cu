@@ -42,7 +42,6 @@ struct Smem {
     static constexpr uint32_t kHP = 8 * NT;                    // padded heads per group
     static constexpr uint32_t kTileBytes = kTileKeys * D * 2;  // one K or V tile
     static constexpr uint32_t kStageBytes = 2 * kTileBytes;
-    static constexpr uint32_t kHalfBytes = kTileKeys * 128;  // one 64-column half of a tile
     static constexpr uint32_t kCombStride = D + 4;           // floats per head row
     static constexpr uint32_t kQStride = D + 8;              // halves per head row
     static constexpr uint32_t kOffComb = STAGES * kStageBytes;
@@ -110,11 +109,17 @@ __device__ __forceinline__ uint32_t kv_len_of(const DecodeParams &p, uint32_t se
     return p.kv_lens ? p.kv_lens[seq] : p.uniform_kv_len;
 }
 
-// Byte offset of (row, 16-byte chunk `c16` of the D*2-byte row) inside a K or V
-// tile laid out [half][64 rows][128 B] with the TMA 128-byte swizzle.
-__device__ __forceinline__ uint32_t tile_off(uint32_t row, uint32_t c16)
+// Byte offset of (row, 16-byte chunk `c16` of the D*2-byte row) inside a K or V tile.
+// A tile is a sequence of TMA boxes of 2^rpb_log2 rows (one page, or 64 rows); each box
+// is laid out [64-column half][rows][128 B] with the TMA 128-byte swizzle.
+template <int D>
+__device__ __forceinline__ uint32_t tile_off(uint32_t row, uint32_t c16, uint32_t rpb_log2)
 {
-    return (c16 >> 3) * (kTileKeys * 128) + row * 128 + (((c16 & 7) ^ (row & 7)) << 4);
+    constexpr uint32_t kRowLog2 = (D == 128) ? 8 : 7;
+    const uint32_t box = row >> rpb_log2;
+    const uint32_t rr = row & ((1u << rpb_log2) - 1u);
+    return (box << (rpb_log2 + kRowLog2)) + ((c16 >> 3) << (rpb_log2 + 7)) + (rr << 7) +
+           (((c16 & 7) ^ (row & 7)) << 4);
 }
 
 // One RoPE'd element pair, rounded to f16 exactly as kv_prep_fused.metal:74-82.
@@ -157,6 +162,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
     const uint32_t rows_per_box = p.page_table ? min(p.page_size, kTileKeys) : kTileKeys;
     const uint32_t boxes_per_tile = kTileKeys / rows_per_box;
+    const uint32_t rpb_log2 = 31 - __clz(rows_per_box);
+
+    // Let the next launch in the stream be scheduled onto SMs as this grid drains.
+    grid_launch_dependents();
 
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------ producer ---
@@ -164,6 +173,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             tma_prefetch_desc(&tm_k);
             tma_prefetch_desc(&tm_v);
         }
+        // K/V pages of earlier tokens were written at least one launch ago; only when the caller
+        // appended with a separate kernel right before must the stream of tiles wait for it.
+        if (!p.early_stream) grid_dependency_wait();
         const uint64_t policy = l2_policy_evict_first();
         ItemCursor cur(p, blockIdx.x);
         WorkItem it;
@@ -199,12 +211,18 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                 if (lane == 0) mbar_arrive_expect_tx(full, n_valid * rows_per_box * D * 4);
                 __syncwarp();
                 if (valid) {
-                    const uint32_t dst_k = smem_base + stage * S::kStageBytes + lane * rows_per_box * 128;
+                    const uint32_t dst_k = smem_base + stage * S::kStageBytes + lane * rows_per_box * (D * 2);
                     const uint32_t dst_v = dst_k + S::kTileBytes;
+                    if (D == 128 && p.whole_rows) {
+                        // one copy per page and tensor: both 64-column halves of every row
+                        tma_load_3d_hint(dst_k, &tm_k, 0, rk, 0, full, policy);
+                        tma_load_3d_hint(dst_v, &tm_v, 0, rv, 0, full, policy);
+                    } else {
 #pragma unroll
-                    for (int h = 0; h < D / 64; ++h) {
-                        tma_load_2d_hint(dst_k + h * S::kHalfBytes, &tm_k, h * 64, rk, full, policy);
-                        tma_load_2d_hint(dst_v + h * S::kHalfBytes, &tm_v, h * 64, rv, full, policy);
+                        for (int h = 0; h < D / 64; ++h) {
+                            tma_load_2d_hint(dst_k + h * rows_per_box * 128, &tm_k, h * 64, rk, full, policy);
+                            tma_load_2d_hint(dst_v + h * rows_per_box * 128, &tm_v, h * 64, rv, full, policy);
+                        }
                     }
                 }
                 ++issued;
@@ -231,6 +249,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     }
 
     // ---------------------------------------------------------------- consumers ---
+    // q, the new k/v, the partial slots and tickets may all have been written by the previous launch.
+    grid_dependency_wait();
     float *comb = reinterpret_cast<float *>(smem + S::kOffComb);
     __half *q_s = reinterpret_cast<__half *>(smem + S::kOffQ);
     float *ml_s = reinterpret_cast<float *>(smem + S::kOffMl);
@@ -349,13 +369,13 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                         }
                         p.k_base[krow * D + di] = oi;
                         p.k_base[krow * D + dj] = oj;
-                        *reinterpret_cast<__half *>(k_tile + tile_off(r_new, di >> 3) + (di & 7) * 2) = oi;
-                        *reinterpret_cast<__half *>(k_tile + tile_off(r_new, dj >> 3) + (dj & 7) * 2) = oj;
+                        *reinterpret_cast<__half *>(k_tile + tile_off<D>(r_new, di >> 3, rpb_log2) + (di & 7) * 2) = oi;
+                        *reinterpret_cast<__half *>(k_tile + tile_off<D>(r_new, dj >> 3, rpb_log2) + (dj & 7) * 2) = oj;
                     }
                     for (uint32_t d = tid; d < (uint32_t)D; d += kConsumerThreads) {
                         const __half x = vs[d];
                         p.v_base[vrow * D + d] = x;
-                        *reinterpret_cast<__half *>(v_tile + tile_off(r_new, d >> 3) + (d & 7) * 2) = x;
+                        *reinterpret_cast<__half *>(v_tile + tile_off<D>(r_new, d >> 3, rpb_log2) + (d & 7) * 2) = x;
                     }
                 }
                 const uint32_t first_dead = L - key0;  // 1..64
@@ -363,7 +383,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                 for (uint32_t c = tid; c < n_chunks; c += kConsumerThreads) {
                     const uint32_t row = first_dead + c / (D / 8);
                     const uint32_t c16 = c % (D / 8);
-                    *reinterpret_cast<uint4 *>(v_tile + tile_off(row, c16)) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4 *>(v_tile + tile_off<D>(row, c16, rpb_log2)) = make_uint4(0, 0, 0, 0);
                 }
                 fence_proxy_async();  // order these writes before the ring's next TMA refill
                 named_bar_sync(2, kConsumerThreads);
@@ -380,7 +400,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll
                     for (int ks = 0; ks < D / 16; ++ks) {
                         uint32_t a[4];
-                        ldmatrix_x4(a, k_addr + tile_off(row, 2 * ks + (lane >> 4)));
+                        ldmatrix_x4(a, k_addr + tile_off<D>(row, 2 * ks + (lane >> 4), rpb_log2));
 #pragma unroll
                         for (int nt = 0; nt < NT; ++nt) mma_m16n8k16(c[nt], a, bq[nt][ks][0], bq[nt][ks][1]);
                     }
@@ -431,7 +451,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll
                     for (int mt = 0; mt < D / 16; ++mt) {
                         uint32_t a[4];
-                        ldmatrix_x4_trans(a, v_addr + tile_off(row, 2 * mt + ((lane >> 3) & 1)));
+                        ldmatrix_x4_trans(a, v_addr + tile_off<D>(row, 2 * mt + ((lane >> 3) & 1), rpb_log2));
 #pragma unroll
                         for (int nt = 0; nt < NT; ++nt) mma_m16n8k16(o[nt][mt], a, bp[nt][0], bp[nt][1]);
                     }
@@ -588,6 +608,22 @@ mf_status launch_one(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap 
             "cudaFuncSetAttribute(decode)");
         if (st != MF_OK) return st;
         configured[ctx->device] = true;
+    }
+    if (ctx->overlap_launches) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(n_ctas);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = S::kDynamic;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tm_k, tm_v, p);
+        if (e != cudaSuccess) return fail(ctx, MF_ERR_CUDA, "launch decode_kernel: %s", cudaGetErrorString(e));
+        ++ctx->launches;
+        return MF_OK;
     }
     kern<<<n_ctas, kThreads, S::kDynamic, ctx->stream>>>(tm_k, tm_v, p);
     return check_launch(ctx, "decode_kernel");

@@ -59,6 +59,8 @@ struct DecodeParams {
     uint32_t rope_position;  // contiguous mode: position of the query token
     uint32_t q_stride_b, q_stride_h, out_stride_b, out_stride_h;
     uint32_t knew_stride_b;  // elements between sequences in k_new / v_new
+    uint32_t whole_rows;     // 1: one TMA box per page fetches both halves (3-D tensor map)
+    uint32_t early_stream;   // 1: the producer may stream K/V before the previous kernel has finished
     float scale_log2;
 };
 
@@ -68,10 +70,11 @@ struct TensorMapKey {
     uint32_t cols;
     uint32_t box_rows;
     uint32_t box_cols;
+    uint32_t whole_rows;  // 1: 3-D map whose box spans both 64-column halves of a row
     bool operator==(const TensorMapKey &o) const
     {
         return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows &&
-               box_cols == o.box_cols;
+               box_cols == o.box_cols && whole_rows == o.whole_rows;
     }
 };
 struct TensorMapKeyHash {
@@ -80,7 +83,7 @@ struct TensorMapKeyHash {
         uint64_t h = reinterpret_cast<uint64_t>(k.base) * 0x9E3779B97F4A7C15ull;
         h ^= k.rows + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
         h ^= (uint64_t(k.cols) << 32 | k.box_rows) + (h << 6) + (h >> 2);
-        h ^= k.box_cols + (h << 6) + (h >> 2);
+        h ^= (k.box_cols * 2 + k.whole_rows) + (h << 6) + (h >> 2);
         return static_cast<size_t>(h);
     }
 };
@@ -100,6 +103,7 @@ struct MfContext {
     uint64_t launches = 0;
     std::unordered_map<mf::TensorMapKey, CUtensorMap, mf::TensorMapKeyHash> tmaps;
     void *encode_fn = nullptr;
+    uint32_t overlap_launches = 0;  // MF_OPTION_OVERLAP_LAUNCHES
 };
 
 struct MfDecodePlan {
@@ -136,10 +140,12 @@ inline __half *tensor_ptr(const MfTensor *t)
     return reinterpret_cast<__half *>(static_cast<char *>(t->dev_ptr) + t->offset_bytes);
 }
 
-// Cached 2-D f16 tensor map over [rows, cols] with a [box_rows, box_cols] box and
-// the 128-byte swizzle.
+// Cached f16 tensor map over [rows, cols] with the 128-byte swizzle.  whole_rows == 0: 2-D map,
+// box [box_rows, 64 cols].  whole_rows == 1 (cols == 128): 3-D map (64 cols, rows, 2 halves) whose
+// box [64, box_rows, 2] brings whole 256-byte rows in one copy, laid out [half][box_rows][128 B].
 mf_status get_tensor_map(MfContext *ctx, const void *base, uint64_t rows, uint32_t cols,
-                         uint32_t box_rows, uint32_t box_cols, CUtensorMap *out);
+                         uint32_t box_rows, uint32_t box_cols, CUtensorMap *out,
+                         uint32_t whole_rows = 0);
 
 mf_status ensure_scratch(MfContext *ctx, uint64_t bytes);
 

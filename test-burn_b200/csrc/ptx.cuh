@@ -99,6 +99,17 @@ __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const void *tmap,
         : "memory");
 }
 
+// 3-D tiled tensor load of one box; coordinates (x innermost, y, z).
+__device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const void *tmap, int32_t x, int32_t y,
+                                                 int32_t z, uint32_t bar, uint64_t policy)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        ".L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;" ::"r"(dst),
+        "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar), "l"(policy)
+        : "memory");
+}
+
 __device__ __forceinline__ uint64_t l2_policy_evict_first()
 {
     uint64_t p;
@@ -157,6 +168,18 @@ __device__ __forceinline__ float fast_exp2(float x)
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// Programmatic dependent launch: wait until the kernels this grid depends on have completed and
+// their memory is visible (no-op for a normally launched grid) / let the next grid in the stream
+// start being scheduled.
+__device__ __forceinline__ void grid_dependency_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 // Named barrier over `count` threads (count a multiple of 32), id 1..15.

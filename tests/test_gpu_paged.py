@@ -232,3 +232,31 @@ def test_paged_decode_rejects_bad_arguments(mfk, foundry):
     assert e.value.kind == "OperationNotSupported"
     plan.close()
     foundry.synchronize()
+
+
+def test_overlapped_launches_give_the_same_bits(mfk, foundry):
+    """MF_OPTION_OVERLAP_LAUNCHES: a chain of fused launches over several layers (separate pools,
+    shared plan, partial slots and tickets) must equal the plainly serialised chain."""
+    import torch
+
+    layers = 6
+    cases = [PagedCase(batch=5, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, seed=100 + i,
+                       cached=[511, 1000, 2049, 3, 4095]) for i in range(layers)]
+    results = {}
+    for overlap in (0, 1):
+        foundry.set_option(mfk.OPTION_OVERLAP_LAUNCHES, overlap)
+        dcs = [DeviceCase(mfk, c) for c in cases]
+        plan = foundry.decode_plan(cases[0].kv_lens, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16)
+        outs = [torch.zeros((5, 16 * 128), dtype=torch.float16, device="cuda") for _ in range(layers)]
+        for _ in range(3):
+            for c, dc, out in zip(cases, dcs, outs):
+                foundry.paged_decode(plan, dc.desc, dc.q, out, n_heads=16, k=dc.k, v=dc.v, cos=dc.cos, sin=dc.sin,
+                                     rope=True, append=True, scale=float(c.scale))
+        foundry.synchronize()
+        results[overlap] = [host(o) for o in outs] + [host(dc.k_pool) for dc in dcs]
+        plan.close()
+    foundry.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 0)
+    for a, b in zip(results[0], results[1]):
+        assert np.array_equal(a, b)
+    ref = cases[0].oracle_step()
+    assert max_abs(results[1][0], ref[3]) <= TOL
