@@ -46,6 +46,8 @@ WORKLOADS = {
                     "ctx U[512,16384], page 16, fused rope+append+decode"),
     "c3-small": dict(layers=4, n_heads=16, n_kv_heads=2, head_dim=128, batch=64, lo=512, hi=16384, page_size=16,
                      theta=1e6, rope_mode=0, name="c3 with 4 layers (profiling case)"),
+    "uniform148": dict(layers=4, n_heads=16, n_kv_heads=2, head_dim=128, batch=74, lo=8191, hi=8191, page_size=16,
+                       theta=1e6, rope_mode=0, name="experiment: 148 equal (sequence, kv head) units of 8192 keys"),
     "c2": dict(layers=28, n_heads=24, n_kv_heads=8, head_dim=128, batch=1, lo=8191, hi=8191, page_size=64,
                theta=5e5, rope_mode=1,
                name="Llama-3.2-3B shape decode step: 28 layers, 24q/8kv heads, D128, batch 1, ctx 8192, "
@@ -194,6 +196,8 @@ def run_ours(args, w):
     f = mfk.Foundry(dev.index, stream.cuda_stream)
     if not args.no_overlap:
         f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 1)
+    if args.stages:
+        f.set_option(2, args.stages)
     plan = f.decode_plan(kv_lens, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P)
     descs = [mfk.paged_kv(k_pools[i].view(n_pages, hkv, P, d), v_pools[i].view(n_pages, hkv, P, d), d_table, d_lens,
                           n_kv_heads=hkv, page_size=P, head_dim=d) for i in range(layers)]
@@ -403,6 +407,7 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-overlap", action="store_true", help="plain launches instead of programmatic dependent launch")
+    ap.add_argument("--stages", type=int, default=0, help="decode ring depth (experiments)")
     ap.add_argument("--page-size", type=int, default=0, help="override the workload's page size (experiments)")
     ap.add_argument("--sequential-pages", action="store_true", help="identity page table (experiments)")
     args = ap.parse_args()

@@ -237,8 +237,9 @@ MF_API uint64_t mf_launch_count(const MfContext *ctx);
  * append+decode launch then starts streaming K/V pages before the previous kernel in the
  * stream has finished; the caller promises that this previous kernel does not write the
  * pools, page table or lengths the launch reads (consecutive layers of a decode step never
- * do).  Everything else a launch reads or writes still waits for the previous kernel. */
-enum { MF_OPTION_OVERLAP_LAUNCHES = 1 };
+ * do).  Everything else a launch reads or writes still waits for the previous kernel.
+ * MF_OPTION_DECODE_STAGES = n: depth of the decode kernel's K/V tile ring (0 = default). */
+enum { MF_OPTION_OVERLAP_LAUNCHES = 1, MF_OPTION_DECODE_STAGES = 2 };
 MF_API mf_status mf_context_set_option(MfContext *ctx, uint32_t option, uint32_t value);
 /* Caller-provided scratch (device); when absent the context allocates its own
  * arena on first use and grows it on demand (pooled scratch of step.rs:927-929). */

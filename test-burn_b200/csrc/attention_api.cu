@@ -82,7 +82,8 @@ mf_status decode_contiguous(MfContext *ctx, const void *q, const void *k, const 
     if (n_splits > 0) {
         span = (T + n_splits - 1) / n_splits;
     } else {
-        const uint32_t want = (uint32_t)std::min<uint64_t>(total, (uint64_t)ctx->sm_count);
+        const uint32_t want = (uint32_t)std::min<uint64_t>(
+            total, (uint64_t)ctx->sm_count * decode_ctas_per_sm(ctx, D, group));
         span = (uint32_t)((total + want - 1) / want);
     }
     span = std::max(1u, span);
@@ -401,7 +402,7 @@ mf_status mf_decode_plan_create(MfContext *ctx, const uint32_t *kv_lens_host, ui
         return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "Flash Decode only supports head_dim=64 or 128, got %u", head_dim);
     if (n_heads / n_kv_heads > 16)
         return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "decode plan: group size %u > 16", n_heads / n_kv_heads);
-    if (max_ctas == 0) max_ctas = (uint32_t)ctx->sm_count;
+    if (max_ctas == 0) max_ctas = (uint32_t)ctx->sm_count * decode_ctas_per_sm(ctx, head_dim, n_heads / n_kv_heads);
     MfDecodePlan *pl = new MfDecodePlan();
     pl->batch = batch;
     pl->n_heads = n_heads;

@@ -42,7 +42,7 @@ struct Smem {
     static constexpr uint32_t kHP = 8 * NT;                    // padded heads per group
     static constexpr uint32_t kTileBytes = kTileKeys * D * 2;  // one K or V tile
     static constexpr uint32_t kStageBytes = 2 * kTileBytes;
-    static constexpr uint32_t kCombStride = D + 4;           // floats per head row
+    static constexpr uint32_t kCombStride = D / 2 + 4;       // floats per head row (half of D per pass)
     static constexpr uint32_t kQStride = D + 8;              // halves per head row
     static constexpr uint32_t kOffComb = STAGES * kStageBytes;
     static constexpr uint32_t kCombBytes = kConsumerWarps * kHP * kCombStride * 4;
@@ -130,8 +130,8 @@ __device__ __forceinline__ void rope_pair(float xi, float xj, float c, float s, 
     oj = __float2half_rn(__fadd_rn(__fmul_rn(xj, c), __fmul_rn(xi, s)));
 }
 
-template <int D, int NT, int STAGES>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int D, int NT, int STAGES, int MINB>
+__global__ void __launch_bounds__(kThreads, MINB)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
               const DecodeParams p)
 {
@@ -482,6 +482,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             }
         }
         named_bar_sync(1, kConsumerThreads);
+        float fac[NT][2];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             const uint32_t h0 = nt * 8 + 2 * (lane & 3);
@@ -491,54 +492,66 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                 ma0 = fmaxf(ma0, ml_s[(w * HP + h0) * 2]);
                 ma1 = fmaxf(ma1, ml_s[(w * HP + h0 + 1) * 2]);
             }
-            const float f0 = fast_exp2(m_run[nt][0] - ma0), f1 = fast_exp2(m_run[nt][1] - ma1);
-            float *c0 = comb + (warp * HP + h0) * S::kCombStride;
-            float *c1 = c0 + S::kCombStride;
-#pragma unroll
-            for (int mt = 0; mt < D / 16; ++mt) {
-                const uint32_t d0 = mt * 16 + (lane >> 2);
-                c0[d0] = o[nt][mt][0] * f0;
-                c1[d0] = o[nt][mt][1] * f1;
-                c0[d0 + 8] = o[nt][mt][2] * f0;
-                c1[d0 + 8] = o[nt][mt][3] * f1;
-            }
+            fac[nt][0] = fast_exp2(m_run[nt][0] - ma0);
+            fac[nt][1] = fast_exp2(m_run[nt][1] - ma1);
         }
-        named_bar_sync(2, kConsumerThreads);
 
         const bool direct = (it.n_parts == 1);
         const bool partial_out = (p.out_acc != nullptr);
-        for (uint32_t e = tid; e < HP * D; e += kConsumerThreads) {
-            const uint32_t g = e / D, d = e - g * D;
-            float m_all = kNegSentinel;
+        // The four warps' accumulators meet in shared memory, one half of the head dimension per
+        // pass (the buffer is half-width so that two CTAs fit one SM).
 #pragma unroll
-            for (uint32_t w = 0; w < kConsumerWarps; ++w) m_all = fmaxf(m_all, ml_s[(w * HP + g) * 2]);
-            float l_all = 0.f, acc = 0.f;
+        for (int hp = 0; hp < 2; ++hp) {
 #pragma unroll
-            for (uint32_t w = 0; w < kConsumerWarps; ++w) {
-                l_all += ml_s[(w * HP + g) * 2 + 1] * fast_exp2(ml_s[(w * HP + g) * 2] - m_all);
-                acc += comb[(w * HP + g) * S::kCombStride + d];
-            }
-            const uint32_t h = it.kvh * G + g;
-            if (!direct) {
-                p.part_acc[((size_t)it.slot * HP + g) * D + d] = acc;
-                if (d == 0) {
-                    p.part_ml[((size_t)it.slot * HP + g) * 2] = m_all * kLn2;
-                    p.part_ml[((size_t)it.slot * HP + g) * 2 + 1] = l_all;
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint32_t h0 = nt * 8 + 2 * (lane & 3);
+                float *c0 = comb + (warp * HP + h0) * S::kCombStride;
+                float *c1 = c0 + S::kCombStride;
+#pragma unroll
+                for (int mh = 0; mh < D / 32; ++mh) {
+                    const int mt = hp * (D / 32) + mh;
+                    const uint32_t d0 = mh * 16 + (lane >> 2);
+                    c0[d0] = o[nt][mt][0] * fac[nt][0];
+                    c1[d0] = o[nt][mt][1] * fac[nt][1];
+                    c0[d0 + 8] = o[nt][mt][2] * fac[nt][0];
+                    c1[d0 + 8] = o[nt][mt][3] * fac[nt][1];
                 }
-            } else if (g < G) {
-                if (partial_out) {
-                    p.out_acc[((size_t)it.seq * p.n_heads + h) * D + d] = acc;
+            }
+            named_bar_sync(2, kConsumerThreads);
+            for (uint32_t e = tid; e < HP * (D / 2); e += kConsumerThreads) {
+                const uint32_t g = e / (D / 2), dd = e - g * (D / 2), d = hp * (D / 2) + dd;
+                float m_all = kNegSentinel;
+#pragma unroll
+                for (uint32_t w = 0; w < kConsumerWarps; ++w) m_all = fmaxf(m_all, ml_s[(w * HP + g) * 2]);
+                float l_all = 0.f, acc = 0.f;
+#pragma unroll
+                for (uint32_t w = 0; w < kConsumerWarps; ++w) {
+                    l_all += ml_s[(w * HP + g) * 2 + 1] * fast_exp2(ml_s[(w * HP + g) * 2] - m_all);
+                    acc += comb[(w * HP + g) * S::kCombStride + dd];
+                }
+                const uint32_t h = it.kvh * G + g;
+                if (!direct) {
+                    p.part_acc[((size_t)it.slot * HP + g) * D + d] = acc;
                     if (d == 0) {
-                        p.out_m[(size_t)it.seq * p.n_heads + h] = m_all * kLn2;
-                        p.out_l[(size_t)it.seq * p.n_heads + h] = l_all;
+                        p.part_ml[((size_t)it.slot * HP + g) * 2] = m_all * kLn2;
+                        p.part_ml[((size_t)it.slot * HP + g) * 2 + 1] = l_all;
                     }
-                } else {
-                    const bool ok = (fabsf(l_all) <= 3.0e38f) && fabsf(l_all) > 1e-6f;
-                    float r = ok ? acc / l_all : acc;
-                    if (!(fabsf(r) <= 3.0e38f)) r = 0.f;
-                    p.out[(size_t)it.seq * p.out_stride_b + (size_t)h * p.out_stride_h + d] = __float2half_rn(r);
+                } else if (g < G) {
+                    if (partial_out) {
+                        p.out_acc[((size_t)it.seq * p.n_heads + h) * D + d] = acc;
+                        if (d == 0) {
+                            p.out_m[(size_t)it.seq * p.n_heads + h] = m_all * kLn2;
+                            p.out_l[(size_t)it.seq * p.n_heads + h] = l_all;
+                        }
+                    } else {
+                        const bool ok = (fabsf(l_all) <= 3.0e38f) && fabsf(l_all) > 1e-6f;
+                        float r = ok ? acc / l_all : acc;
+                        if (!(fabsf(r) <= 3.0e38f)) r = 0.f;
+                        p.out[(size_t)it.seq * p.out_stride_b + (size_t)h * p.out_stride_h + d] = __float2half_rn(r);
+                    }
                 }
             }
+            if (hp == 0) named_bar_sync(1, kConsumerThreads);  // pass 1 reuses the buffer
         }
         if (direct) continue;
 
@@ -554,54 +567,99 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         named_bar_sync(2, kConsumerThreads);
         if (!flags[1]) continue;
         __threadfence();
-        if (tid < HP) {
-            float mx = kNegSentinel;
-            for (uint32_t s = 0; s < it.n_parts; ++s)
-                mx = fmaxf(mx, __ldcg(p.part_ml + ((size_t)(it.first_slot + s) * HP + tid) * 2));
-            float lt = 0.f;
-            for (uint32_t s = 0; s < it.n_parts; ++s) {
-                const float ms = __ldcg(p.part_ml + ((size_t)(it.first_slot + s) * HP + tid) * 2);
-                const float ls = __ldcg(p.part_ml + ((size_t)(it.first_slot + s) * HP + tid) * 2 + 1);
-                if (ls > 0.f) lt += ls * __expf(ms - mx);
+        // Merge (flash_prefill.metal:843-888), arranged so that the loads of one round trip are all
+        // in flight together: this runs at the end of a CTA's work, where latency is not hidden.
+        constexpr uint32_t kMergeCap = 64;                       // parts whose m is cached in smem
+        constexpr uint32_t kPerHead = kConsumerThreads / HP;     // threads per head in pass 1
+        constexpr uint32_t EPT = HP * D / kConsumerThreads;      // consecutive outputs per thread
+        float *msv = comb;                                       // [kMergeCap][HP]
+        float *red = comb + kMergeCap * HP;                      // [threads][2]
+        {
+            const uint32_t g1 = tid % HP;
+            float m_loc = kNegSentinel, l_loc = 0.f;
+            for (uint32_t sp = tid / HP; sp < it.n_parts; sp += kPerHead) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2 *>(p.part_ml) + (size_t)(it.first_slot + sp) * HP + g1);
+                if (sp < kMergeCap) msv[sp * HP + g1] = ml.x;
+                const float mn = fmaxf(m_loc, ml.x);
+                l_loc = l_loc * __expf(m_loc - mn) + (ml.y > 0.f ? ml.y * __expf(ml.x - mn) : 0.f);
+                m_loc = mn;
             }
-            merge_s[tid * 2] = mx;
-            merge_s[tid * 2 + 1] = lt;
+            red[tid * 2] = m_loc;
+            red[tid * 2 + 1] = l_loc;
         }
         named_bar_sync(1, kConsumerThreads);
-        for (uint32_t e = tid; e < HP * D; e += kConsumerThreads) {
-            const uint32_t g = e / D, d = e - g * D;
-            if (g >= G) continue;
-            const float mx = merge_s[g * 2], lt = merge_s[g * 2 + 1];
-            float acc = 0.f;
-            for (uint32_t s = 0; s < it.n_parts; ++s) {
-                const size_t sl = it.first_slot + s;
-                const float ms = __ldcg(p.part_ml + (sl * HP + g) * 2);
-                acc += __ldcg(p.part_acc + (sl * HP + g) * D + d) * __expf(ms - mx);
+        const uint32_t g2 = (tid * EPT) / D, d0 = (tid * EPT) % D;
+        float mx = kNegSentinel, lt = 0.f;
+#pragma unroll
+        for (uint32_t j = 0; j < kPerHead; ++j) mx = fmaxf(mx, red[(j * HP + g2) * 2]);
+#pragma unroll
+        for (uint32_t j = 0; j < kPerHead; ++j) lt += red[(j * HP + g2) * 2 + 1] * __expf(red[(j * HP + g2) * 2] - mx);
+        float acc[EPT];
+#pragma unroll
+        for (uint32_t i = 0; i < EPT; ++i) acc[i] = 0.f;
+        for (uint32_t s0 = 0; s0 < it.n_parts; s0 += 4) {
+            float4 v[4][EPT / 4];
+            float w[4];
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+                const uint32_t sp = s0 + j;
+                if (sp < it.n_parts) {
+                    const size_t sl = it.first_slot + sp;
+                    const float4 *src = reinterpret_cast<const float4 *>(p.part_acc + (sl * HP + g2) * D + d0);
+#pragma unroll
+                    for (uint32_t q4 = 0; q4 < EPT / 4; ++q4) v[j][q4] = __ldcg(src + q4);
+                    const float ms = sp < kMergeCap ? msv[sp * HP + g2] : __ldcg(p.part_ml + (sl * HP + g2) * 2);
+                    w[j] = __expf(ms - mx);
+                } else {
+#pragma unroll
+                    for (uint32_t q4 = 0; q4 < EPT / 4; ++q4) v[j][q4] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    w[j] = 0.f;
+                }
             }
-            const uint32_t h = it.kvh * G + g;
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+#pragma unroll
+                for (uint32_t q4 = 0; q4 < EPT / 4; ++q4) {
+                    acc[q4 * 4 + 0] += v[j][q4].x * w[j];
+                    acc[q4 * 4 + 1] += v[j][q4].y * w[j];
+                    acc[q4 * 4 + 2] += v[j][q4].z * w[j];
+                    acc[q4 * 4 + 3] += v[j][q4].w * w[j];
+                }
+            }
+        }
+        if (g2 < G) {
+            const uint32_t h = it.kvh * G + g2;
             if (partial_out) {
-                p.out_acc[((size_t)it.seq * p.n_heads + h) * D + d] = acc;
-                if (d == 0) {
+                float *dst = p.out_acc + ((size_t)it.seq * p.n_heads + h) * D + d0;
+#pragma unroll
+                for (uint32_t i = 0; i < EPT; ++i) dst[i] = acc[i];
+                if (d0 == 0) {
                     p.out_m[(size_t)it.seq * p.n_heads + h] = mx;
                     p.out_l[(size_t)it.seq * p.n_heads + h] = lt;
                 }
             } else {
                 const bool ok = (fabsf(lt) <= 3.0e38f) && fabsf(lt) > 1e-6f;
-                float r = ok ? acc / lt : 0.f;  // merge rule: flash_prefill.metal:861
-                if (!(fabsf(r) <= 3.0e38f)) r = 0.f;
-                p.out[(size_t)it.seq * p.out_stride_b + (size_t)h * p.out_stride_h + d] = __float2half_rn(r);
+                const float inv = ok ? 1.0f / lt : 0.f;  // merge rule: flash_prefill.metal:861
+                __half *dst = p.out + (size_t)it.seq * p.out_stride_b + (size_t)h * p.out_stride_h + d0;
+#pragma unroll
+                for (uint32_t i = 0; i < EPT; ++i) {
+                    float r = acc[i] * inv;
+                    if (!(fabsf(r) <= 3.0e38f)) r = 0.f;
+                    dst[i] = __float2half_rn(r);
+                }
             }
         }
     }
 }
 
-template <int D, int NT, int STAGES>
+template <int D, int NT, int STAGES, int MINB>
 mf_status launch_one(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap &tm_v,
                      const DecodeParams &p, uint32_t n_ctas)
 {
     using S = Smem<D, NT, STAGES>;
+    static_assert(MINB * (S::kDynamic + 1024) <= 228 * 1024, "CTAs per SM do not fit shared memory");
     static bool configured[64] = {};
-    auto kern = decode_kernel<D, NT, STAGES>;
+    auto kern = decode_kernel<D, NT, STAGES, MINB>;
     if (ctx->device < 64 && !configured[ctx->device]) {
         mf_status st = check_cuda(
             ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic),
@@ -631,18 +689,28 @@ mf_status launch_one(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap 
 
 }  // namespace
 
+uint32_t decode_ctas_per_sm(const MfContext *ctx, uint32_t head_dim, uint32_t group)
+{
+    if (group > 8) return 1;
+    if (head_dim == 128 && ctx && ctx->decode_stages == 6) return 1;
+    return 2;
+}
+
 mf_status launch_decode(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap &tm_v,
                         const DecodeParams &p, uint32_t head_dim, uint32_t n_ctas)
 {
     const uint32_t nt = (p.group + 7) / 8;
     if (nt > 2) return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "decode: group size %u > 16", p.group);
+    // Groups of up to 8 query heads: two CTAs per SM, each with a short ring, so that one CTA's
+    // span boundary (combine, partial write, merge, q load) overlaps the other's tile stream.
     if (head_dim == 128) {
-        return nt == 1 ? launch_one<128, 1, 6>(ctx, tm_k, tm_v, p, n_ctas)
-                       : launch_one<128, 2, 5>(ctx, tm_k, tm_v, p, n_ctas);
+        if (nt == 1 && ctx->decode_stages == 6) return launch_one<128, 1, 6, 1>(ctx, tm_k, tm_v, p, n_ctas);
+        return nt == 1 ? launch_one<128, 1, 3, 2>(ctx, tm_k, tm_v, p, n_ctas)
+                       : launch_one<128, 2, 5, 1>(ctx, tm_k, tm_v, p, n_ctas);
     }
     if (head_dim == 64) {
-        return nt == 1 ? launch_one<64, 1, 8>(ctx, tm_k, tm_v, p, n_ctas)
-                       : launch_one<64, 2, 8>(ctx, tm_k, tm_v, p, n_ctas);
+        return nt == 1 ? launch_one<64, 1, 6, 2>(ctx, tm_k, tm_v, p, n_ctas)
+                       : launch_one<64, 2, 8, 1>(ctx, tm_k, tm_v, p, n_ctas);
     }
     return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "Flash Decode only supports head_dim=64 or 128, got %u",
                 head_dim);
@@ -746,18 +814,18 @@ mf_status static_fail(char *buf, uint32_t len, mf_status code, const char *fmt, 
     return code;
 }
 
-template <int D, int NT, int STAGES>
+template <int D, int NT, int STAGES, int MINB>
 cudaError_t static_prepare_kernel()
 {
-    return cudaFuncSetAttribute(decode_kernel<D, NT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    return cudaFuncSetAttribute(decode_kernel<D, NT, STAGES, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 Smem<D, NT, STAGES>::kDynamic);
 }
 
-template <int D, int NT, int STAGES>
+template <int D, int NT, int STAGES, int MINB>
 cudaError_t static_launch(const CUtensorMap &tm_k, const CUtensorMap &tm_v, const DecodeParams &p, uint32_t n_ctas,
                           cudaStream_t stream)
 {
-    decode_kernel<D, NT, STAGES><<<n_ctas, kThreads, Smem<D, NT, STAGES>::kDynamic, stream>>>(tm_k, tm_v, p);
+    decode_kernel<D, NT, STAGES, MINB><<<n_ctas, kThreads, Smem<D, NT, STAGES>::kDynamic, stream>>>(tm_k, tm_v, p);
     return cudaGetLastError();
 }
 
@@ -781,8 +849,8 @@ mf_status static_setup(int device, char *err, uint32_t err_len)
         q != cudaDriverEntryPointSuccess || !fn)
         return static_fail(err, err_len, MF_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
     st.encode = reinterpret_cast<StaticEncodeFn>(fn);
-    if (static_prepare_kernel<128, 1, 6>() != cudaSuccess || static_prepare_kernel<128, 2, 5>() != cudaSuccess ||
-        static_prepare_kernel<64, 1, 8>() != cudaSuccess || static_prepare_kernel<64, 2, 8>() != cudaSuccess)
+    if (static_prepare_kernel<128, 1, 3, 2>() != cudaSuccess || static_prepare_kernel<128, 2, 5, 1>() != cudaSuccess ||
+        static_prepare_kernel<64, 1, 6, 2>() != cudaSuccess || static_prepare_kernel<64, 2, 8, 1>() != cudaSuccess)
         return static_fail(err, err_len, MF_ERR_CUDA, "cudaFuncSetAttribute(decode) failed");
     st.scratch = static_cast<unsigned char *>(ptr);
     st.ready = true;
@@ -849,7 +917,8 @@ extern "C" mf_status mf_flash_decode_static_scratch(void *cuda_stream, const voi
     const uint64_t U = (uint64_t)batch * cache_heads;
     const uint64_t total = U * T;
     if (total > 0xFFFFFFFFull) return static_fail(err, err_len, MF_ERR_OPERATION_NOT_SUPPORTED, "too many tiles");
-    const uint64_t want = total < (uint64_t)dst.sm_count ? total : (uint64_t)dst.sm_count;
+    const uint64_t resident = (uint64_t)dst.sm_count * (group > 8 ? 1 : 2);  // the rule of mf_flash_decode
+    const uint64_t want = total < resident ? total : resident;
     const uint32_t span = (uint32_t)((total + want - 1) / want);
     const uint32_t n_ctas = (uint32_t)((total + span - 1) / span);
     const uint32_t HP = 8 * ((group + 7) / 8);
@@ -901,9 +970,9 @@ extern "C" mf_status mf_flash_decode_static_scratch(void *cuda_stream, const voi
     const uint32_t nt = (group + 7) / 8;
     cudaError_t e;
     if (D == 128)
-        e = nt == 1 ? static_launch<128, 1, 6>(tm_k, tm_v, p, n_ctas, stream) : static_launch<128, 2, 5>(tm_k, tm_v, p, n_ctas, stream);
+        e = nt == 1 ? static_launch<128, 1, 3, 2>(tm_k, tm_v, p, n_ctas, stream) : static_launch<128, 2, 5, 1>(tm_k, tm_v, p, n_ctas, stream);
     else
-        e = nt == 1 ? static_launch<64, 1, 8>(tm_k, tm_v, p, n_ctas, stream) : static_launch<64, 2, 8>(tm_k, tm_v, p, n_ctas, stream);
+        e = nt == 1 ? static_launch<64, 1, 6, 2>(tm_k, tm_v, p, n_ctas, stream) : static_launch<64, 2, 8, 1>(tm_k, tm_v, p, n_ctas, stream);
     if (e != cudaSuccess) return static_fail(err, err_len, MF_ERR_CUDA, "decode launch failed (%llu)", (unsigned long long)e);
     return MF_OK;
 }

@@ -104,6 +104,7 @@ struct MfContext {
     std::unordered_map<mf::TensorMapKey, CUtensorMap, mf::TensorMapKeyHash> tmaps;
     void *encode_fn = nullptr;
     uint32_t overlap_launches = 0;  // MF_OPTION_OVERLAP_LAUNCHES
+    uint32_t decode_stages = 0;     // MF_OPTION_DECODE_STAGES (0 = default)
 };
 
 struct MfDecodePlan {
@@ -154,6 +155,9 @@ void build_decode_plan(const uint32_t *kv_lens, uint32_t batch, uint32_t n_kv_he
                        uint32_t max_ctas, std::vector<WorkItem> &items,
                        std::vector<uint32_t> &cta_begin, uint32_t *n_units,
                        uint64_t *total_tiles);
+
+// Resident decode CTAs per SM for a head_dim / GQA group size (decode.cu).
+uint32_t decode_ctas_per_sm(const MfContext *ctx, uint32_t head_dim, uint32_t group);
 
 // Launchers (decode.cu, prefill.cu, kv_append.cu).
 mf_status launch_decode(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap &tm_v,
