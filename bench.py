@@ -57,7 +57,7 @@ SEED = 0x5EED
 METRIC = "kv_append_decode_attn_tokens_per_s"
 # DRAM bytes moved by the decode kernel per algorithmic byte, from the ncu capture summarised in
 # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the same launch).
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = None
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0072  # profiles/decode_kernel_c3_paged_decode.md
 
 
 def measured_peak_gbs():
@@ -308,7 +308,7 @@ def run_ours(args, w):
                    % (2 * layers * pool_elems * 2 / 1e9), "ctas": plan.ctas, "work_items": plan.items},
         "hbm_tb_s": achieved / 1e3,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": peak_kind, "kernel": "decode_kernel<128,1,6>", "launch_us": launch_us,
+                     "peak_kind": peak_kind, "kernel": "decode_kernel<128,1,3,2>", "launch_us": launch_us,
                      "algorithmic_bytes_per_launch": bytes_layer,
                      "traffic": (bytes_layer * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE
                                  if NCU_TRAFFIC_PER_ALGORITHMIC_BYTE else None)},
