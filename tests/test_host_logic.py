@@ -1,0 +1,141 @@
+"""CPU tests (no GPU): the C ABI loads and exports every declared symbol, the host-side logic
+gives the reference's known answers, and the step planner keeps its invariants."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "metallic_cuda.h").read_text()
+    return sorted(set(re.findall(r"MF_API\s+[\w\s\*]+?\b(mf_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(mfk):
+    names = declared_symbols()
+    assert len(names) >= 35
+    for n in names:
+        assert hasattr(mfk.lib, n), f"{n} is declared in include/metallic_cuda.h but not exported"
+    assert sorted(mfk.EXPORTED_SYMBOLS) == names, "the Python binding must cover exactly the declared symbols"
+    assert mfk.lib.mf_abi_version() == 1
+
+
+def test_no_cpu_fallback(mfk):
+    """Without an sm_100 device a context cannot be created; nothing computes on the CPU."""
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    with pytest.raises(mfk.MetalError):
+        mfk.Foundry()
+
+
+def test_param_struct_layouts(mfk):
+    """The #[repr(C)] parameter structs are plain 4-byte fields with no padding."""
+    assert C.sizeof(mfk.KvPrepFusedParamsResolved) == 13 * 4  # kv_prep/mod.rs:79-114
+    assert C.sizeof(mfk.RopeParamsResolved) == 4 * 4          # rope/mod.rs:11-22
+    assert C.sizeof(mfk.KvCacheWriteParamsResolved) == 7 * 4  # kv_cache_write/mod.rs:61-78
+    assert C.sizeof(mfk.KvCacheWriteRepeatKvHeadsParamsResolved) == 9 * 4
+    assert C.sizeof(mfk.SdpaParams) == 5 * 4                  # flashattention/stages.rs:456-464
+    assert C.sizeof(mfk.SdpaPrefillParams) == 18 * 4          # stages.rs:240-270
+    assert C.sizeof(mfk.SdpaPrefillSplitKParams) == 20 * 4    # stages.rs:272-306
+    assert mfk.SdpaParams.scale.offset == 8 and mfk.SdpaPrefillParams.query_offset.offset == 20
+    assert mfk.KvPrepFusedParamsResolved.rope_mode.offset == 40
+    assert C.sizeof(mfk.MfTensor) == 8 + 8 + 4 + 4 + 32 + 32
+
+
+def test_align_capacity_known_answers(mfk):
+    """ContextConfig::align_capacity test (src/model/context.rs:308-316)."""
+    for n, want in [(0, 128), (1, 128), (127, 128), (128, 128), (129, 256), (200, 256)]:
+        assert mfk.align_capacity(n) == want
+
+
+def test_memory_estimate_known_answer(mfk):
+    """test_memory_estimation (src/model/context.rs:318-324): 4 layers, 2 kv heads, D 64, ctx 2048."""
+    assert mfk.lib.mf_estimate_kv_memory(4, 2, 64, 2048) == 4194304
+    # per_token_bytes_f16 (kv_geometry.rs:82-89) for Llama-3.2-3B compact: 28 * 2 * 8 * 128 * 2
+    assert mfk.lib.mf_kv_per_token_bytes_f16(28, 8, 128) == 28 * 2 * 8 * 128 * 2
+    # configuration 2: 28 layers of [8, 8192, 128] f16 K and V = 896 MiB
+    assert mfk.lib.mf_estimate_kv_memory(28, 8, 128, 8192) == 896 * 1024 * 1024
+
+
+def test_growth_rule(mfk):
+    """ensure_kv_capacity (src/model/executor.rs:2332-2396): keep, double, clamp, align."""
+    assert mfk.grown_capacity(2048, 100, 8192) == 2048          # already sufficient
+    assert mfk.grown_capacity(2048, 2049, 8192) == 4096         # x2
+    assert mfk.grown_capacity(2048, 5000, 8192) == 5120         # required > 2x, aligned to 128
+    assert mfk.grown_capacity(4096, 4097, 6000) == 6016         # clamped to max, then aligned
+    assert mfk.grown_capacity(2048, 9000, 8192) == 0            # exceeds the context limit
+
+
+def test_prefill_split_k_heuristic(mfk):
+    """src/metals/flashattention/step.rs:849-866."""
+    assert mfk.prefill_split_k(4096, 2048) == 8
+    assert mfk.prefill_split_k(4096, 16) == 8
+    assert mfk.prefill_split_k(4096, 15) == 1
+    assert mfk.prefill_split_k(2048, 64) == 4
+    assert mfk.prefill_split_k(2047, 64) == 1
+    assert mfk.prefill_split_k(1024, 32) == 1
+    assert mfk.prefill_split_k(33, 33) == 1
+
+
+def test_rope_tables_match_oracle(mfk, orc):
+    for theta, d, n in [(1e4, 64, 64), (1e6, 64, 512), (5e5, 128, 300)]:
+        cos, sin = mfk.rope_tables(theta, d, n)
+        c2, s2 = orc.rope_tables(theta, d, n)
+        assert np.array_equal(cos, c2) and np.array_equal(sin, s2)
+    ff = np.linspace(1, 4, 64).astype(np.float32)
+    cos, sin = mfk.rope_tables(5e5, 128, 40, first_pos=1000, freq_factors=ff)
+    c2, s2 = orc.rope_tables(5e5, 128, 40, first_pos=1000, freq_factors=ff)
+    assert np.array_equal(cos, c2) and np.array_equal(sin, s2)
+
+
+def check_plan(items, cta_begin, kv_lens, n_kv_heads, max_ctas):
+    tiles = (np.asarray(kv_lens, np.int64) + 63) // 64
+    total = int(tiles.sum()) * n_kv_heads
+    n_ctas = len(cta_begin) - 1
+    assert n_ctas == min(max_ctas, total) or total == 0
+    if total == 0:
+        assert len(items) == 0
+        return
+    assert cta_begin[0] == 0 and cta_begin[-1] == len(items) and np.all(np.diff(cta_begin) >= 0)
+    per_cta = [int(sum(items[i, 3] - items[i, 2] for i in range(cta_begin[c], cta_begin[c + 1]))) for c in range(n_ctas)]
+    assert max(per_cta) - min(per_cta) <= 1 and sum(per_cta) == total  # equal spans
+    # every (sequence, kv head) unit is covered exactly once, in order, by consecutive slots
+    seen = {}
+    for i, (seq, kvh, tb, te, slot, unit, n_parts, first_slot) in enumerate(items.tolist()):
+        assert te > tb and unit == seq * n_kv_heads + kvh and slot == i
+        cov = seen.setdefault(unit, [])
+        assert tb == (cov[-1][1] if cov else 0)
+        cov.append((tb, te))
+        assert first_slot == slot - (len(cov) - 1)
+    for unit, cov in seen.items():
+        assert cov[-1][1] == tiles[unit // n_kv_heads]
+        assert all(items[i, 6] == len(cov) for i in range(len(items)) if items[i, 5] == unit)
+    assert len(seen) == int((tiles > 0).sum()) * n_kv_heads
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_decode_plan_invariants(mfk, seed):
+    rng = np.random.default_rng(seed)
+    batch = int(rng.integers(1, 70))
+    lens = rng.integers(0, 20000, size=batch).astype(np.uint32)
+    if seed == 0:
+        lens[:] = 0
+    if seed == 1:
+        lens = np.array([1], np.uint32)
+    for n_kv_heads, max_ctas in [(2, 148), (8, 296), (1, 7), (2, 100000)]:
+        items, cta_begin = mfk.build_decode_plan_host(lens, n_kv_heads, max_ctas)
+        check_plan(items, cta_begin, lens, n_kv_heads, max_ctas)
+
+
+def test_decode_plan_c3_shape(mfk):
+    rng = np.random.default_rng(0x5EED)
+    lens = rng.integers(512, 16385, size=64).astype(np.uint32) + 1
+    items, cta_begin = mfk.build_decode_plan_host(lens, 2, 296)
+    check_plan(items, cta_begin, lens, 2, 296)
+    assert len(items) <= 128 + 296
