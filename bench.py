@@ -53,6 +53,15 @@ WORKLOADS = {
                name="Llama-3.2-3B shape decode step: 28 layers, 24q/8kv heads, D128, batch 1, ctx 8192, "
                     "cache as 64-token pages in order"),
 }
+LONG_CONTEXT = {
+    # sequence-sharded single-sequence decode (strong scaling): pages of ONE sequence are cut into
+    # contiguous ranges over the ranks; per layer one all-gather of (acc, m, l) and the merge.
+    "c5": dict(layers=28, n_heads=24, n_kv_heads=8, head_dim=128, kv_len=131072, page_size=64, theta=5e5, rope_mode=1,
+               name="long-context single-sequence decode, Llama-3.2-3B shape: 28 layers, 24q/8kv heads, D128, "
+                    "131072 cached tokens, page 64, sequence-sharded with (O,m,l) all-gather + merge"),
+    "c5-small": dict(layers=4, n_heads=24, n_kv_heads=8, head_dim=128, kv_len=131072, page_size=64, theta=5e5,
+                     rope_mode=1, name="c5 with 4 layers (test case)"),
+}
 SEED = 0x5EED
 METRIC = "kv_append_decode_attn_tokens_per_s"
 # DRAM bytes moved by the decode kernel per algorithmic byte, from the ncu capture summarised in
@@ -332,6 +341,132 @@ def run_ours(args, w):
     return 0 if ok else 1
 
 
+def run_long_context(args, w):
+    """Configuration 5: one long sequence, pages sharded over the ranks."""
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local if world > 1 else 0)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    mfk = importlib.import_module("test-burn_b200")
+    sharding = importlib.import_module("test-burn_b200.sharding")
+    layers, hq, hkv, d, P, L = w["layers"], w["n_heads"], w["n_kv_heads"], w["head_dim"], w["page_size"], w["kv_len"]
+    n_pages = (L + P - 1) // P
+    b, e = sharding.shard_pages(n_pages, world, rank)
+    n_local = sharding.shard_local_len(L, P, b, e)
+    owner = sharding.tail_owner(L, P, n_pages, world)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(SEED + rank)
+    pool_elems = (e - b) * hkv * P * d
+    k_pools = [torch.empty(pool_elems, dtype=torch.float16, device=dev).normal_(generator=gen) for _ in range(layers)]
+    v_pools = [torch.empty(pool_elems, dtype=torch.float16, device=dev).normal_(generator=gen) for _ in range(layers)]
+    table = torch.arange(e - b, dtype=torch.int32, device=dev).view(1, -1)
+    lens_host = np.array([n_local], np.uint32)
+    d_lens = torch.from_numpy(lens_host.view(np.int32)).to(dev)
+    d_pos = torch.tensor([L - 1], dtype=torch.int32, device=dev)
+    cos_np, sin_np = mfk.rope_tables(w["theta"], d, L)
+    d_cos = torch.from_numpy(cos_np.view(np.float16)).to(dev)
+    d_sin = torch.from_numpy(sin_np.view(np.float16)).to(dev)
+    g = torch.Generator().manual_seed(SEED)  # the token is the same on every rank
+    q = torch.randn((layers, 1, hq * d), generator=g).half().to(dev)
+    k = torch.randn((layers, 1, hkv * d), generator=g).half().to(dev)
+    v = torch.randn((layers, 1, hkv * d), generator=g).half().to(dev)
+    out = torch.zeros((layers, hq, d), dtype=torch.float16, device=dev)
+    stream = torch.cuda.Stream(device=dev)
+    f = mfk.Foundry(dev.index, stream.cuda_stream)
+    plan = f.decode_plan(lens_host, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P)
+    descs = [mfk.paged_kv(k_pools[i].view(e - b, hkv, P, d), v_pools[i].view(e - b, hkv, P, d), table, d_lens,
+                          n_kv_heads=hkv, page_size=P, head_dim=d) for i in range(layers)]
+    block = hq * (d + 2)
+    mine = torch.zeros(block, dtype=torch.float32, device=dev)
+    mine[hq * d:hq * d + hq] = -1e30  # a shard without keys contributes nothing
+    acc, m, l = mine[:hq * d].view(1, hq, d), mine[hq * d:hq * d + hq], mine[hq * d + hq:]
+    gathered = torch.empty((world, block), dtype=torch.float32, device=dev)
+    scale = 1.0 / math.sqrt(d)
+    append_here = rank == owner
+
+    def step():
+        with torch.cuda.stream(stream):
+            for i in range(layers):
+                if n_local:
+                    f.paged_decode_partial(plan, descs[i], q[i], acc, m, l, n_heads=hq, rope_positions=d_pos,
+                                           scale=scale, k=k[i] if append_here else None,
+                                           v=v[i] if append_here else None, cos=d_cos, sin=d_sin, rope=True,
+                                           rope_mode=w["rope_mode"], append=append_here)
+                if world > 1:
+                    dist.all_gather_into_tensor(gathered.view(-1), mine)
+                else:
+                    gathered.view(-1).copy_(mine, non_blocking=True)
+                f.merge_gathered(gathered, hq, d, out[i])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    f.synchronize()
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    time.sleep(0.3)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = f.launch_count
+    barrier()
+    t0 = time.time()
+    start.record(stream)
+    for _ in range(args.steps):
+        step()
+    stop.record(stream)
+    barrier()
+    t1 = time.time()
+    ms = start.elapsed_time(stop)
+    launches = f.launch_count - launches0
+    if world > 1:
+        t = torch.tensor([ms, launches], dtype=torch.float64, device=dev)
+        dist.all_reduce(t[:1], op=dist.ReduceOp.MAX)
+        dist.all_reduce(t[1:])
+        ms, launches = float(t[0]), int(t[1])
+    f.synchronize()
+    clocks = sampler.stop(t0, t1)
+    ms_step = ms / args.steps
+    bytes_layer_rank = 2 * hkv * (L // world) * d * 2
+    launch_us = ms_step * 1e3 / layers
+    achieved = bytes_layer_rank / (launch_us * 1e-6) / 1e9
+    peak, peak_kind = measured_peak_gbs()
+    # all ranks hold the same result; it must be finite and equal across ranks
+    ok = bool(torch.isfinite(out.float()).all())
+    if world > 1:
+        ref = out.clone()
+        dist.broadcast(ref, 0)
+        ok = ok and bool(torch.equal(ref, out))
+    result = {
+        "metric": METRIC, "value": 1.0 / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "us_per_step": ms_step * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
+        "config": {"workload": w["name"], "layers": layers, "kv_len": L, "pages_per_rank": e - b,
+                   "l2": "inputs larger than L2 (KV pools %.1f GB per GPU)" % (2 * layers * pool_elems * 2 / 1e9),
+                   "ctas": plan.ctas, "collective": "ncclAllGather of %d bytes per rank per layer" % (block * 4)},
+        "hbm_tb_s_per_gpu": achieved / 1e3,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": peak_kind, "kernel": "decode_kernel<128,1,3,2> + all-gather + merge per layer",
+                     "launch_us": launch_us, "algorithmic_bytes_per_launch": bytes_layer_rank, "traffic": None},
+        "gpu_launches": launches, "clocks": clocks, "self_check": "ok" if ok else "FAILED",
+    }
+    plan.close()
+    f.close()
+    if world > 1:
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(result))
+    return 0 if ok else 1
+
+
 # ---------------------------------------------------------------------- CPU arms ---
 
 def cpu_layer_inputs(w, seed):
@@ -404,13 +539,15 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + sorted(LONG_CONTEXT))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-overlap", action="store_true", help="plain launches instead of programmatic dependent launch")
     ap.add_argument("--stages", type=int, default=0, help="decode ring depth (experiments)")
     ap.add_argument("--page-size", type=int, default=0, help="override the workload's page size (experiments)")
     ap.add_argument("--sequential-pages", action="store_true", help="identity page table (experiments)")
     args = ap.parse_args()
+    if args.workload in LONG_CONTEXT:
+        return run_long_context(args, LONG_CONTEXT[args.workload])
     w = dict(WORKLOADS[args.workload])
     if args.page_size:
         w["page_size"] = args.page_size

@@ -368,6 +368,13 @@ MF_API mf_status mf_merge_partials(MfContext *ctx, const float *acc, const float
                                    const float *l, uint32_t n_splits, uint32_t rows,
                                    uint32_t head_dim, void *out);
 
+/* The same merge over an all-gathered buffer: split s of acc / m / l starts
+ * split_stride floats after split s-1 (e.g. each rank sends [acc | m | l] as one block of
+ * rows*(head_dim+2) floats and split_stride is that block size). */
+MF_API mf_status mf_merge_partials_strided(MfContext *ctx, const float *acc, const float *m,
+                                           const float *l, uint32_t n_splits, uint32_t rows,
+                                           uint32_t head_dim, uint64_t split_stride, void *out);
+
 /* ------------------------------------------------------ paged batched decode ---
  * No counterpart in the reference (contiguous cache, batch 1).  A plan cuts the
  * step's KV tiles into equal spans, one per resident CTA; it depends only on

@@ -135,6 +135,7 @@ _SIGNATURES = {
                                          C.POINTER(SdpaParams), C.POINTER(MfFlashDecodeStrides), u32, u32]),
     "mf_flash_prefill": (C.c_int32, [vp, vp, vp, vp, vp, C.POINTER(SdpaPrefillSplitKParams)]),
     "mf_merge_partials": (C.c_int32, [vp, vp, vp, vp, u32, u32, u32, vp]),
+    "mf_merge_partials_strided": (C.c_int32, [vp, vp, vp, vp, u32, u32, u32, u64, vp]),
     "mf_decode_plan_create": (C.c_int32, [vp, vp, u32, u32, u32, u32, u32, u32, C.POINTER(vp)]),
     "mf_decode_plan_update": (C.c_int32, [vp, vp, vp]),
     "mf_decode_plan_destroy": (None, [vp, vp]),
@@ -283,6 +284,15 @@ class Foundry:
     def merge_partials(self, acc, m, l, out):
         n_splits, rows, d = acc.shape
         self.check(lib.mf_merge_partials(self._h, _ptr(acc), _ptr(m), _ptr(l), n_splits, rows, d, _ptr(out)))
+
+    def merge_gathered(self, gathered, rows, head_dim, out):
+        """Merge an all-gathered [world, rows*(head_dim+2)] f32 buffer of [acc | m | l] blocks."""
+        world = gathered.shape[0]
+        block = rows * (head_dim + 2)
+        base = gathered.data_ptr()
+        self.check(lib.mf_merge_partials_strided(self._h, base, base + rows * head_dim * 4,
+                                                 base + (rows * head_dim + rows) * 4, world, rows, head_dim, block,
+                                                 _ptr(out)))
 
     # -- paged cache -----------------------------------------------------------------------
 

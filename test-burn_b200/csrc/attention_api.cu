@@ -18,21 +18,22 @@ namespace {
 // acc [S, rows, D] f32, m/l [S, rows] -> out [rows, D] f16 (flash_prefill.metal:843-888).
 __global__ void __launch_bounds__(128)
 merge_partials_kernel(const float *__restrict__ acc, const float *__restrict__ m, const float *__restrict__ l,
-                      uint32_t n_splits, uint32_t rows, uint32_t head_dim, __half *__restrict__ out)
+                      uint32_t n_splits, uint32_t rows, uint32_t head_dim, uint64_t acc_stride, uint64_t ml_stride,
+                      __half *__restrict__ out)
 {
     const uint32_t row = blockIdx.x;
     float mx = -1e30f;
-    for (uint32_t s = 0; s < n_splits; ++s) mx = fmaxf(mx, m[(size_t)s * rows + row]);
+    for (uint32_t s = 0; s < n_splits; ++s) mx = fmaxf(mx, m[s * ml_stride + row]);
     float lt = 0.f;
     for (uint32_t s = 0; s < n_splits; ++s) {
-        const float ls = l[(size_t)s * rows + row];
-        if (ls > 0.f) lt += ls * __expf(m[(size_t)s * rows + row] - mx);
+        const float ls = l[s * ml_stride + row];
+        if (ls > 0.f) lt += ls * __expf(m[s * ml_stride + row] - mx);
     }
     const float inv = ((fabsf(lt) <= 3.0e38f) && fabsf(lt) > 1e-6f) ? 1.0f / lt : 0.f;
     for (uint32_t d = threadIdx.x; d < head_dim; d += blockDim.x) {
         float a = 0.f;
         for (uint32_t s = 0; s < n_splits; ++s)
-            a += acc[((size_t)s * rows + row) * head_dim + d] * __expf(m[(size_t)s * rows + row] - mx);
+            a += acc[s * acc_stride + (size_t)row * head_dim + d] * __expf(m[s * ml_stride + row] - mx);
         out[(size_t)row * head_dim + d] = __float2half_rn(a * inv);
     }
 }
@@ -165,7 +166,19 @@ mf_status mf_merge_partials(MfContext *ctx, const float *acc, const float *m, co
     if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
     if (!acc || !m || !l || !out) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "merge: null input");
     if (n_splits == 0 || rows == 0 || head_dim == 0) return MF_OK;
-    merge_partials_kernel<<<rows, 128, 0, ctx->stream>>>(acc, m, l, n_splits, rows, head_dim, static_cast<__half *>(out));
+    merge_partials_kernel<<<rows, 128, 0, ctx->stream>>>(acc, m, l, n_splits, rows, head_dim, (uint64_t)rows * head_dim,
+                                                         (uint64_t)rows, static_cast<__half *>(out));
+    return check_launch(ctx, "merge_partials_kernel");
+}
+
+mf_status mf_merge_partials_strided(MfContext *ctx, const float *acc, const float *m, const float *l, uint32_t n_splits,
+                                    uint32_t rows, uint32_t head_dim, uint64_t split_stride, void *out)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!acc || !m || !l || !out) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "merge: null input");
+    if (n_splits == 0 || rows == 0 || head_dim == 0) return MF_OK;
+    merge_partials_kernel<<<rows, 128, 0, ctx->stream>>>(acc, m, l, n_splits, rows, head_dim, split_stride, split_stride,
+                                                         static_cast<__half *>(out));
     return check_launch(ctx, "merge_partials_kernel");
 }
 
