@@ -467,6 +467,84 @@ def run_long_context(args, w):
     return 0 if ok else 1
 
 
+def run_prefill(args):
+    """Configuration 4: 2048 new tokens after 2048 cached, Llama-3.2-3B heads, one layer per step:
+    KvPrepFused (RoPE + append of 2048 rows) then causal attention over 4096 keys."""
+    import torch
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    mfk = importlib.import_module("test-burn_b200")
+    hq, hkv, d, m, cached, cap = 24, 8, 128, 2048, 2048, 4096
+    g = torch.Generator(device=dev).manual_seed(SEED)
+    q = torch.empty((m, hq * d), dtype=torch.float16, device=dev).normal_(generator=g)
+    k = torch.empty((m, hkv * d), dtype=torch.float16, device=dev).normal_(generator=g)
+    v = torch.empty((m, hkv * d), dtype=torch.float16, device=dev).normal_(generator=g)
+    kc = torch.empty((hkv, cap, d), dtype=torch.float16, device=dev).normal_(generator=g)
+    vc = torch.empty((hkv, cap, d), dtype=torch.float16, device=dev).normal_(generator=g)
+    cos_np, sin_np = mfk.rope_tables(5e5, d, cap)
+    cos = torch.from_numpy(cos_np.view(np.float16)).to(dev)
+    sin = torch.from_numpy(sin_np.view(np.float16)).to(dev)
+    q_rot = torch.empty((hq, m, d), dtype=torch.float16, device=dev)
+    out = torch.empty((m, hq * d), dtype=torch.float16, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.Stream(device=dev)
+    f = mfk.Foundry(0, stream.cuda_stream)
+    if args.prefill_impl:
+        f.set_option(3, args.prefill_impl)
+    p = mfk.KvPrepFusedParamsResolved(hq * d, hkv * d, d, hq, hkv, hq // hkv, m, cached, cap, hq * m * d, 1, 0, 0)
+
+    def step(timed_events=None):
+        with torch.cuda.stream(stream):
+            flush.zero_()  # L2 flush between iterations: write a buffer larger than L2
+            if timed_events:
+                timed_events[0].record(stream)
+            f.kv_prep_fused(q, k, v, q_rot, kc, vc, cos, sin, p)
+            if timed_events:
+                timed_events[1].record(stream)
+            f.flash_attention(q_rot, kc, vc, out, causal=True, query_offset=cached, n_heads=hq, head_dim=d,
+                              kv_seq_len=cached + m, m=m)
+            if timed_events:
+                timed_events[2].record(stream)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    f.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    time.sleep(0.2)
+    t0 = time.time()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    launches0 = f.launch_count
+    for e in evs:
+        step(e)
+    f.synchronize()
+    t1 = time.time()
+    launches = f.launch_count - launches0
+    clocks = sampler.stop(t0, t1)
+    t_append = float(np.median([e[0].elapsed_time(e[1]) for e in evs]))
+    t_attn = float(np.median([e[1].elapsed_time(e[2]) for e in evs]))
+    pairs = sum(cached + i + 1 for i in range(m))
+    flops = 4 * d * pairs * hq
+    peak_path = ROOT / "MEASURED_PEAKS.json"
+    peak = json.loads(peak_path.read_text())["bf16_tflops"] if peak_path.exists() else 1590.0
+    achieved = flops / (t_attn * 1e-3) / 1e12
+    ok = bool(torch.isfinite(out.float()).all())
+    print(json.dumps({
+        "metric": "prefill_attention_tflops", "value": achieved, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": t_append + t_attn, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 inputs, f32 accumulate", "data": "synthetic",
+        "config": {"workload": "chunked causal prefill into cache, Llama-3.2-3B shape: 2048 new after 2048 cached, "
+                               "24q/8kv heads, D128, one layer", "l2": "flushed between iterations (256 MB write)",
+                   "split_k": mfk.prefill_split_k(cached + m, m)},
+        "append_us": t_append * 1e3, "attention_us": t_attn * 1e3, "algorithmic_flops": flops,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                     "peak_kind": "measured" if peak_path.exists() else "fallback", "traffic": None},
+        "gpu_launches": launches, "clocks": clocks, "self_check": "ok" if ok else "FAILED"}))
+    f.close()
+    return 0 if ok else 1
+
+
 # ---------------------------------------------------------------------- CPU arms ---
 
 def cpu_layer_inputs(w, seed):
@@ -489,6 +567,7 @@ def cpu_time_layer(w, repeats):
     import oracle
 
     L = oracle.lib()
+    L.mfo_set_num_threads(len(os.sched_getaffinity(0)))  # torchrun exports OMP_NUM_THREADS=1
     hq, hkv, d, B, P = w["n_heads"], w["n_kv_heads"], w["head_dim"], w["batch"], w["page_size"]
     cached, kv_lens, table, k_pool, v_pool, q, k, v = cpu_layer_inputs(w, SEED)
     cos, sin = oracle.rope_tables(w["theta"], d, int(kv_lens.max()))
@@ -539,13 +618,16 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + sorted(LONG_CONTEXT))
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + sorted(LONG_CONTEXT) + ["c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-overlap", action="store_true", help="plain launches instead of programmatic dependent launch")
+    ap.add_argument("--prefill-impl", type=int, default=0, help="prefill kernel selector (experiments)")
     ap.add_argument("--stages", type=int, default=0, help="decode ring depth (experiments)")
     ap.add_argument("--page-size", type=int, default=0, help="override the workload's page size (experiments)")
     ap.add_argument("--sequential-pages", action="store_true", help="identity page table (experiments)")
     args = ap.parse_args()
+    if args.workload == "c4":
+        return run_prefill(args)
     if args.workload in LONG_CONTEXT:
         return run_long_context(args, LONG_CONTEXT[args.workload])
     w = dict(WORKLOADS[args.workload])

@@ -93,6 +93,7 @@ def lib() -> C.CDLL:
     L.mfo_paged_decode_layer.argtypes = [u16p, u16p, u16p, u16p, u16p, u16p, u16p, u32p, u32, u32p,
                                          u32, u32, u32, u32, u32, u32, C.c_float, u16p]
     L.mfo_num_threads.restype = C.c_int
+    L.mfo_set_num_threads.argtypes = [C.c_int]
     _LIB = L
     return L
 

@@ -695,6 +695,15 @@ void mfo_merge_partials(const float *acc, const float *m, const float *l, uint32
 
 /* ------------------------------------------------------- timed CPU layer --- */
 
+void mfo_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int mfo_num_threads(void)
 {
 #ifdef _OPENMP

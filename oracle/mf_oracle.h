@@ -201,6 +201,7 @@ void mfo_paged_decode_layer(const uint16_t *q, const uint16_t *k, const uint16_t
                             uint32_t page_size, uint32_t rope_mode, float scale,
                             uint16_t *out);
 int mfo_num_threads(void);
+void mfo_set_num_threads(int n); /* launchers may export OMP_NUM_THREADS=1; the timed legs undo that */
 
 #ifdef __cplusplus
 }
