@@ -238,8 +238,10 @@ MF_API uint64_t mf_launch_count(const MfContext *ctx);
  * stream has finished; the caller promises that this previous kernel does not write the
  * pools, page table or lengths the launch reads (consecutive layers of a decode step never
  * do).  Everything else a launch reads or writes still waits for the previous kernel.
- * MF_OPTION_DECODE_STAGES = n: depth of the decode kernel's K/V tile ring (0 = default). */
-enum { MF_OPTION_OVERLAP_LAUNCHES = 1, MF_OPTION_DECODE_STAGES = 2 };
+ * MF_OPTION_DECODE_STAGES = n: depth of the decode kernel's K/V tile ring (0 = default).
+ * MF_OPTION_PREFILL_IMPL: 0 = choose (tcgen05 kernel when the shape allows), 1 = mma.sync
+ * kernel only, 2 = tcgen05 kernel only (like METALLIC_FA_PREFILL_* in the reference). */
+enum { MF_OPTION_OVERLAP_LAUNCHES = 1, MF_OPTION_DECODE_STAGES = 2, MF_OPTION_PREFILL_IMPL = 3 };
 MF_API mf_status mf_context_set_option(MfContext *ctx, uint32_t option, uint32_t value);
 /* Caller-provided scratch (device); when absent the context allocates its own
  * arena on first use and grows it on demand (pooled scratch of step.rs:927-929). */

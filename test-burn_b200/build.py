@@ -22,6 +22,7 @@ SOURCES = [
     HERE / "csrc" / "kv_append.cu",
     HERE / "csrc" / "decode.cu",
     HERE / "csrc" / "prefill.cu",
+    HERE / "csrc" / "prefill_tc.cu",
     HERE / "csrc" / "attention_api.cu",
     HERE / "host" / "host_logic.cpp",
 ]

@@ -153,6 +153,16 @@ struct QLayout {
     uint32_t stride_b, stride_h, stride_m;
 };
 
+// The reference picks split-K from the sequence lengths alone (tuned on Apple GPUs, where one
+// threadgroup per 32 rows and head is all the parallelism there is).  Here the split is only
+// taken when the unsplit grid would leave SMs idle.
+uint32_t effective_prefill_split_k(const MfContext *ctx, uint32_t kv_seq_len, uint32_t q_seq_len, uint32_t n_heads)
+{
+    const uint64_t ctas = (uint64_t)((q_seq_len + 63) / 64) * n_heads;
+    if (ctas >= (uint64_t)ctx->sm_count) return 1;
+    return mf_prefill_split_k(kv_seq_len, q_seq_len);
+}
+
 }  // namespace
 }  // namespace mf
 
@@ -310,7 +320,7 @@ mf_status mf_run_flash_decode(MfContext *ctx, const MfTensor *q, const MfTensor 
         b.group_size = std::max(1u, n_heads / n_kv_heads);
         b.q_len = q_seq_len;
         pp.n_heads = n_heads;
-        pp.split_k = mf_prefill_split_k(kv_seq_len, q_seq_len);
+        pp.split_k = effective_prefill_split_k(ctx, kv_seq_len, q_seq_len, n_heads);
         return launch_prefill(ctx, tensor_ptr(q), tensor_ptr(k), tensor_ptr(v), tensor_ptr(output), pp);
     }
 
@@ -373,7 +383,9 @@ mf_status mf_flash_attention(MfContext *ctx, const MfTensor *q, const MfTensor *
     if (a->query_offset + m != a->kv_seq_len)
         return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "FlashAttention prefill causal offset mismatch (query_offset %u + m %u != kv_seq_len %u)",
                     a->query_offset, m, a->kv_seq_len);
-    if (route_out) *route_out = mf_prefill_split_k(a->kv_seq_len, m) > 1 ? MF_ROUTE_PREFILL_SPLITK : MF_ROUTE_PREFILL;
+    if (route_out)
+        *route_out = effective_prefill_split_k(ctx, a->kv_seq_len, m, a->n_heads) > 1 ? MF_ROUTE_PREFILL_SPLITK
+                                                                                      : MF_ROUTE_PREFILL;
     return mf_run_flash_decode(ctx, q, k, v, output, a->n_heads, a->head_dim, a->kv_seq_len, m, a->kv_head_major);
 }
 

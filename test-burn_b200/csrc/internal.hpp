@@ -105,6 +105,7 @@ struct MfContext {
     void *encode_fn = nullptr;
     uint32_t overlap_launches = 0;  // MF_OPTION_OVERLAP_LAUNCHES
     uint32_t decode_stages = 0;     // MF_OPTION_DECODE_STAGES (0 = default)
+    uint32_t prefill_impl = 0;      // MF_OPTION_PREFILL_IMPL: 0 auto, 1 mma.sync, 2 tcgen05 only
 };
 
 struct MfDecodePlan {

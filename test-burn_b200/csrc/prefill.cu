@@ -347,6 +347,9 @@ mf_status launch_pf(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap &
 
 }  // namespace
 
+mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const void *v, void *out,
+                            const SdpaPrefillSplitKParams &sp, bool *handled);
+
 mf_status launch_prefill(MfContext *ctx, const void *q, const void *k, const void *v, void *out,
                          const SdpaPrefillSplitKParams &sp)
 {
@@ -366,6 +369,14 @@ mf_status launch_prefill(MfContext *ctx, const void *q, const void *k, const voi
     if ((b.q_stride_h | b.q_stride_m) & 1u || (b.out_stride_h | b.out_stride_m) & 1u ||
         (reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 3u)
         return fail(ctx, MF_ERR_INVALID_SHAPE, "Prefill: q/output strides must be even and pointers 4-byte aligned");
+    if (ctx->prefill_impl != 1) {
+        // tcgen05 / TMEM kernel for head_dim 128, unsplit, chunks of 64 rows or more
+        bool handled = false;
+        mf_status st_tc = launch_prefill_tc(ctx, q, k, v, out, sp, &handled);
+        if (st_tc != MF_OK || handled) return st_tc;
+        if (ctx->prefill_impl == 2)
+            return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "Prefill: shape outside the tcgen05 kernel's envelope");
+    }
     const uint32_t cache_heads = sp.n_heads / b.group_size;
     const uint32_t q_tiles = (b.q_len + kPfTileM - 1) / kPfTileM;
     uint32_t split_k = std::max(1u, sp.split_k);

@@ -1,0 +1,470 @@
+// Causal chunked prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM),
+// head_dim 128, for query chunks of 64 rows or more.
+//
+// Same contract as prefill.cu (flash_prefill.metal:94-446 of the reference): key k is
+// visible to query row r iff k <= r + query_offset, f16 x f16 products accumulated in f32,
+// `scale`, running max from -1e30, f32 weights / l / accumulator, acc * (1/l) or 0, rows past
+// q_len not written.  P is rounded to f16 for the PV product.
+//
+// One CTA per (128-row query tile, query head), 6 warps:
+//   warps 0-3  softmax + accumulate + epilogue; thread i owns query row i = TMEM lane i
+//   warp 4     TMA producer: Q tile once, then a 2-stage ring of 128-key K and V tiles
+//   warp 5     TMEM allocation and the single thread that issues tcgen05.mma
+// Per 128-key tile:  S = Q K^T  (tcgen05.mma, A and B from 128-byte-swizzled shared memory,
+// accumulator in TMEM, double buffered) -> the softmax warps read S with tcgen05.ld, write
+// P (f16) back to TMEM with tcgen05.st -> PV = P V (A from TMEM, B = V tile as an MN-major
+// operand) into a TMEM tile that the softmax warps fold into their register accumulator
+// with the online-softmax rescale.  The accumulate of tile i-1 is deferred until after the
+// softmax of tile i, so P(i-1)V(i-1) and Q K(i+1)^T run on the tensor pipe while the
+// softmax warps work on tile i.
+//
+// TMEM columns (512): S0 [0,128) S1 [128,256) PV [256,384) P0 [384,448) P1 [448,512).
+#include <algorithm>
+
+#include "internal.hpp"
+#include "ptx.cuh"
+
+namespace mf {
+namespace {
+
+constexpr uint32_t kBM = 128;             // query rows per CTA
+constexpr uint32_t kBN = 128;             // keys per tile
+constexpr uint32_t kD = 128;              // head_dim
+constexpr uint32_t kTcThreads = 192;
+constexpr uint32_t kHalfTile = 128 * 128; // bytes: 128 rows x 64 f16
+constexpr uint32_t kTile = 2 * kHalfTile; // 32 KB
+constexpr uint32_t kKvStages = 2;
+constexpr uint64_t kTcWaitNs = 2000000000ull;
+constexpr float kNegInf = -1e30f;
+
+struct TcParams {
+    __half *out;
+    uint32_t *status;
+    uint32_t q_len, kv_len, query_offset, group;
+    uint32_t out_stride_h, out_stride_m;
+    float scale_log2;
+};
+
+// ---- tcgen05 wrappers -------------------------------------------------------------------
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// All MMAs issued so far by this thread arrive on `bar` when they have completed.
+__device__ __forceinline__ void tc_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle: start address, leading / stride byte
+// offsets in 16-byte units, descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+    uint64_t d = (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor, kind::f16: f32 accumulator, f16 A and B, M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t n, uint32_t b_mn_major)
+{
+    return (1u << 4) | (b_mn_major << 16) | ((n >> 3) << 17) | ((kBM >> 4) << 24);
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+// 3-D tiled load without a cache hint.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *tmap, int32_t x, int32_t y, int32_t z, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+
+// Barrier slots (8 bytes each) after the tiles.
+enum Bar : uint32_t {
+    kQFull = 0,
+    kKFull = 1,    // [2]
+    kVFull = 3,    // [2]
+    kKEmpty = 5,   // [2]
+    kVEmpty = 7,   // [2]
+    kSFull = 9,    // [2]
+    kSEmpty = 11,  // [2]
+    kPFull = 13,   // [2]
+    kPEmpty = 15,  // [2]
+    kOtFull = 17,
+    kOtEmpty = 18,
+    kNumBars = 19
+};
+
+constexpr uint32_t kSmemTiles = kTile * (1 + 2 * kKvStages);  // Q + K ring + V ring = 160 KB
+constexpr uint32_t kSmemBytes = kSmemTiles + kNumBars * 8 + 16 + 1024;
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                  const __grid_constant__ CUtensorMap tm_v, const TcParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t q_smem = smem_base;
+    const uint32_t k_smem = smem_base + kTile;
+    const uint32_t v_smem = k_smem + kKvStages * kTile;
+    const uint32_t bars = smem_base + kSmemTiles;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + kSmemTiles + kNumBars * 8);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+    auto bar = [&](uint32_t i) { return bars + i * 8; };
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t q_tile = gridDim.x - 1 - blockIdx.x;  // late (long) tiles first
+    const uint32_t head = blockIdx.y;
+    const uint32_t kvh = head / p.group;
+    const uint32_t row0 = q_tile * kBM;
+    const uint32_t last_row = min(p.q_len, row0 + kBM) - 1;
+    const uint32_t key_end = min(p.kv_len, last_row + p.query_offset + 1);
+    const uint32_t n_tiles = (key_end + kBN - 1) / kBN;
+
+    if (tid == 0) {
+        mbar_init(bar(kQFull), 1);
+        for (uint32_t s = 0; s < 2; ++s) {
+            mbar_init(bar(kKFull + s), 1);
+            mbar_init(bar(kVFull + s), 1);
+            mbar_init(bar(kKEmpty + s), 1);
+            mbar_init(bar(kVEmpty + s), 1);
+            mbar_init(bar(kSFull + s), 1);
+            mbar_init(bar(kSEmpty + s), 128);
+            mbar_init(bar(kPFull + s), 128);
+            mbar_init(bar(kPEmpty + s), 1);
+        }
+        mbar_init(bar(kOtFull), 1);
+        mbar_init(bar(kOtEmpty), 128);
+        *abort_flag = 0;
+        mbar_fence_init();
+        fence_proxy_async();
+    }
+    if (warp == 5) {
+        tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    auto wait = [&](uint32_t b, uint32_t parity, uint32_t code) {
+        if (!*abort_flag && !mbar_wait_bounded(b, parity, kTcWaitNs)) {
+            *abort_flag = 1;
+            atomicOr(p.status, code);
+        }
+    };
+
+    if (warp == 4) {
+        // ---------------------------------------------------------------- TMA producer ---
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_k);
+            tma_prefetch_desc(&tm_v);
+            mbar_arrive_expect_tx(bar(kQFull), kTile);
+            tma_load_3d(q_smem, &tm_q, 0, (int32_t)row0, (int32_t)head, bar(kQFull));
+            tma_load_3d(q_smem + kHalfTile, &tm_q, 64, (int32_t)row0, (int32_t)head, bar(kQFull));
+            for (uint32_t i = 0; i < n_tiles; ++i) {
+                const uint32_t s = i & 1, ph = (i >> 1) & 1;
+                // K/V maps are (head_dim, kv_len, kv heads): rows past kv_len arrive as zeros, so a
+                // never-written cache row cannot meet a zero weight as NaN.
+                const int32_t key0 = (int32_t)(i * kBN);
+                wait(bar(kKEmpty + s), ph ^ 1, 16u);
+                mbar_arrive_expect_tx(bar(kKFull + s), kTile);
+                tma_load_3d(k_smem + s * kTile, &tm_k, 0, key0, (int32_t)kvh, bar(kKFull + s));
+                tma_load_3d(k_smem + s * kTile + kHalfTile, &tm_k, 64, key0, (int32_t)kvh, bar(kKFull + s));
+                wait(bar(kVEmpty + s), ph ^ 1, 16u);
+                mbar_arrive_expect_tx(bar(kVFull + s), kTile);
+                tma_load_3d(v_smem + s * kTile, &tm_v, 0, key0, (int32_t)kvh, bar(kVFull + s));
+                tma_load_3d(v_smem + s * kTile + kHalfTile, &tm_v, 64, key0, (int32_t)kvh, bar(kVFull + s));
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------------ MMA issuer ---
+        if (lane == 0) {
+            constexpr uint32_t kIdescQK = instr_desc(kBN, 0);
+            constexpr uint32_t kIdescPV = instr_desc(kD, 1);
+            wait(bar(kQFull), 0, 32u);
+            auto issue_qk = [&](uint32_t i) {
+                const uint32_t s = i & 1, ph = (i >> 1) & 1;
+                wait(bar(kKFull + s), ph, 32u);
+                wait(bar(kSEmpty + s), ph ^ 1, 32u);
+                tc_fence_after();
+#pragma unroll
+                for (uint32_t kk = 0; kk < kD / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * kHalfTile + (kk & 3) * 32;
+                    tc_mma_ss(tmem + s * 128, smem_desc(q_smem + off, 16, 1024),
+                              smem_desc(k_smem + s * kTile + off, 16, 1024), kIdescQK, kk > 0);
+                }
+                tc_commit(bar(kSFull + s));
+                tc_commit(bar(kKEmpty + s));
+            };
+            auto issue_pv = [&](uint32_t i) {
+                const uint32_t s = i & 1, ph = (i >> 1) & 1;
+                wait(bar(kVFull + s), ph, 64u);
+                wait(bar(kPFull + s), ph, 64u);
+                wait(bar(kOtEmpty), (i & 1) ^ 1, 64u);
+                tc_fence_after();
+#pragma unroll
+                for (uint32_t kk = 0; kk < kBN / 16; ++kk) {
+                    // A: 16 keys = 8 packed 32-bit TMEM columns per step; B: V rows kk*16.., MN-major.
+                    tc_mma_ts(tmem + 256, tmem + 384 + s * 64 + kk * 8,
+                              smem_desc(v_smem + s * kTile + kk * 2048, kHalfTile, 1024), kIdescPV, kk > 0);
+                }
+                tc_commit(bar(kOtFull));
+                tc_commit(bar(kVEmpty + s));
+                tc_commit(bar(kPEmpty + s));
+            };
+            for (uint32_t i = 0; i < n_tiles; ++i) {
+                issue_qk(i);
+                if (i >= 1) issue_pv(i - 1);
+            }
+            if (n_tiles) issue_pv(n_tiles - 1);
+        }
+    } else {
+        // ------------------------------------------------- softmax / accumulate / epilogue ---
+        const uint32_t row = row0 + tid;                        // this thread's query row
+        const uint32_t lane_base = (warp * 32u) << 16;          // TMEM lane quadrant of this warp
+        const uint32_t limit = row + p.query_offset;            // last visible key
+        float o[kD];
+#pragma unroll
+        for (uint32_t d = 0; d < kD; ++d) o[d] = 0.f;
+        float m_run = kNegInf, l_run = 0.f, alpha_saved = 1.f;
+
+        auto accumulate = [&](uint32_t i, float alpha) {
+            wait(bar(kOtFull), i & 1, 128u);
+            tc_fence_after();
+#pragma unroll
+            for (uint32_t c = 0; c < kD / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tmem + lane_base + 256 + c * 32, r);
+                tc_wait_ld();
+#pragma unroll
+                for (uint32_t j = 0; j < 32; ++j) o[c * 32 + j] = o[c * 32 + j] * alpha + __uint_as_float(r[j]);
+            }
+            tc_fence_before();
+            mbar_arrive(bar(kOtEmpty));
+        };
+
+        for (uint32_t i = 0; i < n_tiles; ++i) {
+            const uint32_t s = i & 1, ph = (i >> 1) & 1;
+            const uint32_t key0 = i * kBN;
+            const bool need_mask = key0 + kBN - 1 > limit || key0 + kBN > p.kv_len;
+            wait(bar(kSFull + s), ph, 256u);
+            tc_fence_after();
+            // pass 1: row maximum
+            float mx = kNegInf;
+#pragma unroll
+            for (uint32_t c = 0; c < kBN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tmem + lane_base + s * 128 + c * 32, r);
+                tc_wait_ld();
+#pragma unroll
+                for (uint32_t j = 0; j < 32; ++j) {
+                    float v = __uint_as_float(r[j]) * p.scale_log2;
+                    if (!(fabsf(v) <= 3.0e38f)) v = kNegInf;
+                    if (need_mask) {
+                        const uint32_t key = key0 + c * 32 + j;
+                        if (key > limit || key >= p.kv_len) v = kNegInf;
+                    }
+                    mx = fmaxf(mx, v);
+                }
+            }
+            const float m_new = fmaxf(m_run, mx);
+            const float alpha = fast_exp2(m_run - m_new);
+            m_run = m_new;
+            // pass 2: weights -> P (f16) in TMEM, row sum
+            wait(bar(kPEmpty + s), ph ^ 1, 512u);
+            float sum = 0.f;
+#pragma unroll
+            for (uint32_t c = 0; c < kBN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tmem + lane_base + s * 128 + c * 32, r);
+                tc_wait_ld();
+                uint32_t pk[16];
+#pragma unroll
+                for (uint32_t j = 0; j < 32; j += 2) {
+                    float v0 = __uint_as_float(r[j]) * p.scale_log2, v1 = __uint_as_float(r[j + 1]) * p.scale_log2;
+                    float p0 = fast_exp2(v0 - m_new), p1 = fast_exp2(v1 - m_new);
+                    if (!(fabsf(v0) <= 3.0e38f)) p0 = 0.f;
+                    if (!(fabsf(v1) <= 3.0e38f)) p1 = 0.f;
+                    if (need_mask) {
+                        const uint32_t key = key0 + c * 32 + j;
+                        if (key > limit || key >= p.kv_len) p0 = 0.f;
+                        if (key + 1 > limit || key + 1 >= p.kv_len) p1 = 0.f;
+                    }
+                    sum += p0 + p1;
+                    pk[j >> 1] = pack_f16x2(p0, p1);
+                }
+                tmem_st16(tmem + lane_base + 384 + s * 64 + c * 16, pk);
+            }
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(kSEmpty + s));  // S(i) has been read twice: its buffer may be overwritten
+            mbar_arrive(bar(kPFull + s));   // P(i) is in TMEM
+            l_run = l_run * alpha + sum;
+            if (i >= 1) accumulate(i - 1, alpha_saved);
+            alpha_saved = alpha;
+        }
+        if (n_tiles) accumulate(n_tiles - 1, alpha_saved);
+
+        if (row < p.q_len) {
+            const float inv = ((fabsf(l_run) <= 3.0e38f) && fabsf(l_run) > 1e-6f) ? 1.0f / l_run : 0.f;
+            __half *dst = p.out + (size_t)row * p.out_stride_m + (size_t)head * p.out_stride_h;
+#pragma unroll
+            for (uint32_t d = 0; d < kD; d += 8) {
+                uint4 v;
+                v.x = pack_f16x2(o[d] * inv, o[d + 1] * inv);
+                v.y = pack_f16x2(o[d + 2] * inv, o[d + 3] * inv);
+                v.z = pack_f16x2(o[d + 4] * inv, o[d + 5] * inv);
+                v.w = pack_f16x2(o[d + 6] * inv, o[d + 7] * inv);
+                *reinterpret_cast<uint4 *>(dst + d) = v;
+            }
+        }
+    }
+
+    // Everybody meets here before the TMEM columns go back, also after an abort.
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+}  // namespace
+
+// Returns MF_ERR_OPERATION_NOT_SUPPORTED (without touching last_error semantics) when the
+// shape is outside this kernel's envelope; the caller then uses the mma.sync kernel.
+mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const void *v, void *out,
+                            const SdpaPrefillSplitKParams &sp, bool *handled)
+{
+    *handled = false;
+    const SdpaPrefillParams &b = sp.base;
+    if (b.head_dim != kD || std::max(1u, sp.split_k) != 1 || b.q_len < 64) return MF_OK;
+    if (b.stride_k_s != kD || b.stride_v_s != kD) return MF_OK;
+    if ((b.q_stride_m % 8) || (b.q_stride_h % 8) || (b.out_stride_m % 8) || (b.out_stride_h % 8)) return MF_OK;
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 15u) return MF_OK;
+    if (b.k_stride_h % 8 || b.v_stride_h % 8 || (reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u)
+        return MF_OK;
+    if (!ctx->encode_fn) {
+        cudaDriverEntryPointQueryResult qr;
+        void *fn = nullptr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) != cudaSuccess ||
+            qr != cudaDriverEntryPointSuccess || !fn)
+            return fail(ctx, MF_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+        ctx->encode_fn = fn;
+    }
+    typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                 const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    // (head_dim, rows, heads) views with the caller's row and head strides; box = 64 columns x 128 rows.
+    auto encode = [&](CUtensorMap *tm, const void *base, uint64_t rows, uint64_t heads, uint64_t row_stride,
+                      uint64_t head_stride) {
+        cuuint64_t gdim[3] = {kD, rows, heads};
+        cuuint64_t gstride[2] = {row_stride * 2, head_stride * 2};
+        cuuint32_t box[3] = {64, 128, 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        return reinterpret_cast<EncodeFn>(ctx->encode_fn)(
+                   tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base), gdim, gstride, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    };
+    const uint32_t cache_heads = sp.n_heads / b.group_size;
+    CUtensorMap tm_q, tm_k, tm_v;
+    mf_status st;
+    // Unusual strides the encoder refuses are left to the other kernel.
+    if (!encode(&tm_q, q, b.q_len, sp.n_heads, b.q_stride_m, b.q_stride_h)) return MF_OK;
+    if (!encode(&tm_k, k, b.kv_len, cache_heads, kD, b.k_stride_h)) return MF_OK;
+    if (!encode(&tm_v, v, b.kv_len, cache_heads, kD, b.v_stride_h)) return MF_OK;
+    TcParams p{};
+    p.out = static_cast<__half *>(out);
+    p.status = ctx->d_status;
+    p.q_len = b.q_len;
+    p.kv_len = b.kv_len;
+    p.query_offset = b.query_offset;
+    p.group = b.group_size;
+    p.out_stride_h = b.out_stride_h;
+    p.out_stride_m = b.out_stride_m;
+    p.scale_log2 = b.scale * 1.4426950408889634f;
+    static bool configured[64] = {};
+    if (ctx->device < 64 && !configured[ctx->device]) {
+        st = check_cuda(ctx, cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+                        "cudaFuncSetAttribute(prefill_tc)");
+        if (st != MF_OK) return st;
+        configured[ctx->device] = true;
+    }
+    dim3 grid((b.q_len + kBM - 1) / kBM, sp.n_heads);
+    prefill_tc_kernel<<<grid, kTcThreads, kSmemBytes, ctx->stream>>>(tm_q, tm_k, tm_v, p);
+    *handled = true;
+    return check_launch(ctx, "prefill_tc_kernel");
+}
+
+}  // namespace mf

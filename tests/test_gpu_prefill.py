@@ -127,3 +127,47 @@ def test_prefill_split_k_heuristic_route(mfk, foundry):
     foundry.synchronize()
     assert route == mfk.ROUTE_PREFILL_SPLITK
     assert max_abs(host(out), ref) <= TOL and max_abs(host(out), gold) <= TOL
+
+
+# (n_heads, n_kv_heads, cached, m, capacity)
+TC_SHAPES = [(8, 8, 0, 128, 128), (8, 8, 0, 64, 64), (24, 8, 768, 256, 1024), (6, 2, 100, 200, 333),
+             (4, 4, 1, 130, 131), (16, 2, 500, 64, 600), (3, 1, 0, 385, 400)]
+
+
+@pytest.mark.parametrize("shape", TC_SHAPES)
+def test_prefill_tcgen05_kernel(mfk, foundry, shape):
+    """The tcgen05 / TMEM kernel alone (MF_OPTION_PREFILL_IMPL = 2), head_dim 128: whole and ragged
+    tiles, prefixes that are not multiples of the tile, GQA, poisoned rows past kv_len."""
+    hq, hkv, cached, m, cap = shape
+    case = ContigCase(n_heads=hq, n_kv_heads=hkv, head_dim=128, cached=cached, m=m, capacity=cap, poison=True)
+    q_rot, kc, vc = case.oracle_append()
+    ref, gold = oracle_prefill(case, q_rot, kc, vc)
+    foundry.set_option(3, 2)
+    try:
+        got = gpu_prefill(mfk, foundry, case, q_rot, kc, vc)
+    finally:
+        foundry.set_option(3, 0)
+    assert max_abs(got, ref) <= TOL
+    assert max_abs(got, gold) <= TOL
+
+
+def test_prefill_kernels_agree(mfk, foundry):
+    """mma.sync and tcgen05 kernels on the same inputs (token-major q this time)."""
+    import torch
+
+    hq, hkv, d, m, cached, cap = 12, 4, 128, 192, 320, 512
+    case = ContigCase(n_heads=hq, n_kv_heads=hkv, head_dim=d, cached=cached, m=m, capacity=cap)
+    q_rot, kc, vc = case.oracle_append()
+    ref, gold = oracle_prefill(case, q_rot, kc, vc)
+    q_tok = dev(np.ascontiguousarray(q_rot.reshape(hq, m, d).transpose(1, 0, 2)))  # [M, Hq, D]
+    k, v = dev(kc), dev(vc)
+    outs = []
+    for impl in (1, 2):
+        foundry.set_option(3, impl)
+        out = torch.zeros((m, hq * d), dtype=torch.float16, device="cuda")
+        foundry.run_flash_decode(q_tok, k, v, out, hq, d, cached + m, q_seq_len=m)
+        foundry.synchronize()
+        outs.append(host(out))
+    foundry.set_option(3, 0)
+    for o in outs:
+        assert max_abs(o, ref) <= TOL and max_abs(o, gold) <= TOL
