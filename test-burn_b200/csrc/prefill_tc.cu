@@ -6,10 +6,13 @@
 // `scale`, running max from -1e30, f32 weights / l / accumulator, acc * (1/l) or 0, rows past
 // q_len not written.  P is rounded to f16 for the PV product.
 //
-// One CTA per (128-row query tile, query head), 6 warps:
-//   warps 0-3  softmax + accumulate + epilogue; thread i owns query row i = TMEM lane i
-//   warp 4     TMA producer: Q tile once, then a 2-stage ring of 128-key K and V tiles
-//   warp 5     TMEM allocation and the single thread that issues tcgen05.mma
+// One CTA per (128-row query tile, query head), 10 warps:
+//   warps 0-7  softmax + accumulate + epilogue; two threads per query row (= TMEM lane): warp w
+//              works on lane quadrant w % 4 and on column half w / 4 of S, P and PV, so every
+//              scheduler has two such warps to interleave; the two halves of a row exchange their
+//              row maximum through shared memory once per tile
+//   warp 8     TMA producer: Q tile once, then a 2-stage ring of 128-key K and V tiles
+//   warp 9     TMEM allocation and the single thread that issues tcgen05.mma
 // Per 128-key tile:  S = Q K^T  (tcgen05.mma, A and B from 128-byte-swizzled shared memory,
 // accumulator in TMEM, double buffered) -> the softmax warps read S with tcgen05.ld, write
 // P (f16) back to TMEM with tcgen05.st -> PV = P V (A from TMEM, B = V tile as an MN-major
@@ -30,7 +33,8 @@ namespace {
 constexpr uint32_t kBM = 128;             // query rows per CTA
 constexpr uint32_t kBN = 128;             // keys per tile
 constexpr uint32_t kD = 128;              // head_dim
-constexpr uint32_t kTcThreads = 192;
+constexpr uint32_t kSoftmaxThreads = 256;
+constexpr uint32_t kTcThreads = kSoftmaxThreads + 64;
 constexpr uint32_t kHalfTile = 128 * 128; // bytes: 128 rows x 64 f16
 constexpr uint32_t kTile = 2 * kHalfTile; // 32 KB
 constexpr uint32_t kKvStages = 2;
@@ -162,7 +166,8 @@ enum Bar : uint32_t {
 };
 
 constexpr uint32_t kSmemTiles = kTile * (1 + 2 * kKvStages);  // Q + K ring + V ring = 160 KB
-constexpr uint32_t kSmemBytes = kSmemTiles + kNumBars * 8 + 16 + 1024;
+constexpr uint32_t kMaxBufBytes = 2 * 2 * 128 * 4;            // [tile parity][column half][row] f32
+constexpr uint32_t kSmemBytes = kSmemTiles + kMaxBufBytes + kNumBars * 8 + 16 + 1024;
 
 __global__ void __launch_bounds__(kTcThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -174,8 +179,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t q_smem = smem_base;
     const uint32_t k_smem = smem_base + kTile;
     const uint32_t v_smem = k_smem + kKvStages * kTile;
-    const uint32_t bars = smem_base + kSmemTiles;
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + kSmemTiles + kNumBars * 8);
+    float *max_buf = reinterpret_cast<float *>(smem + kSmemTiles);
+    const uint32_t bars = smem_base + kSmemTiles + kMaxBufBytes;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + kSmemTiles + kMaxBufBytes + kNumBars * 8);
     volatile uint32_t *abort_flag = tmem_slot + 1;
     auto bar = [&](uint32_t i) { return bars + i * 8; };
 
@@ -196,17 +202,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             mbar_init(bar(kKEmpty + s), 1);
             mbar_init(bar(kVEmpty + s), 1);
             mbar_init(bar(kSFull + s), 1);
-            mbar_init(bar(kSEmpty + s), 128);
-            mbar_init(bar(kPFull + s), 128);
+            mbar_init(bar(kSEmpty + s), kSoftmaxThreads);
+            mbar_init(bar(kPFull + s), kSoftmaxThreads);
             mbar_init(bar(kPEmpty + s), 1);
         }
         mbar_init(bar(kOtFull), 1);
-        mbar_init(bar(kOtEmpty), 128);
+        mbar_init(bar(kOtEmpty), kSoftmaxThreads);
         *abort_flag = 0;
         mbar_fence_init();
         fence_proxy_async();
     }
-    if (warp == 5) {
+    if (warp == 9) {
         tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), 512);
         tmem_relinquish();
     }
@@ -222,7 +228,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
     };
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ---------------------------------------------------------------- TMA producer ---
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
@@ -246,7 +252,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 tma_load_3d(v_smem + s * kTile + kHalfTile, &tm_v, 64, key0, (int32_t)kvh, bar(kVFull + s));
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issuer ---
         if (lane == 0) {
             constexpr uint32_t kIdescQK = instr_desc(kBN, 0);
@@ -290,24 +296,27 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
     } else {
         // ------------------------------------------------- softmax / accumulate / epilogue ---
-        const uint32_t row = row0 + tid;                        // this thread's query row
-        const uint32_t lane_base = (warp * 32u) << 16;          // TMEM lane quadrant of this warp
+        const uint32_t quad = warp & 3, half = warp >> 2;
+        const uint32_t r_in = quad * 32 + lane;                 // row inside the tile = TMEM lane
+        const uint32_t row = row0 + r_in;
+        const uint32_t lane_base = (quad * 32u) << 16;          // TMEM lane quadrant of this warp
         const uint32_t limit = row + p.query_offset;            // last visible key
-        float o[kD];
+        const uint32_t col0 = half * 64;                        // this thread's 64 S / PV columns
+        float o[64];
 #pragma unroll
-        for (uint32_t d = 0; d < kD; ++d) o[d] = 0.f;
-        float m_run = kNegInf, l_run = 0.f, alpha_saved = 1.f;
+        for (uint32_t d = 0; d < 64; ++d) o[d] = 0.f;
+        float m_run = kNegInf, l_run = 0.f, alpha_saved = 1.f;  // m in the scaled log2 domain
 
         auto accumulate = [&](uint32_t i, float alpha) {
             wait(bar(kOtFull), i & 1, 128u);
             tc_fence_after();
 #pragma unroll
-            for (uint32_t c = 0; c < kD / 32; ++c) {
+            for (uint32_t c = 0; c < 2; ++c) {
                 uint32_t r[32];
-                tmem_ld32(tmem + lane_base + 256 + c * 32, r);
+                tmem_ld32(tmem + lane_base + 256 + col0 + c * 32, r);
                 tc_wait_ld();
 #pragma unroll
-                for (uint32_t j = 0; j < 32; ++j) o[c * 32 + j] = o[c * 32 + j] * alpha + __uint_as_float(r[j]);
+                for (uint32_t j = 0; j < 32; ++j) o[c * 32 + j] = fmaf(o[c * 32 + j], alpha, __uint_as_float(r[j]));
             }
             tc_fence_before();
             mbar_arrive(bar(kOtEmpty));
@@ -315,71 +324,87 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
         for (uint32_t i = 0; i < n_tiles; ++i) {
             const uint32_t s = i & 1, ph = (i >> 1) & 1;
-            const uint32_t key0 = i * kBN;
-            const bool need_mask = key0 + kBN - 1 > limit || key0 + kBN > p.kv_len;
+            const uint32_t key0 = i * kBN + col0;  // first key of this thread's columns
+            // Only tiles on the causal diagonal or at the end of the cache need a mask; the
+            // number of this thread's 64 columns that stay visible covers both conditions.
+            const uint32_t last_ok = min(limit, p.kv_len - 1);
+            const uint32_t n_vis = last_ok < key0 ? 0u : min(64u, last_ok - key0 + 1);
             wait(bar(kSFull + s), ph, 256u);
             tc_fence_after();
-            // pass 1: row maximum
-            float mx = kNegInf;
-#pragma unroll
-            for (uint32_t c = 0; c < kBN / 32; ++c) {
+            // pass 1: row maximum of the raw scores (the scale is positive)
+            float mx = -3.0e38f;
+#pragma unroll 1
+            for (uint32_t c = 0; c < 2; ++c) {
                 uint32_t r[32];
-                tmem_ld32(tmem + lane_base + s * 128 + c * 32, r);
+                tmem_ld32(tmem + lane_base + s * 128 + col0 + c * 32, r);
                 tc_wait_ld();
+                if (n_vis >= (c + 1) * 32) {
 #pragma unroll
-                for (uint32_t j = 0; j < 32; ++j) {
-                    float v = __uint_as_float(r[j]) * p.scale_log2;
-                    if (!(fabsf(v) <= 3.0e38f)) v = kNegInf;
-                    if (need_mask) {
-                        const uint32_t key = key0 + c * 32 + j;
-                        if (key > limit || key >= p.kv_len) v = kNegInf;
-                    }
-                    mx = fmaxf(mx, v);
+                    for (uint32_t j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(r[j]));
+                } else {
+#pragma unroll
+                    for (uint32_t j = 0; j < 32; ++j)
+                        if (c * 32 + j < n_vis) mx = fmaxf(mx, __uint_as_float(r[j]));
                 }
             }
-            const float m_new = fmaxf(m_run, mx);
+            // the other half of this row lives in warp (warp ^ 4): swap maxima through shared memory
+            float *mb = max_buf + (i & 1) * 256;
+            mb[half * 128 + r_in] = mx;
+            named_bar_sync(1 + quad, 64);
+            mx = fmaxf(mx, mb[(half ^ 1) * 128 + r_in]);
+            const float m_new = fmaxf(m_run, mx > -3.0e38f ? mx * p.scale_log2 : kNegInf);
             const float alpha = fast_exp2(m_run - m_new);
             m_run = m_new;
             // pass 2: weights -> P (f16) in TMEM, row sum
             wait(bar(kPEmpty + s), ph ^ 1, 512u);
             float sum = 0.f;
-#pragma unroll
-            for (uint32_t c = 0; c < kBN / 32; ++c) {
+#pragma unroll 1
+            for (uint32_t c = 0; c < 2; ++c) {
                 uint32_t r[32];
-                tmem_ld32(tmem + lane_base + s * 128 + c * 32, r);
+                tmem_ld32(tmem + lane_base + s * 128 + col0 + c * 32, r);
                 tc_wait_ld();
                 uint32_t pk[16];
+                if (n_vis >= (c + 1) * 32) {
 #pragma unroll
-                for (uint32_t j = 0; j < 32; j += 2) {
-                    float v0 = __uint_as_float(r[j]) * p.scale_log2, v1 = __uint_as_float(r[j + 1]) * p.scale_log2;
-                    float p0 = fast_exp2(v0 - m_new), p1 = fast_exp2(v1 - m_new);
-                    if (!(fabsf(v0) <= 3.0e38f)) p0 = 0.f;
-                    if (!(fabsf(v1) <= 3.0e38f)) p1 = 0.f;
-                    if (need_mask) {
-                        const uint32_t key = key0 + c * 32 + j;
-                        if (key > limit || key >= p.kv_len) p0 = 0.f;
-                        if (key + 1 > limit || key + 1 >= p.kv_len) p1 = 0.f;
+                    for (uint32_t j = 0; j < 32; j += 2) {
+                        const float p0 = fast_exp2(fmaf(__uint_as_float(r[j]), p.scale_log2, -m_new));
+                        const float p1 = fast_exp2(fmaf(__uint_as_float(r[j + 1]), p.scale_log2, -m_new));
+                        sum += p0 + p1;
+                        pk[j >> 1] = pack_f16x2(p0, p1);
                     }
-                    sum += p0 + p1;
-                    pk[j >> 1] = pack_f16x2(p0, p1);
+                } else {
+#pragma unroll
+                    for (uint32_t j = 0; j < 32; j += 2) {
+                        float p0 = fast_exp2(fmaf(__uint_as_float(r[j]), p.scale_log2, -m_new));
+                        float p1 = fast_exp2(fmaf(__uint_as_float(r[j + 1]), p.scale_log2, -m_new));
+                        if (c * 32 + j >= n_vis) p0 = 0.f;
+                        if (c * 32 + j + 1 >= n_vis) p1 = 0.f;
+                        sum += p0 + p1;
+                        pk[j >> 1] = pack_f16x2(p0, p1);
+                    }
                 }
-                tmem_st16(tmem + lane_base + 384 + s * 64 + c * 16, pk);
+                tmem_st16(tmem + lane_base + 384 + s * 64 + half * 32 + c * 16, pk);
             }
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(bar(kSEmpty + s));  // S(i) has been read twice: its buffer may be overwritten
             mbar_arrive(bar(kPFull + s));   // P(i) is in TMEM
-            l_run = l_run * alpha + sum;
+            l_run = l_run * alpha + sum;    // partial sum over this thread's columns
             if (i >= 1) accumulate(i - 1, alpha_saved);
             alpha_saved = alpha;
         }
         if (n_tiles) accumulate(n_tiles - 1, alpha_saved);
 
+        // total l = both halves of the row
+        float *lb = max_buf + (n_tiles & 1) * 256;
+        lb[half * 128 + r_in] = l_run;
+        named_bar_sync(1 + quad, 64);
+        l_run += lb[(half ^ 1) * 128 + r_in];
         if (row < p.q_len) {
             const float inv = ((fabsf(l_run) <= 3.0e38f) && fabsf(l_run) > 1e-6f) ? 1.0f / l_run : 0.f;
-            __half *dst = p.out + (size_t)row * p.out_stride_m + (size_t)head * p.out_stride_h;
+            __half *dst = p.out + (size_t)row * p.out_stride_m + (size_t)head * p.out_stride_h + col0;
 #pragma unroll
-            for (uint32_t d = 0; d < kD; d += 8) {
+            for (uint32_t d = 0; d < 64; d += 8) {
                 uint4 v;
                 v.x = pack_f16x2(o[d] * inv, o[d + 1] * inv);
                 v.y = pack_f16x2(o[d + 2] * inv, o[d + 3] * inv);
@@ -393,7 +418,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     // Everybody meets here before the TMEM columns go back, also after an abort.
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         tc_fence_after();
         tmem_dealloc(tmem, 512);
     }

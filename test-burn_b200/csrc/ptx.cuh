@@ -61,15 +61,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 
-// Wait with a wall-clock limit.  Returns false when the limit ran out; the
-// caller records an error status and leaves instead of spinning for ever.
+// Wait with a time limit.  Returns false when the limit ran out; the caller records an error
+// status and leaves instead of spinning for ever.  The limit is counted on the SM's cycle
+// counter (reading the global nanosecond timer costs about a microsecond, which a wait on the
+// critical path cannot afford) and only consulted after a burst of plain polls.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t limit_ns)
 {
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+    for (uint32_t i = 0; i < 64; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    const long long limit_cycles = (long long)limit_ns * 2;  // SM clock is at most ~2 GHz
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 0x3FFu) == 0 && global_timer_ns() - t0 > limit_ns) return false;
+        if ((++spins & 0xFFu) == 0 && clock64() - t0 > limit_cycles) return false;
     }
     return true;
 }
