@@ -28,7 +28,8 @@ SOURCES = [
 ]
 HEADERS = [HERE / "csrc" / "internal.hpp", HERE / "csrc" / "ptx.cuh", ROOT / "include" / "metallic_cuda.h"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+EXTRA = os.environ.get("MF_EXTRA_NVCC_FLAGS", "").split()
+FLAGS = EXTRA + ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC,-fvisibility=hidden", "-x", "cu"]
 
 

@@ -7,12 +7,12 @@
 // q_len not written.  P is rounded to f16 for the PV product.
 //
 // One CTA per (128-row query tile, query head), 10 warps:
-//   warps 0-7  softmax + accumulate + epilogue; two threads per query row (= TMEM lane): warp w
-//              works on lane quadrant w % 4 and on column half w / 4 of S, P and PV, so every
-//              scheduler has two such warps to interleave; the two halves of a row exchange their
+//   warps 0-15 softmax + accumulate + epilogue; four threads per query row (= TMEM lane): warp w
+//              works on lane quadrant w % 4 and on 32-column group w / 4 of S, P and PV, so every
+//              scheduler has four such warps to interleave; the groups of a row exchange their
 //              row maximum through shared memory once per tile
-//   warp 8     TMA producer: Q tile once, then a 2-stage ring of 128-key K and V tiles
-//   warp 9     TMEM allocation and the single thread that issues tcgen05.mma
+//   warp 16    TMA producer: Q tile once, then rings of 128-key K (3 deep) and V (2 deep) tiles
+//   warp 17    TMEM allocation and the single thread that issues tcgen05.mma
 // Per 128-key tile:  S = Q K^T  (tcgen05.mma, A and B from 128-byte-swizzled shared memory,
 // accumulator in TMEM, double buffered) -> the softmax warps read S with tcgen05.ld, write
 // P (f16) back to TMEM with tcgen05.st -> PV = P V (A from TMEM, B = V tile as an MN-major
@@ -33,11 +33,16 @@ namespace {
 constexpr uint32_t kBM = 128;             // query rows per CTA
 constexpr uint32_t kBN = 128;             // keys per tile
 constexpr uint32_t kD = 128;              // head_dim
-constexpr uint32_t kSoftmaxThreads = 256;
+constexpr uint32_t kColGroups = 4;                        // threads per query row
+constexpr uint32_t kColsPerThread = kBN / kColGroups;    // 32 S / PV columns each
+constexpr uint32_t kSoftmaxWarps = 4 * kColGroups;
+constexpr uint32_t kSoftmaxThreads = 32 * kSoftmaxWarps;
 constexpr uint32_t kTcThreads = kSoftmaxThreads + 64;
+static_assert(kColsPerThread == 32, "one 32-column TMEM load per thread and tile");
 constexpr uint32_t kHalfTile = 128 * 128; // bytes: 128 rows x 64 f16
 constexpr uint32_t kTile = 2 * kHalfTile; // 32 KB
-constexpr uint32_t kKvStages = 2;
+constexpr uint32_t kKStages = 3;           // K tiles in flight
+constexpr uint32_t kVStages = 2;           // V tiles in flight
 constexpr uint64_t kTcWaitNs = 2000000000ull;
 constexpr float kNegInf = -1e30f;
 
@@ -48,6 +53,20 @@ struct TcParams {
     uint32_t out_stride_h, out_stride_m;
     float scale_log2;
 };
+
+#ifdef MF_TC_PROFILE
+// Development aid (build with -DMF_TC_PROFILE): cycles spent in each barrier wait, per CTA and role.
+__device__ unsigned long long g_tc_prof[1024 * 32];
+#define TC_PROF_DECL unsigned long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long prof_t0 = clock64();
+#define TC_PROF_WAIT(idx, stmt) { const long long t_ = clock64(); stmt; prof_acc[idx] += (unsigned long long)(clock64() - t_); }
+#define TC_PROF_STORE(role) { const uint32_t cta_ = blockIdx.y * gridDim.x + blockIdx.x; if (cta_ < 1024) { \
+        for (int k_ = 0; k_ < 8; ++k_) g_tc_prof[cta_ * 32 + (role) * 10 + k_] = prof_acc[k_]; \
+        g_tc_prof[cta_ * 32 + (role) * 10 + 8] = (unsigned long long)(clock64() - prof_t0); if ((role) == 0) g_tc_prof[cta_ * 32 + 31] = n_tiles; } }
+#else
+#define TC_PROF_DECL
+#define TC_PROF_WAIT(idx, stmt) stmt;
+#define TC_PROF_STORE(role)
+#endif
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------
 
@@ -152,21 +171,22 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *tmap, int3
 // Barrier slots (8 bytes each) after the tiles.
 enum Bar : uint32_t {
     kQFull = 0,
-    kKFull = 1,    // [2]
-    kVFull = 3,    // [2]
-    kKEmpty = 5,   // [2]
-    kVEmpty = 7,   // [2]
-    kSFull = 9,    // [2]
-    kSEmpty = 11,  // [2]
-    kPFull = 13,   // [2]
-    kPEmpty = 15,  // [2]
-    kOtFull = 17,
-    kOtEmpty = 18,
-    kNumBars = 19
+    kKFull = 1,    // [4]
+    kVFull = 5,    // [4]
+    kKEmpty = 9,   // [4]
+    kVEmpty = 13,  // [4]
+    kSFull = 17,   // [2]
+    kSEmpty = 19,  // [2]
+    kPFull = 21,   // [2]
+    kPEmpty = 23,  // [2]
+    kOtFull = 25,
+    kOtEmpty = 26,
+    kNumBars = 27
 };
+static_assert(kKStages <= 4 && kVStages <= 4, "barrier slots");
 
-constexpr uint32_t kSmemTiles = kTile * (1 + 2 * kKvStages);  // Q + K ring + V ring = 160 KB
-constexpr uint32_t kMaxBufBytes = 2 * 2 * 128 * 4;            // [tile parity][column half][row] f32
+constexpr uint32_t kSmemTiles = kTile * (1 + kKStages + kVStages);  // Q + K ring + V ring
+constexpr uint32_t kMaxBufBytes = 2 * kColGroups * 128 * 4;   // [tile parity][column group][row] f32
 constexpr uint32_t kSmemBytes = kSmemTiles + kMaxBufBytes + kNumBars * 8 + 16 + 1024;
 
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -178,7 +198,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     uint8_t *smem = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t q_smem = smem_base;
     const uint32_t k_smem = smem_base + kTile;
-    const uint32_t v_smem = k_smem + kKvStages * kTile;
+    const uint32_t v_smem = k_smem + kKStages * kTile;
     float *max_buf = reinterpret_cast<float *>(smem + kSmemTiles);
     const uint32_t bars = smem_base + kSmemTiles + kMaxBufBytes;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + kSmemTiles + kMaxBufBytes + kNumBars * 8);
@@ -196,23 +216,25 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
     if (tid == 0) {
         mbar_init(bar(kQFull), 1);
-        for (uint32_t s = 0; s < 2; ++s) {
+        for (uint32_t s = 0; s < 4; ++s) {
             mbar_init(bar(kKFull + s), 1);
             mbar_init(bar(kVFull + s), 1);
             mbar_init(bar(kKEmpty + s), 1);
             mbar_init(bar(kVEmpty + s), 1);
+        }
+        for (uint32_t s = 0; s < 2; ++s) {
             mbar_init(bar(kSFull + s), 1);
-            mbar_init(bar(kSEmpty + s), kSoftmaxThreads);
-            mbar_init(bar(kPFull + s), kSoftmaxThreads);
+            mbar_init(bar(kSEmpty + s), kSoftmaxWarps);  // one arrival per softmax warp
+            mbar_init(bar(kPFull + s), kSoftmaxWarps);
             mbar_init(bar(kPEmpty + s), 1);
         }
         mbar_init(bar(kOtFull), 1);
-        mbar_init(bar(kOtEmpty), kSoftmaxThreads);
+        mbar_init(bar(kOtEmpty), kSoftmaxWarps);
         *abort_flag = 0;
         mbar_fence_init();
         fence_proxy_async();
     }
-    if (warp == 9) {
+    if (warp == kSoftmaxWarps + 1) {
         tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), 512);
         tmem_relinquish();
     }
@@ -228,7 +250,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
     };
 
-    if (warp == 8) {
+    if (warp == kSoftmaxWarps) {
         // ---------------------------------------------------------------- TMA producer ---
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
@@ -237,55 +259,61 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             mbar_arrive_expect_tx(bar(kQFull), kTile);
             tma_load_3d(q_smem, &tm_q, 0, (int32_t)row0, (int32_t)head, bar(kQFull));
             tma_load_3d(q_smem + kHalfTile, &tm_q, 64, (int32_t)row0, (int32_t)head, bar(kQFull));
+            TC_PROF_DECL
             for (uint32_t i = 0; i < n_tiles; ++i) {
-                const uint32_t s = i & 1, ph = (i >> 1) & 1;
+                const uint32_t ks = i % kKStages, kph = (i / kKStages) & 1;
+                const uint32_t vs = i % kVStages, vph = (i / kVStages) & 1;
                 // K/V maps are (head_dim, kv_len, kv heads): rows past kv_len arrive as zeros, so a
                 // never-written cache row cannot meet a zero weight as NaN.
                 const int32_t key0 = (int32_t)(i * kBN);
-                wait(bar(kKEmpty + s), ph ^ 1, 16u);
-                mbar_arrive_expect_tx(bar(kKFull + s), kTile);
-                tma_load_3d(k_smem + s * kTile, &tm_k, 0, key0, (int32_t)kvh, bar(kKFull + s));
-                tma_load_3d(k_smem + s * kTile + kHalfTile, &tm_k, 64, key0, (int32_t)kvh, bar(kKFull + s));
-                wait(bar(kVEmpty + s), ph ^ 1, 16u);
-                mbar_arrive_expect_tx(bar(kVFull + s), kTile);
-                tma_load_3d(v_smem + s * kTile, &tm_v, 0, key0, (int32_t)kvh, bar(kVFull + s));
-                tma_load_3d(v_smem + s * kTile + kHalfTile, &tm_v, 64, key0, (int32_t)kvh, bar(kVFull + s));
+                TC_PROF_WAIT(0, wait(bar(kKEmpty + ks), kph ^ 1, 16u))
+                mbar_arrive_expect_tx(bar(kKFull + ks), kTile);
+                tma_load_3d(k_smem + ks * kTile, &tm_k, 0, key0, (int32_t)kvh, bar(kKFull + ks));
+                tma_load_3d(k_smem + ks * kTile + kHalfTile, &tm_k, 64, key0, (int32_t)kvh, bar(kKFull + ks));
+                TC_PROF_WAIT(1, wait(bar(kVEmpty + vs), vph ^ 1, 16u))
+                mbar_arrive_expect_tx(bar(kVFull + vs), kTile);
+                tma_load_3d(v_smem + vs * kTile, &tm_v, 0, key0, (int32_t)kvh, bar(kVFull + vs));
+                tma_load_3d(v_smem + vs * kTile + kHalfTile, &tm_v, 64, key0, (int32_t)kvh, bar(kVFull + vs));
             }
+            TC_PROF_STORE(2)
         }
-    } else if (warp == 9) {
+    } else if (warp == kSoftmaxWarps + 1) {
         // ------------------------------------------------------------------ MMA issuer ---
         if (lane == 0) {
             constexpr uint32_t kIdescQK = instr_desc(kBN, 0);
             constexpr uint32_t kIdescPV = instr_desc(kD, 1);
+            TC_PROF_DECL
             wait(bar(kQFull), 0, 32u);
             auto issue_qk = [&](uint32_t i) {
                 const uint32_t s = i & 1, ph = (i >> 1) & 1;
-                wait(bar(kKFull + s), ph, 32u);
-                wait(bar(kSEmpty + s), ph ^ 1, 32u);
+                const uint32_t ks = i % kKStages, kph = (i / kKStages) & 1;
+                TC_PROF_WAIT(0, wait(bar(kKFull + ks), kph, 32u))
+                TC_PROF_WAIT(1, wait(bar(kSEmpty + s), ph ^ 1, 32u))
                 tc_fence_after();
 #pragma unroll
                 for (uint32_t kk = 0; kk < kD / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * kHalfTile + (kk & 3) * 32;
                     tc_mma_ss(tmem + s * 128, smem_desc(q_smem + off, 16, 1024),
-                              smem_desc(k_smem + s * kTile + off, 16, 1024), kIdescQK, kk > 0);
+                              smem_desc(k_smem + ks * kTile + off, 16, 1024), kIdescQK, kk > 0);
                 }
                 tc_commit(bar(kSFull + s));
-                tc_commit(bar(kKEmpty + s));
+                tc_commit(bar(kKEmpty + ks));
             };
             auto issue_pv = [&](uint32_t i) {
                 const uint32_t s = i & 1, ph = (i >> 1) & 1;
-                wait(bar(kVFull + s), ph, 64u);
-                wait(bar(kPFull + s), ph, 64u);
-                wait(bar(kOtEmpty), (i & 1) ^ 1, 64u);
+                const uint32_t vs = i % kVStages, vph = (i / kVStages) & 1;
+                TC_PROF_WAIT(2, wait(bar(kVFull + vs), vph, 64u))
+                TC_PROF_WAIT(3, wait(bar(kPFull + s), ph, 64u))
+                TC_PROF_WAIT(3, wait(bar(kOtEmpty), (i & 1) ^ 1, 64u))
                 tc_fence_after();
 #pragma unroll
                 for (uint32_t kk = 0; kk < kBN / 16; ++kk) {
                     // A: 16 keys = 8 packed 32-bit TMEM columns per step; B: V rows kk*16.., MN-major.
                     tc_mma_ts(tmem + 256, tmem + 384 + s * 64 + kk * 8,
-                              smem_desc(v_smem + s * kTile + kk * 2048, kHalfTile, 1024), kIdescPV, kk > 0);
+                              smem_desc(v_smem + vs * kTile + kk * 2048, kHalfTile, 1024), kIdescPV, kk > 0);
                 }
                 tc_commit(bar(kOtFull));
-                tc_commit(bar(kVEmpty + s));
+                tc_commit(bar(kVEmpty + vs));
                 tc_commit(bar(kPEmpty + s));
             };
             for (uint32_t i = 0; i < n_tiles; ++i) {
@@ -293,118 +321,135 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (i >= 1) issue_pv(i - 1);
             }
             if (n_tiles) issue_pv(n_tiles - 1);
+            TC_PROF_STORE(1)
         }
     } else {
         // ------------------------------------------------- softmax / accumulate / epilogue ---
-        const uint32_t quad = warp & 3, half = warp >> 2;
+        const uint32_t quad = warp & 3, grp = warp >> 2;
         const uint32_t r_in = quad * 32 + lane;                 // row inside the tile = TMEM lane
         const uint32_t row = row0 + r_in;
         const uint32_t lane_base = (quad * 32u) << 16;          // TMEM lane quadrant of this warp
         const uint32_t limit = row + p.query_offset;            // last visible key
-        const uint32_t col0 = half * 64;                        // this thread's 64 S / PV columns
-        float o[64];
+        const uint32_t col0 = grp * kColsPerThread;             // this thread's S / PV columns
+        constexpr uint32_t kRowThreads = 32 * kColGroups;       // threads that share a lane quadrant
+        float o[kColsPerThread];
 #pragma unroll
-        for (uint32_t d = 0; d < 64; ++d) o[d] = 0.f;
+        for (uint32_t d = 0; d < kColsPerThread; ++d) o[d] = 0.f;
         float m_run = kNegInf, l_run = 0.f, alpha_saved = 1.f;  // m in the scaled log2 domain
+        TC_PROF_DECL
 
         auto accumulate = [&](uint32_t i, float alpha) {
-            wait(bar(kOtFull), i & 1, 128u);
+            TC_PROF_WAIT(2, wait(bar(kOtFull), i & 1, 128u))
             tc_fence_after();
-#pragma unroll
-            for (uint32_t c = 0; c < 2; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tmem + lane_base + 256 + col0 + c * 32, r);
-                tc_wait_ld();
-#pragma unroll
-                for (uint32_t j = 0; j < 32; ++j) o[c * 32 + j] = fmaf(o[c * 32 + j], alpha, __uint_as_float(r[j]));
-            }
+            uint32_t r[32];
+            tmem_ld32(tmem + lane_base + 256 + col0, r);
+            tc_wait_ld();
             tc_fence_before();
-            mbar_arrive(bar(kOtEmpty));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(kOtEmpty));  // the PV tile is in registers: P V may overwrite it
+#pragma unroll
+            for (uint32_t j = 0; j < 32; ++j) o[j] = fmaf(o[j], alpha, __uint_as_float(r[j]));
         };
 
         for (uint32_t i = 0; i < n_tiles; ++i) {
             const uint32_t s = i & 1, ph = (i >> 1) & 1;
             const uint32_t key0 = i * kBN + col0;  // first key of this thread's columns
             // Only tiles on the causal diagonal or at the end of the cache need a mask; the
-            // number of this thread's 64 columns that stay visible covers both conditions.
+            // number of this thread's columns that stay visible covers both conditions.
             const uint32_t last_ok = min(limit, p.kv_len - 1);
-            const uint32_t n_vis = last_ok < key0 ? 0u : min(64u, last_ok - key0 + 1);
-            wait(bar(kSFull + s), ph, 256u);
+            const uint32_t n_vis = last_ok < key0 ? 0u : min(kColsPerThread, last_ok - key0 + 1);
+            TC_PROF_WAIT(0, wait(bar(kSFull + s), ph, 256u))
             tc_fence_after();
-            // pass 1: row maximum of the raw scores (the scale is positive)
+            uint32_t r[32];
+#ifdef MF_TC_PROFILE
+            long long tp_ = clock64();
+#endif
+            tmem_ld32(tmem + lane_base + s * 128 + col0, r);
+            tc_wait_ld();
+#ifdef MF_TC_PROFILE
+            prof_acc[4] += (unsigned long long)(clock64() - tp_); tp_ = clock64();
+#endif
+            // row maximum of the raw scores (the scale is positive)
             float mx = -3.0e38f;
-#pragma unroll 1
-            for (uint32_t c = 0; c < 2; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tmem + lane_base + s * 128 + col0 + c * 32, r);
-                tc_wait_ld();
-                if (n_vis >= (c + 1) * 32) {
+            if (n_vis == kColsPerThread) {
 #pragma unroll
-                    for (uint32_t j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(r[j]));
-                } else {
+                for (uint32_t j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(r[j]));
+            } else {
 #pragma unroll
-                    for (uint32_t j = 0; j < 32; ++j)
-                        if (c * 32 + j < n_vis) mx = fmaxf(mx, __uint_as_float(r[j]));
-                }
+                for (uint32_t j = 0; j < 32; ++j)
+                    if (j < n_vis) mx = fmaxf(mx, __uint_as_float(r[j]));
             }
-            // the other half of this row lives in warp (warp ^ 4): swap maxima through shared memory
-            float *mb = max_buf + (i & 1) * 256;
-            mb[half * 128 + r_in] = mx;
-            named_bar_sync(1 + quad, 64);
-            mx = fmaxf(mx, mb[(half ^ 1) * 128 + r_in]);
+            // the other column groups of this row live in other warps: swap maxima through smem
+            float *mb = max_buf + (i & 1) * (kColGroups * 128);
+            mb[grp * 128 + r_in] = mx;
+            TC_PROF_WAIT(3, named_bar_sync(1 + quad, kRowThreads))
+#pragma unroll
+            for (uint32_t g = 0; g < kColGroups; ++g) mx = fmaxf(mx, mb[g * 128 + r_in]);
             const float m_new = fmaxf(m_run, mx > -3.0e38f ? mx * p.scale_log2 : kNegInf);
             const float alpha = fast_exp2(m_run - m_new);
             m_run = m_new;
-            // pass 2: weights -> P (f16) in TMEM, row sum
-            wait(bar(kPEmpty + s), ph ^ 1, 512u);
-            float sum = 0.f;
-#pragma unroll 1
-            for (uint32_t c = 0; c < 2; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tmem + lane_base + s * 128 + col0 + c * 32, r);
-                tc_wait_ld();
-                uint32_t pk[16];
-                if (n_vis >= (c + 1) * 32) {
+#ifdef MF_TC_PROFILE
+            prof_acc[5] += (unsigned long long)(clock64() - tp_); tp_ = clock64();
+#endif
+            // weights -> P (f16) in TMEM, row sum
+            float sum0 = 0.f, sum1 = 0.f;
+            uint32_t pk[16];
+            if (n_vis == kColsPerThread) {
 #pragma unroll
-                    for (uint32_t j = 0; j < 32; j += 2) {
-                        const float p0 = fast_exp2(fmaf(__uint_as_float(r[j]), p.scale_log2, -m_new));
-                        const float p1 = fast_exp2(fmaf(__uint_as_float(r[j + 1]), p.scale_log2, -m_new));
-                        sum += p0 + p1;
-                        pk[j >> 1] = pack_f16x2(p0, p1);
-                    }
-                } else {
-#pragma unroll
-                    for (uint32_t j = 0; j < 32; j += 2) {
-                        float p0 = fast_exp2(fmaf(__uint_as_float(r[j]), p.scale_log2, -m_new));
-                        float p1 = fast_exp2(fmaf(__uint_as_float(r[j + 1]), p.scale_log2, -m_new));
-                        if (c * 32 + j >= n_vis) p0 = 0.f;
-                        if (c * 32 + j + 1 >= n_vis) p1 = 0.f;
-                        sum += p0 + p1;
-                        pk[j >> 1] = pack_f16x2(p0, p1);
-                    }
+                for (uint32_t j = 0; j < 32; j += 2) {
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(r[j]), p.scale_log2, -m_new));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(r[j + 1]), p.scale_log2, -m_new));
+                    sum0 += p0;
+                    sum1 += p1;
+                    pk[j >> 1] = pack_f16x2(p0, p1);
                 }
-                tmem_st16(tmem + lane_base + 384 + s * 64 + half * 32 + c * 16, pk);
+            } else {
+#pragma unroll
+                for (uint32_t j = 0; j < 32; j += 2) {
+                    float p0 = fast_exp2(fmaf(__uint_as_float(r[j]), p.scale_log2, -m_new));
+                    float p1 = fast_exp2(fmaf(__uint_as_float(r[j + 1]), p.scale_log2, -m_new));
+                    if (j >= n_vis) p0 = 0.f;
+                    if (j + 1 >= n_vis) p1 = 0.f;
+                    sum0 += p0;
+                    sum1 += p1;
+                    pk[j >> 1] = pack_f16x2(p0, p1);
+                }
             }
+            const float sum = sum0 + sum1;
+#ifdef MF_TC_PROFILE
+            prof_acc[6] += (unsigned long long)(__float_as_uint(sum) & 0) + (unsigned long long)(clock64() - tp_); tp_ = clock64();
+#endif
+            TC_PROF_WAIT(1, wait(bar(kPEmpty + s), ph ^ 1, 512u))
+            tmem_st16(tmem + lane_base + 384 + s * 64 + grp * (kColsPerThread / 2), pk);
             tc_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(kSEmpty + s));  // S(i) has been read twice: its buffer may be overwritten
-            mbar_arrive(bar(kPFull + s));   // P(i) is in TMEM
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar(kSEmpty + s));  // S(i) is in registers: its buffer may be overwritten
+                mbar_arrive(bar(kPFull + s));   // P(i) is in TMEM
+            }
+#ifdef MF_TC_PROFILE
+            prof_acc[7] += (unsigned long long)(clock64() - tp_);
+#endif
             l_run = l_run * alpha + sum;    // partial sum over this thread's columns
             if (i >= 1) accumulate(i - 1, alpha_saved);
             alpha_saved = alpha;
         }
         if (n_tiles) accumulate(n_tiles - 1, alpha_saved);
+        if (tid == 0) TC_PROF_STORE(0)
 
-        // total l = both halves of the row
-        float *lb = max_buf + (n_tiles & 1) * 256;
-        lb[half * 128 + r_in] = l_run;
-        named_bar_sync(1 + quad, 64);
-        l_run += lb[(half ^ 1) * 128 + r_in];
+        // total l = all column groups of the row
+        float *lb = max_buf + (n_tiles & 1) * (kColGroups * 128);
+        lb[grp * 128 + r_in] = l_run;
+        named_bar_sync(1 + quad, kRowThreads);
+        l_run = 0.f;
+#pragma unroll
+        for (uint32_t g = 0; g < kColGroups; ++g) l_run += lb[g * 128 + r_in];
         if (row < p.q_len) {
             const float inv = ((fabsf(l_run) <= 3.0e38f) && fabsf(l_run) > 1e-6f) ? 1.0f / l_run : 0.f;
             __half *dst = p.out + (size_t)row * p.out_stride_m + (size_t)head * p.out_stride_h + col0;
 #pragma unroll
-            for (uint32_t d = 0; d < 64; d += 8) {
+            for (uint32_t d = 0; d < kColsPerThread; d += 8) {
                 uint4 v;
                 v.x = pack_f16x2(o[d] * inv, o[d + 1] * inv);
                 v.y = pack_f16x2(o[d + 2] * inv, o[d + 3] * inv);
@@ -418,13 +463,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     // Everybody meets here before the TMEM columns go back, also after an abort.
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == kSoftmaxWarps + 1) {
         tc_fence_after();
         tmem_dealloc(tmem, 512);
     }
 }
 
 }  // namespace
+
+#ifdef MF_TC_PROFILE
+extern "C" __attribute__((visibility("default"))) int mf_debug_tc_profile(unsigned long long *host_out, uint32_t n)
+{
+    return (int)cudaMemcpyFromSymbol(host_out, g_tc_prof, sizeof(unsigned long long) * n);
+}
+#endif
 
 // Returns MF_ERR_OPERATION_NOT_SUPPORTED (without touching last_error semantics) when the
 // shape is outside this kernel's envelope; the caller then uses the mma.sync kernel.
