@@ -436,7 +436,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             alpha_saved = alpha;
         }
         if (n_tiles) accumulate(n_tiles - 1, alpha_saved);
-        if (tid == 0) TC_PROF_STORE(0)
+        if (tid == 0) {
+            TC_PROF_STORE(0)
+        }
 
         // total l = all column groups of the row
         float *lb = max_buf + (n_tiles & 1) * (kColGroups * 128);
