@@ -6,22 +6,22 @@
 // `scale`, running max from -1e30, f32 weights / l / accumulator, acc * (1/l) or 0, rows past
 // q_len not written.  P is rounded to f16 for the PV product.
 //
-// One CTA per (128-row query tile, query head), 10 warps:
-//   warps 0-15 softmax + accumulate + epilogue; four threads per query row (= TMEM lane): warp w
-//              works on lane quadrant w % 4 and on 32-column group w / 4 of S, P and PV, so every
-//              scheduler has four such warps to interleave; the groups of a row exchange their
-//              row maximum through shared memory once per tile
-//   warp 16    TMA producer: Q tile once, then rings of 128-key K (3 deep) and V (2 deep) tiles
-//   warp 17    TMEM allocation and the single thread that issues tcgen05.mma
-// Per 128-key tile:  S = Q K^T  (tcgen05.mma, A and B from 128-byte-swizzled shared memory,
-// accumulator in TMEM, double buffered) -> the softmax warps read S with tcgen05.ld, write
-// P (f16) back to TMEM with tcgen05.st -> PV = P V (A from TMEM, B = V tile as an MN-major
-// operand) into a TMEM tile that the softmax warps fold into their register accumulator
-// with the online-softmax rescale.  The accumulate of tile i-1 is deferred until after the
-// softmax of tile i, so P(i-1)V(i-1) and Q K(i+1)^T run on the tensor pipe while the
-// softmax warps work on tile i.
+// One CTA per (128-row query tile, query head).  The 128-key tiles of the CTA are dealt to two
+// independent online-softmax streams (even tiles -> stream 0, odd tiles -> stream 1), each with
+// its own running (m, l, O); the streams are merged with the log-sum-exp rule at the end.  While
+// one stream's warps exponentiate, the tensor pipe works on the other stream's products.
+//   warps 0-7   stream 0 softmax, warps 8-15 stream 1 softmax; two threads per query row
+//               (= TMEM lane): warp w works on lane quadrant w % 4 and column half (w / 4) % 2
+//   warp 16     TMA producer: Q tile once, then rings of 128-key K (3 deep) and V (2 deep) tiles
+//   warp 17     TMEM allocation and the single thread that issues tcgen05.mma
+// Per tile of stream x:  S_x = Q K^T (A, B from 128-byte-swizzled shared memory, accumulator in
+// TMEM) -> the stream's warps read S_x with tcgen05.ld, write P (f16) over the first 64 columns
+// of S_x with tcgen05.st -> O_x += P V (A from TMEM, B = V tile as an MN-major operand), O_x
+// staying in TMEM.  The accumulator is only rescaled when a row's maximum has grown by more than
+// 2^8 since the last rescale (the weights are then at most 256, which f16 holds without loss of
+// relative precision); the final normalisation uses the reference maximum actually applied.
 //
-// TMEM columns (512): S0 [0,128) S1 [128,256) PV [256,384) P0 [384,448) P1 [448,512).
+// TMEM columns (512): S_0/P_0 [0,128)  S_1/P_1 [128,256)  O_0 [256,384)  O_1 [384,512).
 #include <algorithm>
 
 #include "internal.hpp"
@@ -33,12 +33,11 @@ namespace {
 constexpr uint32_t kBM = 128;             // query rows per CTA
 constexpr uint32_t kBN = 128;             // keys per tile
 constexpr uint32_t kD = 128;              // head_dim
-constexpr uint32_t kColGroups = 4;                        // threads per query row
-constexpr uint32_t kColsPerThread = kBN / kColGroups;    // 32 S / PV columns each
-constexpr uint32_t kSoftmaxWarps = 4 * kColGroups;
+constexpr uint32_t kStreamWarps = 8;                      // softmax warps per stream
+constexpr uint32_t kSoftmaxWarps = 2 * kStreamWarps;
 constexpr uint32_t kSoftmaxThreads = 32 * kSoftmaxWarps;
 constexpr uint32_t kTcThreads = kSoftmaxThreads + 64;
-static_assert(kColsPerThread == 32, "one 32-column TMEM load per thread and tile");
+constexpr float kRescaleThreshold = 8.0f;                 // log2 of the largest weight kept in P
 constexpr uint32_t kHalfTile = 128 * 128; // bytes: 128 rows x 64 f16
 constexpr uint32_t kTile = 2 * kHalfTile; // 32 KB
 constexpr uint32_t kKStages = 3;           // K tiles in flight
@@ -175,18 +174,15 @@ enum Bar : uint32_t {
     kVFull = 5,    // [4]
     kKEmpty = 9,   // [4]
     kVEmpty = 13,  // [4]
-    kSFull = 17,   // [2]
-    kSEmpty = 19,  // [2]
-    kPFull = 21,   // [2]
-    kPEmpty = 23,  // [2]
-    kOtFull = 25,
-    kOtEmpty = 26,
-    kNumBars = 27
+    kSFull = 17,   // [2] per stream: S_x holds Q K^T of the stream's next tile
+    kPFull = 19,   // [2] per stream: P is in TMEM (and O_x has been rescaled if needed)
+    kOFull = 21,   // [2] per stream: the stream's last issued P V has completed
+    kNumBars = 23
 };
 static_assert(kKStages <= 4 && kVStages <= 4, "barrier slots");
 
 constexpr uint32_t kSmemTiles = kTile * (1 + kKStages + kVStages);  // Q + K ring + V ring
-constexpr uint32_t kMaxBufBytes = 2 * kColGroups * 128 * 4;   // [tile parity][column group][row] f32
+constexpr uint32_t kMaxBufBytes = 2 * 2 * 2 * 128 * 4;        // [stream][tile parity][column half][row] f32
 constexpr uint32_t kSmemBytes = kSmemTiles + kMaxBufBytes + kNumBars * 8 + 16 + 1024;
 
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -222,14 +218,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             mbar_init(bar(kKEmpty + s), 1);
             mbar_init(bar(kVEmpty + s), 1);
         }
-        for (uint32_t s = 0; s < 2; ++s) {
-            mbar_init(bar(kSFull + s), 1);
-            mbar_init(bar(kSEmpty + s), kSoftmaxWarps);  // one arrival per softmax warp
-            mbar_init(bar(kPFull + s), kSoftmaxWarps);
-            mbar_init(bar(kPEmpty + s), 1);
+        for (uint32_t x = 0; x < 2; ++x) {
+            mbar_init(bar(kSFull + x), 1);
+            mbar_init(bar(kPFull + x), kStreamWarps);  // one arrival per softmax warp of the stream
+            mbar_init(bar(kOFull + x), 1);
         }
-        mbar_init(bar(kOtFull), 1);
-        mbar_init(bar(kOtEmpty), kSoftmaxWarps);
         *abort_flag = 0;
         mbar_fence_init();
         fence_proxy_async();
@@ -256,24 +249,31 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
             tma_prefetch_desc(&tm_v);
+            TC_PROF_DECL
             mbar_arrive_expect_tx(bar(kQFull), kTile);
             tma_load_3d(q_smem, &tm_q, 0, (int32_t)row0, (int32_t)head, bar(kQFull));
             tma_load_3d(q_smem + kHalfTile, &tm_q, 64, (int32_t)row0, (int32_t)head, bar(kQFull));
-            TC_PROF_DECL
-            for (uint32_t i = 0; i < n_tiles; ++i) {
+            // K/V maps are (head_dim, kv_len, kv heads): rows past kv_len arrive as zeros, so a
+            // never-written cache row cannot meet a zero weight as NaN.
+            auto load_k = [&](uint32_t i) {
                 const uint32_t ks = i % kKStages, kph = (i / kKStages) & 1;
-                const uint32_t vs = i % kVStages, vph = (i / kVStages) & 1;
-                // K/V maps are (head_dim, kv_len, kv heads): rows past kv_len arrive as zeros, so a
-                // never-written cache row cannot meet a zero weight as NaN.
-                const int32_t key0 = (int32_t)(i * kBN);
                 TC_PROF_WAIT(0, wait(bar(kKEmpty + ks), kph ^ 1, 16u))
                 mbar_arrive_expect_tx(bar(kKFull + ks), kTile);
-                tma_load_3d(k_smem + ks * kTile, &tm_k, 0, key0, (int32_t)kvh, bar(kKFull + ks));
-                tma_load_3d(k_smem + ks * kTile + kHalfTile, &tm_k, 64, key0, (int32_t)kvh, bar(kKFull + ks));
+                tma_load_3d(k_smem + ks * kTile, &tm_k, 0, (int32_t)(i * kBN), (int32_t)kvh, bar(kKFull + ks));
+                tma_load_3d(k_smem + ks * kTile + kHalfTile, &tm_k, 64, (int32_t)(i * kBN), (int32_t)kvh, bar(kKFull + ks));
+            };
+            auto load_v = [&](uint32_t i) {
+                const uint32_t vs = i % kVStages, vph = (i / kVStages) & 1;
                 TC_PROF_WAIT(1, wait(bar(kVEmpty + vs), vph ^ 1, 16u))
                 mbar_arrive_expect_tx(bar(kVFull + vs), kTile);
-                tma_load_3d(v_smem + vs * kTile, &tm_v, 0, key0, (int32_t)kvh, bar(kVFull + vs));
-                tma_load_3d(v_smem + vs * kTile + kHalfTile, &tm_v, 64, key0, (int32_t)kvh, bar(kVFull + vs));
+                tma_load_3d(v_smem + vs * kTile, &tm_v, 0, (int32_t)(i * kBN), (int32_t)kvh, bar(kVFull + vs));
+                tma_load_3d(v_smem + vs * kTile + kHalfTile, &tm_v, 64, (int32_t)(i * kBN), (int32_t)kvh, bar(kVFull + vs));
+            };
+            // K runs two tiles ahead of V, the order in which the tensor pipe frees the rings.
+            for (uint32_t i = 0; i < min(n_tiles, 2u); ++i) load_k(i);
+            for (uint32_t i = 0; i < n_tiles; ++i) {
+                if (i + 2 < n_tiles) load_k(i + 2);
+                load_v(i);
             }
             TC_PROF_STORE(2)
         }
@@ -285,180 +285,212 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             TC_PROF_DECL
             wait(bar(kQFull), 0, 32u);
             auto issue_qk = [&](uint32_t i) {
-                const uint32_t s = i & 1, ph = (i >> 1) & 1;
+                const uint32_t x = i & 1;
                 const uint32_t ks = i % kKStages, kph = (i / kKStages) & 1;
                 TC_PROF_WAIT(0, wait(bar(kKFull + ks), kph, 32u))
-                TC_PROF_WAIT(1, wait(bar(kSEmpty + s), ph ^ 1, 32u))
                 tc_fence_after();
 #pragma unroll
                 for (uint32_t kk = 0; kk < kD / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * kHalfTile + (kk & 3) * 32;
-                    tc_mma_ss(tmem + s * 128, smem_desc(q_smem + off, 16, 1024),
+                    tc_mma_ss(tmem + x * 128, smem_desc(q_smem + off, 16, 1024),
                               smem_desc(k_smem + ks * kTile + off, 16, 1024), kIdescQK, kk > 0);
                 }
-                tc_commit(bar(kSFull + s));
+                tc_commit(bar(kSFull + x));
                 tc_commit(bar(kKEmpty + ks));
             };
             auto issue_pv = [&](uint32_t i) {
-                const uint32_t s = i & 1, ph = (i >> 1) & 1;
+                const uint32_t x = i & 1, j = i >> 1;
                 const uint32_t vs = i % kVStages, vph = (i / kVStages) & 1;
                 TC_PROF_WAIT(2, wait(bar(kVFull + vs), vph, 64u))
-                TC_PROF_WAIT(3, wait(bar(kPFull + s), ph, 64u))
-                TC_PROF_WAIT(3, wait(bar(kOtEmpty), (i & 1) ^ 1, 64u))
+                TC_PROF_WAIT(3, wait(bar(kPFull + x), j & 1, 64u))
                 tc_fence_after();
 #pragma unroll
                 for (uint32_t kk = 0; kk < kBN / 16; ++kk) {
                     // A: 16 keys = 8 packed 32-bit TMEM columns per step; B: V rows kk*16.., MN-major.
-                    tc_mma_ts(tmem + 256, tmem + 384 + s * 64 + kk * 8,
-                              smem_desc(v_smem + vs * kTile + kk * 2048, kHalfTile, 1024), kIdescPV, kk > 0);
+                    tc_mma_ts(tmem + 256 + x * 128, tmem + x * 128 + kk * 8,
+                              smem_desc(v_smem + vs * kTile + kk * 2048, kHalfTile, 1024), kIdescPV,
+                              (j > 0 || kk > 0) ? 1u : 0u);
                 }
-                tc_commit(bar(kOtFull));
+                tc_commit(bar(kOFull + x));
                 tc_commit(bar(kVEmpty + vs));
-                tc_commit(bar(kPEmpty + s));
             };
+            // Q K^T of a stream's next tile is issued right behind its P V: the tensor pipe runs
+            // them in order, so S_x is overwritten only after P (which lives in S_x) was consumed.
+            for (uint32_t i = 0; i < min(n_tiles, 2u); ++i) issue_qk(i);
             for (uint32_t i = 0; i < n_tiles; ++i) {
-                issue_qk(i);
-                if (i >= 1) issue_pv(i - 1);
+                issue_pv(i);
+                if (i + 2 < n_tiles) issue_qk(i + 2);
             }
-            if (n_tiles) issue_pv(n_tiles - 1);
             TC_PROF_STORE(1)
         }
     } else {
-        // ------------------------------------------------- softmax / accumulate / epilogue ---
-        const uint32_t quad = warp & 3, grp = warp >> 2;
+        // ------------------------------------------------- softmax / epilogue, two streams ---
+        const uint32_t x = warp >> 3;                           // stream
+        const uint32_t quad = warp & 3, half = (warp >> 2) & 1;
         const uint32_t r_in = quad * 32 + lane;                 // row inside the tile = TMEM lane
         const uint32_t row = row0 + r_in;
         const uint32_t lane_base = (quad * 32u) << 16;          // TMEM lane quadrant of this warp
         const uint32_t limit = row + p.query_offset;            // last visible key
-        const uint32_t col0 = grp * kColsPerThread;             // this thread's S / PV columns
-        constexpr uint32_t kRowThreads = 32 * kColGroups;       // threads that share a lane quadrant
-        float o[kColsPerThread];
-#pragma unroll
-        for (uint32_t d = 0; d < kColsPerThread; ++d) o[d] = 0.f;
-        float m_run = kNegInf, l_run = 0.f, alpha_saved = 1.f;  // m in the scaled log2 domain
+        const uint32_t col0 = half * 64;                        // this thread's 64 S / O columns
+        const uint32_t s_tm = tmem + lane_base + x * 128;       // S_x / P_x
+        const uint32_t o_tm = tmem + lane_base + 256 + x * 128 + col0;
+        const uint32_t pair_bar = 1 + x * 4 + quad;             // named barrier of the two warps of a row group
+        float *xbuf = max_buf + x * 512;                        // [tile parity][half][row]
+        const uint32_t n_mine = n_tiles > x ? (n_tiles - x + 1) / 2 : 0;
+        float m_ref = kNegInf, l_run = 0.f;                     // m in the scaled log2 domain
         TC_PROF_DECL
 
-        auto accumulate = [&](uint32_t i, float alpha) {
-            TC_PROF_WAIT(2, wait(bar(kOtFull), i & 1, 128u))
-            tc_fence_after();
-            uint32_t r[32];
-            tmem_ld32(tmem + lane_base + 256 + col0, r);
-            tc_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(kOtEmpty));  // the PV tile is in registers: P V may overwrite it
-#pragma unroll
-            for (uint32_t j = 0; j < 32; ++j) o[j] = fmaf(o[j], alpha, __uint_as_float(r[j]));
-        };
-
-        for (uint32_t i = 0; i < n_tiles; ++i) {
-            const uint32_t s = i & 1, ph = (i >> 1) & 1;
+        for (uint32_t j = 0; j < n_mine; ++j) {
+            const uint32_t i = 2 * j + x;
             const uint32_t key0 = i * kBN + col0;  // first key of this thread's columns
             // Only tiles on the causal diagonal or at the end of the cache need a mask; the
-            // number of this thread's columns that stay visible covers both conditions.
+            // number of this thread's 64 columns that stay visible covers both conditions.
             const uint32_t last_ok = min(limit, p.kv_len - 1);
-            const uint32_t n_vis = last_ok < key0 ? 0u : min(kColsPerThread, last_ok - key0 + 1);
-            TC_PROF_WAIT(0, wait(bar(kSFull + s), ph, 256u))
+            const uint32_t n_vis = last_ok < key0 ? 0u : min(64u, last_ok - key0 + 1);
+            TC_PROF_WAIT(0, wait(bar(kSFull + x), j & 1, 256u))
             tc_fence_after();
-            uint32_t r[32];
-#ifdef MF_TC_PROFILE
-            long long tp_ = clock64();
-#endif
-            tmem_ld32(tmem + lane_base + s * 128 + col0, r);
-            tc_wait_ld();
-#ifdef MF_TC_PROFILE
-            prof_acc[4] += (unsigned long long)(clock64() - tp_); tp_ = clock64();
-#endif
-            // row maximum of the raw scores (the scale is positive)
+            // pass 1: row maximum of the raw scores (the scale is positive), 32 columns at a time
             float mx = -3.0e38f;
-            if (n_vis == kColsPerThread) {
 #pragma unroll
-                for (uint32_t j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(r[j]));
-            } else {
+            for (uint32_t c = 0; c < 2; ++c) {
+                uint32_t r[32];
+                tmem_ld32(s_tm + col0 + c * 32, r);
+                tc_wait_ld();
+                float mx0 = -3.0e38f, mx1 = -3.0e38f, mx2 = -3.0e38f, mx3 = -3.0e38f;
+                if (n_vis >= (c + 1) * 32) {
 #pragma unroll
-                for (uint32_t j = 0; j < 32; ++j)
-                    if (j < n_vis) mx = fmaxf(mx, __uint_as_float(r[j]));
+                    for (uint32_t q = 0; q < 32; q += 4) {
+                        mx0 = fmaxf(mx0, __uint_as_float(r[q]));
+                        mx1 = fmaxf(mx1, __uint_as_float(r[q + 1]));
+                        mx2 = fmaxf(mx2, __uint_as_float(r[q + 2]));
+                        mx3 = fmaxf(mx3, __uint_as_float(r[q + 3]));
+                    }
+                } else {
+#pragma unroll
+                    for (uint32_t q = 0; q < 32; ++q)
+                        if (c * 32 + q < n_vis) mx0 = fmaxf(mx0, __uint_as_float(r[q]));
+                }
+                mx = fmaxf(mx, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
             }
-            // the other column groups of this row live in other warps: swap maxima through smem
-            float *mb = max_buf + (i & 1) * (kColGroups * 128);
-            mb[grp * 128 + r_in] = mx;
-            TC_PROF_WAIT(3, named_bar_sync(1 + quad, kRowThreads))
+            // the other half of this row lives in the partner warp: swap maxima through smem
+            float *mb = xbuf + (j & 1) * 256;
+            mb[half * 128 + r_in] = mx;
+            TC_PROF_WAIT(3, named_bar_sync(pair_bar, 64))
+            mx = fmaxf(mx, mb[(half ^ 1) * 128 + r_in]);
+            const float m_new = mx > -3.0e38f ? mx * p.scale_log2 : kNegInf;
+            // Lazy rescale: keep exponentiating against m_ref until a row outgrows it by 2^8.
+            const bool grow = m_new > m_ref + kRescaleThreshold;
+            if (__any_sync(0xffffffffu, grow)) {
+                const float m_next = grow ? m_new : m_ref;
+                const float alpha = fast_exp2(m_ref - m_next);
+                m_ref = m_next;
+                l_run *= alpha;
+                if (j > 0) {
+                    // O_x must hold every earlier P V before it is scaled.
+                    TC_PROF_WAIT(2, wait(bar(kOFull + x), (j - 1) & 1, 128u))
+                    tc_fence_after();
+                    uint32_t ob[32];
 #pragma unroll
-            for (uint32_t g = 0; g < kColGroups; ++g) mx = fmaxf(mx, mb[g * 128 + r_in]);
-            const float m_new = fmaxf(m_run, mx > -3.0e38f ? mx * p.scale_log2 : kNegInf);
-            const float alpha = fast_exp2(m_run - m_new);
-            m_run = m_new;
-#ifdef MF_TC_PROFILE
-            prof_acc[5] += (unsigned long long)(clock64() - tp_); tp_ = clock64();
-#endif
-            // weights -> P (f16) in TMEM, row sum
+                    for (uint32_t c = 0; c < 2; ++c) {
+                        tmem_ld32(o_tm + c * 32, ob);
+                        tc_wait_ld();
+#pragma unroll
+                        for (uint32_t q = 0; q < 32; ++q) ob[q] = __float_as_uint(__uint_as_float(ob[q]) * alpha);
+                        asm volatile(
+                            "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                            "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
+                            "%25,%26,%27,%28,%29,%30,%31,%32};"
+                            ::"r"(o_tm + c * 32), "r"(ob[0]), "r"(ob[1]), "r"(ob[2]), "r"(ob[3]), "r"(ob[4]), "r"(ob[5]),
+                              "r"(ob[6]), "r"(ob[7]), "r"(ob[8]), "r"(ob[9]), "r"(ob[10]), "r"(ob[11]), "r"(ob[12]),
+                              "r"(ob[13]), "r"(ob[14]), "r"(ob[15]), "r"(ob[16]), "r"(ob[17]), "r"(ob[18]), "r"(ob[19]),
+                              "r"(ob[20]), "r"(ob[21]), "r"(ob[22]), "r"(ob[23]), "r"(ob[24]), "r"(ob[25]), "r"(ob[26]),
+                              "r"(ob[27]), "r"(ob[28]), "r"(ob[29]), "r"(ob[30]), "r"(ob[31])
+                            : "memory");
+                    }
+                }
+            }
+            // pass 2: weights (f16) and row sum.  P goes over the first half of S_x, which also holds
+            // the partner's scores: both threads of a row finish reading S before either writes P.
             float sum0 = 0.f, sum1 = 0.f;
-            uint32_t pk[16];
-            if (n_vis == kColsPerThread) {
+            uint32_t pk[32];
 #pragma unroll
-                for (uint32_t j = 0; j < 32; j += 2) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(r[j]), p.scale_log2, -m_new));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(r[j + 1]), p.scale_log2, -m_new));
+            for (uint32_t c = 0; c < 2; ++c) {
+                uint32_t r[32];
+                tmem_ld32(s_tm + col0 + c * 32, r);
+                tc_wait_ld();
+                const bool full = n_vis >= (c + 1) * 32;
+#pragma unroll
+                for (uint32_t q = 0; q < 16; ++q) {
+                    float p0 = fast_exp2(fmaf(__uint_as_float(r[2 * q]), p.scale_log2, -m_ref));
+                    float p1 = fast_exp2(fmaf(__uint_as_float(r[2 * q + 1]), p.scale_log2, -m_ref));
+                    if (!full) {
+                        if (c * 32 + 2 * q >= n_vis) p0 = 0.f;
+                        if (c * 32 + 2 * q + 1 >= n_vis) p1 = 0.f;
+                    }
                     sum0 += p0;
                     sum1 += p1;
-                    pk[j >> 1] = pack_f16x2(p0, p1);
-                }
-            } else {
-#pragma unroll
-                for (uint32_t j = 0; j < 32; j += 2) {
-                    float p0 = fast_exp2(fmaf(__uint_as_float(r[j]), p.scale_log2, -m_new));
-                    float p1 = fast_exp2(fmaf(__uint_as_float(r[j + 1]), p.scale_log2, -m_new));
-                    if (j >= n_vis) p0 = 0.f;
-                    if (j + 1 >= n_vis) p1 = 0.f;
-                    sum0 += p0;
-                    sum1 += p1;
-                    pk[j >> 1] = pack_f16x2(p0, p1);
+                    pk[c * 16 + q] = pack_f16x2(p0, p1);
                 }
             }
-            const float sum = sum0 + sum1;
-#ifdef MF_TC_PROFILE
-            prof_acc[6] += (unsigned long long)(__float_as_uint(sum) & 0) + (unsigned long long)(clock64() - tp_); tp_ = clock64();
-#endif
-            TC_PROF_WAIT(1, wait(bar(kPEmpty + s), ph ^ 1, 512u))
-            tmem_st16(tmem + lane_base + 384 + s * 64 + grp * (kColsPerThread / 2), pk);
+            TC_PROF_WAIT(3, named_bar_sync(pair_bar, 64))
+            tmem_st16(s_tm + half * 32, *reinterpret_cast<uint32_t(*)[16]>(&pk[0]));
+            tmem_st16(s_tm + half * 32 + 16, *reinterpret_cast<uint32_t(*)[16]>(&pk[16]));
+            l_run += sum0 + sum1;  // partial sum over this thread's columns, relative to m_ref
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(bar(kSEmpty + s));  // S(i) is in registers: its buffer may be overwritten
-                mbar_arrive(bar(kPFull + s));   // P(i) is in TMEM
-            }
-#ifdef MF_TC_PROFILE
-            prof_acc[7] += (unsigned long long)(clock64() - tp_);
-#endif
-            l_run = l_run * alpha + sum;    // partial sum over this thread's columns
-            if (i >= 1) accumulate(i - 1, alpha_saved);
-            alpha_saved = alpha;
-        }
-        if (n_tiles) accumulate(n_tiles - 1, alpha_saved);
-        if (tid == 0) {
-            TC_PROF_STORE(0)
+            if (lane == 0) mbar_arrive(bar(kPFull + x));  // P(i) is in TMEM, O_x is consistent with m_ref
         }
 
-        // total l = all column groups of the row
-        float *lb = max_buf + (n_tiles & 1) * (kColGroups * 128);
-        lb[grp * 128 + r_in] = l_run;
-        named_bar_sync(1 + quad, kRowThreads);
-        l_run = 0.f;
+        // ---- merge the two streams and write the rows out --------------------------------------
+        float o[64];
+        if (n_mine) {
+            TC_PROF_WAIT(2, wait(bar(kOFull + x), (n_mine - 1) & 1, 128u))
+            tc_fence_after();
+            tmem_ld32(o_tm, *reinterpret_cast<uint32_t(*)[32]>(&o[0]));
+            tmem_ld32(o_tm + 32, *reinterpret_cast<uint32_t(*)[32]>(&o[32]));
+            tc_wait_ld();
+        } else {
 #pragma unroll
-        for (uint32_t g = 0; g < kColGroups; ++g) l_run += lb[g * 128 + r_in];
-        if (row < p.q_len) {
-            const float inv = ((fabsf(l_run) <= 3.0e38f) && fabsf(l_run) > 1e-6f) ? 1.0f / l_run : 0.f;
+            for (uint32_t c = 0; c < 64; ++c) o[c] = 0.f;
+        }
+        // Every product has completed (both streams waited for their last P V), so the K ring can
+        // carry stream 1's accumulator over to stream 0: [row][128] f32 = 64 KB, plus (m, l).
+        float *xo = reinterpret_cast<float *>(smem + kTile);     // K ring
+        float *xl = max_buf;                                      // [stream][half][row] partial l
+        float *xm = max_buf + 512;                                // [stream][row] reference maxima
+        named_bar_sync(9, kSoftmaxThreads);  // all softmax warps are past their tile loops
+        xl[(x * 2 + half) * 128 + r_in] = l_run;
+        if (half == 0) xm[x * 128 + r_in] = m_ref;
+        if (x == 1) {
+#pragma unroll
+            for (uint32_t c = 0; c < 64; c += 4)
+                *reinterpret_cast<float4 *>(xo + (size_t)r_in * 132 + col0 + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+        }
+        named_bar_sync(10, kSoftmaxThreads);
+        if (x == 0 && row < p.q_len) {
+            const float m0 = xm[r_in], m1 = xm[128 + r_in];
+            const float mm = fmaxf(m0, m1);
+            const float w0 = fast_exp2(m0 - mm), w1 = fast_exp2(m1 - mm);
+            const float l_tot = (xl[r_in] + xl[128 + r_in]) * w0 + (xl[256 + r_in] + xl[384 + r_in]) * w1;
+            const float inv = ((fabsf(l_tot) <= 3.0e38f) && fabsf(l_tot) > 1e-6f) ? 1.0f / l_tot : 0.f;
+            const float f0 = w0 * inv, f1 = w1 * inv;
             __half *dst = p.out + (size_t)row * p.out_stride_m + (size_t)head * p.out_stride_h + col0;
+            const float *other = xo + (size_t)r_in * 132 + col0;
 #pragma unroll
-            for (uint32_t d = 0; d < kColsPerThread; d += 8) {
+            for (uint32_t d = 0; d < 64; d += 8) {
+                const float4 a = *reinterpret_cast<const float4 *>(other + d);
+                const float4 b = *reinterpret_cast<const float4 *>(other + d + 4);
                 uint4 v;
-                v.x = pack_f16x2(o[d] * inv, o[d + 1] * inv);
-                v.y = pack_f16x2(o[d + 2] * inv, o[d + 3] * inv);
-                v.z = pack_f16x2(o[d + 4] * inv, o[d + 5] * inv);
-                v.w = pack_f16x2(o[d + 6] * inv, o[d + 7] * inv);
+                v.x = pack_f16x2(o[d] * f0 + a.x * f1, o[d + 1] * f0 + a.y * f1);
+                v.y = pack_f16x2(o[d + 2] * f0 + a.z * f1, o[d + 3] * f0 + a.w * f1);
+                v.z = pack_f16x2(o[d + 4] * f0 + b.x * f1, o[d + 5] * f0 + b.y * f1);
+                v.w = pack_f16x2(o[d + 6] * f0 + b.z * f1, o[d + 7] * f0 + b.w * f1);
                 *reinterpret_cast<uint4 *>(dst + d) = v;
             }
+        }
+        if (tid == 0) {
+            TC_PROF_STORE(0)
         }
     }
 
