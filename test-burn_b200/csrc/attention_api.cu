@@ -83,8 +83,7 @@ mf_status decode_contiguous(MfContext *ctx, const void *q, const void *k, const 
     if (n_splits > 0) {
         span = (T + n_splits - 1) / n_splits;
     } else {
-        const uint32_t want = (uint32_t)std::min<uint64_t>(
-            total, (uint64_t)ctx->sm_count * decode_ctas_per_sm(ctx, D, group));
+        const uint32_t want = decode_cta_target((uint32_t)ctx->sm_count, decode_ctas_per_sm(ctx, D, group), total);
         span = (uint32_t)((total + want - 1) / want);
     }
     span = std::max(1u, span);
@@ -427,7 +426,8 @@ mf_status mf_decode_plan_create(MfContext *ctx, const uint32_t *kv_lens_host, ui
         return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "Flash Decode only supports head_dim=64 or 128, got %u", head_dim);
     if (n_heads / n_kv_heads > 16)
         return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "decode plan: group size %u > 16", n_heads / n_kv_heads);
-    if (max_ctas == 0) max_ctas = (uint32_t)ctx->sm_count * decode_ctas_per_sm(ctx, head_dim, n_heads / n_kv_heads);
+    const bool auto_ctas = (max_ctas == 0);
+    if (auto_ctas) max_ctas = (uint32_t)ctx->sm_count * decode_ctas_per_sm(ctx, head_dim, n_heads / n_kv_heads);
     MfDecodePlan *pl = new MfDecodePlan();
     pl->batch = batch;
     pl->n_heads = n_heads;
@@ -435,6 +435,9 @@ mf_status mf_decode_plan_create(MfContext *ctx, const uint32_t *kv_lens_host, ui
     pl->head_dim = head_dim;
     pl->page_size = page_size;
     pl->max_ctas = max_ctas;
+    pl->auto_ctas = auto_ctas;
+    pl->ctas_per_sm = decode_ctas_per_sm(ctx, head_dim, n_heads / n_kv_heads);
+    pl->sm_count = (uint32_t)ctx->sm_count;
     pl->n_units = batch * n_kv_heads;
     pl->item_capacity = pl->n_units + max_ctas;
     pl->heads_padded = heads_padded(n_heads / n_kv_heads);
@@ -470,7 +473,13 @@ mf_status mf_decode_plan_update(MfContext *ctx, MfDecodePlan *pl, const uint32_t
 {
     if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
     if (!pl || !kv_lens_host) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "decode plan: null input");
-    build_decode_plan(kv_lens_host, pl->batch, pl->n_kv_heads, pl->max_ctas, pl->h_items, pl->h_cta_begin, &pl->n_units,
+    uint32_t ctas = pl->max_ctas;
+    if (pl->auto_ctas) {
+        uint64_t total = 0;
+        for (uint32_t b = 0; b < pl->batch; ++b) total += (uint64_t)((kv_lens_host[b] + kTileKeys - 1) / kTileKeys) * pl->n_kv_heads;
+        ctas = decode_cta_target(pl->sm_count, pl->ctas_per_sm, total);
+    }
+    build_decode_plan(kv_lens_host, pl->batch, pl->n_kv_heads, ctas, pl->h_items, pl->h_cta_begin, &pl->n_units,
                       &pl->total_tiles);
     return plan_upload(ctx, pl);
 }

@@ -571,7 +571,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         // in flight together: this runs at the end of a CTA's work, where latency is not hidden.
         constexpr uint32_t kMergeCap = 64;                       // parts whose m is cached in smem
         constexpr uint32_t kPerHead = kConsumerThreads / HP;     // threads per head in pass 1
-        constexpr uint32_t EPT = HP * D / kConsumerThreads;      // consecutive outputs per thread
         float *msv = comb;                                       // [kMergeCap][HP]
         float *red = comb + kMergeCap * HP;                      // [threads][2]
         {
@@ -588,51 +587,43 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             red[tid * 2 + 1] = l_loc;
         }
         named_bar_sync(1, kConsumerThreads);
-        const uint32_t g2 = (tid * EPT) / D, d0 = (tid * EPT) % D;
-        float mx = kNegSentinel, lt = 0.f;
+        // Pass 2: one float4 column of one real head per thread and round, eight parts in flight.
+        const uint32_t cols4 = G * (D / 4);
+        for (uint32_t c4 = tid; c4 < cols4; c4 += kConsumerThreads) {
+            const uint32_t g2 = c4 / (D / 4), d0 = (c4 % (D / 4)) * 4;
+            float mx = kNegSentinel, lt = 0.f;
 #pragma unroll
-        for (uint32_t j = 0; j < kPerHead; ++j) mx = fmaxf(mx, red[(j * HP + g2) * 2]);
+            for (uint32_t j = 0; j < kPerHead; ++j) mx = fmaxf(mx, red[(j * HP + g2) * 2]);
 #pragma unroll
-        for (uint32_t j = 0; j < kPerHead; ++j) lt += red[(j * HP + g2) * 2 + 1] * __expf(red[(j * HP + g2) * 2] - mx);
-        float acc[EPT];
+            for (uint32_t j = 0; j < kPerHead; ++j) lt += red[(j * HP + g2) * 2 + 1] * __expf(red[(j * HP + g2) * 2] - mx);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (uint32_t s0 = 0; s0 < it.n_parts; s0 += 8) {
+                float4 v[8];
+                float w[8];
 #pragma unroll
-        for (uint32_t i = 0; i < EPT; ++i) acc[i] = 0.f;
-        for (uint32_t s0 = 0; s0 < it.n_parts; s0 += 4) {
-            float4 v[4][EPT / 4];
-            float w[4];
+                for (uint32_t j = 0; j < 8; ++j) {
+                    const uint32_t sp = s0 + j;
+                    if (sp < it.n_parts) {
+                        const size_t sl = it.first_slot + sp;
+                        v[j] = __ldcg(reinterpret_cast<const float4 *>(p.part_acc + (sl * HP + g2) * D + d0));
+                        const float ms = sp < kMergeCap ? msv[sp * HP + g2] : __ldcg(p.part_ml + (sl * HP + g2) * 2);
+                        w[j] = __expf(ms - mx);
+                    } else {
+                        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        w[j] = 0.f;
+                    }
+                }
 #pragma unroll
-            for (uint32_t j = 0; j < 4; ++j) {
-                const uint32_t sp = s0 + j;
-                if (sp < it.n_parts) {
-                    const size_t sl = it.first_slot + sp;
-                    const float4 *src = reinterpret_cast<const float4 *>(p.part_acc + (sl * HP + g2) * D + d0);
-#pragma unroll
-                    for (uint32_t q4 = 0; q4 < EPT / 4; ++q4) v[j][q4] = __ldcg(src + q4);
-                    const float ms = sp < kMergeCap ? msv[sp * HP + g2] : __ldcg(p.part_ml + (sl * HP + g2) * 2);
-                    w[j] = __expf(ms - mx);
-                } else {
-#pragma unroll
-                    for (uint32_t q4 = 0; q4 < EPT / 4; ++q4) v[j][q4] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    w[j] = 0.f;
+                for (uint32_t j = 0; j < 8; ++j) {
+                    acc.x += v[j].x * w[j];
+                    acc.y += v[j].y * w[j];
+                    acc.z += v[j].z * w[j];
+                    acc.w += v[j].w * w[j];
                 }
             }
-#pragma unroll
-            for (uint32_t j = 0; j < 4; ++j) {
-#pragma unroll
-                for (uint32_t q4 = 0; q4 < EPT / 4; ++q4) {
-                    acc[q4 * 4 + 0] += v[j][q4].x * w[j];
-                    acc[q4 * 4 + 1] += v[j][q4].y * w[j];
-                    acc[q4 * 4 + 2] += v[j][q4].z * w[j];
-                    acc[q4 * 4 + 3] += v[j][q4].w * w[j];
-                }
-            }
-        }
-        if (g2 < G) {
             const uint32_t h = it.kvh * G + g2;
             if (partial_out) {
-                float *dst = p.out_acc + ((size_t)it.seq * p.n_heads + h) * D + d0;
-#pragma unroll
-                for (uint32_t i = 0; i < EPT; ++i) dst[i] = acc[i];
+                *reinterpret_cast<float4 *>(p.out_acc + ((size_t)it.seq * p.n_heads + h) * D + d0) = acc;
                 if (d0 == 0) {
                     p.out_m[(size_t)it.seq * p.n_heads + h] = mx;
                     p.out_l[(size_t)it.seq * p.n_heads + h] = lt;
@@ -640,12 +631,12 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             } else {
                 const bool ok = (fabsf(lt) <= 3.0e38f) && fabsf(lt) > 1e-6f;
                 const float inv = ok ? 1.0f / lt : 0.f;  // merge rule: flash_prefill.metal:861
+                float r[4] = {acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv};
                 __half *dst = p.out + (size_t)it.seq * p.out_stride_b + (size_t)h * p.out_stride_h + d0;
 #pragma unroll
-                for (uint32_t i = 0; i < EPT; ++i) {
-                    float r = acc[i] * inv;
-                    if (!(fabsf(r) <= 3.0e38f)) r = 0.f;
-                    dst[i] = __float2half_rn(r);
+                for (uint32_t i = 0; i < 4; ++i) {
+                    if (!(fabsf(r[i]) <= 3.0e38f)) r[i] = 0.f;
+                    dst[i] = __float2half_rn(r[i]);
                 }
             }
         }
@@ -694,6 +685,18 @@ uint32_t decode_ctas_per_sm(const MfContext *ctx, uint32_t head_dim, uint32_t gr
     if (group > 8) return 1;
     if (head_dim == 128 && ctx && ctx->decode_stages == 6) return 1;
     return 2;
+}
+
+// Number of CTAs for `total` tiles: as many as are resident, but a span shorter than eight
+// tiles mostly pays for its own boundary (q load, combine, partial write, a longer merge), so
+// small problems get one CTA per SM.
+uint32_t decode_cta_target(uint32_t sm_count, uint32_t ctas_per_sm, uint64_t total)
+{
+    const uint64_t resident = (uint64_t)sm_count * ctas_per_sm;
+    uint64_t want = resident;
+    if (ctas_per_sm > 1 && total < resident * 8) want = sm_count;
+    if (want > total) want = total;
+    return (uint32_t)(want ? want : 1);
 }
 
 mf_status launch_decode(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap &tm_v,
@@ -917,8 +920,7 @@ extern "C" mf_status mf_flash_decode_static_scratch(void *cuda_stream, const voi
     const uint64_t U = (uint64_t)batch * cache_heads;
     const uint64_t total = U * T;
     if (total > 0xFFFFFFFFull) return static_fail(err, err_len, MF_ERR_OPERATION_NOT_SUPPORTED, "too many tiles");
-    const uint64_t resident = (uint64_t)dst.sm_count * (group > 8 ? 1 : 2);  // the rule of mf_flash_decode
-    const uint64_t want = total < resident ? total : resident;
+    const uint64_t want = decode_cta_target((uint32_t)dst.sm_count, group > 8 ? 1 : 2, total);  // as mf_flash_decode
     const uint32_t span = (uint32_t)((total + want - 1) / want);
     const uint32_t n_ctas = (uint32_t)((total + span - 1) / span);
     const uint32_t HP = 8 * ((group + 7) / 8);

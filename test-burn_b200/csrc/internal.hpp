@@ -111,6 +111,8 @@ struct MfContext {
 struct MfDecodePlan {
     uint32_t batch = 0, n_heads = 0, n_kv_heads = 0, head_dim = 0, page_size = 0;
     uint32_t max_ctas = 0, n_ctas = 0, n_items = 0, n_units = 0;
+    bool auto_ctas = false;           // the library picks the CTA count from the step's tile total
+    uint32_t ctas_per_sm = 1, sm_count = 0;
     uint64_t total_tiles = 0;
     uint32_t item_capacity = 0;
     std::vector<mf::WorkItem> h_items;
@@ -159,6 +161,7 @@ void build_decode_plan(const uint32_t *kv_lens, uint32_t batch, uint32_t n_kv_he
 
 // Resident decode CTAs per SM for a head_dim / GQA group size (decode.cu).
 uint32_t decode_ctas_per_sm(const MfContext *ctx, uint32_t head_dim, uint32_t group);
+uint32_t decode_cta_target(uint32_t sm_count, uint32_t ctas_per_sm, uint64_t total_tiles);
 
 // Launchers (decode.cu, prefill.cu, kv_append.cu).
 mf_status launch_decode(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap &tm_v,
