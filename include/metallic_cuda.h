@@ -302,6 +302,15 @@ MF_API mf_status mf_kv_cache_write_repeat_kv_heads(MfContext *ctx, const MfTenso
 MF_API mf_status mf_kv_cache_read(MfContext *ctx, const MfTensor *cache, const MfTensor *output,
                                   uint32_t seq_len);
 
+/* KV growth copy, preserve_kv_cache inside reallocate_kv_buffers
+ * (src/model/executor.rs:2437-2513): rows [0, current_pos) of every head move from a
+ * cache [heads, old_capacity, D] to one [heads, new_capacity, D]; the head stride changes
+ * with the capacity, so the reference issues one blit per head - here one launch.  The
+ * new capacity itself comes from mf_grown_capacity; RoPE tables are extended with
+ * mf_rope_tables_host(first_pos = old length). */
+MF_API mf_status mf_kv_cache_grow(MfContext *ctx, const MfTensor *old_cache, const MfTensor *new_cache,
+                                  uint32_t current_pos);
+
 /* "FlashAttention" (src/metals/sdpa/step.rs:160-503): the dispatcher.  m == 1
  * routes to decode, m > 1 (causal, query_offset + m == kv_seq_len) to prefill;
  * anything else returns MF_ERR_OPERATION_NOT_SUPPORTED (the reference falls back
@@ -414,6 +423,12 @@ MF_API mf_status mf_paged_kv_append(MfContext *ctx, const MfPagedKv *cache, cons
                                     const void *sin, uint32_t n_heads, uint32_t rope_mode,
                                     uint32_t apply_rope, uint32_t seq, uint32_t position_offset,
                                     uint32_t seq_len);
+
+/* Migration of a contiguous compact cache [Hkv, capacity, D] into the pages of sequence
+ * `seq`: rows [0, len) of every kv head (K pool when use_v == 0, V pool otherwise).  No
+ * counterpart in the reference; the inverse of mf_paged_gather. */
+MF_API mf_status mf_kv_cache_to_pages(MfContext *ctx, const MfTensor *cache, const MfPagedKv *paged,
+                                      uint32_t use_v, uint32_t seq, uint32_t len);
 
 /* Debug/oracle gather: first `len` tokens of sequence `seq` -> [Hkv, len, D]. */
 MF_API mf_status mf_paged_gather(MfContext *ctx, const MfPagedKv *cache, uint32_t use_v,

@@ -73,6 +73,8 @@ def lib() -> C.CDLL:
     L.mfo_kv_cache_write_repeat.argtypes = [u16p, u16p, u32, u32, u32, u32, u32, u32]
     L.mfo_kv_cache_read.argtypes = [u16p, u16p, u32, u32, u32, u32]
     L.mfo_repeat_kv_heads.argtypes = [u16p, u16p, u32, u32, u32, u32]
+    L.mfo_kv_cache_grow.argtypes = [u16p, u16p, u32, u32, u32, u32, u32]
+    L.mfo_paged_scatter.argtypes = [u16p, u16p, u32p, u32, u32, u32, u32, u32]
     L.mfo_kv_prep_fused.argtypes = [u16p, u16p, u16p, u16p, u16p, u16p, u16p, u16p,
                                     C.POINTER(KvPrepParams), C.c_int]
     L.mfo_paged_kv_append.argtypes = [u16p, u16p, u16p, u16p, u16p, u16p, u16p, u16p, u32p, u32,

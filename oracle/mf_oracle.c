@@ -231,6 +231,26 @@ void mfo_kv_cache_read(const uint16_t *cache, uint16_t *out, uint32_t n_kv_heads
                (size_t)seq_len * head_dim * 2);
 }
 
+void mfo_kv_cache_grow(const uint16_t *old_cache, uint16_t *new_cache, uint32_t heads, uint32_t head_dim,
+                       uint32_t old_capacity, uint32_t new_capacity, uint32_t current_pos)
+{
+    /* src/model/executor.rs:2493-2504: one copy of current_pos*head_dim*2 bytes per head */
+    for (uint32_t h = 0; h < heads; ++h)
+        memcpy(new_cache + (size_t)h * new_capacity * head_dim, old_cache + (size_t)h * old_capacity * head_dim,
+               (size_t)current_pos * head_dim * 2);
+}
+
+void mfo_paged_scatter(const uint16_t *cache, uint16_t *pool, const uint32_t *page_table_row, uint32_t L,
+                       uint32_t n_kv_heads, uint32_t capacity, uint32_t page_size, uint32_t head_dim)
+{
+    for (uint32_t kh = 0; kh < n_kv_heads; ++kh)
+        for (uint32_t t = 0; t < L; ++t) {
+            uint32_t page = page_table_row[t / page_size];
+            size_t dst = (((size_t)page * n_kv_heads + kh) * page_size + t % page_size) * head_dim;
+            memcpy(pool + dst, cache + ((size_t)kh * capacity + t) * head_dim, (size_t)head_dim * 2);
+        }
+}
+
 void mfo_repeat_kv_heads(const uint16_t *in, uint16_t *out, uint32_t n_kv_heads,
                          uint32_t group_size, uint32_t seq, uint32_t head_dim)
 {

@@ -89,6 +89,15 @@ void mfo_kv_cache_write_repeat(uint16_t *cache, const uint16_t *in, uint32_t n_k
 void mfo_kv_cache_read(const uint16_t *cache, uint16_t *out, uint32_t n_kv_heads,
                        uint32_t head_dim, uint32_t seq_len, uint32_t max_seq_len);
 
+/* Growth copy (src/model/executor.rs:2493-2504): per head, current_pos rows move from the old
+ * capacity's stride to the new one. */
+void mfo_kv_cache_grow(const uint16_t *old_cache, uint16_t *new_cache, uint32_t heads, uint32_t head_dim,
+                       uint32_t old_capacity, uint32_t new_capacity, uint32_t current_pos);
+
+/* Contiguous cache rows [0, L) -> pages of one sequence (not in the reference). */
+void mfo_paged_scatter(const uint16_t *cache, uint16_t *pool, const uint32_t *page_table_row, uint32_t L,
+                       uint32_t n_kv_heads, uint32_t capacity, uint32_t page_size, uint32_t head_dim);
+
 /* repeat_kv_heads.metal:11-44: [Hkv, L, D] -> [Hkv*G, L, D]. */
 void mfo_repeat_kv_heads(const uint16_t *in, uint16_t *out, uint32_t n_kv_heads,
                          uint32_t group_size, uint32_t seq, uint32_t head_dim);

@@ -124,6 +124,8 @@ _SIGNATURES = {
     "mf_kv_cache_write_repeat_kv_heads": (C.c_int32, [vp, C.POINTER(MfTensor), C.POINTER(MfTensor),
                                                       C.POINTER(KvCacheWriteRepeatKvHeadsParamsResolved)]),
     "mf_kv_cache_read": (C.c_int32, [vp, C.POINTER(MfTensor), C.POINTER(MfTensor), u32]),
+    "mf_kv_cache_grow": (C.c_int32, [vp, C.POINTER(MfTensor), C.POINTER(MfTensor), u32]),
+    "mf_kv_cache_to_pages": (C.c_int32, [vp, C.POINTER(MfTensor), C.POINTER(MfPagedKv), u32, u32, u32]),
     "mf_flash_attention": (C.c_int32, [vp] + [C.POINTER(MfTensor)] * 4 + [C.POINTER(MfFlashAttentionArgs),
                                                                          C.POINTER(u32)]),
     "mf_run_flash_decode": (C.c_int32, [vp] + [C.POINTER(MfTensor)] * 4 + [u32] * 5),
@@ -246,6 +248,15 @@ class Foundry:
     def kv_cache_read(self, cache, out, seq_len: int):
         a, b = tensor_arg(cache), tensor_arg(out)
         self.check(lib.mf_kv_cache_read(self._h, C.byref(a), C.byref(b), seq_len))
+
+    def kv_cache_grow(self, old_cache, new_cache, current_pos: int):
+        """preserve_kv_cache of reallocate_kv_buffers (src/model/executor.rs:2437-2513)."""
+        a, b = tensor_arg(old_cache), tensor_arg(new_cache)
+        self.check(lib.mf_kv_cache_grow(self._h, C.byref(a), C.byref(b), current_pos))
+
+    def kv_cache_to_pages(self, cache, paged: MfPagedKv, use_v: bool, seq: int, length: int):
+        a = tensor_arg(cache)
+        self.check(lib.mf_kv_cache_to_pages(self._h, C.byref(a), C.byref(paged), int(use_v), seq, length))
 
     def flash_attention(self, q, k, v, output, *, causal, query_offset, n_heads, head_dim, kv_seq_len, m=1,
                         kv_head_major=True, q_meta=None, out_meta=None) -> int:

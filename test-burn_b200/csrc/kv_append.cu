@@ -192,10 +192,12 @@ cache_write_kernel(const __half *in, __half *cache, uint32_t n_kv_heads, uint32_
                                    8 * j) = x;
 }
 
-// cache [H, cap, D] -> [H, L, D]; with a page table: pool -> [Hkv, L, D] of one sequence.
+// cache [H, cap, D] -> [H, out_rows, D] rows [0, len); with a page table: pool -> rows of one sequence.
+// out_rows == len packs the result (KvCacheRead); out_rows == a larger capacity re-strides the cache
+// (growth: the head stride changes with the capacity, src/model/executor.rs:2493-2504).
 __global__ void __launch_bounds__(256)
 cache_read_kernel(const __half *cache, __half *out, uint32_t heads, uint32_t head_dim, uint32_t len,
-                  uint32_t max_seq_len, const uint32_t *page_table_row, uint32_t page_size)
+                  uint32_t max_seq_len, const uint32_t *page_table_row, uint32_t page_size, uint32_t out_rows)
 {
     const uint32_t cpr = head_dim / 8;
     const uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -210,8 +212,26 @@ cache_read_kernel(const __half *cache, __half *out, uint32_t heads, uint32_t hea
     } else {
         src = cache + ((size_t)h * max_seq_len + t) * head_dim;
     }
-    *reinterpret_cast<uint4 *>(out + ((size_t)h * len + t) * head_dim + 8 * j) =
+    *reinterpret_cast<uint4 *>(out + ((size_t)h * out_rows + t) * head_dim + 8 * j) =
         *reinterpret_cast<const uint4 *>(src + 8 * j);
+}
+
+// Contiguous cache rows [0, len) of every kv head -> the pages of one sequence (migration of a
+// contiguous cache into the paged pool; the inverse of the paged read above).
+__global__ void __launch_bounds__(256)
+cache_to_pages_kernel(const __half *cache, __half *pool, uint32_t heads, uint32_t head_dim, uint32_t len,
+                      uint32_t max_seq_len, const uint32_t *page_table_row, uint32_t page_size)
+{
+    const uint32_t cpr = head_dim / 8;
+    const uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= (uint64_t)heads * len * cpr) return;
+    const uint32_t j = gid % cpr;
+    const uint32_t t = (gid / cpr) % len;
+    const uint32_t h = gid / ((uint64_t)cpr * len);
+    const uint32_t page = page_table_row[t / page_size];
+    __half *dst = pool + (((size_t)page * heads + h) * page_size + t % page_size) * head_dim;
+    *reinterpret_cast<uint4 *>(dst + 8 * j) =
+        *reinterpret_cast<const uint4 *>(cache + ((size_t)h * max_seq_len + t) * head_dim + 8 * j);
 }
 
 inline uint32_t blocks_for(uint64_t threads) { return (uint32_t)((threads + 255) / 256); }
@@ -415,8 +435,54 @@ mf_status mf_kv_cache_read(MfContext *ctx, const MfTensor *cache, const MfTensor
     if (seq_len == 0) return MF_OK;
     const uint32_t heads = (uint32_t)cache->dims[0], hd = (uint32_t)cache->dims[2];
     cache_read_kernel<<<blocks_for((uint64_t)heads * seq_len * (hd / 8)), 256, 0, ctx->stream>>>(
-        tensor_ptr(cache), tensor_ptr(output), heads, hd, seq_len, (uint32_t)cache->dims[1], nullptr, 0);
+        tensor_ptr(cache), tensor_ptr(output), heads, hd, seq_len, (uint32_t)cache->dims[1], nullptr, 0, seq_len);
     return check_launch(ctx, "cache_read_kernel");
+}
+
+// reallocate_kv_buffers / preserve_kv_cache (src/model/executor.rs:2437-2513).
+mf_status mf_kv_cache_grow(MfContext *ctx, const MfTensor *old_cache, const MfTensor *new_cache, uint32_t current_pos)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    mf_status st;
+    if ((st = need_tensor(ctx, old_cache, "old cache")) != MF_OK) return st;
+    if ((st = need_tensor(ctx, new_cache, "new cache")) != MF_OK) return st;
+    if (old_cache->rank != 3 || new_cache->rank != 3)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "KV cache tensor must be rank-3 [heads, seq, head_dim]");
+    if (old_cache->dims[0] != new_cache->dims[0])
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "KV cache layout changed during growth: old heads=%llu, new heads=%llu",
+                    (unsigned long long)old_cache->dims[0], (unsigned long long)new_cache->dims[0]);
+    if (old_cache->dims[2] != new_cache->dims[2] || old_cache->dims[2] % 8 != 0)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "KV cache head_dim mismatch during growth");
+    if (current_pos > old_cache->dims[1] || current_pos > new_cache->dims[1])
+        return fail(ctx, MF_ERR_INVALID_OPERATION, "KV growth: %u tokens do not fit capacities %llu -> %llu", current_pos,
+                    (unsigned long long)old_cache->dims[1], (unsigned long long)new_cache->dims[1]);
+    if (current_pos == 0) return MF_OK;
+    const uint32_t heads = (uint32_t)old_cache->dims[0], hd = (uint32_t)old_cache->dims[2];
+    cache_read_kernel<<<blocks_for((uint64_t)heads * current_pos * (hd / 8)), 256, 0, ctx->stream>>>(
+        tensor_ptr(old_cache), tensor_ptr(new_cache), heads, hd, current_pos, (uint32_t)old_cache->dims[1], nullptr, 0,
+        (uint32_t)new_cache->dims[1]);
+    return check_launch(ctx, "cache_read_kernel(grow)");
+}
+
+mf_status mf_kv_cache_to_pages(MfContext *ctx, const MfTensor *cache, const MfPagedKv *paged, uint32_t use_v, uint32_t seq,
+                               uint32_t len)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    mf_status st;
+    if ((st = need_tensor(ctx, cache, "cache")) != MF_OK) return st;
+    if (!paged || !paged->k_pool || !paged->v_pool || !paged->page_table)
+        return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "cache to pages: null input");
+    if (cache->rank != 3 || cache->dims[0] != paged->n_kv_heads || cache->dims[2] != paged->head_dim)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "cache to pages: the cache must be compact [n_kv_heads, capacity, head_dim]");
+    if (seq >= paged->batch) return fail(ctx, MF_ERR_INVALID_OPERATION, "cache to pages: sequence %u of %u", seq, paged->batch);
+    if (len > cache->dims[1] || ((uint64_t)len + paged->page_size - 1) / paged->page_size > paged->page_table_stride)
+        return fail(ctx, MF_ERR_INVALID_OPERATION, "cache to pages: %u tokens exceed the cache or the page table", len);
+    if (len == 0) return MF_OK;
+    __half *pool = static_cast<__half *>(use_v ? paged->v_pool : paged->k_pool);
+    cache_to_pages_kernel<<<blocks_for((uint64_t)paged->n_kv_heads * len * (paged->head_dim / 8)), 256, 0, ctx->stream>>>(
+        tensor_ptr(cache), pool, paged->n_kv_heads, paged->head_dim, len, (uint32_t)cache->dims[1],
+        paged->page_table + (size_t)seq * paged->page_table_stride, paged->page_size);
+    return check_launch(ctx, "cache_to_pages_kernel");
 }
 
 mf_status mf_paged_gather(MfContext *ctx, const MfPagedKv *cache, uint32_t use_v, uint32_t seq, uint32_t len, void *out)
@@ -431,7 +497,7 @@ mf_status mf_paged_gather(MfContext *ctx, const MfPagedKv *cache, uint32_t use_v
     const __half *pool = static_cast<const __half *>(use_v ? cache->v_pool : cache->k_pool);
     cache_read_kernel<<<blocks_for((uint64_t)cache->n_kv_heads * len * (cache->head_dim / 8)), 256, 0, ctx->stream>>>(
         pool, static_cast<__half *>(out), cache->n_kv_heads, cache->head_dim, len, 0,
-        cache->page_table + (size_t)seq * cache->page_table_stride, cache->page_size);
+        cache->page_table + (size_t)seq * cache->page_table_stride, cache->page_size, len);
     return check_launch(ctx, "cache_read_kernel(paged)");
 }
 
