@@ -333,6 +333,9 @@ def run_ours(args, w):
     ok = bool(torch.isfinite(d_out[-1].float()).all()) and bool(torch.equal(h_out[-1].to(dev), d_out[-1]))
     result["self_check"] = "ok" if ok else "FAILED"
     plan.close()
+    if px is not None:
+        barrier()  # nobody unmaps while a peer may still store
+        f.peer_exchange_destroy(px)
     f.close()
     if world > 1:
         dist.destroy_process_group()
@@ -389,8 +392,35 @@ def run_long_context(args, w):
     gathered = torch.empty((world, block), dtype=torch.float32, device=dev)
     scale = 1.0 / math.sqrt(d)
     append_here = rank == owner
+    px, step_no = None, [0]
+    if args.exchange == "push":
+        # the kernels exchange the partials themselves: peer stores into every rank's receive block
+        px, handle = f.peer_exchange_create(world, rank, hq, d)
+        if world > 1:
+            handles = [None] * world
+            dist.all_gather_object(handles, handle)
+            for r in range(world):
+                if r != rank:
+                    f.peer_exchange_attach(px, r, handles[r])
+        units = []
+        for r in range(world):
+            rb, re_ = sharding.shard_pages(n_pages, world, r)
+            units.append(hkv if sharding.shard_local_len(L, P, rb, re_) else 0)
+
+    def step_push():
+        with torch.cuda.stream(stream):
+            for i in range(layers):
+                if n_local:
+                    f.paged_decode_partial_push(plan, descs[i], q[i], px, step_no[0], n_heads=hq, rope_positions=d_pos,
+                                                scale=scale, k=k[i] if append_here else None,
+                                                v=v[i] if append_here else None, cos=d_cos, sin=d_sin, rope=True,
+                                                rope_mode=w["rope_mode"], append=append_here)
+                f.merge_pushed(px, units, step_no[0], hq, d, out[i])
+                step_no[0] += 1
 
     def step():
+        if px is not None:
+            return step_push()
         with torch.cuda.stream(stream):
             for i in range(layers):
                 if n_local:
@@ -451,14 +481,19 @@ def run_long_context(args, w):
         "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
         "config": {"workload": w["name"], "layers": layers, "kv_len": L, "pages_per_rank": e - b,
                    "l2": "inputs larger than L2 (KV pools %.1f GB per GPU)" % (2 * layers * pool_elems * 2 / 1e9),
-                   "ctas": plan.ctas, "collective": "ncclAllGather of %d bytes per rank per layer" % (block * 4)},
+                   "ctas": plan.ctas, "collective": ("none: decode kernels store %d bytes per layer into every rank's receive block "
+                                  "(peer stores + arrival counters), merge kernel waits on the counters" % (block * 4))
+                   if px is not None else "ncclAllGather of %d bytes per rank per layer" % (block * 4)},
         "hbm_tb_s_per_gpu": achieved / 1e3,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": peak_kind, "kernel": "decode_kernel<128,1,3,2> + all-gather + merge per layer",
+                     "peak_kind": peak_kind, "kernel": "decode_kernel<128,1,3,2> + exchange + merge per layer",
                      "launch_us": launch_us, "algorithmic_bytes_per_launch": bytes_layer_rank, "traffic": None},
         "gpu_launches": launches, "clocks": clocks, "self_check": "ok" if ok else "FAILED",
     }
     plan.close()
+    if px is not None:
+        barrier()  # nobody unmaps while a peer may still store
+        f.peer_exchange_destroy(px)
     f.close()
     if world > 1:
         dist.destroy_process_group()
@@ -620,6 +655,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + sorted(LONG_CONTEXT) + ["c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="push", choices=["push", "nccl"],
+                    help="long-context workloads: partials exchanged by the kernels (peer stores) or by ncclAllGather")
     ap.add_argument("--no-overlap", action="store_true", help="plain launches instead of programmatic dependent launch")
     ap.add_argument("--prefill-impl", type=int, default=0, help="prefill kernel selector (experiments)")
     ap.add_argument("--stages", type=int, default=0, help="decode ring depth (experiments)")

@@ -443,6 +443,44 @@ MF_API mf_status mf_paged_decode_partial(MfContext *ctx, const MfDecodePlan *pla
                                          const uint32_t *rope_positions, float *acc, float *m,
                                          float *l);
 
+/* ---- sequence-sharded decode with the exchange fused into the kernels ---------------
+ * No counterpart in the reference.  Instead of all-gathering (acc, m, l) with a
+ * library collective, the decode kernel of every rank stores each finished unit's
+ * partial directly into every rank's receive block (plain peer stores over NVLink),
+ * then bumps that rank's arrival counter; the merge kernel waits (bounded, 2 s, then
+ * MF_ERR_TIMEOUT at mf_synchronize) until every rank's counter has reached the step's
+ * expected value and merges out of its own memory.
+ *   recv[r]     rank r's receive buffer, 2 * world * rows * (head_dim + 2) floats
+ *               ([step parity][source rank][acc | m | l]), mapped in this process
+ *   counters[r] rank r's arrival counters, world u32, zero before the first step
+ * Steps are numbered from 0 and must be issued in the same order on every rank. */
+typedef struct MfPeerExchange {
+    float *recv[8];
+    uint32_t *counters[8];
+    void *mapping[8]; /* what create / attach mapped; released by destroy */
+    uint32_t world;
+    uint32_t rank;
+} MfPeerExchange;
+
+#define MF_IPC_HANDLE_BYTES 64
+/* Allocates this rank's buffers (zeroed), fills px for `rank`, and writes an inter-process
+ * handle (MF_IPC_HANDLE_BYTES) that the other ranks pass to attach.  handle_out may be NULL
+ * when world is 1.  The caller moves the handles between processes by its own means. */
+MF_API mf_status mf_peer_exchange_create(MfContext *ctx, uint32_t world, uint32_t rank, uint32_t rows,
+                                         uint32_t head_dim, MfPeerExchange *px, uint8_t *handle_out);
+MF_API mf_status mf_peer_exchange_attach(MfContext *ctx, MfPeerExchange *px, uint32_t peer, const uint8_t *handle);
+/* Every rank must have finished its last step (a host barrier) before any rank destroys. */
+MF_API mf_status mf_peer_exchange_destroy(MfContext *ctx, MfPeerExchange *px);
+
+MF_API mf_status mf_paged_decode_partial_push(MfContext *ctx, const MfDecodePlan *plan,
+                                              const MfPagedKv *cache, const MfPagedDecodeArgs *args,
+                                              const uint32_t *rope_positions, const MfPeerExchange *px,
+                                              uint32_t step);
+/* units_per_rank[r]: (batch x kv head) units rank r pushes per step (0 for a rank that
+ * holds no keys); rows = batch * n_heads; out is [rows, head_dim] f16. */
+MF_API mf_status mf_merge_pushed(MfContext *ctx, const MfPeerExchange *px, const uint32_t *units_per_rank,
+                                 uint32_t step, uint32_t rows, uint32_t head_dim, void *out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -99,6 +99,10 @@ class MfPagedDecodeArgs(C.Structure):
                 ("n_heads", u32), ("rope", u32), ("rope_mode", u32), ("append", u32), ("scale", C.c_float)]
 
 
+class MfPeerExchange(C.Structure):
+    _fields_ = [("recv", vp * 8), ("counters", vp * 8), ("mapping", vp * 8), ("world", u32), ("rank", u32)]
+
+
 # Every symbol declared in include/metallic_cuda.h, with its signature.
 _SIGNATURES = {
     "mf_context_create": (C.c_int32, [C.c_int32, vp, C.POINTER(vp)]),
@@ -149,6 +153,12 @@ _SIGNATURES = {
     "mf_paged_kv_append": (C.c_int32, [vp, C.POINTER(MfPagedKv), vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32,
                                        u32]),
     "mf_paged_gather": (C.c_int32, [vp, C.POINTER(MfPagedKv), u32, u32, u32, vp]),
+    "mf_paged_decode_partial_push": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv), C.POINTER(MfPagedDecodeArgs), vp,
+                                                 C.POINTER(MfPeerExchange), u32]),
+    "mf_peer_exchange_create": (C.c_int32, [vp, u32, u32, u32, u32, C.POINTER(MfPeerExchange), vp]),
+    "mf_peer_exchange_attach": (C.c_int32, [vp, C.POINTER(MfPeerExchange), u32, vp]),
+    "mf_peer_exchange_destroy": (C.c_int32, [vp, C.POINTER(MfPeerExchange)]),
+    "mf_merge_pushed": (C.c_int32, [vp, C.POINTER(MfPeerExchange), vp, u32, u32, u32, vp]),
     "mf_paged_decode_partial": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv), C.POINTER(MfPagedDecodeArgs), vp, vp, vp,
                                             vp]),
 }
@@ -324,6 +334,33 @@ class Foundry:
                               rope_mode, int(append), scale)
         self.check(lib.mf_paged_decode_partial(self._h, plan._h, C.byref(cache), C.byref(a), _ptr(rope_positions),
                                                _ptr(acc), _ptr(m), _ptr(l)))
+
+    def paged_decode_partial_push(self, plan, cache, q, px: MfPeerExchange, step: int, *, n_heads, rope_positions=None,
+                                  scale=None, k=None, v=None, cos=None, sin=None, rope=False,
+                                  rope_mode=ROPE_MODE_NEOX, append=False):
+        scale = 1.0 / math.sqrt(cache.head_dim) if scale is None else scale
+        a = MfPagedDecodeArgs(_ptr(q), _ptr(k), _ptr(v), None, None, _ptr(cos), _ptr(sin), n_heads, int(rope),
+                              rope_mode, int(append), scale)
+        self.check(lib.mf_paged_decode_partial_push(self._h, plan._h, C.byref(cache), C.byref(a), _ptr(rope_positions),
+                                                    C.byref(px), step))
+
+    def peer_exchange_create(self, world: int, rank: int, rows: int, head_dim: int):
+        """Returns (MfPeerExchange, handle bytes to hand to the other ranks)."""
+        px = MfPeerExchange()
+        handle = (C.c_uint8 * 64)()
+        self.check(lib.mf_peer_exchange_create(self._h, world, rank, rows, head_dim, C.byref(px), handle))
+        return px, bytes(handle)
+
+    def peer_exchange_attach(self, px: MfPeerExchange, peer: int, handle: bytes):
+        buf = (C.c_uint8 * 64).from_buffer_copy(handle)
+        self.check(lib.mf_peer_exchange_attach(self._h, C.byref(px), peer, buf))
+
+    def peer_exchange_destroy(self, px: MfPeerExchange):
+        self.check(lib.mf_peer_exchange_destroy(self._h, C.byref(px)))
+
+    def merge_pushed(self, px: MfPeerExchange, units_per_rank, step: int, rows: int, head_dim: int, out):
+        arr = (u32 * 8)(*list(units_per_rank) + [0] * (8 - len(units_per_rank)))
+        self.check(lib.mf_merge_pushed(self._h, C.byref(px), arr, step, rows, head_dim, _ptr(out)))
 
     def paged_kv_append(self, cache: MfPagedKv, q, k, v, q_rot, cos, sin, *, n_heads, rope_mode=ROPE_MODE_NEOX,
                         apply_rope=True, seq=ALL_SEQUENCES, position_offset=0, seq_len=0):

@@ -24,6 +24,7 @@ SOURCES = [
     HERE / "csrc" / "prefill.cu",
     HERE / "csrc" / "prefill_tc.cu",
     HERE / "csrc" / "attention_api.cu",
+    HERE / "csrc" / "peer_exchange.cu",
     HERE / "host" / "host_logic.cpp",
 ]
 HEADERS = [HERE / "csrc" / "internal.hpp", HERE / "csrc" / "ptx.cuh", ROOT / "include" / "metallic_cuda.h"]

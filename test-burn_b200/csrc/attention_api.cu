@@ -526,13 +526,13 @@ uint64_t mf_decode_plan_tiles(const MfDecodePlan *pl) { return pl ? pl->total_ti
 
 static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, const MfPagedKv *c,
                                      const MfPagedDecodeArgs *a, const uint32_t *rope_positions, float *acc, float *m,
-                                     float *l)
+                                     float *l, const MfPeerExchange *px = nullptr, uint32_t step = 0)
 {
     if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
     if (!pl || !c || !a) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode: null argument");
     if (!c->k_pool || !c->v_pool || !c->page_table || !c->kv_lens || !a->q)
         return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode: null tensor");
-    if (!acc && !a->out) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode: output");
+    if (!acc && !a->out && !px) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode: output");
     if (a->append && (!a->k || !a->v)) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode: k/v of the new token");
     if (a->rope && (!a->cos || !a->sin)) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode: cos/sin");
     if (a->rope_mode > 1) return fail(ctx, MF_ERR_INVALID_OPERATION, "paged decode: rope_mode %u", a->rope_mode);
@@ -586,6 +586,17 @@ static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, con
     // With overlapped launches the tile stream may start early only when this launch does the
     // append itself: then no kernel right before it can have written the pages it reads.
     p.early_stream = (ctx->overlap_launches && a->append) ? 1u : 0u;
+    if (px) {
+        if (px->world == 0 || px->world > 8 || px->rank >= px->world)
+            return fail(ctx, MF_ERR_INVALID_OPERATION, "peer exchange: rank %u of %u", px->rank, px->world);
+        const uint64_t block = (uint64_t)c->batch * a->n_heads * (D + 2);
+        p.push_world = px->world;
+        for (uint32_t r = 0; r < px->world; ++r) {
+            if (!px->recv[r] || !px->counters[r]) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "peer exchange: rank %u buffers", r);
+            p.push_dst[r] = px->recv[r] + ((uint64_t)(step & 1) * px->world + px->rank) * block;
+            p.push_cnt[r] = px->counters[r] + px->rank;
+        }
+    }
     CUtensorMap tm_k, tm_v;
     const uint64_t rows = (uint64_t)c->n_pages * c->n_kv_heads * P;
     const uint32_t box_rows = std::min(P, kTileKeys);
@@ -604,6 +615,14 @@ static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, con
 mf_status mf_paged_decode(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv *cache, const MfPagedDecodeArgs *args)
 {
     return paged_decode_common(ctx, plan, cache, args, nullptr, nullptr, nullptr, nullptr);
+}
+
+mf_status mf_paged_decode_partial_push(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv *cache,
+                                       const MfPagedDecodeArgs *args, const uint32_t *rope_positions,
+                                       const MfPeerExchange *px, uint32_t step)
+{
+    if (ctx && !px) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "peer exchange");
+    return paged_decode_common(ctx, plan, cache, args, rope_positions, nullptr, nullptr, nullptr, px, step);
 }
 
 mf_status mf_paged_decode_partial(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv *cache,

@@ -537,7 +537,16 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                         p.part_ml[((size_t)it.slot * HP + g) * 2 + 1] = l_all;
                     }
                 } else if (g < G) {
-                    if (partial_out) {
+                    if (p.push_world) {
+                        const size_t rows = (size_t)p.batch * p.n_heads, rowi = (size_t)it.seq * p.n_heads + h;
+                        for (uint32_t r = 0; r < p.push_world; ++r) {
+                            p.push_dst[r][rowi * D + d] = acc;
+                            if (d == 0) {
+                                p.push_dst[r][rows * D + rowi] = m_all * kLn2;
+                                p.push_dst[r][rows * D + rows + rowi] = l_all;
+                            }
+                        }
+                    } else if (partial_out) {
                         p.out_acc[((size_t)it.seq * p.n_heads + h) * D + d] = acc;
                         if (d == 0) {
                             p.out_m[(size_t)it.seq * p.n_heads + h] = m_all * kLn2;
@@ -553,7 +562,15 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             }
             if (hp == 0) named_bar_sync(1, kConsumerThreads);  // pass 1 reuses the buffer
         }
-        if (direct) continue;
+        if (direct) {
+            if (p.push_world) {
+                // every peer sees this unit's block before its counter moves
+                __threadfence_system();
+                named_bar_sync(1, kConsumerThreads);
+                if (tid < p.push_world) atomicAdd_system(p.push_cnt[tid], 1u);
+            }
+            continue;
+        }
 
         // ---- ticket: the CTA that completes the unit merges its partials ---------------
         __threadfence();
@@ -622,7 +639,16 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                 }
             }
             const uint32_t h = it.kvh * G + g2;
-            if (partial_out) {
+            if (p.push_world) {
+                const size_t rows = (size_t)p.batch * p.n_heads, rowi = (size_t)it.seq * p.n_heads + h;
+                for (uint32_t r = 0; r < p.push_world; ++r) {
+                    *reinterpret_cast<float4 *>(p.push_dst[r] + rowi * D + d0) = acc;
+                    if (d0 == 0) {
+                        p.push_dst[r][rows * D + rowi] = mx;
+                        p.push_dst[r][rows * D + rows + rowi] = lt;
+                    }
+                }
+            } else if (partial_out) {
                 *reinterpret_cast<float4 *>(p.out_acc + ((size_t)it.seq * p.n_heads + h) * D + d0) = acc;
                 if (d0 == 0) {
                     p.out_m[(size_t)it.seq * p.n_heads + h] = mx;
@@ -639,6 +665,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                     dst[i] = __float2half_rn(r[i]);
                 }
             }
+        }
+        if (p.push_world) {
+            __threadfence_system();
+            named_bar_sync(1, kConsumerThreads);
+            if (tid < p.push_world) atomicAdd_system(p.push_cnt[tid], 1u);
         }
     }
 }

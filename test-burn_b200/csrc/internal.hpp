@@ -61,6 +61,11 @@ struct DecodeParams {
     uint32_t knew_stride_b;  // elements between sequences in k_new / v_new
     uint32_t whole_rows;     // 1: one TMA box per page fetches both halves (3-D tensor map)
     uint32_t early_stream;   // 1: the producer may stream K/V before the previous kernel has finished
+    // Push mode (sequence-sharded decode): the finished (acc, m, l) of every unit is stored straight
+    // into each rank's receive block over NVLink and announced on that rank's arrival counter.
+    uint32_t push_world;     // 0 = off
+    float *push_dst[8];      // rank r's receive block for THIS rank and step parity, as mapped here
+    uint32_t *push_cnt[8];   // rank r's arrival counter for THIS rank
     float scale_log2;
 };
 

@@ -1,0 +1,161 @@
+// Sequence-sharded decode without a library collective: buffers that every rank's decode
+// kernel stores its partials into (over NVLink, through CUDA IPC mappings), and the merge
+// kernel that waits for them.  No counterpart in the reference, whose engine is one GPU.
+#include <cuda_fp16.h>
+
+#include "internal.hpp"
+
+namespace mf {
+namespace {
+
+constexpr size_t kCounterBytes = 256;  // world <= 8 arrival counters, padded so the floats stay aligned
+
+struct PushedMergeArgs {
+    const float *gather;       // this rank's receive buffer, parity already applied: [world][block]
+    const uint32_t *counters;  // this rank's arrival counters [world]
+    uint32_t expected[8];      // counter value that completes the step, 0 = rank sends nothing
+    uint32_t world, rows, head_dim;
+    uint64_t block;            // floats per source rank
+    uint32_t *status;
+};
+
+// Merge of pushed partials: wait (bounded) for every source rank, then the log-sum-exp merge
+// of flash_prefill.metal:843-888 out of local memory.
+__global__ void __launch_bounds__(128) merge_pushed_kernel(const PushedMergeArgs a, __half *__restrict__ out)
+{
+    __shared__ uint32_t ok;
+    const uint32_t row = blockIdx.x;
+    if (threadIdx.x == 0) {
+        uint32_t good = 1;
+        const long long t0 = clock64();
+        for (uint32_t r = 0; r < a.world && good; ++r) {
+            if (!a.expected[r]) continue;
+            uint32_t spins = 0;
+            for (;;) {
+                uint32_t v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.counters + r) : "memory");
+                if ((int32_t)(v - a.expected[r]) >= 0) break;
+                if ((++spins & 0x3Fu) == 0 && clock64() - t0 > 4000000000ll) {
+                    good = 0;
+                    atomicOr(a.status, 1024u);
+                    break;
+                }
+            }
+        }
+        ok = good;
+    }
+    __syncthreads();
+    if (!ok) return;
+    const uint32_t D = a.head_dim;
+    float mx = -1e30f;
+    for (uint32_t r = 0; r < a.world; ++r)
+        if (a.expected[r]) mx = fmaxf(mx, __ldcv(a.gather + r * a.block + (size_t)a.rows * D + row));
+    float lt = 0.f;
+    for (uint32_t r = 0; r < a.world; ++r) {
+        if (!a.expected[r]) continue;
+        const float ls = __ldcv(a.gather + r * a.block + (size_t)a.rows * D + a.rows + row);
+        if (ls > 0.f) lt += ls * __expf(__ldcv(a.gather + r * a.block + (size_t)a.rows * D + row) - mx);
+    }
+    const float inv = ((fabsf(lt) <= 3.0e38f) && fabsf(lt) > 1e-6f) ? 1.0f / lt : 0.f;
+    for (uint32_t d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.f;
+        for (uint32_t r = 0; r < a.world; ++r) {
+            if (!a.expected[r]) continue;
+            acc += __ldcv(a.gather + r * a.block + (size_t)row * D + d) *
+                   __expf(__ldcv(a.gather + r * a.block + (size_t)a.rows * D + row) - mx);
+        }
+        out[(size_t)row * D + d] = __float2half_rn(acc * inv);
+    }
+}
+
+}  // namespace
+}  // namespace mf
+
+using namespace mf;
+
+extern "C" {
+
+mf_status mf_peer_exchange_create(MfContext *ctx, uint32_t world, uint32_t rank, uint32_t rows, uint32_t head_dim,
+                                  MfPeerExchange *px, uint8_t *handle_out)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!px) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "peer exchange: null");
+    if (world == 0 || world > 8 || rank >= world || rows == 0 || head_dim == 0)
+        return fail(ctx, MF_ERR_INVALID_OPERATION, "peer exchange: rank %u of %u, %u rows x %u", rank, world, rows, head_dim);
+    memset(px, 0, sizeof(*px));
+    const size_t bytes = kCounterBytes + (size_t)2 * world * rows * (head_dim + 2) * sizeof(float);
+    void *base = nullptr;
+    mf_status st = check_cuda(ctx, cudaMalloc(&base, bytes), "peer exchange: cudaMalloc");
+    if (st != MF_OK) return st;
+    st = check_cuda(ctx, cudaMemset(base, 0, bytes), "peer exchange: cudaMemset");
+    if (st == MF_OK && handle_out) {
+        cudaIpcMemHandle_t h;
+        st = check_cuda(ctx, cudaIpcGetMemHandle(&h, base), "cudaIpcGetMemHandle");
+        if (st == MF_OK) memcpy(handle_out, &h, sizeof(h));
+    }
+    if (st != MF_OK) {
+        cudaFree(base);
+        return st;
+    }
+    px->world = world;
+    px->rank = rank;
+    px->mapping[rank] = base;
+    px->counters[rank] = static_cast<uint32_t *>(base);
+    px->recv[rank] = reinterpret_cast<float *>(static_cast<char *>(base) + kCounterBytes);
+    return MF_OK;
+}
+
+mf_status mf_peer_exchange_attach(MfContext *ctx, MfPeerExchange *px, uint32_t peer, const uint8_t *handle)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!px || !handle) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "peer exchange: null");
+    if (peer >= px->world || peer == px->rank || px->mapping[peer])
+        return fail(ctx, MF_ERR_INVALID_OPERATION, "peer exchange: cannot attach rank %u", peer);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void *base = nullptr;
+    // opened in this context's device: the runtime enables peer access to the owner's GPU
+    mf_status st = check_cuda(ctx, cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+    if (st != MF_OK) return st;
+    px->mapping[peer] = base;
+    px->counters[peer] = static_cast<uint32_t *>(base);
+    px->recv[peer] = reinterpret_cast<float *>(static_cast<char *>(base) + kCounterBytes);
+    return MF_OK;
+}
+
+mf_status mf_peer_exchange_destroy(MfContext *ctx, MfPeerExchange *px)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!px) return MF_OK;
+    cudaStreamSynchronize(ctx->stream);
+    for (uint32_t r = 0; r < px->world && r < 8; ++r) {
+        if (!px->mapping[r]) continue;
+        if (r == px->rank) cudaFree(px->mapping[r]);
+        else cudaIpcCloseMemHandle(px->mapping[r]);
+    }
+    memset(px, 0, sizeof(*px));
+    return MF_OK;
+}
+
+mf_status mf_merge_pushed(MfContext *ctx, const MfPeerExchange *px, const uint32_t *units_per_rank, uint32_t step,
+                          uint32_t rows, uint32_t head_dim, void *out)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!px || !units_per_rank || !out) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "merge pushed: null input");
+    if (px->world == 0 || px->world > 8 || px->rank >= px->world)
+        return fail(ctx, MF_ERR_INVALID_OPERATION, "peer exchange: rank %u of %u", px->rank, px->world);
+    if (rows == 0 || head_dim == 0) return MF_OK;
+    PushedMergeArgs a{};
+    a.block = (uint64_t)rows * (head_dim + 2);
+    a.gather = px->recv[px->rank] + (uint64_t)(step & 1) * px->world * a.block;
+    a.counters = px->counters[px->rank];
+    a.world = px->world;
+    a.rows = rows;
+    a.head_dim = head_dim;
+    a.status = ctx->d_status;
+    for (uint32_t r = 0; r < px->world; ++r) a.expected[r] = units_per_rank[r] * (step + 1);
+    merge_pushed_kernel<<<rows, 128, 0, ctx->stream>>>(a, static_cast<__half *>(out));
+    return check_launch(ctx, "merge_pushed_kernel");
+}
+
+}  // extern "C"

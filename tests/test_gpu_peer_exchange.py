@@ -1,0 +1,160 @@
+"""GPU parity: sequence-sharded decode whose exchange is done by the kernels themselves.
+
+The decode kernel of each shard stores its (acc, m, l) into every rank's receive block and bumps an
+arrival counter; the merge kernel waits for the counters and merges.  Cases:
+  * two shards emulated on ONE GPU in one stream (every push precedes every merge in stream order,
+    so no kernel ever waits on a later launch), three steps to cover both buffer parities;
+  * a wait that nothing satisfies runs out and comes back as a Timeout status, context still usable;
+  * two processes on two GPUs with buffers mapped through inter-process handles (skipped on one GPU).
+"""
+import importlib
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import oracle
+from kvcases import PagedCase, dev, dev_u32, host, max_abs
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _shard_inputs(mfk, foundry, full, dk, dv, p0, p1, L):
+    P = full.P
+    pt = np.ascontiguousarray(full.page_table[:, p0:p1])
+    lens = np.array([max(0, min(L, p1 * P) - p0 * P)], np.uint32)
+    d_pt, d_len = dev_u32(pt), dev_u32(lens)
+    desc = mfk.paged_kv(dk, dv, d_pt, d_len, n_kv_heads=full.Hkv, page_size=P, head_dim=full.D)
+    plan = foundry.decode_plan(lens, n_heads=full.Hq, n_kv_heads=full.Hkv, head_dim=full.D, page_size=P)
+    return desc, plan, (d_pt, d_len)
+
+
+def test_pushed_partials_two_shards_one_gpu(mfk, foundry):
+    import torch
+
+    Hq, Hkv, D, P, L = 24, 8, 128, 64, 4096 + 17
+    full = PagedCase(batch=1, n_heads=Hq, n_kv_heads=Hkv, head_dim=D, page_size=P, cached=[L - 1], poison=False)
+    q_ref, kp, vp, out_ref, gold = full.oracle_step()
+    dk, dv, q_rot = dev(kp), dev(vp), dev(q_ref)
+    n_pages = full.page_table.shape[1]
+    cut = n_pages // 3
+    shards = [(0, cut), (cut, n_pages)]
+    pxs = [foundry.peer_exchange_create(2, r, Hq, D)[0] for r in range(2)]
+    for r in range(2):  # same process: the "peer" buffers are plain local pointers
+        o = 1 - r
+        pxs[r].recv[o], pxs[r].counters[o] = pxs[o].recv[o], pxs[o].counters[o]
+    parts = [_shard_inputs(mfk, foundry, full, dk, dv, p0, p1, L) for (p0, p1) in shards]
+    # the library-collective path on the same shards, as the bits to match
+    accs = torch.zeros((2, Hq, D), dtype=torch.float32, device="cuda")
+    ms = torch.full((2, Hq), -1e30, dtype=torch.float32, device="cuda")
+    ls = torch.zeros((2, Hq), dtype=torch.float32, device="cuda")
+    for r, (desc, plan, _) in enumerate(parts):
+        foundry.paged_decode_partial(plan, desc, q_rot, accs[r:r + 1], ms[r:r + 1], ls[r:r + 1], n_heads=Hq,
+                                     scale=float(full.scale))
+    want = torch.empty((Hq, D), dtype=torch.float16, device="cuda")
+    foundry.merge_partials(accs, ms, ls, want)
+    foundry.synchronize()
+    for step in range(3):
+        outs = [torch.full((Hq, D), float("nan"), dtype=torch.float16, device="cuda") for _ in range(2)]
+        for r, (desc, plan, _) in enumerate(parts):
+            foundry.paged_decode_partial_push(plan, desc, q_rot, pxs[r], step, n_heads=Hq, scale=float(full.scale))
+        for r in range(2):
+            foundry.merge_pushed(pxs[r], [Hkv, Hkv], step, Hq, D, outs[r])
+        foundry.synchronize()
+        for o in outs:
+            assert np.array_equal(host(o), host(want))
+            assert max_abs(host(o), out_ref) <= TOL and max_abs(host(o), gold.ravel()) <= TOL
+    for (_, plan, _) in parts:
+        plan.close()
+    for r in range(2):  # borrowed pointers are not this exchange's to release
+        o = 1 - r
+        pxs[r].recv[o] = pxs[r].counters[o] = None
+        foundry.peer_exchange_destroy(pxs[r])
+
+
+def test_merge_wait_runs_out_with_a_status(mfk, foundry):
+    """Rank 1 never pushes: the merge kernel gives up after its limit, the status surfaces at
+    synchronize as Timeout, and the context keeps working."""
+    import torch
+
+    Hq, D = 8, 128
+    px, _ = foundry.peer_exchange_create(2, 0, Hq, D)
+    silent, _ = foundry.peer_exchange_create(2, 1, Hq, D)
+    px.recv[1], px.counters[1] = silent.recv[1], silent.counters[1]
+    out = torch.zeros((Hq, D), dtype=torch.float16, device="cuda")
+    foundry.merge_pushed(px, [0, 1], 0, Hq, D, out)
+    with pytest.raises(mfk.MetalError) as e:
+        foundry.synchronize()
+    assert e.value.kind == "Timeout"
+    assert not host(out).any()  # nothing was written
+    foundry.merge_pushed(px, [0, 0], 0, Hq, D, out)  # nobody expected: merges nothing, at once
+    foundry.synchronize()
+    px.recv[1] = px.counters[1] = None
+    foundry.peer_exchange_destroy(px)
+    foundry.peer_exchange_destroy(silent)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _two_gpu_worker(rank, world, port, ret):
+    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(ROOT / "tests"))
+    import torch
+    import torch.distributed as dist
+
+    mfk = importlib.import_module("test-burn_b200")
+    sharding = importlib.import_module("test-burn_b200.sharding")
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)  # host plumbing only
+    torch.cuda.set_device(rank)
+    try:
+        Hq, Hkv, D, P, L = 24, 8, 128, 64, 6000
+        full = PagedCase(batch=1, n_heads=Hq, n_kv_heads=Hkv, head_dim=D, page_size=P, cached=[L - 1], poison=False)
+        q_ref, kp, vp, out_ref, gold = full.oracle_step()
+        f = mfk.Foundry(rank)
+        dk, dv, q_rot = dev(kp), dev(vp), dev(q_ref)
+        n_pages = full.page_table.shape[1]
+        b, e = sharding.shard_pages(n_pages, world, rank)
+        desc, plan, keep = _shard_inputs(mfk, f, full, dk, dv, b, e, L)
+        px, handle = f.peer_exchange_create(world, rank, Hq, D)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle)
+        for r in range(world):
+            if r != rank:
+                f.peer_exchange_attach(px, r, handles[r])
+        ok = True
+        for step in range(4):
+            out = torch.full((Hq, D), float("nan"), dtype=torch.float16, device="cuda")
+            f.paged_decode_partial_push(plan, desc, q_rot, px, step, n_heads=Hq, scale=float(full.scale))
+            f.merge_pushed(px, [Hkv] * world, step, Hq, D, out)
+            f.synchronize()
+            ok = ok and max_abs(host(out), out_ref) <= TOL and max_abs(host(out), gold.ravel()) <= TOL
+        plan.close()
+        dist.barrier()  # nobody unmaps while a peer may still store
+        f.peer_exchange_destroy(px)
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_pushed_partials_two_gpus():
+    import torch
+    import torch.multiprocessing as mp
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world, port = 2, _free_port()
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_two_gpu_worker, args=(world, port, ret), nprocs=world, join=True)
+        assert dict(ret) == {0: True, 1: True}
