@@ -382,6 +382,8 @@ def run_long_context(args, w):
     out = torch.zeros((layers, hq, d), dtype=torch.float16, device=dev)
     stream = torch.cuda.Stream(device=dev)
     f = mfk.Foundry(dev.index, stream.cuda_stream)
+    if not args.no_overlap:
+        f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 1)
     plan = f.decode_plan(lens_host, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P)
     descs = [mfk.paged_kv(k_pools[i].view(e - b, hkv, P, d), v_pools[i].view(e - b, hkv, P, d), table, d_lens,
                           n_kv_heads=hkv, page_size=P, head_dim=d) for i in range(layers)]

@@ -4,6 +4,7 @@
 #include <cuda_fp16.h>
 
 #include "internal.hpp"
+#include "ptx.cuh"
 
 namespace mf {
 namespace {
@@ -25,6 +26,10 @@ __global__ void __launch_bounds__(128) merge_pushed_kernel(const PushedMergeArgs
 {
     __shared__ uint32_t ok;
     const uint32_t row = blockIdx.x;
+    // Launched as a programmatic dependent of this rank's decode kernel, so it may be resident
+    // while that kernel still runs (all of whose CTAs are resident by then, so it cannot be starved).
+    // The arrival counters are the real dependency; the next kernel in the stream may be set up too.
+    grid_launch_dependents();
     if (threadIdx.x == 0) {
         uint32_t good = 1;
         const long long t0 = clock64();
@@ -35,6 +40,7 @@ __global__ void __launch_bounds__(128) merge_pushed_kernel(const PushedMergeArgs
                 uint32_t v;
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.counters + r) : "memory");
                 if ((int32_t)(v - a.expected[r]) >= 0) break;
+                __nanosleep(100);
                 if ((++spins & 0x3Fu) == 0 && clock64() - t0 > 4000000000ll) {
                     good = 0;
                     atomicOr(a.status, 1024u);
@@ -45,6 +51,8 @@ __global__ void __launch_bounds__(128) merge_pushed_kernel(const PushedMergeArgs
         ok = good;
     }
     __syncthreads();
+    // everything earlier in this stream has finished and is visible before out is written
+    grid_dependency_wait();
     if (!ok) return;
     const uint32_t D = a.head_dim;
     float mx = -1e30f;
@@ -154,6 +162,21 @@ mf_status mf_merge_pushed(MfContext *ctx, const MfPeerExchange *px, const uint32
     a.head_dim = head_dim;
     a.status = ctx->d_status;
     for (uint32_t r = 0; r < px->world; ++r) a.expected[r] = units_per_rank[r] * (step + 1);
+    if (ctx->overlap_launches) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(rows);
+        cfg.blockDim = dim3(128);
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, merge_pushed_kernel, a, static_cast<__half *>(out));
+        if (e != cudaSuccess) return fail(ctx, MF_ERR_CUDA, "launch merge_pushed_kernel: %s", cudaGetErrorString(e));
+        ++ctx->launches;
+        return MF_OK;
+    }
     merge_pushed_kernel<<<rows, 128, 0, ctx->stream>>>(a, static_cast<__half *>(out));
     return check_launch(ctx, "merge_pushed_kernel");
 }

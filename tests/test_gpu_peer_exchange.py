@@ -34,7 +34,8 @@ def _shard_inputs(mfk, foundry, full, dk, dv, p0, p1, L):
     return desc, plan, (d_pt, d_len)
 
 
-def test_pushed_partials_two_shards_one_gpu(mfk, foundry):
+@pytest.mark.parametrize("overlap", [0, 1])
+def test_pushed_partials_two_shards_one_gpu(mfk, foundry, overlap):
     import torch
 
     Hq, Hkv, D, P, L = 24, 8, 128, 64, 4096 + 17
@@ -59,6 +60,7 @@ def test_pushed_partials_two_shards_one_gpu(mfk, foundry):
     want = torch.empty((Hq, D), dtype=torch.float16, device="cuda")
     foundry.merge_partials(accs, ms, ls, want)
     foundry.synchronize()
+    foundry.set_option(mfk.OPTION_OVERLAP_LAUNCHES, overlap)  # programmatic dependent launches
     for step in range(3):
         outs = [torch.full((Hq, D), float("nan"), dtype=torch.float16, device="cuda") for _ in range(2)]
         for r, (desc, plan, _) in enumerate(parts):
@@ -69,6 +71,7 @@ def test_pushed_partials_two_shards_one_gpu(mfk, foundry):
         for o in outs:
             assert np.array_equal(host(o), host(want))
             assert max_abs(host(o), out_ref) <= TOL and max_abs(host(o), gold.ravel()) <= TOL
+    foundry.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 0)
     for (_, plan, _) in parts:
         plan.close()
     for r in range(2):  # borrowed pointers are not this exchange's to release
@@ -133,7 +136,8 @@ def _two_gpu_worker(rank, world, port, ret):
             if r != rank:
                 f.peer_exchange_attach(px, r, handles[r])
         ok = True
-        for step in range(4):
+        for step in range(6):
+            f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, step // 3)
             out = torch.full((Hq, D), float("nan"), dtype=torch.float16, device="cuda")
             f.paged_decode_partial_push(plan, desc, q_rot, px, step, n_heads=Hq, scale=float(full.scale))
             f.merge_pushed(px, [Hkv] * world, step, Hq, D, out)
