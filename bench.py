@@ -333,9 +333,6 @@ def run_ours(args, w):
     ok = bool(torch.isfinite(d_out[-1].float()).all()) and bool(torch.equal(h_out[-1].to(dev), d_out[-1]))
     result["self_check"] = "ok" if ok else "FAILED"
     plan.close()
-    if px is not None:
-        barrier()  # nobody unmaps while a peer may still store
-        f.peer_exchange_destroy(px)
     f.close()
     if world > 1:
         dist.destroy_process_group()
