@@ -293,6 +293,15 @@ def run_ours(args, w):
     ms_e2e, _, t1 = timed(e2e_step, args.steps)
     f.synchronize()
     clocks = sampler.stop(t0, t1)
+    # spread of single steps (an event after every step; kept out of the headline region)
+    n_stat = min(args.steps, 100)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(n_stat + 1)]
+    marks[0].record(stream)
+    for i in range(n_stat):
+        device_step()
+        marks[i + 1].record(stream)
+    f.synchronize()
+    per_step = np.array([marks[i].elapsed_time(marks[i + 1]) for i in range(n_stat)])
 
     ms_step = ms / args.steps
     tokens_per_s = B * world / (ms_step * 1e-3)
@@ -325,6 +334,8 @@ def run_ours(args, w):
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
         "gpu_launches": int(launches),
         "clocks": clocks,
+        "step_spread_ms": {"n": n_stat, "min": float(per_step.min()), "median": float(np.median(per_step)),
+                           "mean": float(per_step.mean()), "sd": float(per_step.std())},
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         result["cpu_baseline"] = cpu_baseline(w, steps=1)
@@ -579,6 +590,79 @@ def run_prefill(args):
     return 0 if ok else 1
 
 
+def run_single_token_latency(args):
+    """Configuration 1: Qwen2.5-0.5B shape, one layer, batch 1, 511 cached + 1, contiguous cache
+    [2, 512, 64]: KvPrepFused then FlashAttention (decode route), the reference's own two ops.  The
+    whole working set (0.27 MB) sits in L2, so this is a latency figure, not a bandwidth one."""
+    import torch
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    mfk = importlib.import_module("test-burn_b200")
+    hq, hkv, d, cached, cap = 14, 2, 64, 511, 512
+    g = torch.Generator(device=dev).manual_seed(SEED)
+    q = torch.empty((1, hq * d), dtype=torch.float16, device=dev).normal_(generator=g)
+    k = torch.empty((1, hkv * d), dtype=torch.float16, device=dev).normal_(generator=g)
+    v = torch.empty((1, hkv * d), dtype=torch.float16, device=dev).normal_(generator=g)
+    kc = torch.empty((hkv, cap, d), dtype=torch.float16, device=dev).normal_(generator=g)
+    vc = torch.empty((hkv, cap, d), dtype=torch.float16, device=dev).normal_(generator=g)
+    cos_np, sin_np = mfk.rope_tables(1e6, d, cap)
+    cos = torch.from_numpy(cos_np.view(np.float16)).to(dev)
+    sin = torch.from_numpy(sin_np.view(np.float16)).to(dev)
+    q_rot = torch.empty((1, hq * d), dtype=torch.float16, device=dev)
+    out = torch.empty((1, hq * d), dtype=torch.float16, device=dev)
+    stream = torch.cuda.Stream(device=dev)
+    f = mfk.Foundry(0, stream.cuda_stream)
+    p = mfk.KvPrepFusedParamsResolved(hq * d, hkv * d, d, hq, hkv, hq // hkv, 1, cached, cap, hq * d, 0, 0, 0)
+
+    def step():
+        f.kv_prep_fused(q, k, v, q_rot, kc, vc, cos, sin, p)
+        f.flash_attention(q_rot, kc, vc, out, causal=True, query_offset=cached, n_heads=hq, head_dim=d,
+                          kv_seq_len=cached + 1, m=1)
+
+    for _ in range(max(args.warmup, 25)):
+        step()
+    f.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    time.sleep(0.3)
+    trials, iters = 10, max(args.steps, 100)
+    per_iter_us = []
+    launches0 = f.launch_count
+    t0 = time.time()
+    for _ in range(trials):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(iters):
+            step()
+        b.record(stream)
+        f.synchronize()
+        per_iter_us.append(a.elapsed_time(b) * 1e3 / iters)
+    t1 = time.time()
+    launches = f.launch_count - launches0
+    clocks = sampler.stop(t0, t1)
+    us = np.array(per_iter_us)
+    med = float(np.median(us))
+    bytes_step = 2 * hkv * (cached + 1) * d * 2 + 4 * hkv * d * 2 + 2 * hq * d * 2 + 2 * (d // 2) * 2
+    peak, peak_kind = measured_peak_gbs()
+    achieved = bytes_step / (med * 1e-6) / 1e9
+    ok = bool(torch.isfinite(out.float()).all())
+    print(json.dumps({
+        "metric": METRIC, "value": 1e6 / med, "unit": "tokens/s", "n_gpus": 1, "steps": iters * trials,
+        "warmup": max(args.warmup, 25), "ms_per_step": med * 1e-3, "us_per_step": med, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
+        "config": {"workload": "single-token latency, Qwen2.5-0.5B shape: 1 layer, 14q/2kv heads, D64, batch 1, "
+                               "511 cached + 1, contiguous cache, KvPrepFused then FlashAttention (2 launches)",
+                   "l2": "L2-resident by construction (0.27 MB): latency only, not a bandwidth figure"},
+        "latency_us": {"trials": trials, "iterations": iters, "min": float(us.min()), "median": med,
+                       "mean": float(us.mean()), "sd": float(us.std())},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": peak_kind, "traffic": None, "note": "launch-bound; see latency_us"},
+        "gpu_launches": launches, "clocks": clocks, "self_check": "ok" if ok else "FAILED"}))
+    f.close()
+    return 0 if ok else 1
+
+
 # ---------------------------------------------------------------------- CPU arms ---
 
 def cpu_layer_inputs(w, seed):
@@ -652,7 +736,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + sorted(LONG_CONTEXT) + ["c4"])
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + sorted(LONG_CONTEXT) + ["c1", "c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", default="push", choices=["push", "nccl"],
                     help="long-context workloads: partials exchanged by the kernels (peer stores) or by ncclAllGather")
@@ -664,6 +748,8 @@ def main():
     args = ap.parse_args()
     if args.workload == "c4":
         return run_prefill(args)
+    if args.workload == "c1":
+        return run_single_token_latency(args)
     if args.workload in LONG_CONTEXT:
         return run_long_context(args, LONG_CONTEXT[args.workload])
     w = dict(WORKLOADS[args.workload])

@@ -10,10 +10,11 @@
 // independent online-softmax streams (even tiles -> stream 0, odd tiles -> stream 1), each with
 // its own running (m, l, O); the streams are merged with the log-sum-exp rule at the end.  While
 // one stream's warps exponentiate, the tensor pipe works on the other stream's products.
-//   warps 0-7   stream 0 softmax, warps 8-15 stream 1 softmax; two threads per query row
-//               (= TMEM lane): warp w works on lane quadrant w % 4 and column half (w / 4) % 2
-//   warp 16     TMA producer: Q tile once, then rings of 128-key K (3 deep) and V (2 deep) tiles
-//   warp 17     TMEM allocation and the single thread that issues tcgen05.mma
+//   warps 0-3   stream 0 softmax, warps 4-7 stream 1 softmax; one thread per query row
+//               (= TMEM lane) holds the row's 128 scores in registers: warp w works on lane
+//               quadrant w % 4
+//   warp 8      TMA producer: Q tile once, then rings of 128-key K and V tiles (3 deep each)
+//   warp 9      TMEM allocation and the single thread that issues tcgen05.mma
 // Per tile of stream x:  S_x = Q K^T (A, B from 128-byte-swizzled shared memory, accumulator in
 // TMEM) -> the stream's warps read S_x with tcgen05.ld, write P (f16) over the first 64 columns
 // of S_x with tcgen05.st -> O_x += P V (A from TMEM, B = V tile as an MN-major operand), O_x
@@ -30,18 +31,29 @@
 namespace mf {
 namespace {
 
+#ifndef MF_TC_VSTAGES
+#define MF_TC_VSTAGES 3
+#endif
+#ifndef MF_TC_ISSUERS
+#define MF_TC_ISSUERS 1
+#endif
+constexpr uint32_t kIssuers = MF_TC_ISSUERS;  // threads issuing tcgen05.mma: one for both streams, or one each
 constexpr uint32_t kBM = 128;             // query rows per CTA
 constexpr uint32_t kBN = 128;             // keys per tile
 constexpr uint32_t kD = 128;              // head_dim
-constexpr uint32_t kStreamWarps = 8;                      // softmax warps per stream
+constexpr uint32_t kStreamWarps = 4;                      // softmax warps per stream (one thread per row)
 constexpr uint32_t kSoftmaxWarps = 2 * kStreamWarps;
 constexpr uint32_t kSoftmaxThreads = 32 * kSoftmaxWarps;
-constexpr uint32_t kTcThreads = kSoftmaxThreads + 64;
+constexpr uint32_t kTcThreads = kSoftmaxThreads + 32 + 32 * kIssuers;
 constexpr float kRescaleThreshold = 8.0f;                 // log2 of the largest weight kept in P
+#ifndef MF_TC_POLY_MASK
+#define MF_TC_POLY_MASK 0x00u
+#endif
+constexpr uint32_t kPolyMask = MF_TC_POLY_MASK;           // which of every 8 column pairs use the FMA-pipe exp2
 constexpr uint32_t kHalfTile = 128 * 128; // bytes: 128 rows x 64 f16
 constexpr uint32_t kTile = 2 * kHalfTile; // 32 KB
 constexpr uint32_t kKStages = 3;           // K tiles in flight
-constexpr uint32_t kVStages = 2;           // V tiles in flight
+constexpr uint32_t kVStages = MF_TC_VSTAGES;  // V tiles in flight
 constexpr uint64_t kTcWaitNs = 2000000000ull;
 constexpr float kNegInf = -1e30f;
 
@@ -65,6 +77,13 @@ __device__ unsigned long long g_tc_prof[1024 * 32];
 #define TC_PROF_DECL
 #define TC_PROF_WAIT(idx, stmt) stmt;
 #define TC_PROF_STORE(role)
+#endif
+#ifdef MF_TC_PROFILE
+#define TC_PROF_MARK(var) const long long var = clock64();
+#define TC_PROF_SPAN(idx, a, b) prof_acc[idx] += (unsigned long long)((b) - (a));
+#else
+#define TC_PROF_MARK(var)
+#define TC_PROF_SPAN(idx, a, b)
 #endif
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------
@@ -158,6 +177,46 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         : "memory");
 }
 
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
+        "%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c)
+{
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// 2^t for two values without the special-function unit, for t <= ~8: round t to the nearest integer n
+// with the 1.5 * 2^23 trick, a cubic for 2^f on f = t - n in [-0.5, 0.5] (relative error 7.5e-5, under
+// half an f16 ulp, which is what the weights are rounded to), then n is added to the exponent field.
+// The special-function unit delivers 16 exponentials per clock and SM, as many clocks per tile as the
+// two matrix products take; moving part of the row to the FMA pipe takes it off the critical path.
+__device__ __forceinline__ float2 exp2_poly2(float2 t)
+{
+    t.x = fmaxf(t.x, -125.f);
+    t.y = fmaxf(t.y, -125.f);
+    const float2 tt = __fadd2_rn(t, make_float2(12582912.f, 12582912.f));
+    const float2 n = __fadd2_rn(tt, make_float2(-12582912.f, -12582912.f));
+    const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), t);
+    float2 y = __ffma2_rn(f, make_float2(0.0551716685f, 0.0551716685f), make_float2(0.2426111251f, 0.2426111251f));
+    y = __ffma2_rn(y, f, make_float2(0.6932609677f, 0.6932609677f));
+    y = __ffma2_rn(y, f, make_float2(0.9999280572f, 0.9999280572f));
+    y.x = __uint_as_float(__float_as_uint(y.x) + (__float_as_uint(tt.x) << 23));
+    y.y = __uint_as_float(__float_as_uint(y.y) + (__float_as_uint(tt.y) << 23));
+    return y;
+}
+
 // 3-D tiled load without a cache hint.
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *tmap, int32_t x, int32_t y, int32_t z, uint32_t bar)
 {
@@ -182,8 +241,9 @@ enum Bar : uint32_t {
 static_assert(kKStages <= 4 && kVStages <= 4, "barrier slots");
 
 constexpr uint32_t kSmemTiles = kTile * (1 + kKStages + kVStages);  // Q + K ring + V ring
-constexpr uint32_t kMaxBufBytes = 2 * 2 * 2 * 128 * 4;        // [stream][tile parity][column half][row] f32
+constexpr uint32_t kMaxBufBytes = 0;  // (l, m) of both streams travel through the Q tile, free by then
 constexpr uint32_t kSmemBytes = kSmemTiles + kMaxBufBytes + kNumBars * 8 + 16 + 1024;
+static_assert(kSmemBytes <= 227 * 1024, "shared memory");
 
 __global__ void __launch_bounds__(kTcThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -195,7 +255,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t q_smem = smem_base;
     const uint32_t k_smem = smem_base + kTile;
     const uint32_t v_smem = k_smem + kKStages * kTile;
-    float *max_buf = reinterpret_cast<float *>(smem + kSmemTiles);
+    float *max_buf = reinterpret_cast<float *>(smem);  // epilogue only: the Q tile is no longer read
     const uint32_t bars = smem_base + kSmemTiles + kMaxBufBytes;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + kSmemTiles + kMaxBufBytes + kNumBars * 8);
     volatile uint32_t *abort_flag = tmem_slot + 1;
@@ -277,26 +337,35 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
             TC_PROF_STORE(2)
         }
-    } else if (warp == kSoftmaxWarps + 1) {
-        // ------------------------------------------------------------------ MMA issuer ---
-        if (lane == 0) {
+    } else if (warp >= kSoftmaxWarps + 1) {
+        // ------------------------------------------------------------------ MMA issuer(s) ---
+        const uint32_t me = warp - (kSoftmaxWarps + 1);
+        if (lane == 0 && me < n_tiles) {
             constexpr uint32_t kIdescQK = instr_desc(kBN, 0);
             constexpr uint32_t kIdescPV = instr_desc(kD, 1);
             TC_PROF_DECL
             wait(bar(kQFull), 0, 32u);
+            // The descriptors of one operand differ only in the 14-bit start-address field: build each
+            // once and add the 16-byte-unit offsets, so that an MMA costs this thread a few instructions.
+            const uint64_t q_desc = smem_desc(q_smem, 16, 1024);
             auto issue_qk = [&](uint32_t i) {
                 const uint32_t x = i & 1;
                 const uint32_t ks = i % kKStages, kph = (i / kKStages) & 1;
                 TC_PROF_WAIT(0, wait(bar(kKFull + ks), kph, 32u))
                 tc_fence_after();
+                TC_PROF_MARK(ma)
+                const uint64_t k_desc = smem_desc(k_smem + ks * kTile, 16, 1024);
 #pragma unroll
                 for (uint32_t kk = 0; kk < kD / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * kHalfTile + (kk & 3) * 32;
-                    tc_mma_ss(tmem + x * 128, smem_desc(q_smem + off, 16, 1024),
-                              smem_desc(k_smem + ks * kTile + off, 16, 1024), kIdescQK, kk > 0);
+                    const uint32_t off = ((kk >> 2) * kHalfTile + (kk & 3) * 32) >> 4;
+                    tc_mma_ss(tmem + x * 128, q_desc + off, k_desc + off, kIdescQK, kk > 0);
                 }
+                TC_PROF_MARK(mb)
                 tc_commit(bar(kSFull + x));
                 tc_commit(bar(kKEmpty + ks));
+                TC_PROF_MARK(mc)
+                TC_PROF_SPAN(4, ma, mb)
+                TC_PROF_SPAN(6, mb, mc)
             };
             auto issue_pv = [&](uint32_t i) {
                 const uint32_t x = i & 1, j = i >> 1;
@@ -304,79 +373,88 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 TC_PROF_WAIT(2, wait(bar(kVFull + vs), vph, 64u))
                 TC_PROF_WAIT(3, wait(bar(kPFull + x), j & 1, 64u))
                 tc_fence_after();
+                TC_PROF_MARK(ma)
+                const uint64_t v_desc = smem_desc(v_smem + vs * kTile, kHalfTile, 1024);
 #pragma unroll
                 for (uint32_t kk = 0; kk < kBN / 16; ++kk) {
                     // A: 16 keys = 8 packed 32-bit TMEM columns per step; B: V rows kk*16.., MN-major.
-                    tc_mma_ts(tmem + 256 + x * 128, tmem + x * 128 + kk * 8,
-                              smem_desc(v_smem + vs * kTile + kk * 2048, kHalfTile, 1024), kIdescPV,
+                    tc_mma_ts(tmem + 256 + x * 128, tmem + x * 128 + kk * 8, v_desc + kk * (2048 >> 4), kIdescPV,
                               (j > 0 || kk > 0) ? 1u : 0u);
                 }
+                TC_PROF_MARK(mb)
                 tc_commit(bar(kOFull + x));
                 tc_commit(bar(kVEmpty + vs));
+                TC_PROF_MARK(mc)
+                TC_PROF_SPAN(5, ma, mb)
+                TC_PROF_SPAN(7, mb, mc)
             };
-            // Q K^T of a stream's next tile is issued right behind its P V: the tensor pipe runs
-            // them in order, so S_x is overwritten only after P (which lives in S_x) was consumed.
-            for (uint32_t i = 0; i < min(n_tiles, 2u); ++i) issue_qk(i);
-            for (uint32_t i = 0; i < n_tiles; ++i) {
-                issue_pv(i);
-                if (i + 2 < n_tiles) issue_qk(i + 2);
+            // Q K^T of a stream's next tile is issued right behind its P V by the same thread, whose
+            // MMAs run in order, so S_x is overwritten only after P (which lives in S_x) was consumed.
+            if (kIssuers == 1) {
+                for (uint32_t i = 0; i < min(n_tiles, 2u); ++i) issue_qk(i);
+                for (uint32_t i = 0; i < n_tiles; ++i) {
+                    issue_pv(i);
+                    if (i + 2 < n_tiles) issue_qk(i + 2);
+                }
+            } else {
+                issue_qk(me);
+                for (uint32_t i = me; i < n_tiles; i += 2) {
+                    issue_pv(i);
+                    if (i + 2 < n_tiles) issue_qk(i + 2);
+                }
             }
-            TC_PROF_STORE(1)
+            if (me == 0) { TC_PROF_STORE(1) }
         }
     } else {
         // ------------------------------------------------- softmax / epilogue, two streams ---
-        const uint32_t x = warp >> 3;                           // stream
-        const uint32_t quad = warp & 3, half = (warp >> 2) & 1;
+        // One thread per query row (= TMEM lane) and stream: the whole row of S is in registers,
+        // so the maximum and the sum need no exchange between threads.
+        const uint32_t x = warp >> 2;                           // stream
+        const uint32_t quad = warp & 3;
         const uint32_t r_in = quad * 32 + lane;                 // row inside the tile = TMEM lane
         const uint32_t row = row0 + r_in;
         const uint32_t lane_base = (quad * 32u) << 16;          // TMEM lane quadrant of this warp
         const uint32_t limit = row + p.query_offset;            // last visible key
-        const uint32_t col0 = half * 64;                        // this thread's 64 S / O columns
         const uint32_t s_tm = tmem + lane_base + x * 128;       // S_x / P_x
-        const uint32_t o_tm = tmem + lane_base + 256 + x * 128 + col0;
-        const uint32_t pair_bar = 1 + x * 4 + quad;             // named barrier of the two warps of a row group
-        float *xbuf = max_buf + x * 512;                        // [tile parity][half][row]
+        const uint32_t o_tm = tmem + lane_base + 256 + x * 128;
         const uint32_t n_mine = n_tiles > x ? (n_tiles - x + 1) / 2 : 0;
+        const uint32_t last_ok = min(limit, p.kv_len - 1);
         float m_ref = kNegInf, l_run = 0.f;                     // m in the scaled log2 domain
         TC_PROF_DECL
 
         for (uint32_t j = 0; j < n_mine; ++j) {
-            const uint32_t i = 2 * j + x;
-            const uint32_t key0 = i * kBN + col0;  // first key of this thread's columns
-            // Only tiles on the causal diagonal or at the end of the cache need a mask; the
-            // number of this thread's 64 columns that stay visible covers both conditions.
-            const uint32_t last_ok = min(limit, p.kv_len - 1);
-            const uint32_t n_vis = last_ok < key0 ? 0u : min(64u, last_ok - key0 + 1);
+            const uint32_t key0 = (2 * j + x) * kBN;
+            // Only tiles on the causal diagonal or at the end of the cache need a mask.
+            const uint32_t n_vis = last_ok < key0 ? 0u : min(kBN, last_ok - key0 + 1);
             TC_PROF_WAIT(0, wait(bar(kSFull + x), j & 1, 256u))
             tc_fence_after();
-            // pass 1: row maximum of the raw scores (the scale is positive), 32 columns at a time
-            float mx = -3.0e38f;
+            // The TMEM accesses below are warp-collective: the choice between the plain and the
+            // masked form of the row must be the same for all 32 rows of the warp.
+            const bool whole = __all_sync(0xffffffffu, n_vis == kBN);
+            TC_PROF_MARK(pt0)
+            uint32_t r[128];
 #pragma unroll
-            for (uint32_t c = 0; c < 2; ++c) {
-                uint32_t r[32];
-                tmem_ld32(s_tm + col0 + c * 32, r);
-                tc_wait_ld();
-                float mx0 = -3.0e38f, mx1 = -3.0e38f, mx2 = -3.0e38f, mx3 = -3.0e38f;
-                if (n_vis >= (c + 1) * 32) {
+            for (uint32_t c = 0; c < 4; ++c) tmem_ld32(s_tm + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+            tc_wait_ld();
+            TC_PROF_MARK(pt1)
+            // row maximum of the raw scores (the scale is positive)
+            float mx0 = -3.0e38f, mx1 = -3.0e38f, mx2 = -3.0e38f, mx3 = -3.0e38f;
+            if (whole) {
 #pragma unroll
-                    for (uint32_t q = 0; q < 32; q += 4) {
-                        mx0 = fmaxf(mx0, __uint_as_float(r[q]));
-                        mx1 = fmaxf(mx1, __uint_as_float(r[q + 1]));
-                        mx2 = fmaxf(mx2, __uint_as_float(r[q + 2]));
-                        mx3 = fmaxf(mx3, __uint_as_float(r[q + 3]));
-                    }
-                } else {
-#pragma unroll
-                    for (uint32_t q = 0; q < 32; ++q)
-                        if (c * 32 + q < n_vis) mx0 = fmaxf(mx0, __uint_as_float(r[q]));
+                for (uint32_t q = 0; q < 128; q += 8) {
+                    mx0 = max3(mx0, __uint_as_float(r[q]), __uint_as_float(r[q + 1]));
+                    mx1 = max3(mx1, __uint_as_float(r[q + 2]), __uint_as_float(r[q + 3]));
+                    mx2 = max3(mx2, __uint_as_float(r[q + 4]), __uint_as_float(r[q + 5]));
+                    mx3 = max3(mx3, __uint_as_float(r[q + 6]), __uint_as_float(r[q + 7]));
                 }
-                mx = fmaxf(mx, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+            } else {
+#pragma unroll
+                for (uint32_t q = 0; q < 128; ++q) {
+                    if (q >= n_vis) r[q] = 0xFF800000u;  // -inf: weight exactly 0 below
+                    mx0 = fmaxf(mx0, __uint_as_float(r[q]));
+                }
             }
-            // the other half of this row lives in the partner warp: swap maxima through smem
-            float *mb = xbuf + (j & 1) * 256;
-            mb[half * 128 + r_in] = mx;
-            TC_PROF_WAIT(3, named_bar_sync(pair_bar, 64))
-            mx = fmaxf(mx, mb[(half ^ 1) * 128 + r_in]);
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
             const float m_new = mx > -3.0e38f ? mx * p.scale_log2 : kNegInf;
             // Lazy rescale: keep exponentiating against m_ref until a row outgrows it by 2^8.
             const bool grow = m_new > m_ref + kRescaleThreshold;
@@ -386,107 +464,134 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 m_ref = m_next;
                 l_run *= alpha;
                 if (j > 0) {
-                    // O_x must hold every earlier P V before it is scaled.
+                    // O_x must hold every earlier P V before it is scaled.  S(j) being there implies that
+                    // P V (j - 2), issued before it, is done, so one parity bit is unambiguous here.
                     TC_PROF_WAIT(2, wait(bar(kOFull + x), (j - 1) & 1, 128u))
                     tc_fence_after();
-                    uint32_t ob[32];
-#pragma unroll
-                    for (uint32_t c = 0; c < 2; ++c) {
+#pragma unroll 1
+                    for (uint32_t c = 0; c < 4; ++c) {
+                        uint32_t ob[32];
                         tmem_ld32(o_tm + c * 32, ob);
                         tc_wait_ld();
 #pragma unroll
                         for (uint32_t q = 0; q < 32; ++q) ob[q] = __float_as_uint(__uint_as_float(ob[q]) * alpha);
-                        asm volatile(
-                            "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-                            "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
-                            "%25,%26,%27,%28,%29,%30,%31,%32};"
-                            ::"r"(o_tm + c * 32), "r"(ob[0]), "r"(ob[1]), "r"(ob[2]), "r"(ob[3]), "r"(ob[4]), "r"(ob[5]),
-                              "r"(ob[6]), "r"(ob[7]), "r"(ob[8]), "r"(ob[9]), "r"(ob[10]), "r"(ob[11]), "r"(ob[12]),
-                              "r"(ob[13]), "r"(ob[14]), "r"(ob[15]), "r"(ob[16]), "r"(ob[17]), "r"(ob[18]), "r"(ob[19]),
-                              "r"(ob[20]), "r"(ob[21]), "r"(ob[22]), "r"(ob[23]), "r"(ob[24]), "r"(ob[25]), "r"(ob[26]),
-                              "r"(ob[27]), "r"(ob[28]), "r"(ob[29]), "r"(ob[30]), "r"(ob[31])
-                            : "memory");
+                        tmem_st32(o_tm + c * 32, ob);
                     }
                 }
             }
-            // pass 2: weights (f16) and row sum.  P goes over the first half of S_x, which also holds
-            // the partner's scores: both threads of a row finish reading S before either writes P.
-            float sum0 = 0.f, sum1 = 0.f;
-            uint32_t pk[32];
+            // weights (f16) over the first 64 columns of S_x, and the row sum
+            TC_PROF_MARK(pt2)
+            if (whole) {
+                const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_ref, -m_ref);
+                float2 acc_a = make_float2(0.f, 0.f), acc_b = make_float2(0.f, 0.f);
 #pragma unroll
-            for (uint32_t c = 0; c < 2; ++c) {
-                uint32_t r[32];
-                tmem_ld32(s_tm + col0 + c * 32, r);
-                tc_wait_ld();
-                const bool full = n_vis >= (c + 1) * 32;
+                for (uint32_t c = 0; c < 4; ++c) {
+                    uint32_t pk[16];
 #pragma unroll
-                for (uint32_t q = 0; q < 16; ++q) {
-                    float p0 = fast_exp2(fmaf(__uint_as_float(r[2 * q]), p.scale_log2, -m_ref));
-                    float p1 = fast_exp2(fmaf(__uint_as_float(r[2 * q + 1]), p.scale_log2, -m_ref));
-                    if (!full) {
-                        if (c * 32 + 2 * q >= n_vis) p0 = 0.f;
-                        if (c * 32 + 2 * q + 1 >= n_vis) p1 = 0.f;
+                    for (uint32_t q = 0; q < 16; ++q) {
+                        const float2 t = __ffma2_rn(make_float2(__uint_as_float(r[c * 32 + 2 * q]),
+                                                                __uint_as_float(r[c * 32 + 2 * q + 1])), sc2, nm2);
+                        float2 w;
+                        if (kPolyMask & (1u << (q & 7))) {
+                            w = exp2_poly2(t);
+                        } else {
+                            w.x = fast_exp2(t.x);
+                            w.y = fast_exp2(t.y);
+                        }
+                        if (q & 1) acc_b = __fadd2_rn(acc_b, w);
+                        else acc_a = __fadd2_rn(acc_a, w);
+                        pk[q] = pack_f16x2(w.x, w.y);
                     }
-                    sum0 += p0;
-                    sum1 += p1;
-                    pk[c * 16 + q] = pack_f16x2(p0, p1);
+                    tmem_st16(s_tm + c * 16, pk);
                 }
+                const float2 acc = __fadd2_rn(acc_a, acc_b);
+                l_run += acc.x + acc.y;  // relative to m_ref
+            } else {
+                float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+                for (uint32_t c = 0; c < 4; ++c) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (uint32_t q = 0; q < 16; ++q) {
+                        const float p0 = fast_exp2(fmaf(__uint_as_float(r[c * 32 + 2 * q]), p.scale_log2, -m_ref));
+                        const float p1 = fast_exp2(fmaf(__uint_as_float(r[c * 32 + 2 * q + 1]), p.scale_log2, -m_ref));
+                        sum0 += p0;
+                        sum1 += p1;
+                        pk[q] = pack_f16x2(p0, p1);
+                    }
+                    tmem_st16(s_tm + c * 16, pk);
+                }
+                l_run += sum0 + sum1;
             }
-            TC_PROF_WAIT(3, named_bar_sync(pair_bar, 64))
-            tmem_st16(s_tm + half * 32, *reinterpret_cast<uint32_t(*)[16]>(&pk[0]));
-            tmem_st16(s_tm + half * 32 + 16, *reinterpret_cast<uint32_t(*)[16]>(&pk[16]));
-            l_run += sum0 + sum1;  // partial sum over this thread's columns, relative to m_ref
+            TC_PROF_MARK(pt3)
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(kPFull + x));  // P(i) is in TMEM, O_x is consistent with m_ref
+            TC_PROF_MARK(pt4)
+            TC_PROF_SPAN(4, pt0, pt1)
+            TC_PROF_SPAN(5, pt1, pt2)
+            TC_PROF_SPAN(6, pt2, pt3)
+            TC_PROF_SPAN(7, pt3, pt4)
         }
 
         // ---- merge the two streams and write the rows out --------------------------------------
-        float o[64];
         if (n_mine) {
             TC_PROF_WAIT(2, wait(bar(kOFull + x), (n_mine - 1) & 1, 128u))
             tc_fence_after();
-            tmem_ld32(o_tm, *reinterpret_cast<uint32_t(*)[32]>(&o[0]));
-            tmem_ld32(o_tm + 32, *reinterpret_cast<uint32_t(*)[32]>(&o[32]));
-            tc_wait_ld();
-        } else {
-#pragma unroll
-            for (uint32_t c = 0; c < 64; ++c) o[c] = 0.f;
         }
         // Every product has completed (both streams waited for their last P V), so the K ring can
-        // carry stream 1's accumulator over to stream 0: [row][128] f32 = 64 KB, plus (m, l).
+        // carry stream 1's accumulator over to stream 0: [row][128 (+4 pad)] f32 = 66 KB, plus (m, l).
         float *xo = reinterpret_cast<float *>(smem + kTile);     // K ring
-        float *xl = max_buf;                                      // [stream][half][row] partial l
-        float *xm = max_buf + 512;                                // [stream][row] reference maxima
+        float *xl = max_buf;                                      // [stream][row] l relative to m_ref
+        float *xm = max_buf + 256;                                // [stream][row] reference maxima
         named_bar_sync(9, kSoftmaxThreads);  // all softmax warps are past their tile loops
-        xl[(x * 2 + half) * 128 + r_in] = l_run;
-        if (half == 0) xm[x * 128 + r_in] = m_ref;
+        xl[x * 128 + r_in] = l_run;
+        xm[x * 128 + r_in] = m_ref;
         if (x == 1) {
+#pragma unroll 1
+            for (uint32_t c = 0; c < 4; ++c) {
+                float o[32];
+                if (n_mine) {
+                    tmem_ld32(o_tm + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&o[0]));
+                    tc_wait_ld();
+                } else {
 #pragma unroll
-            for (uint32_t c = 0; c < 64; c += 4)
-                *reinterpret_cast<float4 *>(xo + (size_t)r_in * 132 + col0 + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+                    for (uint32_t q = 0; q < 32; ++q) o[q] = 0.f;
+                }
+#pragma unroll
+                for (uint32_t q = 0; q < 32; q += 4)
+                    *reinterpret_cast<float4 *>(xo + (size_t)r_in * 132 + c * 32 + q) = make_float4(o[q], o[q + 1], o[q + 2], o[q + 3]);
+            }
         }
         named_bar_sync(10, kSoftmaxThreads);
-        if (x == 0 && row < p.q_len) {
+        if (x == 0) {
             const float m0 = xm[r_in], m1 = xm[128 + r_in];
             const float mm = fmaxf(m0, m1);
             const float w0 = fast_exp2(m0 - mm), w1 = fast_exp2(m1 - mm);
-            const float l_tot = (xl[r_in] + xl[128 + r_in]) * w0 + (xl[256 + r_in] + xl[384 + r_in]) * w1;
+            const float l_tot = xl[r_in] * w0 + xl[128 + r_in] * w1;
             const float inv = ((fabsf(l_tot) <= 3.0e38f) && fabsf(l_tot) > 1e-6f) ? 1.0f / l_tot : 0.f;
             const float f0 = w0 * inv, f1 = w1 * inv;
-            __half *dst = p.out + (size_t)row * p.out_stride_m + (size_t)head * p.out_stride_h + col0;
-            const float *other = xo + (size_t)r_in * 132 + col0;
+            __half *dst = p.out + (size_t)row * p.out_stride_m + (size_t)head * p.out_stride_h;
+#pragma unroll 1
+            for (uint32_t c = 0; c < 4; ++c) {
+                float o[32];
+                tmem_ld32(o_tm + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&o[0]));  // n_tiles >= 1: stream 0 has a tile
+                tc_wait_ld();
+                if (row < p.q_len) {
+                    const float *other = xo + (size_t)r_in * 132 + c * 32;
 #pragma unroll
-            for (uint32_t d = 0; d < 64; d += 8) {
-                const float4 a = *reinterpret_cast<const float4 *>(other + d);
-                const float4 b = *reinterpret_cast<const float4 *>(other + d + 4);
-                uint4 v;
-                v.x = pack_f16x2(o[d] * f0 + a.x * f1, o[d + 1] * f0 + a.y * f1);
-                v.y = pack_f16x2(o[d + 2] * f0 + a.z * f1, o[d + 3] * f0 + a.w * f1);
-                v.z = pack_f16x2(o[d + 4] * f0 + b.x * f1, o[d + 5] * f0 + b.y * f1);
-                v.w = pack_f16x2(o[d + 6] * f0 + b.z * f1, o[d + 7] * f0 + b.w * f1);
-                *reinterpret_cast<uint4 *>(dst + d) = v;
+                    for (uint32_t d = 0; d < 32; d += 8) {
+                        const float4 a = *reinterpret_cast<const float4 *>(other + d);
+                        const float4 b = *reinterpret_cast<const float4 *>(other + d + 4);
+                        uint4 v;
+                        v.x = pack_f16x2(o[d] * f0 + a.x * f1, o[d + 1] * f0 + a.y * f1);
+                        v.y = pack_f16x2(o[d + 2] * f0 + a.z * f1, o[d + 3] * f0 + a.w * f1);
+                        v.z = pack_f16x2(o[d + 4] * f0 + b.x * f1, o[d + 5] * f0 + b.y * f1);
+                        v.w = pack_f16x2(o[d + 6] * f0 + b.z * f1, o[d + 7] * f0 + b.w * f1);
+                        *reinterpret_cast<uint4 *>(dst + c * 32 + d) = v;
+                    }
+                }
             }
         }
         if (tid == 0) {
