@@ -6,23 +6,25 @@
 // `scale`, running max from -1e30, f32 weights / l / accumulator, acc * (1/l) or 0, rows past
 // q_len not written.  P is rounded to f16 for the PV product.
 //
-// One CTA per (128-row query tile, query head).  The 128-key tiles of the CTA are dealt to two
-// independent online-softmax streams (even tiles -> stream 0, odd tiles -> stream 1), each with
-// its own running (m, l, O); the streams are merged with the log-sum-exp rule at the end.  While
-// one stream's warps exponentiate, the tensor pipe works on the other stream's products.
-//   warps 0-3   stream 0 softmax, warps 4-7 stream 1 softmax; one thread per query row
-//               (= TMEM lane) holds the row's 128 scores in registers: warp w works on lane
+// One CTA per (128-row query tile, query head), walking the visible 128-key tiles in order.
+//   warps 0-3   softmax group 0 (even tiles), warps 4-7 group 1 (odd tiles); one thread per query
+//               row (= TMEM lane) holds the row's 128 scores in registers: warp w works on lane
 //               quadrant w % 4
 //   warp 8      TMA producer: Q tile once, then rings of 128-key K and V tiles (3 deep each)
 //   warp 9      TMEM allocation and the single thread that issues tcgen05.mma
-// Per tile of stream x:  S_x = Q K^T (A, B from 128-byte-swizzled shared memory, accumulator in
-// TMEM) -> the stream's warps read S_x with tcgen05.ld, write P (f16) over the first 64 columns
-// of S_x with tcgen05.st -> O_x += P V (A from TMEM, B = V tile as an MN-major operand), O_x
-// staying in TMEM.  The accumulator is only rescaled when a row's maximum has grown by more than
-// 2^8 since the last rescale (the weights are then at most 256, which f16 holds without loss of
-// relative precision); the final normalisation uses the reference maximum actually applied.
+// Three score buffers and ONE output accumulator live in TMEM.  Per tile i, buffer b = i % 3:
+//   S_b = Q K_i^T (A, B from 128-byte-swizzled shared memory, accumulator in TMEM)
+//   -> group i % 2 reads S_b with tcgen05.ld, folds the row maxima into the running reference
+//      m_ref (handed between the groups through shared memory, a few hundred cycles per tile),
+//      writes P (f16) over the first 64 columns of S_b with tcgen05.st
+//   -> O += P V_i (A from TMEM, B = V tile as an MN-major operand), O staying in TMEM
+//   -> Q K_{i+3}^T is issued behind that product into the same buffer.
+// With three buffers the two groups exponentiate two tiles at once while the tensor pipe works
+// on the third.  O is only rescaled when a row's maximum has grown by more than 2^8 since the
+// last rescale (the weights are then at most 256, which f16 holds without loss of relative
+// precision); the final normalisation uses the reference maximum actually applied.
 //
-// TMEM columns (512): S_0/P_0 [0,128)  S_1/P_1 [128,256)  O_0 [256,384)  O_1 [384,512).
+// TMEM columns (512): S_0/P_0 [0,128)  S_1/P_1 [128,256)  S_2/P_2 [256,384)  O [384,512).
 #include <algorithm>
 
 #include "internal.hpp"
@@ -34,17 +36,13 @@ namespace {
 #ifndef MF_TC_VSTAGES
 #define MF_TC_VSTAGES 3
 #endif
-#ifndef MF_TC_ISSUERS
-#define MF_TC_ISSUERS 1
-#endif
-constexpr uint32_t kIssuers = MF_TC_ISSUERS;  // threads issuing tcgen05.mma: one for both streams, or one each
 constexpr uint32_t kBM = 128;             // query rows per CTA
 constexpr uint32_t kBN = 128;             // keys per tile
 constexpr uint32_t kD = 128;              // head_dim
-constexpr uint32_t kStreamWarps = 4;                      // softmax warps per stream (one thread per row)
-constexpr uint32_t kSoftmaxWarps = 2 * kStreamWarps;
+constexpr uint32_t kGroupWarps = 4;                       // softmax warps per group (one thread per row)
+constexpr uint32_t kSoftmaxWarps = 2 * kGroupWarps;
 constexpr uint32_t kSoftmaxThreads = 32 * kSoftmaxWarps;
-constexpr uint32_t kTcThreads = kSoftmaxThreads + 32 + 32 * kIssuers;
+constexpr uint32_t kTcThreads = kSoftmaxThreads + 64;
 constexpr float kRescaleThreshold = 8.0f;                 // log2 of the largest weight kept in P
 #ifndef MF_TC_POLY_MASK
 #define MF_TC_POLY_MASK 0x00u
@@ -229,20 +227,21 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *tmap, int3
 // Barrier slots (8 bytes each) after the tiles.
 enum Bar : uint32_t {
     kQFull = 0,
-    kKFull = 1,    // [4]
-    kVFull = 5,    // [4]
-    kKEmpty = 9,   // [4]
-    kVEmpty = 13,  // [4]
-    kSFull = 17,   // [2] per stream: S_x holds Q K^T of the stream's next tile
-    kPFull = 19,   // [2] per stream: P is in TMEM (and O_x has been rescaled if needed)
-    kOFull = 21,   // [2] per stream: the stream's last issued P V has completed
-    kNumBars = 23
+    kKFull = 1,    // [3]
+    kVFull = 4,    // [3]
+    kKEmpty = 7,   // [3]
+    kVEmpty = 10,  // [3]
+    kSFull = 13,   // [3] per score buffer: it holds Q K^T of its next tile
+    kPFull = 16,   // [3] per score buffer: P is in it (and O has been rescaled if needed)
+    kOFull = 19,   // [3] per score buffer: the P V that read it has completed
+    kDec = 22,     // [2] by tile parity: the tile's row maxima have been folded into m_ref
+    kNumBars = 24
 };
-static_assert(kKStages <= 4 && kVStages <= 4, "barrier slots");
+static_assert(kKStages == 3 && kVStages == 3, "barrier slots");
 
 constexpr uint32_t kSmemTiles = kTile * (1 + kKStages + kVStages);  // Q + K ring + V ring
-constexpr uint32_t kMaxBufBytes = 0;  // (l, m) of both streams travel through the Q tile, free by then
-constexpr uint32_t kSmemBytes = kSmemTiles + kMaxBufBytes + kNumBars * 8 + 16 + 1024;
+constexpr uint32_t kRefBytes = 128 * 4;                             // m_ref per query row
+constexpr uint32_t kSmemBytes = kSmemTiles + kRefBytes + kNumBars * 8 + 16 + 1024;
 static_assert(kSmemBytes <= 227 * 1024, "shared memory");
 
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -255,9 +254,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t q_smem = smem_base;
     const uint32_t k_smem = smem_base + kTile;
     const uint32_t v_smem = k_smem + kKStages * kTile;
-    float *max_buf = reinterpret_cast<float *>(smem);  // epilogue only: the Q tile is no longer read
-    const uint32_t bars = smem_base + kSmemTiles + kMaxBufBytes;
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + kSmemTiles + kMaxBufBytes + kNumBars * 8);
+    volatile float *mref = reinterpret_cast<volatile float *>(smem + kSmemTiles);
+    float *lbuf = reinterpret_cast<float *>(smem);  // epilogue only: the Q tile is no longer read
+    const uint32_t bars = smem_base + kSmemTiles + kRefBytes;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + kSmemTiles + kRefBytes + kNumBars * 8);
     volatile uint32_t *abort_flag = tmem_slot + 1;
     auto bar = [&](uint32_t i) { return bars + i * 8; };
 
@@ -272,17 +272,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
     if (tid == 0) {
         mbar_init(bar(kQFull), 1);
-        for (uint32_t s = 0; s < 4; ++s) {
+        for (uint32_t s = 0; s < 3; ++s) {
             mbar_init(bar(kKFull + s), 1);
             mbar_init(bar(kVFull + s), 1);
             mbar_init(bar(kKEmpty + s), 1);
             mbar_init(bar(kVEmpty + s), 1);
+            mbar_init(bar(kSFull + s), 1);
+            mbar_init(bar(kPFull + s), kGroupWarps);  // one arrival per softmax warp of the group
+            mbar_init(bar(kOFull + s), 1);
         }
-        for (uint32_t x = 0; x < 2; ++x) {
-            mbar_init(bar(kSFull + x), 1);
-            mbar_init(bar(kPFull + x), kStreamWarps);  // one arrival per softmax warp of the stream
-            mbar_init(bar(kOFull + x), 1);
-        }
+        mbar_init(bar(kDec), kGroupWarps);
+        mbar_init(bar(kDec + 1), kGroupWarps);
         *abort_flag = 0;
         mbar_fence_init();
         fence_proxy_async();
@@ -329,18 +329,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 tma_load_3d(v_smem + vs * kTile, &tm_v, 0, (int32_t)(i * kBN), (int32_t)kvh, bar(kVFull + vs));
                 tma_load_3d(v_smem + vs * kTile + kHalfTile, &tm_v, 64, (int32_t)(i * kBN), (int32_t)kvh, bar(kVFull + vs));
             };
-            // K runs two tiles ahead of V, the order in which the tensor pipe frees the rings.
-            for (uint32_t i = 0; i < min(n_tiles, 2u); ++i) load_k(i);
+            // The order in which the tensor pipe asks for the tiles: K runs three tiles ahead of V.
+            for (uint32_t i = 0; i < min(n_tiles, 3u); ++i) load_k(i);
             for (uint32_t i = 0; i < n_tiles; ++i) {
-                if (i + 2 < n_tiles) load_k(i + 2);
                 load_v(i);
+                if (i + 3 < n_tiles) load_k(i + 3);
             }
             TC_PROF_STORE(2)
         }
-    } else if (warp >= kSoftmaxWarps + 1) {
-        // ------------------------------------------------------------------ MMA issuer(s) ---
-        const uint32_t me = warp - (kSoftmaxWarps + 1);
-        if (lane == 0 && me < n_tiles) {
+    } else if (warp == kSoftmaxWarps + 1) {
+        // ------------------------------------------------------------------ MMA issuer ---
+        if (lane == 0) {
             constexpr uint32_t kIdescQK = instr_desc(kBN, 0);
             constexpr uint32_t kIdescPV = instr_desc(kD, 1);
             TC_PROF_DECL
@@ -349,7 +348,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             // once and add the 16-byte-unit offsets, so that an MMA costs this thread a few instructions.
             const uint64_t q_desc = smem_desc(q_smem, 16, 1024);
             auto issue_qk = [&](uint32_t i) {
-                const uint32_t x = i & 1;
+                const uint32_t b = i % 3;
                 const uint32_t ks = i % kKStages, kph = (i / kKStages) & 1;
                 TC_PROF_WAIT(0, wait(bar(kKFull + ks), kph, 32u))
                 tc_fence_after();
@@ -358,75 +357,70 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
                 for (uint32_t kk = 0; kk < kD / 16; ++kk) {
                     const uint32_t off = ((kk >> 2) * kHalfTile + (kk & 3) * 32) >> 4;
-                    tc_mma_ss(tmem + x * 128, q_desc + off, k_desc + off, kIdescQK, kk > 0);
+                    tc_mma_ss(tmem + b * 128, q_desc + off, k_desc + off, kIdescQK, kk > 0);
                 }
                 TC_PROF_MARK(mb)
-                tc_commit(bar(kSFull + x));
+                tc_commit(bar(kSFull + b));
                 tc_commit(bar(kKEmpty + ks));
                 TC_PROF_MARK(mc)
                 TC_PROF_SPAN(4, ma, mb)
                 TC_PROF_SPAN(6, mb, mc)
             };
             auto issue_pv = [&](uint32_t i) {
-                const uint32_t x = i & 1, j = i >> 1;
+                const uint32_t b = i % 3;
                 const uint32_t vs = i % kVStages, vph = (i / kVStages) & 1;
                 TC_PROF_WAIT(2, wait(bar(kVFull + vs), vph, 64u))
-                TC_PROF_WAIT(3, wait(bar(kPFull + x), j & 1, 64u))
+                TC_PROF_WAIT(3, wait(bar(kPFull + b), (i / 3) & 1, 64u))
                 tc_fence_after();
                 TC_PROF_MARK(ma)
                 const uint64_t v_desc = smem_desc(v_smem + vs * kTile, kHalfTile, 1024);
 #pragma unroll
                 for (uint32_t kk = 0; kk < kBN / 16; ++kk) {
                     // A: 16 keys = 8 packed 32-bit TMEM columns per step; B: V rows kk*16.., MN-major.
-                    tc_mma_ts(tmem + 256 + x * 128, tmem + x * 128 + kk * 8, v_desc + kk * (2048 >> 4), kIdescPV,
-                              (j > 0 || kk > 0) ? 1u : 0u);
+                    tc_mma_ts(tmem + 384, tmem + b * 128 + kk * 8, v_desc + kk * (2048 >> 4), kIdescPV,
+                              (i > 0 || kk > 0) ? 1u : 0u);
                 }
                 TC_PROF_MARK(mb)
-                tc_commit(bar(kOFull + x));
+                tc_commit(bar(kOFull + b));
                 tc_commit(bar(kVEmpty + vs));
                 TC_PROF_MARK(mc)
                 TC_PROF_SPAN(5, ma, mb)
                 TC_PROF_SPAN(7, mb, mc)
             };
-            // Q K^T of a stream's next tile is issued right behind its P V by the same thread, whose
-            // MMAs run in order, so S_x is overwritten only after P (which lives in S_x) was consumed.
-            if (kIssuers == 1) {
-                for (uint32_t i = 0; i < min(n_tiles, 2u); ++i) issue_qk(i);
-                for (uint32_t i = 0; i < n_tiles; ++i) {
-                    issue_pv(i);
-                    if (i + 2 < n_tiles) issue_qk(i + 2);
-                }
-            } else {
-                issue_qk(me);
-                for (uint32_t i = me; i < n_tiles; i += 2) {
-                    issue_pv(i);
-                    if (i + 2 < n_tiles) issue_qk(i + 2);
-                }
+            // Q K^T of tile i + 3 goes into the buffer that P V of tile i has just read: the tensor
+            // pipe runs this thread's MMAs in order, so S overwrites P only after P was consumed.
+            for (uint32_t i = 0; i < min(n_tiles, 3u); ++i) issue_qk(i);
+            for (uint32_t i = 0; i < n_tiles; ++i) {
+                issue_pv(i);
+                if (i + 3 < n_tiles) issue_qk(i + 3);
             }
-            if (me == 0) { TC_PROF_STORE(1) }
+            TC_PROF_STORE(1)
         }
     } else {
-        // ------------------------------------------------- softmax / epilogue, two streams ---
-        // One thread per query row (= TMEM lane) and stream: the whole row of S is in registers,
-        // so the maximum and the sum need no exchange between threads.
-        const uint32_t x = warp >> 2;                           // stream
+        // --------------------------------------------------------- softmax groups / epilogue ---
+        // One thread per query row (= TMEM lane) and group: the whole row of S is in registers, so
+        // the row maximum and sum need no exchange inside a tile; between tiles the two groups hand
+        // the row's reference maximum to each other through shared memory.
+        const uint32_t g = warp >> 2;                           // group: tiles i = g, g + 2, ...
         const uint32_t quad = warp & 3;
         const uint32_t r_in = quad * 32 + lane;                 // row inside the tile = TMEM lane
         const uint32_t row = row0 + r_in;
         const uint32_t lane_base = (quad * 32u) << 16;          // TMEM lane quadrant of this warp
         const uint32_t limit = row + p.query_offset;            // last visible key
-        const uint32_t s_tm = tmem + lane_base + x * 128;       // S_x / P_x
-        const uint32_t o_tm = tmem + lane_base + 256 + x * 128;
-        const uint32_t n_mine = n_tiles > x ? (n_tiles - x + 1) / 2 : 0;
+        const uint32_t o_tm = tmem + lane_base + 384;
         const uint32_t last_ok = min(limit, p.kv_len - 1);
-        float m_ref = kNegInf, l_run = 0.f;                     // m in the scaled log2 domain
+        float my_ref = kNegInf, l_part = 0.f;                   // my_ref in the scaled log2 domain
+        uint32_t last_mine = 0xFFFFFFFFu;
         TC_PROF_DECL
 
-        for (uint32_t j = 0; j < n_mine; ++j) {
-            const uint32_t key0 = (2 * j + x) * kBN;
+        for (uint32_t i = g; i < n_tiles; i += 2) {
+            const uint32_t b = i % 3, sph = (i / 3) & 1;
+            const uint32_t s_tm = tmem + lane_base + b * 128;   // S / P buffer of this tile
+            const uint32_t key0 = i * kBN;
             // Only tiles on the causal diagonal or at the end of the cache need a mask.
             const uint32_t n_vis = last_ok < key0 ? 0u : min(kBN, last_ok - key0 + 1);
-            TC_PROF_WAIT(0, wait(bar(kSFull + x), j & 1, 256u))
+            last_mine = i;
+            TC_PROF_WAIT(0, wait(bar(kSFull + b), sph, 256u))
             tc_fence_after();
             // The TMEM accesses below are warp-collective: the choice between the plain and the
             // masked form of the row must be the same for all 32 rows of the warp.
@@ -436,7 +430,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
             for (uint32_t c = 0; c < 4; ++c) tmem_ld32(s_tm + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
             tc_wait_ld();
-            TC_PROF_MARK(pt1)
             // row maximum of the raw scores (the scale is positive)
             float mx0 = -3.0e38f, mx1 = -3.0e38f, mx2 = -3.0e38f, mx3 = -3.0e38f;
             if (whole) {
@@ -456,30 +449,43 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
             const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
             const float m_new = mx > -3.0e38f ? mx * p.scale_log2 : kNegInf;
-            // Lazy rescale: keep exponentiating against m_ref until a row outgrows it by 2^8.
-            const bool grow = m_new > m_ref + kRescaleThreshold;
-            if (__any_sync(0xffffffffu, grow)) {
-                const float m_next = grow ? m_new : m_ref;
-                const float alpha = fast_exp2(m_ref - m_next);
-                m_ref = m_next;
-                l_run *= alpha;
-                if (j > 0) {
-                    // O_x must hold every earlier P V before it is scaled.  S(j) being there implies that
-                    // P V (j - 2), issued before it, is done, so one parity bit is unambiguous here.
-                    TC_PROF_WAIT(2, wait(bar(kOFull + x), (j - 1) & 1, 128u))
-                    tc_fence_after();
-#pragma unroll 1
-                    for (uint32_t c = 0; c < 4; ++c) {
-                        uint32_t ob[32];
-                        tmem_ld32(o_tm + c * 32, ob);
-                        tc_wait_ld();
-#pragma unroll
-                        for (uint32_t q = 0; q < 32; ++q) ob[q] = __float_as_uint(__uint_as_float(ob[q]) * alpha);
-                        tmem_st32(o_tm + c * 32, ob);
-                    }
-                }
+            TC_PROF_MARK(pt1)
+            // The reference maximum after tile i - 1, decided by the other group.
+            float m_prev = kNegInf;
+            if (i > 0) {
+                TC_PROF_WAIT(1, wait(bar(kDec + ((i - 1) & 1)), ((i - 1) >> 1) & 1, 512u))
+                m_prev = mref[r_in];
             }
-            // weights (f16) over the first 64 columns of S_x, and the row sum
+            // Lazy rescale: keep exponentiating against the old reference until a row outgrows it by 2^8.
+            const bool grow = m_new > m_prev + kRescaleThreshold;
+            const float m_ref = grow ? m_new : m_prev;
+            if (m_ref != my_ref) {
+                l_part *= fast_exp2(my_ref - m_ref);
+                my_ref = m_ref;
+            }
+            if (i > 0 && __any_sync(0xffffffffu, grow)) {
+                // O must hold every earlier P V before it is scaled.  S(i) being there implies that
+                // P V (i - 3) is done, so the parity of the buffer's barrier is unambiguous.
+                const uint32_t pb = (i - 1) % 3;
+                TC_PROF_WAIT(2, wait(bar(kOFull + pb), ((i - 1) / 3) & 1, 128u))
+                tc_fence_after();
+                const float alpha = fast_exp2(m_prev - m_ref);
+#pragma unroll 1
+                for (uint32_t c = 0; c < 4; ++c) {
+                    uint32_t ob[32];
+                    tmem_ld32(o_tm + c * 32, ob);
+                    tc_wait_ld();
+#pragma unroll
+                    for (uint32_t q = 0; q < 32; ++q) ob[q] = __float_as_uint(__uint_as_float(ob[q]) * alpha);
+                    tmem_st32(o_tm + c * 32, ob);
+                }
+                tc_wait_st();
+            }
+            mref[r_in] = m_ref;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(kDec + (i & 1)));  // the other group may fold in tile i + 1
+            // weights (f16) over the first 64 columns of the buffer, and the row sum
             TC_PROF_MARK(pt2)
             if (whole) {
                 const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_ref, -m_ref);
@@ -505,7 +511,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     tmem_st16(s_tm + c * 16, pk);
                 }
                 const float2 acc = __fadd2_rn(acc_a, acc_b);
-                l_run += acc.x + acc.y;  // relative to m_ref
+                l_part += acc.x + acc.y;  // relative to my_ref
             } else {
                 float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
@@ -521,13 +527,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     }
                     tmem_st16(s_tm + c * 16, pk);
                 }
-                l_run += sum0 + sum1;
+                l_part += sum0 + sum1;
             }
             TC_PROF_MARK(pt3)
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(kPFull + x));  // P(i) is in TMEM, O_x is consistent with m_ref
+            if (lane == 0) mbar_arrive(bar(kPFull + b));  // P(i) is in TMEM, O is consistent with m_ref
             TC_PROF_MARK(pt4)
             TC_PROF_SPAN(4, pt0, pt1)
             TC_PROF_SPAN(5, pt1, pt2)
@@ -535,62 +541,34 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             TC_PROF_SPAN(7, pt3, pt4)
         }
 
-        // ---- merge the two streams and write the rows out --------------------------------------
-        if (n_mine) {
-            TC_PROF_WAIT(2, wait(bar(kOFull + x), (n_mine - 1) & 1, 128u))
-            tc_fence_after();
+        // ---- normalise and write the rows out: group g takes columns [64 g, 64 g + 64) ------------
+        if (last_mine != 0xFFFFFFFFu) {
+            // The product of this group's last tile; the other group waits for its own, and the
+            // tensor pipe completes them in order.
+            TC_PROF_WAIT(2, wait(bar(kOFull + last_mine % 3), (last_mine / 3) & 1, 128u))
         }
-        // Every product has completed (both streams waited for their last P V), so the K ring can
-        // carry stream 1's accumulator over to stream 0: [row][128 (+4 pad)] f32 = 66 KB, plus (m, l).
-        float *xo = reinterpret_cast<float *>(smem + kTile);     // K ring
-        float *xl = max_buf;                                      // [stream][row] l relative to m_ref
-        float *xm = max_buf + 256;                                // [stream][row] reference maxima
-        named_bar_sync(9, kSoftmaxThreads);  // all softmax warps are past their tile loops
-        xl[x * 128 + r_in] = l_run;
-        xm[x * 128 + r_in] = m_ref;
-        if (x == 1) {
-#pragma unroll 1
-            for (uint32_t c = 0; c < 4; ++c) {
-                float o[32];
-                if (n_mine) {
-                    tmem_ld32(o_tm + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&o[0]));
-                    tc_wait_ld();
-                } else {
-#pragma unroll
-                    for (uint32_t q = 0; q < 32; ++q) o[q] = 0.f;
-                }
-#pragma unroll
-                for (uint32_t q = 0; q < 32; q += 4)
-                    *reinterpret_cast<float4 *>(xo + (size_t)r_in * 132 + c * 32 + q) = make_float4(o[q], o[q + 1], o[q + 2], o[q + 3]);
-            }
-        }
+        named_bar_sync(9, kSoftmaxThreads);  // every product is done, every decision published
+        tc_fence_after();
+        const float m_fin = mref[r_in];
+        lbuf[g * 128 + r_in] = l_part * fast_exp2(my_ref - m_fin);
         named_bar_sync(10, kSoftmaxThreads);
-        if (x == 0) {
-            const float m0 = xm[r_in], m1 = xm[128 + r_in];
-            const float mm = fmaxf(m0, m1);
-            const float w0 = fast_exp2(m0 - mm), w1 = fast_exp2(m1 - mm);
-            const float l_tot = xl[r_in] * w0 + xl[128 + r_in] * w1;
-            const float inv = ((fabsf(l_tot) <= 3.0e38f) && fabsf(l_tot) > 1e-6f) ? 1.0f / l_tot : 0.f;
-            const float f0 = w0 * inv, f1 = w1 * inv;
-            __half *dst = p.out + (size_t)row * p.out_stride_m + (size_t)head * p.out_stride_h;
+        const float l_tot = lbuf[r_in] + lbuf[128 + r_in];
+        const float inv = ((fabsf(l_tot) <= 3.0e38f) && fabsf(l_tot) > 1e-6f) ? 1.0f / l_tot : 0.f;
+        __half *dst = p.out + (size_t)row * p.out_stride_m + (size_t)head * p.out_stride_h + g * 64;
 #pragma unroll 1
-            for (uint32_t c = 0; c < 4; ++c) {
-                float o[32];
-                tmem_ld32(o_tm + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&o[0]));  // n_tiles >= 1: stream 0 has a tile
-                tc_wait_ld();
-                if (row < p.q_len) {
-                    const float *other = xo + (size_t)r_in * 132 + c * 32;
+        for (uint32_t c = 0; c < 2; ++c) {
+            float o[32];
+            tmem_ld32(o_tm + g * 64 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&o[0]));
+            tc_wait_ld();
+            if (row < p.q_len) {
 #pragma unroll
-                    for (uint32_t d = 0; d < 32; d += 8) {
-                        const float4 a = *reinterpret_cast<const float4 *>(other + d);
-                        const float4 b = *reinterpret_cast<const float4 *>(other + d + 4);
-                        uint4 v;
-                        v.x = pack_f16x2(o[d] * f0 + a.x * f1, o[d + 1] * f0 + a.y * f1);
-                        v.y = pack_f16x2(o[d + 2] * f0 + a.z * f1, o[d + 3] * f0 + a.w * f1);
-                        v.z = pack_f16x2(o[d + 4] * f0 + b.x * f1, o[d + 5] * f0 + b.y * f1);
-                        v.w = pack_f16x2(o[d + 6] * f0 + b.z * f1, o[d + 7] * f0 + b.w * f1);
-                        *reinterpret_cast<uint4 *>(dst + c * 32 + d) = v;
-                    }
+                for (uint32_t d = 0; d < 32; d += 8) {
+                    uint4 v;
+                    v.x = pack_f16x2(o[d] * inv, o[d + 1] * inv);
+                    v.y = pack_f16x2(o[d + 2] * inv, o[d + 3] * inv);
+                    v.z = pack_f16x2(o[d + 4] * inv, o[d + 5] * inv);
+                    v.w = pack_f16x2(o[d + 6] * inv, o[d + 7] * inv);
+                    *reinterpret_cast<uint4 *>(dst + c * 32 + d) = v;
                 }
             }
         }
