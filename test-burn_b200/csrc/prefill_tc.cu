@@ -58,7 +58,7 @@ constexpr float kNegInf = -1e30f;
 struct TcParams {
     __half *out;
     uint32_t *status;
-    uint32_t q_len, kv_len, query_offset, group;
+    uint32_t q_len, kv_len, query_offset, group, n_heads, n_q_tiles;
     uint32_t out_stride_h, out_stride_m;
     float scale_log2;
 };
@@ -66,11 +66,14 @@ struct TcParams {
 #ifdef MF_TC_PROFILE
 // Development aid (build with -DMF_TC_PROFILE): cycles spent in each barrier wait, per CTA and role.
 __device__ unsigned long long g_tc_prof[1024 * 32];
-#define TC_PROF_DECL unsigned long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long prof_t0 = clock64();
+#define TC_PROF_DECL unsigned long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long prof_t0 = clock64(); \
+    unsigned long long prof_g0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_g0));
 #define TC_PROF_WAIT(idx, stmt) { const long long t_ = clock64(); stmt; prof_acc[idx] += (unsigned long long)(clock64() - t_); }
-#define TC_PROF_STORE(role) { const uint32_t cta_ = blockIdx.y * gridDim.x + blockIdx.x; if (cta_ < 1024) { \
+#define TC_PROF_STORE(role) { const uint32_t cta_ = blockIdx.x; if (cta_ < 1024) { \
         for (int k_ = 0; k_ < 8; ++k_) g_tc_prof[cta_ * 32 + (role) * 10 + k_] = prof_acc[k_]; \
-        g_tc_prof[cta_ * 32 + (role) * 10 + 8] = (unsigned long long)(clock64() - prof_t0); if ((role) == 0) g_tc_prof[cta_ * 32 + 31] = n_tiles; } }
+        g_tc_prof[cta_ * 32 + (role) * 10 + 8] = (unsigned long long)(clock64() - prof_t0); if ((role) == 0) { g_tc_prof[cta_ * 32 + 31] = n_tiles; g_tc_prof[cta_ * 32 + 29] = prof_g0; \
+        unsigned int smid_; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid_)); g_tc_prof[cta_ * 32 + 30] = smid_; \
+        unsigned long long g1_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1_)); g_tc_prof[cta_ * 32 + 9] = g1_; } } }
 #else
 #define TC_PROF_DECL
 #define TC_PROF_WAIT(idx, stmt) stmt;
@@ -215,12 +218,13 @@ __device__ __forceinline__ float2 exp2_poly2(float2 t)
     return y;
 }
 
-// 3-D tiled load without a cache hint.
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *tmap, int32_t x, int32_t y, int32_t z, uint32_t bar)
+// 4-D tiled load without a cache hint: (column in half, row, half, head).
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void *tmap, int32_t x, int32_t y, int32_t z, int32_t w,
+                                            uint32_t bar)
 {
     asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-        ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar)
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
         : "memory");
 }
 
@@ -262,8 +266,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     auto bar = [&](uint32_t i) { return bars + i * 8; };
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t q_tile = gridDim.x - 1 - blockIdx.x;  // late (long) tiles first
-    const uint32_t head = blockIdx.y;
+    // CTAs are handed out in blockIdx order: all heads of the last (longest) query tile first, so the
+    // short tiles fill the tail of the grid.
+    const uint32_t q_tile = p.n_q_tiles - 1 - blockIdx.x / p.n_heads;
+    const uint32_t head = blockIdx.x % p.n_heads;
     const uint32_t kvh = head / p.group;
     const uint32_t row0 = q_tile * kBM;
     const uint32_t last_row = min(p.q_len, row0 + kBM) - 1;
@@ -311,23 +317,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tma_prefetch_desc(&tm_v);
             TC_PROF_DECL
             mbar_arrive_expect_tx(bar(kQFull), kTile);
-            tma_load_3d(q_smem, &tm_q, 0, (int32_t)row0, (int32_t)head, bar(kQFull));
-            tma_load_3d(q_smem + kHalfTile, &tm_q, 64, (int32_t)row0, (int32_t)head, bar(kQFull));
+            tma_load_4d(q_smem, &tm_q, 0, (int32_t)row0, 0, (int32_t)head, bar(kQFull));
             // K/V maps are (head_dim, kv_len, kv heads): rows past kv_len arrive as zeros, so a
             // never-written cache row cannot meet a zero weight as NaN.
             auto load_k = [&](uint32_t i) {
                 const uint32_t ks = i % kKStages, kph = (i / kKStages) & 1;
                 TC_PROF_WAIT(0, wait(bar(kKEmpty + ks), kph ^ 1, 16u))
                 mbar_arrive_expect_tx(bar(kKFull + ks), kTile);
-                tma_load_3d(k_smem + ks * kTile, &tm_k, 0, (int32_t)(i * kBN), (int32_t)kvh, bar(kKFull + ks));
-                tma_load_3d(k_smem + ks * kTile + kHalfTile, &tm_k, 64, (int32_t)(i * kBN), (int32_t)kvh, bar(kKFull + ks));
+                tma_load_4d(k_smem + ks * kTile, &tm_k, 0, (int32_t)(i * kBN), 0, (int32_t)kvh, bar(kKFull + ks));
             };
             auto load_v = [&](uint32_t i) {
                 const uint32_t vs = i % kVStages, vph = (i / kVStages) & 1;
                 TC_PROF_WAIT(1, wait(bar(kVEmpty + vs), vph ^ 1, 16u))
                 mbar_arrive_expect_tx(bar(kVFull + vs), kTile);
-                tma_load_3d(v_smem + vs * kTile, &tm_v, 0, (int32_t)(i * kBN), (int32_t)kvh, bar(kVFull + vs));
-                tma_load_3d(v_smem + vs * kTile + kHalfTile, &tm_v, 64, (int32_t)(i * kBN), (int32_t)kvh, bar(kVFull + vs));
+                tma_load_4d(v_smem + vs * kTile, &tm_v, 0, (int32_t)(i * kBN), 0, (int32_t)kvh, bar(kVFull + vs));
             };
             // The order in which the tensor pipe asks for the tiles: K runs three tiles ahead of V.
             for (uint32_t i = 0; i < min(n_tiles, 3u); ++i) load_k(i);
@@ -619,15 +622,16 @@ mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const 
     typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    // (head_dim, rows, heads) views with the caller's row and head strides; box = 64 columns x 128 rows.
+    // (64 columns, rows, 2 column halves, heads) views with the caller's row and head strides: one box of
+    // 64 columns x 128 rows x 2 halves brings a whole tile and lands as [half][row][128 B].
     auto encode = [&](CUtensorMap *tm, const void *base, uint64_t rows, uint64_t heads, uint64_t row_stride,
                       uint64_t head_stride) {
-        cuuint64_t gdim[3] = {kD, rows, heads};
-        cuuint64_t gstride[2] = {row_stride * 2, head_stride * 2};
-        cuuint32_t box[3] = {64, 128, 1};
-        cuuint32_t estr[3] = {1, 1, 1};
+        cuuint64_t gdim[4] = {64, rows, 2, heads};
+        cuuint64_t gstride[3] = {row_stride * 2, 128, head_stride * 2};
+        cuuint32_t box[4] = {64, 128, 2, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
         return reinterpret_cast<EncodeFn>(ctx->encode_fn)(
-                   tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base), gdim, gstride, box, estr,
+                   tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(base), gdim, gstride, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
     };
@@ -655,7 +659,9 @@ mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const 
         if (st != MF_OK) return st;
         configured[ctx->device] = true;
     }
-    dim3 grid((b.q_len + kBM - 1) / kBM, sp.n_heads);
+    p.n_heads = sp.n_heads;
+    p.n_q_tiles = (b.q_len + kBM - 1) / kBM;
+    dim3 grid(p.n_q_tiles * sp.n_heads);
     prefill_tc_kernel<<<grid, kTcThreads, kSmemBytes, ctx->stream>>>(tm_q, tm_k, tm_v, p);
     *handled = true;
     return check_launch(ctx, "prefill_tc_kernel");
