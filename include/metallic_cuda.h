@@ -443,6 +443,45 @@ MF_API mf_status mf_paged_decode_partial(MfContext *ctx, const MfDecodePlan *pla
                                          const uint32_t *rope_positions, float *acc, float *m,
                                          float *l);
 
+/* ---- paged cache life cycle: page allocator and prefix cache (host) ---------------------
+ * Replaces the reference's prefix snapshots (src/model/executor.rs:1136-1675): same
+ * entry rules (at most max_entries, default 8, clamped to 1..64; a store replaces the entry of
+ * the same key, or without key of the same tokens, and drops the oldest when full; a lookup
+ * without key takes the longest snapshot that is a prefix of the prompt, with key the longest
+ * common prefix among that key's entries not longer than the prompt; later entry on ties; a hit
+ * moves the entry to the back), but a snapshot is a list of page ids with raised reference
+ * counts instead of a copy of the rows.  Not thread-safe: one owner, like a context. */
+typedef struct MfPagePool MfPagePool;
+typedef struct MfPrefixCache MfPrefixCache;
+MF_API mf_status mf_page_pool_create(uint32_t n_pages, MfPagePool **out);
+MF_API void mf_page_pool_destroy(MfPagePool *pool);
+/* n pages with reference count 1, or MF_ERR_OUT_OF_MEMORY and none. */
+MF_API mf_status mf_page_pool_alloc(MfPagePool *pool, uint32_t n, uint32_t *ids_out);
+MF_API mf_status mf_page_pool_retain(MfPagePool *pool, const uint32_t *ids, uint32_t n);
+/* A page returns to the free list when its count reaches zero. */
+MF_API mf_status mf_page_pool_release(MfPagePool *pool, const uint32_t *ids, uint32_t n);
+MF_API uint32_t mf_page_pool_free_count(const MfPagePool *pool);
+MF_API uint32_t mf_page_pool_refcount(const MfPagePool *pool, uint32_t id);
+MF_API uint32_t mf_prefix_cache_default_entries(void);
+MF_API mf_status mf_prefix_cache_create(MfPagePool *pool, uint32_t page_size, uint32_t max_entries,
+                                        MfPrefixCache **out);
+/* Releases the pages its entries hold. */
+MF_API void mf_prefix_cache_destroy(MfPrefixCache *cache);
+MF_API uint32_t mf_prefix_cache_entries(const MfPrefixCache *cache);
+/* page_ids: the ceil(n_tokens / page_size) pages holding the prefix; they are retained. */
+MF_API mf_status mf_prefix_cache_store(MfPrefixCache *cache, const uint32_t *tokens, uint32_t n_tokens,
+                                       const char *key, const uint32_t *page_ids, uint32_t n_pages);
+/* On a hit *matched_out tokens are covered by the first *n_pages_out ids written to
+ * page_ids_out, each retained for the caller.  When matched % page_size != 0, or the caller
+ * will append into the last page, that page must be replaced by a private copy first
+ * (mf_page_pool_alloc + mf_paged_copy_pages + release of the shared id). */
+MF_API mf_status mf_prefix_cache_lookup(MfPrefixCache *cache, const uint32_t *prompt, uint32_t n_prompt,
+                                        const char *key, uint32_t *matched_out, uint32_t *page_ids_out,
+                                        uint32_t page_ids_cap, uint32_t *n_pages_out);
+/* Copies whole pages (all kv heads, K and V pools) dst_ids[i] <- src_ids[i]; ids are device arrays. */
+MF_API mf_status mf_paged_copy_pages(MfContext *ctx, const MfPagedKv *cache, const uint32_t *src_ids,
+                                     const uint32_t *dst_ids, uint32_t n);
+
 /* ---- sequence-sharded decode with the exchange fused into the kernels ---------------
  * No counterpart in the reference.  Instead of all-gathering (acc, m, l) with a
  * library collective, the decode kernel of every rank stores each finished unit's

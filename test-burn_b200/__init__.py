@@ -17,6 +17,8 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+
+import numpy as np
 from pathlib import Path
 
 _HERE = Path(__file__).resolve().parent
@@ -155,6 +157,20 @@ _SIGNATURES = {
     "mf_paged_gather": (C.c_int32, [vp, C.POINTER(MfPagedKv), u32, u32, u32, vp]),
     "mf_paged_decode_partial_push": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv), C.POINTER(MfPagedDecodeArgs), vp,
                                                  C.POINTER(MfPeerExchange), u32]),
+    "mf_page_pool_create": (C.c_int32, [u32, C.POINTER(vp)]),
+    "mf_page_pool_destroy": (None, [vp]),
+    "mf_page_pool_alloc": (C.c_int32, [vp, u32, vp]),
+    "mf_page_pool_retain": (C.c_int32, [vp, vp, u32]),
+    "mf_page_pool_release": (C.c_int32, [vp, vp, u32]),
+    "mf_page_pool_free_count": (u32, [vp]),
+    "mf_page_pool_refcount": (u32, [vp, u32]),
+    "mf_prefix_cache_default_entries": (u32, []),
+    "mf_prefix_cache_create": (C.c_int32, [vp, u32, u32, C.POINTER(vp)]),
+    "mf_prefix_cache_destroy": (None, [vp]),
+    "mf_prefix_cache_entries": (u32, [vp]),
+    "mf_prefix_cache_store": (C.c_int32, [vp, vp, u32, C.c_char_p, vp, u32]),
+    "mf_prefix_cache_lookup": (C.c_int32, [vp, vp, u32, C.c_char_p, C.POINTER(u32), vp, u32, C.POINTER(u32)]),
+    "mf_paged_copy_pages": (C.c_int32, [vp, C.POINTER(MfPagedKv), vp, vp, u32]),
     "mf_peer_exchange_create": (C.c_int32, [vp, u32, u32, u32, u32, C.POINTER(MfPeerExchange), vp]),
     "mf_peer_exchange_attach": (C.c_int32, [vp, C.POINTER(MfPeerExchange), u32, vp]),
     "mf_peer_exchange_destroy": (C.c_int32, [vp, C.POINTER(MfPeerExchange)]),
@@ -362,6 +378,10 @@ class Foundry:
         arr = (u32 * 8)(*list(units_per_rank) + [0] * (8 - len(units_per_rank)))
         self.check(lib.mf_merge_pushed(self._h, C.byref(px), arr, step, rows, head_dim, _ptr(out)))
 
+    def paged_copy_pages(self, cache: MfPagedKv, src_ids, dst_ids, n: int):
+        """dst page <- src page for all kv heads of both pools; ids are device int32/uint32 tensors."""
+        self.check(lib.mf_paged_copy_pages(self._h, C.byref(cache), _ptr(src_ids), _ptr(dst_ids), n))
+
     def paged_kv_append(self, cache: MfPagedKv, q, k, v, q_rot, cos, sin, *, n_heads, rope_mode=ROPE_MODE_NEOX,
                         apply_rope=True, seq=ALL_SEQUENCES, position_offset=0, seq_len=0):
         self.check(lib.mf_paged_kv_append(self._h, C.byref(cache), _ptr(q), _ptr(k), _ptr(v), _ptr(q_rot), _ptr(cos),
@@ -381,6 +401,88 @@ def flash_decode_static_scratch(stream, q, k, v, output, strides: MfFlashDecodeS
                                             _ptr(output), C.byref(strides), C.byref(params), n_heads, batch, buf, 256)
     if st != MF_OK:
         raise MetalError(st, buf.value.decode())
+
+
+class PagePool:
+    """Host-side page allocator with reference counts (mf_page_pool_*)."""
+
+    def __init__(self, n_pages: int):
+        h = vp()
+        st = lib.mf_page_pool_create(n_pages, C.byref(h))
+        if st != 0:
+            raise MetalError(st, "mf_page_pool_create")
+        self._h = h
+
+    def close(self):
+        if self._h:
+            lib.mf_page_pool_destroy(self._h)
+            self._h = None
+
+    def _check(self, st, what):
+        if st != 0:
+            raise MetalError(st, what)
+
+    def alloc(self, n: int) -> np.ndarray:
+        ids = np.empty(n, np.uint32)
+        self._check(lib.mf_page_pool_alloc(self._h, n, ids.ctypes.data_as(vp)), "page pool: not enough free pages")
+        return ids
+
+    def retain(self, ids):
+        ids = np.ascontiguousarray(ids, np.uint32)
+        self._check(lib.mf_page_pool_retain(self._h, ids.ctypes.data_as(vp), ids.size), "page pool: retain of a free page")
+
+    def release(self, ids):
+        ids = np.ascontiguousarray(ids, np.uint32)
+        self._check(lib.mf_page_pool_release(self._h, ids.ctypes.data_as(vp), ids.size), "page pool: release of a free page")
+
+    @property
+    def free_count(self) -> int:
+        return int(lib.mf_page_pool_free_count(self._h))
+
+    def refcount(self, page: int) -> int:
+        return int(lib.mf_page_pool_refcount(self._h, page))
+
+
+class PrefixCache:
+    """Prefix cache over shared pages (mf_prefix_cache_*); entry rules of src/model/executor.rs:1352-1636."""
+
+    def __init__(self, pool: PagePool, page_size: int, max_entries: int | None = None):
+        if max_entries is None:
+            max_entries = int(lib.mf_prefix_cache_default_entries())
+        h = vp()
+        st = lib.mf_prefix_cache_create(pool._h, page_size, max_entries, C.byref(h))
+        if st != 0:
+            raise MetalError(st, "mf_prefix_cache_create")
+        self._h, self.page_size, self.pool = h, page_size, pool
+
+    def close(self):
+        if self._h:
+            lib.mf_prefix_cache_destroy(self._h)
+            self._h = None
+
+    def __len__(self):
+        return int(lib.mf_prefix_cache_entries(self._h))
+
+    def store(self, tokens, page_ids, key: str | None = None):
+        tokens = np.ascontiguousarray(tokens, np.uint32)
+        page_ids = np.ascontiguousarray(page_ids, np.uint32)
+        st = lib.mf_prefix_cache_store(self._h, tokens.ctypes.data_as(vp), tokens.size,
+                                       None if key is None else key.encode(), page_ids.ctypes.data_as(vp), page_ids.size)
+        if st != 0:
+            raise MetalError(st, "prefix cache store")
+
+    def lookup(self, prompt, key: str | None = None):
+        """Returns (matched tokens, page ids retained for the caller)."""
+        prompt = np.ascontiguousarray(prompt, np.uint32)
+        cap = (prompt.size + self.page_size - 1) // self.page_size + 1
+        ids = np.empty(cap, np.uint32)
+        matched, n = u32(0), u32(0)
+        st = lib.mf_prefix_cache_lookup(self._h, prompt.ctypes.data_as(vp), prompt.size,
+                                        None if key is None else key.encode(), C.byref(matched), ids.ctypes.data_as(vp), cap,
+                                        C.byref(n))
+        if st != 0:
+            raise MetalError(st, "prefix cache lookup")
+        return int(matched.value), ids[:n.value].copy()
 
 
 class DecodePlan:

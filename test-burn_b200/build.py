@@ -26,6 +26,7 @@ SOURCES = [
     HERE / "csrc" / "attention_api.cu",
     HERE / "csrc" / "peer_exchange.cu",
     HERE / "host" / "host_logic.cpp",
+    HERE / "host" / "prefix_cache.cpp",
 ]
 HEADERS = [HERE / "csrc" / "internal.hpp", HERE / "csrc" / "ptx.cuh", ROOT / "include" / "metallic_cuda.h"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

@@ -234,6 +234,20 @@ cache_to_pages_kernel(const __half *cache, __half *pool, uint32_t heads, uint32_
         *reinterpret_cast<const uint4 *>(cache + ((size_t)h * max_seq_len + t) * head_dim + 8 * j);
 }
 
+// Whole pages of both pools, dst_ids[i] <- src_ids[i]; one thread per 16 bytes.
+__global__ void __launch_bounds__(256)
+copy_pages_kernel(uint4 *k_pool, uint4 *v_pool, const uint32_t *__restrict__ src_ids, const uint32_t *__restrict__ dst_ids,
+                  uint32_t n, uint64_t chunks_per_page)
+{
+    const uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= (uint64_t)n * chunks_per_page * 2) return;
+    const uint64_t c = gid % chunks_per_page;
+    const uint64_t pi = gid / chunks_per_page;
+    uint4 *pool = (pi & 1) ? v_pool : k_pool;
+    const uint32_t i = (uint32_t)(pi >> 1);
+    pool[(uint64_t)dst_ids[i] * chunks_per_page + c] = pool[(uint64_t)src_ids[i] * chunks_per_page + c];
+}
+
 inline uint32_t blocks_for(uint64_t threads) { return (uint32_t)((threads + 255) / 256); }
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -483,6 +497,19 @@ mf_status mf_kv_cache_to_pages(MfContext *ctx, const MfTensor *cache, const MfPa
         tensor_ptr(cache), pool, paged->n_kv_heads, paged->head_dim, len, (uint32_t)cache->dims[1],
         paged->page_table + (size_t)seq * paged->page_table_stride, paged->page_size);
     return check_launch(ctx, "cache_to_pages_kernel");
+}
+
+mf_status mf_paged_copy_pages(MfContext *ctx, const MfPagedKv *cache, const uint32_t *src_ids, const uint32_t *dst_ids,
+                              uint32_t n)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!cache || !cache->k_pool || !cache->v_pool || (n && (!src_ids || !dst_ids)))
+        return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "copy pages: null input");
+    if (n == 0) return MF_OK;
+    const uint64_t chunks = (uint64_t)cache->n_kv_heads * cache->page_size * (cache->head_dim / 8);  // 16-byte units per page
+    copy_pages_kernel<<<blocks_for((uint64_t)n * chunks * 2), 256, 0, ctx->stream>>>(
+        static_cast<uint4 *>(cache->k_pool), static_cast<uint4 *>(cache->v_pool), src_ids, dst_ids, n, chunks);
+    return check_launch(ctx, "copy_pages_kernel");
 }
 
 mf_status mf_paged_gather(MfContext *ctx, const MfPagedKv *cache, uint32_t use_v, uint32_t seq, uint32_t len, void *out)

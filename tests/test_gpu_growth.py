@@ -125,3 +125,87 @@ def test_prefix_snapshot_and_restore(mfk, foundry):
         return host(out)
 
     assert np.array_equal(decode(k2, v2, new_cap), decode(k_dev, v_dev, cap))
+
+
+def test_prefix_pages_shared_between_sequences(mfk, foundry):
+    """A cached prefix is handed to a new sequence as shared pages; only the partly filled last page
+    is copied before the new sequence appends into it.  The sharing sequence must produce the same
+    bits as one that owns private copies of the same rows, and the cached pages must stay untouched."""
+    import torch
+
+    hq, hkv, d, P, n_prefix = 16, 2, 128, 16, 40
+    n_pages = 12
+    pool = mfk.PagePool(n_pages)
+    cache = mfk.PrefixCache(pool, P)
+    rng = np.random.default_rng(11)
+    k_pool = np.full((n_pages, hkv, P, d), 0x7E00, np.uint16)  # NaN everywhere that is not written
+    v_pool = np.full((n_pages, hkv, P, d), 0x7E00, np.uint16)
+    rows_k = rng.standard_normal((hkv, n_prefix, d), dtype=np.float32).astype(np.float16).view(np.uint16)
+    rows_v = rng.standard_normal((hkv, n_prefix, d), dtype=np.float32).astype(np.float16).view(np.uint16)
+
+    def fill(pages):
+        for t in range(n_prefix):
+            k_pool[pages[t // P], :, t % P] = rows_k[:, t]
+            v_pool[pages[t // P], :, t % P] = rows_v[:, t]
+
+    tokens = rng.integers(1, 1000, size=n_prefix).astype(np.uint32)
+    a_pages = pool.alloc(3)  # the sequence that computed the prefix
+    fill(a_pages)
+    cache.store(tokens, a_pages)
+    pool.release(a_pages)  # it ends; the cache keeps the pages alive
+    assert all(pool.refcount(int(p)) == 1 for p in a_pages)
+    own_pages = pool.alloc(3)  # a sequence with private copies of the same rows
+    fill(own_pages)
+
+    dk, dv = dev(k_pool), dev(v_pool)
+    prompt = np.concatenate([tokens, np.array([5, 6], np.uint32)])
+    matched, shared = cache.lookup(prompt)
+    assert matched == n_prefix and shared.tolist() == a_pages.tolist()
+    # the new sequence will append at row 40, inside the last shared page: copy it first
+    private = pool.alloc(1)
+    desc0 = mfk.paged_kv(dk, dv, dev_u32(np.zeros((1, 1), np.uint32)), dev_u32(np.zeros(1, np.uint32)), n_kv_heads=hkv,
+                         page_size=P, head_dim=d)
+    foundry.paged_copy_pages(desc0, dev_u32(shared[-1:]), dev_u32(private), 1)
+    pool.release(shared[-1:])
+    b_pages = np.concatenate([shared[:-1], private])
+    assert pool.refcount(int(a_pages[0])) == 2 and pool.refcount(int(a_pages[2])) == 1
+
+    table = np.stack([b_pages, own_pages]).astype(np.uint32)
+    kv_lens = np.array([n_prefix + 1, n_prefix + 1], np.uint32)
+    d_table, d_lens = dev_u32(table), dev_u32(kv_lens)
+    desc = mfk.paged_kv(dk, dv, d_table, d_lens, n_kv_heads=hkv, page_size=P, head_dim=d)
+    q = rng.standard_normal((1, hq * d), dtype=np.float32).astype(np.float16).view(np.uint16).repeat(2, axis=0)
+    k = rng.standard_normal((1, hkv * d), dtype=np.float32).astype(np.float16).view(np.uint16).repeat(2, axis=0)
+    v = rng.standard_normal((1, hkv * d), dtype=np.float32).astype(np.float16).view(np.uint16).repeat(2, axis=0)
+    cos, sin = oracle.rope_tables(1e6, d, n_prefix + 1)
+    plan = foundry.decode_plan(kv_lens, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P)
+    out = torch.full((2, hq * d), float("nan"), dtype=torch.float16, device="cuda")
+    foundry.paged_decode(plan, desc, dev(q), out, n_heads=hq, k=dev(k), v=dev(v), cos=dev(cos), sin=dev(sin), rope=True,
+                         rope_mode=0, append=True)
+    foundry.synchronize()
+    plan.close()
+    got = host(out)
+    assert np.isfinite(oracle.h2f(got)).all()
+    assert np.array_equal(got[0], got[1])  # sharing changes nothing
+    kp, vp = host(dk), host(dv)
+    assert np.array_equal(kp[a_pages[2]], k_pool[a_pages[2]])  # the cached last page was not appended to
+    assert np.array_equal(vp[a_pages[2]], v_pool[a_pages[2]])
+    assert np.array_equal(kp[private[0], :, :n_prefix % P], k_pool[a_pages[2], :, :n_prefix % P])
+    assert np.array_equal(kp[private[0], :, n_prefix % P], kp[own_pages[2], :, n_prefix % P])  # the appended row
+    # the oracle on the private copy agrees within tolerance
+    zero_row = np.zeros((hkv, 1, d), np.uint16)
+    kc = np.ascontiguousarray(np.concatenate([rows_k, zero_row], axis=1))
+    vc = np.ascontiguousarray(np.concatenate([rows_v, zero_row], axis=1))
+    q_rot = oracle.kv_prep_fused(np.ascontiguousarray(q[0]), np.ascontiguousarray(k[0]), np.ascontiguousarray(v[0]), kc, vc,
+                                 cos, sin, n_heads=hq, n_kv_heads=hkv, head_dim=d, seq_len=1, position_offset=n_prefix,
+                                 max_seq_len=n_prefix + 1, rope_mode=0)
+    assert np.array_equal(kc[:, n_prefix], kp[private[0], :, n_prefix % P])  # appended rows, bit-exact
+    assert np.array_equal(vc[:, n_prefix], vp[private[0], :, n_prefix % P])
+    ref = oracle.decode_online(q_rot, kc, vc, n_heads=hq, cache_heads=hkv, head_dim=d, capacity=n_prefix + 1,
+                               kv_len=n_prefix + 1, scale=np.float32(1.0 / np.sqrt(d)))
+    assert max_abs(got[0], ref) <= 2e-3
+    pool.release(b_pages)
+    pool.release(own_pages)
+    cache.close()
+    assert pool.free_count == n_pages
+    pool.close()
