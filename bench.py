@@ -391,7 +391,9 @@ def run_long_context(args, w):
     stream = torch.cuda.Stream(device=dev)
     f = mfk.Foundry(dev.index, stream.cuda_stream)
     if not args.no_overlap:
-        f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 1)
+        # 2: the pools of a layer are written by nothing but that layer's own fused append, so every rank
+        # (not only the one that appends) may stream K/V before the previous launch has ended
+        f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 2)
     plan = f.decode_plan(lens_host, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P)
     descs = [mfk.paged_kv(k_pools[i].view(e - b, hkv, P, d), v_pools[i].view(e - b, hkv, P, d), table, d_lens,
                           n_kv_heads=hkv, page_size=P, head_dim=d) for i in range(layers)]
@@ -403,7 +405,7 @@ def run_long_context(args, w):
     scale = 1.0 / math.sqrt(d)
     append_here = rank == owner
     px, step_no = None, [0]
-    if args.exchange == "push":
+    if args.exchange in ("push", "fused"):
         # the kernels exchange the partials themselves: peer stores into every rank's receive block
         px, handle = f.peer_exchange_create(world, rank, hq, d)
         if world > 1:
@@ -428,7 +430,21 @@ def run_long_context(args, w):
                 f.merge_pushed(px, units, step_no[0], hq, d, out[i])
                 step_no[0] += 1
 
+    all_push = px is not None and all(units)
+    pusher_mask = (1 << world) - 1
+
+    def step_fused():
+        with torch.cuda.stream(stream):
+            for i in range(layers):
+                f.paged_decode_push_merge(plan, descs[i], q[i], out[i], px, step_no[0], pusher_mask, n_heads=hq,
+                                          rope_positions=d_pos, scale=scale, k=k[i] if append_here else None,
+                                          v=v[i] if append_here else None, cos=d_cos, sin=d_sin, rope=True,
+                                          rope_mode=w["rope_mode"], append=append_here)
+                step_no[0] += 1
+
     def step():
+        if args.exchange == "fused" and all_push:
+            return step_fused()
         if px is not None:
             return step_push()
         with torch.cuda.stream(stream):
@@ -492,7 +508,9 @@ def run_long_context(args, w):
         "config": {"workload": w["name"], "layers": layers, "kv_len": L, "pages_per_rank": e - b,
                    "l2": "inputs larger than L2 (KV pools %.1f GB per GPU)" % (2 * layers * pool_elems * 2 / 1e9),
                    "ctas": plan.ctas, "collective": ("none: decode kernels store %d bytes per layer into every rank's receive block "
-                                  "(peer stores + arrival counters), merge kernel waits on the counters" % (block * 4))
+                                  "(peer stores + arrival counters), " % (block * 4)
+                                  + ("and merge them themselves once every rank has delivered: one launch per layer"
+                                     if args.exchange == "fused" and all_push else "merge kernel waits on the counters"))
                    if px is not None else "ncclAllGather of %d bytes per rank per layer" % (block * 4)},
         "hbm_tb_s_per_gpu": achieved / 1e3,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -738,8 +756,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + sorted(LONG_CONTEXT) + ["c1", "c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--exchange", default="push", choices=["push", "nccl"],
-                    help="long-context workloads: partials exchanged by the kernels (peer stores) or by ncclAllGather")
+    ap.add_argument("--exchange", default="fused", choices=["fused", "push", "nccl"],
+                    help="long-context workloads: partials exchanged and merged inside the decode kernel (fused), "
+                         "exchanged by the decode kernel and merged by a second one (push), or by ncclAllGather")
     ap.add_argument("--no-overlap", action="store_true", help="plain launches instead of programmatic dependent launch")
     ap.add_argument("--prefill-impl", type=int, default=0, help="prefill kernel selector (experiments)")
     ap.add_argument("--stages", type=int, default=0, help="decode ring depth (experiments)")

@@ -238,6 +238,9 @@ MF_API uint64_t mf_launch_count(const MfContext *ctx);
  * stream has finished; the caller promises that this previous kernel does not write the
  * pools, page table or lengths the launch reads (consecutive layers of a decode step never
  * do).  Everything else a launch reads or writes still waits for the previous kernel.
+ * Value 2 extends the early streaming to launches WITHOUT a fused append (the shards of a
+ * sequence-sharded step that do not own the tail page): the caller then also promises that no
+ * separate append kernel precedes the launch in the stream.
  * MF_OPTION_DECODE_STAGES = n: depth of the decode kernel's K/V tile ring (0 = default).
  * MF_OPTION_PREFILL_IMPL: 0 = choose (tcgen05 kernel when the shape allows), 1 = mma.sync
  * kernel only, 2 = tcgen05 kernel only (like METALLIC_FA_PREFILL_* in the reference). */
@@ -491,7 +494,8 @@ MF_API mf_status mf_paged_copy_pages(MfContext *ctx, const MfPagedKv *cache, con
  * expected value and merges out of its own memory.
  *   recv[r]     rank r's receive buffer, 2 * world * rows * (head_dim + 2) floats
  *               ([step parity][source rank][acc | m | l]), mapped in this process
- *   counters[r] rank r's arrival counters, world u32, zero before the first step
+ *   counters[r] rank r's arrival counters (8 per-source totals, then one per unit), zero before
+ *               the first step
  * Steps are numbered from 0 and must be issued in the same order on every rank. */
 typedef struct MfPeerExchange {
     float *recv[8];
@@ -499,6 +503,8 @@ typedef struct MfPeerExchange {
     void *mapping[8]; /* what create / attach mapped; released by destroy */
     uint32_t world;
     uint32_t rank;
+    uint32_t rows;     /* batch * n_heads, as given to create */
+    uint32_t head_dim;
 } MfPeerExchange;
 
 #define MF_IPC_HANDLE_BYTES 64
@@ -515,6 +521,15 @@ MF_API mf_status mf_paged_decode_partial_push(MfContext *ctx, const MfDecodePlan
                                               const MfPagedKv *cache, const MfPagedDecodeArgs *args,
                                               const uint32_t *rope_positions, const MfPeerExchange *px,
                                               uint32_t step);
+/* The same with the merge inside the decode kernel too: the CTA that finishes a (sequence, kv
+ * head) unit pushes it, then waits (bounded) until every rank of pusher_mask (bit r = rank r
+ * holds keys and runs this call in this step) has pushed that unit, merges the unit's query
+ * heads out of local memory and writes args->out.  One launch per layer and rank, no second
+ * kernel.  A rank that holds no keys cannot use this form (it has nothing to launch): it calls
+ * mf_merge_pushed, and the ranks that do hold keys still push to it. */
+MF_API mf_status mf_paged_decode_push_merge(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv *cache,
+                                            const MfPagedDecodeArgs *args, const uint32_t *rope_positions,
+                                            const MfPeerExchange *px, uint32_t step, uint32_t pusher_mask);
 /* units_per_rank[r]: (batch x kv head) units rank r pushes per step (0 for a rank that
  * holds no keys); rows = batch * n_heads; out is [rows, head_dim] f16. */
 MF_API mf_status mf_merge_pushed(MfContext *ctx, const MfPeerExchange *px, const uint32_t *units_per_rank,

@@ -102,7 +102,8 @@ class MfPagedDecodeArgs(C.Structure):
 
 
 class MfPeerExchange(C.Structure):
-    _fields_ = [("recv", vp * 8), ("counters", vp * 8), ("mapping", vp * 8), ("world", u32), ("rank", u32)]
+    _fields_ = [("recv", vp * 8), ("counters", vp * 8), ("mapping", vp * 8), ("world", u32), ("rank", u32),
+                ("rows", u32), ("head_dim", u32)]
 
 
 # Every symbol declared in include/metallic_cuda.h, with its signature.
@@ -174,6 +175,8 @@ _SIGNATURES = {
     "mf_peer_exchange_create": (C.c_int32, [vp, u32, u32, u32, u32, C.POINTER(MfPeerExchange), vp]),
     "mf_peer_exchange_attach": (C.c_int32, [vp, C.POINTER(MfPeerExchange), u32, vp]),
     "mf_peer_exchange_destroy": (C.c_int32, [vp, C.POINTER(MfPeerExchange)]),
+    "mf_paged_decode_push_merge": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv), C.POINTER(MfPagedDecodeArgs), vp,
+                                               C.POINTER(MfPeerExchange), u32, u32]),
     "mf_merge_pushed": (C.c_int32, [vp, C.POINTER(MfPeerExchange), vp, u32, u32, u32, vp]),
     "mf_paged_decode_partial": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv), C.POINTER(MfPagedDecodeArgs), vp, vp, vp,
                                             vp]),
@@ -373,6 +376,16 @@ class Foundry:
 
     def peer_exchange_destroy(self, px: MfPeerExchange):
         self.check(lib.mf_peer_exchange_destroy(self._h, C.byref(px)))
+
+    def paged_decode_push_merge(self, plan, cache, q, out, px: MfPeerExchange, step: int, pusher_mask: int, *, n_heads,
+                                rope_positions=None, scale=None, k=None, v=None, cos=None, sin=None, rope=False,
+                                rope_mode=ROPE_MODE_NEOX, append=False):
+        """Sequence-sharded decode in one launch: partials pushed to every rank, merged by the same kernel."""
+        scale = 1.0 / math.sqrt(cache.head_dim) if scale is None else scale
+        a = MfPagedDecodeArgs(_ptr(q), _ptr(k), _ptr(v), None, _ptr(out), _ptr(cos), _ptr(sin), n_heads, int(rope),
+                              rope_mode, int(append), scale)
+        self.check(lib.mf_paged_decode_push_merge(self._h, plan._h, C.byref(cache), C.byref(a), _ptr(rope_positions),
+                                                  C.byref(px), step, pusher_mask))
 
     def merge_pushed(self, px: MfPeerExchange, units_per_rank, step: int, rows: int, head_dim: int, out):
         arr = (u32 * 8)(*list(units_per_rank) + [0] * (8 - len(units_per_rank)))

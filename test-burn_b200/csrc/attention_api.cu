@@ -526,13 +526,14 @@ uint64_t mf_decode_plan_tiles(const MfDecodePlan *pl) { return pl ? pl->total_ti
 
 static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, const MfPagedKv *c,
                                      const MfPagedDecodeArgs *a, const uint32_t *rope_positions, float *acc, float *m,
-                                     float *l, const MfPeerExchange *px = nullptr, uint32_t step = 0)
+                                     float *l, const MfPeerExchange *px = nullptr, uint32_t step = 0,
+                                     uint32_t merge_mask = 0)
 {
     if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
     if (!pl || !c || !a) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode: null argument");
     if (!c->k_pool || !c->v_pool || !c->page_table || !c->kv_lens || !a->q)
         return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode: null tensor");
-    if (!acc && !a->out && !px) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode: output");
+    if (!acc && !a->out && !(px && !merge_mask)) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode: output");
     if (a->append && (!a->k || !a->v)) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode: k/v of the new token");
     if (a->rope && (!a->cos || !a->sin)) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode: cos/sin");
     if (a->rope_mode > 1) return fail(ctx, MF_ERR_INVALID_OPERATION, "paged decode: rope_mode %u", a->rope_mode);
@@ -585,7 +586,9 @@ static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, con
     p.scale_log2 = a->scale * 1.4426950408889634f;
     // With overlapped launches the tile stream may start early only when this launch does the
     // append itself: then no kernel right before it can have written the pages it reads.
-    p.early_stream = (ctx->overlap_launches && a->append) ? 1u : 0u;
+    // Streaming K/V ahead of the previous kernel's end is safe when nothing earlier in the stream writes
+    // these pools: with the fused append this call is the only writer; without it the caller says so (2).
+    p.early_stream = ((ctx->overlap_launches && a->append) || ctx->overlap_launches == 2) ? 1u : 0u;
     if (px) {
         if (px->world == 0 || px->world > 8 || px->rank >= px->world)
             return fail(ctx, MF_ERR_INVALID_OPERATION, "peer exchange: rank %u of %u", px->rank, px->world);
@@ -595,6 +598,20 @@ static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, con
             if (!px->recv[r] || !px->counters[r]) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "peer exchange: rank %u buffers", r);
             p.push_dst[r] = px->recv[r] + ((uint64_t)(step & 1) * px->world + px->rank) * block;
             p.push_cnt[r] = px->counters[r] + px->rank;
+            p.push_unit_cnt[r] = px->counters[r] + 8;
+        }
+        if ((uint64_t)c->batch * a->n_heads != px->rows || D != px->head_dim)
+            return fail(ctx, MF_ERR_INVALID_SHAPE, "peer exchange was created for %u rows x %u, this call has %llu x %u",
+                        px->rows, px->head_dim, (unsigned long long)c->batch * a->n_heads, D);
+        if (merge_mask) {
+            if (!(merge_mask >> px->rank & 1u) || (merge_mask >> px->world))
+                return fail(ctx, MF_ERR_INVALID_OPERATION, "pusher mask 0x%x does not fit rank %u of %u", merge_mask, px->rank,
+                            px->world);
+            p.push_merge = 1;
+            p.push_mask = merge_mask;
+            p.push_expected = (uint32_t)__builtin_popcount(merge_mask) * (step + 1);
+            p.push_local = px->recv[px->rank] + (uint64_t)(step & 1) * px->world * block;
+            p.push_local_cnt = px->counters[px->rank] + 8;
         }
     }
     CUtensorMap tm_k, tm_v;
@@ -623,6 +640,16 @@ mf_status mf_paged_decode_partial_push(MfContext *ctx, const MfDecodePlan *plan,
 {
     if (ctx && !px) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "peer exchange");
     return paged_decode_common(ctx, plan, cache, args, rope_positions, nullptr, nullptr, nullptr, px, step);
+}
+
+mf_status mf_paged_decode_push_merge(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv *cache,
+                                     const MfPagedDecodeArgs *args, const uint32_t *rope_positions,
+                                     const MfPeerExchange *px, uint32_t step, uint32_t pusher_mask)
+{
+    if (ctx && !px) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "peer exchange");
+    if (ctx && !pusher_mask) return fail(ctx, MF_ERR_INVALID_OPERATION, "empty pusher mask");
+    if (ctx && args && !args->out) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "push merge: output");
+    return paged_decode_common(ctx, plan, cache, args, rope_positions, nullptr, nullptr, nullptr, px, step, pusher_mask);
 }
 
 mf_status mf_paged_decode_partial(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv *cache,

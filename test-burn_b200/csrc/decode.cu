@@ -130,6 +130,84 @@ __device__ __forceinline__ void rope_pair(float xi, float xj, float c, float s, 
     oj = __float2half_rn(__fadd_rn(__fmul_rn(xj, c), __fmul_rn(xi, s)));
 }
 
+// Sequence-sharded decode, end of a unit: announce the block this CTA has just stored into every
+// rank's receive buffer; with push_merge also wait (bounded) until every pushing rank has delivered
+// the same unit, merge the unit's query heads out of local memory (flash_prefill.metal:843-888)
+// and write the output rows.  Called by all consumer threads.
+template <int D>
+__device__ __forceinline__ void push_signal_and_merge(const DecodeParams &p, const WorkItem &it, uint32_t tid,
+                                                      volatile uint32_t *flags)
+{
+    // every peer sees this unit's block before its counters move
+    __threadfence_system();
+    named_bar_sync(1, kConsumerThreads);
+    if (tid < p.push_world) {
+        atomicAdd_system(p.push_cnt[tid], 1u);
+        atomicAdd_system(p.push_unit_cnt[tid] + it.unit, 1u);
+    }
+    if (!p.push_merge) return;
+    // push_local_cnt is this rank's own counter array: the wait polls local memory, never NVLink
+    if (tid == 0) {
+        uint32_t good = 1, spins = 0;
+        const long long t0 = clock64();
+        for (;;) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.push_local_cnt + it.unit) : "memory");
+            if ((int32_t)(v - p.push_expected) >= 0) break;
+            if ((++spins & 0x3Fu) == 0 && clock64() - t0 > 4000000000ll) {
+                good = 0;
+                atomicOr(p.status, 2048u);
+                break;
+            }
+        }
+        flags[1] = good;
+    }
+    named_bar_sync(2, kConsumerThreads);
+    if (!flags[1]) return;
+    const uint32_t G = p.group;
+    const size_t rows = (size_t)p.batch * p.n_heads;
+    const size_t block = rows * (D + 2);
+    const uint32_t cols4 = G * (D / 4);
+    for (uint32_t c4 = tid; c4 < cols4; c4 += kConsumerThreads) {
+        const uint32_t g2 = c4 / (D / 4), d0 = (c4 % (D / 4)) * 4;
+        const uint32_t h = it.kvh * G + g2;
+        const size_t rowi = (size_t)it.seq * p.n_heads + h;
+        float mr[8], lr[8];
+        float mx = kNegSentinel;
+#pragma unroll
+        for (uint32_t r = 0; r < 8; ++r) {
+            if (r < p.push_world && (p.push_mask >> r & 1u)) {
+                mr[r] = __ldcg(p.push_local + r * block + rows * D + rowi);
+                lr[r] = __ldcg(p.push_local + r * block + rows * D + rows + rowi);
+                mx = fmaxf(mx, mr[r]);
+            } else {
+                mr[r] = kNegSentinel;
+                lr[r] = 0.f;
+            }
+        }
+        float lt = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (uint32_t r = 0; r < 8; ++r) {
+            if (r < p.push_world && (p.push_mask >> r & 1u)) {
+                const float w = __expf(mr[r] - mx);
+                if (lr[r] > 0.f) lt += lr[r] * w;
+                const float4 a = __ldcg(reinterpret_cast<const float4 *>(p.push_local + r * block + rowi * D + d0));
+                acc.x += a.x * w;
+                acc.y += a.y * w;
+                acc.z += a.z * w;
+                acc.w += a.w * w;
+            }
+        }
+        const float inv = ((fabsf(lt) <= 3.0e38f) && fabsf(lt) > 1e-6f) ? 1.0f / lt : 0.f;
+        __half *dst = p.out + (size_t)it.seq * p.out_stride_b + (size_t)h * p.out_stride_h + d0;
+        dst[0] = __float2half_rn(acc.x * inv);
+        dst[1] = __float2half_rn(acc.y * inv);
+        dst[2] = __float2half_rn(acc.z * inv);
+        dst[3] = __float2half_rn(acc.w * inv);
+    }
+}
+
 template <int D, int NT, int STAGES, int MINB>
 __global__ void __launch_bounds__(kThreads, MINB)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -563,12 +641,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             if (hp == 0) named_bar_sync(1, kConsumerThreads);  // pass 1 reuses the buffer
         }
         if (direct) {
-            if (p.push_world) {
-                // every peer sees this unit's block before its counter moves
-                __threadfence_system();
-                named_bar_sync(1, kConsumerThreads);
-                if (tid < p.push_world) atomicAdd_system(p.push_cnt[tid], 1u);
-            }
+            if (p.push_world) push_signal_and_merge<D>(p, it, tid, flags);
             continue;
         }
 
@@ -666,11 +739,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                 }
             }
         }
-        if (p.push_world) {
-            __threadfence_system();
-            named_bar_sync(1, kConsumerThreads);
-            if (tid < p.push_world) atomicAdd_system(p.push_cnt[tid], 1u);
-        }
+        if (p.push_world) push_signal_and_merge<D>(p, it, tid, flags);
     }
 }
 

@@ -66,6 +66,13 @@ struct DecodeParams {
     uint32_t push_world;     // 0 = off
     float *push_dst[8];      // rank r's receive block for THIS rank and step parity, as mapped here
     uint32_t *push_cnt[8];   // rank r's arrival counter for THIS rank
+    uint32_t *push_unit_cnt[8];  // rank r's per-unit arrival counters
+    // Merge inside the kernel: after pushing a unit, wait for the ranks of push_mask and write `out`.
+    uint32_t push_merge;     // 0 = the caller merges with a second kernel
+    uint32_t push_mask;      // ranks that push in this step
+    uint32_t push_expected;  // value the unit counter reaches when all of them have
+    const float *push_local; // this rank's receive blocks of this step parity: [world][block]
+    const uint32_t *push_local_cnt;  // this rank's per-unit arrival counters
     float scale_log2;
 };
 

@@ -9,7 +9,9 @@
 namespace mf {
 namespace {
 
-constexpr size_t kCounterBytes = 256;  // world <= 8 arrival counters, padded so the floats stay aligned
+// Counter region in front of the receive blocks: 8 per-source totals, then one counter per unit
+// (units <= rows), padded so that the floats stay 256-byte aligned.
+inline size_t counter_bytes(uint32_t rows) { return ((size_t)(8 + rows) * 4 + 255) & ~(size_t)255; }
 
 struct PushedMergeArgs {
     const float *gather;       // this rank's receive buffer, parity already applied: [world][block]
@@ -91,7 +93,7 @@ mf_status mf_peer_exchange_create(MfContext *ctx, uint32_t world, uint32_t rank,
     if (world == 0 || world > 8 || rank >= world || rows == 0 || head_dim == 0)
         return fail(ctx, MF_ERR_INVALID_OPERATION, "peer exchange: rank %u of %u, %u rows x %u", rank, world, rows, head_dim);
     memset(px, 0, sizeof(*px));
-    const size_t bytes = kCounterBytes + (size_t)2 * world * rows * (head_dim + 2) * sizeof(float);
+    const size_t bytes = counter_bytes(rows) + (size_t)2 * world * rows * (head_dim + 2) * sizeof(float);
     void *base = nullptr;
     mf_status st = check_cuda(ctx, cudaMalloc(&base, bytes), "peer exchange: cudaMalloc");
     if (st != MF_OK) return st;
@@ -107,9 +109,11 @@ mf_status mf_peer_exchange_create(MfContext *ctx, uint32_t world, uint32_t rank,
     }
     px->world = world;
     px->rank = rank;
+    px->rows = rows;
+    px->head_dim = head_dim;
     px->mapping[rank] = base;
     px->counters[rank] = static_cast<uint32_t *>(base);
-    px->recv[rank] = reinterpret_cast<float *>(static_cast<char *>(base) + kCounterBytes);
+    px->recv[rank] = reinterpret_cast<float *>(static_cast<char *>(base) + counter_bytes(rows));
     return MF_OK;
 }
 
@@ -127,7 +131,7 @@ mf_status mf_peer_exchange_attach(MfContext *ctx, MfPeerExchange *px, uint32_t p
     if (st != MF_OK) return st;
     px->mapping[peer] = base;
     px->counters[peer] = static_cast<uint32_t *>(base);
-    px->recv[peer] = reinterpret_cast<float *>(static_cast<char *>(base) + kCounterBytes);
+    px->recv[peer] = reinterpret_cast<float *>(static_cast<char *>(base) + counter_bytes(px->rows));
     return MF_OK;
 }
 

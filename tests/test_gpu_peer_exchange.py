@@ -71,6 +71,16 @@ def test_pushed_partials_two_shards_one_gpu(mfk, foundry, overlap):
         for o in outs:
             assert np.array_equal(host(o), host(want))
             assert max_abs(host(o), out_ref) <= TOL and max_abs(host(o), gold.ravel()) <= TOL
+    # the one-launch form with a single pusher (a second rank's kernel could not run beside it on
+    # this one GPU): pusher mask = this shard only, so the result is the shard's own normalised partial
+    for r, (desc, plan, _) in enumerate(parts):
+        solo = torch.full((Hq, D), float("nan"), dtype=torch.float16, device="cuda")
+        foundry.paged_decode_push_merge(plan, desc, q_rot, solo, pxs[r], 3, 1 << r, n_heads=Hq, scale=float(full.scale))
+        foundry.synchronize()
+        one = torch.empty((Hq, D), dtype=torch.float16, device="cuda")
+        foundry.merge_partials(accs[r:r + 1], ms[r:r + 1], ls[r:r + 1], one)
+        foundry.synchronize()
+        assert np.array_equal(host(solo), host(one))
     foundry.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 0)
     for (_, plan, _) in parts:
         plan.close()
@@ -139,8 +149,12 @@ def _two_gpu_worker(rank, world, port, ret):
         for step in range(6):
             f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, step // 3)
             out = torch.full((Hq, D), float("nan"), dtype=torch.float16, device="cuda")
-            f.paged_decode_partial_push(plan, desc, q_rot, px, step, n_heads=Hq, scale=float(full.scale))
-            f.merge_pushed(px, [Hkv] * world, step, Hq, D, out)
+            if step % 2 == 0:  # two launches: push, then the waiting merge kernel
+                f.paged_decode_partial_push(plan, desc, q_rot, px, step, n_heads=Hq, scale=float(full.scale))
+                f.merge_pushed(px, [Hkv] * world, step, Hq, D, out)
+            else:              # one launch: the decode kernel also waits for the peers and merges
+                f.paged_decode_push_merge(plan, desc, q_rot, out, px, step, (1 << world) - 1, n_heads=Hq,
+                                          scale=float(full.scale))
             f.synchronize()
             ok = ok and max_abs(host(out), out_ref) <= TOL and max_abs(host(out), gold.ravel()) <= TOL
         plan.close()
