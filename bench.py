@@ -221,12 +221,18 @@ def run_ours(args, w):
     # table, lengths and work plan are rebuilt from host state each step as a serving loop would; per
     # layer the q/k/v rows go up and the attention output comes back; the KV pools are cache state
     # and stay resident.  Uploads and downloads run on copy streams, ordered by events.
-    e2e_q = torch.empty((2, B, hq * d), dtype=torch.float16, device=dev)
-    e2e_k = torch.empty((2, B, hkv * d), dtype=torch.float16, device=dev)
-    e2e_v = torch.empty((2, B, hkv * d), dtype=torch.float16, device=dev)
+    # q, k and v rows of a layer travel as ONE pinned block and one copy
+    nq, nk = B * hq * d, B * hkv * d
+    h_qkv = torch.empty((layers, nq + 2 * nk), dtype=torch.float16).pin_memory()
+    h_qkv[:, :nq] = h_q.view(layers, -1)
+    h_qkv[:, nq:nq + nk] = h_k.view(layers, -1)
+    h_qkv[:, nq + nk:] = h_v.view(layers, -1)
+    e2e_qkv = torch.empty((2, nq + 2 * nk), dtype=torch.float16, device=dev)
+    e2e_q = [e2e_qkv[s, :nq].view(B, hq * d) for s in range(2)]
+    e2e_k = [e2e_qkv[s, nq:nq + nk].view(B, hkv * d) for s in range(2)]
+    e2e_v = [e2e_qkv[s, nq + nk:].view(B, hkv * d) for s in range(2)]
     e2e_out = torch.empty((2, B, hq * d), dtype=torch.float16, device=dev)
     ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_free = [torch.cuda.Event() for _ in range(2)]
     ev_done = [torch.cuda.Event() for _ in range(2)]
     ev_out_free = [torch.cuda.Event() for _ in range(2)]
 
@@ -238,16 +244,13 @@ def run_ours(args, w):
         for i in range(layers):
             s = i & 1
             with torch.cuda.stream(copy_in):
-                copy_in.wait_event(ev_free[s])
-                e2e_q[s].copy_(h_q[i], non_blocking=True)
-                e2e_k[s].copy_(h_k[i], non_blocking=True)
-                e2e_v[s].copy_(h_v[i], non_blocking=True)
+                copy_in.wait_event(ev_done[s])  # the launch that read this slot two layers ago
+                e2e_qkv[s].copy_(h_qkv[i], non_blocking=True)
                 ev_in[s].record(copy_in)
             stream.wait_event(ev_in[s])
             stream.wait_event(ev_out_free[s])
             f.paged_decode(plan, descs[i], e2e_q[s], e2e_out[s], n_heads=hq, k=e2e_k[s], v=e2e_v[s], cos=d_cos,
                            sin=d_sin, rope=True, rope_mode=w["rope_mode"], append=True, scale=scale)
-            ev_free[s].record(stream)
             ev_done[s].record(stream)
             with torch.cuda.stream(copy_out):
                 copy_out.wait_event(ev_done[s])
