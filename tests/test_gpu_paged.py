@@ -260,3 +260,47 @@ def test_overlapped_launches_give_the_same_bits(mfk, foundry):
         assert np.array_equal(a, b)
     ref = cases[0].oracle_step()
     assert max_abs(results[1][0], ref[3]) <= TOL
+
+
+def test_decode_chain_replays_from_a_cuda_graph(mfk):
+    """A chain of fused launches (two layers sharing one plan) is captured once into a CUDA graph and
+    replayed: the replay must give the bits of the eager chain.  The first (eager) pass also does the
+    one-time work that does not belong inside a capture (function attributes, tensor-map encoding)."""
+    import torch
+
+    case = PagedCase(batch=5, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[300, 17, 2049, 64, 1000])
+    ref = case.oracle_step()
+    stream = torch.cuda.Stream()
+    f = mfk.Foundry(0, stream.cuda_stream)
+    f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 1)
+    layers = [DeviceCase(mfk, case) for _ in range(2)]
+    plan = f.decode_plan(case.kv_lens, n_heads=case.Hq, n_kv_heads=case.Hkv, head_dim=case.D, page_size=case.P)
+    outs = [torch.full((case.B, case.Hq * case.D), float("nan"), dtype=torch.float16, device="cuda") for _ in range(2)]
+
+    def chain():
+        for dc, out in zip(layers, outs):
+            f.paged_decode(plan, dc.desc, dc.q, out, n_heads=case.Hq, k=dc.k, v=dc.v, cos=dc.cos, sin=dc.sin, rope=True,
+                           rope_mode=case.rope_mode, append=True, scale=float(case.scale))
+
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        chain()
+    f.synchronize()
+    eager = [host(o).copy() for o in outs]
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        chain()
+    for o in outs:
+        o.fill_(float("nan"))
+    torch.cuda.synchronize()
+    for _ in range(2):
+        graph.replay()
+    torch.cuda.synchronize()
+    f.synchronize()  # reads the device status word
+    for o, e in zip(outs, eager):
+        assert np.array_equal(host(o), e)
+        assert max_abs(host(o), ref[3]) <= TOL
+    for dc in layers:
+        assert np.array_equal(host(dc.k_pool), ref[1]) and np.array_equal(host(dc.v_pool), ref[2])
+    plan.close()
+    f.close()
