@@ -180,7 +180,7 @@ typedef struct MfFlashAttentionArgs {
 } MfFlashAttentionArgs;
 
 /* Which route the dispatcher took (for tests and logging). */
-enum { MF_ROUTE_DECODE = 1, MF_ROUTE_PREFILL = 2, MF_ROUTE_PREFILL_SPLITK = 3 };
+enum { MF_ROUTE_DECODE = 1, MF_ROUTE_PREFILL = 2, MF_ROUTE_PREFILL_SPLITK = 3, MF_ROUTE_REFERENCE = 4 };
 
 /* ----------------------------------------------------------- paged KV cache ---
  * Not in the reference (its cache is contiguous only).  Pool layout per layer,
@@ -314,10 +314,20 @@ MF_API mf_status mf_kv_cache_read(MfContext *ctx, const MfTensor *cache, const M
 MF_API mf_status mf_kv_cache_grow(MfContext *ctx, const MfTensor *old_cache, const MfTensor *new_cache,
                                   uint32_t current_pos);
 
-/* "FlashAttention" (src/metals/sdpa/step.rs:160-503): the dispatcher.  m == 1
- * routes to decode, m > 1 (causal, query_offset + m == kv_seq_len) to prefill;
- * anything else returns MF_ERR_OPERATION_NOT_SUPPORTED (the reference falls back
- * to its materialised path there).  route_out may be NULL. */
+/* "FlashAttention" (src/metals/sdpa/step.rs:160-503): the dispatcher.  m == 1 with
+ * query_offset + 1 == kv_seq_len routes to decode, m > 1 (causal, query_offset + m ==
+ * kv_seq_len) to prefill; anything else (non-causal, or an offset that breaks the causal
+ * invariant) takes mf_sdpa_reference, as the reference falls back to its materialised
+ * path there (MF_ROUTE_REFERENCE).  route_out may be NULL. */
+/* "SdpaReference" (src/metals/sdpa/step.rs:89-158, execute_sdpa_reference :558-779,
+ * softmax_sdpa_batched.metal:14-115): attention with the general mask, key i hidden from query
+ * row r iff causal and i > r + query_offset; q and output layouts as in the prefill route.
+ * The reference stores S and P as f16 scratch [Hq, m, kv_seq_len] and has no GQA map; here the
+ * tiled kernels compute the same rows without scratch, with f32 softmax, and map query heads
+ * to cache heads by the stride ratio like every other route. */
+MF_API mf_status mf_sdpa_reference(MfContext *ctx, const MfTensor *q, const MfTensor *k, const MfTensor *v,
+                                   const MfTensor *output, const MfFlashAttentionArgs *args);
+
 MF_API mf_status mf_flash_attention(MfContext *ctx, const MfTensor *q, const MfTensor *k,
                                     const MfTensor *v, const MfTensor *output,
                                     const MfFlashAttentionArgs *args, uint32_t *route_out);

@@ -35,7 +35,7 @@ MF_OK = 0
 STATUS_NAMES = {0: "Ok", 1: "OperationNotSupported", 2: "InvalidShape", 3: "InvalidOperation", 4: "InputNotFound",
                 5: "UnsupportedDtype", 6: "OutOfMemory", 7: "CudaError", 8: "NcclError", 9: "Timeout"}
 ROPE_MODE_NEOX, ROPE_MODE_NORMAL = 0, 1
-ROUTE_DECODE, ROUTE_PREFILL, ROUTE_PREFILL_SPLITK = 1, 2, 3
+ROUTE_DECODE, ROUTE_PREFILL, ROUTE_PREFILL_SPLITK, ROUTE_REFERENCE = 1, 2, 3, 4
 DTYPE_F16, DTYPE_F32, DTYPE_U32 = 0, 1, 2
 ALL_SEQUENCES = 0xFFFFFFFF
 OPTION_OVERLAP_LAUNCHES = 1
@@ -133,6 +133,7 @@ _SIGNATURES = {
     "mf_kv_cache_read": (C.c_int32, [vp, C.POINTER(MfTensor), C.POINTER(MfTensor), u32]),
     "mf_kv_cache_grow": (C.c_int32, [vp, C.POINTER(MfTensor), C.POINTER(MfTensor), u32]),
     "mf_kv_cache_to_pages": (C.c_int32, [vp, C.POINTER(MfTensor), C.POINTER(MfPagedKv), u32, u32, u32]),
+    "mf_sdpa_reference": (C.c_int32, [vp] + [C.POINTER(MfTensor)] * 4 + [C.POINTER(MfFlashAttentionArgs)]),
     "mf_flash_attention": (C.c_int32, [vp] + [C.POINTER(MfTensor)] * 4 + [C.POINTER(MfFlashAttentionArgs),
                                                                          C.POINTER(u32)]),
     "mf_run_flash_decode": (C.c_int32, [vp] + [C.POINTER(MfTensor)] * 4 + [u32] * 5),
@@ -298,6 +299,15 @@ class Foundry:
         self.check(lib.mf_flash_attention(self._h, C.byref(tq), C.byref(tk), C.byref(tv), C.byref(to), C.byref(args),
                                           C.byref(route)))
         return route.value
+
+    def sdpa_reference(self, q, k, v, output, *, causal, query_offset, n_heads, head_dim, kv_seq_len, m=1, q_meta=None,
+                       out_meta=None):
+        """SdpaReferenceStep (src/metals/sdpa/step.rs:89-158): attention with the general mask."""
+        args = MfFlashAttentionArgs(int(causal), query_offset, n_heads, head_dim, kv_seq_len, m, 1)
+        tq = tensor_arg(q, *(q_meta or (None, None)))
+        to = tensor_arg(output, *(out_meta or (None, None)))
+        tk, tv = tensor_arg(k), tensor_arg(v)
+        self.check(lib.mf_sdpa_reference(self._h, C.byref(tq), C.byref(tk), C.byref(tv), C.byref(to), C.byref(args)))
 
     def run_flash_decode(self, q, k, v, output, n_heads, head_dim, kv_seq_len, q_seq_len=1, kv_head_major=True,
                          q_meta=None, out_meta=None):

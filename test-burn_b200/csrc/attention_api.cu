@@ -218,9 +218,12 @@ mf_status mf_flash_prefill(MfContext *ctx, const void *q, const void *k, const v
 }
 
 // run_flash_decode (src/metals/flashattention/step.rs:558-1086).
-mf_status mf_run_flash_decode(MfContext *ctx, const MfTensor *q, const MfTensor *k, const MfTensor *v,
-                              const MfTensor *output, uint32_t n_heads, uint32_t head_dim, uint32_t kv_seq_len,
-                              uint32_t q_seq_len, uint32_t kv_head_major)
+// general_offset < 0: the reference's flash routes (decode for one row, causal prefill with
+// query_offset = kv_len - q_len).  general_offset >= 0: the tiled kernels with that visibility rule
+// (key k visible to row r iff k <= r + general_offset), also for one row.
+static mf_status run_flash_decode_impl(MfContext *ctx, const MfTensor *q, const MfTensor *k, const MfTensor *v,
+                                       const MfTensor *output, uint32_t n_heads, uint32_t head_dim, uint32_t kv_seq_len,
+                                       uint32_t q_seq_len, uint32_t kv_head_major, int64_t general_offset)
 {
     if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
     mf_status st;
@@ -239,7 +242,7 @@ mf_status mf_run_flash_decode(MfContext *ctx, const MfTensor *q, const MfTensor 
     // n_kv_heads from the cache tensor (step.rs:430-446).
     const uint32_t n_kv_heads = std::max<uint32_t>(1, (uint32_t)(k->rank == 3 ? k->dims[0] : k->dims[1]));
 
-    if (q_seq_len > 1) {
+    if (q_seq_len > 1 || general_offset >= 0) {
         if (D != 64 && D != 128)
             return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "Prefill only supports head_dim=64 or 128, got %u", D);
         if ((st = last_contig(q, "q")) != MF_OK) return st;
@@ -309,7 +312,7 @@ mf_status mf_run_flash_decode(MfContext *ctx, const MfTensor *q, const MfTensor 
             b.v_stride_h = (uint32_t)v->strides[0];
             b.stride_v_s = (uint32_t)v->strides[1];
         }
-        b.query_offset = kv_seq_len > q_seq_len ? kv_seq_len - q_seq_len : 0;
+        b.query_offset = general_offset >= 0 ? (uint32_t)general_offset : (kv_seq_len > q_seq_len ? kv_seq_len - q_seq_len : 0);
         b.q_stride_b = ql.stride_b;
         b.q_stride_h = ql.stride_h;
         b.q_stride_m = ql.stride_m;
@@ -342,6 +345,27 @@ mf_status mf_run_flash_decode(MfContext *ctx, const MfTensor *q, const MfTensor 
                              0, nullptr, nullptr, nullptr);
 }
 
+mf_status mf_run_flash_decode(MfContext *ctx, const MfTensor *q, const MfTensor *k, const MfTensor *v,
+                              const MfTensor *output, uint32_t n_heads, uint32_t head_dim, uint32_t kv_seq_len,
+                              uint32_t q_seq_len, uint32_t kv_head_major)
+{
+    return run_flash_decode_impl(ctx, q, k, v, output, n_heads, head_dim, kv_seq_len, q_seq_len, kv_head_major, -1);
+}
+
+// SdpaReferenceStep (src/metals/sdpa/step.rs:89-158, 558-779): attention for the cases the flash routes
+// refuse.  The reference materialises S and P in f16 scratch; here the same result comes from the tiled
+// kernels with the general visibility rule, without scratch and with f32 softmax.
+mf_status mf_sdpa_reference(MfContext *ctx, const MfTensor *q, const MfTensor *k, const MfTensor *v,
+                            const MfTensor *output, const MfFlashAttentionArgs *a)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!a) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "SdpaReference: args");
+    if (a->kv_seq_len == 0) return MF_OK;
+    // mask rule of softmax_sdpa_batched.metal:25-37: causal hides keys i > row + query_offset
+    const int64_t offset = a->causal ? (int64_t)a->query_offset : (int64_t)a->kv_seq_len;
+    return run_flash_decode_impl(ctx, q, k, v, output, a->n_heads, a->head_dim, a->kv_seq_len, std::max(1u, a->m), 1, offset);
+}
+
 // FlashAttentionStep dispatcher (src/metals/sdpa/step.rs:160-503).
 mf_status mf_flash_attention(MfContext *ctx, const MfTensor *q, const MfTensor *k, const MfTensor *v,
                              const MfTensor *output, const MfFlashAttentionArgs *a, uint32_t *route_out)
@@ -359,11 +383,11 @@ mf_status mf_flash_attention(MfContext *ctx, const MfTensor *q, const MfTensor *
         return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "FlashAttention only supports kv_head_major=true for now");
     if (m == 1) {
         // Online path only when nothing has to be masked (sdpa/step.rs:271).
-        if (a->causal && a->query_offset + 1 != a->kv_seq_len)
-            return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED,
-                        "FlashAttention m=1 but causal offset mismatch (query_offset %u, kv_seq_len %u): the reference "
-                        "takes its materialised path here, which this library does not provide",
-                        a->query_offset, a->kv_seq_len);
+        if (a->causal && a->query_offset + 1 != a->kv_seq_len) {
+            // "FlashAttention m=1 but causal offset mismatch; falling back" (sdpa/step.rs:271-303)
+            if (route_out) *route_out = MF_ROUTE_REFERENCE;
+            return mf_sdpa_reference(ctx, q, k, v, output, a);
+        }
         // Token-major row check (sdpa/step.rs:305-349).
         const uint64_t dm = (uint64_t)a->n_heads * a->head_dim;
         auto row_ok = [&](const MfTensor *t) {
@@ -377,11 +401,11 @@ mf_status mf_flash_attention(MfContext *ctx, const MfTensor *q, const MfTensor *
         if (route_out) *route_out = MF_ROUTE_DECODE;
         return mf_run_flash_decode(ctx, q, k, v, output, a->n_heads, a->head_dim, a->kv_seq_len, 1, a->kv_head_major);
     }
-    if (!a->causal)
-        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "FlashAttention prefill non-causal: materialised path not provided");
-    if (a->query_offset + m != a->kv_seq_len)
-        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "FlashAttention prefill causal offset mismatch (query_offset %u + m %u != kv_seq_len %u)",
-                    a->query_offset, m, a->kv_seq_len);
+    if (!a->causal || a->query_offset + m != a->kv_seq_len) {
+        // non-causal, or the causal invariant does not hold: the reference falls back (sdpa/step.rs:442-470)
+        if (route_out) *route_out = MF_ROUTE_REFERENCE;
+        return mf_sdpa_reference(ctx, q, k, v, output, a);
+    }
     if (route_out)
         *route_out = effective_prefill_split_k(ctx, a->kv_seq_len, m, a->n_heads) > 1 ? MF_ROUTE_PREFILL_SPLITK
                                                                                       : MF_ROUTE_PREFILL;

@@ -150,9 +150,14 @@ def test_flash_attention_dispatcher(mfk, foundry):
         foundry.flash_attention(q, k, v, out, causal=True, query_offset=99, n_heads=14, head_dim=64, kv_seq_len=100,
                                 kv_head_major=False)
     assert e.value.kind == "OperationNotSupported"
-    with pytest.raises(mfk.MetalError) as e:  # causal decode with a masked tail: reference falls back
-        foundry.flash_attention(q, k, v, out, causal=True, query_offset=50, n_heads=14, head_dim=64, kv_seq_len=100)
-    assert e.value.kind == "OperationNotSupported"
+    # causal decode with a masked tail: the reference falls back to SdpaReference (sdpa/step.rs:271-303);
+    # only keys 0..50 are visible
+    route = foundry.flash_attention(q, k, v, out, causal=True, query_offset=50, n_heads=14, head_dim=64, kv_seq_len=100)
+    foundry.synchronize()
+    assert route == mfk.ROUTE_REFERENCE
+    masked = oracle.decode_online(q_rot, kc, vc, n_heads=14, cache_heads=2, head_dim=64, capacity=128, kv_len=51,
+                                  scale=case.scale)
+    assert max_abs(host(out).ravel(), masked) <= TOL
     with pytest.raises(mfk.MetalError) as e:  # head_dim 96
         foundry.flash_attention(dev(q_rot[:96 * 14]).view(1, -1), k, v, out[:, :96 * 14].contiguous(), causal=True,
                                 query_offset=99, n_heads=14, head_dim=96, kv_seq_len=100)

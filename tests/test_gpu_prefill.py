@@ -101,15 +101,19 @@ def test_prefill_through_kv_prep_and_dispatcher(mfk, foundry):
     got = host(out)[0, :m]
     assert max_abs(got, ref) <= TOL and max_abs(got, gold) <= TOL
     assert not host(out)[0, m:].any()  # rows past q_len are not written
-    with pytest.raises(mfk.MetalError) as e:  # causal invariant broken -> the reference falls back
-        foundry.flash_attention(q_rot, kc, vc, out, causal=True, query_offset=cached + 1, n_heads=hq, head_dim=d,
-                                kv_seq_len=cached + m, m=m)
-    assert e.value.kind == "OperationNotSupported"
-    with pytest.raises(mfk.MetalError) as e:
-        foundry.flash_attention(q_rot, kc, vc, out, causal=False, query_offset=cached, n_heads=hq, head_dim=d,
-                                kv_seq_len=cached + m, m=m)
-    assert e.value.kind == "OperationNotSupported"
-    foundry.synchronize()
+    # causal invariant broken, or non-causal: the reference falls back to SdpaReference (sdpa/step.rs:442-470)
+    for causal, offset in ((True, cached + 1), (True, cached - 3), (False, cached)):
+        out.zero_()
+        route = foundry.flash_attention(q_rot, kc, vc, out, causal=causal, query_offset=offset, n_heads=hq, head_dim=d,
+                                        kv_seq_len=cached + m, m=m)
+        foundry.synchronize()
+        assert route == mfk.ROUTE_REFERENCE
+        args = dict(n_heads=hq, cache_heads=hkv, head_dim=d, capacity=cap, q_len=m, kv_len=cached + m,
+                    query_offset=offset if causal else cached + m, scale=case.scale)
+        want = oracle.prefill_causal(q_ref, kc_ref, vc_ref, **args)
+        gold_g = oracle.prefill_gold(q_ref, kc_ref, vc_ref, **args)
+        got = host(out)[0, :m]
+        assert max_abs(got, want) <= TOL and max_abs(got, gold_g) <= TOL
 
 
 def test_prefill_split_k_heuristic_route(mfk, foundry):
