@@ -301,6 +301,25 @@ MF_API mf_status mf_kv_cache_write_repeat_kv_heads(MfContext *ctx, const MfTenso
                                                    const MfTensor *cache,
                                                    const KvCacheWriteRepeatKvHeadsParamsResolved *params);
 
+/* "KvRearrange" (src/metals/kv_rearrange/mod.rs:11-58, kv_rearrange.metal:10-47): projection rows
+ * [batch*seq, row_stride] -> head-major [batch*n_heads, seq, head_dim], query head h reading kv
+ * head h / (n_heads / n_kv_heads) at column kv_h * kv_head_dim + hd (skipped when >= kv_dim). */
+typedef struct KvRearrangeParamsResolved {
+    uint32_t kv_dim, row_stride, kv_head_dim, n_heads, n_kv_heads, head_dim, seq, total_elements;
+} KvRearrangeParamsResolved;
+MF_API mf_status mf_kv_rearrange(MfContext *ctx, const MfTensor *input, const MfTensor *output,
+                                 const KvRearrangeParamsResolved *params);
+
+/* "RepeatKvHeads" (src/metals/repeat_kv_heads/mod.rs:14-60, repeat_kv_heads.metal:11-44): cache
+ * [batch*n_kv_heads, cache_stride, head_dim] -> [batch*n_heads, seq, head_dim], each kv head
+ * repeated group_size times.  The attention routes of this library never need the repeated
+ * copy (they index the compact cache); the op exists for callers of the unfused chain. */
+typedef struct RepeatKvHeadsParamsResolved {
+    uint32_t group_size, batch, n_kv_heads, n_heads, seq, head_dim, cache_stride, total_elements;
+} RepeatKvHeadsParamsResolved;
+MF_API mf_status mf_repeat_kv_heads(MfContext *ctx, const MfTensor *input, const MfTensor *output,
+                                    const RepeatKvHeadsParamsResolved *params);
+
 /* "KvCacheRead" (kv_cache_read.metal:7-29): cache [H, cap, D] -> [H, seq_len, D]. */
 MF_API mf_status mf_kv_cache_read(MfContext *ctx, const MfTensor *cache, const MfTensor *output,
                                   uint32_t seq_len);

@@ -96,6 +96,16 @@ class MfPagedKv(C.Structure):
                 ("batch", u32)]
 
 
+class KvRearrangeParamsResolved(C.Structure):
+    _fields_ = [(n, u32) for n in ("kv_dim", "row_stride", "kv_head_dim", "n_heads", "n_kv_heads", "head_dim", "seq",
+                                   "total_elements")]
+
+
+class RepeatKvHeadsParamsResolved(C.Structure):
+    _fields_ = [(n, u32) for n in ("group_size", "batch", "n_kv_heads", "n_heads", "seq", "head_dim", "cache_stride",
+                                   "total_elements")]
+
+
 class MfPagedDecodeArgs(C.Structure):
     _fields_ = [("q", vp), ("k", vp), ("v", vp), ("q_rot", vp), ("out", vp), ("cos", vp), ("sin", vp),
                 ("n_heads", u32), ("rope", u32), ("rope_mode", u32), ("append", u32), ("scale", C.c_float)]
@@ -133,6 +143,9 @@ _SIGNATURES = {
     "mf_kv_cache_read": (C.c_int32, [vp, C.POINTER(MfTensor), C.POINTER(MfTensor), u32]),
     "mf_kv_cache_grow": (C.c_int32, [vp, C.POINTER(MfTensor), C.POINTER(MfTensor), u32]),
     "mf_kv_cache_to_pages": (C.c_int32, [vp, C.POINTER(MfTensor), C.POINTER(MfPagedKv), u32, u32, u32]),
+    "mf_kv_rearrange": (C.c_int32, [vp, C.POINTER(MfTensor), C.POINTER(MfTensor), C.POINTER(KvRearrangeParamsResolved)]),
+    "mf_repeat_kv_heads": (C.c_int32, [vp, C.POINTER(MfTensor), C.POINTER(MfTensor),
+                                       C.POINTER(RepeatKvHeadsParamsResolved)]),
     "mf_sdpa_reference": (C.c_int32, [vp] + [C.POINTER(MfTensor)] * 4 + [C.POINTER(MfFlashAttentionArgs)]),
     "mf_flash_attention": (C.c_int32, [vp] + [C.POINTER(MfTensor)] * 4 + [C.POINTER(MfFlashAttentionArgs),
                                                                          C.POINTER(u32)]),
@@ -299,6 +312,14 @@ class Foundry:
         self.check(lib.mf_flash_attention(self._h, C.byref(tq), C.byref(tk), C.byref(tv), C.byref(to), C.byref(args),
                                           C.byref(route)))
         return route.value
+
+    def kv_rearrange(self, input, output, params: KvRearrangeParamsResolved):
+        ti, to = tensor_arg(input), tensor_arg(output)
+        self.check(lib.mf_kv_rearrange(self._h, C.byref(ti), C.byref(to), C.byref(params)))
+
+    def repeat_kv_heads(self, input, output, params: RepeatKvHeadsParamsResolved):
+        ti, to = tensor_arg(input), tensor_arg(output)
+        self.check(lib.mf_repeat_kv_heads(self._h, C.byref(ti), C.byref(to), C.byref(params)))
 
     def sdpa_reference(self, q, k, v, output, *, causal, query_offset, n_heads, head_dim, kv_seq_len, m=1, q_meta=None,
                        out_meta=None):

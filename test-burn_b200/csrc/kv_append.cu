@@ -234,6 +234,38 @@ cache_to_pages_kernel(const __half *cache, __half *pool, uint32_t heads, uint32_
         *reinterpret_cast<const uint4 *>(cache + ((size_t)h * max_seq_len + t) * head_dim + 8 * j);
 }
 
+// kv_rearrange.metal:10-47 and repeat_kv_heads.metal:11-44: one thread per output element, same index
+// arithmetic (the unfused chain is not on the hot path; the fused kernels never materialise these).
+__global__ void __launch_bounds__(256)
+kv_rearrange_kernel(const __half *__restrict__ in, __half *__restrict__ out, const KvRearrangeParamsResolved p)
+{
+    const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= p.total_elements) return;
+    const uint32_t hd = gid % p.head_dim;
+    const uint32_t tmp = gid / p.head_dim;
+    const uint32_t s = tmp % p.seq;
+    const uint32_t out_batch = tmp / p.seq;
+    const uint32_t b = out_batch / p.n_heads, h = out_batch % p.n_heads;
+    const uint32_t kv_h = h / (p.n_heads / p.n_kv_heads);
+    const uint32_t base = kv_h * p.kv_head_dim + hd;
+    if (base >= p.kv_dim) return;
+    out[gid] = in[(size_t)(b * p.seq + s) * p.row_stride + base];
+}
+
+__global__ void __launch_bounds__(256)
+repeat_kv_heads_kernel(const __half *__restrict__ in, __half *__restrict__ out, const RepeatKvHeadsParamsResolved p)
+{
+    const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= p.total_elements) return;
+    const uint32_t d = gid % p.head_dim;
+    const uint32_t tmp = gid / p.head_dim;
+    const uint32_t s = tmp % p.seq;
+    const uint32_t bh = tmp / p.seq;
+    const uint32_t b = bh / p.n_heads, h = bh % p.n_heads;
+    const uint32_t src_bh = b * p.n_kv_heads + h / p.group_size;
+    out[gid] = in[((size_t)src_bh * p.cache_stride + s) * p.head_dim + d];
+}
+
 // Whole pages of both pools, dst_ids[i] <- src_ids[i]; one thread per 16 bytes.
 __global__ void __launch_bounds__(256)
 copy_pages_kernel(uint4 *k_pool, uint4 *v_pool, const uint32_t *__restrict__ src_ids, const uint32_t *__restrict__ dst_ids,
@@ -497,6 +529,38 @@ mf_status mf_kv_cache_to_pages(MfContext *ctx, const MfTensor *cache, const MfPa
         tensor_ptr(cache), pool, paged->n_kv_heads, paged->head_dim, len, (uint32_t)cache->dims[1],
         paged->page_table + (size_t)seq * paged->page_table_stride, paged->page_size);
     return check_launch(ctx, "cache_to_pages_kernel");
+}
+
+mf_status mf_kv_rearrange(MfContext *ctx, const MfTensor *input, const MfTensor *output, const KvRearrangeParamsResolved *p)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    mf_status st;
+    if ((st = need_tensor(ctx, input, "input")) != MF_OK) return st;
+    if ((st = need_tensor(ctx, output, "output")) != MF_OK) return st;
+    if (!p) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "KvRearrange: params");
+    if (p->total_elements == 0) return MF_OK;
+    if (p->n_kv_heads == 0 || p->n_heads % p->n_kv_heads != 0 || p->head_dim == 0 || p->seq == 0)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "KvRearrange: n_heads %u, n_kv_heads %u, head_dim %u, seq %u", p->n_heads,
+                    p->n_kv_heads, p->head_dim, p->seq);
+    kv_rearrange_kernel<<<blocks_for(p->total_elements), 256, 0, ctx->stream>>>(tensor_ptr(input), tensor_ptr(output), *p);
+    return check_launch(ctx, "kv_rearrange_kernel");
+}
+
+mf_status mf_repeat_kv_heads(MfContext *ctx, const MfTensor *input, const MfTensor *output,
+                             const RepeatKvHeadsParamsResolved *p)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    mf_status st;
+    if ((st = need_tensor(ctx, input, "input")) != MF_OK) return st;
+    if ((st = need_tensor(ctx, output, "output")) != MF_OK) return st;
+    if (!p) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "RepeatKvHeads: params");
+    if (p->total_elements == 0) return MF_OK;
+    if (p->group_size == 0 || p->n_heads != p->n_kv_heads * p->group_size || p->head_dim == 0 || p->seq == 0 ||
+        p->seq > p->cache_stride)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "RepeatKvHeads: n_heads %u, n_kv_heads %u, group %u, seq %u, cache_stride %u",
+                    p->n_heads, p->n_kv_heads, p->group_size, p->seq, p->cache_stride);
+    repeat_kv_heads_kernel<<<blocks_for(p->total_elements), 256, 0, ctx->stream>>>(tensor_ptr(input), tensor_ptr(output), *p);
+    return check_launch(ctx, "repeat_kv_heads_kernel");
 }
 
 mf_status mf_paged_copy_pages(MfContext *ctx, const MfPagedKv *cache, const uint32_t *src_ids, const uint32_t *dst_ids,

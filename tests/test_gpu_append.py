@@ -60,18 +60,25 @@ def test_kv_prep_fused_equals_unfused_chain(mfk, foundry):
     m, off, cap, hq, hkv, d = 4, 3, 32, 14, 2, 64
     case = ContigCase(n_heads=hq, n_kv_heads=hkv, head_dim=d, cached=off, m=m, capacity=cap, theta=1e4, rope_mode=0)
     _, k_fused, v_fused = run_kv_prep(mfk, foundry, case)
-    # unfused chain on the GPU: rearrange on the host (pure indexing), then Rope + KvCacheWrite kernels
+    # the unfused chain on the GPU: KvRearrange, Rope, KvCacheWrite
     k_heads = np.empty((hkv, m, d), np.uint16)
     v_heads = np.empty((hkv, m, d), np.uint16)
     L = oracle.lib()
     L.mfo_kv_rearrange(case.k, k_heads, hkv * d, d, hkv, hkv, d, m)
     L.mfo_kv_rearrange(case.v, v_heads, hkv * d, d, hkv, hkv, d, m)
-    k_in, k_rot = dev(k_heads), torch.empty((hkv, m, d), dtype=torch.float16, device="cuda")
+    rp = mfk.KvRearrangeParamsResolved(hkv * d, hkv * d, d, hkv, hkv, d, m, hkv * m * d)
+    k_in = torch.empty((hkv, m, d), dtype=torch.float16, device="cuda")
+    v_in = torch.empty((hkv, m, d), dtype=torch.float16, device="cuda")
+    foundry.kv_rearrange(dev(case.k), k_in, rp)
+    foundry.kv_rearrange(dev(case.v), v_in, rp)
+    foundry.synchronize()
+    assert np.array_equal(host(k_in), k_heads) and np.array_equal(host(v_in), v_heads)
+    k_rot = torch.empty((hkv, m, d), dtype=torch.float16, device="cuda")
     foundry.rope(k_in, k_rot, dev(case.cos), dev(case.sin), mfk.RopeParamsResolved(d, m, off, hkv * m * d))
     kc, vc = dev(case.k_cache), dev(case.v_cache)
     wp = mfk.KvCacheWriteParamsResolved(hkv, d, m, off, cap, hkv * m * d, 0)
     foundry.kv_cache_write(k_rot, kc, wp)
-    foundry.kv_cache_write(dev(v_heads), vc, wp)
+    foundry.kv_cache_write(v_in, vc, wp)
     foundry.synchronize()
     assert np.array_equal(host(kc), k_fused)
     assert np.array_equal(host(vc), v_fused)
@@ -166,3 +173,36 @@ def test_kv_prep_rejects_bad_arguments(mfk, foundry):
     assert e.value.kind == "UnsupportedDtype"
     foundry.synchronize()
     assert np.array_equal(host(kc), case.k_cache)  # nothing was launched
+
+
+def test_kv_rearrange_and_repeat_kv_heads(mfk, foundry):
+    """KvRearrange with grouped heads and a padded row stride (kv_rearrange.metal:27-46), RepeatKvHeads out
+    of a cache with capacity slack (repeat_kv_heads.metal:25-43): pure index maps, bit-exact."""
+    import torch
+
+    hq, hkv, d, seq, row_stride = 12, 4, 64, 7, 4 * 64 + 32
+    rows = oracle.normal_fill(5, 1, seq * row_stride).reshape(seq, row_stride)
+    want = np.empty((hq, seq, d), np.uint16)
+    oracle.lib().mfo_kv_rearrange(rows, want, row_stride, d, hq, hkv, d, seq)
+    got = torch.full((hq, seq, d), float("nan"), dtype=torch.float16, device="cuda")
+    foundry.kv_rearrange(dev(rows), got, mfk.KvRearrangeParamsResolved(hkv * d, row_stride, d, hq, hkv, d, seq, hq * seq * d))
+    foundry.synchronize()
+    assert np.array_equal(host(got), want)
+    # kv_dim smaller than the heads ask for: the elements past it are left alone (kv_rearrange.metal:40)
+    got2 = torch.zeros((hq, seq, d), dtype=torch.float16, device="cuda")
+    foundry.kv_rearrange(dev(rows), got2, mfk.KvRearrangeParamsResolved(3 * d, row_stride, d, hq, hkv, d, seq, hq * seq * d))
+    foundry.synchronize()
+    g = hq // hkv
+    assert np.array_equal(host(got2)[:3 * g], want[:3 * g]) and not host(got2)[3 * g:].any()
+
+    cap, live = 32, 19
+    cache = oracle.normal_fill(5, 2, hkv * cap * d).reshape(hkv, cap, d)
+    rep_want = np.empty((hq, live, d), np.uint16)
+    oracle.lib().mfo_repeat_kv_heads(np.ascontiguousarray(cache[:, :live]), rep_want, hkv, g, live, d)
+    rep = torch.full((hq, live, d), float("nan"), dtype=torch.float16, device="cuda")
+    foundry.repeat_kv_heads(dev(cache), rep, mfk.RepeatKvHeadsParamsResolved(g, 1, hkv, hq, live, d, cap, hq * live * d))
+    foundry.synchronize()
+    assert np.array_equal(host(rep), rep_want)
+    with pytest.raises(mfk.MetalError) as e:
+        foundry.repeat_kv_heads(dev(cache), rep, mfk.RepeatKvHeadsParamsResolved(g, 1, hkv, hq + 1, live, d, cap, 1))
+    assert e.value.kind == "InvalidShape"
