@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the KV-cache hot path: fused RoPE + K/V append + paged GQA flash-decode.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3|c2|c3-small]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c1|c2|c2-paged|c3|c3-small|c4|c5]
 
 Workload (default `c3`, the batched paged-decode configuration the headline metric is quoted on):
 Qwen2.5-3B shape, 36 layers, 16 q heads / 2 kv heads, head_dim 128, batch 64, per-sequence
@@ -48,10 +48,10 @@ WORKLOADS = {
                      theta=1e6, rope_mode=0, name="c3 with 4 layers (profiling case)"),
     "uniform148": dict(layers=4, n_heads=16, n_kv_heads=2, head_dim=128, batch=74, lo=8191, hi=8191, page_size=16,
                        theta=1e6, rope_mode=0, name="experiment: 148 equal (sequence, kv head) units of 8192 keys"),
-    "c2": dict(layers=28, n_heads=24, n_kv_heads=8, head_dim=128, batch=1, lo=8191, hi=8191, page_size=64,
-               theta=5e5, rope_mode=1,
-               name="Llama-3.2-3B shape decode step: 28 layers, 24q/8kv heads, D128, batch 1, ctx 8192, "
-                    "cache as 64-token pages in order"),
+    "c2-paged": dict(layers=28, n_heads=24, n_kv_heads=8, head_dim=128, batch=1, lo=8191, hi=8191, page_size=64,
+                     theta=5e5, rope_mode=1,
+                     name="Llama-3.2-3B shape decode step: 28 layers, 24q/8kv heads, D128, batch 1, ctx 8192, "
+                          "cache as 64-token pages in order, one fused launch per layer"),
 }
 LONG_CONTEXT = {
     # sequence-sharded single-sequence decode (strong scaling): pages of ONE sequence are cut into
@@ -611,43 +611,59 @@ def run_prefill(args):
     return 0 if ok else 1
 
 
-def run_single_token_latency(args):
-    """Configuration 1: Qwen2.5-0.5B shape, one layer, batch 1, 511 cached + 1, contiguous cache
-    [2, 512, 64]: KvPrepFused then FlashAttention (decode route), the reference's own two ops.  The
-    whole working set (0.27 MB) sits in L2, so this is a latency figure, not a bandwidth one."""
+CONTIGUOUS = {
+    # the reference's own layout and op order: contiguous cache [Hkv, capacity, D] per layer, KvPrepFused then
+    # FlashAttention (decode route), batch 1
+    "c1": dict(layers=1, n_heads=14, n_kv_heads=2, head_dim=64, cached=511, capacity=512, theta=1e6, rope_mode=0,
+               name="single-token latency, Qwen2.5-0.5B shape: 1 layer, 14q/2kv heads, D64, batch 1, 511 cached + 1, "
+                    "contiguous cache, KvPrepFused then FlashAttention (2 launches)"),
+    "c2": dict(layers=28, n_heads=24, n_kv_heads=8, head_dim=128, cached=8191, capacity=8192, theta=5e5, rope_mode=1,
+               name="Llama-3.2-3B shape decode step: 28 layers, 24q/8kv heads, D128, batch 1, ctx 8192, contiguous "
+                    "cache, KvPrepFused then FlashAttention per layer (56 launches)"),
+}
+
+
+def run_contiguous_decode(args, w):
+    """Configurations 1 and 2: batch-1 decode steps on contiguous caches through the reference's two ops per
+    layer.  The step is timed twice: launched call by call from the Python binding (host-bound for
+    launches this short) and replayed from a CUDA graph, which is the device-side figure reported as
+    `value`.  Configuration 1 (0.27 MB) is L2-resident: latency only."""
     import torch
 
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     mfk = importlib.import_module("test-burn_b200")
-    hq, hkv, d, cached, cap = 14, 2, 64, 511, 512
+    layers, hq, hkv, d, cached, cap = w["layers"], w["n_heads"], w["n_kv_heads"], w["head_dim"], w["cached"], w["capacity"]
     g = torch.Generator(device=dev).manual_seed(SEED)
-    q = torch.empty((1, hq * d), dtype=torch.float16, device=dev).normal_(generator=g)
-    k = torch.empty((1, hkv * d), dtype=torch.float16, device=dev).normal_(generator=g)
-    v = torch.empty((1, hkv * d), dtype=torch.float16, device=dev).normal_(generator=g)
-    kc = torch.empty((hkv, cap, d), dtype=torch.float16, device=dev).normal_(generator=g)
-    vc = torch.empty((hkv, cap, d), dtype=torch.float16, device=dev).normal_(generator=g)
-    cos_np, sin_np = mfk.rope_tables(1e6, d, cap)
+    q = torch.empty((layers, 1, hq * d), dtype=torch.float16, device=dev).normal_(generator=g)
+    k = torch.empty((layers, 1, hkv * d), dtype=torch.float16, device=dev).normal_(generator=g)
+    v = torch.empty((layers, 1, hkv * d), dtype=torch.float16, device=dev).normal_(generator=g)
+    kcs = [torch.empty((hkv, cap, d), dtype=torch.float16, device=dev).normal_(generator=g) for _ in range(layers)]
+    vcs = [torch.empty((hkv, cap, d), dtype=torch.float16, device=dev).normal_(generator=g) for _ in range(layers)]
+    cos_np, sin_np = mfk.rope_tables(w["theta"], d, cap)
     cos = torch.from_numpy(cos_np.view(np.float16)).to(dev)
     sin = torch.from_numpy(sin_np.view(np.float16)).to(dev)
-    q_rot = torch.empty((1, hq * d), dtype=torch.float16, device=dev)
-    out = torch.empty((1, hq * d), dtype=torch.float16, device=dev)
+    q_rot = torch.empty((layers, 1, hq * d), dtype=torch.float16, device=dev)
+    out = torch.empty((layers, 1, hq * d), dtype=torch.float16, device=dev)
     stream = torch.cuda.Stream(device=dev)
     f = mfk.Foundry(0, stream.cuda_stream)
-    p = mfk.KvPrepFusedParamsResolved(hq * d, hkv * d, d, hq, hkv, hq // hkv, 1, cached, cap, hq * d, 0, 0, 0)
+    if not args.no_overlap:
+        f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 1)
+    p = mfk.KvPrepFusedParamsResolved(hq * d, hkv * d, d, hq, hkv, hq // hkv, 1, cached, cap, hq * d, w["rope_mode"], 0, 0)
 
     def step():
-        f.kv_prep_fused(q, k, v, q_rot, kc, vc, cos, sin, p)
-        f.flash_attention(q_rot, kc, vc, out, causal=True, query_offset=cached, n_heads=hq, head_dim=d,
-                          kv_seq_len=cached + 1, m=1)
+        for i in range(layers):
+            f.kv_prep_fused(q[i], k[i], v[i], q_rot[i], kcs[i], vcs[i], cos, sin, p)
+            f.flash_attention(q_rot[i], kcs[i], vcs[i], out[i], causal=True, query_offset=cached, n_heads=hq, head_dim=d,
+                              kv_seq_len=cached + 1, m=1)
 
-    for _ in range(max(args.warmup, 25)):
+    for _ in range(max(args.warmup, 25 if layers == 1 else 3)):
         step()
     f.synchronize()
     sampler = ClockSampler(0)
     sampler.start()
     time.sleep(0.3)
-    trials, iters = 10, max(args.steps, 100)
+    trials, iters = 10, max(args.steps, 100) if layers == 1 else max(10, min(args.steps, 40))
     per_iter_us = []
     launches0 = f.launch_count
     t0 = time.time()
@@ -660,11 +676,11 @@ def run_single_token_latency(args):
         f.synchronize()
         per_iter_us.append(a.elapsed_time(b) * 1e3 / iters)
     launches = f.launch_count - launches0
-    # The same two launches replayed from a CUDA graph (20 steps per graph): the device-side latency
-    # without the per-call cost of the Python binding.  The step is idempotent (same row, same values).
+    # The same launches replayed from a CUDA graph: the device-side time without the per-call cost of
+    # the Python binding.  The step is idempotent (same rows, same values).
     graph_us = None
     try:
-        g_steps = 20
+        g_steps = 20 if layers == 1 else 2
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             for _ in range(g_steps):
@@ -686,29 +702,32 @@ def run_single_token_latency(args):
                     "mean": float(np.mean(per_graph)), "sd": float(np.std(per_graph))}
     except Exception as e:  # capture is an extra; the eager figure stands on its own
         graph_us = {"unavailable": str(e)[:200]}
+    f.synchronize()
     t1 = time.time()
     clocks = sampler.stop(t0, t1)
     us = np.array(per_iter_us)
     eager_med = float(np.median(us))
     med = graph_us["median"] if "median" in graph_us else eager_med  # the device-side figure when it exists
-    bytes_step = 2 * hkv * (cached + 1) * d * 2 + 4 * hkv * d * 2 + 2 * hq * d * 2 + 2 * (d // 2) * 2
+    bytes_layer = 2 * hkv * (cached + 1) * d * 2 + 4 * hkv * d * 2 + 2 * hq * d * 2 + 2 * (d // 2) * 2
     peak, peak_kind = measured_peak_gbs()
-    achieved = bytes_step / (med * 1e-6) / 1e9
+    achieved = bytes_layer * layers / (med * 1e-6) / 1e9
+    l2_note = ("L2-resident by construction (0.27 MB): latency only, not a bandwidth figure" if layers == 1 else
+               "inputs larger than L2 (caches %.2f GB)" % (2 * layers * hkv * cap * d * 2 / 1e9))
     ok = bool(torch.isfinite(out.float()).all())
     print(json.dumps({
         "metric": METRIC, "value": 1e6 / med, "unit": "tokens/s", "n_gpus": 1, "steps": iters * trials,
-        "warmup": max(args.warmup, 25), "ms_per_step": med * 1e-3, "us_per_step": med, "higher_is_better": True,
+        "warmup": max(args.warmup, 3), "ms_per_step": med * 1e-3, "us_per_step": med, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
-        "config": {"workload": "single-token latency, Qwen2.5-0.5B shape: 1 layer, 14q/2kv heads, D64, batch 1, "
-                               "511 cached + 1, contiguous cache, KvPrepFused then FlashAttention (2 launches)",
-                   "l2": "L2-resident by construction (0.27 MB): latency only, not a bandwidth figure",
-                   "timing": "value / us_per_step = CUDA-graph replay of the two launches when capture works, else eager"},
+        "config": {"workload": w["name"], "l2": l2_note,
+                   "timing": "value / us_per_step = CUDA-graph replay of the step when capture works, else eager"},
         "latency_us": {"trials": trials, "iterations": iters, "min": float(us.min()), "median": eager_med,
                        "mean": float(us.mean()), "sd": float(us.std()),
                        "note": "launched call by call from the Python binding: host-bound"},
         "latency_us_cuda_graph": graph_us,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": peak_kind, "traffic": None, "note": "launch-bound; see latency_us"},
+                     "peak_kind": peak_kind, "traffic": None, "launch_us": med / layers,
+                     "algorithmic_bytes_per_launch": bytes_layer,
+                     "note": "launch-bound" if layers == 1 else "per layer: kv_append_kernel + decode_kernel"},
         "gpu_launches": launches, "clocks": clocks, "self_check": "ok" if ok else "FAILED"}))
     f.close()
     return 0 if ok else 1
@@ -787,7 +806,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + sorted(LONG_CONTEXT) + ["c1", "c4"])
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + sorted(LONG_CONTEXT) + sorted(CONTIGUOUS) + ["c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", default="fused", choices=["fused", "push", "nccl"],
                     help="long-context workloads: partials exchanged and merged inside the decode kernel (fused), "
@@ -800,8 +819,8 @@ def main():
     args = ap.parse_args()
     if args.workload == "c4":
         return run_prefill(args)
-    if args.workload == "c1":
-        return run_single_token_latency(args)
+    if args.workload in CONTIGUOUS:
+        return run_contiguous_decode(args, CONTIGUOUS[args.workload])
     if args.workload in LONG_CONTEXT:
         return run_long_context(args, LONG_CONTEXT[args.workload])
     w = dict(WORKLOADS[args.workload])
