@@ -33,6 +33,18 @@
 namespace mf {
 namespace {
 
+#ifndef MF_TC_LOAD_DIV
+#define MF_TC_LOAD_DIV 1  // timing probe only: > 1 loads that fraction of every K/V tile (results are then wrong)
+#endif
+#ifndef MF_TC_PROBE_QK_DIV
+#define MF_TC_PROBE_QK_DIV 1  // timing probes: issue only 1/DIV of the MMAs of a product (results are then wrong)
+#endif
+#ifndef MF_TC_PROBE_PV_DIV
+#define MF_TC_PROBE_PV_DIV 1
+#endif
+#ifndef MF_TC_PROBE_NOEXP
+#define MF_TC_PROBE_NOEXP 0
+#endif
 #ifndef MF_TC_VSTAGES
 #define MF_TC_VSTAGES 3
 #endif
@@ -233,15 +245,14 @@ enum Bar : uint32_t {
     kQFull = 0,
     kKFull = 1,    // [3]
     kVFull = 4,    // [3]
-    kKEmpty = 7,   // [3]
-    kVEmpty = 10,  // [3]
+    kUnused7 = 7,  // [6] slots kept so that the numbering stays put
     kSFull = 13,   // [3] per score buffer: it holds Q K^T of its next tile
     kPFull = 16,   // [3] per score buffer: P is in it (and O has been rescaled if needed)
     kOFull = 19,   // [3] per score buffer: the P V that read it has completed
     kDec = 22,     // [2] by tile parity: the tile's row maxima have been folded into m_ref
     kNumBars = 24
 };
-static_assert(kKStages == 3 && kVStages == 3, "barrier slots");
+static_assert(kKStages == 3 && kVStages == 3, "ring slot = score buffer = tile % 3");
 
 constexpr uint32_t kSmemTiles = kTile * (1 + kKStages + kVStages);  // Q + K ring + V ring
 constexpr uint32_t kRefBytes = 128 * 4;                             // m_ref per query row
@@ -281,8 +292,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         for (uint32_t s = 0; s < 3; ++s) {
             mbar_init(bar(kKFull + s), 1);
             mbar_init(bar(kVFull + s), 1);
-            mbar_init(bar(kKEmpty + s), 1);
-            mbar_init(bar(kVEmpty + s), 1);
             mbar_init(bar(kSFull + s), 1);
             mbar_init(bar(kPFull + s), kGroupWarps);  // one arrival per softmax warp of the group
             mbar_init(bar(kOFull + s), 1);
@@ -302,7 +311,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
+    // The common case is a barrier that has already completed: one try, nothing else.  (The thread that
+    // issues the MMAs runs every instruction of this on the kernel's critical path.)
     auto wait = [&](uint32_t b, uint32_t parity, uint32_t code) {
+        if (mbar_try_wait(b, parity)) return;
         if (!*abort_flag && !mbar_wait_bounded(b, parity, kTcWaitNs)) {
             *abort_flag = 1;
             atomicOr(p.status, code);
@@ -320,16 +332,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tma_load_4d(q_smem, &tm_q, 0, (int32_t)row0, 0, (int32_t)head, bar(kQFull));
             // K/V maps are (head_dim, kv_len, kv heads): rows past kv_len arrive as zeros, so a
             // never-written cache row cannot meet a zero weight as NaN.
+            // A K slot is free when the Q K^T that read it has completed (= its score buffer is full), a V
+            // slot when the P V that read it has: the tensor pipe's own completion barriers say both.
             auto load_k = [&](uint32_t i) {
                 const uint32_t ks = i % kKStages, kph = (i / kKStages) & 1;
-                TC_PROF_WAIT(0, wait(bar(kKEmpty + ks), kph ^ 1, 16u))
-                mbar_arrive_expect_tx(bar(kKFull + ks), kTile);
+                if (i >= kKStages) { TC_PROF_WAIT(0, wait(bar(kSFull + ks), kph ^ 1, 16u)) }
+                mbar_arrive_expect_tx(bar(kKFull + ks), kTile / MF_TC_LOAD_DIV);
                 tma_load_4d(k_smem + ks * kTile, &tm_k, 0, (int32_t)(i * kBN), 0, (int32_t)kvh, bar(kKFull + ks));
             };
             auto load_v = [&](uint32_t i) {
                 const uint32_t vs = i % kVStages, vph = (i / kVStages) & 1;
-                TC_PROF_WAIT(1, wait(bar(kVEmpty + vs), vph ^ 1, 16u))
-                mbar_arrive_expect_tx(bar(kVFull + vs), kTile);
+                if (i >= kVStages) { TC_PROF_WAIT(1, wait(bar(kOFull + vs), vph ^ 1, 16u)) }
+                mbar_arrive_expect_tx(bar(kVFull + vs), kTile / MF_TC_LOAD_DIV);
                 tma_load_4d(v_smem + vs * kTile, &tm_v, 0, (int32_t)(i * kBN), 0, (int32_t)kvh, bar(kVFull + vs));
             };
             // The order in which the tensor pipe asks for the tiles: K runs three tiles ahead of V.
@@ -350,52 +364,53 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             // The descriptors of one operand differ only in the 14-bit start-address field: build each
             // once and add the 16-byte-unit offsets, so that an MMA costs this thread a few instructions.
             const uint64_t q_desc = smem_desc(q_smem, 16, 1024);
-            auto issue_qk = [&](uint32_t i) {
-                const uint32_t b = i % 3;
-                const uint32_t ks = i % kKStages, kph = (i / kKStages) & 1;
-                TC_PROF_WAIT(0, wait(bar(kKFull + ks), kph, 32u))
+            // b = i % 3 is tile i's score buffer and its K and V ring slot, ph = (i / 3) & 1 their phase;
+            // both are carried as counters: this thread's instructions are the kernel's critical path.
+            auto issue_qk = [&](uint32_t b, uint32_t ph) {
+                TC_PROF_WAIT(0, wait(bar(kKFull + b), ph, 32u))
                 tc_fence_after();
                 TC_PROF_MARK(ma)
-                const uint64_t k_desc = smem_desc(k_smem + ks * kTile, 16, 1024);
+                const uint64_t k_desc = smem_desc(k_smem + b * kTile, 16, 1024);
 #pragma unroll
-                for (uint32_t kk = 0; kk < kD / 16; ++kk) {
+                for (uint32_t kk = 0; kk < kD / 16 / MF_TC_PROBE_QK_DIV; ++kk) {
                     const uint32_t off = ((kk >> 2) * kHalfTile + (kk & 3) * 32) >> 4;
                     tc_mma_ss(tmem + b * 128, q_desc + off, k_desc + off, kIdescQK, kk > 0);
                 }
                 TC_PROF_MARK(mb)
                 tc_commit(bar(kSFull + b));
-                tc_commit(bar(kKEmpty + ks));
                 TC_PROF_MARK(mc)
                 TC_PROF_SPAN(4, ma, mb)
                 TC_PROF_SPAN(6, mb, mc)
             };
-            auto issue_pv = [&](uint32_t i) {
-                const uint32_t b = i % 3;
-                const uint32_t vs = i % kVStages, vph = (i / kVStages) & 1;
-                TC_PROF_WAIT(2, wait(bar(kVFull + vs), vph, 64u))
-                TC_PROF_WAIT(3, wait(bar(kPFull + b), (i / 3) & 1, 64u))
+            auto issue_pv = [&](uint32_t b, uint32_t ph, uint32_t first) {
+                TC_PROF_WAIT(2, wait(bar(kVFull + b), ph, 64u))
+                TC_PROF_WAIT(3, wait(bar(kPFull + b), ph, 64u))
                 tc_fence_after();
                 TC_PROF_MARK(ma)
-                const uint64_t v_desc = smem_desc(v_smem + vs * kTile, kHalfTile, 1024);
+                const uint64_t v_desc = smem_desc(v_smem + b * kTile, kHalfTile, 1024);
 #pragma unroll
-                for (uint32_t kk = 0; kk < kBN / 16; ++kk) {
+                for (uint32_t kk = 0; kk < kBN / 16 / MF_TC_PROBE_PV_DIV; ++kk) {
                     // A: 16 keys = 8 packed 32-bit TMEM columns per step; B: V rows kk*16.., MN-major.
                     tc_mma_ts(tmem + 384, tmem + b * 128 + kk * 8, v_desc + kk * (2048 >> 4), kIdescPV,
-                              (i > 0 || kk > 0) ? 1u : 0u);
+                              (!first || kk > 0) ? 1u : 0u);
                 }
                 TC_PROF_MARK(mb)
                 tc_commit(bar(kOFull + b));
-                tc_commit(bar(kVEmpty + vs));
                 TC_PROF_MARK(mc)
                 TC_PROF_SPAN(5, ma, mb)
                 TC_PROF_SPAN(7, mb, mc)
             };
             // Q K^T of tile i + 3 goes into the buffer that P V of tile i has just read: the tensor
             // pipe runs this thread's MMAs in order, so S overwrites P only after P was consumed.
-            for (uint32_t i = 0; i < min(n_tiles, 3u); ++i) issue_qk(i);
+            for (uint32_t i = 0; i < min(n_tiles, 3u); ++i) issue_qk(i, 0);
+            uint32_t b = 0, ph = 0;
             for (uint32_t i = 0; i < n_tiles; ++i) {
-                issue_pv(i);
-                if (i + 3 < n_tiles) issue_qk(i + 3);
+                issue_pv(b, ph, i == 0);
+                if (i + 3 < n_tiles) issue_qk(b, ph ^ 1);
+                if (++b == 3) {
+                    b = 0;
+                    ph ^= 1;
+                }
             }
             TC_PROF_STORE(1)
         }
@@ -504,8 +519,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         if (kPolyMask & (1u << (q & 7))) {
                             w = exp2_poly2(t);
                         } else {
+#if MF_TC_PROBE_NOEXP
+                            w = t;  // timing probe: no special-function work (results are wrong)
+#else
                             w.x = fast_exp2(t.x);
                             w.y = fast_exp2(t.y);
+#endif
                         }
                         if (q & 1) acc_b = __fadd2_rn(acc_b, w);
                         else acc_a = __fadd2_rn(acc_a, w);
@@ -625,10 +644,10 @@ mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const 
     // (64 columns, rows, 2 column halves, heads) views with the caller's row and head strides: one box of
     // 64 columns x 128 rows x 2 halves brings a whole tile and lands as [half][row][128 B].
     auto encode = [&](CUtensorMap *tm, const void *base, uint64_t rows, uint64_t heads, uint64_t row_stride,
-                      uint64_t head_stride) {
+                      uint64_t head_stride, uint32_t box_rows = 128) {
         cuuint64_t gdim[4] = {64, rows, 2, heads};
         cuuint64_t gstride[3] = {row_stride * 2, 128, head_stride * 2};
-        cuuint32_t box[4] = {64, 128, 2, 1};
+        cuuint32_t box[4] = {64, box_rows, 2, 1};
         cuuint32_t estr[4] = {1, 1, 1, 1};
         return reinterpret_cast<EncodeFn>(ctx->encode_fn)(
                    tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(base), gdim, gstride, box, estr,
@@ -640,8 +659,8 @@ mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const 
     mf_status st;
     // Unusual strides the encoder refuses are left to the other kernel.
     if (!encode(&tm_q, q, b.q_len, sp.n_heads, b.q_stride_m, b.q_stride_h)) return MF_OK;
-    if (!encode(&tm_k, k, b.kv_len, cache_heads, kD, b.k_stride_h)) return MF_OK;
-    if (!encode(&tm_v, v, b.kv_len, cache_heads, kD, b.v_stride_h)) return MF_OK;
+    if (!encode(&tm_k, k, b.kv_len, cache_heads, kD, b.k_stride_h, 128 / MF_TC_LOAD_DIV)) return MF_OK;
+    if (!encode(&tm_v, v, b.kv_len, cache_heads, kD, b.v_stride_h, 128 / MF_TC_LOAD_DIV)) return MF_OK;
     TcParams p{};
     p.out = static_cast<__half *>(out);
     p.status = ctx->d_status;
