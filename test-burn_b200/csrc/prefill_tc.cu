@@ -243,8 +243,8 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void *tmap, int3
 // Barrier slots (8 bytes each) after the tiles.
 enum Bar : uint32_t {
     kQFull = 0,
-    kKFull = 1,    // [3]
-    kVFull = 4,    // [3]
+    kKFull = 1,    // [3] the first three K tiles
+    kVFull = 4,    // [3] V tile i together with K tile i + 3
     kUnused7 = 7,  // [6] slots kept so that the numbering stays put
     kSFull = 13,   // [3] per score buffer: it holds Q K^T of its next tile
     kPFull = 16,   // [3] per score buffer: P is in it (and O has been rescaled if needed)
@@ -332,25 +332,29 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tma_load_4d(q_smem, &tm_q, 0, (int32_t)row0, 0, (int32_t)head, bar(kQFull));
             // K/V maps are (head_dim, kv_len, kv heads): rows past kv_len arrive as zeros, so a
             // never-written cache row cannot meet a zero weight as NaN.
-            // A K slot is free when the Q K^T that read it has completed (= its score buffer is full), a V
-            // slot when the P V that read it has: the tensor pipe's own completion barriers say both.
-            auto load_k = [&](uint32_t i) {
-                const uint32_t ks = i % kKStages, kph = (i / kKStages) & 1;
-                if (i >= kKStages) { TC_PROF_WAIT(0, wait(bar(kSFull + ks), kph ^ 1, 16u)) }
-                mbar_arrive_expect_tx(bar(kKFull + ks), kTile / MF_TC_LOAD_DIV);
-                tma_load_4d(k_smem + ks * kTile, &tm_k, 0, (int32_t)(i * kBN), 0, (int32_t)kvh, bar(kKFull + ks));
-            };
-            auto load_v = [&](uint32_t i) {
-                const uint32_t vs = i % kVStages, vph = (i / kVStages) & 1;
-                if (i >= kVStages) { TC_PROF_WAIT(1, wait(bar(kOFull + vs), vph ^ 1, 16u)) }
-                mbar_arrive_expect_tx(bar(kVFull + vs), kTile / MF_TC_LOAD_DIV);
-                tma_load_4d(v_smem + vs * kTile, &tm_v, 0, (int32_t)(i * kBN), 0, (int32_t)kvh, bar(kVFull + vs));
-            };
-            // The order in which the tensor pipe asks for the tiles: K runs three tiles ahead of V.
-            for (uint32_t i = 0; i < min(n_tiles, 3u); ++i) load_k(i);
+            // The first three K tiles have barriers of their own; after that V(i) and K(i + 3) travel as a
+            // pair on ONE barrier, because the MMA-issuing thread wants them together (P V of tile i, then
+            // Q K^T of tile i + 3) and every wait it makes is on the kernel's critical path.  The V slot
+            // is free when the P V that read it has completed, the K slot when the Q K^T of tile i has:
+            // the tensor pipe's own completion barriers say both.
+            for (uint32_t i = 0; i < min(n_tiles, 3u); ++i) {
+                mbar_arrive_expect_tx(bar(kKFull + i), kTile / MF_TC_LOAD_DIV);
+                tma_load_4d(k_smem + i * kTile, &tm_k, 0, (int32_t)(i * kBN), 0, (int32_t)kvh, bar(kKFull + i));
+            }
+            uint32_t b = 0, ph = 0;  // slot i % 3 and phase (i / 3) & 1
             for (uint32_t i = 0; i < n_tiles; ++i) {
-                load_v(i);
-                if (i + 3 < n_tiles) load_k(i + 3);
+                if (i >= 3) { TC_PROF_WAIT(1, wait(bar(kOFull + b), ph ^ 1, 16u)) }  // P V (i - 3) done
+                const bool with_k = i + 3 < n_tiles;
+                mbar_arrive_expect_tx(bar(kVFull + b), (with_k ? 2 : 1) * (kTile / MF_TC_LOAD_DIV));
+                tma_load_4d(v_smem + b * kTile, &tm_v, 0, (int32_t)(i * kBN), 0, (int32_t)kvh, bar(kVFull + b));
+                if (with_k) {
+                    TC_PROF_WAIT(0, wait(bar(kSFull + b), ph, 16u))  // Q K^T (i) done: K slot b is free
+                    tma_load_4d(k_smem + b * kTile, &tm_k, 0, (int32_t)((i + 3) * kBN), 0, (int32_t)kvh, bar(kVFull + b));
+                }
+                if (++b == 3) {
+                    b = 0;
+                    ph ^= 1;
+                }
             }
             TC_PROF_STORE(2)
         }
@@ -366,9 +370,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             const uint64_t q_desc = smem_desc(q_smem, 16, 1024);
             // b = i % 3 is tile i's score buffer and its K and V ring slot, ph = (i / 3) & 1 their phase;
             // both are carried as counters: this thread's instructions are the kernel's critical path.
-            auto issue_qk = [&](uint32_t b, uint32_t ph) {
-                TC_PROF_WAIT(0, wait(bar(kKFull + b), ph, 32u))
-                tc_fence_after();
+            auto issue_qk = [&](uint32_t b, bool first_round) {
+                if (first_round) {  // later K tiles arrive together with the V tile waited for just before
+                    TC_PROF_WAIT(0, wait(bar(kKFull + b), 0, 32u))
+                    tc_fence_after();
+                }
                 TC_PROF_MARK(ma)
                 const uint64_t k_desc = smem_desc(k_smem + b * kTile, 16, 1024);
 #pragma unroll
@@ -402,11 +408,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             };
             // Q K^T of tile i + 3 goes into the buffer that P V of tile i has just read: the tensor
             // pipe runs this thread's MMAs in order, so S overwrites P only after P was consumed.
-            for (uint32_t i = 0; i < min(n_tiles, 3u); ++i) issue_qk(i, 0);
+            for (uint32_t i = 0; i < min(n_tiles, 3u); ++i) issue_qk(i, true);
             uint32_t b = 0, ph = 0;
             for (uint32_t i = 0; i < n_tiles; ++i) {
                 issue_pv(b, ph, i == 0);
-                if (i + 3 < n_tiles) issue_qk(b, ph ^ 1);
+                if (i + 3 < n_tiles) issue_qk(b, false);
                 if (++b == 3) {
                     b = 0;
                     ph ^= 1;
