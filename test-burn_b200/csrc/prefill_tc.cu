@@ -36,6 +36,9 @@ namespace {
 #ifndef MF_TC_LOAD_DIV
 #define MF_TC_LOAD_DIV 1  // timing probe only: > 1 loads that fraction of every K/V tile (results are then wrong)
 #endif
+#ifndef MF_TC_SPLIT_ISSUE
+#define MF_TC_SPLIT_ISSUE 1  // 1: Q K^T and P V are issued by two threads in two warps, 0: by one
+#endif
 #ifndef MF_TC_PROBE_QK_DIV
 #define MF_TC_PROBE_QK_DIV 1  // timing probes: issue only 1/DIV of the MMAs of a product (results are then wrong)
 #endif
@@ -54,7 +57,7 @@ constexpr uint32_t kD = 128;              // head_dim
 constexpr uint32_t kGroupWarps = 4;                       // softmax warps per group (one thread per row)
 constexpr uint32_t kSoftmaxWarps = 2 * kGroupWarps;
 constexpr uint32_t kSoftmaxThreads = 32 * kSoftmaxWarps;
-constexpr uint32_t kTcThreads = kSoftmaxThreads + 64;
+constexpr uint32_t kTcThreads = kSoftmaxThreads + 64 + 32 * MF_TC_SPLIT_ISSUE;
 constexpr float kRescaleThreshold = 8.0f;                 // log2 of the largest weight kept in P
 #ifndef MF_TC_POLY_MASK
 #define MF_TC_POLY_MASK 0x00u
@@ -358,6 +361,56 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
             TC_PROF_STORE(2)
         }
+#if MF_TC_SPLIT_ISSUE
+    } else if (warp == kSoftmaxWarps + 2) {
+        // ------------------------------------------------ MMA issuer for Q K^T (split issue) ---
+        if (lane == 0) {
+            constexpr uint32_t kIdescQK = instr_desc(kBN, 0);
+            wait(bar(kQFull), 0, 32u);
+            const uint64_t q_desc = smem_desc(q_smem, 16, 1024);
+            uint32_t b = 0, ph = 0;  // tile i: buffer i % 3, phase (i / 3) & 1
+            for (uint32_t i = 0; i < n_tiles; ++i) {
+                if (i < 3) {
+                    wait(bar(kKFull + b), 0, 32u);
+                } else {
+                    wait(bar(kVFull + b), ph ^ 1, 32u);  // K(i) came with V(i - 3)
+                    wait(bar(kOFull + b), ph ^ 1, 32u);  // P V (i - 3) has read the buffer
+                }
+                tc_fence_after();
+                const uint64_t k_desc = smem_desc(k_smem + b * kTile, 16, 1024);
+#pragma unroll
+                for (uint32_t kk = 0; kk < kD / 16; ++kk) {
+                    const uint32_t off = ((kk >> 2) * kHalfTile + (kk & 3) * 32) >> 4;
+                    tc_mma_ss(tmem + b * 128, q_desc + off, k_desc + off, kIdescQK, kk > 0);
+                }
+                tc_commit(bar(kSFull + b));
+                if (++b == 3) {
+                    b = 0;
+                    ph ^= 1;
+                }
+            }
+        }
+    } else if (warp == kSoftmaxWarps + 1) {
+        // ------------------------------------------------- MMA issuer for P V (split issue) ---
+        if (lane == 0) {
+            constexpr uint32_t kIdescPV = instr_desc(kD, 1);
+            uint32_t b = 0, ph = 0;
+            for (uint32_t i = 0; i < n_tiles; ++i) {
+                wait(bar(kVFull + b), ph, 64u);
+                wait(bar(kPFull + b), ph, 64u);
+                tc_fence_after();
+                const uint64_t v_desc = smem_desc(v_smem + b * kTile, kHalfTile, 1024);
+#pragma unroll
+                for (uint32_t kk = 0; kk < kBN / 16; ++kk)
+                    tc_mma_ts(tmem + 384, tmem + b * 128 + kk * 8, v_desc + kk * (2048 >> 4), kIdescPV, (i > 0 || kk > 0) ? 1u : 0u);
+                tc_commit(bar(kOFull + b));
+                if (++b == 3) {
+                    b = 0;
+                    ph ^= 1;
+                }
+            }
+        }
+#else
     } else if (warp == kSoftmaxWarps + 1) {
         // ------------------------------------------------------------------ MMA issuer ---
         if (lane == 0) {
@@ -420,6 +473,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
             TC_PROF_STORE(1)
         }
+#endif
     } else {
         // --------------------------------------------------------- softmax groups / epilogue ---
         // One thread per query row (= TMEM lane) and group: the whole row of S is in registers, so
