@@ -54,7 +54,12 @@ namespace {
 constexpr uint32_t kBM = 128;             // query rows per CTA
 constexpr uint32_t kBN = 128;             // keys per tile
 constexpr uint32_t kD = 128;              // head_dim
-constexpr uint32_t kGroupWarps = 4;                       // softmax warps per group (one thread per row)
+#ifndef MF_TC_ROW_SPLIT
+#define MF_TC_ROW_SPLIT 1
+#endif
+constexpr uint32_t kRowSplit = MF_TC_ROW_SPLIT;           // softmax threads per query row
+constexpr uint32_t kCols = 128 / kRowSplit;               // score columns per thread
+constexpr uint32_t kGroupWarps = 4 * kRowSplit;           // softmax warps per group
 constexpr uint32_t kSoftmaxWarps = 2 * kGroupWarps;
 constexpr uint32_t kSoftmaxThreads = 32 * kSoftmaxWarps;
 constexpr uint32_t kTcThreads = kSoftmaxThreads + 64 + 32 * MF_TC_SPLIT_ISSUE;
@@ -259,7 +264,8 @@ static_assert(kKStages == 3 && kVStages == 3, "ring slot = score buffer = tile %
 
 constexpr uint32_t kSmemTiles = kTile * (1 + kKStages + kVStages);  // Q + K ring + V ring
 constexpr uint32_t kRefBytes = 128 * 4;                             // m_ref per query row
-constexpr uint32_t kSmemBytes = kSmemTiles + kRefBytes + kNumBars * 8 + 16 + 1024;
+constexpr uint32_t kXmaxBytes = 0;
+constexpr uint32_t kSmemBytes = kSmemTiles + kRefBytes + kXmaxBytes + kNumBars * 8 + 16 + 1024;
 static_assert(kSmemBytes <= 227 * 1024, "shared memory");
 
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -274,8 +280,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t v_smem = k_smem + kKStages * kTile;
     volatile float *mref = reinterpret_cast<volatile float *>(smem + kSmemTiles);
     float *lbuf = reinterpret_cast<float *>(smem);  // epilogue only: the Q tile is no longer read
-    const uint32_t bars = smem_base + kSmemTiles + kRefBytes;
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + kSmemTiles + kRefBytes + kNumBars * 8);
+    const uint32_t bars = smem_base + kSmemTiles + kRefBytes + kXmaxBytes;
+    volatile uint32_t *tmem_slot =
+        reinterpret_cast<volatile uint32_t *>(smem + kSmemTiles + kRefBytes + kXmaxBytes + kNumBars * 8);
     volatile uint32_t *abort_flag = tmem_slot + 1;
     auto bar = [&](uint32_t i) { return bars + i * 8; };
 
@@ -476,17 +483,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #endif
     } else {
         // --------------------------------------------------------- softmax groups / epilogue ---
-        // One thread per query row (= TMEM lane) and group: the whole row of S is in registers, so
-        // the row maximum and sum need no exchange inside a tile; between tiles the two groups hand
-        // the row's reference maximum to each other through shared memory.
-        const uint32_t g = warp >> 2;                           // group: tiles i = g, g + 2, ...
+        // kRowSplit threads per query row (= TMEM lane) and group, each holding 128 / kRowSplit scores of
+        // the row in registers.  With two threads per row the halves of a row swap their maxima through
+        // shared memory once per tile; between tiles the two groups hand the row's reference maximum to
+        // each other the same way.
+        const uint32_t g = warp / (4 * kRowSplit);              // group: tiles i = g, g + 2, ...
         const uint32_t quad = warp & 3;
+        const uint32_t half = (warp >> 2) % kRowSplit;          // which part of the row's columns
         const uint32_t r_in = quad * 32 + lane;                 // row inside the tile = TMEM lane
         const uint32_t row = row0 + r_in;
         const uint32_t lane_base = (quad * 32u) << 16;          // TMEM lane quadrant of this warp
         const uint32_t limit = row + p.query_offset;            // last visible key
         const uint32_t o_tm = tmem + lane_base + 384;
         const uint32_t last_ok = min(limit, p.kv_len - 1);
+        const uint32_t col0 = half * kCols;                     // this thread's S columns
+        const uint32_t pair_bar = 1 + g * 4 + quad;             // named barrier of the warps that share rows
         float my_ref = kNegInf, l_part = 0.f;                   // my_ref in the scaled log2 domain
         uint32_t last_mine = 0xFFFFFFFFu;
         TC_PROF_DECL
@@ -494,25 +505,54 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         for (uint32_t i = g; i < n_tiles; i += 2) {
             const uint32_t b = i % 3, sph = (i / 3) & 1;
             const uint32_t s_tm = tmem + lane_base + b * 128;   // S / P buffer of this tile
-            const uint32_t key0 = i * kBN;
+            const uint32_t key0 = i * kBN + col0;
             // Only tiles on the causal diagonal or at the end of the cache need a mask.
-            const uint32_t n_vis = last_ok < key0 ? 0u : min(kBN, last_ok - key0 + 1);
+            const uint32_t n_vis = last_ok < key0 ? 0u : min(kCols, last_ok - key0 + 1);
             last_mine = i;
             TC_PROF_WAIT(0, wait(bar(kSFull + b), sph, 256u))
             tc_fence_after();
             // The TMEM accesses below are warp-collective: the choice between the plain and the
             // masked form of the row must be the same for all 32 rows of the warp.
-            const bool whole = __all_sync(0xffffffffu, n_vis == kBN);
+            const bool whole = __all_sync(0xffffffffu, n_vis == kCols);
             TC_PROF_MARK(pt0)
-            uint32_t r[128];
+            float mx0 = -3.0e38f, mx1 = -3.0e38f, mx2 = -3.0e38f, mx3 = -3.0e38f;
+            if (kRowSplit == 2) {
+                // The row maximum needs the partner's columns too: stream them through registers for the
+                // maximum only (cheaper than swapping maxima through shared memory, and exact).  Their
+                // visible count follows from the same limit.
+                const uint32_t pcol0 = (half ^ 1) * kCols;
+                const uint32_t pkey0 = i * kBN + pcol0;
+                const uint32_t p_vis = last_ok < pkey0 ? 0u : min(kCols, last_ok - pkey0 + 1);
+                const bool p_whole = __all_sync(0xffffffffu, p_vis == kCols);
 #pragma unroll
-            for (uint32_t c = 0; c < 4; ++c) tmem_ld32(s_tm + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+                for (uint32_t c = 0; c < kCols / 32; ++c) {
+                    uint32_t t[32];
+                    tmem_ld32(s_tm + pcol0 + c * 32, t);
+                    tc_wait_ld();
+                    if (p_whole) {
+#pragma unroll
+                        for (uint32_t q = 0; q < 32; q += 8) {
+                            mx0 = max3(mx0, __uint_as_float(t[q]), __uint_as_float(t[q + 1]));
+                            mx1 = max3(mx1, __uint_as_float(t[q + 2]), __uint_as_float(t[q + 3]));
+                            mx2 = max3(mx2, __uint_as_float(t[q + 4]), __uint_as_float(t[q + 5]));
+                            mx3 = max3(mx3, __uint_as_float(t[q + 6]), __uint_as_float(t[q + 7]));
+                        }
+                    } else {
+#pragma unroll
+                        for (uint32_t q = 0; q < 32; ++q)
+                            if (c * 32 + q < p_vis) mx0 = fmaxf(mx0, __uint_as_float(t[q]));
+                    }
+                }
+            }
+            uint32_t r[kCols];
+#pragma unroll
+            for (uint32_t c = 0; c < kCols / 32; ++c)
+                tmem_ld32(s_tm + col0 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
             tc_wait_ld();
             // row maximum of the raw scores (the scale is positive)
-            float mx0 = -3.0e38f, mx1 = -3.0e38f, mx2 = -3.0e38f, mx3 = -3.0e38f;
             if (whole) {
 #pragma unroll
-                for (uint32_t q = 0; q < 128; q += 8) {
+                for (uint32_t q = 0; q < kCols; q += 8) {
                     mx0 = max3(mx0, __uint_as_float(r[q]), __uint_as_float(r[q + 1]));
                     mx1 = max3(mx1, __uint_as_float(r[q + 2]), __uint_as_float(r[q + 3]));
                     mx2 = max3(mx2, __uint_as_float(r[q + 4]), __uint_as_float(r[q + 5]));
@@ -520,12 +560,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
             } else {
 #pragma unroll
-                for (uint32_t q = 0; q < 128; ++q) {
+                for (uint32_t q = 0; q < kCols; ++q) {
                     if (q >= n_vis) r[q] = 0xFF800000u;  // -inf: weight exactly 0 below
                     mx0 = fmaxf(mx0, __uint_as_float(r[q]));
                 }
             }
             const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            if (kRowSplit == 2) {
+                // Both threads of a row have every score they need in registers: from here on either may
+                // overwrite the buffer with P.
+                TC_PROF_WAIT(3, named_bar_sync(pair_bar, 64))
+            }
             const float m_new = mx > -3.0e38f ? mx * p.scale_log2 : kNegInf;
             TC_PROF_MARK(pt1)
             // The reference maximum after tile i - 1, decided by the other group.
@@ -549,17 +594,30 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 tc_fence_after();
                 const float alpha = fast_exp2(m_prev - m_ref);
 #pragma unroll 1
-                for (uint32_t c = 0; c < 4; ++c) {
+                for (uint32_t c = 0; c < kCols / 32; ++c) {  // this thread's share of the row's O columns
                     uint32_t ob[32];
-                    tmem_ld32(o_tm + c * 32, ob);
+                    tmem_ld32(o_tm + col0 + c * 32, ob);
                     tc_wait_ld();
 #pragma unroll
                     for (uint32_t q = 0; q < 32; ++q) ob[q] = __float_as_uint(__uint_as_float(ob[q]) * alpha);
-                    tmem_st32(o_tm + c * 32, ob);
+                    tmem_st32(o_tm + col0 + c * 32, ob);
                 }
                 tc_wait_st();
+                // The scores are fetched again rather than kept in registers across this rare block.
+#pragma unroll
+                for (uint32_t c = 0; c < kCols / 32; ++c)
+                    tmem_ld32(s_tm + col0 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+                tc_wait_ld();
+                if (!whole) {
+#pragma unroll
+                    for (uint32_t q = 0; q < kCols; ++q)
+                        if (q >= n_vis) r[q] = 0xFF800000u;
+                }
+                // The partner warp holds the same rows, took the same decision and is in this block too:
+                // neither may write P before both have their scores back.
+                if (kRowSplit == 2) named_bar_sync(pair_bar, 64);
             }
-            mref[r_in] = m_ref;
+            if (half == 0) mref[r_in] = m_ref;  // both threads of a row reach the same decision
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(kDec + (i & 1)));  // the other group may fold in tile i + 1
@@ -569,7 +627,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_ref, -m_ref);
                 float2 acc_a = make_float2(0.f, 0.f), acc_b = make_float2(0.f, 0.f);
 #pragma unroll
-                for (uint32_t c = 0; c < 4; ++c) {
+                for (uint32_t c = 0; c < kCols / 32; ++c) {
                     uint32_t pk[16];
 #pragma unroll
                     for (uint32_t q = 0; q < 16; ++q) {
@@ -590,14 +648,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         else acc_a = __fadd2_rn(acc_a, w);
                         pk[q] = pack_f16x2(w.x, w.y);
                     }
-                    tmem_st16(s_tm + c * 16, pk);
+                    tmem_st16(s_tm + col0 / 2 + c * 16, pk);
                 }
                 const float2 acc = __fadd2_rn(acc_a, acc_b);
                 l_part += acc.x + acc.y;  // relative to my_ref
             } else {
                 float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-                for (uint32_t c = 0; c < 4; ++c) {
+                for (uint32_t c = 0; c < kCols / 32; ++c) {
                     uint32_t pk[16];
 #pragma unroll
                     for (uint32_t q = 0; q < 16; ++q) {
@@ -607,7 +665,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         sum1 += p1;
                         pk[q] = pack_f16x2(p0, p1);
                     }
-                    tmem_st16(s_tm + c * 16, pk);
+                    tmem_st16(s_tm + col0 / 2 + c * 16, pk);
                 }
                 l_part += sum0 + sum1;
             }
@@ -623,24 +681,28 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             TC_PROF_SPAN(7, pt3, pt4)
         }
 
-        // ---- normalise and write the rows out: group g takes columns [64 g, 64 g + 64) ------------
+        // ---- normalise and write the rows out: every thread takes 128 / (2 kRowSplit) columns --------
         if (last_mine != 0xFFFFFFFFu) {
-            // The product of this group's last tile; the other group waits for its own, and the
-            // tensor pipe completes them in order.
+            // The product of this group's last tile; the other group waits for its own, and both
+            // issuing threads' products on O have then completed.
             TC_PROF_WAIT(2, wait(bar(kOFull + last_mine % 3), (last_mine / 3) & 1, 128u))
         }
         named_bar_sync(9, kSoftmaxThreads);  // every product is done, every decision published
         tc_fence_after();
         const float m_fin = mref[r_in];
-        lbuf[g * 128 + r_in] = l_part * fast_exp2(my_ref - m_fin);
+        lbuf[(g * kRowSplit + half) * 128 + r_in] = l_part * fast_exp2(my_ref - m_fin);
         named_bar_sync(10, kSoftmaxThreads);
-        const float l_tot = lbuf[r_in] + lbuf[128 + r_in];
+        float l_tot = 0.f;
+#pragma unroll
+        for (uint32_t s2 = 0; s2 < 2 * kRowSplit; ++s2) l_tot += lbuf[s2 * 128 + r_in];
         const float inv = ((fabsf(l_tot) <= 3.0e38f) && fabsf(l_tot) > 1e-6f) ? 1.0f / l_tot : 0.f;
-        __half *dst = p.out + (size_t)row * p.out_stride_m + (size_t)head * p.out_stride_h + g * 64;
+        constexpr uint32_t kOutCols = 128 / (2 * kRowSplit);
+        const uint32_t oc0 = (g * kRowSplit + half) * kOutCols;
+        __half *dst = p.out + (size_t)row * p.out_stride_m + (size_t)head * p.out_stride_h + oc0;
 #pragma unroll 1
-        for (uint32_t c = 0; c < 2; ++c) {
+        for (uint32_t c = 0; c < kOutCols / 32; ++c) {
             float o[32];
-            tmem_ld32(o_tm + g * 64 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&o[0]));
+            tmem_ld32(o_tm + oc0 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&o[0]));
             tc_wait_ld();
             if (row < p.q_len) {
 #pragma unroll
