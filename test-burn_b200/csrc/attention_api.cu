@@ -79,15 +79,9 @@ mf_status decode_contiguous(MfContext *ctx, const void *q, const void *k, const 
     if (U > kMaxUniformUnits) return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "FlashDecode: %u (batch x kv head) units", U);
     const uint64_t total = (uint64_t)U * T;
     if (total > 0xFFFFFFFFull) return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "FlashDecode: too many tiles");
-    uint32_t span;
-    if (n_splits > 0) {
-        span = (T + n_splits - 1) / n_splits;
-    } else {
-        const uint32_t want = decode_cta_target((uint32_t)ctx->sm_count, decode_ctas_per_sm(ctx, D, group), total);
-        span = (uint32_t)((total + want - 1) / want);
-    }
-    span = std::max(1u, span);
-    const uint32_t n_ctas = (uint32_t)((total + span - 1) / span);
+    const uint32_t want = decode_cta_target((uint32_t)ctx->sm_count, decode_ctas_per_sm(ctx, D, group), total);
+    const UniformSplit split = uniform_split(U, T, n_splits, want);
+    const uint32_t span = split.span, n_ctas = split.n_ctas;
 
     const uint64_t slot_bytes = partial_slot_bytes(group, D);
     const uint64_t need = kCounterRegionBytes + (uint64_t)(U + n_ctas) * slot_bytes;
@@ -116,7 +110,8 @@ mf_status decode_contiguous(MfContext *ctx, const void *q, const void *k, const 
     p.uniform_kv_len = sp->kv_len;
     p.uniform_tiles = T;
     p.uniform_span = span;
-    p.uniform_total = (uint32_t)total;
+    p.uniform_parts = split.parts;
+    p.uniform_total = split.parts ? n_ctas * span : (uint32_t)total;  // the cursor turns flat / span into the CTA index
     p.q_stride_b = s->q_stride_b;
     p.q_stride_h = s->q_stride_h;
     p.out_stride_b = s->out_stride_b;

@@ -36,6 +36,21 @@ constexpr uint32_t kThreads = kConsumerThreads + 32;
 constexpr float kNegSentinel = -1e30f;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per barrier wait
 constexpr float kLn2 = 0.6931471805599453f;
+constexpr uint32_t kMergeFlight = 16;  // partials whose loads are in flight together in the merge
+
+#ifdef MF_DEC_PROFILE
+// Development aid (build with -DMF_DEC_PROFILE): global-timer stamps of one consumer thread per CTA.
+__device__ unsigned long long g_dec_prof[512 * 8];
+__device__ __forceinline__ unsigned long long dec_now()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define DEC_STAMP(k) { if (tid == 0 && blockIdx.x < 512) g_dec_prof[blockIdx.x * 8 + (k)] = dec_now(); }
+#else
+#define DEC_STAMP(k)
+#endif
 
 template <int D, int NT, int STAGES>
 struct Smem {
@@ -86,6 +101,21 @@ struct ItemCursor {
         }
         if (flat >= flat_end) return false;
         const uint32_t T = p.uniform_tiles;
+        if (p.uniform_parts) {
+            // flat / span is the CTA index: unit = cta / parts, range `cta % parts` of the unit
+            const uint32_t cta = flat / p.uniform_span;
+            const uint32_t u = cta / p.uniform_parts, part = cta - u * p.uniform_parts;
+            it.seq = u / p.n_kv_heads;
+            it.kvh = u - it.seq * p.n_kv_heads;
+            it.tile_begin = part * p.uniform_span;
+            it.tile_end = min(T, it.tile_begin + p.uniform_span);
+            it.unit = u;
+            it.n_parts = p.uniform_parts;
+            it.first_slot = u * p.uniform_parts;
+            it.slot = it.first_slot + part;
+            flat = flat_end;
+            return true;
+        }
         const uint32_t u = flat / T;
         const uint32_t tb = flat - u * T;
         const uint32_t te = min(T, tb + (flat_end - flat));
@@ -328,7 +358,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
     // ---------------------------------------------------------------- consumers ---
     // q, the new k/v, the partial slots and tickets may all have been written by the previous launch.
+    DEC_STAMP(0)
     grid_dependency_wait();
+    DEC_STAMP(1)
     float *comb = reinterpret_cast<float *>(smem + S::kOffComb);
     __half *q_s = reinterpret_cast<__half *>(smem + S::kOffQ);
     float *ml_s = reinterpret_cast<float *>(smem + S::kOffMl);
@@ -403,6 +435,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             for (int mt = 0; mt < D / 16; ++mt) o[nt][mt][0] = o[nt][mt][1] = o[nt][mt][2] = o[nt][mt][3] = 0.f;
         }
 
+        DEC_STAMP(2)
         for (uint32_t t = it.tile_begin; t < it.tile_end; ++t) {
             if (!flags[0] && !mbar_wait_bounded(bar_full + stage * 8, phase, kWaitLimitNs)) {
                 flags[0] = 1;
@@ -543,6 +576,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             }
         }
 
+        DEC_STAMP(3)
         // ---- combine the four warps' states ------------------------------------------
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -646,6 +680,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         }
 
         // ---- ticket: the CTA that completes the unit merges its partials ---------------
+        DEC_STAMP(4)
         __threadfence();
         named_bar_sync(1, kConsumerThreads);
         if (tid == 0) {
@@ -655,6 +690,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             flags[1] = last;
         }
         named_bar_sync(2, kConsumerThreads);
+        DEC_STAMP(5)
         if (!flags[1]) continue;
         __threadfence();
         // Merge (flash_prefill.metal:843-888), arranged so that the loads of one round trip are all
@@ -677,7 +713,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             red[tid * 2 + 1] = l_loc;
         }
         named_bar_sync(1, kConsumerThreads);
-        // Pass 2: one float4 column of one real head per thread and round, eight parts in flight.
+        // Pass 2: one float4 column of one real head per thread and round, kMergeFlight parts in flight.
         const uint32_t cols4 = G * (D / 4);
         for (uint32_t c4 = tid; c4 < cols4; c4 += kConsumerThreads) {
             const uint32_t g2 = c4 / (D / 4), d0 = (c4 % (D / 4)) * 4;
@@ -687,11 +723,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll
             for (uint32_t j = 0; j < kPerHead; ++j) lt += red[(j * HP + g2) * 2 + 1] * __expf(red[(j * HP + g2) * 2] - mx);
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (uint32_t s0 = 0; s0 < it.n_parts; s0 += 8) {
-                float4 v[8];
-                float w[8];
+            for (uint32_t s0 = 0; s0 < it.n_parts; s0 += kMergeFlight) {
+                float4 v[kMergeFlight];
+                float w[kMergeFlight];
 #pragma unroll
-                for (uint32_t j = 0; j < 8; ++j) {
+                for (uint32_t j = 0; j < kMergeFlight; ++j) {
                     const uint32_t sp = s0 + j;
                     if (sp < it.n_parts) {
                         const size_t sl = it.first_slot + sp;
@@ -704,7 +740,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                     }
                 }
 #pragma unroll
-                for (uint32_t j = 0; j < 8; ++j) {
+                for (uint32_t j = 0; j < kMergeFlight; ++j) {
                     acc.x += v[j].x * w[j];
                     acc.y += v[j].y * w[j];
                     acc.z += v[j].z * w[j];
@@ -740,6 +776,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             }
         }
         if (p.push_world) push_signal_and_merge<D>(p, it, tid, flags);
+        DEC_STAMP(6)
     }
 }
 
@@ -780,6 +817,13 @@ mf_status launch_one(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap 
 
 }  // namespace
 
+#ifdef MF_DEC_PROFILE
+extern "C" __attribute__((visibility("default"))) int mf_debug_dec_profile(unsigned long long *host_out, uint32_t n)
+{
+    return (int)cudaMemcpyFromSymbol(host_out, g_dec_prof, sizeof(unsigned long long) * n);
+}
+#endif
+
 uint32_t decode_ctas_per_sm(const MfContext *ctx, uint32_t head_dim, uint32_t group)
 {
     if (group > 8) return 1;
@@ -790,6 +834,38 @@ uint32_t decode_ctas_per_sm(const MfContext *ctx, uint32_t head_dim, uint32_t gr
 // Number of CTAs for `total` tiles: as many as are resident, but a span shorter than eight
 // tiles mostly pays for its own boundary (q load, combine, partial write, a longer merge), so
 // small problems get one CTA per SM.
+// A CTA that straddles two units pays the per-item work twice (q staging, combine, partial write,
+// ticket: about 3 us), and the launch ends with the slowest CTA.  When the launch is short - few tiles
+// per CTA - and there are several CTAs per unit anyway, cutting every unit on its own is cheaper than
+// perfectly equal spans.
+constexpr uint32_t kAlignMaxSpan = 32;   // tiles per CTA up to which units are cut separately
+constexpr uint32_t kAlignMinParts = 4;   // ... given at least this many CTAs per unit
+
+UniformSplit uniform_split(uint32_t units, uint32_t tiles_per_unit, uint32_t n_splits, uint32_t want_ctas)
+{
+    UniformSplit r{};
+    const uint32_t T = tiles_per_unit;
+    const uint64_t total = (uint64_t)units * T;
+    if (n_splits > 0) {
+        r.span = std::max(1u, (T + n_splits - 1) / n_splits);
+        r.parts = (T + r.span - 1) / r.span;
+        r.n_ctas = units * r.parts;
+        return r;
+    }
+    const uint32_t flat_span = std::max<uint32_t>(1, (uint32_t)((total + want_ctas - 1) / want_ctas));
+    if (want_ctas >= kAlignMinParts * units && flat_span <= kAlignMaxSpan) {
+        const uint32_t parts = std::min(want_ctas / units, T);
+        r.span = (T + parts - 1) / parts;
+        r.parts = (T + r.span - 1) / r.span;
+        r.n_ctas = units * r.parts;
+        return r;
+    }
+    r.span = flat_span;
+    r.parts = 0;
+    r.n_ctas = (uint32_t)((total + flat_span - 1) / flat_span);
+    return r;
+}
+
 uint32_t decode_cta_target(uint32_t sm_count, uint32_t ctas_per_sm, uint64_t total)
 {
     const uint64_t resident = (uint64_t)sm_count * ctas_per_sm;
@@ -834,6 +910,65 @@ void build_decode_plan(const uint32_t *kv_lens, uint32_t batch, uint32_t n_kv_he
         return;
     }
     const uint32_t n_ctas = (uint32_t)(total < max_ctas ? total : max_ctas);
+    // Short launch with several CTAs per unit: cut every unit on its own (see uniform_split).
+    uint32_t live_units = 0;
+    for (uint32_t b = 0; b < batch; ++b) live_units += kv_lens[b] ? n_kv_heads : 0;
+    if (n_ctas >= kAlignMinParts * live_units && (total + n_ctas - 1) / n_ctas <= kAlignMaxSpan) {
+        // CTAs per unit in proportion to its tiles, at least one, never more than its tiles
+        std::vector<uint32_t> parts(batch, 0);  // per sequence: the same for each of its kv heads
+        uint64_t used = 0;
+        for (uint32_t b = 0; b < batch; ++b) {
+            const uint32_t tiles = (kv_lens[b] + kTileKeys - 1) / kTileKeys;
+            if (!tiles) continue;
+            uint64_t want = (uint64_t)tiles * n_ctas / total;
+            parts[b] = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(want, 1), tiles);
+            used += (uint64_t)parts[b] * n_kv_heads;
+        }
+        // hand the CTAs left over to the sequences whose ranges are longest
+        for (;;) {
+            uint32_t best = batch;
+            double best_len = 0.0;
+            for (uint32_t b = 0; b < batch; ++b) {
+                const uint32_t tiles = (kv_lens[b] + kTileKeys - 1) / kTileKeys;
+                if (!tiles || parts[b] >= tiles) continue;
+                const double len = (double)tiles / parts[b];
+                if (len > best_len) {
+                    best_len = len;
+                    best = b;
+                }
+            }
+            if (best == batch || used + n_kv_heads > n_ctas) break;
+            ++parts[best];
+            used += n_kv_heads;
+        }
+        uint32_t slot = 0;
+        for (uint32_t b = 0; b < batch; ++b) {
+            const uint32_t tiles = (kv_lens[b] + kTileKeys - 1) / kTileKeys;
+            if (!tiles) continue;
+            const uint32_t np = parts[b], base_t = tiles / np, rem_t = tiles % np;
+            for (uint32_t kh = 0; kh < n_kv_heads; ++kh) {
+                const uint32_t first_slot = slot;
+                uint32_t t = 0;
+                for (uint32_t pi = 0; pi < np; ++pi) {
+                    const uint32_t take = base_t + (pi < rem_t ? 1 : 0);
+                    WorkItem it{};
+                    it.seq = b;
+                    it.kvh = kh;
+                    it.tile_begin = t;
+                    it.tile_end = t + take;
+                    it.slot = slot++;
+                    it.unit = b * n_kv_heads + kh;
+                    it.first_slot = first_slot;
+                    it.n_parts = np;
+                    cta_begin.push_back((uint32_t)items.size());
+                    items.push_back(it);
+                    t += take;
+                }
+            }
+        }
+        cta_begin.push_back((uint32_t)items.size());
+        return;
+    }
     const uint64_t base = total / n_ctas, rem = total % n_ctas;
     uint32_t cta = 0;
     uint64_t room = base + (0 < rem ? 1 : 0);  // tiles the current CTA can still take
@@ -1020,9 +1155,9 @@ extern "C" mf_status mf_flash_decode_static_scratch(void *cuda_stream, const voi
     const uint64_t U = (uint64_t)batch * cache_heads;
     const uint64_t total = U * T;
     if (total > 0xFFFFFFFFull) return static_fail(err, err_len, MF_ERR_OPERATION_NOT_SUPPORTED, "too many tiles");
-    const uint64_t want = decode_cta_target((uint32_t)dst.sm_count, group > 8 ? 1 : 2, total);  // as mf_flash_decode
-    const uint32_t span = (uint32_t)((total + want - 1) / want);
-    const uint32_t n_ctas = (uint32_t)((total + span - 1) / span);
+    const uint32_t want = decode_cta_target((uint32_t)dst.sm_count, group > 8 ? 1 : 2, total);  // as mf_flash_decode
+    const UniformSplit split = uniform_split((uint32_t)U, T, 0, want);
+    const uint32_t span = split.span, n_ctas = split.n_ctas;
     const uint32_t HP = 8 * ((group + 7) / 8);
     const uint64_t slots = U + n_ctas;
     const uint64_t need = (uint64_t)kStaticStatusBytes + kStaticTicketBytes + slots * HP * (D + 2) * 4;
@@ -1056,7 +1191,8 @@ extern "C" mf_status mf_flash_decode_static_scratch(void *cuda_stream, const voi
     p.uniform_kv_len = sp->kv_len;
     p.uniform_tiles = T;
     p.uniform_span = span;
-    p.uniform_total = (uint32_t)total;
+    p.uniform_parts = split.parts;
+    p.uniform_total = split.parts ? n_ctas * span : (uint32_t)total;  // the cursor turns flat / span into the CTA index
     p.q_stride_b = s->q_stride_b;
     p.q_stride_h = s->q_stride_h;
     p.out_stride_b = s->out_stride_b;

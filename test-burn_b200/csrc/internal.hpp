@@ -55,6 +55,7 @@ struct DecodeParams {
     uint32_t n_heads, n_kv_heads, group, page_size, pt_stride, batch;
     uint32_t k_rows_b, k_rows_h, v_rows_b, v_rows_h;  // contiguous: row strides
     uint32_t uniform_kv_len, uniform_tiles, uniform_span, uniform_total;
+    uint32_t uniform_parts;  // > 0: every unit is cut into this many ranges of uniform_span tiles, one CTA each
     uint32_t rope, rope_mode, append;
     uint32_t rope_position;  // contiguous mode: position of the query token
     uint32_t q_stride_b, q_stride_h, out_stride_b, out_stride_h;
@@ -173,6 +174,13 @@ void build_decode_plan(const uint32_t *kv_lens, uint32_t batch, uint32_t n_kv_he
 
 // Resident decode CTAs per SM for a head_dim / GQA group size (decode.cu).
 uint32_t decode_ctas_per_sm(const MfContext *ctx, uint32_t head_dim, uint32_t group);
+// How a decode with equal lengths is cut: parts > 0 means every (sequence, kv head) unit is cut into
+// `parts` ranges of `span` tiles, one CTA each (no CTA straddles two units); parts == 0 means equal
+// spans over the flat tile list.
+struct UniformSplit {
+    uint32_t span, n_ctas, parts;
+};
+UniformSplit uniform_split(uint32_t units, uint32_t tiles_per_unit, uint32_t n_splits, uint32_t want_ctas);
 uint32_t decode_cta_target(uint32_t sm_count, uint32_t ctas_per_sm, uint64_t total_tiles);
 
 // Launchers (decode.cu, prefill.cu, kv_append.cu).

@@ -139,3 +139,30 @@ def test_decode_plan_c3_shape(mfk):
     items, cta_begin = mfk.build_decode_plan_host(lens, 2, 296)
     check_plan(items, cta_begin, lens, 2, 296)
     assert len(items) <= 128 + 296
+
+
+@pytest.mark.parametrize("lens,n_kv_heads,max_ctas", [([8192], 8, 148), ([131072 // 8], 8, 296), ([100, 900, 2000], 2, 148),
+                                                       ([4097, 4100], 4, 148)])
+def test_decode_plan_cuts_units_separately_when_the_launch_is_short(mfk, lens, n_kv_heads, max_ctas):
+    """Few tiles per CTA and several CTAs per unit: no CTA straddles two (sequence, kv head) units (a
+    straddling CTA pays the per-item work twice and the launch ends with the slowest CTA)."""
+    lens = np.array(lens, np.uint32)
+    items, cta_begin = mfk.build_decode_plan_host(lens, n_kv_heads, max_ctas)
+    tiles = (lens.astype(np.int64) + 63) // 64
+    n_ctas = len(cta_begin) - 1
+    assert n_ctas <= max_ctas and len(items) == n_ctas
+    assert np.array_equal(cta_begin, np.arange(n_ctas + 1))  # one item per CTA
+    seen = {}
+    for i, (seq, kvh, tb, te, slot, unit, n_parts, first_slot) in enumerate(items.tolist()):
+        assert te > tb and unit == seq * n_kv_heads + kvh and slot == i
+        cov = seen.setdefault(unit, [])
+        assert tb == (cov[-1][1] if cov else 0) and first_slot == slot - len(cov)
+        cov.append((tb, te))
+    assert len(seen) == len(lens) * n_kv_heads
+    for unit, cov in seen.items():
+        assert cov[-1][1] == tiles[unit // n_kv_heads]
+        sizes = [b - a for a, b in cov]
+        assert max(sizes) - min(sizes) <= 1
+        assert all(items[i, 6] == len(cov) for i in range(len(items)) if items[i, 5] == unit)
+    # longest range within one tile of the ideal
+    assert max(items[:, 3] - items[:, 2]) <= -(-int(tiles.sum()) * n_kv_heads // n_ctas) + 1
