@@ -1,5 +1,5 @@
 // Causal chunked prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM),
-// head_dim 128, for query chunks of 64 rows or more.
+// head_dim 64 or 128, for query chunks of 64 rows or more.
 //
 // Same contract as prefill.cu (flash_prefill.metal:94-446 of the reference): key k is
 // visible to query row r iff k <= r + query_offset, f16 x f16 products accumulated in f32,
@@ -53,7 +53,6 @@ namespace {
 #endif
 constexpr uint32_t kBM = 128;             // query rows per CTA
 constexpr uint32_t kBN = 128;             // keys per tile
-constexpr uint32_t kD = 128;              // head_dim
 #ifndef MF_TC_ROW_SPLIT
 #define MF_TC_ROW_SPLIT 1
 #endif
@@ -69,7 +68,7 @@ constexpr float kRescaleThreshold = 8.0f;                 // log2 of the largest
 #endif
 constexpr uint32_t kPolyMask = MF_TC_POLY_MASK;           // which of every 8 column pairs use the FMA-pipe exp2
 constexpr uint32_t kHalfTile = 128 * 128; // bytes: 128 rows x 64 f16
-constexpr uint32_t kTile = 2 * kHalfTile; // 32 KB
+__host__ __device__ constexpr uint32_t tc_tile_bytes(uint32_t d) { return (d / 64) * kHalfTile; }  // 16 or 32 KB
 constexpr uint32_t kKStages = 3;           // K tiles in flight
 constexpr uint32_t kVStages = MF_TC_VSTAGES;  // V tiles in flight
 constexpr uint64_t kTcWaitNs = 2000000000ull;
@@ -262,16 +261,23 @@ enum Bar : uint32_t {
 };
 static_assert(kKStages == 3 && kVStages == 3, "ring slot = score buffer = tile % 3");
 
-constexpr uint32_t kSmemTiles = kTile * (1 + kKStages + kVStages);  // Q + K ring + V ring
+__host__ __device__ constexpr uint32_t tc_smem_tiles(uint32_t d) { return tc_tile_bytes(d) * (1 + kKStages + kVStages); }  // Q + K ring + V ring
 constexpr uint32_t kRefBytes = 128 * 4;                             // m_ref per query row
 constexpr uint32_t kXmaxBytes = 0;
-constexpr uint32_t kSmemBytes = kSmemTiles + kRefBytes + kXmaxBytes + kNumBars * 8 + 16 + 1024;
-static_assert(kSmemBytes <= 227 * 1024, "shared memory");
+__host__ __device__ constexpr uint32_t tc_smem_bytes(uint32_t d)
+{
+    return tc_smem_tiles(d) + kRefBytes + kXmaxBytes + kNumBars * 8 + 16 + 1024;
+}
+static_assert(tc_smem_bytes(128) <= 227 * 1024, "shared memory");
 
+template <uint32_t D>
 __global__ void __launch_bounds__(kTcThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const TcParams p)
 {
+    static_assert(D == 64 || D == 128, "head_dim");
+    constexpr uint32_t kTile = tc_tile_bytes(D);             // one Q, K or V tile: 128 rows x D f16
+    constexpr uint32_t kSmemTiles = tc_smem_tiles(D);
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -386,7 +392,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 tc_fence_after();
                 const uint64_t k_desc = smem_desc(k_smem + b * kTile, 16, 1024);
 #pragma unroll
-                for (uint32_t kk = 0; kk < kD / 16; ++kk) {
+                for (uint32_t kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = ((kk >> 2) * kHalfTile + (kk & 3) * 32) >> 4;
                     tc_mma_ss(tmem + b * 128, q_desc + off, k_desc + off, kIdescQK, kk > 0);
                 }
@@ -400,7 +406,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     } else if (warp == kSoftmaxWarps + 1) {
         // ------------------------------------------------- MMA issuer for P V (split issue) ---
         if (lane == 0) {
-            constexpr uint32_t kIdescPV = instr_desc(kD, 1);
+            constexpr uint32_t kIdescPV = instr_desc(D, 1);
             uint32_t b = 0, ph = 0;
             for (uint32_t i = 0; i < n_tiles; ++i) {
                 wait(bar(kVFull + b), ph, 64u);
@@ -422,7 +428,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // ------------------------------------------------------------------ MMA issuer ---
         if (lane == 0) {
             constexpr uint32_t kIdescQK = instr_desc(kBN, 0);
-            constexpr uint32_t kIdescPV = instr_desc(kD, 1);
+            constexpr uint32_t kIdescPV = instr_desc(D, 1);
             TC_PROF_DECL
             wait(bar(kQFull), 0, 32u);
             // The descriptors of one operand differ only in the 14-bit start-address field: build each
@@ -438,7 +444,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 TC_PROF_MARK(ma)
                 const uint64_t k_desc = smem_desc(k_smem + b * kTile, 16, 1024);
 #pragma unroll
-                for (uint32_t kk = 0; kk < kD / 16 / MF_TC_PROBE_QK_DIV; ++kk) {
+                for (uint32_t kk = 0; kk < D / 16 / MF_TC_PROBE_QK_DIV; ++kk) {
                     const uint32_t off = ((kk >> 2) * kHalfTile + (kk & 3) * 32) >> 4;
                     tc_mma_ss(tmem + b * 128, q_desc + off, k_desc + off, kIdescQK, kk > 0);
                 }
@@ -594,13 +600,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 tc_fence_after();
                 const float alpha = fast_exp2(m_prev - m_ref);
 #pragma unroll 1
-                for (uint32_t c = 0; c < kCols / 32; ++c) {  // this thread's share of the row's O columns
+                for (uint32_t c = 0; c < D / kRowSplit / 32; ++c) {  // this thread's share of the row's O columns
                     uint32_t ob[32];
-                    tmem_ld32(o_tm + col0 + c * 32, ob);
+                    tmem_ld32(o_tm + half * (D / kRowSplit) + c * 32, ob);
                     tc_wait_ld();
 #pragma unroll
                     for (uint32_t q = 0; q < 32; ++q) ob[q] = __float_as_uint(__uint_as_float(ob[q]) * alpha);
-                    tmem_st32(o_tm + col0 + c * 32, ob);
+                    tmem_st32(o_tm + half * (D / kRowSplit) + c * 32, ob);
                 }
                 tc_wait_st();
                 // The scores are fetched again rather than kept in registers across this rare block.
@@ -696,7 +702,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
         for (uint32_t s2 = 0; s2 < 2 * kRowSplit; ++s2) l_tot += lbuf[s2 * 128 + r_in];
         const float inv = ((fabsf(l_tot) <= 3.0e38f) && fabsf(l_tot) > 1e-6f) ? 1.0f / l_tot : 0.f;
-        constexpr uint32_t kOutCols = 128 / (2 * kRowSplit);
+        constexpr uint32_t kOutCols = D / (2 * kRowSplit);
         const uint32_t oc0 = (g * kRowSplit + half) * kOutCols;
         __half *dst = p.out + (size_t)row * p.out_stride_m + (size_t)head * p.out_stride_h + oc0;
 #pragma unroll 1
@@ -746,7 +752,8 @@ mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const 
 {
     *handled = false;
     const SdpaPrefillParams &b = sp.base;
-    if (b.head_dim != kD || std::max(1u, sp.split_k) != 1 || b.q_len < 64) return MF_OK;
+    const uint32_t kD = b.head_dim;
+    if ((kD != 64 && kD != 128) || std::max(1u, sp.split_k) != 1 || b.q_len < 64) return MF_OK;
     if (b.stride_k_s != kD || b.stride_v_s != kD) return MF_OK;
     if ((b.q_stride_m % 8) || (b.q_stride_h % 8) || (b.out_stride_m % 8) || (b.out_stride_h % 8)) return MF_OK;
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 15u) return MF_OK;
@@ -767,9 +774,9 @@ mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const 
     // 64 columns x 128 rows x 2 halves brings a whole tile and lands as [half][row][128 B].
     auto encode = [&](CUtensorMap *tm, const void *base, uint64_t rows, uint64_t heads, uint64_t row_stride,
                       uint64_t head_stride, uint32_t box_rows = 128) {
-        cuuint64_t gdim[4] = {64, rows, 2, heads};
+        cuuint64_t gdim[4] = {64, rows, kD / 64, heads};
         cuuint64_t gstride[3] = {row_stride * 2, 128, head_stride * 2};
-        cuuint32_t box[4] = {64, box_rows, 2, 1};
+        cuuint32_t box[4] = {64, box_rows, kD / 64, 1};
         cuuint32_t estr[4] = {1, 1, 1, 1};
         return reinterpret_cast<EncodeFn>(ctx->encode_fn)(
                    tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(base), gdim, gstride, box, estr,
@@ -793,17 +800,22 @@ mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const 
     p.out_stride_h = b.out_stride_h;
     p.out_stride_m = b.out_stride_m;
     p.scale_log2 = b.scale * 1.4426950408889634f;
-    static bool configured[64] = {};
-    if (ctx->device < 64 && !configured[ctx->device]) {
-        st = check_cuda(ctx, cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+    static bool configured[64][2] = {};
+    const int di = kD == 128 ? 1 : 0;
+    const uint32_t smem_bytes = tc_smem_bytes(kD);
+    if (ctx->device < 64 && !configured[ctx->device][di]) {
+        st = check_cuda(ctx,
+                        di ? cudaFuncSetAttribute(prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes)
+                           : cudaFuncSetAttribute(prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes),
                         "cudaFuncSetAttribute(prefill_tc)");
         if (st != MF_OK) return st;
-        configured[ctx->device] = true;
+        configured[ctx->device][di] = true;
     }
     p.n_heads = sp.n_heads;
     p.n_q_tiles = (b.q_len + kBM - 1) / kBM;
     dim3 grid(p.n_q_tiles * sp.n_heads);
-    prefill_tc_kernel<<<grid, kTcThreads, kSmemBytes, ctx->stream>>>(tm_q, tm_k, tm_v, p);
+    if (di) prefill_tc_kernel<128><<<grid, kTcThreads, smem_bytes, ctx->stream>>>(tm_q, tm_k, tm_v, p);
+    else prefill_tc_kernel<64><<<grid, kTcThreads, smem_bytes, ctx->stream>>>(tm_q, tm_k, tm_v, p);
     *handled = true;
     return check_launch(ctx, "prefill_tc_kernel");
 }

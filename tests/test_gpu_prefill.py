@@ -133,17 +133,19 @@ def test_prefill_split_k_heuristic_route(mfk, foundry):
     assert max_abs(host(out), ref) <= TOL and max_abs(host(out), gold) <= TOL
 
 
-# (n_heads, n_kv_heads, cached, m, capacity)
+# (n_heads, n_kv_heads, cached, m, capacity[, head_dim = 128])
 TC_SHAPES = [(8, 8, 0, 128, 128), (8, 8, 0, 64, 64), (24, 8, 768, 256, 1024), (6, 2, 100, 200, 333),
-             (4, 4, 1, 130, 131), (16, 2, 500, 64, 600), (3, 1, 0, 385, 400)]
+             (4, 4, 1, 130, 131), (16, 2, 500, 64, 600), (3, 1, 0, 385, 400),
+             (14, 2, 64, 130, 256, 64), (14, 14, 0, 64, 64, 64), (8, 2, 500, 200, 768, 64), (2, 1, 3, 513, 520, 64)]
 
 
 @pytest.mark.parametrize("shape", TC_SHAPES)
 def test_prefill_tcgen05_kernel(mfk, foundry, shape):
-    """The tcgen05 / TMEM kernel alone (MF_OPTION_PREFILL_IMPL = 2), head_dim 128: whole and ragged
-    tiles, prefixes that are not multiples of the tile, GQA, poisoned rows past kv_len."""
-    hq, hkv, cached, m, cap = shape
-    case = ContigCase(n_heads=hq, n_kv_heads=hkv, head_dim=128, cached=cached, m=m, capacity=cap, poison=True)
+    """The tcgen05 / TMEM kernel alone (MF_OPTION_PREFILL_IMPL = 2), head_dim 128 and 64: whole and
+    ragged tiles, prefixes that are not multiples of the tile, GQA, poisoned rows past kv_len."""
+    hq, hkv, cached, m, cap = shape[:5]
+    d = shape[5] if len(shape) > 5 else 128
+    case = ContigCase(n_heads=hq, n_kv_heads=hkv, head_dim=d, cached=cached, m=m, capacity=cap, poison=True)
     q_rot, kc, vc = case.oracle_append()
     ref, gold = oracle_prefill(case, q_rot, kc, vc)
     foundry.set_option(3, 2)
