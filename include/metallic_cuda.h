@@ -462,6 +462,20 @@ MF_API mf_status mf_paged_kv_append(MfContext *ctx, const MfPagedKv *cache, cons
 MF_API mf_status mf_kv_cache_to_pages(MfContext *ctx, const MfTensor *cache, const MfPagedKv *paged,
                                       uint32_t use_v, uint32_t seq, uint32_t len);
 
+/* Causal chunked prefill attention over the PAGES of sequence `seq` (after mf_paged_kv_append has put
+ * the chunk's rows there): the math of mf_flash_prefill (flash_prefill.metal:94-446, split-K
+ * :452-983), K/V tiles fetched page by page through the page table.  Key k is visible to query row
+ * r iff k <= r + query_offset; q rows are at q + head * q_stride_h + r * q_stride_m (elements), out
+ * likewise; kv_len keys of the sequence are attended.  No counterpart in the reference. */
+typedef struct MfPagedPrefillArgs {
+    const void *q;
+    void *out;
+    uint32_t seq, q_len, kv_len, query_offset, n_heads;
+    uint32_t q_stride_h, q_stride_m, out_stride_h, out_stride_m;
+    float scale;
+} MfPagedPrefillArgs;
+MF_API mf_status mf_paged_prefill(MfContext *ctx, const MfPagedKv *cache, const MfPagedPrefillArgs *args);
+
 /* Debug/oracle gather: first `len` tokens of sequence `seq` -> [Hkv, len, D]. */
 MF_API mf_status mf_paged_gather(MfContext *ctx, const MfPagedKv *cache, uint32_t use_v,
                                  uint32_t seq, uint32_t len, void *out);

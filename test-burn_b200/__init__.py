@@ -111,6 +111,12 @@ class MfPagedDecodeArgs(C.Structure):
                 ("n_heads", u32), ("rope", u32), ("rope_mode", u32), ("append", u32), ("scale", C.c_float)]
 
 
+class MfPagedPrefillArgs(C.Structure):
+    _fields_ = [("q", vp), ("out", vp), ("seq", u32), ("q_len", u32), ("kv_len", u32), ("query_offset", u32),
+                ("n_heads", u32), ("q_stride_h", u32), ("q_stride_m", u32), ("out_stride_h", u32), ("out_stride_m", u32),
+                ("scale", C.c_float)]
+
+
 class MfPeerExchange(C.Structure):
     _fields_ = [("recv", vp * 8), ("counters", vp * 8), ("mapping", vp * 8), ("world", u32), ("rank", u32),
                 ("rows", u32), ("head_dim", u32)]
@@ -185,6 +191,7 @@ _SIGNATURES = {
     "mf_prefix_cache_entries": (u32, [vp]),
     "mf_prefix_cache_store": (C.c_int32, [vp, vp, u32, C.c_char_p, vp, u32]),
     "mf_prefix_cache_lookup": (C.c_int32, [vp, vp, u32, C.c_char_p, C.POINTER(u32), vp, u32, C.POINTER(u32)]),
+    "mf_paged_prefill": (C.c_int32, [vp, C.POINTER(MfPagedKv), C.POINTER(MfPagedPrefillArgs)]),
     "mf_paged_copy_pages": (C.c_int32, [vp, C.POINTER(MfPagedKv), vp, vp, u32]),
     "mf_peer_exchange_create": (C.c_int32, [vp, u32, u32, u32, u32, C.POINTER(MfPeerExchange), vp]),
     "mf_peer_exchange_attach": (C.c_int32, [vp, C.POINTER(MfPeerExchange), u32, vp]),
@@ -422,6 +429,18 @@ class Foundry:
         arr = (u32 * 8)(*list(units_per_rank) + [0] * (8 - len(units_per_rank)))
         self.check(lib.mf_merge_pushed(self._h, C.byref(px), arr, step, rows, head_dim, _ptr(out)))
 
+    def paged_prefill(self, cache: MfPagedKv, q, out, *, seq, q_len, kv_len, query_offset, n_heads, scale=None,
+                      q_stride_h=None, q_stride_m=None, out_stride_h=None, out_stride_m=None):
+        """Causal prefill attention over the pages of one sequence; q head-major [Hq, M, D] and out token-major
+        [M, Hq*D] unless strides say otherwise."""
+        d = cache.head_dim
+        scale = 1.0 / math.sqrt(d) if scale is None else scale
+        a = MfPagedPrefillArgs(_ptr(q), _ptr(out), seq, q_len, kv_len, query_offset, n_heads,
+                               q_len * d if q_stride_h is None else q_stride_h, d if q_stride_m is None else q_stride_m,
+                               d if out_stride_h is None else out_stride_h,
+                               n_heads * d if out_stride_m is None else out_stride_m, scale)
+        self.check(lib.mf_paged_prefill(self._h, C.byref(cache), C.byref(a)))
+
     def paged_copy_pages(self, cache: MfPagedKv, src_ids, dst_ids, n: int):
         """dst page <- src page for all kv heads of both pools; ids are device int32/uint32 tensors."""
         self.check(lib.mf_paged_copy_pages(self._h, C.byref(cache), _ptr(src_ids), _ptr(dst_ids), n))
@@ -577,8 +596,10 @@ class DecodePlan:
 def paged_kv(k_pool, v_pool, page_table, kv_lens, *, n_kv_heads, page_size, head_dim) -> MfPagedKv:
     """Describe torch-owned pools [n_pages, Hkv, P, D] and a [batch, stride] page table."""
     n_pages = k_pool.shape[0]
-    return MfPagedKv(k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(), kv_lens.data_ptr(), n_pages,
+    desc = MfPagedKv(k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(), kv_lens.data_ptr(), n_pages,
                      n_kv_heads, page_size, head_dim, page_table.shape[1], page_table.shape[0])
+    desc._keep = (k_pool, v_pool, page_table, kv_lens)  # the descriptor holds raw pointers: keep their owners alive
+    return desc
 
 
 def rope_tables(rope_base: float, head_dim: int, n_pos: int, first_pos: int = 0, freq_factors=None):

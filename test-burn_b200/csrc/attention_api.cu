@@ -11,7 +11,7 @@
 namespace mf {
 
 mf_status launch_prefill(MfContext *ctx, const void *q, const void *k, const void *v, void *out,
-                         const SdpaPrefillSplitKParams &p);
+                         const SdpaPrefillSplitKParams &sp, const MfPagedKv *paged = nullptr, uint32_t seq = 0);
 
 namespace {
 
@@ -651,6 +651,34 @@ static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, con
 mf_status mf_paged_decode(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv *cache, const MfPagedDecodeArgs *args)
 {
     return paged_decode_common(ctx, plan, cache, args, nullptr, nullptr, nullptr, nullptr);
+}
+
+mf_status mf_paged_prefill(MfContext *ctx, const MfPagedKv *cache, const MfPagedPrefillArgs *a)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!cache || !cache->k_pool || !cache->v_pool || !cache->page_table || !a || !a->q || !a->out)
+        return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged prefill: null input");
+    if (a->q_len == 0 || a->kv_len == 0) return MF_OK;
+    if (a->n_heads == 0 || cache->n_kv_heads == 0 || a->n_heads % cache->n_kv_heads != 0)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "paged prefill: n_heads %u, n_kv_heads %u", a->n_heads, cache->n_kv_heads);
+    SdpaPrefillSplitKParams pp{};
+    SdpaPrefillParams &b = pp.base;
+    const uint32_t D = cache->head_dim;
+    b.kv_len = a->kv_len;
+    b.head_dim = D;
+    b.scale = a->scale;
+    b.stride_k_s = D;
+    b.stride_v_s = D;
+    b.query_offset = a->query_offset;
+    b.q_stride_h = a->q_stride_h;
+    b.q_stride_m = a->q_stride_m;
+    b.out_stride_h = a->out_stride_h;
+    b.out_stride_m = a->out_stride_m;
+    b.group_size = a->n_heads / cache->n_kv_heads;
+    b.q_len = a->q_len;
+    pp.n_heads = a->n_heads;
+    pp.split_k = effective_prefill_split_k(ctx, a->kv_len, a->q_len, a->n_heads);
+    return launch_prefill(ctx, a->q, nullptr, nullptr, a->out, pp, cache, a->seq);
 }
 
 mf_status mf_paged_decode_partial_push(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv *cache,

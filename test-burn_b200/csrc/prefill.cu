@@ -39,6 +39,9 @@ struct PrefillParams {
     uint32_t k_rows_h, v_rows_h;  // cache rows per head
     uint32_t n_heads, split_k, keys_per_split;
     float scale_log2;
+    // Paged cache: the sequence's page ids (device), tokens per page, kv heads; null for a contiguous cache.
+    const uint32_t *page_table_row;
+    uint32_t page_size, n_kv_heads;
 };
 
 __device__ __forceinline__ uint32_t pf_tile_off(uint32_t row, uint32_t c16)
@@ -97,14 +100,33 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
                     atomicOr(p.status, 4u);
                 }
                 const uint32_t full = bar_full + stage * 8;
-                mbar_arrive_expect_tx(full, kStageBytes);
                 const uint32_t dst_k = smem_base + stage * kStageBytes, dst_v = dst_k + kTileBytes;
-                const int32_t rk = (int32_t)(kvh * p.k_rows_h + t * kTileKeys);
-                const int32_t rv = (int32_t)(kvh * p.v_rows_h + t * kTileKeys);
+                if (p.page_table_row) {
+                    // one box per page (or per 64 rows of a larger page) and 64-column half; pages past the
+                    // last key are not fetched: their rows are masked, and cleared in V, by the consumers
+                    const uint32_t rpb = min(p.page_size, kTileKeys), n_box = kTileKeys / rpb;
+                    uint32_t live = 0;
+                    for (uint32_t j = 0; j < n_box; ++j) live += (t * kTileKeys + j * rpb < p.kv_len) ? 1u : 0u;
+                    mbar_arrive_expect_tx(full, live * rpb * D * 4);
+                    for (uint32_t j = 0; j < live; ++j) {
+                        const uint32_t tok = t * kTileKeys + j * rpb;
+                        const uint32_t page = __ldg(p.page_table_row + tok / p.page_size);
+                        const int32_t r = (int32_t)((page * p.n_kv_heads + kvh) * p.page_size + tok % p.page_size);
 #pragma unroll
-                for (int h = 0; h < D / 64; ++h) {
-                    tma_load_2d(dst_k + h * kHalfBytes, &tm_k, h * 64, rk, full);
-                    tma_load_2d(dst_v + h * kHalfBytes, &tm_v, h * 64, rv, full);
+                        for (int h = 0; h < D / 64; ++h) {
+                            tma_load_2d(dst_k + h * kHalfBytes + j * rpb * 128, &tm_k, h * 64, r, full);
+                            tma_load_2d(dst_v + h * kHalfBytes + j * rpb * 128, &tm_v, h * 64, r, full);
+                        }
+                    }
+                } else {
+                    mbar_arrive_expect_tx(full, kStageBytes);
+                    const int32_t rk = (int32_t)(kvh * p.k_rows_h + t * kTileKeys);
+                    const int32_t rv = (int32_t)(kvh * p.v_rows_h + t * kTileKeys);
+#pragma unroll
+                    for (int h = 0; h < D / 64; ++h) {
+                        tma_load_2d(dst_k + h * kHalfBytes, &tm_k, h * 64, rk, full);
+                        tma_load_2d(dst_v + h * kHalfBytes, &tm_v, h * 64, rv, full);
+                    }
                 }
                 ++issued;
                 if (++stage == STAGES) {
@@ -351,7 +373,7 @@ mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const 
                             const SdpaPrefillSplitKParams &sp, bool *handled);
 
 mf_status launch_prefill(MfContext *ctx, const void *q, const void *k, const void *v, void *out,
-                         const SdpaPrefillSplitKParams &sp)
+                         const SdpaPrefillSplitKParams &sp, const MfPagedKv *paged, uint32_t seq)
 {
     const SdpaPrefillParams &b = sp.base;
     const uint32_t D = b.head_dim;
@@ -362,14 +384,26 @@ mf_status launch_prefill(MfContext *ctx, const void *q, const void *k, const voi
     if (b.q_len == 0 || b.kv_len == 0 || sp.n_heads == 0) return MF_OK;
     if (b.group_size == 0 || sp.n_heads % b.group_size != 0)
         return fail(ctx, MF_ERR_INVALID_SHAPE, "Prefill: n_heads %u / group_size %u", sp.n_heads, b.group_size);
-    if (b.k_stride_h % D || b.v_stride_h % D)
-        return fail(ctx, MF_ERR_INVALID_SHAPE, "Prefill: K/V head strides must be multiples of head_dim");
-    if ((uint64_t)b.kv_len * D > b.k_stride_h || (uint64_t)b.kv_len * D > b.v_stride_h)
-        return fail(ctx, MF_ERR_INVALID_OPERATION, "Prefill: kv_len %u exceeds the cache capacity", b.kv_len);
+    if (paged) {
+        const uint32_t P = paged->page_size;
+        if (P < 8 || (P & (P - 1)) != 0)
+            return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "Paged prefill: page size %u (power of two >= 8)", P);
+        if (seq >= paged->batch) return fail(ctx, MF_ERR_INVALID_OPERATION, "Paged prefill: sequence %u of %u", seq, paged->batch);
+        if (((uint64_t)b.kv_len + P - 1) / P > paged->page_table_stride)
+            return fail(ctx, MF_ERR_INVALID_OPERATION, "Paged prefill: kv_len %u exceeds the page table", b.kv_len);
+        if (paged->head_dim != D || sp.n_heads / b.group_size != paged->n_kv_heads)
+            return fail(ctx, MF_ERR_INVALID_SHAPE, "Paged prefill: cache is %u kv heads x %u, call has %u x %u", paged->n_kv_heads,
+                        paged->head_dim, sp.n_heads / b.group_size, D);
+    } else {
+        if (b.k_stride_h % D || b.v_stride_h % D)
+            return fail(ctx, MF_ERR_INVALID_SHAPE, "Prefill: K/V head strides must be multiples of head_dim");
+        if ((uint64_t)b.kv_len * D > b.k_stride_h || (uint64_t)b.kv_len * D > b.v_stride_h)
+            return fail(ctx, MF_ERR_INVALID_OPERATION, "Prefill: kv_len %u exceeds the cache capacity", b.kv_len);
+    }
     if ((b.q_stride_h | b.q_stride_m) & 1u || (b.out_stride_h | b.out_stride_m) & 1u ||
         (reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 3u)
         return fail(ctx, MF_ERR_INVALID_SHAPE, "Prefill: q/output strides must be even and pointers 4-byte aligned");
-    if (ctx->prefill_impl != 1) {
+    if (ctx->prefill_impl != 1 && !paged) {
         // tcgen05 / TMEM kernel for head_dim 128, unsplit, chunks of 64 rows or more
         bool handled = false;
         mf_status st_tc = launch_prefill_tc(ctx, q, k, v, out, sp, &handled);
@@ -414,8 +448,18 @@ mf_status launch_prefill(MfContext *ctx, const void *q, const void *k, const voi
         p.part_l = p.part_m + rows;
     }
     CUtensorMap tm_k, tm_v;
-    if ((st = get_tensor_map(ctx, k, (uint64_t)cache_heads * p.k_rows_h, D, kTileKeys, 64, &tm_k)) != MF_OK) return st;
-    if ((st = get_tensor_map(ctx, v, (uint64_t)cache_heads * p.v_rows_h, D, kTileKeys, 64, &tm_v)) != MF_OK) return st;
+    if (paged) {
+        p.page_table_row = paged->page_table + (size_t)seq * paged->page_table_stride;
+        p.page_size = paged->page_size;
+        p.n_kv_heads = paged->n_kv_heads;
+        const uint64_t rows = (uint64_t)paged->n_pages * paged->n_kv_heads * paged->page_size;
+        const uint32_t box_rows = std::min(paged->page_size, kTileKeys);
+        if ((st = get_tensor_map(ctx, paged->k_pool, rows, D, box_rows, 64, &tm_k)) != MF_OK) return st;
+        if ((st = get_tensor_map(ctx, paged->v_pool, rows, D, box_rows, 64, &tm_v)) != MF_OK) return st;
+    } else {
+        if ((st = get_tensor_map(ctx, k, (uint64_t)cache_heads * p.k_rows_h, D, kTileKeys, 64, &tm_k)) != MF_OK) return st;
+        if ((st = get_tensor_map(ctx, v, (uint64_t)cache_heads * p.v_rows_h, D, kTileKeys, 64, &tm_v)) != MF_OK) return st;
+    }
     dim3 grid(q_tiles, sp.n_heads, split_k);
     st = (D == 128) ? launch_pf<128, 4>(ctx, tm_k, tm_v, p, grid) : launch_pf<64, 4>(ctx, tm_k, tm_v, p, grid);
     if (st != MF_OK || split_k == 1) return st;

@@ -163,8 +163,8 @@ def test_prefix_pages_shared_between_sequences(mfk, foundry):
     assert matched == n_prefix and shared.tolist() == a_pages.tolist()
     # the new sequence will append at row 40, inside the last shared page: copy it first
     private = pool.alloc(1)
-    desc0 = mfk.paged_kv(dk, dv, dev_u32(np.zeros((1, 1), np.uint32)), dev_u32(np.zeros(1, np.uint32)), n_kv_heads=hkv,
-                         page_size=P, head_dim=d)
+    t0, l0 = dev_u32(np.zeros((1, 1), np.uint32)), dev_u32(np.zeros(1, np.uint32))  # kept alive: the descriptor holds pointers
+    desc0 = mfk.paged_kv(dk, dv, t0, l0, n_kv_heads=hkv, page_size=P, head_dim=d)
     foundry.paged_copy_pages(desc0, dev_u32(shared[-1:]), dev_u32(private), 1)
     pool.release(shared[-1:])
     b_pages = np.concatenate([shared[:-1], private])
