@@ -615,9 +615,11 @@ CONTIGUOUS = {
     # the reference's own layout and op order: contiguous cache [Hkv, capacity, D] per layer, KvPrepFused then
     # FlashAttention (decode route), batch 1
     "c1": dict(layers=1, n_heads=14, n_kv_heads=2, head_dim=64, cached=511, capacity=512, theta=1e6, rope_mode=0,
+               hidden=896, qkv_bias=True,
                name="single-token latency, Qwen2.5-0.5B shape: 1 layer, 14q/2kv heads, D64, batch 1, 511 cached + 1, "
                     "contiguous cache, KvPrepFused then FlashAttention (2 launches)"),
     "c2": dict(layers=28, n_heads=24, n_kv_heads=8, head_dim=128, cached=8191, capacity=8192, theta=5e5, rope_mode=1,
+               hidden=3072, qkv_bias=False,
                name="Llama-3.2-3B shape decode step: 28 layers, 24q/8kv heads, D128, batch 1, ctx 8192, contiguous "
                     "cache, KvPrepFused then FlashAttention per layer (56 launches)"),
 }
@@ -651,9 +653,29 @@ def run_contiguous_decode(args, w):
         f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 1)
     p = mfk.KvPrepFusedParamsResolved(hq * d, hkv * d, d, hq, hkv, hq // hkv, 1, cached, cap, hq * d, w["rope_mode"], 0, 0)
 
+    qkv_args, weight_bytes = None, 0
+    if args.projection:
+        # the step in front of the path as well: RMSNorm + fused Q/K/V projection (f16 weights in the
+        # reference's blocked layout) + RoPE + append in one launch, then FlashAttention
+        hidden = w["hidden"]
+        x = torch.empty((1, hidden), dtype=torch.float16, device=dev).normal_(generator=g)
+        gamma = torch.empty((hidden,), dtype=torch.float16, device=dev).uniform_(0.5, 1.5, generator=g)
+        qkv_args = []
+        for _ in range(layers):
+            ws = [torch.empty((n * hidden,), dtype=torch.float16, device=dev).uniform_(-0.05, 0.05, generator=g)
+                  for n in (hq * d, hkv * d, hkv * d)]
+            bias = tuple(torch.empty((n,), dtype=torch.float16, device=dev).uniform_(-0.1, 0.1, generator=g)
+                         for n in (hq * d, hkv * d, hkv * d)) if w["qkv_bias"] else None
+            qkv_args.append(f.fused_qkv_args(x, *ws, k_dim=hidden, n_dim=hq * d, n_kv=hkv * d, m=1, gamma=gamma, bias=bias,
+                                             weights_per_block=32))
+        weight_bytes = (hq + 2 * hkv) * d * hidden * 2
+
     def step():
         for i in range(layers):
-            f.kv_prep_fused(q[i], k[i], v[i], q_rot[i], kcs[i], vcs[i], cos, sin, p)
+            if qkv_args is not None:
+                f.fused_qkv_kv_prep(qkv_args[i], q_rot[i], kcs[i], vcs[i], cos, sin, p)
+            else:
+                f.kv_prep_fused(q[i], k[i], v[i], q_rot[i], kcs[i], vcs[i], cos, sin, p)
             f.flash_attention(q_rot[i], kcs[i], vcs[i], out[i], causal=True, query_offset=cached, n_heads=hq, head_dim=d,
                               kv_seq_len=cached + 1, m=1)
 
@@ -709,6 +731,7 @@ def run_contiguous_decode(args, w):
     eager_med = float(np.median(us))
     med = graph_us["median"] if "median" in graph_us else eager_med  # the device-side figure when it exists
     bytes_layer = 2 * hkv * (cached + 1) * d * 2 + 4 * hkv * d * 2 + 2 * hq * d * 2 + 2 * (d // 2) * 2
+    bytes_layer += weight_bytes
     peak, peak_kind = measured_peak_gbs()
     achieved = bytes_layer * layers / (med * 1e-6) / 1e9
     l2_note = ("L2-resident by construction (0.27 MB): latency only, not a bandwidth figure" if layers == 1 else
@@ -718,7 +741,9 @@ def run_contiguous_decode(args, w):
         "metric": METRIC, "value": 1e6 / med, "unit": "tokens/s", "n_gpus": 1, "steps": iters * trials,
         "warmup": max(args.warmup, 3), "ms_per_step": med * 1e-3, "us_per_step": med, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
-        "config": {"workload": w["name"], "l2": l2_note,
+        "config": {"workload": w["name"] + ("; with --projection the first launch of a layer is RMSNorm + fused QKV "
+                                            "projection + RoPE + append (weights %.1f MB per layer)" % (weight_bytes / 1e6)
+                                            if args.projection else ""), "l2": l2_note,
                    "timing": "value / us_per_step = CUDA-graph replay of the step when capture works, else eager"},
         "latency_us": {"trials": trials, "iterations": iters, "min": float(us.min()), "median": eager_med,
                        "mean": float(us.mean()), "sd": float(us.std()),
@@ -727,7 +752,8 @@ def run_contiguous_decode(args, w):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": peak_kind, "traffic": None, "launch_us": med / layers,
                      "algorithmic_bytes_per_launch": bytes_layer,
-                     "note": "launch-bound" if layers == 1 else "per layer: kv_append_kernel + decode_kernel"},
+                     "note": "launch-bound" if layers == 1 else "per layer: %s + decode_kernel" %
+                             ("fused_qkv_kernel" if args.projection else "kv_append_kernel")},
         "gpu_launches": launches, "clocks": clocks, "self_check": "ok" if ok else "FAILED"}))
     f.close()
     return 0 if ok else 1
@@ -812,6 +838,9 @@ def main():
                     help="long-context workloads: partials exchanged and merged inside the decode kernel (fused), "
                          "exchanged by the decode kernel and merged by a second one (push), or by ncclAllGather")
     ap.add_argument("--no-overlap", action="store_true", help="plain launches instead of programmatic dependent launch")
+    ap.add_argument("--projection", action="store_true",
+                    help="c1 / c2: start each layer from the hidden state (RMSNorm + fused QKV projection + RoPE + append "
+                         "in one launch) instead of from q, k, v")
     ap.add_argument("--prefill-impl", type=int, default=0, help="prefill kernel selector (experiments)")
     ap.add_argument("--stages", type=int, default=0, help="decode ring depth (experiments)")
     ap.add_argument("--page-size", type=int, default=0, help="override the workload's page size (experiments)")

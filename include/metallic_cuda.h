@@ -456,6 +456,45 @@ MF_API mf_status mf_paged_kv_append(MfContext *ctx, const MfPagedKv *cache, cons
                                     uint32_t apply_rope, uint32_t seq, uint32_t position_offset,
                                     uint32_t seq_len);
 
+/* ------------------------------------------- projection in front of the append --- */
+
+/* "FusedQkv" (src/metals/gemv/qkv_step.rs:14-37,59-101; qkv_project.metal:4-272), f16 weights
+ * (the reference's F16 policy; its block-quantised policies are not built):
+ *   inv_rms = 1 / sqrt(mean(x^2) + epsilon), xn = f16((x * inv_rms) * gamma)   (gamma NULL: xn = x)
+ *   out_q[r] = f16(sum_k xn[k] * Wq[r, k] + bias_q[r]), same for K and V        (bias NULL: none)
+ * input [m, k_dim], out_q [m, n_dim], out_k / out_v [m, n_kv], all f16 row-major.
+ * weights_per_block == 0: weights row-major [N, k_dim]; 32: the reference's blocked layout, element
+ * (r, k) at (k % 32) + 32 * (r + (k / 32) * N) (compound/stages/layout.rs:100).  k_dim must be a
+ * multiple of 32, n_dim and n_kv multiples of 16.  Sums are f32 in a fixed order that does not depend
+ * on m or on which entry point runs, so the three functions below produce the same bits. */
+typedef struct MfFusedQkvArgs {
+    const void *input;
+    const void *w_q, *w_k, *w_v;
+    const void *gamma;                      /* f16 [k_dim] or NULL */
+    const void *bias_q, *bias_k, *bias_v;   /* f16, all three or none */
+    void *out_q, *out_k, *out_v;            /* may be NULL in the two append forms */
+    uint32_t k_dim, n_dim, n_kv, m;
+    uint32_t weights_per_block;
+    float epsilon;
+} MfFusedQkvArgs;
+MF_API mf_status mf_fused_qkv(MfContext *ctx, const MfFusedQkvArgs *args);
+
+/* FusedQkv followed by KvPrepFused in ONE launch: the projected rows never reach memory as q/k/v
+ * (unless out_* are given); each is rounded to f16 exactly as the two-launch sequence would store
+ * it, rotated, and written to q_rot / the caches.  Same bits as mf_fused_qkv then mf_kv_prep_fused.
+ * args->m = params->seq_len, n_dim = n_heads*head_dim, n_kv = n_kv_heads*head_dim.  No counterpart
+ * in the reference, which runs the two steps back to back (models/qwen25.json layer block). */
+MF_API mf_status mf_fused_qkv_kv_prep(MfContext *ctx, const MfFusedQkvArgs *args, const MfTensor *q_rot,
+                                      const MfTensor *k_cache, const MfTensor *v_cache,
+                                      const MfTensor *cos, const MfTensor *sin,
+                                      const KvPrepFusedParamsResolved *params);
+
+/* The same in front of a paged cache: arguments after `args` as mf_paged_kv_append (seq_len = args->m). */
+MF_API mf_status mf_fused_qkv_paged_append(MfContext *ctx, const MfFusedQkvArgs *args,
+                                           const MfPagedKv *cache, void *q_rot, const void *cos,
+                                           const void *sin, uint32_t n_heads, uint32_t rope_mode,
+                                           uint32_t apply_rope, uint32_t seq, uint32_t position_offset);
+
 /* Migration of a contiguous compact cache [Hkv, capacity, D] into the pages of sequence
  * `seq`: rows [0, len) of every kv head (K pool when use_v == 0, V pool otherwise).  No
  * counterpart in the reference; the inverse of mf_paged_gather. */

@@ -77,6 +77,8 @@ def lib() -> C.CDLL:
     L.mfo_paged_scatter.argtypes = [u16p, u16p, u32p, u32, u32, u32, u32, u32]
     L.mfo_kv_prep_fused.argtypes = [u16p, u16p, u16p, u16p, u16p, u16p, u16p, u16p,
                                     C.POINTER(KvPrepParams), C.c_int]
+    L.mfo_fused_qkv.argtypes = [u16p, u16p, u16p, u16p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, u32, u32, u32,
+                                u32, u32, C.c_float, u16p, u16p, u16p]
     L.mfo_paged_kv_append.argtypes = [u16p, u16p, u16p, u16p, u16p, u16p, u16p, u16p, u32p, u32,
                                       u32p, u32, u32, u32, u32, u32, u32, C.c_int]
     L.mfo_paged_gather.argtypes = [u16p, u32p, u32, u32, u32, u32, u16p]
@@ -144,6 +146,18 @@ def kv_prep_fused(q, k, v, k_cache, v_cache, cos, sin, *, n_heads, n_kv_heads, h
     q_rot = np.empty(n_heads * seq_len * head_dim, np.uint16)
     lib().mfo_kv_prep_fused(q, k, v, q_rot, k_cache, v_cache, cos, sin, C.byref(p), int(expanded))
     return q_rot
+
+
+def fused_qkv(x, w_q, w_k, w_v, *, m, k_dim, n_dim, n_kv, gamma=None, b_q=None, b_k=None, b_v=None,
+              weights_per_block=0, eps=1e-6):
+    """RMSNorm -> Q/K/V projection (+bias) as the reference's FusedQkv computes it
+    (src/metals/gemv/qkv_project.metal:4-272).  All arrays are f16 bit patterns (uint16)."""
+    q = np.empty(m * n_dim, np.uint16)
+    k = np.empty(m * n_kv, np.uint16)
+    v = np.empty(m * n_kv, np.uint16)
+    lib().mfo_fused_qkv(x, w_q, w_k, w_v, _ptr(gamma), _ptr(b_q), _ptr(b_k), _ptr(b_v), m, k_dim, n_dim, n_kv,
+                        weights_per_block, eps, q, k, v)
+    return q, k, v
 
 
 def decode_online(q_rot, k_cache, v_cache, *, n_heads, cache_heads, head_dim, capacity, kv_len,

@@ -284,6 +284,45 @@ static inline uint16_t rope_elem(const uint16_t *x, const uint16_t *c_row, const
     return mfo_f32_to_f16(r);
 }
 
+static void project_rows(const uint16_t *xn, const uint16_t *w, const uint16_t *bias, uint32_t k_dim,
+                         uint32_t n, uint32_t wpb, uint16_t *out)
+{
+    for (uint32_t r = 0; r < n; ++r) {
+        float acc = 0.0f;
+        for (uint32_t k = 0; k < k_dim; ++k) {
+            size_t idx = wpb ? (size_t)(k % wpb) + (size_t)wpb * (r + (size_t)(k / wpb) * n)
+                             : (size_t)r * k_dim + k;
+            acc += H2F(xn[k]) * H2F(w[idx]);
+        }
+        out[r] = mfo_f32_to_f16(acc + (bias ? H2F(bias[r]) : 0.0f));
+    }
+}
+
+void mfo_fused_qkv(const uint16_t *input, const uint16_t *w_q, const uint16_t *w_k,
+                   const uint16_t *w_v, const uint16_t *gamma, const uint16_t *b_q,
+                   const uint16_t *b_k, const uint16_t *b_v, uint32_t m, uint32_t k_dim,
+                   uint32_t n_dim, uint32_t n_kv, uint32_t weights_per_block, float eps,
+                   uint16_t *out_q, uint16_t *out_k, uint16_t *out_v)
+{
+    h2f_init();
+    uint16_t *xn = (uint16_t *)malloc((size_t)k_dim * sizeof(uint16_t));
+    for (uint32_t row = 0; row < m; ++row) {
+        const uint16_t *x = input + (size_t)row * k_dim;
+        if (gamma) {
+            float sum_sq = 0.0f;
+            for (uint32_t k = 0; k < k_dim; ++k) sum_sq += H2F(x[k]) * H2F(x[k]);
+            const float inv_rms = 1.0f / sqrtf(sum_sq / (float)k_dim + eps);
+            for (uint32_t k = 0; k < k_dim; ++k) xn[k] = mfo_f32_to_f16((H2F(x[k]) * inv_rms) * H2F(gamma[k]));
+        } else {
+            memcpy(xn, x, (size_t)k_dim * sizeof(uint16_t));
+        }
+        project_rows(xn, w_q, b_q, k_dim, n_dim, weights_per_block, out_q + (size_t)row * n_dim);
+        project_rows(xn, w_k, b_k, k_dim, n_kv, weights_per_block, out_k + (size_t)row * n_kv);
+        project_rows(xn, w_v, b_v, k_dim, n_kv, weights_per_block, out_v + (size_t)row * n_kv);
+    }
+    free(xn);
+}
+
 void mfo_kv_prep_fused(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t *q_rot,
                        uint16_t *k_cache, uint16_t *v_cache, const uint16_t *cos_t,
                        const uint16_t *sin_t, const mfo_kv_prep_params *p, int expanded)

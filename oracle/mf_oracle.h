@@ -102,6 +102,21 @@ void mfo_paged_scatter(const uint16_t *cache, uint16_t *pool, const uint32_t *pa
 void mfo_repeat_kv_heads(const uint16_t *in, uint16_t *out, uint32_t n_kv_heads,
                          uint32_t group_size, uint32_t seq, uint32_t head_dim);
 
+/* ---- fused QKV projection (src/metals/gemv/qkv_project.metal:4-272,
+ *      src/metals/rmsnorm/rmsnorm.metal:18-95; CPU checks in tests/qkv_parity_f16.rs:18-69
+ *      and tests/fused_qkv_batched_rmsnorm_parity.rs:23-56) ------------------------------
+ * For each of the m rows of input [m, k_dim]:
+ *   inv_rms = 1 / sqrt(sum(x^2) / k_dim + eps)            (f32, skipped when gamma == NULL)
+ *   xn[k]   = f16((x[k] * inv_rms) * gamma[k])            (xn = x without gamma)
+ *   out[r]  = f16(sum_k xn[k] * W[r, k] + bias[r])        (f32 sum in k order; bias may be NULL)
+ * weights_per_block == 0: W row-major [N, k_dim]; otherwise the reference's blocked
+ * ("canonical") layout: element (r, k) at (k % wpb) + wpb * (r + (k / wpb) * N). */
+void mfo_fused_qkv(const uint16_t *input, const uint16_t *w_q, const uint16_t *w_k,
+                   const uint16_t *w_v, const uint16_t *gamma, const uint16_t *b_q,
+                   const uint16_t *b_k, const uint16_t *b_v, uint32_t m, uint32_t k_dim,
+                   uint32_t n_dim, uint32_t n_kv, uint32_t weights_per_block, float eps,
+                   uint16_t *out_q, uint16_t *out_k, uint16_t *out_v);
+
 /* ---- fused append (src/metals/kv_prep/kv_prep_fused.metal:38-122) ---------- */
 typedef struct {
     uint32_t d_model, kv_dim, head_dim, n_heads, n_kv_heads, group_size, seq_len,

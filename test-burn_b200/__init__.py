@@ -117,6 +117,12 @@ class MfPagedPrefillArgs(C.Structure):
                 ("scale", C.c_float)]
 
 
+class MfFusedQkvArgs(C.Structure):
+    _fields_ = [("input", vp), ("w_q", vp), ("w_k", vp), ("w_v", vp), ("gamma", vp), ("bias_q", vp), ("bias_k", vp),
+                ("bias_v", vp), ("out_q", vp), ("out_k", vp), ("out_v", vp), ("k_dim", u32), ("n_dim", u32),
+                ("n_kv", u32), ("m", u32), ("weights_per_block", u32), ("epsilon", C.c_float)]
+
+
 class MfPeerExchange(C.Structure):
     _fields_ = [("recv", vp * 8), ("counters", vp * 8), ("mapping", vp * 8), ("world", u32), ("rank", u32),
                 ("rows", u32), ("head_dim", u32)]
@@ -176,6 +182,11 @@ _SIGNATURES = {
     "mf_paged_kv_append": (C.c_int32, [vp, C.POINTER(MfPagedKv), vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32,
                                        u32]),
     "mf_paged_gather": (C.c_int32, [vp, C.POINTER(MfPagedKv), u32, u32, u32, vp]),
+    "mf_fused_qkv": (C.c_int32, [vp, C.POINTER(MfFusedQkvArgs)]),
+    "mf_fused_qkv_kv_prep": (C.c_int32, [vp, C.POINTER(MfFusedQkvArgs)] + [C.POINTER(MfTensor)] * 5 +
+                             [C.POINTER(KvPrepFusedParamsResolved)]),
+    "mf_fused_qkv_paged_append": (C.c_int32, [vp, C.POINTER(MfFusedQkvArgs), C.POINTER(MfPagedKv), vp, vp, vp, u32, u32,
+                                              u32, u32, u32]),
     "mf_paged_decode_partial_push": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv), C.POINTER(MfPagedDecodeArgs), vp,
                                                  C.POINTER(MfPeerExchange), u32]),
     "mf_page_pool_create": (C.c_int32, [u32, C.POINTER(vp)]),
@@ -450,6 +461,31 @@ class Foundry:
         self.check(lib.mf_paged_kv_append(self._h, C.byref(cache), _ptr(q), _ptr(k), _ptr(v), _ptr(q_rot), _ptr(cos),
                                           _ptr(sin), n_heads, rope_mode, int(apply_rope), seq, position_offset,
                                           seq_len))
+
+    @staticmethod
+    def fused_qkv_args(x, w_q, w_k, w_v, *, k_dim, n_dim, n_kv, m, gamma=None, bias=None, out=None,
+                       weights_per_block=0, epsilon=1e-6) -> MfFusedQkvArgs:
+        """Arguments of FusedQkv (src/metals/gemv/qkv_step.rs:14-37); `bias` and `out` are (q, k, v) triples."""
+        b = bias or (None, None, None)
+        o = out or (None, None, None)
+        a = MfFusedQkvArgs(_ptr(x), _ptr(w_q), _ptr(w_k), _ptr(w_v), _ptr(gamma), _ptr(b[0]), _ptr(b[1]), _ptr(b[2]),
+                           _ptr(o[0]), _ptr(o[1]), _ptr(o[2]), k_dim, n_dim, n_kv, m, weights_per_block, epsilon)
+        a._keep = (x, w_q, w_k, w_v, gamma, b, o)
+        return a
+
+    def fused_qkv(self, args: MfFusedQkvArgs):
+        self.check(lib.mf_fused_qkv(self._h, C.byref(args)))
+
+    def fused_qkv_kv_prep(self, args: MfFusedQkvArgs, q_rot, k_cache, v_cache, cos, sin,
+                          params: KvPrepFusedParamsResolved):
+        """FusedQkv and KvPrepFused in one launch."""
+        ts = [tensor_arg(x) for x in (q_rot, k_cache, v_cache, cos, sin)]
+        self.check(lib.mf_fused_qkv_kv_prep(self._h, C.byref(args), *[C.byref(t) for t in ts], C.byref(params)))
+
+    def fused_qkv_paged_append(self, args: MfFusedQkvArgs, cache: MfPagedKv, q_rot, cos, sin, *, n_heads,
+                               rope_mode=ROPE_MODE_NEOX, apply_rope=True, seq=ALL_SEQUENCES, position_offset=0):
+        self.check(lib.mf_fused_qkv_paged_append(self._h, C.byref(args), C.byref(cache), _ptr(q_rot), _ptr(cos),
+                                                 _ptr(sin), n_heads, rope_mode, int(apply_rope), seq, position_offset))
 
     def paged_gather(self, cache: MfPagedKv, use_v: bool, seq: int, length: int, out):
         self.check(lib.mf_paged_gather(self._h, C.byref(cache), int(use_v), seq, length, _ptr(out)))

@@ -14,6 +14,7 @@
 // in f32 (both products are exact in f32, so contraction cannot change a bit),
 // one round-to-nearest-even to f16.  V is a bit copy.
 #include "internal.hpp"
+#include "ptx.cuh"
 
 namespace mf {
 namespace {
@@ -92,20 +93,12 @@ struct AppendParams {
     uint32_t q_head_major;       // 1: q_rot is [Hq, M, D] (KvPrepFused); 0: [M, Hq*D]
 };
 
-// One thread per (row s, head slot, chunk pair j).  Head slots: Hq query heads,
-// then Hkv key heads, then Hkv value heads.
-__global__ void __launch_bounds__(256) kv_append_kernel(const AppendParams p)
+// Rotate (unless V or RoPE is off) and store chunk pair j of head slot `slot` for input
+// row s: the q slots go to q_rot, the k / v slots to the cache row of the token's position.
+__device__ __forceinline__ void rope_and_store(const AppendParams &p, uint32_t s, uint32_t slot, uint32_t j,
+                                               Chunk a, Chunk c)
 {
-    const uint32_t cpr = p.head_dim / 16;  // chunk pairs per head row
-    const uint32_t slots = p.n_heads + 2 * p.n_kv_heads;
-    const uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const uint64_t total = (uint64_t)p.seq_len * slots * cpr;
-    if (gid >= total) return;
-    const uint32_t j = gid % cpr;
-    const uint32_t slot = (gid / cpr) % slots;
-    const uint32_t s = gid / ((uint64_t)cpr * slots);
     const uint32_t D = p.head_dim;
-
     uint32_t pos, b = 0;
     if (p.kv_lens && p.seq == 0xFFFFFFFFu) {
         b = s;  // one token per sequence
@@ -114,23 +107,12 @@ __global__ void __launch_bounds__(256) kv_append_kernel(const AppendParams p)
         b = p.page_table ? p.seq : 0;
         pos = p.position_offset + s;
     }
-    const __half *cos_row = p.cos_t + (size_t)pos * (D / 2);
-    const __half *sin_row = p.sin_t + (size_t)pos * (D / 2);
-
-    const __half *src;
-    if (slot < p.n_heads)
-        src = p.q + (size_t)s * p.n_heads * D + (size_t)slot * D;
-    else if (slot < p.n_heads + p.n_kv_heads)
-        src = p.k + (size_t)s * p.n_kv_heads * D + (size_t)(slot - p.n_heads) * D;
-    else
-        src = p.v + (size_t)s * p.n_kv_heads * D + (size_t)(slot - p.n_heads - p.n_kv_heads) * D;
-
-    Chunk a, c;
-    a.u = *reinterpret_cast<const uint4 *>(src + 8 * j);
-    c.u = *reinterpret_cast<const uint4 *>(src + 8 * j + D / 2);
     const bool is_v = slot >= p.n_heads + p.n_kv_heads;
-    if (p.apply_rope && !is_v) rope_chunks(a, c, cos_row, sin_row, j, D, p.rope_mode);
-
+    if (p.apply_rope && !is_v) {
+        const __half *cos_row = p.cos_t + (size_t)pos * (D / 2);
+        const __half *sin_row = p.sin_t + (size_t)pos * (D / 2);
+        rope_chunks(a, c, cos_row, sin_row, j, D, p.rope_mode);
+    }
     if (slot < p.n_heads) {
         if (!p.q_rot) return;
         __half *dst = p.q_head_major ? p.q_rot + ((size_t)slot * p.seq_len + s) * D
@@ -154,6 +136,278 @@ __global__ void __launch_bounds__(256) kv_append_kernel(const AppendParams p)
         }
     }
 }
+
+// One thread per (row s, head slot, chunk pair j).  Head slots: Hq query heads,
+// then Hkv key heads, then Hkv value heads.
+__global__ void __launch_bounds__(256) kv_append_kernel(const AppendParams p)
+{
+    const uint32_t cpr = p.head_dim / 16;  // chunk pairs per head row
+    const uint32_t slots = p.n_heads + 2 * p.n_kv_heads;
+    const uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t total = (uint64_t)p.seq_len * slots * cpr;
+    if (gid >= total) return;
+    const uint32_t j = gid % cpr;
+    const uint32_t slot = (gid / cpr) % slots;
+    const uint32_t s = gid / ((uint64_t)cpr * slots);
+    const uint32_t D = p.head_dim;
+
+    const __half *src;
+    if (slot < p.n_heads)
+        src = p.q + (size_t)s * p.n_heads * D + (size_t)slot * D;
+    else if (slot < p.n_heads + p.n_kv_heads)
+        src = p.k + (size_t)s * p.n_kv_heads * D + (size_t)(slot - p.n_heads) * D;
+    else
+        src = p.v + (size_t)s * p.n_kv_heads * D + (size_t)(slot - p.n_heads - p.n_kv_heads) * D;
+
+    Chunk a, c;
+    a.u = *reinterpret_cast<const uint4 *>(src + 8 * j);
+    c.u = *reinterpret_cast<const uint4 *>(src + 8 * j + D / 2);
+    rope_and_store(p, s, slot, j, a, c);
+}
+
+// RMSNorm -> Q/K/V projection (+bias) with f16 weights, optionally followed by the append above
+// (qkv_project.metal:4-272 computes the projection with one warp per output row and scalar FMAs).
+// Here a CTA owns one chunk pair of one head slot: the 16 output rows [8j, 8j+8) and
+// [8j + D/2, 8j + D/2 + 8) of a head, which is exactly what one thread of kv_append_kernel consumes,
+// for up to eight input rows, and the products run on mma.sync m16n8k16 (f16 in, f32 accumulate):
+// the 16 weight rows are the m side, the input rows the n side.  Warp w takes the 32-wide k blocks
+// w, w+8, ...; lane l reads 16 bytes of row l/4 of each row group at k quarter l%4 (in the blocked
+// weight layout the eight rows of a group are 512 contiguous bytes per k block: one full line per
+// warp load) and uses them directly as its A fragments of two mma steps; the k order inside a step
+// is therefore permuted, the same way for the input fragment read from shared memory, which leaves
+// the dot product unchanged.  A row's sum = the warp's accumulator chain over its k blocks, then the
+// eight warps added in order: independent of the number of input rows and of the append.
+struct QkvParams {
+    const __half *x, *w_q, *w_k, *w_v, *gamma, *b_q, *b_k, *b_v;
+    __half *out_q, *out_k, *out_v;
+    uint32_t k_dim, n_dim, n_kv, m;
+    uint32_t blocked;    // 1: element (r, k) at (k % 32) + 32 * (r + (k / 32) * N)
+    uint32_t head_dim;   // rows per head slot (16 without the append)
+    uint32_t q_slots, kv_slots;
+    uint32_t rows_per_cta;  // input rows staged per CTA, at most 8
+    float eps;
+    uint32_t append;
+};
+
+constexpr uint32_t kQkvRows = 8;   // the n side of the mma
+constexpr int kQkvDepth = 4;       // k blocks per register buffer; two buffers in flight
+constexpr uint32_t kQkvPad = 32;   // halves between staged rows beyond K: rows 64 bytes apart modulo 128
+
+struct QkvWeights {
+    uint4 lo[kQkvDepth], hi[kQkvDepth];
+};
+
+__device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gmem_src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
+                 "l"(gmem_src)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all()
+{
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+#ifdef MF_QKV_PROFILE
+// Development aid (build with -DMF_QKV_PROFILE): global-timer stamps of thread 0 of each CTA.
+__device__ unsigned long long g_qkv_prof[512 * 8];
+__device__ __forceinline__ unsigned long long qkv_now()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define QKV_STAMP(k) { if (tid == 0 && blockIdx.x < 512 && blockIdx.y == 0) g_qkv_prof[blockIdx.x * 8 + (k)] = qkv_now(); }
+#else
+#define QKV_STAMP(k)
+#endif
+
+// What a CTA needs to know about one slab (chunk pair j of head slot `slot`).
+struct QkvSlab {
+    const __half *wl_lo, *wl_hi, *bias;  // this lane's weight pointers (k block 0), bias of the matrix
+    __half *plain;                       // optional projected output of the matrix
+    size_t kb_stride;
+    uint32_t n, slot, j, first_row;      // first_row: of row group 0; group 1 is head_dim/2 further
+};
+
+__global__ void __launch_bounds__(256, 2) fused_qkv_kernel(const QkvParams qp, const AppendParams ap)
+{
+    extern __shared__ __align__(16) unsigned char qkv_smem[];
+    __half *xs = reinterpret_cast<__half *>(qkv_smem);  // [rows_per_cta][K + pad], normalised
+    __shared__ float red[8][16][kQkvRows];
+    __shared__ float ssq[8][kQkvRows];
+    __shared__ __align__(16) __half outv[kQkvRows][16];
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t cpr = qp.head_dim / 16;
+    const uint32_t n_slabs = (qp.q_slots + 2 * qp.kv_slots) * cpr;
+    const uint32_t row0 = blockIdx.y * qp.rows_per_cta;
+    const uint32_t rows = min(qp.rows_per_cta, qp.m - row0);
+    const uint32_t K = qp.k_dim, xstride = K + kQkvPad, nkb = K / 32;
+    const uint32_t r_in = lane >> 2, kq = lane & 3;
+
+    auto describe = [&](uint32_t slab) {
+        QkvSlab d;
+        d.slot = slab / cpr, d.j = slab % cpr;
+        const __half *w;
+        uint32_t head;
+        if (d.slot < qp.q_slots) {
+            w = qp.w_q, d.bias = qp.b_q, d.plain = qp.out_q, d.n = qp.n_dim, head = d.slot;
+        } else if (d.slot < qp.q_slots + qp.kv_slots) {
+            w = qp.w_k, d.bias = qp.b_k, d.plain = qp.out_k, d.n = qp.n_kv, head = d.slot - qp.q_slots;
+        } else {
+            w = qp.w_v, d.bias = qp.b_v, d.plain = qp.out_v, d.n = qp.n_kv, head = d.slot - qp.q_slots - qp.kv_slots;
+        }
+        d.first_row = head * qp.head_dim + 8 * d.j;
+        const uint32_t row_lo = d.first_row + r_in, row_hi = row_lo + qp.head_dim / 2;
+        d.wl_lo = qp.blocked ? w + (size_t)row_lo * 32 + kq * 8 : w + (size_t)row_lo * K + kq * 8;
+        d.wl_hi = qp.blocked ? w + (size_t)row_hi * 32 + kq * 8 : w + (size_t)row_hi * K + kq * 8;
+        d.kb_stride = qp.blocked ? (size_t)d.n * 32 : 32;
+        return d;
+    };
+    auto fetch = [&](QkvWeights &dst, const QkvSlab &d, uint32_t chunk) {
+#pragma unroll
+        for (int u = 0; u < kQkvDepth; ++u) {
+            const uint32_t kb = warp + 8 * (chunk * kQkvDepth + u);
+            if (kb < nkb) {
+                dst.lo[u] = __ldg(reinterpret_cast<const uint4 *>(d.wl_lo + kb * d.kb_stride));
+                dst.hi[u] = __ldg(reinterpret_cast<const uint4 *>(d.wl_hi + kb * d.kb_stride));
+            } else {
+                dst.lo[u] = dst.hi[u] = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+
+    QKV_STAMP(0)
+    grid_launch_dependents();
+    // The weights are constants: the first 64 KB of them are requested before the grid waits for the
+    // kernel in front of it (under a programmatic dependent launch they travel during its tail) and
+    // keep arriving while the input rows are staged and normalised.
+    uint32_t slab = blockIdx.x;
+    QkvSlab sd = describe(slab);
+    QkvWeights cur, nxt;
+    fetch(cur, sd, 0);
+    fetch(nxt, sd, 1);
+    grid_dependency_wait();  // from here on: reads of what that kernel may have produced, and writes
+    const uint32_t vecs = K / 8;
+    __half *gs = xs + (size_t)qp.rows_per_cta * xstride;  // gamma, staged once
+    for (uint32_t b = 0; b < rows; ++b)
+        for (uint32_t i = tid; i < vecs; i += 256)
+            cp_async_16(xs + (size_t)b * xstride + 8 * i, qp.x + (size_t)(row0 + b) * K + 8 * i);
+    if (qp.gamma)
+        for (uint32_t i = tid; i < vecs; i += 256) cp_async_16(gs + 8 * i, qp.gamma + 8 * i);
+    QKV_STAMP(1)
+    cp_async_wait_all();
+    QKV_STAMP(2)
+    if (qp.gamma) {
+        // each thread squares, and later scales, the vectors it copied itself
+        for (uint32_t b = 0; b < rows; ++b) {
+            float sq = 0.f;
+            for (uint32_t i = tid; i < vecs; i += 256) {
+                Chunk c;
+                c.u = *reinterpret_cast<const uint4 *>(xs + (size_t)b * xstride + 8 * i);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float f = __half2float(c.h[e]);
+                    sq = fmaf(f, f, sq);
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            if (lane == 0) ssq[warp][b] = sq;
+        }
+        __syncthreads();
+        for (uint32_t b = 0; b < rows; ++b) {
+            float t = 0.f;
+#pragma unroll
+            for (int wv = 0; wv < 8; ++wv) t += ssq[wv][b];
+            const float inv = 1.0f / sqrtf(t / (float)K + qp.eps);
+            for (uint32_t i = tid; i < vecs; i += 256) {
+                Chunk c, g;
+                c.u = *reinterpret_cast<const uint4 *>(xs + (size_t)b * xstride + 8 * i);
+                g.u = *reinterpret_cast<const uint4 *>(gs + 8 * i);
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    c.h[e] = __float2half_rn(__fmul_rn(__fmul_rn(__half2float(c.h[e]), inv), __half2float(g.h[e])));
+                *reinterpret_cast<uint4 *>(xs + (size_t)b * xstride + 8 * i) = c.u;
+            }
+        }
+    }
+    __syncthreads();
+    QKV_STAMP(3)
+
+    const bool has_x = r_in < rows;  // this lane's input row on the n side
+    const __half *xl = xs + (size_t)r_in * xstride + kq * 8;
+    const uint32_t per_warp = (nkb + 7 - warp) / 8;
+    const uint32_t chunks = (per_warp + kQkvDepth - 1) / kQkvDepth;
+    for (;;) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
+#pragma unroll
+            for (int u = 0; u < kQkvDepth; ++u) {
+                const uint32_t kb = warp + 8 * (chunk * kQkvDepth + u);
+                if (kb < nkb) {
+                    const uint4 xv = has_x ? *reinterpret_cast<const uint4 *>(xl + kb * 32) : make_uint4(0, 0, 0, 0);
+                    const uint32_t a1[4] = {cur.lo[u].x, cur.hi[u].x, cur.lo[u].y, cur.hi[u].y};
+                    mma_m16n8k16(acc, a1, xv.x, xv.y);
+                    const uint32_t a2[4] = {cur.lo[u].z, cur.hi[u].z, cur.lo[u].w, cur.hi[u].w};
+                    mma_m16n8k16(acc, a2, xv.z, xv.w);
+                }
+            }
+            cur = nxt;
+            if (chunk + 2 < chunks) fetch(nxt, sd, chunk + 2);
+        }
+        QKV_STAMP(4)
+        red[warp][r_in][2 * kq] = acc[0];
+        red[warp][r_in][2 * kq + 1] = acc[1];
+        red[warp][r_in + 8][2 * kq] = acc[2];
+        red[warp][r_in + 8][2 * kq + 1] = acc[3];
+        // the next slab's weights travel during this slab's reduction and stores
+        const QkvSlab done = sd;
+        slab += gridDim.x;
+        const bool more = slab < n_slabs;
+        if (more) {
+            sd = describe(slab);
+            fetch(cur, sd, 0);
+            fetch(nxt, sd, 1);
+        }
+        __syncthreads();
+        if (tid < 16 * kQkvRows) {
+            const uint32_t r = tid & 15, b = tid >> 4;
+            float sum = red[0][r][b];
+#pragma unroll
+            for (int wv = 1; wv < 8; ++wv) sum += red[wv][r][b];
+            if (done.bias) sum += __half2float(done.bias[done.first_row + (r >> 3) * (qp.head_dim / 2) + (r & 7)]);
+            outv[b][r] = __float2half_rn(sum);
+        }
+        __syncthreads();
+        if (tid < rows) {
+            const uint32_t s = row0 + tid;
+            Chunk a, c;
+            a.u = *reinterpret_cast<const uint4 *>(&outv[tid][0]);
+            c.u = *reinterpret_cast<const uint4 *>(&outv[tid][8]);
+            if (done.plain) {
+                __half *dst = done.plain + (size_t)s * done.n + done.first_row;
+                *reinterpret_cast<uint4 *>(dst) = a.u;
+                *reinterpret_cast<uint4 *>(dst + qp.head_dim / 2) = c.u;
+            }
+            if (qp.append) rope_and_store(ap, s, done.slot, done.j, a, c);
+        }
+        QKV_STAMP(5)
+        if (!more) break;
+    }
+}
+
+#ifdef MF_QKV_PROFILE
+}  // namespace
+}  // namespace mf
+extern "C" __attribute__((visibility("default"))) int mf_debug_qkv_profile(unsigned long long *host_out, uint32_t n)
+{
+    return (int)cudaMemcpyFromSymbol(host_out, mf::g_qkv_prof, sizeof(unsigned long long) * n);
+}
+namespace mf {
+namespace {
+#endif
 
 // NeoX RoPE over rows of `dim` (rope.metal:36-74): pos = (row % seq_len) + offset.
 __global__ void __launch_bounds__(256)
@@ -291,16 +545,18 @@ using namespace mf;
 
 extern "C" {
 
-mf_status mf_kv_prep_fused(MfContext *ctx, const MfTensor *q, const MfTensor *k, const MfTensor *v,
-                           const MfTensor *q_rot, const MfTensor *k_cache, const MfTensor *v_cache,
-                           const MfTensor *cos, const MfTensor *sin, const KvPrepFusedParamsResolved *pr)
+// Checks and kernel parameters of KvPrepFused.  with_inputs == false: q, k, v come from a
+// projection inside the launch and are not looked at.
+static mf_status kv_prep_params(MfContext *ctx, const MfTensor *q, const MfTensor *k, const MfTensor *v,
+                                const MfTensor *q_rot, const MfTensor *k_cache, const MfTensor *v_cache,
+                                const MfTensor *cos, const MfTensor *sin, const KvPrepFusedParamsResolved *pr,
+                                bool with_inputs, AppendParams &p)
 {
-    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
     if (!pr) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "params");
     mf_status st;
     const MfTensor *ts[8] = {q, k, v, q_rot, k_cache, v_cache, cos, sin};
     const char *names[8] = {"q", "k", "v", "q_rot", "k_cache", "v_cache", "cos", "sin"};
-    for (int i = 0; i < 8; ++i)
+    for (int i = with_inputs ? 0 : 3; i < 8; ++i)
         if ((st = need_tensor(ctx, ts[i], names[i])) != MF_OK) return st;
     // Constraints stated on the reference kernel (kv_prep/mod.rs:149-156).
     if (pr->head_dim == 0 || pr->head_dim % 16 != 0)
@@ -330,18 +586,17 @@ mf_status mf_kv_prep_fused(MfContext *ctx, const MfTensor *q, const MfTensor *k,
     else
         return fail(ctx, MF_ERR_INVALID_SHAPE, "KV cache heads mismatch: got %llu, expected %u (expanded) or %u (compact)",
                     (unsigned long long)k_cache->dims[0], pr->n_heads, pr->n_kv_heads);
-    if (pr->seq_len == 0) return MF_OK;
-    AppendParams p{};
-    p.q = tensor_ptr(q);
-    p.k = tensor_ptr(k);
-    p.v = tensor_ptr(v);
+    p = AppendParams{};
+    p.q = with_inputs ? tensor_ptr(q) : nullptr;
+    p.k = with_inputs ? tensor_ptr(k) : nullptr;
+    p.v = with_inputs ? tensor_ptr(v) : nullptr;
     p.q_rot = tensor_ptr(q_rot);
     p.k_cache = tensor_ptr(k_cache);
     p.v_cache = tensor_ptr(v_cache);
     p.cos_t = tensor_ptr(cos);
     p.sin_t = tensor_ptr(sin);
     const void *ptrs[8] = {p.q, p.k, p.v, p.q_rot, p.k_cache, p.v_cache, p.cos_t, p.sin_t};
-    for (int i = 0; i < 8; ++i)
+    for (int i = with_inputs ? 0 : 3; i < 8; ++i)
         if (!aligned16(ptrs[i])) return fail(ctx, MF_ERR_INVALID_SHAPE, "KvPrepFused: %s must be 16-byte aligned", names[i]);
     p.n_heads = pr->n_heads;
     p.n_kv_heads = pr->n_kv_heads;
@@ -355,23 +610,34 @@ mf_status mf_kv_prep_fused(MfContext *ctx, const MfTensor *q, const MfTensor *k,
     // SmolLM3-style skip: no RoPE on every N-th layer (kv_prep_fused.metal:56-57).
     p.apply_rope = pr->no_rope_layer_step == 0 || ((pr->layer_idx + 1u) % pr->no_rope_layer_step) != 0u;
     p.q_head_major = 1;
+    return MF_OK;
+}
+
+mf_status mf_kv_prep_fused(MfContext *ctx, const MfTensor *q, const MfTensor *k, const MfTensor *v,
+                           const MfTensor *q_rot, const MfTensor *k_cache, const MfTensor *v_cache,
+                           const MfTensor *cos, const MfTensor *sin, const KvPrepFusedParamsResolved *pr)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    AppendParams p;
+    const mf_status st = kv_prep_params(ctx, q, k, v, q_rot, k_cache, v_cache, cos, sin, pr, true, p);
+    if (st != MF_OK || p.seq_len == 0) return st;
     const uint64_t threads = (uint64_t)p.seq_len * (p.n_heads + 2 * p.n_kv_heads) * (p.head_dim / 16);
     kv_append_kernel<<<blocks_for(threads), 256, 0, ctx->stream>>>(p);
     return check_launch(ctx, "kv_append_kernel");
 }
 
-mf_status mf_paged_kv_append(MfContext *ctx, const MfPagedKv *cache, const void *q, const void *k, const void *v,
-                             void *q_rot, const void *cos, const void *sin, uint32_t n_heads, uint32_t rope_mode,
-                             uint32_t apply_rope, uint32_t seq, uint32_t position_offset, uint32_t seq_len)
+static mf_status paged_append_params(MfContext *ctx, const MfPagedKv *cache, const void *q, const void *k,
+                                     const void *v, void *q_rot, const void *cos, const void *sin, uint32_t n_heads,
+                                     uint32_t rope_mode, uint32_t apply_rope, uint32_t seq, uint32_t position_offset,
+                                     uint32_t seq_len, bool with_inputs, AppendParams &p)
 {
-    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
-    if (!cache || !cache->k_pool || !cache->v_pool || !cache->page_table || !q || !k || !v)
+    if (!cache || !cache->k_pool || !cache->v_pool || !cache->page_table || (with_inputs && (!q || !k || !v)))
         return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged append: null input");
     if (apply_rope && (!cos || !sin)) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged append: cos/sin");
     if (cache->head_dim % 16 != 0 || cache->n_kv_heads == 0 || n_heads % cache->n_kv_heads != 0)
         return fail(ctx, MF_ERR_INVALID_SHAPE, "paged append: geometry");
     if (rope_mode > 1) return fail(ctx, MF_ERR_INVALID_OPERATION, "paged append: rope_mode %u", rope_mode);
-    AppendParams p{};
+    p = AppendParams{};
     p.q = static_cast<const __half *>(q);
     p.k = static_cast<const __half *>(k);
     p.v = static_cast<const __half *>(v);
@@ -404,10 +670,133 @@ mf_status mf_paged_kv_append(MfContext *ctx, const MfPagedKv *cache, const void 
         p.position_offset = position_offset;
         p.q_head_major = 1;
     }
-    if (p.seq_len == 0) return MF_OK;
+    return MF_OK;
+}
+
+mf_status mf_paged_kv_append(MfContext *ctx, const MfPagedKv *cache, const void *q, const void *k, const void *v,
+                             void *q_rot, const void *cos, const void *sin, uint32_t n_heads, uint32_t rope_mode,
+                             uint32_t apply_rope, uint32_t seq, uint32_t position_offset, uint32_t seq_len)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    AppendParams p;
+    const mf_status st = paged_append_params(ctx, cache, q, k, v, q_rot, cos, sin, n_heads, rope_mode, apply_rope, seq,
+                                             position_offset, seq_len, true, p);
+    if (st != MF_OK || p.seq_len == 0) return st;
     const uint64_t threads = (uint64_t)p.seq_len * (p.n_heads + 2 * p.n_kv_heads) * (p.head_dim / 16);
     kv_append_kernel<<<blocks_for(threads), 256, 0, ctx->stream>>>(p);
     return check_launch(ctx, "kv_append_kernel(paged)");
+}
+
+// ---- FusedQkv and its two append forms -----------------------------------------------------------
+
+static mf_status launch_fused_qkv(MfContext *ctx, const MfFusedQkvArgs *a, uint32_t head_dim, uint32_t q_slots,
+                                  uint32_t kv_slots, const AppendParams *ap, bool want_plain, const char *what)
+{
+    if (!a->input || !a->w_q || !a->w_k || !a->w_v) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "%s: input / weights", what);
+    if (want_plain && (!a->out_q || !a->out_k || !a->out_v)) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "%s: outputs", what);
+    const bool any_bias = a->bias_q || a->bias_k || a->bias_v;
+    if (any_bias && !(a->bias_q && a->bias_k && a->bias_v))
+        return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "%s: give all three biases or none", what);
+    if (a->weights_per_block != 0 && a->weights_per_block != 32)
+        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "%s: weights_per_block %u (0 = row-major, 32 = blocked)", what,
+                    a->weights_per_block);
+    if (a->k_dim == 0 || a->k_dim % 32 != 0 || a->n_dim % 16 != 0 || a->n_kv % 16 != 0 || a->n_dim == 0)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "%s: k_dim %u must be a multiple of 32, n_dim %u and n_kv %u of 16", what,
+                    a->k_dim, a->n_dim, a->n_kv);
+    const void *ptrs[] = {a->input, a->w_q, a->w_k, a->w_v, a->gamma, a->bias_q, a->bias_k, a->bias_v,
+                          a->out_q, a->out_k, a->out_v};
+    for (const void *ptr : ptrs)
+        if (ptr && !aligned16(ptr)) return fail(ctx, MF_ERR_INVALID_SHAPE, "%s: pointers must be 16-byte aligned", what);
+    if (a->m == 0) return MF_OK;
+    QkvParams qp{};
+    qp.x = static_cast<const __half *>(a->input);
+    qp.w_q = static_cast<const __half *>(a->w_q);
+    qp.w_k = static_cast<const __half *>(a->w_k);
+    qp.w_v = static_cast<const __half *>(a->w_v);
+    qp.gamma = static_cast<const __half *>(a->gamma);
+    qp.b_q = static_cast<const __half *>(a->bias_q);
+    qp.b_k = static_cast<const __half *>(a->bias_k);
+    qp.b_v = static_cast<const __half *>(a->bias_v);
+    qp.out_q = static_cast<__half *>(a->out_q);
+    qp.out_k = static_cast<__half *>(a->out_k);
+    qp.out_v = static_cast<__half *>(a->out_v);
+    qp.k_dim = a->k_dim, qp.n_dim = a->n_dim, qp.n_kv = a->n_kv, qp.m = a->m;
+    qp.blocked = a->weights_per_block == 32;
+    qp.head_dim = head_dim, qp.q_slots = q_slots, qp.kv_slots = kv_slots;
+    qp.eps = a->epsilon;
+    qp.append = ap != nullptr;
+    const AppendParams none{};
+    const AppendParams &app = ap ? *ap : none;
+    // input rows per CTA: eight, fewer when the staged rows would not fit in shared memory
+    const size_t row_bytes = ((size_t)a->k_dim + kQkvPad) * sizeof(__half), budget = 200 * 1024;
+    if (2 * row_bytes > budget) return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "%s: k_dim %u too large", what, a->k_dim);
+    uint32_t rows = a->m < kQkvRows ? a->m : kQkvRows;
+    while ((rows + 1) * row_bytes > budget) --rows;  // + 1: gamma
+    qp.rows_per_cta = rows;
+    // CTAs loop over slabs; two CTAs are resident per SM
+    const uint32_t slabs = (q_slots + 2 * kv_slots) * (head_dim / 16), tiles = (a->m + rows - 1) / rows;
+    const size_t smem = rows * row_bytes + (a->gamma ? (size_t)a->k_dim * sizeof(__half) : 0);
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(fused_qkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget) != cudaSuccess)
+        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "%s: cannot get %zu bytes of shared memory", what, smem);
+    const uint32_t resident = std::max(1u, 2u * (uint32_t)ctx->sm_count / tiles);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(std::min(slabs, resident), tiles, 1);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    cfg.attrs = attr;
+    cfg.numAttrs = 0;
+    if (ctx->overlap_launches) {
+        // programmatic dependent launch: the grid may be scheduled while the kernel before it drains;
+        // it waits before it reads or writes anything
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 1;
+    }
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, fused_qkv_kernel, qp, app);
+    if (e != cudaSuccess) return fail(ctx, MF_ERR_CUDA, "launch fused_qkv_kernel: %s", cudaGetErrorString(e));
+    ++ctx->launches;
+    return MF_OK;
+}
+
+mf_status mf_fused_qkv(MfContext *ctx, const MfFusedQkvArgs *args)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!args) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "FusedQkv: args");
+    return launch_fused_qkv(ctx, args, 16, args->n_dim / 16, args->n_kv / 16, nullptr, true, "FusedQkv");
+}
+
+mf_status mf_fused_qkv_kv_prep(MfContext *ctx, const MfFusedQkvArgs *args, const MfTensor *q_rot,
+                               const MfTensor *k_cache, const MfTensor *v_cache, const MfTensor *cos,
+                               const MfTensor *sin, const KvPrepFusedParamsResolved *pr)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!args) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "FusedQkv+KvPrepFused: args");
+    AppendParams p;
+    const mf_status st = kv_prep_params(ctx, nullptr, nullptr, nullptr, q_rot, k_cache, v_cache, cos, sin, pr, false, p);
+    if (st != MF_OK) return st;
+    if (args->m != pr->seq_len || args->n_dim != pr->d_model || args->n_kv != pr->kv_dim)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "FusedQkv+KvPrepFused: m %u / n_dim %u / n_kv %u against seq_len %u / d_model %u / kv_dim %u",
+                    args->m, args->n_dim, args->n_kv, pr->seq_len, pr->d_model, pr->kv_dim);
+    return launch_fused_qkv(ctx, args, p.head_dim, p.n_heads, p.n_kv_heads, &p, false, "FusedQkv+KvPrepFused");
+}
+
+mf_status mf_fused_qkv_paged_append(MfContext *ctx, const MfFusedQkvArgs *args, const MfPagedKv *cache, void *q_rot,
+                                    const void *cos, const void *sin, uint32_t n_heads, uint32_t rope_mode,
+                                    uint32_t apply_rope, uint32_t seq, uint32_t position_offset)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!args) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "FusedQkv+paged append: args");
+    AppendParams p;
+    const mf_status st = paged_append_params(ctx, cache, nullptr, nullptr, nullptr, q_rot, cos, sin, n_heads, rope_mode,
+                                             apply_rope, seq, position_offset, args->m, false, p);
+    if (st != MF_OK) return st;
+    if (args->m != p.seq_len || args->n_dim != n_heads * p.head_dim || args->n_kv != p.n_kv_heads * p.head_dim)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "FusedQkv+paged append: m %u / n_dim %u / n_kv %u against the cache geometry",
+                    args->m, args->n_dim, args->n_kv);
+    return launch_fused_qkv(ctx, args, p.head_dim, p.n_heads, p.n_kv_heads, &p, false, "FusedQkv+paged append");
 }
 
 mf_status mf_rope(MfContext *ctx, const MfTensor *input, const MfTensor *output, const MfTensor *cos,

@@ -296,3 +296,37 @@ def test_prefill_split_k_partials(orc):
     assert covered == kv // 32
     merged = orc.merge_partials(np.stack(accs), np.stack(ms), np.stack(ls)).reshape(hq, m, d).transpose(1, 0, 2)
     assert ulp_distance(merged.reshape(m, hq * d), single) <= 2
+
+
+@pytest.mark.parametrize("shape", [(2, 128, 128, 64, False, True), (1, 1024, 1024, 128, True, False)])
+def test_fused_qkv_restatement(orc, shape):
+    """The projection in front of the append, on the two shapes the reference checks on its CPU
+    (tests/fused_qkv_batched_rmsnorm_parity.rs:23-56,58-66: f32 RMSNorm then x @ W^T, blocked weights;
+    tests/qkv_parity_f16.rs:18-69,87-89: f16-rounded norm, row-major weights, bias): the restatement
+    follows the second (the kernel's own rounding points) and is compared with a float64 version of
+    the same steps; the blocked and the row-major layouts must give the same bits."""
+    m, k_dim, n_dim, n_kv, bias, blocked = shape
+    rng = np.random.default_rng(7)
+    f16 = lambda lo, hi, n: rng.uniform(lo, hi, n).astype(np.float32).astype(np.float16)
+    x, gamma = f16(-1, 1, (m, k_dim)), f16(0.5, 1.5, k_dim)
+    ws = [f16(-0.1, 0.1, (n, k_dim)) for n in (n_dim, n_kv, n_kv)]
+    bs = [f16(-0.1, 0.1, n) for n in (n_dim, n_kv, n_kv)] if bias else [None] * 3
+    bits = lambda a: None if a is None else np.ascontiguousarray(a).view(np.uint16).ravel()
+    kw = dict(m=m, k_dim=k_dim, n_dim=n_dim, n_kv=n_kv, gamma=bits(gamma), b_q=bits(bs[0]), b_k=bits(bs[1]),
+              b_v=bits(bs[2]))
+    row_major = orc.fused_qkv(bits(x), *[bits(w) for w in ws], weights_per_block=0, **kw)
+    packed = [np.ascontiguousarray(w.reshape(w.shape[0], k_dim // 32, 32).transpose(1, 0, 2)) for w in ws]
+    blocked_out = orc.fused_qkv(bits(x), *[bits(w) for w in packed], weights_per_block=32, **kw)
+    for a, b in zip(row_major, blocked_out):
+        assert np.array_equal(a, b)
+    xf = x.astype(np.float64)
+    inv = 1.0 / np.sqrt((xf * xf).mean(axis=1, keepdims=True) + 1e-6)
+    xn = (xf * inv * gamma.astype(np.float64)).astype(np.float16).astype(np.float64)
+    for got, w, b in zip(blocked_out if blocked else row_major, ws, bs):
+        ref = xn @ w.astype(np.float64).T + (0.0 if b is None else b.astype(np.float64))
+        got = got.view(np.float16).astype(np.float64).reshape(ref.shape)
+        assert np.all(np.abs(got - ref) <= np.abs(ref) * 2.0 ** -10 + 1e-3)
+    # no gamma: the input goes into the projection as it is
+    plain = orc.fused_qkv(bits(x), *[bits(w) for w in ws], m=m, k_dim=k_dim, n_dim=n_dim, n_kv=n_kv)
+    ref = x.astype(np.float64) @ ws[0].astype(np.float64).T
+    assert np.all(np.abs(plain[0].view(np.float16).astype(np.float64).reshape(ref.shape) - ref) <= np.abs(ref) * 2.0 ** -10 + 1e-3)
