@@ -559,17 +559,36 @@ def run_prefill(args):
     if args.prefill_impl:
         f.set_option(3, args.prefill_impl)
     p = mfk.KvPrepFusedParamsResolved(hq * d, hkv * d, d, hq, hkv, hq // hkv, m, cached, cap, hq * m * d, 1, 0, 0)
+    desc = None
+    if args.page_size:
+        # the same chunk into a PAGED cache: pages of the sequence scattered over the pool
+        P = args.page_size
+        n_pages = cap // P + 7
+        kp = torch.empty((n_pages, hkv, P, d), dtype=torch.float16, device=dev).normal_(generator=g)
+        vp = torch.empty((n_pages, hkv, P, d), dtype=torch.float16, device=dev).normal_(generator=g)
+        table = torch.randperm(n_pages, device=dev, generator=g)[: cap // P].to(torch.int32).reshape(1, -1).contiguous()
+        lens = torch.tensor([cached + m], dtype=torch.int32, device=dev)
+        desc = mfk.paged_kv(kp, vp, table, lens, n_kv_heads=hkv, page_size=P, head_dim=d)
+    scale = 1.0 / math.sqrt(d)
 
     def step(timed_events=None):
         with torch.cuda.stream(stream):
             flush.zero_()  # L2 flush between iterations: write a buffer larger than L2
             if timed_events:
                 timed_events[0].record(stream)
-            f.kv_prep_fused(q, k, v, q_rot, kc, vc, cos, sin, p)
+            if desc is not None:
+                f.paged_kv_append(desc, q, k, v, q_rot, cos, sin, n_heads=hq, rope_mode=1, seq=0, position_offset=cached,
+                                  seq_len=m)
+            else:
+                f.kv_prep_fused(q, k, v, q_rot, kc, vc, cos, sin, p)
             if timed_events:
                 timed_events[1].record(stream)
-            f.flash_attention(q_rot, kc, vc, out, causal=True, query_offset=cached, n_heads=hq, head_dim=d,
-                              kv_seq_len=cached + m, m=m)
+            if desc is not None:
+                f.paged_prefill(desc, q_rot, out, seq=0, q_len=m, kv_len=cached + m, query_offset=cached, n_heads=hq,
+                                scale=scale)
+            else:
+                f.flash_attention(q_rot, kc, vc, out, causal=True, query_offset=cached, n_heads=hq, head_dim=d,
+                                  kv_seq_len=cached + m, m=m)
             if timed_events:
                 timed_events[2].record(stream)
 
@@ -601,7 +620,9 @@ def run_prefill(args):
         "warmup": max(args.warmup, 3), "ms_per_step": t_append + t_attn, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 inputs, f32 accumulate", "data": "synthetic",
         "config": {"workload": "chunked causal prefill into cache, Llama-3.2-3B shape: 2048 new after 2048 cached, "
-                               "24q/8kv heads, D128, one layer", "l2": "flushed between iterations (256 MB write)",
+                               "24q/8kv heads, D128, one layer" +
+                               (", paged cache (page %d)" % args.page_size if args.page_size else ", contiguous cache"),
+                   "l2": "flushed between iterations (256 MB write)",
                    "split_k": mfk.prefill_split_k(cached + m, m)},
         "append_us": t_append * 1e3, "attention_us": t_attn * 1e3, "algorithmic_flops": flops,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
@@ -843,7 +864,7 @@ def main():
                          "in one launch) instead of from q, k, v")
     ap.add_argument("--prefill-impl", type=int, default=0, help="prefill kernel selector (experiments)")
     ap.add_argument("--stages", type=int, default=0, help="decode ring depth (experiments)")
-    ap.add_argument("--page-size", type=int, default=0, help="override the workload's page size (experiments)")
+    ap.add_argument("--page-size", type=int, default=0, help="override the workload's page size (experiments); c4: prefill into a paged cache with pages of this many rows")
     ap.add_argument("--sequential-pages", action="store_true", help="identity page table (experiments)")
     args = ap.parse_args()
     if args.workload == "c4":

@@ -370,7 +370,7 @@ mf_status launch_pf(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap &
 }  // namespace
 
 mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const void *v, void *out,
-                            const SdpaPrefillSplitKParams &sp, bool *handled);
+                            const SdpaPrefillSplitKParams &sp, bool *handled, const MfPagedKv *paged, uint32_t seq);
 
 mf_status launch_prefill(MfContext *ctx, const void *q, const void *k, const void *v, void *out,
                          const SdpaPrefillSplitKParams &sp, const MfPagedKv *paged, uint32_t seq)
@@ -403,10 +403,10 @@ mf_status launch_prefill(MfContext *ctx, const void *q, const void *k, const voi
     if ((b.q_stride_h | b.q_stride_m) & 1u || (b.out_stride_h | b.out_stride_m) & 1u ||
         (reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 3u)
         return fail(ctx, MF_ERR_INVALID_SHAPE, "Prefill: q/output strides must be even and pointers 4-byte aligned");
-    if (ctx->prefill_impl != 1 && !paged) {
-        // tcgen05 / TMEM kernel for head_dim 128, unsplit, chunks of 64 rows or more
+    if (ctx->prefill_impl != 1) {
+        // tcgen05 / TMEM kernel: unsplit, chunks of 64 rows or more, contiguous cache or pages of 8-128 rows
         bool handled = false;
-        mf_status st_tc = launch_prefill_tc(ctx, q, k, v, out, sp, &handled);
+        mf_status st_tc = launch_prefill_tc(ctx, q, k, v, out, sp, &handled, paged, seq);
         if (st_tc != MF_OK || handled) return st_tc;
         if (ctx->prefill_impl == 2)
             return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "Prefill: shape outside the tcgen05 kernel's envelope");

@@ -80,6 +80,9 @@ struct TcParams {
     uint32_t q_len, kv_len, query_offset, group, n_heads, n_q_tiles;
     uint32_t out_stride_h, out_stride_m;
     float scale_log2;
+    // paged cache: K/V tiles are gathered page by page through the sequence's page-table row
+    const uint32_t *page_table_row;  // null: contiguous cache
+    uint32_t page_size, n_kv_heads;
 };
 
 #ifdef MF_TC_PROFILE
@@ -247,6 +250,18 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void *tmap, int3
         : "memory");
 }
 
+// Zero rows [first_dead, 128) of a V tile laid out [column half][128 rows][128 bytes]; called by the
+// 128 * kRowSplit threads of one softmax group (rarely: kept out of line, off the tile loop's registers).
+template <uint32_t D>
+__device__ __noinline__ void clear_dead_rows(uint8_t *v_tile, uint32_t first_dead, uint32_t gtid)
+{
+    for (uint32_t c = gtid; c < (kBN - first_dead) * (D / 8); c += 128 * kRowSplit) {
+        const uint32_t r = first_dead + c / (D / 8), ch = c % (D / 8);
+        *reinterpret_cast<uint4 *>(v_tile + (ch / 8) * (kBN * 128) + r * 128 + (ch % 8) * 16) = make_uint4(0, 0, 0, 0);
+    }
+    fence_proxy_async();
+}
+
 // Barrier slots (8 bytes each) after the tiles.
 enum Bar : uint32_t {
     kQFull = 0,
@@ -264,13 +279,17 @@ static_assert(kKStages == 3 && kVStages == 3, "ring slot = score buffer = tile %
 __host__ __device__ constexpr uint32_t tc_smem_tiles(uint32_t d) { return tc_tile_bytes(d) * (1 + kKStages + kVStages); }  // Q + K ring + V ring
 constexpr uint32_t kRefBytes = 128 * 4;                             // m_ref per query row
 constexpr uint32_t kXmaxBytes = 0;
+constexpr uint32_t kPidTiles = 8;                                   // page ids kept for this many tiles
+constexpr uint32_t kPidBytes = kPidTiles * 32 * 4;                  // one id per producer lane and tile
 __host__ __device__ constexpr uint32_t tc_smem_bytes(uint32_t d)
 {
-    return tc_smem_tiles(d) + kRefBytes + kXmaxBytes + kNumBars * 8 + 16 + 1024;
+    return tc_smem_tiles(d) + kRefBytes + kXmaxBytes + kNumBars * 8 + 16 + kPidBytes + 1024;
 }
 static_assert(tc_smem_bytes(128) <= 227 * 1024, "shared memory");
 
-template <uint32_t D>
+// PAGED: K/V tiles gathered page by page (a separate instantiation: the extra code costs the
+// contiguous form 3 % when it is merely present).
+template <uint32_t D, bool PAGED>
 __global__ void __launch_bounds__(kTcThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const TcParams p)
@@ -337,7 +356,66 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
     };
 
-    if (warp == kSoftmaxWarps) {
+    if (warp == kSoftmaxWarps && PAGED) {
+        // ------------------------------------------------ TMA producer, paged cache (whole warp) ---
+        // A tile is 128 / P pages; lane l brings (page l / halves, column half l % halves) of a tile with
+        // one copy of P rows x 128 bytes, to where the whole-tile box of the contiguous form would
+        // have put those rows (P is a multiple of 8, so the 128-byte swizzle pattern lines up).  Page
+        // ids are read six tiles ahead and parked in shared memory, one word per lane and tile.
+        // Rows past kv_len are not loaded: K columns there are masked, V rows are cleared by the
+        // softmax group of the last tile.
+        constexpr uint32_t kHalves = D / 64, kHalfBytes = kBN * 128;
+        const uint32_t P = p.page_size, per_tile = kBN / P;
+        const uint32_t my_page = lane / kHalves, my_half = lane % kHalves;
+        const uint32_t total_pages = (p.kv_len + P - 1) / P;
+        uint32_t *pid = reinterpret_cast<uint32_t *>(smem + kSmemTiles + kRefBytes + kXmaxBytes + kNumBars * 8 + 16);
+        auto pages_of = [&](uint32_t t) { return min(per_tile, total_pages - min(total_pages, t * per_tile)); };
+        auto read_id = [&](uint32_t t) -> uint32_t {
+            return (t < n_tiles && my_page < pages_of(t)) ? __ldg(p.page_table_row + t * per_tile + my_page) : 0u;
+        };
+        auto load_tile = [&](uint32_t dst_tile, const CUtensorMap *tm, uint32_t t, uint32_t barrier) {
+            if (my_page < pages_of(t)) {
+                const uint32_t id = pid[(t % kPidTiles) * 32 + lane];
+                tma_load_4d(dst_tile + my_half * kHalfBytes + my_page * P * 128, tm, 0, 0, (int32_t)my_half,
+                            (int32_t)(id * p.n_kv_heads + kvh), barrier);
+            }
+        };
+        auto tile_bytes = [&](uint32_t t) { return pages_of(t) * P * D * 2; };
+        for (uint32_t t = 0; t < 6; ++t) pid[(t % kPidTiles) * 32 + lane] = read_id(t);
+        uint32_t pending = read_id(6);
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_k);
+            tma_prefetch_desc(&tm_v);
+            mbar_arrive_expect_tx(bar(kQFull), kTile);
+            tma_load_4d(q_smem, &tm_q, 0, (int32_t)row0, 0, (int32_t)head, bar(kQFull));
+            for (uint32_t i = 0; i < min(n_tiles, 3u); ++i) mbar_arrive_expect_tx(bar(kKFull + i), tile_bytes(i));
+        }
+        __syncwarp();
+        for (uint32_t i = 0; i < min(n_tiles, 3u); ++i) load_tile(k_smem + i * kTile, &tm_k, i, bar(kKFull + i));
+        uint32_t b = 0, ph = 0;  // slot i % 3 and phase (i / 3) & 1
+        for (uint32_t i = 0; i < n_tiles; ++i) {
+            // ids of tile i + 6 arrived during the last iteration; those of tile i + 7 are requested now
+            pid[((i + 6) % kPidTiles) * 32 + lane] = pending;
+            pending = read_id(i + 7);
+            const bool with_k = i + 3 < n_tiles;
+            if (lane == 0) {
+                if (i >= 3) wait(bar(kOFull + b), ph ^ 1, 16u);  // P V (i - 3) done: V slot b is free
+                mbar_arrive_expect_tx(bar(kVFull + b), tile_bytes(i) + (with_k ? tile_bytes(i + 3) : 0u));
+            }
+            __syncwarp();
+            load_tile(v_smem + b * kTile, &tm_v, i, bar(kVFull + b));
+            if (with_k) {
+                if (lane == 0) wait(bar(kSFull + b), ph, 16u);  // Q K^T (i) done: K slot b is free
+                __syncwarp();
+                load_tile(k_smem + b * kTile, &tm_k, i + 3, bar(kVFull + b));
+            }
+            if (++b == 3) {
+                b = 0;
+                ph ^= 1;
+            }
+        }
+    } else if (warp == kSoftmaxWarps) {
         // ---------------------------------------------------------------- TMA producer ---
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
@@ -676,6 +754,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 l_part += sum0 + sum1;
             }
             TC_PROF_MARK(pt3)
+            if (PAGED && i + 1 == n_tiles && p.kv_len < (i + 1) * kBN) {
+                // Paged cache: the rows of this tile past kv_len were never written or never loaded.
+                // Their weights are exactly zero, but zero times a stale NaN is not: clear them in V
+                // once V(i) has landed and before this group reports P(i).
+                wait(bar(kVFull + b), sph, 64u);
+                clear_dead_rows<D>(smem + (v_smem - smem_base) + b * kTile, p.kv_len - i * kBN,
+                                   (warp % (4 * kRowSplit)) * 32 + lane);
+            }
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
@@ -748,7 +834,7 @@ extern "C" __attribute__((visibility("default"))) int mf_debug_tc_profile(unsign
 // Returns MF_ERR_OPERATION_NOT_SUPPORTED (without touching last_error semantics) when the
 // shape is outside this kernel's envelope; the caller then uses the mma.sync kernel.
 mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const void *v, void *out,
-                            const SdpaPrefillSplitKParams &sp, bool *handled)
+                            const SdpaPrefillSplitKParams &sp, bool *handled, const MfPagedKv *paged, uint32_t seq)
 {
     *handled = false;
     const SdpaPrefillParams &b = sp.base;
@@ -757,8 +843,15 @@ mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const 
     if (b.stride_k_s != kD || b.stride_v_s != kD) return MF_OK;
     if ((b.q_stride_m % 8) || (b.q_stride_h % 8) || (b.out_stride_m % 8) || (b.out_stride_h % 8)) return MF_OK;
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 15u) return MF_OK;
-    if (b.k_stride_h % 8 || b.v_stride_h % 8 || (reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u)
+    if (paged) {
+        // pages of 8 to 128 rows (a power of two): a tile is a whole number of pages
+        if (paged->page_size < 8 || paged->page_size > kBN) return MF_OK;
+        k = paged->k_pool, v = paged->v_pool;
+        if ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u) return MF_OK;
+    } else if (b.k_stride_h % 8 || b.v_stride_h % 8 ||
+               (reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u) {
         return MF_OK;
+    }
     if (!ctx->encode_fn) {
         cudaDriverEntryPointQueryResult qr;
         void *fn = nullptr;
@@ -788,9 +881,31 @@ mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const 
     mf_status st;
     // Unusual strides the encoder refuses are left to the other kernel.
     if (!encode(&tm_q, q, b.q_len, sp.n_heads, b.q_stride_m, b.q_stride_h)) return MF_OK;
-    if (!encode(&tm_k, k, b.kv_len, cache_heads, kD, b.k_stride_h, 128 / MF_TC_LOAD_DIV)) return MF_OK;
-    if (!encode(&tm_v, v, b.kv_len, cache_heads, kD, b.v_stride_h, 128 / MF_TC_LOAD_DIV)) return MF_OK;
+    if (paged) {
+        // pool [n_pages, Hkv, P, D] as (64 columns, P rows, column halves, page x kv head); one copy = one
+        // column half of one page of one kv head
+        auto encode_pool = [&](CUtensorMap *tm, const void *base) {
+            const uint64_t P = paged->page_size;
+            cuuint64_t gdim[4] = {64, P, kD / 64, (uint64_t)paged->n_pages * paged->n_kv_heads};
+            cuuint64_t gstride[3] = {(uint64_t)kD * 2, 128, P * kD * 2};
+            cuuint32_t box[4] = {64, (cuuint32_t)P, 1, 1};
+            cuuint32_t estr[4] = {1, 1, 1, 1};
+            return reinterpret_cast<EncodeFn>(ctx->encode_fn)(
+                       tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(base), gdim, gstride, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+        };
+        if (!encode_pool(&tm_k, k) || !encode_pool(&tm_v, v)) return MF_OK;
+    } else {
+        if (!encode(&tm_k, k, b.kv_len, cache_heads, kD, b.k_stride_h, 128 / MF_TC_LOAD_DIV)) return MF_OK;
+        if (!encode(&tm_v, v, b.kv_len, cache_heads, kD, b.v_stride_h, 128 / MF_TC_LOAD_DIV)) return MF_OK;
+    }
     TcParams p{};
+    if (paged) {
+        p.page_table_row = paged->page_table + (size_t)seq * paged->page_table_stride;
+        p.page_size = paged->page_size;
+        p.n_kv_heads = paged->n_kv_heads;
+    }
     p.out = static_cast<__half *>(out);
     p.status = ctx->d_status;
     p.q_len = b.q_len;
@@ -800,13 +915,14 @@ mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const 
     p.out_stride_h = b.out_stride_h;
     p.out_stride_m = b.out_stride_m;
     p.scale_log2 = b.scale * 1.4426950408889634f;
-    static bool configured[64][2] = {};
-    const int di = kD == 128 ? 1 : 0;
+    static bool configured[64][4] = {};
+    const int di = (kD == 128 ? 1 : 0) + (paged ? 2 : 0);
     const uint32_t smem_bytes = tc_smem_bytes(kD);
+    void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, TcParams) =
+        di == 0 ? prefill_tc_kernel<64, false> : di == 1 ? prefill_tc_kernel<128, false>
+        : di == 2 ? prefill_tc_kernel<64, true> : prefill_tc_kernel<128, true>;
     if (ctx->device < 64 && !configured[ctx->device][di]) {
-        st = check_cuda(ctx,
-                        di ? cudaFuncSetAttribute(prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes)
-                           : cudaFuncSetAttribute(prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes),
+        st = check_cuda(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes),
                         "cudaFuncSetAttribute(prefill_tc)");
         if (st != MF_OK) return st;
         configured[ctx->device][di] = true;
@@ -814,8 +930,7 @@ mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const 
     p.n_heads = sp.n_heads;
     p.n_q_tiles = (b.q_len + kBM - 1) / kBM;
     dim3 grid(p.n_q_tiles * sp.n_heads);
-    if (di) prefill_tc_kernel<128><<<grid, kTcThreads, smem_bytes, ctx->stream>>>(tm_q, tm_k, tm_v, p);
-    else prefill_tc_kernel<64><<<grid, kTcThreads, smem_bytes, ctx->stream>>>(tm_q, tm_k, tm_v, p);
+    kern<<<grid, kTcThreads, smem_bytes, ctx->stream>>>(tm_q, tm_k, tm_v, p);
     *handled = true;
     return check_launch(ctx, "prefill_tc_kernel");
 }

@@ -20,6 +20,12 @@ CASES = [
     (8, 8, 128, 32, 0, 70),
     (16, 2, 128, 128, 1000, 48),
     (8, 2, 64, 8, 2100, 17),     # long enough for the split-K route
+    # chunks of 64 rows and more take the tcgen05 kernel, which gathers its 128-key tiles page by page
+    (16, 2, 128, 16, 500, 333),  # ragged tail: 833 keys, the last page holds one row
+    (14, 2, 64, 16, 300, 200),
+    (8, 2, 128, 8, 130, 129),
+    (16, 2, 128, 128, 1000, 148),
+    (24, 8, 128, 64, 2048, 512),
 ]
 
 
@@ -72,6 +78,19 @@ def test_paged_chunked_prefill(mfk, foundry, case):
         assert np.array_equal(got, cache_ref.reshape(hkv, L, d))
     assert max_abs(host(out), want) <= TOL
     assert max_abs(host(out), gold) <= TOL
+    if m >= 64 and mfk.prefill_split_k(L, m) == 1:
+        # both kernels on the same pages: the tcgen05 one (or fail) and the mma.sync one
+        outs = {}
+        for impl in (2, 1):
+            foundry.set_option(3, impl)
+            o = torch.full((m, hq * d), float("nan"), dtype=torch.float16, device="cuda")
+            foundry.paged_prefill(desc, q_rot, o, seq=0, q_len=m, kv_len=L, query_offset=cached, n_heads=hq,
+                                  scale=float(scale))
+            foundry.synchronize()
+            outs[impl] = host(o)
+        foundry.set_option(3, 0)
+        assert max_abs(outs[2], want) <= TOL and max_abs(outs[2], gold) <= TOL
+        assert max_abs(outs[1], want) <= TOL
 
 
 def test_paged_prefill_rejects_bad_arguments(mfk, foundry):
