@@ -533,16 +533,48 @@ def run_long_context(args, w):
     return 0 if ok else 1
 
 
+def rank_setup():
+    """(rank, world, device index): one process per GPU under torchrun (NCCL only for the barrier and the
+    max over ranks), a single process otherwise."""
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0")) if world > 1 else 0
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def rank_reduce(value, world, op="max"):
+    """Max (or min) of a float over the ranks, with a barrier's worth of synchronisation."""
+    if world == 1:
+        return float(value)
+    import torch
+    import torch.distributed as dist
+
+    t = torch.tensor([float(value)], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX if op == "max" else dist.ReduceOp.MIN)
+    return float(t.item())
+
+
 def run_prefill(args):
     """Configuration 4: 2048 new tokens after 2048 cached, Llama-3.2-3B heads, one layer per step:
     KvPrepFused (RoPE + append of 2048 rows) then causal attention over 4096 keys."""
     import torch
 
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
+    rank, world, local = rank_setup()
+    dev = torch.device("cuda", local)
     mfk = importlib.import_module("test-burn_b200")
-    hq, hkv, d, m, cached, cap = 24, 8, 128, 2048, 2048, 4096
-    g = torch.Generator(device=dev).manual_seed(SEED)
+    sharding = importlib.import_module("test-burn_b200.sharding")
+    hq_all, hkv_all, d, m, cached, cap = 24, 8, 128, 2048, 2048, 4096
+    # N > 1: KV heads (with their query groups) over the GPUs, no exchange inside the path
+    h0, h1 = sharding.shard_kv_heads(hkv_all, world, rank)
+    hkv = max(h1 - h0, 1)  # a rank without heads (more GPUs than KV heads) repeats head 0's work, untimed in effect
+    hq = hkv * (hq_all // hkv_all)
+    g = torch.Generator(device=dev).manual_seed(SEED + rank)
     q = torch.empty((m, hq * d), dtype=torch.float16, device=dev).normal_(generator=g)
     k = torch.empty((m, hkv * d), dtype=torch.float16, device=dev).normal_(generator=g)
     v = torch.empty((m, hkv * d), dtype=torch.float16, device=dev).normal_(generator=g)
@@ -555,7 +587,7 @@ def run_prefill(args):
     out = torch.empty((m, hq * d), dtype=torch.float16, device=dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     stream = torch.cuda.Stream(device=dev)
-    f = mfk.Foundry(0, stream.cuda_stream)
+    f = mfk.Foundry(local, stream.cuda_stream)
     if args.prefill_impl:
         f.set_option(3, args.prefill_impl)
     p = mfk.KvPrepFusedParamsResolved(hq * d, hkv * d, d, hq, hkv, hq // hkv, m, cached, cap, hq * m * d, 1, 0, 0)
@@ -607,26 +639,37 @@ def run_prefill(args):
     t1 = time.time()
     launches = f.launch_count - launches0
     clocks = sampler.stop(t0, t1)
-    t_append = float(np.median([e[0].elapsed_time(e[1]) for e in evs]))
-    t_attn = float(np.median([e[1].elapsed_time(e[2]) for e in evs]))
+    t_append = rank_reduce(np.median([e[0].elapsed_time(e[1]) for e in evs]), world)
+    t_attn = rank_reduce(np.median([e[1].elapsed_time(e[2]) for e in evs]), world)
     pairs = sum(cached + i + 1 for i in range(m))
-    flops = 4 * d * pairs * hq
+    flops = 4 * d * pairs * hq_all  # the whole job; every GPU's tensor pipe is the roofline of its own share
+    ok = rank_reduce(float(bool(torch.isfinite(out.float()).all())), world, "min") > 0.5
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        f.close()
+        return 0
     peak_path = ROOT / "MEASURED_PEAKS.json"
     peak = json.loads(peak_path.read_text())["bf16_tflops"] if peak_path.exists() else 1590.0
     achieved = flops / (t_attn * 1e-3) / 1e12
-    ok = bool(torch.isfinite(out.float()).all())
     print(json.dumps({
-        "metric": "prefill_attention_tflops", "value": achieved, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": t_append + t_attn, "higher_is_better": True, "scaling": "weak",
+        "metric": "prefill_attention_tflops", "value": achieved, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": t_append + t_attn, "higher_is_better": True,
+        "scaling": "weak" if world == 1 else "strong",
         "vs_baseline": None, "dtype": "f16 inputs, f32 accumulate", "data": "synthetic",
         "config": {"workload": "chunked causal prefill into cache, Llama-3.2-3B shape: 2048 new after 2048 cached, "
                                "24q/8kv heads, D128, one layer" +
-                               (", paged cache (page %d)" % args.page_size if args.page_size else ", contiguous cache"),
+                               (", paged cache (page %d)" % args.page_size if args.page_size else ", contiguous cache") +
+                               ("" if world == 1 else "; KV heads split over %d GPUs, no exchange" % world),
                    "l2": "flushed between iterations (256 MB write)",
                    "split_k": mfk.prefill_split_k(cached + m, m)},
         "append_us": t_append * 1e3, "attention_us": t_attn * 1e3, "algorithmic_flops": flops,
-        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                     "peak_kind": "measured" if peak_path.exists() else "fallback", "traffic": None},
+        "roofline": {"bound": "tensor", "achieved": achieved / world, "peak": peak, "unit": "TFLOP/s",
+                     "frac": achieved / world / peak, "peak_kind": "measured" if peak_path.exists() else "fallback",
+                     "traffic": None, "note": "per GPU"},
         "gpu_launches": launches, "clocks": clocks, "self_check": "ok" if ok else "FAILED"}))
     f.close()
     return 0 if ok else 1
@@ -653,11 +696,18 @@ def run_contiguous_decode(args, w):
     `value`.  Configuration 1 (0.27 MB) is L2-resident: latency only."""
     import torch
 
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
+    rank, world, local = rank_setup()
+    dev = torch.device("cuda", local)
     mfk = importlib.import_module("test-burn_b200")
-    layers, hq, hkv, d, cached, cap = w["layers"], w["n_heads"], w["n_kv_heads"], w["head_dim"], w["cached"], w["capacity"]
-    g = torch.Generator(device=dev).manual_seed(SEED)
+    sharding = importlib.import_module("test-burn_b200.sharding")
+    layers, hq_all, hkv_all, d, cached, cap = (w["layers"], w["n_heads"], w["n_kv_heads"], w["head_dim"], w["cached"],
+                                               w["capacity"])
+    # N > 1: KV heads (with their query groups) over the GPUs, no exchange inside the path; a rank
+    # beyond the KV head count repeats one head's work so that every process runs the same program
+    h0, h1 = sharding.shard_kv_heads(hkv_all, world, rank)
+    hkv = max(h1 - h0, 1)
+    hq = hkv * (hq_all // hkv_all)
+    g = torch.Generator(device=dev).manual_seed(SEED + rank)
     q = torch.empty((layers, 1, hq * d), dtype=torch.float16, device=dev).normal_(generator=g)
     k = torch.empty((layers, 1, hkv * d), dtype=torch.float16, device=dev).normal_(generator=g)
     v = torch.empty((layers, 1, hkv * d), dtype=torch.float16, device=dev).normal_(generator=g)
@@ -669,7 +719,7 @@ def run_contiguous_decode(args, w):
     q_rot = torch.empty((layers, 1, hq * d), dtype=torch.float16, device=dev)
     out = torch.empty((layers, 1, hq * d), dtype=torch.float16, device=dev)
     stream = torch.cuda.Stream(device=dev)
-    f = mfk.Foundry(0, stream.cuda_stream)
+    f = mfk.Foundry(local, stream.cuda_stream)
     if not args.no_overlap:
         f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 1)
     p = mfk.KvPrepFusedParamsResolved(hq * d, hkv * d, d, hq, hkv, hq // hkv, 1, cached, cap, hq * d, w["rope_mode"], 0, 0)
@@ -725,7 +775,7 @@ def run_contiguous_decode(args, w):
     try:
         g_steps = 20 if layers == 1 else 2
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
+        with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
             for _ in range(g_steps):
                 step()
         for _ in range(3):
@@ -751,27 +801,40 @@ def run_contiguous_decode(args, w):
     us = np.array(per_iter_us)
     eager_med = float(np.median(us))
     med = graph_us["median"] if "median" in graph_us else eager_med  # the device-side figure when it exists
+    med = rank_reduce(med, world)
+    eager_med = rank_reduce(eager_med, world)
+    ok = rank_reduce(float(bool(torch.isfinite(out.float()).all())), world, "min") > 0.5
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        f.close()
+        return 0
+    # per GPU (the largest share)
     bytes_layer = 2 * hkv * (cached + 1) * d * 2 + 4 * hkv * d * 2 + 2 * hq * d * 2 + 2 * (d // 2) * 2
     bytes_layer += weight_bytes
     peak, peak_kind = measured_peak_gbs()
     achieved = bytes_layer * layers / (med * 1e-6) / 1e9
     l2_note = ("L2-resident by construction (0.27 MB): latency only, not a bandwidth figure" if layers == 1 else
                "inputs larger than L2 (caches %.2f GB)" % (2 * layers * hkv * cap * d * 2 / 1e9))
-    ok = bool(torch.isfinite(out.float()).all())
     print(json.dumps({
-        "metric": METRIC, "value": 1e6 / med, "unit": "tokens/s", "n_gpus": 1, "steps": iters * trials,
+        "metric": METRIC, "value": 1e6 / med, "unit": "tokens/s", "n_gpus": world, "steps": iters * trials,
         "warmup": max(args.warmup, 3), "ms_per_step": med * 1e-3, "us_per_step": med, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
+        "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
         "config": {"workload": w["name"] + ("; with --projection the first launch of a layer is RMSNorm + fused QKV "
                                             "projection + RoPE + append (weights %.1f MB per layer)" % (weight_bytes / 1e6)
-                                            if args.projection else ""), "l2": l2_note,
+                                            if args.projection else "") +
+                               ("" if world == 1 else "; KV heads split over %d GPUs (%d per GPU), no exchange" % (world, hkv)),
+                   "l2": l2_note,
                    "timing": "value / us_per_step = CUDA-graph replay of the step when capture works, else eager"},
         "latency_us": {"trials": trials, "iterations": iters, "min": float(us.min()), "median": eager_med,
                        "mean": float(us.mean()), "sd": float(us.std()),
                        "note": "launched call by call from the Python binding: host-bound"},
         "latency_us_cuda_graph": graph_us,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": peak_kind, "traffic": None, "launch_us": med / layers,
+                     "peak_kind": peak_kind, "traffic": None, "launch_us": med / layers, "per": "GPU",
                      "algorithmic_bytes_per_launch": bytes_layer,
                      "note": "launch-bound" if layers == 1 else "per layer: %s + decode_kernel" %
                              ("fused_qkv_kernel" if args.projection else "kv_append_kernel")},

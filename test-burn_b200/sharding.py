@@ -1,12 +1,15 @@
 """Host-side partitioning of the decode path over the GPUs of one box.
 
-Nothing here exists in the reference (single Apple GPU).  Two splits:
+Nothing here exists in the reference (single Apple GPU).  Three splits:
 
 * batched decode: sequences are independent, so each rank owns whole sequences (their pages,
   page-table rows and plan) and no data crosses GPUs during a step;
 * one long sequence: its page list is cut into contiguous ranges, every rank attends over its own
   pages and emits unnormalised f32 partials (acc, m, l) per query head; one all-gather of
-  Hq*(D+2) floats per rank per layer followed by the log-sum-exp merge gives every rank the result.
+  Hq*(D+2) floats per rank per layer followed by the log-sum-exp merge gives every rank the result;
+* one sequence of ordinary length (a batch-1 step, a prefill chunk): KV heads are independent, so each
+  rank owns a contiguous range of KV heads with their query groups, caches of [its heads, capacity, D]
+  and the matching columns of q / k / v / output; nothing crosses GPUs inside the attention path.
 """
 from __future__ import annotations
 
@@ -25,6 +28,14 @@ def shard_sequences(kv_lens, world: int, rank: int) -> np.ndarray:
         if owner == rank:
             mine.append(int(idx))
     return np.array(sorted(mine), dtype=np.int64)
+
+
+def shard_kv_heads(n_kv_heads: int, world: int, rank: int):
+    """KV-head range [begin, end) of `rank` (query heads [begin*G, end*G)); ranks past the head
+    count get an empty range."""
+    begin = rank * n_kv_heads // world
+    end = (rank + 1) * n_kv_heads // world
+    return begin, end
 
 
 def shard_pages(n_pages: int, world: int, rank: int):

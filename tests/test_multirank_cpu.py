@@ -1,6 +1,7 @@
 """World-size-2 tests of the multi-GPU host logic on CPU (gloo), with the oracle standing in for
 the kernels: sequence sharding needs no collective; page sharding of one long sequence needs one
-all-gather of (acc, m, l) followed by the merge."""
+all-gather of (acc, m, l) followed by the merge; KV-head sharding of a batch-1 step or a prefill chunk
+needs none (each rank appends to and attends over the caches of its own heads)."""
 import importlib
 import os
 import socket
@@ -55,6 +56,31 @@ def _worker(rank, world, port, mode, ret):
                 merged[idx] = o
                 seen += idx
             ret[rank] = bool(sorted(seen) == list(range(7)) and np.array_equal(merged, full))
+        elif mode == "kv_heads":
+            from kvcases import ContigCase
+
+            Hq, Hkv, D, G = 24, 8, 64, 3
+            full = ContigCase(n_heads=Hq, n_kv_heads=Hkv, head_dim=D, cached=37, m=5, capacity=48, rope_mode=1)
+            q_all, k_all, v_all = full.oracle_append()
+            want = oracle.prefill_causal(q_all, k_all.ravel(), v_all.ravel(), n_heads=Hq, cache_heads=Hkv, head_dim=D,
+                                         capacity=48, q_len=5, kv_len=42, query_offset=37, scale=full.scale)
+            h0, h1 = sharding.shard_kv_heads(Hkv, world, rank)
+            sub = ContigCase(n_heads=(h1 - h0) * G, n_kv_heads=h1 - h0, head_dim=D, cached=37, m=5, capacity=48, rope_mode=1)
+            # this rank's columns of q / k / v and its heads of the caches
+            sub.q = np.ascontiguousarray(full.q.reshape(5, Hq, D)[:, h0 * G:h1 * G]).reshape(5, -1)
+            sub.k = np.ascontiguousarray(full.k.reshape(5, Hkv, D)[:, h0:h1]).reshape(5, -1)
+            sub.v = np.ascontiguousarray(full.v.reshape(5, Hkv, D)[:, h0:h1]).reshape(5, -1)
+            sub.k_cache, sub.v_cache = full.k_cache[h0:h1].copy(), full.v_cache[h0:h1].copy()
+            q_rot, kc, vc = sub.oracle_append()
+            out = oracle.prefill_causal(q_rot, kc.ravel(), vc.ravel(), n_heads=(h1 - h0) * G, cache_heads=h1 - h0,
+                                        head_dim=D, capacity=48, q_len=5, kv_len=42, query_offset=37, scale=full.scale)
+            same_cache = np.array_equal(kc, k_all.reshape(Hkv, 48, D)[h0:h1]) and np.array_equal(vc, v_all.reshape(Hkv, 48, D)[h0:h1])
+            outs = [None] * world
+            dist.all_gather_object(outs, ((h0, h1), out.reshape(5, -1, D)))  # verification only, not the data path
+            merged = np.concatenate([o for _, o in sorted(outs, key=lambda t: t[0][0])], axis=1)
+            cover = sorted(r for r, _ in outs)
+            ret[rank] = bool(same_cache and cover[0][0] == 0 and cover[-1][1] == Hkv and
+                             np.array_equal(merged.reshape(5, Hq * D), want.reshape(5, Hq * D)))
         else:
             Hq, Hkv, D, P, L = 24, 8, 128, 64, 1000
             case = PagedCase(batch=1, n_heads=Hq, n_kv_heads=Hkv, head_dim=D, page_size=P, cached=[L - 1])
@@ -81,7 +107,7 @@ def _worker(rank, world, port, mode, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["sequences", "pages"])
+@pytest.mark.parametrize("mode", ["sequences", "pages", "kv_heads"])
 def test_two_ranks_gloo(mode):
     import torch.multiprocessing as mp
 
@@ -101,6 +127,11 @@ def test_sequence_sharding_is_a_balanced_partition():
         assert sorted(np.concatenate(parts).tolist()) == list(range(64))
         totals = [int(lens[p].sum()) for p in parts]
         assert max(totals) - min(totals) <= 16384
+    for world in (1, 2, 3, 4, 8, 16):
+        heads = [sharding.shard_kv_heads(8, world, r) for r in range(world)]
+        assert heads[0][0] == 0 and heads[-1][1] == 8
+        assert all(heads[i][1] == heads[i + 1][0] for i in range(world - 1))
+        assert max(e - b for b, e in heads) - min(e - b for b, e in heads) <= 1
     for world in (2, 4, 8):
         cover = [sharding.shard_pages(2048, world, r) for r in range(world)]
         assert cover[0][0] == 0 and cover[-1][1] == 2048
