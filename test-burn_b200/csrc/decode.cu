@@ -36,7 +36,7 @@ constexpr uint32_t kThreads = kConsumerThreads + 32;
 constexpr float kNegSentinel = -1e30f;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per barrier wait
 constexpr float kLn2 = 0.6931471805599453f;
-constexpr uint32_t kMergeFlight = 16;  // partials whose loads are in flight together in the merge
+constexpr uint32_t kMergeFlight = 20;  // partials whose loads are in flight together in the merge
 
 #ifdef MF_DEC_PROFILE
 // Development aid (build with -DMF_DEC_PROFILE): global-timer stamps of one consumer thread per CTA.
