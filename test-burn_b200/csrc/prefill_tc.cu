@@ -82,7 +82,7 @@ struct TcParams {
     float scale_log2;
     // paged cache: K/V tiles are gathered page by page through the sequence's page-table row
     const uint32_t *page_table_row;  // null: contiguous cache
-    uint32_t page_size, n_kv_heads;
+    uint32_t page_size, page_shift, n_kv_heads;  // page_size = 1 << page_shift
 };
 
 #ifdef MF_TC_PROFILE
@@ -253,13 +253,41 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void *tmap, int3
 // Zero rows [first_dead, 128) of a V tile laid out [column half][128 rows][128 bytes]; called by the
 // 128 * kRowSplit threads of one softmax group (rarely: kept out of line, off the tile loop's registers).
 template <uint32_t D>
-__device__ __noinline__ void clear_dead_rows(uint8_t *v_tile, uint32_t first_dead, uint32_t gtid)
+__device__ __noinline__ void clear_dead_rows(uint8_t *v_tile, uint32_t first_dead, uint32_t gtid, uint32_t page_shift)
 {
+    // paged V tile: [page][half][P rows][128 bytes] (head_dim 128), [128 rows][128 bytes] (head_dim 64)
     for (uint32_t c = gtid; c < (kBN - first_dead) * (D / 8); c += 128 * kRowSplit) {
         const uint32_t r = first_dead + c / (D / 8), ch = c % (D / 8);
-        *reinterpret_cast<uint4 *>(v_tile + (ch / 8) * (kBN * 128) + r * 128 + (ch % 8) * 16) = make_uint4(0, 0, 0, 0);
+        const uint32_t off = D == 64 ? r * 128
+                                     : ((r >> page_shift) << (page_shift + 8)) + ((ch / 8) << (page_shift + 7)) +
+                                           ((r & ((1u << page_shift) - 1)) << 7);
+        *reinterpret_cast<uint4 *>(v_tile + off + (ch % 8) * 16) = make_uint4(0, 0, 0, 0);
     }
     fence_proxy_async();
+}
+
+// Where the 16 keys of P V step kk start inside a V tile, and the distance between the two 64-column
+// halves.  Contiguous cache (and head_dim 64): [half][128 rows][128 bytes].  Paged cache, head_dim 128:
+// [page][half][P rows][128 bytes], one TMA copy per page.
+template <uint32_t D, bool PAGED>
+__device__ __forceinline__ uint32_t v_step_offset(uint32_t kk, uint32_t page_shift)
+{
+    if (!PAGED || D == 64) return kk * 2048;
+    const uint32_t row = kk * 16;
+    return ((row >> page_shift) << (page_shift + 8)) + ((row & ((1u << page_shift) - 1)) << 7);
+}
+template <uint32_t D, bool PAGED>
+__device__ __forceinline__ uint32_t v_half_stride(uint32_t page_shift)
+{
+    return (!PAGED || D == 64) ? kHalfTile : (128u << page_shift);
+}
+
+// Distance between the two 8-key groups of a step: the next 1024 bytes, except with 8-row pages, where
+// the second group is the next page.
+template <uint32_t D, bool PAGED>
+__device__ __forceinline__ uint32_t v_group_stride(uint32_t page_shift)
+{
+    return (PAGED && D == 128 && page_shift == 3) ? 2048u : 1024u;
 }
 
 // Barrier slots (8 bytes each) after the tiles.
@@ -404,7 +432,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 mbar_arrive_expect_tx(bar(kVFull + b), tile_bytes(i) + (with_k ? tile_bytes(i + 3) : 0u));
             }
             __syncwarp();
-            load_tile(v_smem + b * kTile, &tm_v, i, bar(kVFull + b));
+            // V: one copy per page, both column halves, landing as [page][half][P rows][128 bytes]; the
+            // P V products address it with their own descriptor (see v_step_offsets).  The page's id
+            // sits in the ring slot of the lane that brings the page's first K half.
+            if (lane < pages_of(i))
+                tma_load_4d(v_smem + b * kTile + lane * (kHalves * P * 128), &tm_v, 0, 0, 0,
+                            (int32_t)(pid[(i % kPidTiles) * 32 + lane * kHalves] * p.n_kv_heads + kvh), bar(kVFull + b));
             if (with_k) {
                 if (lane == 0) wait(bar(kSFull + b), ph, 16u);  // Q K^T (i) done: K slot b is free
                 __syncwarp();
@@ -485,15 +518,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // ------------------------------------------------- MMA issuer for P V (split issue) ---
         if (lane == 0) {
             constexpr uint32_t kIdescPV = instr_desc(D, 1);
+            uint32_t voff[kBN / 16];  // descriptor address steps of the eight products of a tile
+#pragma unroll
+            for (uint32_t kk = 0; kk < kBN / 16; ++kk) voff[kk] = v_step_offset<D, PAGED>(kk, p.page_shift) >> 4;
             uint32_t b = 0, ph = 0;
             for (uint32_t i = 0; i < n_tiles; ++i) {
                 wait(bar(kVFull + b), ph, 64u);
                 wait(bar(kPFull + b), ph, 64u);
                 tc_fence_after();
-                const uint64_t v_desc = smem_desc(v_smem + b * kTile, kHalfTile, 1024);
+                const uint64_t v_desc = smem_desc(v_smem + b * kTile, v_half_stride<D, PAGED>(p.page_shift), v_group_stride<D, PAGED>(p.page_shift));
 #pragma unroll
                 for (uint32_t kk = 0; kk < kBN / 16; ++kk)
-                    tc_mma_ts(tmem + 384, tmem + b * 128 + kk * 8, v_desc + kk * (2048 >> 4), kIdescPV, (i > 0 || kk > 0) ? 1u : 0u);
+                    tc_mma_ts(tmem + 384, tmem + b * 128 + kk * 8, v_desc + voff[kk], kIdescPV, (i > 0 || kk > 0) ? 1u : 0u);
                 tc_commit(bar(kOFull + b));
                 if (++b == 3) {
                     b = 0;
@@ -537,11 +573,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 TC_PROF_WAIT(3, wait(bar(kPFull + b), ph, 64u))
                 tc_fence_after();
                 TC_PROF_MARK(ma)
-                const uint64_t v_desc = smem_desc(v_smem + b * kTile, kHalfTile, 1024);
+                const uint64_t v_desc = smem_desc(v_smem + b * kTile, v_half_stride<D, PAGED>(p.page_shift), v_group_stride<D, PAGED>(p.page_shift));
 #pragma unroll
                 for (uint32_t kk = 0; kk < kBN / 16 / MF_TC_PROBE_PV_DIV; ++kk) {
                     // A: 16 keys = 8 packed 32-bit TMEM columns per step; B: V rows kk*16.., MN-major.
-                    tc_mma_ts(tmem + 384, tmem + b * 128 + kk * 8, v_desc + kk * (2048 >> 4), kIdescPV,
+                    tc_mma_ts(tmem + 384, tmem + b * 128 + kk * 8,
+                              v_desc + (v_step_offset<D, PAGED>(kk, p.page_shift) >> 4), kIdescPV,
                               (!first || kk > 0) ? 1u : 0u);
                 }
                 TC_PROF_MARK(mb)
@@ -760,7 +797,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 // once V(i) has landed and before this group reports P(i).
                 wait(bar(kVFull + b), sph, 64u);
                 clear_dead_rows<D>(smem + (v_smem - smem_base) + b * kTile, p.kv_len - i * kBN,
-                                   (warp % (4 * kRowSplit)) * 32 + lane);
+                                   (warp % (4 * kRowSplit)) * 32 + lane, p.page_shift);
             }
             tc_wait_st();
             tc_fence_before();
@@ -884,18 +921,19 @@ mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const 
     if (paged) {
         // pool [n_pages, Hkv, P, D] as (64 columns, P rows, column halves, page x kv head); one copy = one
         // column half of one page of one kv head
-        auto encode_pool = [&](CUtensorMap *tm, const void *base) {
+        auto encode_pool = [&](CUtensorMap *tm, const void *base, uint32_t halves_per_copy) {
             const uint64_t P = paged->page_size;
             cuuint64_t gdim[4] = {64, P, kD / 64, (uint64_t)paged->n_pages * paged->n_kv_heads};
             cuuint64_t gstride[3] = {(uint64_t)kD * 2, 128, P * kD * 2};
-            cuuint32_t box[4] = {64, (cuuint32_t)P, 1, 1};
+            cuuint32_t box[4] = {64, (cuuint32_t)P, halves_per_copy, 1};
             cuuint32_t estr[4] = {1, 1, 1, 1};
             return reinterpret_cast<EncodeFn>(ctx->encode_fn)(
                        tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(base), gdim, gstride, box, estr,
                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
         };
-        if (!encode_pool(&tm_k, k) || !encode_pool(&tm_v, v)) return MF_OK;
+        // K by column half (its descriptor needs the 128 rows of a half evenly spaced), V by whole page
+        if (!encode_pool(&tm_k, k, 1) || !encode_pool(&tm_v, v, kD / 64)) return MF_OK;
     } else {
         if (!encode(&tm_k, k, b.kv_len, cache_heads, kD, b.k_stride_h, 128 / MF_TC_LOAD_DIV)) return MF_OK;
         if (!encode(&tm_v, v, b.kv_len, cache_heads, kD, b.v_stride_h, 128 / MF_TC_LOAD_DIV)) return MF_OK;
@@ -904,6 +942,7 @@ mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const 
     if (paged) {
         p.page_table_row = paged->page_table + (size_t)seq * paged->page_table_stride;
         p.page_size = paged->page_size;
+        for (p.page_shift = 0; (1u << p.page_shift) < paged->page_size; ++p.page_shift) {}
         p.n_kv_heads = paged->n_kv_heads;
     }
     p.out = static_cast<__half *>(out);
