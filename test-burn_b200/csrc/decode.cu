@@ -36,7 +36,11 @@ constexpr uint32_t kThreads = kConsumerThreads + 32;
 constexpr float kNegSentinel = -1e30f;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per barrier wait
 constexpr float kLn2 = 0.6931471805599453f;
-constexpr uint32_t kMergeFlight = 20;  // partials whose loads are in flight together in the merge
+#ifndef MF_MERGE_FLIGHT
+#define MF_MERGE_FLIGHT 20
+#endif
+constexpr uint32_t kMergeFlight = MF_MERGE_FLIGHT;  // partials whose loads are in flight together in the merge
+constexpr uint32_t kMergeFlightFew = 8;                // ... for units cut in at most this many parts
 
 #ifdef MF_DEC_PROFILE
 // Development aid (build with -DMF_DEC_PROFILE): global-timer stamps of one consumer thread per CTA.
@@ -722,31 +726,40 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             for (uint32_t j = 0; j < kPerHead; ++j) mx = fmaxf(mx, red[(j * HP + g2) * 2]);
 #pragma unroll
             for (uint32_t j = 0; j < kPerHead; ++j) lt += red[(j * HP + g2) * 2 + 1] * __expf(red[(j * HP + g2) * 2] - mx);
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (uint32_t s0 = 0; s0 < it.n_parts; s0 += kMergeFlight) {
-                float4 v[kMergeFlight];
-                float w[kMergeFlight];
+            // Rounds of F loads in flight; parts are added in order, so F does not change the bits.  Units
+            // cut in a few parts (the batched step) take the narrow form: a round costs F slots whether
+            // they are used or not.
+            auto accumulate = [&](auto flight) {
+                constexpr uint32_t F = decltype(flight)::value;
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (uint32_t s0 = 0; s0 < it.n_parts; s0 += F) {
+                    float4 v[F];
+                    float w[F];
 #pragma unroll
-                for (uint32_t j = 0; j < kMergeFlight; ++j) {
-                    const uint32_t sp = s0 + j;
-                    if (sp < it.n_parts) {
-                        const size_t sl = it.first_slot + sp;
-                        v[j] = __ldcg(reinterpret_cast<const float4 *>(p.part_acc + (sl * HP + g2) * D + d0));
-                        const float ms = sp < kMergeCap ? msv[sp * HP + g2] : __ldcg(p.part_ml + (sl * HP + g2) * 2);
-                        w[j] = __expf(ms - mx);
-                    } else {
-                        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        w[j] = 0.f;
+                    for (uint32_t j = 0; j < F; ++j) {
+                        const uint32_t sp = s0 + j;
+                        if (sp < it.n_parts) {
+                            const size_t sl = it.first_slot + sp;
+                            v[j] = __ldcg(reinterpret_cast<const float4 *>(p.part_acc + (sl * HP + g2) * D + d0));
+                            const float ms = sp < kMergeCap ? msv[sp * HP + g2] : __ldcg(p.part_ml + (sl * HP + g2) * 2);
+                            w[j] = __expf(ms - mx);
+                        } else {
+                            v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            w[j] = 0.f;
+                        }
+                    }
+#pragma unroll
+                    for (uint32_t j = 0; j < F; ++j) {
+                        a.x += v[j].x * w[j];
+                        a.y += v[j].y * w[j];
+                        a.z += v[j].z * w[j];
+                        a.w += v[j].w * w[j];
                     }
                 }
-#pragma unroll
-                for (uint32_t j = 0; j < kMergeFlight; ++j) {
-                    acc.x += v[j].x * w[j];
-                    acc.y += v[j].y * w[j];
-                    acc.z += v[j].z * w[j];
-                    acc.w += v[j].w * w[j];
-                }
-            }
+                return a;
+            };
+            const float4 acc = it.n_parts <= kMergeFlightFew ? accumulate(std::integral_constant<uint32_t, kMergeFlightFew>{})
+                                                             : accumulate(std::integral_constant<uint32_t, kMergeFlight>{});
             const uint32_t h = it.kvh * G + g2;
             if (p.push_world) {
                 const size_t rows = (size_t)p.batch * p.n_heads, rowi = (size_t)it.seq * p.n_heads + h;
