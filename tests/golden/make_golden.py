@@ -51,10 +51,51 @@ def build(name, hq, hkv, d, cached, m, cap, mode, seed, scale):
     return out
 
 
+# Fused QKV projection (name, m, k_dim, n_dim, n_kv, gamma, bias, weights_per_block, lcg seed): the
+# shapes of the reference's tests/fused_qkv_batched_rmsnorm_parity.rs:58-66 and tests/qkv_parity_f16.rs:87-89
+QKV_CASES = [
+    ("qkv_m2_k128_blocked", 2, 128, 128, 64, True, False, 32, 3),
+    ("qkv_m1_k1024_rowmajor_bias", 1, 1024, 1024, 128, True, True, 0, 5),
+]
+
+
+def qkv_inputs(m, k_dim, n_dim, n_kv, gamma, bias, wpb, seed):
+    """Deterministic inputs: activations in [-1, 1), weights and biases in [-0.1, 0.1), gamma in [0.5, 1.5)."""
+    st = seed
+    x, st = oracle.lcg_fill(st, m * k_dim, 1.0)
+    ws = []
+    for n in (n_dim, n_kv, n_kv):
+        w, st = oracle.lcg_fill(st, n * k_dim, 0.1)
+        ws.append(w)
+    g = None
+    if gamma:
+        g, st = oracle.lcg_fill(st, k_dim, 0.5)
+        g = (g.view(np.float16).astype(np.float32) + 1.0).astype(np.float16).view(np.uint16)
+    bs = [None] * 3
+    if bias:
+        bs = []
+        for n in (n_dim, n_kv, n_kv):
+            b, st = oracle.lcg_fill(st, n, 0.1)
+            bs.append(b)
+    return x, ws, g, bs
+
+
+def build_qkv(name, m, k_dim, n_dim, n_kv, gamma, bias, wpb, seed):
+    x, ws, g, bs = qkv_inputs(m, k_dim, n_dim, n_kv, gamma, bias, wpb, seed)
+    if wpb:  # row-major [n, k] -> the reference's blocked layout
+        ws = [np.ascontiguousarray(w.reshape(n, k_dim // wpb, wpb).transpose(1, 0, 2)).ravel()
+              for w, n in zip(ws, (n_dim, n_kv, n_kv))]
+    q, k, v = oracle.fused_qkv(x, *ws, m=m, k_dim=k_dim, n_dim=n_dim, n_kv=n_kv, gamma=g, b_q=bs[0], b_k=bs[1],
+                               b_v=bs[2], weights_per_block=wpb)
+    return {f"{name}/q": q, f"{name}/k": k, f"{name}/v": v}
+
+
 def main():
     data = {}
     for c in CASES:
         data.update(build(*c))
+    for c in QKV_CASES:
+        data.update(build_qkv(*c))
     cos, sin = oracle.rope_tables(1e6, 64, 512)
     data["rope_1e6_d64/cos_rows"] = cos[[0, 1, 2, 255, 511]]
     data["rope_1e6_d64/sin_rows"] = sin[[0, 1, 2, 255, 511]]

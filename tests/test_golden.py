@@ -28,6 +28,8 @@ def test_oracle_reproduces_golden(orc, gold):
     fresh = {}
     for c in make_golden.CASES:
         fresh.update(make_golden.build(*c))
+    for c in make_golden.QKV_CASES:
+        fresh.update(make_golden.build_qkv(*c))
     for k, v in fresh.items():
         assert np.array_equal(v, gold[k]), k
     assert np.array_equal(orc.lcg_fill(1, 256, 0.25)[0], gold["lcg_seed1_scale025"])
@@ -68,3 +70,27 @@ def test_cuda_against_golden(mfk, foundry, gold, case_def):
     assert np.array_equal(host(vc)[:, cached:cached + m], gold[f"{name}/v_rows"])
     if not name.startswith("append"):
         assert max_abs(host(out).reshape(gold[f"{name}/out"].shape), gold[f"{name}/out"]) <= 2e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case_def", make_golden.QKV_CASES, ids=[c[0] for c in make_golden.QKV_CASES])
+def test_cuda_fused_qkv_against_golden(mfk, foundry, gold, case_def):
+    """The projection in front of the append: one f16 ulp of the value plus 1e-3 (f32 sums in another order)."""
+    import torch
+
+    name, m, k_dim, n_dim, n_kv, gamma, bias, wpb, seed = case_def
+    x, ws, g, bs = make_golden.qkv_inputs(m, k_dim, n_dim, n_kv, gamma, bias, wpb, seed)
+    if wpb:
+        ws = [np.ascontiguousarray(w.reshape(n, k_dim // wpb, wpb).transpose(1, 0, 2)).ravel()
+              for w, n in zip(ws, (n_dim, n_kv, n_kv))]
+    out = tuple(torch.zeros(m * n, dtype=torch.float16, device="cuda") for n in (n_dim, n_kv, n_kv))
+    args = foundry.fused_qkv_args(dev(x), *[dev(w) for w in ws], k_dim=k_dim, n_dim=n_dim, n_kv=n_kv, m=m,
+                                  gamma=None if g is None else dev(g),
+                                  bias=None if bs[0] is None else tuple(dev(b) for b in bs), out=out,
+                                  weights_per_block=wpb)
+    foundry.fused_qkv(args)
+    foundry.synchronize()
+    for o, key in zip(out, ("q", "k", "v")):
+        got = host(o).view(np.float16).astype(np.float32)
+        ref = gold[f"{name}/{key}"].view(np.float16).astype(np.float32)
+        assert np.all(np.abs(got - ref) <= np.abs(ref) * 2.0 ** -10 + 1e-3)
