@@ -227,11 +227,16 @@ def run_ours(args, w):
     h_qkv[:, :nq] = h_q.view(layers, -1)
     h_qkv[:, nq:nq + nk] = h_k.view(layers, -1)
     h_qkv[:, nq + nk:] = h_v.view(layers, -1)
-    e2e_qkv = torch.empty((2, nq + 2 * nk), dtype=torch.float16, device=dev)
-    e2e_q = [e2e_qkv[s, :nq].view(B, hq * d) for s in range(2)]
-    e2e_k = [e2e_qkv[s, nq:nq + nk].view(B, hkv * d) for s in range(2)]
-    e2e_v = [e2e_qkv[s, nq + nk:].view(B, hkv * d) for s in range(2)]
-    e2e_out = torch.empty((2, B, hq * d), dtype=torch.float16, device=dev)
+    # Layers travel in groups: one upload and one download per group and slot, two slots in rotation.
+    # Every event wait on the launch stream breaks the programmatic overlap of two launches, so the
+    # fewer the better; the group size keeps a group's transfers well inside its compute time.
+    GROUP = max(1, min(args.e2e_group, layers))
+    n_groups = (layers + GROUP - 1) // GROUP
+    e2e_qkv = torch.empty((2, GROUP, nq + 2 * nk), dtype=torch.float16, device=dev)
+    e2e_q = [[e2e_qkv[s, j, :nq].view(B, hq * d) for j in range(GROUP)] for s in range(2)]
+    e2e_k = [[e2e_qkv[s, j, nq:nq + nk].view(B, hkv * d) for j in range(GROUP)] for s in range(2)]
+    e2e_v = [[e2e_qkv[s, j, nq + nk:].view(B, hkv * d) for j in range(GROUP)] for s in range(2)]
+    e2e_out = torch.empty((2, GROUP, B, hq * d), dtype=torch.float16, device=dev)
     ev_in = [torch.cuda.Event() for _ in range(2)]
     ev_done = [torch.cuda.Event() for _ in range(2)]
     ev_out_free = [torch.cuda.Event() for _ in range(2)]
@@ -241,20 +246,23 @@ def run_ours(args, w):
             d_table.copy_(h_table, non_blocking=True)
             d_lens.copy_(h_lens, non_blocking=True)
         plan.update(kv_lens)
-        for i in range(layers):
-            s = i & 1
+        for gi in range(n_groups):
+            s = gi & 1
+            l0, l1 = gi * GROUP, min(layers, (gi + 1) * GROUP)
             with torch.cuda.stream(copy_in):
-                copy_in.wait_event(ev_done[s])  # the launch that read this slot two layers ago
-                e2e_qkv[s].copy_(h_qkv[i], non_blocking=True)
+                copy_in.wait_event(ev_done[s])  # the launches that read this slot two groups ago
+                e2e_qkv[s, :l1 - l0].copy_(h_qkv[l0:l1], non_blocking=True)
                 ev_in[s].record(copy_in)
             stream.wait_event(ev_in[s])
             stream.wait_event(ev_out_free[s])
-            f.paged_decode(plan, descs[i], e2e_q[s], e2e_out[s], n_heads=hq, k=e2e_k[s], v=e2e_v[s], cos=d_cos,
-                           sin=d_sin, rope=True, rope_mode=w["rope_mode"], append=True, scale=scale)
+            for i in range(l0, l1):
+                j = i - l0
+                f.paged_decode(plan, descs[i], e2e_q[s][j], e2e_out[s, j], n_heads=hq, k=e2e_k[s][j], v=e2e_v[s][j],
+                               cos=d_cos, sin=d_sin, rope=True, rope_mode=w["rope_mode"], append=True, scale=scale)
             ev_done[s].record(stream)
             with torch.cuda.stream(copy_out):
                 copy_out.wait_event(ev_done[s])
-                h_out[i].copy_(e2e_out[s], non_blocking=True)
+                h_out[l0:l1].copy_(e2e_out[s, :l1 - l0], non_blocking=True)
                 ev_out_free[s].record(copy_out)
         stream.wait_stream(copy_out)
 
@@ -918,6 +926,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + sorted(LONG_CONTEXT) + sorted(CONTIGUOUS) + ["c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-group", type=int, default=6, help="layers per host<->device transfer in the end-to-end step")
     ap.add_argument("--exchange", default="fused", choices=["fused", "push", "nccl"],
                     help="long-context workloads: partials exchanged and merged inside the decode kernel (fused), "
                          "exchanged by the decode kernel and merged by a second one (push), or by ncclAllGather")
