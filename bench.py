@@ -231,7 +231,19 @@ def run_ours(args, w):
     # Every event wait on the launch stream breaks the programmatic overlap of two launches, so the
     # fewer the better; the group size keeps a group's transfers well inside its compute time.
     GROUP = max(1, min(args.e2e_group, layers))
-    n_groups = (layers + GROUP - 1) // GROUP
+    # the first upload and the last download are the two transfers nothing hides: one layer each
+    bounds = [0]
+    if layers > 2 and GROUP > 1:
+        bounds.append(1)
+        while bounds[-1] + GROUP < layers - 1:
+            bounds.append(bounds[-1] + GROUP)
+        if bounds[-1] < layers - 1:
+            bounds.append(layers - 1)
+        bounds.append(layers)
+    else:
+        while bounds[-1] < layers:
+            bounds.append(min(layers, bounds[-1] + GROUP))
+    n_groups = len(bounds) - 1
     e2e_qkv = torch.empty((2, GROUP, nq + 2 * nk), dtype=torch.float16, device=dev)
     e2e_q = [[e2e_qkv[s, j, :nq].view(B, hq * d) for j in range(GROUP)] for s in range(2)]
     e2e_k = [[e2e_qkv[s, j, nq:nq + nk].view(B, hkv * d) for j in range(GROUP)] for s in range(2)]
@@ -248,7 +260,7 @@ def run_ours(args, w):
         plan.update(kv_lens)
         for gi in range(n_groups):
             s = gi & 1
-            l0, l1 = gi * GROUP, min(layers, (gi + 1) * GROUP)
+            l0, l1 = bounds[gi], bounds[gi + 1]
             with torch.cuda.stream(copy_in):
                 copy_in.wait_event(ev_done[s])  # the launches that read this slot two groups ago
                 e2e_qkv[s, :l1 - l0].copy_(h_qkv[l0:l1], non_blocking=True)
