@@ -466,7 +466,12 @@ MF_API mf_status mf_paged_kv_append(MfContext *ctx, const MfPagedKv *cache, cons
  * weights_per_block == 0: weights row-major [N, k_dim]; 32: the reference's blocked layout, element
  * (r, k) at (k % 32) + 32 * (r + (k / 32) * N) (compound/stages/layout.rs:100).  k_dim must be a
  * multiple of 32, n_dim and n_kv multiples of 16.  Sums are f32 in a fixed order that does not depend
- * on m or on which entry point runs, so the three functions below produce the same bits. */
+ * on m or on which entry point runs, so the three functions below produce the same bits.
+ * The weights, gamma excepted, are treated as constants of the stream: with MF_OPTION_OVERLAP_LAUNCHES
+ * set the kernel is a programmatic dependent of the launch before it and requests its first weights
+ * before that launch has finished, so the preceding kernel in the stream must not be the one that
+ * writes them.  Input rows, gamma and biases are read, and everything is written, after the wait.
+ * Up to eight input rows share one pass over the weights; more rows repeat the pass per eight. */
 typedef struct MfFusedQkvArgs {
     const void *input;
     const void *w_q, *w_k, *w_v;
