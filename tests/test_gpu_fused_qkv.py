@@ -84,7 +84,9 @@ PROJ_SHAPES = [
     (1, 3072, 3072, 1024, True, False, True),   # Llama-3.2-3B layer
     (3, 3072, 3072, 1024, True, False, False),
     (5, 256, 64, 32, False, False, True),       # no norm, rows not a multiple of the rows per CTA
-    (9, 160, 48, 16, True, True, False),        # k blocks (5) not a multiple of the four k phases
+    (9, 160, 48, 16, True, True, False),        # k blocks (5) not a multiple of the eight warps
+    (8, 8192, 128, 32, True, True, True),       # staged rows above 48 KB of shared memory (opt-in size)
+    (8, 16384, 64, 16, True, False, False),     # rows per CTA cut to what fits: five, then three
 ]
 
 
@@ -101,7 +103,7 @@ def test_fused_qkv_against_oracle(mfk, foundry, shape):
 
 
 def test_fused_qkv_rows_per_cta_do_not_change_bits(mfk, foundry):
-    """Seven rows run as 4 + 3 rows per CTA; each row alone (one row per CTA) gives the same bits."""
+    """Seven rows share one pass over the weights; each row alone, and two of them together, give the same bits."""
     pj = Proj(m=7, k_dim=512, n_dim=256, n_kv=64, gamma=True, bias=True, blocked=True)
     all_rows = _run_plain(foundry, pj)
     x = dev(pj.x).reshape(7, 512)
