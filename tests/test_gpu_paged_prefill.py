@@ -26,6 +26,8 @@ CASES = [
     (8, 2, 128, 8, 130, 129),
     (16, 2, 128, 128, 1000, 148),
     (24, 8, 128, 64, 2048, 512),
+    (16, 2, 128, 32, 700, 200),
+    (14, 2, 64, 8, 200, 100),
 ]
 
 
