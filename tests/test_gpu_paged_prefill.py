@@ -63,15 +63,19 @@ def test_paged_chunked_prefill(mfk, foundry, case):
     gold = oracle.prefill_gold(q_ref, kc.ravel(), vc.ravel(), **args)
 
     dk, dv = dev(k_pool), dev(v_pool)
-    table = np.full((1, n_seq_pages), 0, np.uint32)
-    table[0] = pages
-    d_table, d_lens = dev_u32(table), dev_u32(np.array([L], np.uint32))  # the descriptor holds raw pointers: keep these alive
+    # the sequence is one of three in the batch; the other rows of the table point past the pool
+    seq = (cached + m) % 3
+    table = np.full((3, n_seq_pages), 0x7FFFFFF0, np.uint32)
+    table[seq] = pages
+    lens = np.ones(3, np.uint32)
+    lens[seq] = L
+    d_table, d_lens = dev_u32(table), dev_u32(lens)  # the descriptor holds raw pointers: keep these alive
     desc = mfk.paged_kv(dk, dv, d_table, d_lens, n_kv_heads=hkv, page_size=P, head_dim=d)
     q_rot = torch.full((hq, m, d), float("nan"), dtype=torch.float16, device="cuda")
-    foundry.paged_kv_append(desc, dev(q), dev(k), dev(v), q_rot, dev(cos), dev(sin), n_heads=hq, rope_mode=0, seq=0,
+    foundry.paged_kv_append(desc, dev(q), dev(k), dev(v), q_rot, dev(cos), dev(sin), n_heads=hq, rope_mode=0, seq=seq,
                             position_offset=cached, seq_len=m)
     out = torch.full((m, hq * d), float("nan"), dtype=torch.float16, device="cuda")
-    foundry.paged_prefill(desc, q_rot, out, seq=0, q_len=m, kv_len=L, query_offset=cached, n_heads=hq, scale=float(scale))
+    foundry.paged_prefill(desc, q_rot, out, seq=seq, q_len=m, kv_len=L, query_offset=cached, n_heads=hq, scale=float(scale))
     foundry.synchronize()
     assert np.array_equal(host(q_rot).ravel(), q_ref)
     for pool_dev, cache_ref in ((dk, kc), (dv, vc)):  # the chunk's rows landed in the right pages, bit-exact
@@ -86,7 +90,7 @@ def test_paged_chunked_prefill(mfk, foundry, case):
         for impl in (2, 1):
             foundry.set_option(3, impl)
             o = torch.full((m, hq * d), float("nan"), dtype=torch.float16, device="cuda")
-            foundry.paged_prefill(desc, q_rot, o, seq=0, q_len=m, kv_len=L, query_offset=cached, n_heads=hq,
+            foundry.paged_prefill(desc, q_rot, o, seq=seq, q_len=m, kv_len=L, query_offset=cached, n_heads=hq,
                                   scale=float(scale))
             foundry.synchronize()
             outs[impl] = host(o)
