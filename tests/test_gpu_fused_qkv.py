@@ -211,3 +211,32 @@ def test_fused_qkv_rejects_what_it_cannot_do(mfk, foundry):
             foundry.fused_qkv(bad)
         assert e.value.kind == kind, field
     foundry.synchronize()
+
+
+def test_projection_and_paged_append_more_rows_than_one_pass(mfk, foundry):
+    """Nineteen sequences: three passes of up to eight input rows, one new token per sequence."""
+    import torch
+
+    hq, hkv, d, P, k_dim = 14, 2, 64, 16, 896
+    cached = [3 + 7 * i for i in range(19)]
+    case = PagedCase(batch=len(cached), n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P, cached=cached, poison=False)
+    B = case.B
+    pj = Proj(m=B, k_dim=k_dim, n_dim=hq * d, n_kv=hkv * d, gamma=True, bias=True, blocked=True)
+    q_bits, k_bits, v_bits = _run_plain(foundry, pj)
+    cos, sin = dev(case.cos), dev(case.sin)
+    d_table, d_lens = dev_u32(case.page_table), dev_u32(case.kv_lens)
+    res = []
+    for fused in (False, True):
+        kp, vp = dev(case.k_pool), dev(case.v_pool)
+        desc = mfk.paged_kv(kp, vp, d_table, d_lens, n_kv_heads=hkv, page_size=P, head_dim=d)
+        q_rot = torch.full((B, hq * d), float("nan"), dtype=torch.float16, device="cuda")
+        if fused:
+            foundry.fused_qkv_paged_append(pj.args(foundry), desc, q_rot, cos, sin, n_heads=hq, rope_mode=1)
+        else:
+            foundry.paged_kv_append(desc, dev(q_bits.reshape(B, hq * d)), dev(k_bits.reshape(B, hkv * d)),
+                                    dev(v_bits.reshape(B, hkv * d)), q_rot, cos, sin, n_heads=hq, rope_mode=1)
+        foundry.synchronize()
+        res.append((host(q_rot), host(kp), host(vp)))
+    for a, b in zip(*res):
+        assert np.array_equal(a, b)
+    assert not np.array_equal(res[0][1], case.k_pool)  # rows were written
