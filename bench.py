@@ -765,6 +765,10 @@ def run_contiguous_decode(args, w):
         for i in range(layers):
             if qkv_args is not None:
                 f.fused_qkv_kv_prep(qkv_args[i], q_rot[i], kcs[i], vcs[i], cos, sin, p)
+            elif args.one_launch:
+                # KvPrepFused and FlashAttention of the layer in one launch
+                f.kv_prep_flash_decode(q[i], k[i], v[i], q_rot[i], kcs[i], vcs[i], cos, sin, out[i], p)
+                continue
             else:
                 f.kv_prep_fused(q[i], k[i], v[i], q_rot[i], kcs[i], vcs[i], cos, sin, p)
             f.flash_attention(q_rot[i], kcs[i], vcs[i], out[i], causal=True, query_offset=cached, n_heads=hq, head_dim=d,
@@ -846,6 +850,7 @@ def run_contiguous_decode(args, w):
         "config": {"workload": w["name"] + ("; with --projection the first launch of a layer is RMSNorm + fused QKV "
                                             "projection + RoPE + append (weights %.1f MB per layer)" % (weight_bytes / 1e6)
                                             if args.projection else "") +
+                               ("; --one-launch: the two ops of a layer fused into one launch" if args.one_launch else "") +
                                ("" if world == 1 else "; KV heads split over %d GPUs (%d per GPU), no exchange" % (world, hkv)),
                    "l2": l2_note,
                    "timing": "value / us_per_step = CUDA-graph replay of the step when capture works, else eager"},
@@ -943,6 +948,8 @@ def main():
                     help="long-context workloads: partials exchanged and merged inside the decode kernel (fused), "
                          "exchanged by the decode kernel and merged by a second one (push), or by ncclAllGather")
     ap.add_argument("--no-overlap", action="store_true", help="plain launches instead of programmatic dependent launch")
+    ap.add_argument("--one-launch", action="store_true",
+                    help="c1 / c2: KvPrepFused and FlashAttention of a layer in one launch (mf_kv_prep_flash_decode)")
     ap.add_argument("--projection", action="store_true",
                     help="c1 / c2: start each layer from the hidden state (RMSNorm + fused QKV projection + RoPE + append "
                          "in one launch) instead of from q, k, v")

@@ -456,6 +456,19 @@ MF_API mf_status mf_paged_kv_append(MfContext *ctx, const MfPagedKv *cache, cons
                                     uint32_t apply_rope, uint32_t seq, uint32_t position_offset,
                                     uint32_t seq_len);
 
+/* KvPrepFused and the decode route of FlashAttention in ONE launch, for one new token (seq_len = 1) on a
+ * compact contiguous cache: q is rotated on its way into the kernel (and stored to q_rot when q_rot is
+ * not NULL), the new key is rotated, the new K/V rows are written to cache row position_offset, and
+ * attention runs over rows [0, position_offset] -- the same bits in the caches and in q_rot as
+ * mf_kv_prep_fused, the same attention as mf_flash_attention after it.  An expanded cache
+ * ([n_heads, cap, D]) is answered with MF_ERR_OPERATION_NOT_SUPPORTED: use the two calls.  No
+ * counterpart in the reference, which launches the two steps one after the other
+ * (src/metals/kv_prep/step.rs:93-132, src/metals/sdpa/step.rs:160-503). */
+MF_API mf_status mf_kv_prep_flash_decode(MfContext *ctx, const MfTensor *q, const MfTensor *k, const MfTensor *v,
+                                         const MfTensor *q_rot, const MfTensor *k_cache,
+                                         const MfTensor *v_cache, const MfTensor *cos, const MfTensor *sin,
+                                         const MfTensor *output, const KvPrepFusedParamsResolved *params);
+
 /* ------------------------------------------- projection in front of the append --- */
 
 /* "FusedQkv" (src/metals/gemv/qkv_step.rs:14-37,59-101; qkv_project.metal:4-272), f16 weights

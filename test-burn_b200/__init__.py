@@ -182,6 +182,7 @@ _SIGNATURES = {
     "mf_paged_kv_append": (C.c_int32, [vp, C.POINTER(MfPagedKv), vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32,
                                        u32]),
     "mf_paged_gather": (C.c_int32, [vp, C.POINTER(MfPagedKv), u32, u32, u32, vp]),
+    "mf_kv_prep_flash_decode": (C.c_int32, [vp] + [C.POINTER(MfTensor)] * 9 + [C.POINTER(KvPrepFusedParamsResolved)]),
     "mf_fused_qkv": (C.c_int32, [vp, C.POINTER(MfFusedQkvArgs)]),
     "mf_fused_qkv_kv_prep": (C.c_int32, [vp, C.POINTER(MfFusedQkvArgs)] + [C.POINTER(MfTensor)] * 5 +
                              [C.POINTER(KvPrepFusedParamsResolved)]),
@@ -295,6 +296,11 @@ class Foundry:
         """foundry.run(&KvPrepFused{..}) (src/metals/kv_prep/mod.rs:157-182)."""
         ts = [tensor_arg(x) for x in (q, k, v, q_rot, k_cache, v_cache, cos, sin)]
         self.check(lib.mf_kv_prep_fused(self._h, *[C.byref(t) for t in ts], C.byref(params)))
+
+    def kv_prep_flash_decode(self, q, k, v, q_rot, k_cache, v_cache, cos, sin, output, params: KvPrepFusedParamsResolved):
+        """KvPrepFused and FlashAttention (decode route) in one launch; q_rot may be None."""
+        ts = [None if x is None else tensor_arg(x) for x in (q, k, v, q_rot, k_cache, v_cache, cos, sin, output)]
+        self.check(lib.mf_kv_prep_flash_decode(self._h, *[None if t is None else C.byref(t) for t in ts], C.byref(params)))
 
     def rope(self, x, out, cos, sin, params: RopeParamsResolved):
         ts = [tensor_arg(t) for t in (x, out, cos, sin)]

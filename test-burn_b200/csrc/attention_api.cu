@@ -46,9 +46,17 @@ uint64_t partial_slot_bytes(uint32_t group, uint32_t head_dim)
 }
 
 // Contiguous-cache decode through the shared kernel with an arithmetic plan.
+// The new token's rows for the form that appends inside the decode launch (one sequence).
+struct ContigAppend {
+    const void *k_new, *v_new;  // [Hkv * D] each, not rotated
+    void *q_rot;                // optional copy of the rotated q
+    uint32_t rope_mode, apply_rope;
+};
+
 mf_status decode_contiguous(MfContext *ctx, const void *q, const void *k, const void *v, void *output,
                             const MfFlashDecodeStrides *s, const SdpaParams *sp, uint32_t n_heads, uint32_t batch,
-                            uint32_t n_splits, const void *cos, const void *sin, const RopeParamsResolved *rope)
+                            uint32_t n_splits, const void *cos, const void *sin, const RopeParamsResolved *rope,
+                            const ContigAppend *app = nullptr)
 {
     if (!q || !k || !v || !output) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "FlashDecode: null tensor");
     if (!s || !sp) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "FlashDecode: params");
@@ -125,6 +133,22 @@ mf_status decode_contiguous(MfContext *ctx, const void *q, const void *k, const 
         p.rope_position = rope->position_offset;
         p.cos_t = static_cast<const __half *>(cos);
         p.sin_t = static_cast<const __half *>(sin);
+    }
+    if (app) {
+        // RoPE of q and of the new key at position kv_len - 1, the new K/V rows written to the cache and
+        // spliced into the last tile by the CTA that owns it: this launch is the only writer of the caches,
+        // so its producers may stream ahead of the previous launch's end.
+        p.append = 1;
+        p.k_new = static_cast<const __half *>(app->k_new);
+        p.v_new = static_cast<const __half *>(app->v_new);
+        p.knew_stride_b = cache_heads * D;
+        p.q_rot = static_cast<__half *>(app->q_rot);
+        p.rope = app->apply_rope;
+        p.rope_mode = app->rope_mode;
+        p.rope_position = sp->kv_len - 1;
+        p.cos_t = static_cast<const __half *>(cos);
+        p.sin_t = static_cast<const __half *>(sin);
+        p.early_stream = ctx->overlap_launches ? 1u : 0u;
     }
     // The tensor maps cover every row any (batch, head) can address.
     const uint64_t k_rows = (uint64_t)(batch - 1) * p.k_rows_b + (uint64_t)(cache_heads - 1) * p.k_rows_h + p.k_rows_h;
@@ -345,6 +369,65 @@ mf_status mf_run_flash_decode(MfContext *ctx, const MfTensor *q, const MfTensor 
                               uint32_t q_seq_len, uint32_t kv_head_major)
 {
     return run_flash_decode_impl(ctx, q, k, v, output, n_heads, head_dim, kv_seq_len, q_seq_len, kv_head_major, -1);
+}
+
+// KvPrepFused (src/metals/kv_prep/step.rs:93-132) and the decode route of FlashAttention
+// (src/metals/sdpa/step.rs:160-503) for ONE new token on a compact contiguous cache, in one launch.
+mf_status mf_kv_prep_flash_decode(MfContext *ctx, const MfTensor *q, const MfTensor *k, const MfTensor *v,
+                                  const MfTensor *q_rot, const MfTensor *k_cache, const MfTensor *v_cache,
+                                  const MfTensor *cos, const MfTensor *sin, const MfTensor *output,
+                                  const KvPrepFusedParamsResolved *pr)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!pr) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "KvPrepFused+FlashDecode: params");
+    mf_status st;
+    const MfTensor *ts[8] = {q, k, v, k_cache, v_cache, cos, sin, output};
+    const char *names[8] = {"q", "k", "v", "k_cache", "v_cache", "cos", "sin", "output"};
+    for (int i = 0; i < 8; ++i)
+        if ((st = need_tensor(ctx, ts[i], names[i])) != MF_OK) return st;
+    const uint32_t D = pr->head_dim;
+    if (pr->seq_len != 1)
+        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "KvPrepFused+FlashDecode: one new token per call, got %u", pr->seq_len);
+    if (D != 64 && D != 128)
+        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "Flash Decode only supports head_dim=64 or 128, got %u", D);
+    if (pr->n_kv_heads == 0 || pr->n_heads % pr->n_kv_heads != 0 || pr->group_size != pr->n_heads / pr->n_kv_heads ||
+        pr->d_model != pr->n_heads * D || pr->kv_dim != pr->n_kv_heads * D)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "KvPrepFused+FlashDecode: head geometry");
+    if (pr->position_offset >= pr->max_seq_len)
+        return fail(ctx, MF_ERR_INVALID_OPERATION, "KvPrepFused+FlashDecode: position %u outside the cache of %u rows",
+                    pr->position_offset, pr->max_seq_len);
+    if (pr->rope_mode > 1) return fail(ctx, MF_ERR_INVALID_OPERATION, "KvPrepFused+FlashDecode: rope_mode %u", pr->rope_mode);
+    if (k_cache->rank != 3 || v_cache->rank != 3 || k_cache->dims[1] != pr->max_seq_len || k_cache->dims[2] != D ||
+        v_cache->dims[0] != k_cache->dims[0] || v_cache->dims[1] != k_cache->dims[1] || v_cache->dims[2] != D)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "KvPrepFused+FlashDecode: caches must be rank-3 [heads, max_seq_len, head_dim]");
+    if (k_cache->dims[0] != pr->n_kv_heads)  // an expanded cache takes G writes per row: the two-call form does that
+        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "KvPrepFused+FlashDecode: compact cache only (%llu heads, %u kv heads)",
+                    (unsigned long long)k_cache->dims[0], pr->n_kv_heads);
+    const void *ptrs[9] = {tensor_ptr(q), tensor_ptr(k), tensor_ptr(v), tensor_ptr(k_cache), tensor_ptr(v_cache),
+                           tensor_ptr(cos), tensor_ptr(sin), tensor_ptr(output), q_rot ? tensor_ptr(q_rot) : nullptr};
+    for (const void *ptr : ptrs)
+        if (reinterpret_cast<uintptr_t>(ptr) & 15u)
+            return fail(ctx, MF_ERR_INVALID_SHAPE, "KvPrepFused+FlashDecode: 16-byte alignment");
+    const uint32_t cap = pr->max_seq_len, kv_len = pr->position_offset + 1;
+    MfFlashDecodeStrides s{};
+    s.q_stride_b = pr->n_heads * D;
+    s.q_stride_h = D;
+    s.k_stride_b = pr->n_kv_heads * cap * D;
+    s.k_stride_h = cap * D;
+    s.v_stride_b = s.k_stride_b;
+    s.v_stride_h = s.k_stride_h;
+    s.out_stride_b = pr->n_heads * D;
+    s.out_stride_h = D;
+    SdpaParams sp{kv_len, D, 1.0f / sqrtf((float)D), D, D};
+    ContigAppend app{};
+    app.k_new = ptrs[1];
+    app.v_new = ptrs[2];
+    app.q_rot = const_cast<void *>(ptrs[8]);
+    app.rope_mode = pr->rope_mode;
+    // SmolLM3-style skip: no RoPE on every N-th layer (kv_prep_fused.metal:56-57)
+    app.apply_rope = pr->no_rope_layer_step == 0 || ((pr->layer_idx + 1u) % pr->no_rope_layer_step) != 0u;
+    return decode_contiguous(ctx, ptrs[0], ptrs[3], ptrs[4], const_cast<void *>(ptrs[7]), &s, &sp, pr->n_heads, 1, 0,
+                             ptrs[5], ptrs[6], nullptr, &app);
 }
 
 // SdpaReferenceStep (src/metals/sdpa/step.rs:89-158, 558-779): attention for the cases the flash routes
