@@ -237,7 +237,10 @@ MF_API uint64_t mf_launch_count(const MfContext *ctx);
  * append+decode launch then starts streaming K/V pages before the previous kernel in the
  * stream has finished; the caller promises that this previous kernel does not write the
  * pools, page table or lengths the launch reads (consecutive layers of a decode step never
- * do).  Everything else a launch reads or writes still waits for the previous kernel.
+ * do).  The library itself keeps track of the caches its last three appending decode launches
+ * wrote and does not stream early from one of those (a one-layer model, or two calls in a row on
+ * one cache); kernels of other origins are the caller's to vouch for.  Everything else a launch
+ * reads or writes still waits for the previous kernel.
  * Value 2 extends the early streaming to launches WITHOUT a fused append (the shards of a
  * sequence-sharded step that do not own the tail page): the caller then also promises that no
  * separate append kernel precedes the launch in the stream.

@@ -148,7 +148,10 @@ mf_status decode_contiguous(MfContext *ctx, const void *q, const void *k, const 
         p.rope_position = sp->kv_len - 1;
         p.cos_t = static_cast<const __half *>(cos);
         p.sin_t = static_cast<const __half *>(sin);
-        p.early_stream = ctx->overlap_launches ? 1u : 0u;
+        // ... unless one of the last few launches appended to this same cache (a one-layer model, two
+        // calls in a row on one cache): its new row may not have landed yet
+        const bool fresh = ctx->may_stream_early(k, true);
+        p.early_stream = (ctx->overlap_launches && fresh) ? 1u : 0u;
     }
     // The tensor maps cover every row any (batch, head) can address.
     const uint64_t k_rows = (uint64_t)(batch - 1) * p.k_rows_b + (uint64_t)(cache_heads - 1) * p.k_rows_h + p.k_rows_h;
@@ -690,7 +693,10 @@ static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, con
     // append itself: then no kernel right before it can have written the pages it reads.
     // Streaming K/V ahead of the previous kernel's end is safe when nothing earlier in the stream writes
     // these pools: with the fused append this call is the only writer; without it the caller says so (2).
-    p.early_stream = ((ctx->overlap_launches && a->append) || ctx->overlap_launches == 2) ? 1u : 0u;
+    // Not when one of the last few launches appended to these same pools (a one-layer model, two calls in a
+    // row on one cache): its new rows may not have landed yet.
+    const bool fresh = ctx->may_stream_early(c->k_pool, a->append != 0);
+    p.early_stream = (((ctx->overlap_launches && a->append) || ctx->overlap_launches == 2) && fresh) ? 1u : 0u;
     if (px) {
         if (px->world == 0 || px->world > 8 || px->rank >= px->world)
             return fail(ctx, MF_ERR_INVALID_OPERATION, "peer exchange: rank %u of %u", px->rank, px->world);

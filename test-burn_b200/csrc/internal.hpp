@@ -117,6 +117,22 @@ struct MfContext {
     std::unordered_map<mf::TensorMapKey, CUtensorMap, mf::TensorMapKeyHash> tmaps;
     void *encode_fn = nullptr;
     uint32_t overlap_launches = 0;  // MF_OPTION_OVERLAP_LAUNCHES
+    // Caches (K base pointers) that the last few decode launches appended to.  A launch that streams
+    // K/V ahead of the end of the launches before it must not read a row one of them is still writing.
+    static constexpr int kRecentAppends = 3;
+    const void *recent_append[kRecentAppends] = {};
+    uint32_t recent_append_pos = 0;
+    // True when `cache` is not among them (early streaming is safe); an appending launch is then noted.
+    bool may_stream_early(const void *cache, bool appends)
+    {
+        bool fresh = true;
+        for (const void *r : recent_append) fresh = fresh && r != cache;
+        if (appends) {
+            recent_append[recent_append_pos] = cache;
+            recent_append_pos = (recent_append_pos + 1) % kRecentAppends;
+        }
+        return fresh;
+    }
     uint32_t decode_stages = 0;     // MF_OPTION_DECODE_STAGES (0 = default)
     uint32_t prefill_impl = 0;      // MF_OPTION_PREFILL_IMPL: 0 auto, 1 mma.sync, 2 tcgen05 only
 };

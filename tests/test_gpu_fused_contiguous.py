@@ -96,3 +96,34 @@ def test_one_launch_refuses_what_the_two_calls_are_for(mfk, foundry):
                                      dev(compact.v_cache), cos, sin, out, p)
     assert e.value.kind == "OperationNotSupported"
     foundry.synchronize()
+
+
+@pytest.mark.parametrize("overlap", [0, 1])
+def test_steps_in_a_row_on_one_cache(mfk, foundry, overlap):
+    """A one-layer model: every launch appends to the cache the next one reads, positions advancing.
+    With overlapped launches the library must not let a launch stream the cache ahead of the row the
+    launch before it is still writing."""
+    import torch
+
+    hq, hkv, d, cap, start, steps = 16, 2, 128, 512, 300, 48
+    case = ContigCase(n_heads=hq, n_kv_heads=hkv, head_dim=d, cached=start, m=steps, capacity=cap, theta=1e4, rope_mode=0)
+    cos, sin = dev(case.cos), dev(case.sin)
+    kc, vc = dev(case.k_cache), dev(case.v_cache)
+    q_all, k_all, v_all = dev(case.q), dev(case.k), dev(case.v)  # [steps, ...]: row t is step t's token
+    outs = torch.full((steps, hq * d), float("nan"), dtype=torch.float16, device="cuda")
+    foundry.set_option(mfk.OPTION_OVERLAP_LAUNCHES, overlap)
+    for t in range(steps):
+        p = mfk.KvPrepFusedParamsResolved(hq * d, hkv * d, d, hq, hkv, hq // hkv, 1, start + t, cap, hq * d, 0, 0, 0)
+        foundry.kv_prep_flash_decode(q_all[t:t + 1], k_all[t:t + 1], v_all[t:t + 1], None, kc, vc, cos, sin, outs[t:t + 1], p)
+    foundry.synchronize()
+    foundry.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 0)
+    # the oracle: all rows appended at once, then each step attends over its prefix
+    q_ref, k_ref, v_ref = case.oracle_append()
+    assert np.array_equal(host(kc), k_ref) and np.array_equal(host(vc), v_ref)
+    q_rows = q_ref.reshape(hq, steps, d)
+    got = host(outs)
+    for t in range(steps):
+        q_t = np.ascontiguousarray(q_rows[:, t]).ravel()
+        want = oracle.decode_online(q_t, k_ref, v_ref, n_heads=hq, cache_heads=hkv, head_dim=d, capacity=cap,
+                                    kv_len=start + t + 1, scale=case.scale)
+        assert max_abs(got[t], want) <= TOL, t
