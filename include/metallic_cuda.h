@@ -380,19 +380,28 @@ MF_API mf_status mf_flash_decode(MfContext *ctx, const void *q, const void *k, c
  * the process exits).  Meant for hosts whose own pool owns the whole GPU and forbids
  * plug-ins to allocate, for decode loops that cannot take the device-wide
  * synchronisation an allocation implies, and for sandboxes that deny the call.
- *  - Limit: batch x kv heads <= 4096 and (batch x kv heads + SM count) partial slots of
- *    8*ceil(G/8)*(head_dim+2)*4 bytes within the 4 MiB; larger requests return
+ *  - Limit: batch x kv heads <= 4096 and (batch x kv heads + 2 x SM count) partial slots
+ *    of 8*ceil(G/8)*(head_dim+2)*4 bytes within the 4 MiB; larger requests return
  *    MF_ERR_OUT_OF_MEMORY with a message and launch nothing.
  *  - The first call on a device looks the array's device address up and configures
  *    the kernels; make that first call before any stream capture begins.
  *  - All calls on a GPU share the array: calls that overlap on the GPU (other streams
  *    or threads) race; each call clears the status word and tickets on its stream.
  *  - err / err_len: optional host buffer for a message; a timed-out device-side wait
- *    is recorded in word 0 of the array, which this entry point does not read back. */
+ *    is recorded in word 0 of the array, which this entry point does not read back:
+ *    mf_static_scratch_status does, and the next call clears it.
+ *  - Calls on one GPU must also be serialised by the host for the first-call set-up. */
 MF_API mf_status mf_flash_decode_static_scratch(void *cuda_stream, const void *q, const void *k, const void *v,
                                                 void *output, const MfFlashDecodeStrides *strides,
                                                 const SdpaParams *params, uint32_t n_heads, uint32_t batch,
                                                 char *err, uint32_t err_len);
+
+/* Status word of the built-in array (no counterpart in the reference; allocates nothing):
+ * enqueues one 4-byte copy on `cuda_stream` into *host_status (pinned memory keeps it
+ * asynchronous).  Once the stream has drained, non-zero means that a device-side wait of
+ * the last mf_flash_decode_static_scratch call on the current GPU ran out and that its
+ * output must not be used. */
+MF_API mf_status mf_static_scratch_status(void *cuda_stream, uint32_t *host_status);
 
 /* RopeFlashDecodeStep (src/metals/flashattention/step.rs:54-306): NeoX RoPE of q
  * at rope->position_offset fused in front of decode.  q is un-roped [batch, Hq, D]. */

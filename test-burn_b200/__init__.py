@@ -166,6 +166,7 @@ _SIGNATURES = {
                                     u32, u32, u32]),
     "mf_flash_decode_static_scratch": (C.c_int32, [vp, vp, vp, vp, vp, C.POINTER(MfFlashDecodeStrides),
                                                    C.POINTER(SdpaParams), u32, u32, C.c_char_p, u32]),
+    "mf_static_scratch_status": (C.c_int32, [vp, C.POINTER(u32)]),
     "mf_rope_flash_decode": (C.c_int32, [vp, vp, vp, vp, vp, vp, vp, C.POINTER(RopeParamsResolved),
                                          C.POINTER(SdpaParams), C.POINTER(MfFlashDecodeStrides), u32, u32]),
     "mf_flash_prefill": (C.c_int32, [vp, vp, vp, vp, vp, C.POINTER(SdpaPrefillSplitKParams)]),

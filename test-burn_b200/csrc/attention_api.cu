@@ -148,10 +148,9 @@ mf_status decode_contiguous(MfContext *ctx, const void *q, const void *k, const 
         p.rope_position = sp->kv_len - 1;
         p.cos_t = static_cast<const __half *>(cos);
         p.sin_t = static_cast<const __half *>(sin);
-        // ... unless one of the last few launches appended to this same cache (a one-layer model, two
-        // calls in a row on one cache): its new row may not have landed yet
-        const bool fresh = ctx->may_stream_early(k, true);
-        p.early_stream = (ctx->overlap_launches && fresh) ? 1u : 0u;
+        // ... unless the launch directly in front of this one appended to this same cache (a one-layer
+        // model, two calls in a row on one cache): its new row may not have landed yet
+        p.early_stream = (ctx->overlap_launches && ctx->may_stream_early(k, v)) ? 1u : 0u;
     }
     // The tensor maps cover every row any (batch, head) can address.
     const uint64_t k_rows = (uint64_t)(batch - 1) * p.k_rows_b + (uint64_t)(cache_heads - 1) * p.k_rows_h + p.k_rows_h;
@@ -167,7 +166,9 @@ mf_status decode_contiguous(MfContext *ctx, const void *q, const void *k, const 
         if ((st = get_tensor_map(ctx, k, k_rows, D, kTileKeys, 64, &tm_k)) != MF_OK) return st;
         if ((st = get_tensor_map(ctx, v, v_rows, D, kTileKeys, 64, &tm_v)) != MF_OK) return st;
     }
-    return launch_decode(ctx, tm_k, tm_v, p, D, n_ctas);
+    st = launch_decode(ctx, tm_k, tm_v, p, D, n_ctas);
+    if (st == MF_OK && app) ctx->note_append(k, v);
+    return st;
 }
 
 struct QLayout {
@@ -679,6 +680,7 @@ static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, con
     p.group = a->n_heads / c->n_kv_heads;
     p.page_size = P;
     p.pt_stride = c->page_table_stride;
+    p.n_pages = c->n_pages;
     p.batch = c->batch;
     p.rope = a->rope;
     p.rope_mode = a->rope_mode;
@@ -689,14 +691,12 @@ static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, con
     p.out_stride_h = D;
     p.knew_stride_b = c->n_kv_heads * D;
     p.scale_log2 = a->scale * 1.4426950408889634f;
-    // With overlapped launches the tile stream may start early only when this launch does the
-    // append itself: then no kernel right before it can have written the pages it reads.
-    // Streaming K/V ahead of the previous kernel's end is safe when nothing earlier in the stream writes
-    // these pools: with the fused append this call is the only writer; without it the caller says so (2).
-    // Not when one of the last few launches appended to these same pools (a one-layer model, two calls in a
-    // row on one cache): its new rows may not have landed yet.
-    const bool fresh = ctx->may_stream_early(c->k_pool, a->append != 0);
-    p.early_stream = (((ctx->overlap_launches && a->append) || ctx->overlap_launches == 2) && fresh) ? 1u : 0u;
+    // Streaming K/V ahead of the previous kernel's end is safe when nothing in flight writes these pools.
+    // With the fused append this call is their only writer in this step; without it the caller says so
+    // (option value 2).  Not when the launch directly in front appended to these same pools (a one-layer
+    // model, two calls in a row on one cache): its new rows may not have landed yet.
+    p.early_stream = (((ctx->overlap_launches && a->append) || ctx->overlap_launches == 2) &&
+                      ctx->may_stream_early(c->k_pool, c->v_pool)) ? 1u : 0u;
     if (px) {
         if (px->world == 0 || px->world > 8 || px->rank >= px->world)
             return fail(ctx, MF_ERR_INVALID_OPERATION, "peer exchange: rank %u of %u", px->rank, px->world);
@@ -734,7 +734,9 @@ static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, con
         if ((st = get_tensor_map(ctx, c->k_pool, rows, D, box_rows, 64, &tm_k)) != MF_OK) return st;
         if ((st = get_tensor_map(ctx, c->v_pool, rows, D, box_rows, 64, &tm_v)) != MF_OK) return st;
     }
-    return launch_decode(ctx, tm_k, tm_v, p, D, pl->n_ctas);
+    st = launch_decode(ctx, tm_k, tm_v, p, D, pl->n_ctas);
+    if (st == MF_OK && a->append) ctx->note_append(c->k_pool, c->v_pool);
+    return st;
 }
 
 mf_status mf_paged_decode(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv *cache, const MfPagedDecodeArgs *args)

@@ -249,8 +249,13 @@ mf_status mf_synchronize(MfContext *ctx)
     if (st != MF_OK) return st;
     if (flag) {
         cudaMemset(ctx->d_status, 0, 4);
-        if (ctx->scratch) cudaMemset(ctx->scratch, 0, kCounterRegionBytes);
-        return fail(ctx, MF_ERR_TIMEOUT, "a device-side barrier wait ran out (status 0x%x)", flag);
+        if (flag & ~kStatusBadPage) {
+            if (ctx->scratch) cudaMemset(ctx->scratch, 0, kCounterRegionBytes);
+            return fail(ctx, MF_ERR_TIMEOUT, "a device-side barrier wait ran out (status 0x%x)", flag);
+        }
+        return fail(ctx, MF_ERR_INVALID_OPERATION,
+                    "a cache access was skipped: a page id outside the pool, or a position outside the page table, "
+                    "in the caller's device-side table or lengths (status 0x%x)", flag);
     }
     return MF_OK;
 }

@@ -276,9 +276,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     const uint32_t boxes_per_tile = kTileKeys / rows_per_box;
     const uint32_t rpb_log2 = 31 - __clz(rows_per_box);
 
-    // Let the next launch in the stream be scheduled onto SMs as this grid drains.
-    grid_launch_dependents();
-
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------ producer ---
         if (lane == 0) {
@@ -299,7 +296,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                 const uint32_t tok = tile * kTileKeys + lane * rows_per_box;
                 if (lane >= boxes_per_tile) return false;
                 if (p.page_table) {
-                    if (tok >= L) return false;
+                    // rows past the sequence, or past the page table when the device-side length is larger
+                    // than the table allows (the consumers report that), are not fetched
+                    if (tok >= L || tok / p.page_size >= p.pt_stride) return false;
                     const uint32_t page = __ldg(p.page_table + (size_t)it.seq * p.pt_stride + tok / p.page_size);
                     const uint32_t row = (page * p.n_kv_heads + it.kvh) * p.page_size + tok % p.page_size;
                     rk = rv = static_cast<int32_t>(row);
@@ -362,9 +361,13 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
     // ---------------------------------------------------------------- consumers ---
     // q, the new k/v, the partial slots and tickets may all have been written by the previous launch.
-    DEC_STAMP(0)
     grid_dependency_wait();
-    DEC_STAMP(1)
+    // Only now may the next launch of the stream be scheduled (it sets up, and its producer may stream its
+    // own K/V, while this grid works).  Releasing it AFTER the wait is what bounds the overlap: the launch
+    // behind this one cannot start before every CTA here has seen the launch in front of this one complete,
+    // so never more than two launches of a stream are in flight, and the only launch whose writes an early
+    // K/V stream can race with is the one directly in front of it.
+    grid_launch_dependents();
     float *comb = reinterpret_cast<float *>(smem + S::kOffComb);
     __half *q_s = reinterpret_cast<__half *>(smem + S::kOffQ);
     float *ml_s = reinterpret_cast<float *>(smem + S::kOffMl);
@@ -379,7 +382,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         const uint32_t L = kv_len_of(p, it.seq);
         const uint32_t n_tiles = (L + kTileKeys - 1) / kTileKeys;
         const uint32_t pos = p.rope_positions ? p.rope_positions[it.seq]
-                                              : (p.kv_lens ? L - 1 : p.rope_position);
+                                              : (p.kv_lens ? (L ? L - 1 : 0) : p.rope_position);
         const __half *cos_row = p.cos_t + (size_t)pos * half_d;
         const __half *sin_row = p.sin_t + (size_t)pos * half_d;
 
@@ -457,10 +460,23 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                 // this step (and store it to the cache), then clear V rows past L so
                 // that stale or never-written rows cannot leak NaNs through 0 * NaN.
                 const uint32_t r_new = (L - 1) - key0;
-                if (p.append) {
+                // The page id of the new row comes from the caller's device-side table: one that is not a
+                // page of this pool (or a length the table has no entry for) skips the store and the splice
+                // and raises the status bit; the output of that sequence is then not meaningful.
+                bool store_ok = true;
+                uint32_t new_page = 0;
+                if (p.append && p.page_table) {
+                    store_ok = (L - 1) / p.page_size < p.pt_stride;
+                    if (store_ok) {
+                        new_page = p.page_table[(size_t)it.seq * p.pt_stride + (L - 1) / p.page_size];
+                        store_ok = new_page < p.n_pages;
+                    }
+                    if (!store_ok && tid == 0) atomicOr(p.status, kStatusBadPage);
+                }
+                if (p.append && store_ok) {
                     size_t krow, vrow;
                     if (p.page_table) {
-                        const uint32_t page = p.page_table[(size_t)it.seq * p.pt_stride + (L - 1) / p.page_size];
+                        const uint32_t page = new_page;
                         krow = vrow = ((size_t)page * p.n_kv_heads + it.kvh) * p.page_size + (L - 1) % p.page_size;
                     } else {
                         krow = (size_t)it.seq * p.k_rows_b + (size_t)it.kvh * p.k_rows_h + (L - 1);
@@ -1163,7 +1179,8 @@ extern "C" mf_status mf_flash_decode_static_scratch(void *cuda_stream, const voi
     if ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u)
         return static_fail(err, err_len, MF_ERR_INVALID_SHAPE, "K/V base pointers must be 16-byte aligned");
 
-    // Same span rule as mf_flash_decode with n_splits = 0, so both produce the same bits.
+    // Same span rule as mf_flash_decode with n_splits = 0 on a context with default options, so both
+    // produce the same bits (a context whose MF_OPTION_DECODE_STAGES selects another variant cuts differently).
     const uint32_t T = (sp->kv_len + kTileKeys - 1) / kTileKeys;
     const uint64_t U = (uint64_t)batch * cache_heads;
     const uint64_t total = U * T;
@@ -1226,4 +1243,22 @@ extern "C" mf_status mf_flash_decode_static_scratch(void *cuda_stream, const voi
         e = nt == 1 ? static_launch<64, 1, 6, 2>(tm_k, tm_v, p, n_ctas, stream) : static_launch<64, 2, 8, 1>(tm_k, tm_v, p, n_ctas, stream);
     if (e != cudaSuccess) return static_fail(err, err_len, MF_ERR_CUDA, "decode launch failed (%llu)", (unsigned long long)e);
     return MF_OK;
+}
+
+// Reads the status word of the built-in array without allocating: one 4-byte asynchronous copy on the
+// caller's stream into the caller's (preferably pinned) host word.  Non-zero after the stream has
+// drained means a device-side wait of the last mf_flash_decode_static_scratch call on this GPU ran
+// out and its output is not valid.
+extern "C" mf_status mf_static_scratch_status(void *cuda_stream, uint32_t *host_status)
+{
+    using namespace mf;
+    if (!host_status) return MF_ERR_INPUT_NOT_FOUND;
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return MF_ERR_CUDA;
+    if (!g_static_state[device].ready) {
+        const mf_status st = static_setup(device, nullptr, 0);
+        if (st != MF_OK) return st;
+    }
+    return cudaMemcpyAsync(host_status, g_static_state[device].scratch, 4, cudaMemcpyDeviceToHost,
+                           static_cast<cudaStream_t>(cuda_stream)) == cudaSuccess ? MF_OK : MF_ERR_CUDA;
 }

@@ -17,6 +17,10 @@ namespace mf {
 constexpr uint32_t kTileKeys = 64;          // keys per pipeline stage
 constexpr uint32_t kCounterRegionBytes = 64 * 1024;  // head of a scratch arena: unit counters
 constexpr uint32_t kMaxUniformUnits = kCounterRegionBytes / 4;
+// Bit of the device status word set when a kernel skipped a cache access because a page id taken
+// from the caller's device-side table lies outside the pool, or a position outside the table
+// (the lower bits record barrier waits that ran out).
+constexpr uint32_t kStatusBadPage = 4096u;
 
 // One span of KV tiles of one (sequence, kv head) unit, processed by one CTA.
 struct WorkItem {
@@ -53,6 +57,7 @@ struct DecodeParams {
     float *out_l;
     uint32_t *status;
     uint32_t n_heads, n_kv_heads, group, page_size, pt_stride, batch;
+    uint32_t n_pages;        // paged: pages in the pool (page ids are checked against it before a store)
     uint32_t k_rows_b, k_rows_h, v_rows_b, v_rows_h;  // contiguous: row strides
     uint32_t uniform_kv_len, uniform_tiles, uniform_span, uniform_total;
     uint32_t uniform_parts;  // > 0: every unit is cut into this many ranges of uniform_span tiles, one CTA each
@@ -117,21 +122,28 @@ struct MfContext {
     std::unordered_map<mf::TensorMapKey, CUtensorMap, mf::TensorMapKeyHash> tmaps;
     void *encode_fn = nullptr;
     uint32_t overlap_launches = 0;  // MF_OPTION_OVERLAP_LAUNCHES
-    // Caches (K base pointers) that the last few decode launches appended to.  A launch that streams
-    // K/V ahead of the end of the launches before it must not read a row one of them is still writing.
-    static constexpr int kRecentAppends = 3;
-    const void *recent_append[kRecentAppends] = {};
-    uint32_t recent_append_pos = 0;
-    // True when `cache` is not among them (early streaming is safe); an appending launch is then noted.
-    bool may_stream_early(const void *cache, bool appends)
+    // Early K/V streaming under programmatic dependent launches.  Every kernel of this library that
+    // releases its dependents before it ends (decode_kernel, fused_qkv_kernel, merge_pushed_kernel) does so
+    // only after its own dependency wait has returned, and that wait returns only when the launch in front
+    // has completed (which, by the same rule, had waited for the one in front of it).  So when a launch
+    // starts, every launch but the one directly in front of it has completed: the caches written by that
+    // one launch are the only ones a producer must not read before its own wait.  `launches` counts every
+    // launch made through the context; an appending decode launch records the caches it writes together
+    // with the count after it, and the next launch may stream a cache early unless it is that cache and no
+    // other launch of this context has come between.  (A launch the count misses only makes the answer
+    // "wait", the safe one.)
+    const void *appended_k = nullptr, *appended_v = nullptr;
+    uint64_t appended_at = ~0ull;
+    bool may_stream_early(const void *k_cache, const void *v_cache) const
     {
-        bool fresh = true;
-        for (const void *r : recent_append) fresh = fresh && r != cache;
-        if (appends) {
-            recent_append[recent_append_pos] = cache;
-            recent_append_pos = (recent_append_pos + 1) % kRecentAppends;
-        }
-        return fresh;
+        if (appended_at != launches) return true;
+        return k_cache != appended_k && k_cache != appended_v && v_cache != appended_k && v_cache != appended_v;
+    }
+    void note_append(const void *k_cache, const void *v_cache)
+    {
+        appended_k = k_cache;
+        appended_v = v_cache;
+        appended_at = launches;
     }
     uint32_t decode_stages = 0;     // MF_OPTION_DECODE_STAGES (0 = default)
     uint32_t prefill_impl = 0;      // MF_OPTION_PREFILL_IMPL: 0 auto, 1 mma.sync, 2 tcgen05 only

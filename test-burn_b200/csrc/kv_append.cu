@@ -89,6 +89,8 @@ struct AppendParams {
     uint32_t max_seq_len;        // contiguous: cache capacity
     uint32_t cache_repeat;       // contiguous: 1 compact, G expanded
     uint32_t page_size, pt_stride, seq;  // paged
+    uint32_t n_pages;            // paged: pages in the pool
+    uint32_t *status;            // device status word (kStatusBadPage when a store was skipped)
     uint32_t rope_mode, apply_rope;
     uint32_t q_head_major;       // 1: q_rot is [Hq, M, D] (KvPrepFused); 0: [M, Hq*D]
 };
@@ -102,10 +104,22 @@ __device__ __forceinline__ void rope_and_store(const AppendParams &p, uint32_t s
     uint32_t pos, b = 0;
     if (p.kv_lens && p.seq == 0xFFFFFFFFu) {
         b = s;  // one token per sequence
-        pos = p.kv_lens[b] - 1;
+        const uint32_t len = p.kv_lens[b];
+        if (len == 0) {  // nothing to append for an empty sequence; the table has no row for it
+            atomicOr(p.status, kStatusBadPage);
+            return;
+        }
+        pos = len - 1;
     } else {
         b = p.page_table ? p.seq : 0;
         pos = p.position_offset + s;
+    }
+    // The table and the lengths are the caller's device data: a position past the table or a page id
+    // past the pool skips the access and raises the status bit instead of leaving the pool (the
+    // reference's kernels return silently on a broken contract, flash_decode.metal:165-170).
+    if (p.page_table && pos / p.page_size >= p.pt_stride) {
+        atomicOr(p.status, kStatusBadPage);
+        return;
     }
     const bool is_v = slot >= p.n_heads + p.n_kv_heads;
     if (p.apply_rope && !is_v) {
@@ -125,6 +139,10 @@ __device__ __forceinline__ void rope_and_store(const AppendParams &p, uint32_t s
     __half *cache = is_v ? p.v_cache : p.k_cache;
     if (p.page_table) {
         const uint32_t page = p.page_table[(size_t)b * p.pt_stride + pos / p.page_size];
+        if (page >= p.n_pages) {
+            atomicOr(p.status, kStatusBadPage);
+            return;
+        }
         __half *dst = cache + (((size_t)page * p.n_kv_heads + kvh) * p.page_size + pos % p.page_size) * D;
         *reinterpret_cast<uint4 *>(dst + 8 * j) = a.u;
         *reinterpret_cast<uint4 *>(dst + 8 * j + D / 2) = c.u;
@@ -279,7 +297,6 @@ __global__ void __launch_bounds__(256, 2) fused_qkv_kernel(const QkvParams qp, c
     };
 
     QKV_STAMP(0)
-    grid_launch_dependents();
     // The weights are constants: the first 64 KB of them are requested before the grid waits for the
     // kernel in front of it (under a programmatic dependent launch they travel during its tail) and
     // keep arriving while the input rows are staged and normalised.
@@ -289,6 +306,9 @@ __global__ void __launch_bounds__(256, 2) fused_qkv_kernel(const QkvParams qp, c
     fetch(cur, sd, 0);
     fetch(nxt, sd, 1);
     grid_dependency_wait();  // from here on: reads of what that kernel may have produced, and writes
+    // The next launch of the stream is released only after this wait, so that at most two launches
+    // are ever in flight (the bound the decode kernel's early K/V stream relies on).
+    grid_launch_dependents();
     const uint32_t vecs = K / 8;
     __half *gs = xs + (size_t)qp.rows_per_cta * xstride;  // gamma, staged once
     for (uint32_t b = 0; b < rows; ++b)
@@ -451,7 +471,8 @@ cache_write_kernel(const __half *in, __half *cache, uint32_t n_kv_heads, uint32_
 // (growth: the head stride changes with the capacity, src/model/executor.rs:2493-2504).
 __global__ void __launch_bounds__(256)
 cache_read_kernel(const __half *cache, __half *out, uint32_t heads, uint32_t head_dim, uint32_t len,
-                  uint32_t max_seq_len, const uint32_t *page_table_row, uint32_t page_size, uint32_t out_rows)
+                  uint32_t max_seq_len, const uint32_t *page_table_row, uint32_t page_size, uint32_t out_rows,
+                  uint32_t n_pages = 0, uint32_t *status = nullptr)
 {
     const uint32_t cpr = head_dim / 8;
     const uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -462,6 +483,11 @@ cache_read_kernel(const __half *cache, __half *out, uint32_t heads, uint32_t hea
     const __half *src;
     if (page_table_row) {
         const uint32_t page = page_table_row[t / page_size];
+        if (page >= n_pages) {  // not a page of this pool: the row reads as zero, the status word says why
+            atomicOr(status, kStatusBadPage);
+            *reinterpret_cast<uint4 *>(out + ((size_t)h * out_rows + t) * head_dim + 8 * j) = make_uint4(0, 0, 0, 0);
+            return;
+        }
         src = cache + (((size_t)page * heads + h) * page_size + t % page_size) * head_dim;
     } else {
         src = cache + ((size_t)h * max_seq_len + t) * head_dim;
@@ -474,7 +500,8 @@ cache_read_kernel(const __half *cache, __half *out, uint32_t heads, uint32_t hea
 // contiguous cache into the paged pool; the inverse of the paged read above).
 __global__ void __launch_bounds__(256)
 cache_to_pages_kernel(const __half *cache, __half *pool, uint32_t heads, uint32_t head_dim, uint32_t len,
-                      uint32_t max_seq_len, const uint32_t *page_table_row, uint32_t page_size)
+                      uint32_t max_seq_len, const uint32_t *page_table_row, uint32_t page_size, uint32_t n_pages,
+                      uint32_t *status)
 {
     const uint32_t cpr = head_dim / 8;
     const uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -483,6 +510,10 @@ cache_to_pages_kernel(const __half *cache, __half *pool, uint32_t heads, uint32_
     const uint32_t t = (gid / cpr) % len;
     const uint32_t h = gid / ((uint64_t)cpr * len);
     const uint32_t page = page_table_row[t / page_size];
+    if (page >= n_pages) {
+        atomicOr(status, kStatusBadPage);
+        return;
+    }
     __half *dst = pool + (((size_t)page * heads + h) * page_size + t % page_size) * head_dim;
     *reinterpret_cast<uint4 *>(dst + 8 * j) =
         *reinterpret_cast<const uint4 *>(cache + ((size_t)h * max_seq_len + t) * head_dim + 8 * j);
@@ -523,7 +554,7 @@ repeat_kv_heads_kernel(const __half *__restrict__ in, __half *__restrict__ out, 
 // Whole pages of both pools, dst_ids[i] <- src_ids[i]; one thread per 16 bytes.
 __global__ void __launch_bounds__(256)
 copy_pages_kernel(uint4 *k_pool, uint4 *v_pool, const uint32_t *__restrict__ src_ids, const uint32_t *__restrict__ dst_ids,
-                  uint32_t n, uint64_t chunks_per_page)
+                  uint32_t n, uint64_t chunks_per_page, uint32_t n_pages, uint32_t *status)
 {
     const uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (gid >= (uint64_t)n * chunks_per_page * 2) return;
@@ -531,7 +562,12 @@ copy_pages_kernel(uint4 *k_pool, uint4 *v_pool, const uint32_t *__restrict__ src
     const uint64_t pi = gid / chunks_per_page;
     uint4 *pool = (pi & 1) ? v_pool : k_pool;
     const uint32_t i = (uint32_t)(pi >> 1);
-    pool[(uint64_t)dst_ids[i] * chunks_per_page + c] = pool[(uint64_t)src_ids[i] * chunks_per_page + c];
+    const uint32_t src = src_ids[i], dst = dst_ids[i];
+    if (src >= n_pages || dst >= n_pages) {
+        atomicOr(status, kStatusBadPage);
+        return;
+    }
+    pool[(uint64_t)dst * chunks_per_page + c] = pool[(uint64_t)src * chunks_per_page + c];
 }
 
 inline uint32_t blocks_for(uint64_t threads) { return (uint32_t)((threads + 255) / 256); }
@@ -653,6 +689,8 @@ static mf_status paged_append_params(MfContext *ctx, const MfPagedKv *cache, con
     p.group = n_heads / cache->n_kv_heads;
     p.page_size = cache->page_size;
     p.pt_stride = cache->page_table_stride;
+    p.n_pages = cache->n_pages;
+    p.status = ctx->d_status;
     p.rope_mode = rope_mode;
     p.apply_rope = apply_rope;
     p.seq = seq;
@@ -758,6 +796,9 @@ static mf_status launch_fused_qkv(MfContext *ctx, const MfFusedQkvArgs *a, uint3
     const cudaError_t e = cudaLaunchKernelEx(&cfg, fused_qkv_kernel, qp, app);
     if (e != cudaSuccess) return fail(ctx, MF_ERR_CUDA, "launch fused_qkv_kernel: %s", cudaGetErrorString(e));
     ++ctx->launches;
+    // this kernel releases its dependents before it ends: a decode launch right behind it must not
+    // stream the caches it is writing ahead of its own dependency wait
+    if (ap && ctx->overlap_launches) ctx->note_append(ap->k_cache, ap->v_cache);
     return MF_OK;
 }
 
@@ -916,7 +957,7 @@ mf_status mf_kv_cache_to_pages(MfContext *ctx, const MfTensor *cache, const MfPa
     __half *pool = static_cast<__half *>(use_v ? paged->v_pool : paged->k_pool);
     cache_to_pages_kernel<<<blocks_for((uint64_t)paged->n_kv_heads * len * (paged->head_dim / 8)), 256, 0, ctx->stream>>>(
         tensor_ptr(cache), pool, paged->n_kv_heads, paged->head_dim, len, (uint32_t)cache->dims[1],
-        paged->page_table + (size_t)seq * paged->page_table_stride, paged->page_size);
+        paged->page_table + (size_t)seq * paged->page_table_stride, paged->page_size, paged->n_pages, ctx->d_status);
     return check_launch(ctx, "cache_to_pages_kernel");
 }
 
@@ -961,7 +1002,8 @@ mf_status mf_paged_copy_pages(MfContext *ctx, const MfPagedKv *cache, const uint
     if (n == 0) return MF_OK;
     const uint64_t chunks = (uint64_t)cache->n_kv_heads * cache->page_size * (cache->head_dim / 8);  // 16-byte units per page
     copy_pages_kernel<<<blocks_for((uint64_t)n * chunks * 2), 256, 0, ctx->stream>>>(
-        static_cast<uint4 *>(cache->k_pool), static_cast<uint4 *>(cache->v_pool), src_ids, dst_ids, n, chunks);
+        static_cast<uint4 *>(cache->k_pool), static_cast<uint4 *>(cache->v_pool), src_ids, dst_ids, n, chunks,
+        cache->n_pages, ctx->d_status);
     return check_launch(ctx, "copy_pages_kernel");
 }
 
@@ -977,7 +1019,7 @@ mf_status mf_paged_gather(MfContext *ctx, const MfPagedKv *cache, uint32_t use_v
     const __half *pool = static_cast<const __half *>(use_v ? cache->v_pool : cache->k_pool);
     cache_read_kernel<<<blocks_for((uint64_t)cache->n_kv_heads * len * (cache->head_dim / 8)), 256, 0, ctx->stream>>>(
         pool, static_cast<__half *>(out), cache->n_kv_heads, cache->head_dim, len, 0,
-        cache->page_table + (size_t)seq * cache->page_table_stride, cache->page_size, len);
+        cache->page_table + (size_t)seq * cache->page_table_stride, cache->page_size, len, cache->n_pages, ctx->d_status);
     return check_launch(ctx, "cache_read_kernel(paged)");
 }
 

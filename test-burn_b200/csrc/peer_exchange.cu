@@ -30,8 +30,7 @@ __global__ void __launch_bounds__(128) merge_pushed_kernel(const PushedMergeArgs
     const uint32_t row = blockIdx.x;
     // Launched as a programmatic dependent of this rank's decode kernel, so it may be resident
     // while that kernel still runs (all of whose CTAs are resident by then, so it cannot be starved).
-    // The arrival counters are the real dependency; the next kernel in the stream may be set up too.
-    grid_launch_dependents();
+    // The arrival counters are the real dependency.
     if (threadIdx.x == 0) {
         uint32_t good = 1;
         const long long t0 = clock64();
@@ -55,6 +54,8 @@ __global__ void __launch_bounds__(128) merge_pushed_kernel(const PushedMergeArgs
     __syncthreads();
     // everything earlier in this stream has finished and is visible before out is written
     grid_dependency_wait();
+    // the next launch is released only after the wait: at most two launches of a stream are in flight
+    grid_launch_dependents();
     if (!ok) return;
     const uint32_t D = a.head_dim;
     float mx = -1e30f;

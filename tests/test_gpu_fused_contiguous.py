@@ -127,3 +127,105 @@ def test_steps_in_a_row_on_one_cache(mfk, foundry, overlap):
         want = oracle.decode_online(q_t, k_ref, v_ref, n_heads=hq, cache_heads=hkv, head_dim=d, capacity=cap,
                                     kv_len=start + t + 1, scale=case.scale)
         assert max_abs(got[t], want) <= TOL, t
+
+
+@pytest.mark.parametrize("n_caches", [4, 5, 8])
+@pytest.mark.parametrize("overlap", [0, 1, 2])
+def test_steps_in_a_row_on_rotating_caches(mfk, foundry, n_caches, overlap):
+    """A model of 4, 5 or 8 layers, each with a cache of its own, short context (a handful of CTAs per
+    launch, so that many launches would fit on the GPU at once): launch after launch appends to the
+    cache that the launch `n_caches` later reads.  Under overlapped launches no launch may stream a
+    cache ahead of a row that an earlier launch is still writing; the reference puts a barrier after
+    every dispatch (src/types/mod.rs:577-595).  Every step of every layer is checked."""
+    import torch
+
+    hq, hkv, d, cap, start, steps = 14, 2, 64, 384, 300, 48
+    cases = [ContigCase(n_heads=hq, n_kv_heads=hkv, head_dim=d, cached=start, m=steps, capacity=cap, theta=1e6,
+                        rope_mode=0, seed=0x5EED + 17 * layer) for layer in range(n_caches)]
+    cos, sin = dev(cases[0].cos), dev(cases[0].sin)
+    caches = [(dev(c.k_cache), dev(c.v_cache)) for c in cases]
+    inputs = [(dev(c.q), dev(c.k), dev(c.v)) for c in cases]  # [steps, ...]: row t is step t's token
+    outs = torch.full((n_caches, steps, hq * d), float("nan"), dtype=torch.float16, device="cuda")
+    foundry.set_option(mfk.OPTION_OVERLAP_LAUNCHES, overlap)
+    for t in range(steps):
+        p = mfk.KvPrepFusedParamsResolved(hq * d, hkv * d, d, hq, hkv, hq // hkv, 1, start + t, cap, hq * d, 0, 0, 0)
+        for layer in range(n_caches):
+            q_all, k_all, v_all = inputs[layer]
+            kc, vc = caches[layer]
+            foundry.kv_prep_flash_decode(q_all[t:t + 1], k_all[t:t + 1], v_all[t:t + 1], None, kc, vc, cos, sin,
+                                         outs[layer, t:t + 1], p)
+    foundry.synchronize()
+    foundry.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 0)
+    got = host(outs)
+    for layer, case in enumerate(cases):
+        q_ref, k_ref, v_ref = case.oracle_append()
+        kc, vc = caches[layer]
+        assert np.array_equal(host(kc), k_ref) and np.array_equal(host(vc), v_ref), layer
+        q_rows = q_ref.reshape(hq, steps, d)
+        for t in range(steps):
+            q_t = np.ascontiguousarray(q_rows[:, t]).ravel()
+            want = oracle.decode_online(q_t, k_ref, v_ref, n_heads=hq, cache_heads=hkv, head_dim=d, capacity=cap,
+                                        kv_len=start + t + 1, scale=case.scale)
+            assert max_abs(got[layer, t], want) <= TOL, (layer, t)
+
+
+def test_rotating_caches_replayed_from_a_cuda_graph(mfk):
+    """The same rotation with the launches of one step captured into a CUDA graph and replayed: the
+    early-stream decision is frozen at capture time, replays follow one another in stream order."""
+    import torch
+
+    hq, hkv, d, cap, start, steps, n_caches = 14, 2, 64, 384, 300, 24, 4
+    cases = [ContigCase(n_heads=hq, n_kv_heads=hkv, head_dim=d, cached=start, m=steps, capacity=cap, theta=1e6,
+                        rope_mode=0, seed=0xABC + layer) for layer in range(n_caches)]
+    stream = torch.cuda.Stream()
+    f = mfk.Foundry(0, stream.cuda_stream)
+    f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 1)
+    cos, sin = dev(cases[0].cos), dev(cases[0].sin)
+    caches = [(dev(c.k_cache), dev(c.v_cache)) for c in cases]
+    inputs = [(dev(c.q), dev(c.k), dev(c.v)) for c in cases]
+    # a graph replays fixed addresses: the step's rows are copied into these before each replay
+    q_in = [torch.zeros((1, hq * d), dtype=torch.float16, device="cuda") for _ in range(n_caches)]
+    k_in = [torch.zeros((1, hkv * d), dtype=torch.float16, device="cuda") for _ in range(n_caches)]
+    v_in = [torch.zeros((1, hkv * d), dtype=torch.float16, device="cuda") for _ in range(n_caches)]
+    out_s = [torch.zeros((1, hq * d), dtype=torch.float16, device="cuda") for _ in range(n_caches)]
+    outs = torch.full((n_caches, steps, hq * d), float("nan"), dtype=torch.float16, device="cuda")
+
+    def params(t):
+        return mfk.KvPrepFusedParamsResolved(hq * d, hkv * d, d, hq, hkv, hq // hkv, 1, start + t, cap, hq * d, 0, 0, 0)
+
+    # one eager call on a scratch copy does what does not belong inside a capture (attributes, arena)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        f.kv_prep_flash_decode(q_in[0], k_in[0], v_in[0], None, dev(cases[0].k_cache), dev(cases[0].v_cache), cos, sin,
+                               out_s[0], params(0))
+    f.synchronize()
+    for t in range(steps):
+        with torch.cuda.stream(stream):
+            for layer in range(n_caches):
+                q_in[layer].copy_(inputs[layer][0][t:t + 1])
+                k_in[layer].copy_(inputs[layer][1][t:t + 1])
+                v_in[layer].copy_(inputs[layer][2][t:t + 1])
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()  # the position is a launch argument: one graph per step
+        with torch.cuda.graph(g, stream=stream):
+            for layer in range(n_caches):
+                kc, vc = caches[layer]
+                f.kv_prep_flash_decode(q_in[layer], k_in[layer], v_in[layer], None, kc, vc, cos, sin, out_s[layer], params(t))
+        with torch.cuda.stream(stream):
+            g.replay()
+            for layer in range(n_caches):
+                outs[layer, t:t + 1].copy_(out_s[layer])
+        stream.synchronize()
+    f.synchronize()
+    got = host(outs)
+    for layer, case in enumerate(cases):
+        q_ref, k_ref, v_ref = case.oracle_append()
+        kc, vc = caches[layer]
+        assert np.array_equal(host(kc), k_ref) and np.array_equal(host(vc), v_ref), layer
+        q_rows = q_ref.reshape(hq, steps, d)
+        for t in range(steps):
+            q_t = np.ascontiguousarray(q_rows[:, t]).ravel()
+            want = oracle.decode_online(q_t, k_ref, v_ref, n_heads=hq, cache_heads=hkv, head_dim=d, capacity=cap,
+                                        kv_len=start + t + 1, scale=case.scale)
+            assert max_abs(got[layer, t], want) <= TOL, (layer, t)
+    f.close()

@@ -304,3 +304,162 @@ def test_decode_chain_replays_from_a_cuda_graph(mfk):
         assert np.array_equal(host(dc.k_pool), ref[1]) and np.array_equal(host(dc.v_pool), ref[2])
     plan.close()
     f.close()
+
+
+@pytest.mark.parametrize("n_layers", [4, 6])
+@pytest.mark.parametrize("overlap", [1, 2])
+def test_steps_in_a_row_on_rotating_pools(mfk, foundry, n_layers, overlap):
+    """Several decode steps of a model whose layers each own a pool, short sequences (few CTAs per
+    launch), overlapped launches: the launch that reads a pool comes `n_layers` launches after the
+    one that appended the row before.  Pools bit-exact and every output checked, every step."""
+    import torch
+
+    from kvcases import normal
+
+    base, steps = np.array([200, 37, 450], np.uint32), 12
+    cfg = dict(batch=3, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16)
+    cases = [PagedCase(cached=base + steps, seed=0x77 + 5 * layer, **cfg) for layer in range(n_layers)]
+    for c in cases:
+        # rows from `base` on are still to be appended: poison them
+        for b in range(c.B):
+            for t in range(int(base[b]), int(base[b]) + steps + 1):
+                page = c.page_table[b, t // c.P]
+                c.k_pool[page, :, t % c.P] = 0x7E00
+                c.v_pool[page, :, t % c.P] = 0x7E00
+        c.cached = base.copy()
+        c.kv_lens = c.cached + 1
+    dcs = [DeviceCase(mfk, c) for c in cases]
+    c0 = cases[0]
+    plan = foundry.decode_plan(c0.kv_lens, n_heads=c0.Hq, n_kv_heads=c0.Hkv, head_dim=c0.D, page_size=c0.P)
+    n_q, n_kv = c0.B * c0.Hq * c0.D, c0.B * c0.Hkv * c0.D
+    outs = torch.full((steps, n_layers, c0.B, c0.Hq * c0.D), float("nan"), dtype=torch.float16, device="cuda")
+    step_in = []
+    for s in range(steps):
+        step_in.append([(normal(1000 + 10 * s + 100 * layer, n_q).reshape(c0.B, -1), normal(1001 + 10 * s + 100 * layer, n_kv).reshape(c0.B, -1),
+                         normal(1002 + 10 * s + 100 * layer, n_kv).reshape(c0.B, -1)) for layer in range(n_layers)])
+    dev_in = [[tuple(dev(x) for x in trio) for trio in row] for row in step_in]
+    lens_dev = [dev_u32(base + 1 + s) for s in range(steps)]
+    foundry.set_option(mfk.OPTION_OVERLAP_LAUNCHES, overlap)
+    for s in range(steps):
+        plan.update(base + 1 + s)
+        for dc in dcs:
+            dc.kv_lens.copy_(lens_dev[s])
+        for layer, dc in enumerate(dcs):
+            q, k, v = dev_in[s][layer]
+            foundry.paged_decode(plan, dc.desc, q, outs[s, layer], n_heads=c0.Hq, k=k, v=v, cos=dc.cos, sin=dc.sin,
+                                 rope=True, rope_mode=0, append=True, scale=float(c0.scale))
+    foundry.synchronize()
+    foundry.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 0)
+    got = host(outs)
+    for layer, c in enumerate(cases):
+        for s in range(steps):
+            c.cached = base + s
+            c.kv_lens = c.cached + 1
+            c.q, c.k, c.v = step_in[s][layer]
+            _, kp, vp, out_ref, gold = c.oracle_step()
+            c.k_pool, c.v_pool = kp, vp
+            assert max_abs(got[s, layer], out_ref) <= TOL, (layer, s)
+            assert max_abs(got[s, layer], gold.ravel()) <= TOL, (layer, s)
+        assert np.array_equal(host(dcs[layer].k_pool), c.k_pool), layer
+        assert np.array_equal(host(dcs[layer].v_pool), c.v_pool), layer
+    plan.close()
+
+
+def _case_with_spare_pages(spare=4):
+    """A case whose pools hold `spare` pages more than the descriptor will declare: an access that a
+    guard fails to stop still lands inside the allocation."""
+    case = PagedCase(batch=4, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[100, 31, 15, 700],
+                     extra_pages=spare)
+    return case, case.n_pages - spare
+
+
+def test_append_skips_a_page_id_outside_the_pool(mfk, foundry):
+    """The page id of the new row comes from the caller's device-side table.  One that is not a page
+    of the pool must not be written through: the store is skipped, mf_synchronize reports
+    InvalidOperation, and the other sequences are unaffected."""
+    import torch
+
+    case, declared = _case_with_spare_pages()
+    bad_seq, bad_page = 1, declared + 1  # inside the allocation, outside the declared pool
+    ref = case.oracle_step()
+    slot = int(case.cached[bad_seq]) // case.P
+    # the valid pages of the case must all be inside the declared pool for this to be a fair test
+    valid = case.page_table[case.page_table < 0x7FFFFFF0]
+    remap = {int(p): i for i, p in enumerate(np.sort(valid))}
+    assert len(remap) <= declared
+    # the seeded permutation may have used the spare ids: renumber pages into [0, len(valid))
+    new_k, new_v = case.k_pool.copy(), case.v_pool.copy()
+    new_k[:], new_v[:] = 0x7E00, 0x7E00
+    for old, new in remap.items():
+        new_k[new], new_v[new] = case.k_pool[old], case.v_pool[old]
+    pt = case.page_table.copy()
+    for b in range(case.B):
+        for j in range(pt.shape[1]):
+            if pt[b, j] < 0x7FFFFFF0:
+                pt[b, j] = remap[int(pt[b, j])]
+    good_pt = pt.copy()
+    pt[bad_seq, slot] = bad_page
+    for fused in (True, False):
+        k_pool, v_pool = dev(new_k), dev(new_v)
+        table, lens = dev_u32(pt), dev_u32(case.kv_lens)
+        desc = mfk.paged_kv(k_pool, v_pool, table, lens, n_kv_heads=case.Hkv, page_size=case.P, head_dim=case.D)
+        desc.n_pages = declared
+        out = torch.zeros((case.B, case.Hq * case.D), dtype=torch.float16, device="cuda")
+        q_rot = torch.zeros_like(out)
+        if fused:
+            plan = foundry.decode_plan(case.kv_lens, n_heads=case.Hq, n_kv_heads=case.Hkv, head_dim=case.D, page_size=case.P)
+            foundry.paged_decode(plan, desc, dev(case.q), out, n_heads=case.Hq, k=dev(case.k), v=dev(case.v), cos=dev(case.cos),
+                                 sin=dev(case.sin), rope=True, rope_mode=0, append=True, scale=float(case.scale))
+        else:
+            foundry.paged_kv_append(desc, dev(case.q), dev(case.k), dev(case.v), q_rot, dev(case.cos), dev(case.sin),
+                                    n_heads=case.Hq, rope_mode=0)
+        with pytest.raises(mfk.MetalError) as e:
+            foundry.synchronize()
+        assert e.value.kind == "InvalidOperation", str(e.value)
+        foundry.synchronize()  # the status word is cleared by the report
+        kp, vp = host(k_pool), host(v_pool)
+        assert np.all(kp[declared:] == 0x7E00) and np.all(vp[declared:] == 0x7E00)  # nothing beyond the declared pool
+        # every other sequence's row was appended as the oracle says
+        for b in range(case.B):
+            if b == bad_seq:
+                continue
+            t = int(case.cached[b])
+            page_old = int(case.page_table[b, t // case.P])
+            page_new = int(good_pt[b, t // case.P])
+            assert np.array_equal(kp[page_new, :, t % case.P], ref[1][page_old, :, t % case.P])
+            assert np.array_equal(vp[page_new, :, t % case.P], ref[2][page_old, :, t % case.P])
+            if fused:
+                assert max_abs(host(out)[b], ref[3][b]) <= TOL
+        if fused:
+            plan.close()
+
+
+def test_append_skips_an_empty_sequence_and_a_length_past_the_table(mfk, foundry):
+    """kv_lens is device data too: a length of zero has no row to append (position -1), one past the
+    table has no page entry.  Both are skipped with a status; the other sequences' rows are written."""
+    import torch
+
+    case, _ = _case_with_spare_pages()
+    ref = case.oracle_step()
+    bad = 2
+    for bad_len in (0, case.pt_stride * case.P + 1):
+        lens = case.kv_lens.copy()
+        lens[bad] = bad_len
+        k_pool, v_pool = dev(case.k_pool), dev(case.v_pool)
+        table, dlens = dev_u32(case.page_table), dev_u32(lens)
+        desc = mfk.paged_kv(k_pool, v_pool, table, dlens, n_kv_heads=case.Hkv, page_size=case.P, head_dim=case.D)
+        q_rot = torch.zeros((case.B, case.Hq * case.D), dtype=torch.float16, device="cuda")
+        foundry.paged_kv_append(desc, dev(case.q), dev(case.k), dev(case.v), q_rot, dev(case.cos), dev(case.sin),
+                                n_heads=case.Hq, rope_mode=0)
+        with pytest.raises(mfk.MetalError) as e:
+            foundry.synchronize()
+        assert e.value.kind == "InvalidOperation"
+        want_k, want_v = case.k_pool.copy(), case.v_pool.copy()
+        for b in range(case.B):
+            if b == bad:
+                continue
+            t = int(case.cached[b])
+            page = int(case.page_table[b, t // case.P])
+            want_k[page, :, t % case.P] = ref[1][page, :, t % case.P]
+            want_v[page, :, t % case.P] = ref[2][page, :, t % case.P]
+        assert np.array_equal(host(k_pool), want_k) and np.array_equal(host(v_pool), want_v)

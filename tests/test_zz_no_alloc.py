@@ -4,8 +4,9 @@ Some hosts cannot call cudaMalloc at decode time: their own memory pool owns the
 forbids plug-ins to allocate, or the loop cannot take the device-wide synchronisation an
 allocation implies.  This entry point keeps the kernel's split-KV partials and tickets in an
 array compiled into the library instead.  The test calls it through the C ABI twice in a row
-(the array is shared and keeps the previous call's contents) and compares with mf_flash_decode,
-the allocating entry point, on the same inputs.  It must pass both alone in a fresh process and
+(the array is shared and keeps the previous call's contents) and checks the result against the CPU
+oracle and the fp64 gold, and against mf_flash_decode, the allocating entry point, on the same
+inputs.  It must pass both alone in a fresh process and
 after every other test, so it builds its own inputs and relies on no state left by others.
 
 This file sorts last on purpose: a run that stops at the first failure has then already run
@@ -16,6 +17,7 @@ import ctypes as C
 import numpy as np
 import pytest
 
+import oracle
 from kvcases import ContigCase, dev, host, max_abs
 
 pytestmark = pytest.mark.gpu
@@ -50,10 +52,19 @@ def test_static_scratch_decode_matches_allocating_decode(mfk, foundry, shape):
                                                     err, 256)
         assert rc == 0, err.value.decode()
         outs.append(out)
+    status = C.c_uint32(0xFFFFFFFF)
+    assert mfk.lib.mf_static_scratch_status(stream if stream else None, C.byref(status)) == 0
     torch.cuda.synchronize()
+    assert status.value == 0  # no device-side wait ran out
+    want = oracle.decode_online(q_rot, kc, vc, n_heads=hq, cache_heads=hkv, head_dim=d, capacity=cap, kv_len=case.L,
+                                scale=case.scale)
+    gold = oracle.decode_gold(q_rot, kc, vc, n_heads=hq, cache_heads=hkv, head_dim=d, capacity=cap, kv_len=case.L,
+                              scale=case.scale)
     for out in outs:
-        assert max_abs(host(out), host(ref)) <= TOL
-        assert torch.equal(out, ref)  # same kernel, same spans: the bits agree too
+        assert max_abs(host(out), want) <= TOL
+        assert max_abs(host(out), gold.ravel()) <= TOL
+        # and, on a context with default options, the allocating entry point cuts the work the same way
+        assert torch.equal(out, ref)
     assert torch.equal(outs[0], outs[1])
 
 
