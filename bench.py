@@ -113,6 +113,18 @@ def algorithmic_bytes_per_layer(w, kv_lens):
     return int(total)
 
 
+def config_of(w):
+    """The `config` object of a batched-decode line: the same for this arm and the reference arm (rank 0's
+    figures; rank r draws its lengths and page table from seed + r)."""
+    cached, kv_lens = make_lengths(w, SEED)
+    P = w["page_size"]
+    n_pages = int(((kv_lens + P - 1) // P).sum())
+    pool_gb = 2 * w["layers"] * n_pages * w["n_kv_heads"] * P * w["head_dim"] * 2 / 1e9
+    return {"workload": w["name"], "layers": w["layers"], "batch_per_gpu": w["batch"],
+            "tokens_cached_per_gpu": int(cached.sum()), "pages_per_layer": n_pages, "seed": SEED,
+            "seed_rule": "rank r uses seed + r", "l2": "inputs larger than L2 (KV pools %.1f GB per GPU)" % pool_gb}
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
@@ -344,9 +356,8 @@ def run_ours(args, w):
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "us_per_step": ms_step * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate",
         "data": "synthetic",
-        "config": {"workload": w["name"], "layers": layers, "batch_per_gpu": B, "tokens_cached_per_gpu": int(cached.sum()),
-                   "pages_per_layer": n_pages, "seed": SEED, "l2": "inputs larger than L2 (KV pools %.1f GB per GPU)"
-                   % (2 * layers * pool_elems * 2 / 1e9), "ctas": plan.ctas, "work_items": plan.items},
+        "config": config_of(w),
+        "plan": {"ctas": plan.ctas, "work_items": plan.items},
         "hbm_tb_s": achieved / 1e3,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": peak_kind, "kernel": "decode_kernel<128,1,3,2>", "launch_us": launch_us,
@@ -361,7 +372,7 @@ def run_ours(args, w):
                            "mean": float(per_step.mean()), "sd": float(per_step.std())},
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        result["cpu_baseline"] = cpu_baseline(w, steps=1)
+        result["cpu_baseline"] = cpu_baseline(w, steps=3)
     # Sanity on the timed buffers: the last layer's output is finite and the end-to-end output equals it.
     torch.cuda.synchronize()
     ok = bool(torch.isfinite(d_out[-1].float()).all()) and bool(torch.equal(h_out[-1].to(dev), d_out[-1]))
@@ -887,30 +898,45 @@ def cpu_layer_inputs(w, seed):
 
 
 def cpu_time_layer(w, repeats):
+    """One layer of the workload on the host cores with the fast CPU arm (oracle/mf_oracle_fast.c, built here
+    for this machine); the strict scalar oracle stands in if that build is not possible.  Returns the times,
+    the threads used and a description of the build."""
     import oracle
 
-    L = oracle.lib()
-    L.mfo_set_num_threads(len(os.sched_getaffinity(0)))  # torchrun exports OMP_NUM_THREADS=1
+    threads = len(os.sched_getaffinity(0))  # torchrun exports OMP_NUM_THREADS=1
     hq, hkv, d, B, P = w["n_heads"], w["n_kv_heads"], w["head_dim"], w["batch"], w["page_size"]
     cached, kv_lens, table, k_pool, v_pool, q, k, v = cpu_layer_inputs(w, SEED)
     cos, sin = oracle.rope_tables(w["theta"], d, int(kv_lens.max()))
     out = np.empty(B * hq * d, np.uint16)
+    try:
+        F = oracle.fast_lib()
+        F.mfo_fast_set_num_threads(threads)
+        fn, threads = F.mfo_fast_paged_decode_layer, int(F.mfo_fast_num_threads())
+        build = "fast build (gcc -O3 -march=native, %s, one K/V pass per KV head, OpenMP)" % (
+            "F16C + FMA vectors" if F.mfo_fast_simd() else "no F16C/AVX2 on this host: scalar conversions")
+    except Exception as e:  # no gcc on this host, or the build failed
+        L = oracle.lib()
+        L.mfo_set_num_threads(threads)
+        fn, threads = L.mfo_paged_decode_layer, int(L.mfo_num_threads())
+        build = "strict scalar build (-O2 -ffp-contract=off; the fast build failed: %s)" % type(e).__name__
     times = []
     for _ in range(repeats):
         t0 = time.perf_counter()
-        L.mfo_paged_decode_layer(q, k, v, k_pool, v_pool, cos, sin, table, table.shape[1], kv_lens, B, hq, hkv, d, P,
-                                 w["rope_mode"], 1.0 / math.sqrt(d), out)
+        fn(q, k, v, k_pool, v_pool, cos, sin, table, table.shape[1], kv_lens, B, hq, hkv, d, P, w["rope_mode"],
+           1.0 / math.sqrt(d), out)
         times.append(time.perf_counter() - t0)
-    return times, int(L.mfo_num_threads())
+    return times, threads, build
 
 
-def cpu_baseline(w, steps=1):
-    times, threads = cpu_time_layer(w, steps)
+def cpu_baseline(w, steps=3):
+    times, threads, build = cpu_time_layer(w, steps)
     t_layer = float(np.median(times))
+    kv_lens = make_lengths(w, SEED)[1]
     return {"value": w["batch"] / (t_layer * w["layers"]), "unit": "tokens/s", "cores": threads, "kind": "port",
-            "sample": "1 of %d layers, all %d sequences, timed %d time(s) (%.2f s per layer), scaled by the layer count; "
-                      "scalar C restatement of the reference math with OpenMP over (sequence, kv head)"
-                      % (w["layers"], w["batch"], steps, t_layer)}
+            "build": build, "achieved_gbs": algorithmic_bytes_per_layer(w, kv_lens) / t_layer / 1e9,
+            "extrapolated": "1 of %d layers x %d" % (w["layers"], w["layers"]),
+            "sample": "1 of %d layers, all %d sequences, timed %d time(s) (median %.3f s per layer), scaled by the layer "
+                      "count; CPU restatement of the reference math, %s" % (w["layers"], w["batch"], steps, t_layer, build)}
 
 
 def run_reference(args, w):
@@ -918,18 +944,22 @@ def run_reference(args, w):
     if rank != 0:
         return 0
     n = int(os.environ.get("WORLD_SIZE", "1"))
-    times, threads = cpu_time_layer(w, max(1, args.steps + min(args.warmup, 1)))
+    times, threads, build = cpu_time_layer(w, max(1, args.steps + min(args.warmup, 1)))
     times = times[min(args.warmup, 1):] or times
     t_layer = float(np.mean(times))
     ms_step = t_layer * w["layers"] * 1e3
     value = w["batch"] / (ms_step * 1e-3)
-    sample = ("each step = 1 of %d layers on all %d sequences (%.2f s), scaled by the layer count; CPU restatement of "
-              "the reference math (the reference is Rust + Metal and cannot run on this host)" % (w["layers"], w["batch"], t_layer))
+    kv_lens = make_lengths(w, SEED)[1]
+    sample = ("each step = 1 of %d layers on all %d sequences (%.3f s), scaled by the layer count; CPU restatement of "
+              "the reference math (the reference is Rust + Metal and cannot run on this host), %s"
+              % (w["layers"], w["batch"], t_layer, build))
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": n, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f16 storage, f32 accumulate", "data": "synthetic", "config": {"workload": w["name"]},
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "warmup": args.warmup, "ms_per_step": ms_step, "extrapolated": "1 of %d layers x %d" % (w["layers"], w["layers"]),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16 storage, f32 accumulate", "data": "synthetic", "config": config_of(w),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "build": build,
+                         "achieved_gbs": algorithmic_bytes_per_layer(w, kv_lens) / t_layer / 1e9, "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
     return 0
@@ -958,6 +988,10 @@ def main():
     ap.add_argument("--page-size", type=int, default=0, help="override the workload's page size (experiments); c4: prefill into a paged cache with pages of this many rows")
     ap.add_argument("--sequential-pages", action="store_true", help="identity page table (experiments)")
     args = ap.parse_args()
+    if args.impl == "reference" and args.workload not in WORKLOADS:
+        sys.stderr.write("--impl reference times the batched paged decode workloads (%s) only; %s has no CPU arm\n"
+                         % (", ".join(sorted(WORKLOADS)), args.workload))
+        return 2
     if args.workload == "c4":
         return run_prefill(args)
     if args.workload in CONTIGUOUS:

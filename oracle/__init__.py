@@ -39,6 +39,53 @@ f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
 f64p = np.ctypeslib.ndpointer(dtype=np.float64, flags="C_CONTIGUOUS")
 u32 = C.c_uint32
 
+_FAST_SRC = _HERE / "mf_oracle_fast.c"
+_FAST_LIB = None
+
+
+def _cpu_tag() -> str:
+    """A short tag of this machine's CPU features: the fast build uses -march=native, so a library
+    built on one machine must not be loaded on another."""
+    import hashlib
+
+    flags = ""
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("flags"):
+                flags = line
+                break
+    except OSError:
+        pass
+    return hashlib.sha1(flags.encode()).hexdigest()[:10]
+
+
+def build_fast(force: bool = False) -> Path:
+    """Compile oracle/mf_oracle_fast.c for THIS machine (gcc -O3 -march=native, OpenMP) ->
+    oracle/libmf_oracle_fast.<cpu tag>.so."""
+    so = _HERE / f"libmf_oracle_fast.{_cpu_tag()}.so"
+    if not force and so.exists() and so.stat().st_mtime >= _FAST_SRC.stat().st_mtime:
+        return so
+    cmd = ["gcc", "-O3", "-march=native", "-fPIC", "-shared", "-fopenmp", "-std=c11", "-Wall", "-Wextra", "-o", str(so),
+           str(_FAST_SRC), "-lm"]
+    subprocess.run(cmd, check=True, cwd=_HERE)
+    return so
+
+
+def fast_lib() -> C.CDLL:
+    """The timed CPU arm (see mf_oracle_fast.c).  Built on first use on the machine that runs it."""
+    global _FAST_LIB
+    if _FAST_LIB is not None:
+        return _FAST_LIB
+    L = C.CDLL(str(build_fast()))
+    L.mfo_fast_paged_decode_layer.argtypes = [u16p, u16p, u16p, u16p, u16p, u16p, u16p, u32p, u32, u32p, u32, u32, u32, u32,
+                                              u32, u32, C.c_float, u16p]
+    L.mfo_fast_paged_decode_layer.restype = C.c_int
+    L.mfo_fast_num_threads.restype = C.c_int
+    L.mfo_fast_set_num_threads.argtypes = [C.c_int]
+    L.mfo_fast_simd.restype = C.c_int
+    _FAST_LIB = L
+    return L
+
 
 class KvPrepParams(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in (
@@ -94,6 +141,8 @@ def lib() -> C.CDLL:
                                    f64p]
     L.mfo_splitk_tile_range.argtypes = [u32, u32, u32, C.POINTER(u32), C.POINTER(u32)]
     L.mfo_merge_partials.argtypes = [f32p, f32p, f32p, u32, u32, u32, u16p]
+    L.mfo_sdpa_materialized.argtypes = [u16p, u16p, u16p, u32, u32, u32, u32, u32, u32, C.c_uint64, C.c_uint64,
+                                        C.c_uint64, C.c_uint64, C.c_int, u32, C.c_float, u16p]
     L.mfo_paged_decode_layer.argtypes = [u16p, u16p, u16p, u16p, u16p, u16p, u16p, u32p, u32, u32p,
                                          u32, u32, u32, u32, u32, u32, C.c_float, u16p]
     L.mfo_num_threads.restype = C.c_int
@@ -209,6 +258,21 @@ def prefill_gold(q, k_cache, v_cache, *, n_heads, cache_heads, head_dim, capacit
     out = np.empty((q_len, n_heads * head_dim), np.float64)
     lib().mfo_prefill_gold(q, k_cache, v_cache, n_heads, cache_heads, head_dim, capacity, q_len,
                            kv_len, query_offset, scale, out)
+    return out
+
+
+def sdpa_materialized(q, k, v, *, n_heads, head_dim, m, kv_len, causal, query_offset, scale, q_head_major,
+                      k_rows=None):
+    """The reference's materialised fallback (S and P stored as f16).  q is token-major [m, H*D]
+    or, with q_head_major, packed head-major [H, m, D]; k, v are [H, k_rows, D]; returns the
+    token-major output [m, H*D] as f16 bits."""
+    k_rows = kv_len if k_rows is None else k_rows
+    D = head_dim
+    out = np.zeros((m, n_heads * D), np.uint16)
+    qs_h, qs_m = (m * D, D) if q_head_major else (D, n_heads * D)
+    lib().mfo_sdpa_materialized(np.ascontiguousarray(q).ravel(), np.ascontiguousarray(k).ravel(),
+                                np.ascontiguousarray(v).ravel(), n_heads, D, m, kv_len, k_rows, k_rows, qs_h, qs_m,
+                                D, n_heads * D, int(bool(causal)), query_offset, scale, out.reshape(-1))
     return out
 
 

@@ -752,6 +752,69 @@ void mfo_merge_partials(const float *acc, const float *m, const float *l, uint32
     }
 }
 
+/* ------------------------------------------------- materialised attention ---
+ * SdpaReferenceStep / execute_sdpa_reference (src/metals/sdpa/step.rs:558-779) with the
+ * rounding points of its three dispatches:
+ *   1. S = scale * (Q K^T): f32 accumulation, alpha = scale applied to the sum, S stored
+ *      as f16 scratch (step.rs:660-705; the scratch tensors are F16, sdpa/scratch.rs);
+ *   2. row softmax of softmax_sdpa_batched.metal:14-115: masked entries (causal and
+ *      i > row + query_offset) count as -INFINITY, max over the row, sum of exp(val - max)
+ *      over the visible entries in f32, P = exp(val - max) / sum stored as f16; a row whose
+ *      max or sum is not finite, or whose sum is <= 0, gets all-zero probabilities;
+ *   3. O = P V: f16 x f16 products, f32 accumulation, stored as f16 (step.rs:735-776).
+ * There is no GQA map: head h of Q uses head h of K and V (batch_stride_b per query head,
+ * step.rs:690, 750), so the caches passed here are expanded [n_heads, k_rows, D].
+ * Strides are in elements: q[h*q_stride_h + r*q_stride_m + d], out[h*out_stride_h +
+ * r*out_stride_m + d].  expf stands in for metal::fast::exp. */
+void mfo_sdpa_materialized(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint32_t n_heads,
+                           uint32_t head_dim, uint32_t m, uint32_t kv_len, uint32_t k_rows,
+                           uint32_t v_rows, uint64_t q_stride_h, uint64_t q_stride_m,
+                           uint64_t out_stride_h, uint64_t out_stride_m, int causal,
+                           uint32_t query_offset, float scale, uint16_t *out)
+{
+    h2f_init();
+    const uint32_t D = head_dim;
+    uint16_t *s16 = (uint16_t *)malloc(sizeof(uint16_t) * (size_t)(kv_len ? kv_len : 1));
+    uint16_t *p16 = (uint16_t *)malloc(sizeof(uint16_t) * (size_t)(kv_len ? kv_len : 1));
+    for (uint32_t h = 0; h < n_heads; ++h) {
+        const uint16_t *kh = k + (size_t)h * k_rows * D;
+        const uint16_t *vh = v + (size_t)h * v_rows * D;
+        for (uint32_t r = 0; r < m; ++r) {
+            const uint16_t *qr = q + (size_t)h * q_stride_h + (size_t)r * q_stride_m;
+            const uint64_t mask_pos = (uint64_t)r + query_offset;
+            for (uint32_t i = 0; i < kv_len; ++i) s16[i] = mfo_f32_to_f16(dot_f16(qr, kh + (size_t)i * D, D) * scale);
+            float row_max = -INFINITY;
+            for (uint32_t i = 0; i < kv_len; ++i) {
+                float val = H2F(s16[i]);
+                if (causal && i > mask_pos) val = -INFINITY;
+                if (val > row_max) row_max = val;
+            }
+            float row_sum = 0.0f;
+            if (isfinite(row_max))
+                for (uint32_t i = 0; i < kv_len; ++i)
+                    if (!causal || i <= mask_pos) row_sum += expf(H2F(s16[i]) - row_max);
+            const int invalid = !isfinite(row_max) || !isfinite(row_sum) || row_sum <= 0.0f;
+            for (uint32_t i = 0; i < kv_len; ++i) {
+                float prob = 0.0f;
+                if (!(causal && i > mask_pos) && !invalid) {
+                    const float diff = H2F(s16[i]) - row_max;
+                    prob = (isfinite(diff) ? expf(diff) : 0.0f) / row_sum;
+                    if (!isfinite(prob)) prob = 0.0f;
+                }
+                p16[i] = mfo_f32_to_f16(prob);
+            }
+            uint16_t *dst = out + (size_t)h * out_stride_h + (size_t)r * out_stride_m;
+            for (uint32_t d = 0; d < D; ++d) {
+                float acc = 0.0f;
+                for (uint32_t i = 0; i < kv_len; ++i) acc += H2F(p16[i]) * H2F(vh[(size_t)i * D + d]);
+                dst[d] = mfo_f32_to_f16(acc);
+            }
+        }
+    }
+    free(s16);
+    free(p16);
+}
+
 /* ------------------------------------------------------- timed CPU layer --- */
 
 void mfo_set_num_threads(int n)

@@ -213,6 +213,19 @@ void mfo_merge_partials(const float *acc, const float *m, const float *l,
                         uint32_t n_splits, uint32_t rows, uint32_t head_dim,
                         uint16_t *out);
 
+/* ---- materialised attention (src/metals/sdpa/step.rs:558-779,
+ *      src/metals/softmax/softmax_sdpa_batched.metal:14-115) --------------------
+ * The reference's fallback path with its own rounding points: S = scale*QK^T stored as
+ * f16, row softmax with a -INFINITY mask (causal: key i hidden from row r iff
+ * i > r + query_offset), P stored as f16, O = P V.  No GQA map (head h of Q reads head h
+ * of K/V): K is [n_heads, k_rows, D], V is [n_heads, v_rows, D].  Strides in elements.
+ * This is the function the reference's flash-vs-materialised tests compare against. */
+void mfo_sdpa_materialized(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint32_t n_heads,
+                           uint32_t head_dim, uint32_t m, uint32_t kv_len, uint32_t k_rows,
+                           uint32_t v_rows, uint64_t q_stride_h, uint64_t q_stride_m,
+                           uint64_t out_stride_h, uint64_t out_stride_m, int causal,
+                           uint32_t query_offset, float scale, uint16_t *out);
+
 /* ---- timed CPU baseline ----------------------------------------------------
  * One layer of batched paged decode (append + attention) over `batch` sequences,
  * threaded with OpenMP over (sequence, kv head) when built with -fopenmp.

@@ -276,6 +276,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     const uint32_t boxes_per_tile = kTileKeys / rows_per_box;
     const uint32_t rpb_log2 = 31 - __clz(rows_per_box);
 
+#ifdef MF_EXP_EARLY_TRIGGER
+    grid_launch_dependents();
+#endif
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------ producer ---
         if (lane == 0) {

@@ -330,3 +330,26 @@ def test_fused_qkv_restatement(orc, shape):
     plain = orc.fused_qkv(bits(x), *[bits(w) for w in ws], m=m, k_dim=k_dim, n_dim=n_dim, n_kv=n_kv)
     ref = x.astype(np.float64) @ ws[0].astype(np.float64).T
     assert np.all(np.abs(plain[0].view(np.float16).astype(np.float64).reshape(ref.shape) - ref) <= np.abs(ref) * 2.0 ** -10 + 1e-3)
+
+
+@pytest.mark.parametrize("cfg", [dict(batch=5, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[511, 1000, 2049, 3, 0]),
+                                 dict(batch=3, n_heads=14, n_kv_heads=2, head_dim=64, page_size=16, cached=[511, 31, 32]),
+                                 dict(batch=2, n_heads=24, n_kv_heads=8, head_dim=128, page_size=64, cached=[63, 700])])
+@pytest.mark.parametrize("rope_mode", [0, 1])
+def test_fast_cpu_arm_agrees_with_the_strict_oracle(cfg, rope_mode):
+    """The timed CPU arm (mf_oracle_fast.c: F16C, FMA vectors, one K/V pass per KV head, blocked softmax,
+    OpenMP) against the strict scalar oracle on the same layer: pools bit-exact, outputs within 2e-3."""
+    from kvcases import PagedCase, max_abs
+
+    case = PagedCase(rope_mode=rope_mode, **cfg)
+    _, kp_ref, vp_ref, out_ref, gold = case.oracle_step()
+    F = oracle.fast_lib()
+    kp, vp = case.k_pool.copy(), case.v_pool.copy()
+    out = np.zeros((case.B, case.Hq * case.D), np.uint16)
+    rc = F.mfo_fast_paged_decode_layer(case.q, case.k, case.v, kp, vp, case.cos, case.sin, case.page_table, case.pt_stride,
+                                       case.kv_lens, case.B, case.Hq, case.Hkv, case.D, case.P, rope_mode,
+                                       float(case.scale), out)
+    assert rc == 0
+    assert np.array_equal(kp, kp_ref) and np.array_equal(vp, vp_ref)
+    assert max_abs(out, out_ref) <= 2e-3
+    assert max_abs(out, gold.ravel()) <= 2e-3
