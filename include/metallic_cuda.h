@@ -275,6 +275,61 @@ MF_API uint64_t mf_estimate_kv_memory(uint32_t n_layers, uint32_t cache_heads, u
 /* Prefill split-K heuristic (src/metals/flashattention/step.rs:849-866). */
 MF_API uint32_t mf_prefill_split_k(uint32_t kv_seq_len, uint32_t q_seq_len);
 
+/* KvCacheLayout / KvGeometry (src/model/kv_geometry.rs:6-90). */
+enum { MF_KV_LAYOUT_EXPANDED_HEADS = 0, MF_KV_LAYOUT_COMPACT_KV_HEADS = 1 };
+typedef struct MfKvGeometry {
+    uint32_t n_heads;
+    uint32_t n_kv_heads;
+    uint32_t group_size;
+    uint32_t head_dim;
+    uint32_t layout;      /* MF_KV_LAYOUT_* */
+    uint32_t cache_heads; /* n_heads (expanded) or n_kv_heads (compact) */
+} MfKvGeometry;
+/* KvGeometry::from_architecture (src/model/kv_geometry.rs:26-63) from the three architecture
+ * numbers it reads: n_heads >= 1; n_kv_heads 0 means n_heads and is clamped to n_heads;
+ * group_size = n_heads / n_kv_heads when that divides, else 1; head_dim = d_model / n_heads;
+ * compact layout when n_kv_heads < n_heads, expanded otherwise.  (The reference can also
+ * take the layout from the model file's cache tensor declaration; a caller that has one
+ * overrides `layout` and `cache_heads` itself or uses mf_kv_geometry_from_cache_tensor.) */
+MF_API mf_status mf_kv_geometry_from_architecture(uint32_t n_heads, uint32_t n_kv_heads, uint32_t d_model,
+                                                  MfKvGeometry *out);
+/* KvGeometry::from_cache_tensor (src/model/kv_geometry.rs:92-150): checks a cache tensor
+ * against the architecture and returns the layout it implies.  MF_ERR_INVALID_SHAPE with the
+ * reference's message in err (optional host buffer) when the tensor is not F16, not rank 3,
+ * has another capacity than expected_capacity, another head_dim, or a head count that is
+ * neither n_heads nor n_kv_heads. */
+MF_API mf_status mf_kv_geometry_from_cache_tensor(uint32_t n_heads, uint32_t n_kv_heads, uint32_t d_model,
+                                                  const MfTensor *cache, uint64_t expected_capacity,
+                                                  MfKvGeometry *out, char *err, uint32_t err_len);
+
+/* ContextConfig (src/model/context.rs:11-49). */
+typedef struct MfContextConfig {
+    uint64_t max_context_len;
+    uint64_t allocated_capacity;
+    uint64_t budget_bytes;      /* explicit budget; 0 with budget_auto_pct > 0 means "auto" */
+    float budget_auto_pct;      /* MemoryBudget::Auto { percentage }; 0 when the budget is explicit */
+    uint32_t full_reserve;      /* GrowthStrategy::FullReserve (else grow on demand from 2048, x2) */
+} MfContextConfig;
+/* ContextConfig::from_architecture (src/model/context.rs:105-152) as a pure function of what
+ * it reads: the model's max_seq_len (0 = none), the caller's cap (0 = none), the value of
+ * METALLIC_MAX_CONTEXT_LEN (0 = unset), whether METALLIC_FULL_CONTEXT_RESERVE is set, and
+ * METALLIC_KV_MEMORY_BUDGET_MB (negative = unset -> Auto 50 %).  The caller's cap wins over
+ * the environment's; either is clamped to the model's maximum; with neither a model maximum
+ * nor a cap the limit is 2048; never below 1.  allocated_capacity = align(min(2048, max)),
+ * or align(max) under full reserve. */
+MF_API mf_status mf_context_config_from_architecture(uint64_t model_max_seq_len, uint64_t override_len,
+                                                     uint64_t env_max_context_len, uint32_t full_reserve,
+                                                     int64_t kv_memory_budget_mb, MfContextConfig *out);
+/* The same, reading the three environment variables itself as the reference does. */
+MF_API mf_status mf_context_config_from_env(uint64_t model_max_seq_len, uint64_t override_len, MfContextConfig *out);
+/* ContextConfig::apply_memory_budget (src/model/context.rs:158-210): budget = the explicit
+ * bytes, or pct x device_recommended_bytes; max tokens = budget / per_token_bytes; a budget
+ * below one token pins both fields to 1 / align(1); otherwise max_context_len is lowered to
+ * align(max tokens) when that is smaller, and allocated_capacity follows it down.
+ * per_token_bytes comes from mf_kv_per_token_bytes_f16.  Nothing changes when either is 0. */
+MF_API mf_status mf_apply_memory_budget(MfContextConfig *cfg, uint64_t device_recommended_bytes,
+                                        uint64_t per_token_bytes);
+
 /* ---------------------------------------------------------------- operators --- */
 
 /* "KvPrepFused" (src/metals/kv_prep/step.rs:93-132, kv_prep_fused.metal:26-123):
@@ -606,9 +661,18 @@ MF_API mf_status mf_paged_copy_pages(MfContext *ctx, const MfPagedKv *cache, con
  * expected value and merges out of its own memory.
  *   recv[r]     rank r's receive buffer, 2 * world * rows * (head_dim + 2) floats
  *               ([step parity][source rank][acc | m | l]), mapped in this process
- *   counters[r] rank r's arrival counters (8 per-source totals, then one per unit), zero before
- *               the first step
- * Steps are numbered from 0 and must be issued in the same order on every rank. */
+ *   counters[r] rank r's counters (8 per-source totals, 8 "merged by rank" counts, then one per
+ *               unit), zero before the first step
+ * Steps are numbered from 0 and must be issued in the same order on every rank, and a rank
+ * pushes the same number of units in every step (the counters only ever grow: the value that
+ * completes step s is units * (s + 1)).
+ * Two step parities of receive blocks suffice between ranks that push: a rank's push of step
+ * s + 2 follows its own merge of step s + 1, which waited for every other pusher's push of
+ * s + 1, which that pusher's stream ordered after its merge of step s.  A rank that only merges
+ * waits for nobody, so nothing in that chain holds the pushers back for it: such ranks are
+ * named in merge_only_mask, they count every row they have merged on the pushers' "merged by"
+ * words, and a pusher's decode kernel of step s >= 2 waits (bounded, 2 s, then a Timeout at
+ * mf_synchronize) until each of them has merged step s - 2 before it overwrites that block. */
 typedef struct MfPeerExchange {
     float *recv[8];
     uint32_t *counters[8];
@@ -617,6 +681,8 @@ typedef struct MfPeerExchange {
     uint32_t rank;
     uint32_t rows;     /* batch * n_heads, as given to create */
     uint32_t head_dim;
+    uint32_t merge_only_mask; /* bit r: rank r never pushes, it only calls mf_merge_pushed (set by the
+                               * caller, the same on every rank, before the first step; 0 after create) */
 } MfPeerExchange;
 
 #define MF_IPC_HANDLE_BYTES 64

@@ -39,6 +39,7 @@ ROUTE_DECODE, ROUTE_PREFILL, ROUTE_PREFILL_SPLITK, ROUTE_REFERENCE = 1, 2, 3, 4
 DTYPE_F16, DTYPE_F32, DTYPE_U32 = 0, 1, 2
 ALL_SEQUENCES = 0xFFFFFFFF
 OPTION_OVERLAP_LAUNCHES = 1
+KV_LAYOUT_EXPANDED_HEADS, KV_LAYOUT_COMPACT_KV_HEADS = 0, 1
 
 
 class MetalError(RuntimeError):
@@ -90,6 +91,15 @@ class SdpaPrefillSplitKParams(C.Structure):
     _fields_ = [("base", SdpaPrefillParams), ("n_heads", u32), ("split_k", u32)]
 
 
+class MfKvGeometry(C.Structure):
+    _fields_ = [(f, u32) for f in ("n_heads", "n_kv_heads", "group_size", "head_dim", "layout", "cache_heads")]
+
+
+class MfContextConfig(C.Structure):
+    _fields_ = [("max_context_len", u64), ("allocated_capacity", u64), ("budget_bytes", u64), ("budget_auto_pct", C.c_float),
+                ("full_reserve", u32)]
+
+
 class MfPagedKv(C.Structure):
     _fields_ = [("k_pool", vp), ("v_pool", vp), ("page_table", vp), ("kv_lens", vp), ("n_pages", u32),
                 ("n_kv_heads", u32), ("page_size", u32), ("head_dim", u32), ("page_table_stride", u32),
@@ -125,7 +135,7 @@ class MfFusedQkvArgs(C.Structure):
 
 class MfPeerExchange(C.Structure):
     _fields_ = [("recv", vp * 8), ("counters", vp * 8), ("mapping", vp * 8), ("world", u32), ("rank", u32),
-                ("rows", u32), ("head_dim", u32)]
+                ("rows", u32), ("head_dim", u32), ("merge_only_mask", u32)]
 
 
 # Every symbol declared in include/metallic_cuda.h, with its signature.
@@ -146,6 +156,12 @@ _SIGNATURES = {
     "mf_kv_per_token_bytes_f16": (u64, [u32, u32, u32]),
     "mf_estimate_kv_memory": (u64, [u32, u32, u32, u64]),
     "mf_prefill_split_k": (u32, [u32, u32]),
+    "mf_kv_geometry_from_architecture": (C.c_int32, [u32, u32, u32, C.POINTER(MfKvGeometry)]),
+    "mf_kv_geometry_from_cache_tensor": (C.c_int32, [u32, u32, u32, C.POINTER(MfTensor), u64, C.POINTER(MfKvGeometry),
+                                                     C.c_char_p, u32]),
+    "mf_context_config_from_architecture": (C.c_int32, [u64, u64, u64, u32, C.c_int64, C.POINTER(MfContextConfig)]),
+    "mf_context_config_from_env": (C.c_int32, [u64, u64, C.POINTER(MfContextConfig)]),
+    "mf_apply_memory_budget": (C.c_int32, [C.POINTER(MfContextConfig), u64, u64]),
     "mf_kv_prep_fused": (C.c_int32, [vp] + [C.POINTER(MfTensor)] * 8 + [C.POINTER(KvPrepFusedParamsResolved)]),
     "mf_rope": (C.c_int32, [vp] + [C.POINTER(MfTensor)] * 4 + [C.POINTER(RopeParamsResolved)]),
     "mf_kv_cache_write": (C.c_int32, [vp, C.POINTER(MfTensor), C.POINTER(MfTensor),

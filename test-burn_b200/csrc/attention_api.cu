@@ -148,8 +148,8 @@ mf_status decode_contiguous(MfContext *ctx, const void *q, const void *k, const 
         p.rope_position = sp->kv_len - 1;
         p.cos_t = static_cast<const __half *>(cos);
         p.sin_t = static_cast<const __half *>(sin);
-        // ... unless the launch directly in front of this one appended to this same cache (a one-layer
-        // model, two calls in a row on one cache): its new row may not have landed yet
+        // ... unless a launch that may still be in flight appended to this same cache (a one-layer model,
+        // two calls in a row on one cache): its new row may not have landed yet
         p.early_stream = (ctx->overlap_launches && ctx->may_stream_early(k, v)) ? 1u : 0u;
     }
     // The tensor maps cover every row any (batch, head) can address.
@@ -166,9 +166,7 @@ mf_status decode_contiguous(MfContext *ctx, const void *q, const void *k, const 
         if ((st = get_tensor_map(ctx, k, k_rows, D, kTileKeys, 64, &tm_k)) != MF_OK) return st;
         if ((st = get_tensor_map(ctx, v, v_rows, D, kTileKeys, 64, &tm_v)) != MF_OK) return st;
     }
-    st = launch_decode(ctx, tm_k, tm_v, p, D, n_ctas);
-    if (st == MF_OK && app) ctx->note_append(k, v);
-    return st;
+    return launch_decode(ctx, tm_k, tm_v, p, D, n_ctas, app ? k : nullptr, app ? v : nullptr);
 }
 
 struct QLayout {
@@ -693,8 +691,8 @@ static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, con
     p.scale_log2 = a->scale * 1.4426950408889634f;
     // Streaming K/V ahead of the previous kernel's end is safe when nothing in flight writes these pools.
     // With the fused append this call is their only writer in this step; without it the caller says so
-    // (option value 2).  Not when the launch directly in front appended to these same pools (a one-layer
-    // model, two calls in a row on one cache): its new rows may not have landed yet.
+    // (option value 2).  Not when a launch that may still be in flight appended to these same pools (a
+    // one-layer model, two calls in a row on one cache): its new rows may not have landed yet.
     p.early_stream = (((ctx->overlap_launches && a->append) || ctx->overlap_launches == 2) &&
                       ctx->may_stream_early(c->k_pool, c->v_pool)) ? 1u : 0u;
     if (px) {
@@ -706,7 +704,15 @@ static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, con
             if (!px->recv[r] || !px->counters[r]) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "peer exchange: rank %u buffers", r);
             p.push_dst[r] = px->recv[r] + ((uint64_t)(step & 1) * px->world + px->rank) * block;
             p.push_cnt[r] = px->counters[r] + px->rank;
-            p.push_unit_cnt[r] = px->counters[r] + 8;
+            p.push_unit_cnt[r] = px->counters[r] + kPeerUnitCounters;
+        }
+        // ranks that only merge: their merge of step - 2 read the parity block this step overwrites
+        if (px->merge_only_mask >> px->rank & 1u)
+            return fail(ctx, MF_ERR_INVALID_OPERATION, "peer exchange: rank %u is in merge_only_mask and cannot push", px->rank);
+        if (px->merge_only_mask && step >= 2) {
+            p.push_wait_mask = px->merge_only_mask & ((1u << px->world) - 1u);
+            p.push_wait_expected = px->rows * (step - 1);
+            p.push_merged_local = px->counters[px->rank] + kPeerMergedBy;
         }
         if ((uint64_t)c->batch * a->n_heads != px->rows || D != px->head_dim)
             return fail(ctx, MF_ERR_INVALID_SHAPE, "peer exchange was created for %u rows x %u, this call has %llu x %u",
@@ -719,7 +725,7 @@ static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, con
             p.push_mask = merge_mask;
             p.push_expected = (uint32_t)__builtin_popcount(merge_mask) * (step + 1);
             p.push_local = px->recv[px->rank] + (uint64_t)(step & 1) * px->world * block;
-            p.push_local_cnt = px->counters[px->rank] + 8;
+            p.push_local_cnt = px->counters[px->rank] + kPeerUnitCounters;
         }
     }
     CUtensorMap tm_k, tm_v;
@@ -734,9 +740,7 @@ static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, con
         if ((st = get_tensor_map(ctx, c->k_pool, rows, D, box_rows, 64, &tm_k)) != MF_OK) return st;
         if ((st = get_tensor_map(ctx, c->v_pool, rows, D, box_rows, 64, &tm_v)) != MF_OK) return st;
     }
-    st = launch_decode(ctx, tm_k, tm_v, p, D, pl->n_ctas);
-    if (st == MF_OK && a->append) ctx->note_append(c->k_pool, c->v_pool);
-    return st;
+    return launch_decode(ctx, tm_k, tm_v, p, D, pl->n_ctas, a->append ? c->k_pool : nullptr, a->append ? c->v_pool : nullptr);
 }
 
 mf_status mf_paged_decode(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv *cache, const MfPagedDecodeArgs *args)

@@ -168,6 +168,30 @@ __device__ __forceinline__ void rope_pair(float xi, float xj, float c, float s, 
 // rank's receive buffer; with push_merge also wait (bounded) until every pushing rank has delivered
 // the same unit, merge the unit's query heads out of local memory (flash_prefill.metal:843-888)
 // and write the output rows.  Called by all consumer threads.
+// Sequence-sharded decode, before a CTA's first push of a launch: ranks that only merge never wait for
+// anybody, so this is what keeps a pusher from overwriting the parity block such a rank still reads.
+// Polls this rank's own memory (the merging rank counts its merged rows there), bounded.
+__device__ __forceinline__ void push_wait_for_mergers(const DecodeParams &p, uint32_t tid)
+{
+    if (tid == 0) {
+        const long long t0 = clock64();
+        for (uint32_t r = 0; r < 8; ++r) {
+            if (!(p.push_wait_mask >> r & 1u)) continue;
+            uint32_t spins = 0;
+            for (;;) {
+                uint32_t v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.push_merged_local + r) : "memory");
+                if ((int32_t)(v - p.push_wait_expected) >= 0) break;
+                if ((++spins & 0x3Fu) == 0 && clock64() - t0 > 4000000000ll) {
+                    atomicOr(p.status, kStatusPushWait);
+                    break;
+                }
+            }
+        }
+    }
+    named_bar_sync(2, kConsumerThreads);
+}
+
 template <int D>
 __device__ __forceinline__ void push_signal_and_merge(const DecodeParams &p, const WorkItem &it, uint32_t tid,
                                                       volatile uint32_t *flags)
@@ -276,9 +300,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     const uint32_t boxes_per_tile = kTileKeys / rows_per_box;
     const uint32_t rpb_log2 = 31 - __clz(rows_per_box);
 
-#ifdef MF_EXP_EARLY_TRIGGER
-    grid_launch_dependents();
-#endif
+    // Relaxed launches let the next launch of the stream be scheduled right away (it sets up, and its
+    // producer may stream its own K/V, while this grid works); strict ones do so only after their wait.
+    if (!p.strict_release) grid_launch_dependents();
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------ producer ---
         if (lane == 0) {
@@ -365,12 +389,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     // ---------------------------------------------------------------- consumers ---
     // q, the new k/v, the partial slots and tickets may all have been written by the previous launch.
     grid_dependency_wait();
-    // Only now may the next launch of the stream be scheduled (it sets up, and its producer may stream its
-    // own K/V, while this grid works).  Releasing it AFTER the wait is what bounds the overlap: the launch
-    // behind this one cannot start before every CTA here has seen the launch in front of this one complete,
-    // so never more than two launches of a stream are in flight, and the only launch whose writes an early
-    // K/V stream can race with is the one directly in front of it.
-    grid_launch_dependents();
+    // A strict launch releases its dependents only here: the launch behind it then cannot start before
+    // every CTA of this one has seen the launch in front complete, which is what bounds the set of launches
+    // an early K/V stream can race with.
+    if (p.strict_release) grid_launch_dependents();
+    if (p.push_wait_mask) push_wait_for_mergers(p, tid);
     float *comb = reinterpret_cast<float *>(smem + S::kOffComb);
     __half *q_s = reinterpret_cast<__half *>(smem + S::kOffQ);
     float *ml_s = reinterpret_cast<float *>(smem + S::kOffMl);
@@ -814,7 +837,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
 template <int D, int NT, int STAGES, int MINB>
 mf_status launch_one(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap &tm_v,
-                     const DecodeParams &p, uint32_t n_ctas)
+                     DecodeParams &p, uint32_t n_ctas, const void *writes_k, const void *writes_v)
 {
     using S = Smem<D, NT, STAGES>;
     static_assert(MINB * (S::kDynamic + 1024) <= 228 * 1024, "CTAs per SM do not fit shared memory");
@@ -828,6 +851,7 @@ mf_status launch_one(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap 
         configured[ctx->device] = true;
     }
     if (ctx->overlap_launches) {
+        p.strict_release = ctx->next_launch_strict() ? 1u : 0u;
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(n_ctas);
         cfg.blockDim = dim3(kThreads);
@@ -841,6 +865,7 @@ mf_status launch_one(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap 
         cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tm_k, tm_v, p);
         if (e != cudaSuccess) return fail(ctx, MF_ERR_CUDA, "launch decode_kernel: %s", cudaGetErrorString(e));
         ++ctx->launches;
+        ctx->note_programmatic_launch(p.strict_release != 0, writes_k, writes_v);
         return MF_OK;
     }
     kern<<<n_ctas, kThreads, S::kDynamic, ctx->stream>>>(tm_k, tm_v, p);
@@ -908,20 +933,21 @@ uint32_t decode_cta_target(uint32_t sm_count, uint32_t ctas_per_sm, uint64_t tot
 }
 
 mf_status launch_decode(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap &tm_v,
-                        const DecodeParams &p, uint32_t head_dim, uint32_t n_ctas)
+                        DecodeParams &p, uint32_t head_dim, uint32_t n_ctas, const void *writes_k,
+                        const void *writes_v)
 {
     const uint32_t nt = (p.group + 7) / 8;
     if (nt > 2) return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "decode: group size %u > 16", p.group);
     // Groups of up to 8 query heads: two CTAs per SM, each with a short ring, so that one CTA's
     // span boundary (combine, partial write, merge, q load) overlaps the other's tile stream.
     if (head_dim == 128) {
-        if (nt == 1 && ctx->decode_stages == 6) return launch_one<128, 1, 6, 1>(ctx, tm_k, tm_v, p, n_ctas);
-        return nt == 1 ? launch_one<128, 1, 3, 2>(ctx, tm_k, tm_v, p, n_ctas)
-                       : launch_one<128, 2, 5, 1>(ctx, tm_k, tm_v, p, n_ctas);
+        if (nt == 1 && ctx->decode_stages == 6) return launch_one<128, 1, 6, 1>(ctx, tm_k, tm_v, p, n_ctas, writes_k, writes_v);
+        return nt == 1 ? launch_one<128, 1, 3, 2>(ctx, tm_k, tm_v, p, n_ctas, writes_k, writes_v)
+                       : launch_one<128, 2, 5, 1>(ctx, tm_k, tm_v, p, n_ctas, writes_k, writes_v);
     }
     if (head_dim == 64) {
-        return nt == 1 ? launch_one<64, 1, 6, 2>(ctx, tm_k, tm_v, p, n_ctas)
-                       : launch_one<64, 2, 8, 1>(ctx, tm_k, tm_v, p, n_ctas);
+        return nt == 1 ? launch_one<64, 1, 6, 2>(ctx, tm_k, tm_v, p, n_ctas, writes_k, writes_v)
+                       : launch_one<64, 2, 8, 1>(ctx, tm_k, tm_v, p, n_ctas, writes_k, writes_v);
     }
     return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "Flash Decode only supports head_dim=64 or 128, got %u",
                 head_dim);

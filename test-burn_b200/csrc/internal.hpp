@@ -22,6 +22,12 @@ constexpr uint32_t kMaxUniformUnits = kCounterRegionBytes / 4;
 // (the lower bits record barrier waits that ran out).
 constexpr uint32_t kStatusBadPage = 4096u;
 
+// Word offsets inside a rank's peer-exchange counter block: per-source totals, "merged by rank" counts,
+// per-unit arrival counters.
+constexpr uint32_t kPeerMergedBy = 8;
+constexpr uint32_t kPeerUnitCounters = 16;
+constexpr uint32_t kStatusPushWait = 8192u;  // a pusher gave up waiting for a merge-only rank to free its block
+
 // One span of KV tiles of one (sequence, kv head) unit, processed by one CTA.
 struct WorkItem {
     uint32_t seq;
@@ -67,6 +73,7 @@ struct DecodeParams {
     uint32_t knew_stride_b;  // elements between sequences in k_new / v_new
     uint32_t whole_rows;     // 1: one TMA box per page fetches both halves (3-D tensor map)
     uint32_t early_stream;   // 1: the producer may stream K/V before the previous kernel has finished
+    uint32_t strict_release; // 1: dependents are released after this grid's own dependency wait, not at its start
     // Push mode (sequence-sharded decode): the finished (acc, m, l) of every unit is stored straight
     // into each rank's receive block over NVLink and announced on that rank's arrival counter.
     uint32_t push_world;     // 0 = off
@@ -79,6 +86,12 @@ struct DecodeParams {
     uint32_t push_expected;  // value the unit counter reaches when all of them have
     const float *push_local; // this rank's receive blocks of this step parity: [world][block]
     const uint32_t *push_local_cnt;  // this rank's per-unit arrival counters
+    // Back-pressure of ranks that only merge (they never wait for anybody, so nothing else keeps a pusher
+    // from overwriting the parity block they still read): before this launch's first push, wait until every
+    // rank of push_wait_mask has counted push_wait_expected merged rows on this rank's "merged by" words.
+    uint32_t push_wait_mask;
+    uint32_t push_wait_expected;
+    const uint32_t *push_merged_local;
     float scale_log2;
 };
 
@@ -122,28 +135,49 @@ struct MfContext {
     std::unordered_map<mf::TensorMapKey, CUtensorMap, mf::TensorMapKeyHash> tmaps;
     void *encode_fn = nullptr;
     uint32_t overlap_launches = 0;  // MF_OPTION_OVERLAP_LAUNCHES
-    // Early K/V streaming under programmatic dependent launches.  Every kernel of this library that
-    // releases its dependents before it ends (decode_kernel, fused_qkv_kernel, merge_pushed_kernel) does so
-    // only after its own dependency wait has returned, and that wait returns only when the launch in front
-    // has completed (which, by the same rule, had waited for the one in front of it).  So when a launch
-    // starts, every launch but the one directly in front of it has completed: the caches written by that
-    // one launch are the only ones a producer must not read before its own wait.  `launches` counts every
-    // launch made through the context; an appending decode launch records the caches it writes together
-    // with the count after it, and the next launch may stream a cache early unless it is that cache and no
-    // other launch of this context has come between.  (A launch the count misses only makes the answer
-    // "wait", the safe one.)
-    const void *appended_k = nullptr, *appended_v = nullptr;
-    uint64_t appended_at = ~0ull;
+    // Early K/V streaming under programmatic dependent launches, and what bounds it.
+    //
+    // A kernel launched with the programmatic attribute may start as soon as every CTA of the launch in
+    // front of it has released its dependents (or exited).  Every such kernel of this library
+    // (decode_kernel, fused_qkv_kernel, merge_pushed_kernel) takes a flag: RELAXED launches release at their
+    // very start, STRICT launches only after their own dependency wait has returned - and that wait returns
+    // only when the launch in front has completed, which in turn had waited for the one before it.
+    // Claim: when launch m starts, every launch still in flight lies in {s, ..., m-1}, s being the last
+    // strict launch before m.  (If m-1 is strict, all its CTAs saw m-2 complete before m could start.  If
+    // m-1 is relaxed, m starting only shows that m-1 has started; whatever bound held at m-1's start still
+    // holds, and s is the same for both.)  A launch made without the attribute starts after everything
+    // before it has completed, so it can only shrink that set.
+    // The context therefore keeps the caches written by the launches since the last strict one (at most
+    // kWindow of them: every kWindow-th launch with the attribute is made strict) and a decode launch may
+    // stream a cache ahead of its own wait only if that cache is not in the list.  The decision is exact in
+    // the sense that it follows from the launch protocol alone, not from grid sizes or timing.
+    static constexpr int kWindow = 8;
+    const void *inflight_k[kWindow] = {}, *inflight_v[kWindow] = {};
+    int n_inflight = 0;      // entries of the list
+    int since_strict = 0;    // launches with the attribute after the last strict one
     bool may_stream_early(const void *k_cache, const void *v_cache) const
     {
-        if (appended_at != launches) return true;
-        return k_cache != appended_k && k_cache != appended_v && v_cache != appended_k && v_cache != appended_v;
+        for (int i = 0; i < n_inflight; ++i)
+            if (k_cache == inflight_k[i] || k_cache == inflight_v[i] || v_cache == inflight_k[i] || v_cache == inflight_v[i])
+                return false;
+        return true;
     }
-    void note_append(const void *k_cache, const void *v_cache)
+    // Whether the next launch with the attribute has to be strict.
+    bool next_launch_strict() const { return since_strict + 1 >= kWindow; }
+    // After such a launch succeeded; k_cache / v_cache: what it writes (null: no cache).
+    void note_programmatic_launch(bool strict, const void *k_cache, const void *v_cache)
     {
-        appended_k = k_cache;
-        appended_v = v_cache;
-        appended_at = launches;
+        if (strict) {
+            n_inflight = 0;
+            since_strict = 0;
+        } else {
+            ++since_strict;
+        }
+        if ((k_cache || v_cache) && n_inflight < kWindow) {
+            inflight_k[n_inflight] = k_cache;
+            inflight_v[n_inflight] = v_cache;
+            ++n_inflight;
+        }
     }
     uint32_t decode_stages = 0;     // MF_OPTION_DECODE_STAGES (0 = default)
     uint32_t prefill_impl = 0;      // MF_OPTION_PREFILL_IMPL: 0 auto, 1 mma.sync, 2 tcgen05 only
@@ -212,7 +246,9 @@ UniformSplit uniform_split(uint32_t units, uint32_t tiles_per_unit, uint32_t n_s
 uint32_t decode_cta_target(uint32_t sm_count, uint32_t ctas_per_sm, uint64_t total_tiles);
 
 // Launchers (decode.cu, prefill.cu, kv_append.cu).
+// writes_k / writes_v: the caches this launch appends to (null when it only reads).
 mf_status launch_decode(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap &tm_v,
-                        const DecodeParams &p, uint32_t head_dim, uint32_t n_ctas);
+                        DecodeParams &p, uint32_t head_dim, uint32_t n_ctas, const void *writes_k = nullptr,
+                        const void *writes_v = nullptr);
 
 }  // namespace mf

@@ -205,6 +205,7 @@ struct QkvParams {
     uint32_t rows_per_cta;  // input rows staged per CTA, at most 8
     float eps;
     uint32_t append;
+    uint32_t strict_release;  // 1: dependents are released after the dependency wait, not at the start
 };
 
 constexpr uint32_t kQkvRows = 8;   // the n side of the mma
@@ -297,6 +298,7 @@ __global__ void __launch_bounds__(256, 2) fused_qkv_kernel(const QkvParams qp, c
     };
 
     QKV_STAMP(0)
+    if (!qp.strict_release) grid_launch_dependents();
     // The weights are constants: the first 64 KB of them are requested before the grid waits for the
     // kernel in front of it (under a programmatic dependent launch they travel during its tail) and
     // keep arriving while the input rows are staged and normalised.
@@ -306,9 +308,8 @@ __global__ void __launch_bounds__(256, 2) fused_qkv_kernel(const QkvParams qp, c
     fetch(cur, sd, 0);
     fetch(nxt, sd, 1);
     grid_dependency_wait();  // from here on: reads of what that kernel may have produced, and writes
-    // The next launch of the stream is released only after this wait, so that at most two launches
-    // are ever in flight (the bound the decode kernel's early K/V stream relies on).
-    grid_launch_dependents();
+    // a strict launch releases the next one only now (the bound the decode kernel's early K/V stream relies on)
+    if (qp.strict_release) grid_launch_dependents();
     const uint32_t vecs = K / 8;
     __half *gs = xs + (size_t)qp.rows_per_cta * xstride;  // gamma, staged once
     for (uint32_t b = 0; b < rows; ++b)
@@ -792,13 +793,15 @@ static mf_status launch_fused_qkv(MfContext *ctx, const MfFusedQkvArgs *a, uint3
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.numAttrs = 1;
+        qp.strict_release = ctx->next_launch_strict() ? 1u : 0u;
     }
     const cudaError_t e = cudaLaunchKernelEx(&cfg, fused_qkv_kernel, qp, app);
     if (e != cudaSuccess) return fail(ctx, MF_ERR_CUDA, "launch fused_qkv_kernel: %s", cudaGetErrorString(e));
     ++ctx->launches;
-    // this kernel releases its dependents before it ends: a decode launch right behind it must not
-    // stream the caches it is writing ahead of its own dependency wait
-    if (ap && ctx->overlap_launches) ctx->note_append(ap->k_cache, ap->v_cache);
+    // this kernel releases its dependents before it ends: a decode launch behind it must not stream the
+    // caches it is writing ahead of its own dependency wait
+    if (ctx->overlap_launches)
+        ctx->note_programmatic_launch(qp.strict_release != 0, ap ? ap->k_cache : nullptr, ap ? ap->v_cache : nullptr);
     return MF_OK;
 }
 

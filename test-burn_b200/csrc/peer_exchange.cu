@@ -9,9 +9,10 @@
 namespace mf {
 namespace {
 
-// Counter region in front of the receive blocks: 8 per-source totals, then one counter per unit
-// (units <= rows), padded so that the floats stay 256-byte aligned.
-inline size_t counter_bytes(uint32_t rows) { return ((size_t)(8 + rows) * 4 + 255) & ~(size_t)255; }
+// Counter region in front of the receive blocks: 8 per-source totals, 8 "merged by rank m" counts
+// (the back-pressure of ranks that only merge), then one counter per unit (units <= rows), padded so
+// that the floats stay 256-byte aligned.
+inline size_t counter_bytes(uint32_t rows) { return ((size_t)(kPeerUnitCounters + rows) * 4 + 255) & ~(size_t)255; }
 
 struct PushedMergeArgs {
     const float *gather;       // this rank's receive buffer, parity already applied: [world][block]
@@ -20,6 +21,10 @@ struct PushedMergeArgs {
     uint32_t world, rows, head_dim;
     uint64_t block;            // floats per source rank
     uint32_t *status;
+    // A rank that only merges tells the pushers when it is done with a step's blocks: one count per
+    // merged row on every other rank's "merged by" word for this rank (null = this rank also pushes).
+    uint32_t *merged_dst[8];
+    uint32_t strict_release;  // 1: dependents are released after the dependency wait, not at the start
 };
 
 // Merge of pushed partials: wait (bounded) for every source rank, then the log-sum-exp merge
@@ -31,6 +36,7 @@ __global__ void __launch_bounds__(128) merge_pushed_kernel(const PushedMergeArgs
     // Launched as a programmatic dependent of this rank's decode kernel, so it may be resident
     // while that kernel still runs (all of whose CTAs are resident by then, so it cannot be starved).
     // The arrival counters are the real dependency.
+    if (!a.strict_release) grid_launch_dependents();
     if (threadIdx.x == 0) {
         uint32_t good = 1;
         const long long t0 = clock64();
@@ -54,8 +60,7 @@ __global__ void __launch_bounds__(128) merge_pushed_kernel(const PushedMergeArgs
     __syncthreads();
     // everything earlier in this stream has finished and is visible before out is written
     grid_dependency_wait();
-    // the next launch is released only after the wait: at most two launches of a stream are in flight
-    grid_launch_dependents();
+    if (a.strict_release) grid_launch_dependents();
     if (!ok) return;
     const uint32_t D = a.head_dim;
     float mx = -1e30f;
@@ -77,6 +82,8 @@ __global__ void __launch_bounds__(128) merge_pushed_kernel(const PushedMergeArgs
         }
         out[(size_t)row * D + d] = __float2half_rn(acc * inv);
     }
+    __syncthreads();  // every thread of the block has consumed what it read from the receive blocks
+    if (threadIdx.x < a.world && a.merged_dst[threadIdx.x]) atomicAdd_system(a.merged_dst[threadIdx.x], 1u);
 }
 
 }  // namespace
@@ -158,6 +165,9 @@ mf_status mf_merge_pushed(MfContext *ctx, const MfPeerExchange *px, const uint32
     if (px->world == 0 || px->world > 8 || px->rank >= px->world)
         return fail(ctx, MF_ERR_INVALID_OPERATION, "peer exchange: rank %u of %u", px->rank, px->world);
     if (rows == 0 || head_dim == 0) return MF_OK;
+    if (rows != px->rows || head_dim != px->head_dim)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "merge pushed: the exchange was created for %u rows x %u, this call has %u x %u",
+                    px->rows, px->head_dim, rows, head_dim);
     PushedMergeArgs a{};
     a.block = (uint64_t)rows * (head_dim + 2);
     a.gather = px->recv[px->rank] + (uint64_t)(step & 1) * px->world * a.block;
@@ -167,7 +177,15 @@ mf_status mf_merge_pushed(MfContext *ctx, const MfPeerExchange *px, const uint32
     a.head_dim = head_dim;
     a.status = ctx->d_status;
     for (uint32_t r = 0; r < px->world; ++r) a.expected[r] = units_per_rank[r] * (step + 1);
+    if (px->merge_only_mask >> px->rank & 1u) {
+        if (units_per_rank[px->rank])
+            return fail(ctx, MF_ERR_INVALID_OPERATION, "merge pushed: rank %u is in merge_only_mask but pushes %u units",
+                        px->rank, units_per_rank[px->rank]);
+        for (uint32_t r = 0; r < px->world; ++r)
+            if (r != px->rank && px->counters[r]) a.merged_dst[r] = px->counters[r] + kPeerMergedBy + px->rank;
+    }
     if (ctx->overlap_launches) {
+        a.strict_release = ctx->next_launch_strict() ? 1u : 0u;
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(rows);
         cfg.blockDim = dim3(128);
@@ -180,6 +198,7 @@ mf_status mf_merge_pushed(MfContext *ctx, const MfPeerExchange *px, const uint32
         cudaError_t e = cudaLaunchKernelEx(&cfg, merge_pushed_kernel, a, static_cast<__half *>(out));
         if (e != cudaSuccess) return fail(ctx, MF_ERR_CUDA, "launch merge_pushed_kernel: %s", cudaGetErrorString(e));
         ++ctx->launches;
+        ctx->note_programmatic_launch(a.strict_release != 0, nullptr, nullptr);
         return MF_OK;
     }
     merge_pushed_kernel<<<rows, 128, 0, ctx->stream>>>(a, static_cast<__half *>(out));

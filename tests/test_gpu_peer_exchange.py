@@ -176,3 +176,53 @@ def test_pushed_partials_two_gpus():
         ret = mgr.dict()
         mp.spawn(_two_gpu_worker, args=(world, port, ret), nprocs=world, join=True)
         assert dict(ret) == {0: True, 1: True}
+
+
+def test_a_rank_that_only_merges_holds_the_pushers_back(mfk, foundry):
+    """Rank 1 holds no keys: it never pushes, it only merges what rank 0 pushes to it.  Nothing in the
+    pushers' own hand-shake waits for such a rank, so it is named in merge_only_mask: it counts the rows
+    it has merged on the pusher's side, and the pusher's kernel of step s >= 2 waits for its merge of
+    step s - 2 before overwriting that parity block.  Both ranks are emulated on one GPU in one stream,
+    so the merging rank runs "on time" in the first part; in the second it skips a merge and the
+    pusher's bounded wait runs out with a Timeout status instead of overwriting (or hanging)."""
+    import torch
+
+    Hq, Hkv, D, P, L = 24, 8, 128, 64, 1000
+    full = PagedCase(batch=1, n_heads=Hq, n_kv_heads=Hkv, head_dim=D, page_size=P, cached=[L - 1], poison=False)
+    q_ref, kp, vp, out_ref, gold = full.oracle_step()
+    dk, dv, q_rot = dev(kp), dev(vp), dev(q_ref)
+    n_pages = full.page_table.shape[1]
+    pxs = [foundry.peer_exchange_create(2, r, Hq, D)[0] for r in range(2)]
+    for r in range(2):
+        o = 1 - r
+        pxs[r].recv[o], pxs[r].counters[o] = pxs[o].recv[o], pxs[o].counters[o]
+        pxs[r].merge_only_mask = 0b10
+    desc, plan, keep = _shard_inputs(mfk, foundry, full, dk, dv, 0, n_pages, L)
+    units = [Hkv, 0]
+    for step in range(5):
+        outs = [torch.full((Hq, D), float("nan"), dtype=torch.float16, device="cuda") for _ in range(2)]
+        foundry.paged_decode_partial_push(plan, desc, q_rot, pxs[0], step, n_heads=Hq, scale=float(full.scale))
+        for r in range(2):
+            foundry.merge_pushed(pxs[r], units, step, Hq, D, outs[r])
+        foundry.synchronize()
+        for o in outs:
+            assert max_abs(host(o), out_ref) <= TOL and max_abs(host(o), gold.ravel()) <= TOL
+    # the merging rank falls behind: steps 5 and 6 are pushed, rank 1 merges neither; the push of step 7
+    # would overwrite the block of step 5 that rank 1 has not read yet
+    for step in (5, 6, 7):
+        foundry.paged_decode_partial_push(plan, desc, q_rot, pxs[0], step, n_heads=Hq, scale=float(full.scale))
+        out0 = torch.zeros((Hq, D), dtype=torch.float16, device="cuda")
+        foundry.merge_pushed(pxs[0], units, step, Hq, D, out0)
+        if step < 7:
+            foundry.synchronize()
+    with pytest.raises(mfk.MetalError) as e:
+        foundry.synchronize()
+    assert e.value.kind == "Timeout"
+    with pytest.raises(mfk.MetalError):  # a rank named as merge-only cannot push
+        foundry.paged_decode_partial_push(plan, desc, q_rot, pxs[1], 8, n_heads=Hq, scale=float(full.scale))
+    foundry.synchronize()
+    plan.close()
+    for r in range(2):
+        o = 1 - r
+        pxs[r].recv[o] = pxs[r].counters[o] = None
+        foundry.peer_exchange_destroy(pxs[r])

@@ -166,3 +166,96 @@ def test_decode_plan_cuts_units_separately_when_the_launch_is_short(mfk, lens, n
         assert all(items[i, 6] == len(cov) for i in range(len(items)) if items[i, 5] == unit)
     # longest range within one tile of the ideal
     assert max(items[:, 3] - items[:, 2]) <= -(-int(tiles.sum()) * n_kv_heads // n_ctas) + 1
+
+
+def _ctx_cfg(mfk, model_max, override=0, env_cap=0, full_reserve=0, budget_mb=-1):
+    cfg = mfk.MfContextConfig()
+    assert mfk.lib.mf_context_config_from_architecture(model_max, override, env_cap, full_reserve, budget_mb, C.byref(cfg)) == 0
+    return cfg
+
+
+def test_context_config_priority_known_answers(mfk):
+    """test_context_config_priority (src/model/context.rs:288-305) and the rules of from_architecture (:105-152)."""
+    assert _ctx_cfg(mfk, 4096).max_context_len == 4096                      # 1. defaults to the model max
+    assert _ctx_cfg(mfk, 4096, override=2048).max_context_len == 2048       # 2. the caller's value is a cap
+    assert _ctx_cfg(mfk, 4096, env_cap=1024).max_context_len == 1024        # 3. so is the environment's
+    assert _ctx_cfg(mfk, 4096, override=2048, env_cap=1024).max_context_len == 2048  # the caller's wins over the env
+    assert _ctx_cfg(mfk, 4096, override=100000).max_context_len == 4096     # never beyond the model
+    assert _ctx_cfg(mfk, 0, override=3000).max_context_len == 3000          # no model max: the cap
+    assert _ctx_cfg(mfk, 0).max_context_len == 2048                         # neither: 2048
+    c = _ctx_cfg(mfk, 32768)
+    assert (c.allocated_capacity, c.full_reserve, c.budget_bytes) == (2048, 0, 0) and abs(c.budget_auto_pct - 0.5) < 1e-7
+    assert _ctx_cfg(mfk, 1000).allocated_capacity == 1024                   # align(min(2048, max))
+    assert _ctx_cfg(mfk, 32768, full_reserve=1).allocated_capacity == 32768
+    c = _ctx_cfg(mfk, 32768, budget_mb=64)
+    assert c.budget_bytes == 64 << 20 and c.budget_auto_pct == 0.0
+
+
+def test_context_config_reads_the_reference_environment(mfk, monkeypatch):
+    monkeypatch.setenv("METALLIC_MAX_CONTEXT_LEN", " 1024 ")  # trimmed, as the reference does (:107-109)
+    monkeypatch.setenv("METALLIC_FULL_CONTEXT_RESERVE", "1")
+    monkeypatch.setenv("METALLIC_KV_MEMORY_BUDGET_MB", "8")
+    cfg = mfk.MfContextConfig()
+    assert mfk.lib.mf_context_config_from_env(4096, 0, C.byref(cfg)) == 0
+    assert (cfg.max_context_len, cfg.allocated_capacity, cfg.full_reserve, cfg.budget_bytes) == (1024, 1024, 1, 8 << 20)
+    monkeypatch.setenv("METALLIC_MAX_CONTEXT_LEN", "not a number")  # parse failure = unset
+    monkeypatch.delenv("METALLIC_FULL_CONTEXT_RESERVE")
+    assert mfk.lib.mf_context_config_from_env(4096, 0, C.byref(cfg)) == 0
+    assert (cfg.max_context_len, cfg.allocated_capacity, cfg.full_reserve) == (4096, 2048, 0)
+
+
+def test_apply_memory_budget(mfk):
+    """apply_memory_budget (src/model/context.rs:158-210): budget / per_token_bytes, aligned to 128, floor of 1."""
+    per_token = mfk.lib.mf_kv_per_token_bytes_f16(28, 8, 128)  # Llama-3.2-3B compact: 114 688 B per token
+    assert per_token == 28 * 2 * 8 * 128 * 2
+    cfg = _ctx_cfg(mfk, 131072, full_reserve=1, budget_mb=1024)  # 1 GiB / 114 688 = 9362 tokens -> 9472
+    assert mfk.lib.mf_apply_memory_budget(C.byref(cfg), 0, per_token) == 0
+    assert (cfg.max_context_len, cfg.allocated_capacity) == (9472, 9472)
+    cfg = _ctx_cfg(mfk, 8192, budget_mb=1024)                    # the budget allows more than the model: unchanged
+    mfk.lib.mf_apply_memory_budget(C.byref(cfg), 0, per_token)
+    assert (cfg.max_context_len, cfg.allocated_capacity) == (8192, 2048)
+    cfg = _ctx_cfg(mfk, 8192)                                    # Auto 50 % of the device figure
+    mfk.lib.mf_apply_memory_budget(C.byref(cfg), 2 * 4096 * per_token, per_token)
+    assert (cfg.max_context_len, cfg.allocated_capacity) == (4096, 2048)
+    cfg = _ctx_cfg(mfk, 8192, budget_mb=0)                       # a zero budget changes nothing (:186-188)
+    mfk.lib.mf_apply_memory_budget(C.byref(cfg), 0, per_token)
+    assert cfg.max_context_len == 8192
+    cfg = _ctx_cfg(mfk, 8192)                                    # too small for one token: pinned to 1 / 128
+    mfk.lib.mf_apply_memory_budget(C.byref(cfg), per_token, per_token)  # 50 % of one token
+    assert (cfg.max_context_len, cfg.allocated_capacity) == (1, 128)
+
+
+def test_kv_geometry_known_answers(mfk):
+    """kv_geometry_compact_defaults_for_gqa (src/model/kv_geometry.rs:221-230) and the clamps of :26-36."""
+    g = mfk.MfKvGeometry()
+    assert mfk.lib.mf_kv_geometry_from_architecture(24, 8, 3072, C.byref(g)) == 0
+    assert (g.layout, g.n_heads, g.n_kv_heads, g.group_size, g.head_dim, g.cache_heads) == (
+        mfk.KV_LAYOUT_COMPACT_KV_HEADS, 24, 8, 3, 128, 8)
+    mfk.lib.mf_kv_geometry_from_architecture(8, 0, 512, C.byref(g))    # no kv head count: MHA, expanded
+    assert (g.n_kv_heads, g.group_size, g.layout, g.cache_heads) == (8, 1, 0, 8)
+    mfk.lib.mf_kv_geometry_from_architecture(8, 16, 512, C.byref(g))   # clamped to n_heads
+    assert g.n_kv_heads == 8
+    mfk.lib.mf_kv_geometry_from_architecture(14, 4, 896, C.byref(g))   # does not divide: group 1
+    assert (g.group_size, g.layout, g.cache_heads) == (1, 1, 4)
+
+
+def test_kv_geometry_from_cache_tensor(mfk):
+    """from_cache_tensor (src/model/kv_geometry.rs:92-150): layout from the head count, four refusals."""
+    def tensor(dims, dtype=0):
+        t = mfk.MfTensor()
+        t.dev_ptr, t.offset_bytes, t.dtype, t.rank = 0x1000, 0, dtype, len(dims)
+        for i, d in enumerate(dims):
+            t.dims[i] = d
+        return t
+
+    g, err = mfk.MfKvGeometry(), C.create_string_buffer(256)
+    call = lambda t, cap=8192: mfk.lib.mf_kv_geometry_from_cache_tensor(24, 8, 3072, C.byref(t), cap, C.byref(g), err, 256)
+    assert call(tensor([8, 8192, 128])) == 0 and (g.layout, g.cache_heads) == (1, 8)
+    assert call(tensor([24, 8192, 128])) == 0 and (g.layout, g.cache_heads) == (0, 24)
+    INVALID_SHAPE = 2
+    assert call(tensor([8, 8192, 128], dtype=1)) == INVALID_SHAPE and b"must be F16" in err.value
+    assert call(tensor([8, 8192])) == INVALID_SHAPE and b"rank-3" in err.value
+    assert call(tensor([8, 4096, 128])) == INVALID_SHAPE and err.value == b"KV cache capacity mismatch: got 4096, expected 8192"
+    assert call(tensor([8, 8192, 64])) == INVALID_SHAPE and err.value == b"KV cache head_dim mismatch: got 64, expected 128"
+    assert call(tensor([12, 8192, 128])) == INVALID_SHAPE
+    assert err.value == b"KV cache heads mismatch: got 12, expected 24 (expanded) or 8 (compact)"
