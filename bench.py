@@ -46,8 +46,6 @@ WORKLOADS = {
                     "ctx U[512,16384], page 16, fused rope+append+decode"),
     "c3-small": dict(layers=4, n_heads=16, n_kv_heads=2, head_dim=128, batch=64, lo=512, hi=16384, page_size=16,
                      theta=1e6, rope_mode=0, name="c3 with 4 layers (profiling case)"),
-    "uniform148": dict(layers=4, n_heads=16, n_kv_heads=2, head_dim=128, batch=74, lo=8191, hi=8191, page_size=16,
-                       theta=1e6, rope_mode=0, name="experiment: 148 equal (sequence, kv head) units of 8192 keys"),
     "c2-paged": dict(layers=28, n_heads=24, n_kv_heads=8, head_dim=128, batch=1, lo=8191, hi=8191, page_size=64,
                      theta=5e5, rope_mode=1,
                      name="Llama-3.2-3B shape decode step: 28 layers, 24q/8kv heads, D128, batch 1, ctx 8192, "
@@ -64,9 +62,9 @@ LONG_CONTEXT = {
 }
 SEED = 0x5EED
 METRIC = "kv_append_decode_attn_tokens_per_s"
-# DRAM bytes moved by the decode kernel per algorithmic byte, from the ncu capture summarised in
-# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the same launch).
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0072  # profiles/decode_kernel_c3_paged_decode.md
+# DRAM bytes moved by the decode kernel per algorithmic byte: dram__bytes_read.sum + dram__bytes_write.sum of
+# one ncu capture of a 4-layer C3 step over the algorithmic bytes of the same launch.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0072
 
 
 def measured_peak_gbs():
@@ -90,7 +88,7 @@ def make_page_table(w, kv_lens, seed):
     pages = (kv_lens + P - 1) // P
     n_pages = int(pages.sum())
     rng = np.random.default_rng(seed + 1)
-    shuffle = w["batch"] > 1 and not w.get("sequential")
+    shuffle = w["batch"] > 1
     perm = rng.permutation(n_pages).astype(np.uint32) if shuffle else np.arange(n_pages, dtype=np.uint32)
     stride = int(pages.max())
     table = np.zeros((w["batch"], stride), np.uint32)
@@ -217,8 +215,6 @@ def run_ours(args, w):
     f = mfk.Foundry(dev.index, stream.cuda_stream)
     if not args.no_overlap:
         f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 1)
-    if args.stages:
-        f.set_option(2, args.stages)
     plan = f.decode_plan(kv_lens, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P)
     descs = [mfk.paged_kv(k_pools[i].view(n_pages, hkv, P, d), v_pools[i].view(n_pages, hkv, P, d), d_table, d_lens,
                           n_kv_heads=hkv, page_size=P, head_dim=d) for i in range(layers)]
@@ -619,8 +615,6 @@ def run_prefill(args):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     stream = torch.cuda.Stream(device=dev)
     f = mfk.Foundry(local, stream.cuda_stream)
-    if args.prefill_impl:
-        f.set_option(3, args.prefill_impl)
     p = mfk.KvPrepFusedParamsResolved(hq * d, hkv * d, d, hq, hkv, hq // hkv, m, cached, cap, hq * m * d, 1, 0, 0)
     desc = None
     if args.page_size:
@@ -983,10 +977,8 @@ def main():
     ap.add_argument("--projection", action="store_true",
                     help="c1 / c2: start each layer from the hidden state (RMSNorm + fused QKV projection + RoPE + append "
                          "in one launch) instead of from q, k, v")
-    ap.add_argument("--prefill-impl", type=int, default=0, help="prefill kernel selector (experiments)")
-    ap.add_argument("--stages", type=int, default=0, help="decode ring depth (experiments)")
-    ap.add_argument("--page-size", type=int, default=0, help="override the workload's page size (experiments); c4: prefill into a paged cache with pages of this many rows")
-    ap.add_argument("--sequential-pages", action="store_true", help="identity page table (experiments)")
+    ap.add_argument("--page-size", type=int, default=0,
+                    help="c4 only: prefill into a paged cache with pages of this many rows (default: contiguous cache)")
     args = ap.parse_args()
     if args.impl == "reference" and args.workload not in WORKLOADS:
         sys.stderr.write("--impl reference times the batched paged decode workloads (%s) only; %s has no CPU arm\n"
@@ -999,12 +991,6 @@ def main():
     if args.workload in LONG_CONTEXT:
         return run_long_context(args, LONG_CONTEXT[args.workload])
     w = dict(WORKLOADS[args.workload])
-    if args.page_size:
-        w["page_size"] = args.page_size
-        w["name"] += " [page size %d]" % args.page_size
-    if args.sequential_pages:
-        w["sequential"] = True
-        w["name"] += " [sequential pages]"
     if args.impl == "reference":
         return run_reference(args, w)
     return run_ours(args, w)

@@ -36,25 +36,9 @@ constexpr uint32_t kThreads = kConsumerThreads + 32;
 constexpr float kNegSentinel = -1e30f;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per barrier wait
 constexpr float kLn2 = 0.6931471805599453f;
-#ifndef MF_MERGE_FLIGHT
-#define MF_MERGE_FLIGHT 20
-#endif
-constexpr uint32_t kMergeFlight = MF_MERGE_FLIGHT;  // partials whose loads are in flight together in the merge
+constexpr uint32_t kMergeFlight = 20;  // partials whose loads are in flight together in the merge
 constexpr uint32_t kMergeFlightFew = 8;                // ... for units cut in at most this many parts
 
-#ifdef MF_DEC_PROFILE
-// Development aid (build with -DMF_DEC_PROFILE): global-timer stamps of one consumer thread per CTA.
-__device__ unsigned long long g_dec_prof[512 * 8];
-__device__ __forceinline__ unsigned long long dec_now()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define DEC_STAMP(k) { if (tid == 0 && blockIdx.x < 512) g_dec_prof[blockIdx.x * 8 + (k)] = dec_now(); }
-#else
-#define DEC_STAMP(k)
-#endif
 
 template <int D, int NT, int STAGES>
 struct Smem {
@@ -468,7 +452,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             for (int mt = 0; mt < D / 16; ++mt) o[nt][mt][0] = o[nt][mt][1] = o[nt][mt][2] = o[nt][mt][3] = 0.f;
         }
 
-        DEC_STAMP(2)
         for (uint32_t t = it.tile_begin; t < it.tile_end; ++t) {
             if (!flags[0] && !mbar_wait_bounded(bar_full + stage * 8, phase, kWaitLimitNs)) {
                 flags[0] = 1;
@@ -622,7 +605,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             }
         }
 
-        DEC_STAMP(3)
         // ---- combine the four warps' states ------------------------------------------
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -726,7 +708,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         }
 
         // ---- ticket: the CTA that completes the unit merges its partials ---------------
-        DEC_STAMP(4)
         __threadfence();
         named_bar_sync(1, kConsumerThreads);
         if (tid == 0) {
@@ -736,7 +717,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             flags[1] = last;
         }
         named_bar_sync(2, kConsumerThreads);
-        DEC_STAMP(5)
         if (!flags[1]) continue;
         __threadfence();
         // Merge (flash_prefill.metal:843-888), arranged so that the loads of one round trip are all
@@ -831,7 +811,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             }
         }
         if (p.push_world) push_signal_and_merge<D>(p, it, tid, flags);
-        DEC_STAMP(6)
     }
 }
 
@@ -874,12 +853,6 @@ mf_status launch_one(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap 
 
 }  // namespace
 
-#ifdef MF_DEC_PROFILE
-extern "C" __attribute__((visibility("default"))) int mf_debug_dec_profile(unsigned long long *host_out, uint32_t n)
-{
-    return (int)cudaMemcpyFromSymbol(host_out, g_dec_prof, sizeof(unsigned long long) * n);
-}
-#endif
 
 uint32_t decode_ctas_per_sm(const MfContext *ctx, uint32_t head_dim, uint32_t group)
 {

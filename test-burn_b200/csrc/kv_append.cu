@@ -227,19 +227,6 @@ __device__ __forceinline__ void cp_async_wait_all()
     asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
 
-#ifdef MF_QKV_PROFILE
-// Development aid (build with -DMF_QKV_PROFILE): global-timer stamps of thread 0 of each CTA.
-__device__ unsigned long long g_qkv_prof[512 * 8];
-__device__ __forceinline__ unsigned long long qkv_now()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define QKV_STAMP(k) { if (tid == 0 && blockIdx.x < 512 && blockIdx.y == 0) g_qkv_prof[blockIdx.x * 8 + (k)] = qkv_now(); }
-#else
-#define QKV_STAMP(k)
-#endif
 
 // What a CTA needs to know about one slab (chunk pair j of head slot `slot`).
 struct QkvSlab {
@@ -297,7 +284,6 @@ __global__ void __launch_bounds__(256, 2) fused_qkv_kernel(const QkvParams qp, c
         }
     };
 
-    QKV_STAMP(0)
     if (!qp.strict_release) grid_launch_dependents();
     // The weights are constants: the first 64 KB of them are requested before the grid waits for the
     // kernel in front of it (under a programmatic dependent launch they travel during its tail) and
@@ -317,9 +303,7 @@ __global__ void __launch_bounds__(256, 2) fused_qkv_kernel(const QkvParams qp, c
             cp_async_16(xs + (size_t)b * xstride + 8 * i, qp.x + (size_t)(row0 + b) * K + 8 * i);
     if (qp.gamma)
         for (uint32_t i = tid; i < vecs; i += 256) cp_async_16(gs + 8 * i, qp.gamma + 8 * i);
-    QKV_STAMP(1)
     cp_async_wait_all();
-    QKV_STAMP(2)
     if (qp.gamma) {
         // each thread squares, and later scales, the vectors it copied itself
         for (uint32_t b = 0; b < rows; ++b) {
@@ -355,7 +339,6 @@ __global__ void __launch_bounds__(256, 2) fused_qkv_kernel(const QkvParams qp, c
         }
     }
     __syncthreads();
-    QKV_STAMP(3)
 
     const bool has_x = r_in < rows;  // this lane's input row on the n side
     const __half *xl = xs + (size_t)r_in * xstride + kq * 8;
@@ -378,7 +361,6 @@ __global__ void __launch_bounds__(256, 2) fused_qkv_kernel(const QkvParams qp, c
             cur = nxt;
             if (chunk + 2 < chunks) fetch(nxt, sd, chunk + 2);
         }
-        QKV_STAMP(4)
         red[warp][r_in][2 * kq] = acc[0];
         red[warp][r_in][2 * kq + 1] = acc[1];
         red[warp][r_in + 8][2 * kq] = acc[2];
@@ -414,21 +396,10 @@ __global__ void __launch_bounds__(256, 2) fused_qkv_kernel(const QkvParams qp, c
             }
             if (qp.append) rope_and_store(ap, s, done.slot, done.j, a, c);
         }
-        QKV_STAMP(5)
         if (!more) break;
     }
 }
 
-#ifdef MF_QKV_PROFILE
-}  // namespace
-}  // namespace mf
-extern "C" __attribute__((visibility("default"))) int mf_debug_qkv_profile(unsigned long long *host_out, uint32_t n)
-{
-    return (int)cudaMemcpyFromSymbol(host_out, mf::g_qkv_prof, sizeof(unsigned long long) * n);
-}
-namespace mf {
-namespace {
-#endif
 
 // NeoX RoPE over rows of `dim` (rope.metal:36-74): pos = (row % seq_len) + offset.
 __global__ void __launch_bounds__(256)

@@ -33,44 +33,19 @@
 namespace mf {
 namespace {
 
-#ifndef MF_TC_LOAD_DIV
-#define MF_TC_LOAD_DIV 1  // timing probe only: > 1 loads that fraction of every K/V tile (results are then wrong)
-#endif
-#ifndef MF_TC_SPLIT_ISSUE
-#define MF_TC_SPLIT_ISSUE 1  // 1: Q K^T and P V are issued by two threads in two warps, 0: by one
-#endif
-#ifndef MF_TC_PROBE_QK_DIV
-#define MF_TC_PROBE_QK_DIV 1  // timing probes: issue only 1/DIV of the MMAs of a product (results are then wrong)
-#endif
-#ifndef MF_TC_PROBE_PV_DIV
-#define MF_TC_PROBE_PV_DIV 1
-#endif
-#ifndef MF_TC_PROBE_NOEXP
-#define MF_TC_PROBE_NOEXP 0
-#endif
-#ifndef MF_TC_VSTAGES
-#define MF_TC_VSTAGES 3
-#endif
 constexpr uint32_t kBM = 128;             // query rows per CTA
 constexpr uint32_t kBN = 128;             // keys per tile
-#ifndef MF_TC_ROW_SPLIT
-#define MF_TC_ROW_SPLIT 1
-#endif
-constexpr uint32_t kRowSplit = MF_TC_ROW_SPLIT;           // softmax threads per query row
+constexpr uint32_t kRowSplit = 1;                         // softmax threads per query row
 constexpr uint32_t kCols = 128 / kRowSplit;               // score columns per thread
 constexpr uint32_t kGroupWarps = 4 * kRowSplit;           // softmax warps per group
 constexpr uint32_t kSoftmaxWarps = 2 * kGroupWarps;
 constexpr uint32_t kSoftmaxThreads = 32 * kSoftmaxWarps;
-constexpr uint32_t kTcThreads = kSoftmaxThreads + 64 + 32 * MF_TC_SPLIT_ISSUE;
+constexpr uint32_t kTcThreads = kSoftmaxThreads + 96;
 constexpr float kRescaleThreshold = 8.0f;                 // log2 of the largest weight kept in P
-#ifndef MF_TC_POLY_MASK
-#define MF_TC_POLY_MASK 0x00u
-#endif
-constexpr uint32_t kPolyMask = MF_TC_POLY_MASK;           // which of every 8 column pairs use the FMA-pipe exp2
 constexpr uint32_t kHalfTile = 128 * 128; // bytes: 128 rows x 64 f16
 __host__ __device__ constexpr uint32_t tc_tile_bytes(uint32_t d) { return (d / 64) * kHalfTile; }  // 16 or 32 KB
 constexpr uint32_t kKStages = 3;           // K tiles in flight
-constexpr uint32_t kVStages = MF_TC_VSTAGES;  // V tiles in flight
+constexpr uint32_t kVStages = 3;  // V tiles in flight
 constexpr uint64_t kTcWaitNs = 2000000000ull;
 constexpr float kNegInf = -1e30f;
 
@@ -84,30 +59,6 @@ struct TcParams {
     const uint32_t *page_table_row;  // null: contiguous cache
     uint32_t page_size, page_shift, n_kv_heads;  // page_size = 1 << page_shift
 };
-
-#ifdef MF_TC_PROFILE
-// Development aid (build with -DMF_TC_PROFILE): cycles spent in each barrier wait, per CTA and role.
-__device__ unsigned long long g_tc_prof[1024 * 32];
-#define TC_PROF_DECL unsigned long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long prof_t0 = clock64(); \
-    unsigned long long prof_g0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_g0));
-#define TC_PROF_WAIT(idx, stmt) { const long long t_ = clock64(); stmt; prof_acc[idx] += (unsigned long long)(clock64() - t_); }
-#define TC_PROF_STORE(role) { const uint32_t cta_ = blockIdx.x; if (cta_ < 1024) { \
-        for (int k_ = 0; k_ < 8; ++k_) g_tc_prof[cta_ * 32 + (role) * 10 + k_] = prof_acc[k_]; \
-        g_tc_prof[cta_ * 32 + (role) * 10 + 8] = (unsigned long long)(clock64() - prof_t0); if ((role) == 0) { g_tc_prof[cta_ * 32 + 31] = n_tiles; g_tc_prof[cta_ * 32 + 29] = prof_g0; \
-        unsigned int smid_; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid_)); g_tc_prof[cta_ * 32 + 30] = smid_; \
-        unsigned long long g1_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1_)); g_tc_prof[cta_ * 32 + 9] = g1_; } } }
-#else
-#define TC_PROF_DECL
-#define TC_PROF_WAIT(idx, stmt) stmt;
-#define TC_PROF_STORE(role)
-#endif
-#ifdef MF_TC_PROFILE
-#define TC_PROF_MARK(var) const long long var = clock64();
-#define TC_PROF_SPAN(idx, a, b) prof_acc[idx] += (unsigned long long)((b) - (a));
-#else
-#define TC_PROF_MARK(var)
-#define TC_PROF_SPAN(idx, a, b)
-#endif
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------
 
@@ -218,26 +169,6 @@ __device__ __forceinline__ float max3(float a, float b, float c)
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
-}
-
-// 2^t for two values without the special-function unit, for t <= ~8: round t to the nearest integer n
-// with the 1.5 * 2^23 trick, a cubic for 2^f on f = t - n in [-0.5, 0.5] (relative error 7.5e-5, under
-// half an f16 ulp, which is what the weights are rounded to), then n is added to the exponent field.
-// The special-function unit delivers 16 exponentials per clock and SM, as many clocks per tile as the
-// two matrix products take; moving part of the row to the FMA pipe takes it off the critical path.
-__device__ __forceinline__ float2 exp2_poly2(float2 t)
-{
-    t.x = fmaxf(t.x, -125.f);
-    t.y = fmaxf(t.y, -125.f);
-    const float2 tt = __fadd2_rn(t, make_float2(12582912.f, 12582912.f));
-    const float2 n = __fadd2_rn(tt, make_float2(-12582912.f, -12582912.f));
-    const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), t);
-    float2 y = __ffma2_rn(f, make_float2(0.0551716685f, 0.0551716685f), make_float2(0.2426111251f, 0.2426111251f));
-    y = __ffma2_rn(y, f, make_float2(0.6932609677f, 0.6932609677f));
-    y = __ffma2_rn(y, f, make_float2(0.9999280572f, 0.9999280572f));
-    y.x = __uint_as_float(__float_as_uint(y.x) + (__float_as_uint(tt.x) << 23));
-    y.y = __uint_as_float(__float_as_uint(y.y) + (__float_as_uint(tt.y) << 23));
-    return y;
 }
 
 // 4-D tiled load without a cache hint: (column in half, row, half, head).
@@ -454,7 +385,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
             tma_prefetch_desc(&tm_v);
-            TC_PROF_DECL
             mbar_arrive_expect_tx(bar(kQFull), kTile);
             tma_load_4d(q_smem, &tm_q, 0, (int32_t)row0, 0, (int32_t)head, bar(kQFull));
             // K/V maps are (head_dim, kv_len, kv heads): rows past kv_len arrive as zeros, so a
@@ -465,17 +395,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             // is free when the P V that read it has completed, the K slot when the Q K^T of tile i has:
             // the tensor pipe's own completion barriers say both.
             for (uint32_t i = 0; i < min(n_tiles, 3u); ++i) {
-                mbar_arrive_expect_tx(bar(kKFull + i), kTile / MF_TC_LOAD_DIV);
+                mbar_arrive_expect_tx(bar(kKFull + i), kTile);
                 tma_load_4d(k_smem + i * kTile, &tm_k, 0, (int32_t)(i * kBN), 0, (int32_t)kvh, bar(kKFull + i));
             }
             uint32_t b = 0, ph = 0;  // slot i % 3 and phase (i / 3) & 1
             for (uint32_t i = 0; i < n_tiles; ++i) {
-                if (i >= 3) { TC_PROF_WAIT(1, wait(bar(kOFull + b), ph ^ 1, 16u)) }  // P V (i - 3) done
+                if (i >= 3) { wait(bar(kOFull + b), ph ^ 1, 16u); }  // P V (i - 3) done
                 const bool with_k = i + 3 < n_tiles;
-                mbar_arrive_expect_tx(bar(kVFull + b), (with_k ? 2 : 1) * (kTile / MF_TC_LOAD_DIV));
+                mbar_arrive_expect_tx(bar(kVFull + b), (with_k ? 2 : 1) * kTile);
                 tma_load_4d(v_smem + b * kTile, &tm_v, 0, (int32_t)(i * kBN), 0, (int32_t)kvh, bar(kVFull + b));
                 if (with_k) {
-                    TC_PROF_WAIT(0, wait(bar(kSFull + b), ph, 16u))  // Q K^T (i) done: K slot b is free
+                    wait(bar(kSFull + b), ph, 16u);  // Q K^T (i) done: K slot b is free
                     tma_load_4d(k_smem + b * kTile, &tm_k, 0, (int32_t)((i + 3) * kBN), 0, (int32_t)kvh, bar(kVFull + b));
                 }
                 if (++b == 3) {
@@ -483,9 +413,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     ph ^= 1;
                 }
             }
-            TC_PROF_STORE(2)
         }
-#if MF_TC_SPLIT_ISSUE
     } else if (warp == kSoftmaxWarps + 2) {
         // ------------------------------------------------ MMA issuer for Q K^T (split issue) ---
         if (lane == 0) {
@@ -537,71 +465,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
             }
         }
-#else
-    } else if (warp == kSoftmaxWarps + 1) {
-        // ------------------------------------------------------------------ MMA issuer ---
-        if (lane == 0) {
-            constexpr uint32_t kIdescQK = instr_desc(kBN, 0);
-            constexpr uint32_t kIdescPV = instr_desc(D, 1);
-            TC_PROF_DECL
-            wait(bar(kQFull), 0, 32u);
-            // The descriptors of one operand differ only in the 14-bit start-address field: build each
-            // once and add the 16-byte-unit offsets, so that an MMA costs this thread a few instructions.
-            const uint64_t q_desc = smem_desc(q_smem, 16, 1024);
-            // b = i % 3 is tile i's score buffer and its K and V ring slot, ph = (i / 3) & 1 their phase;
-            // both are carried as counters: this thread's instructions are the kernel's critical path.
-            auto issue_qk = [&](uint32_t b, bool first_round) {
-                if (first_round) {  // later K tiles arrive together with the V tile waited for just before
-                    TC_PROF_WAIT(0, wait(bar(kKFull + b), 0, 32u))
-                    tc_fence_after();
-                }
-                TC_PROF_MARK(ma)
-                const uint64_t k_desc = smem_desc(k_smem + b * kTile, 16, 1024);
-#pragma unroll
-                for (uint32_t kk = 0; kk < D / 16 / MF_TC_PROBE_QK_DIV; ++kk) {
-                    const uint32_t off = ((kk >> 2) * kHalfTile + (kk & 3) * 32) >> 4;
-                    tc_mma_ss(tmem + b * 128, q_desc + off, k_desc + off, kIdescQK, kk > 0);
-                }
-                TC_PROF_MARK(mb)
-                tc_commit(bar(kSFull + b));
-                TC_PROF_MARK(mc)
-                TC_PROF_SPAN(4, ma, mb)
-                TC_PROF_SPAN(6, mb, mc)
-            };
-            auto issue_pv = [&](uint32_t b, uint32_t ph, uint32_t first) {
-                TC_PROF_WAIT(2, wait(bar(kVFull + b), ph, 64u))
-                TC_PROF_WAIT(3, wait(bar(kPFull + b), ph, 64u))
-                tc_fence_after();
-                TC_PROF_MARK(ma)
-                const uint64_t v_desc = smem_desc(v_smem + b * kTile, v_half_stride<D, PAGED>(p.page_shift), v_group_stride<D, PAGED>(p.page_shift));
-#pragma unroll
-                for (uint32_t kk = 0; kk < kBN / 16 / MF_TC_PROBE_PV_DIV; ++kk) {
-                    // A: 16 keys = 8 packed 32-bit TMEM columns per step; B: V rows kk*16.., MN-major.
-                    tc_mma_ts(tmem + 384, tmem + b * 128 + kk * 8,
-                              v_desc + (v_step_offset<D, PAGED>(kk, p.page_shift) >> 4), kIdescPV,
-                              (!first || kk > 0) ? 1u : 0u);
-                }
-                TC_PROF_MARK(mb)
-                tc_commit(bar(kOFull + b));
-                TC_PROF_MARK(mc)
-                TC_PROF_SPAN(5, ma, mb)
-                TC_PROF_SPAN(7, mb, mc)
-            };
-            // Q K^T of tile i + 3 goes into the buffer that P V of tile i has just read: the tensor
-            // pipe runs this thread's MMAs in order, so S overwrites P only after P was consumed.
-            for (uint32_t i = 0; i < min(n_tiles, 3u); ++i) issue_qk(i, true);
-            uint32_t b = 0, ph = 0;
-            for (uint32_t i = 0; i < n_tiles; ++i) {
-                issue_pv(b, ph, i == 0);
-                if (i + 3 < n_tiles) issue_qk(b, false);
-                if (++b == 3) {
-                    b = 0;
-                    ph ^= 1;
-                }
-            }
-            TC_PROF_STORE(1)
-        }
-#endif
     } else {
         // --------------------------------------------------------- softmax groups / epilogue ---
         // kRowSplit threads per query row (= TMEM lane) and group, each holding 128 / kRowSplit scores of
@@ -621,7 +484,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const uint32_t pair_bar = 1 + g * 4 + quad;             // named barrier of the warps that share rows
         float my_ref = kNegInf, l_part = 0.f;                   // my_ref in the scaled log2 domain
         uint32_t last_mine = 0xFFFFFFFFu;
-        TC_PROF_DECL
 
         for (uint32_t i = g; i < n_tiles; i += 2) {
             const uint32_t b = i % 3, sph = (i / 3) & 1;
@@ -630,12 +492,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             // Only tiles on the causal diagonal or at the end of the cache need a mask.
             const uint32_t n_vis = last_ok < key0 ? 0u : min(kCols, last_ok - key0 + 1);
             last_mine = i;
-            TC_PROF_WAIT(0, wait(bar(kSFull + b), sph, 256u))
+            wait(bar(kSFull + b), sph, 256u);
             tc_fence_after();
             // The TMEM accesses below are warp-collective: the choice between the plain and the
             // masked form of the row must be the same for all 32 rows of the warp.
             const bool whole = __all_sync(0xffffffffu, n_vis == kCols);
-            TC_PROF_MARK(pt0)
             float mx0 = -3.0e38f, mx1 = -3.0e38f, mx2 = -3.0e38f, mx3 = -3.0e38f;
             if (kRowSplit == 2) {
                 // The row maximum needs the partner's columns too: stream them through registers for the
@@ -690,14 +551,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (kRowSplit == 2) {
                 // Both threads of a row have every score they need in registers: from here on either may
                 // overwrite the buffer with P.
-                TC_PROF_WAIT(3, named_bar_sync(pair_bar, 64))
+                named_bar_sync(pair_bar, 64);
             }
             const float m_new = mx > -3.0e38f ? mx * p.scale_log2 : kNegInf;
-            TC_PROF_MARK(pt1)
             // The reference maximum after tile i - 1, decided by the other group.
             float m_prev = kNegInf;
             if (i > 0) {
-                TC_PROF_WAIT(1, wait(bar(kDec + ((i - 1) & 1)), ((i - 1) >> 1) & 1, 512u))
+                wait(bar(kDec + ((i - 1) & 1)), ((i - 1) >> 1) & 1, 512u);
                 m_prev = mref[r_in];
             }
             // Lazy rescale: keep exponentiating against the old reference until a row outgrows it by 2^8.
@@ -711,7 +571,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 // O must hold every earlier P V before it is scaled.  S(i) being there implies that
                 // P V (i - 3) is done, so the parity of the buffer's barrier is unambiguous.
                 const uint32_t pb = (i - 1) % 3;
-                TC_PROF_WAIT(2, wait(bar(kOFull + pb), ((i - 1) / 3) & 1, 128u))
+                wait(bar(kOFull + pb), ((i - 1) / 3) & 1, 128u);
                 tc_fence_after();
                 const float alpha = fast_exp2(m_prev - m_ref);
 #pragma unroll 1
@@ -743,7 +603,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(kDec + (i & 1)));  // the other group may fold in tile i + 1
             // weights (f16) over the first 64 columns of the buffer, and the row sum
-            TC_PROF_MARK(pt2)
             if (whole) {
                 const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_ref, -m_ref);
                 float2 acc_a = make_float2(0.f, 0.f), acc_b = make_float2(0.f, 0.f);
@@ -755,16 +614,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         const float2 t = __ffma2_rn(make_float2(__uint_as_float(r[c * 32 + 2 * q]),
                                                                 __uint_as_float(r[c * 32 + 2 * q + 1])), sc2, nm2);
                         float2 w;
-                        if (kPolyMask & (1u << (q & 7))) {
-                            w = exp2_poly2(t);
-                        } else {
-#if MF_TC_PROBE_NOEXP
-                            w = t;  // timing probe: no special-function work (results are wrong)
-#else
-                            w.x = fast_exp2(t.x);
-                            w.y = fast_exp2(t.y);
-#endif
-                        }
+                        w.x = fast_exp2(t.x);
+                        w.y = fast_exp2(t.y);
                         if (q & 1) acc_b = __fadd2_rn(acc_b, w);
                         else acc_a = __fadd2_rn(acc_a, w);
                         pk[q] = pack_f16x2(w.x, w.y);
@@ -790,7 +641,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
                 l_part += sum0 + sum1;
             }
-            TC_PROF_MARK(pt3)
             if (PAGED && i + 1 == n_tiles && p.kv_len < (i + 1) * kBN) {
                 // Paged cache: the rows of this tile past kv_len were never written or never loaded.
                 // Their weights are exactly zero, but zero times a stale NaN is not: clear them in V
@@ -803,18 +653,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(kPFull + b));  // P(i) is in TMEM, O is consistent with m_ref
-            TC_PROF_MARK(pt4)
-            TC_PROF_SPAN(4, pt0, pt1)
-            TC_PROF_SPAN(5, pt1, pt2)
-            TC_PROF_SPAN(6, pt2, pt3)
-            TC_PROF_SPAN(7, pt3, pt4)
         }
 
         // ---- normalise and write the rows out: every thread takes 128 / (2 kRowSplit) columns --------
         if (last_mine != 0xFFFFFFFFu) {
             // The product of this group's last tile; the other group waits for its own, and both
             // issuing threads' products on O have then completed.
-            TC_PROF_WAIT(2, wait(bar(kOFull + last_mine % 3), (last_mine / 3) & 1, 128u))
+            wait(bar(kOFull + last_mine % 3), (last_mine / 3) & 1, 128u);
         }
         named_bar_sync(9, kSoftmaxThreads);  // every product is done, every decision published
         tc_fence_after();
@@ -845,9 +690,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
             }
         }
-        if (tid == 0) {
-            TC_PROF_STORE(0)
-        }
     }
 
     // Everybody meets here before the TMEM columns go back, also after an abort.
@@ -860,13 +702,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 }
 
 }  // namespace
-
-#ifdef MF_TC_PROFILE
-extern "C" __attribute__((visibility("default"))) int mf_debug_tc_profile(unsigned long long *host_out, uint32_t n)
-{
-    return (int)cudaMemcpyFromSymbol(host_out, g_tc_prof, sizeof(unsigned long long) * n);
-}
-#endif
 
 // Returns MF_ERR_OPERATION_NOT_SUPPORTED (without touching last_error semantics) when the
 // shape is outside this kernel's envelope; the caller then uses the mma.sync kernel.
@@ -935,8 +770,8 @@ mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const 
         // K by column half (its descriptor needs the 128 rows of a half evenly spaced), V by whole page
         if (!encode_pool(&tm_k, k, 1) || !encode_pool(&tm_v, v, kD / 64)) return MF_OK;
     } else {
-        if (!encode(&tm_k, k, b.kv_len, cache_heads, kD, b.k_stride_h, 128 / MF_TC_LOAD_DIV)) return MF_OK;
-        if (!encode(&tm_v, v, b.kv_len, cache_heads, kD, b.v_stride_h, 128 / MF_TC_LOAD_DIV)) return MF_OK;
+        if (!encode(&tm_k, k, b.kv_len, cache_heads, kD, b.k_stride_h, 128)) return MF_OK;
+        if (!encode(&tm_v, v, b.kv_len, cache_heads, kD, b.v_stride_h, 128)) return MF_OK;
     }
     TcParams p{};
     if (paged) {
