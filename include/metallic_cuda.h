@@ -237,17 +237,28 @@ MF_API uint64_t mf_launch_count(const MfContext *ctx);
  * append+decode launch then starts streaming K/V pages before the previous kernel in the
  * stream has finished; the caller promises that this previous kernel does not write the
  * pools, page table or lengths the launch reads (consecutive layers of a decode step never
- * do).  The library itself keeps track of the caches its last three appending decode launches
- * wrote and does not stream early from one of those (a one-layer model, or two calls in a row on
- * one cache); kernels of other origins are the caller's to vouch for.  Everything else a launch
- * reads or writes still waits for the previous kernel.
+ * do).  The library itself knows which of its own launches can still be in flight when a new
+ * one starts (every eighth launch releases its dependents only after its own dependency wait,
+ * which bounds that set by the launch protocol alone), keeps the caches those launches write
+ * and does not stream early from one of them (a one-layer model, or two calls in a row on one
+ * cache); kernels of other origins that release their dependents early are the caller's to
+ * vouch for.  Everything else a launch reads or writes still waits for the previous kernel.
  * Value 2 extends the early streaming to launches WITHOUT a fused append (the shards of a
  * sequence-sharded step that do not own the tail page): the caller then also promises that no
  * separate append kernel precedes the launch in the stream.
  * MF_OPTION_DECODE_STAGES = n: depth of the decode kernel's K/V tile ring (0 = default).
  * MF_OPTION_PREFILL_IMPL: 0 = choose (tcgen05 kernel when the shape allows), 1 = mma.sync
- * kernel only, 2 = tcgen05 kernel only (like METALLIC_FA_PREFILL_* in the reference). */
-enum { MF_OPTION_OVERLAP_LAUNCHES = 1, MF_OPTION_DECODE_STAGES = 2, MF_OPTION_PREFILL_IMPL = 3 };
+ * kernel only, 2 = tcgen05 kernel only (like METALLIC_FA_PREFILL_* in the reference).
+ * MF_OPTION_DECODE_CLUSTERS: 0 = short decode launches (few tiles per CTA, several CTAs per
+ * (sequence, kv head) unit) run the CTAs of a unit as a thread-block cluster that combines
+ * its states through distributed shared memory; 1 = never (every span writes a partial and
+ * the last one merges, as long launches do). */
+enum {
+    MF_OPTION_OVERLAP_LAUNCHES = 1,
+    MF_OPTION_DECODE_STAGES = 2,
+    MF_OPTION_PREFILL_IMPL = 3,
+    MF_OPTION_DECODE_CLUSTERS = 4
+};
 MF_API mf_status mf_context_set_option(MfContext *ctx, uint32_t option, uint32_t value);
 /* Caller-provided scratch (device); when absent the context allocates its own
  * arena on first use and grows it on demand (pooled scratch of step.rs:927-929). */
@@ -506,6 +517,8 @@ MF_API uint32_t mf_decode_plan_build_host(const uint32_t *kv_lens_host, uint32_t
                                           uint32_t max_ctas, uint32_t *items_out, uint32_t item_capacity,
                                           uint32_t *cta_begin_out, uint32_t *n_ctas_out);
 MF_API uint32_t mf_decode_plan_ctas(const MfDecodePlan *plan);
+/* CTAs per thread-block cluster of the plan's launches (0: the plain form, see MF_OPTION_DECODE_CLUSTERS). */
+MF_API uint32_t mf_decode_plan_cluster(const MfDecodePlan *plan);
 MF_API uint32_t mf_decode_plan_items(const MfDecodePlan *plan);
 MF_API uint64_t mf_decode_plan_tiles(const MfDecodePlan *plan);
 

@@ -38,7 +38,7 @@ ROPE_MODE_NEOX, ROPE_MODE_NORMAL = 0, 1
 ROUTE_DECODE, ROUTE_PREFILL, ROUTE_PREFILL_SPLITK, ROUTE_REFERENCE = 1, 2, 3, 4
 DTYPE_F16, DTYPE_F32, DTYPE_U32 = 0, 1, 2
 ALL_SEQUENCES = 0xFFFFFFFF
-OPTION_OVERLAP_LAUNCHES = 1
+OPTION_OVERLAP_LAUNCHES, OPTION_DECODE_STAGES, OPTION_PREFILL_IMPL, OPTION_DECODE_CLUSTERS = 1, 2, 3, 4
 KV_LAYOUT_EXPANDED_HEADS, KV_LAYOUT_COMPACT_KV_HEADS = 0, 1
 
 
@@ -193,6 +193,7 @@ _SIGNATURES = {
     "mf_decode_plan_destroy": (None, [vp, vp]),
     "mf_decode_plan_build_host": (u32, [vp, u32, u32, u32, vp, u32, vp, C.POINTER(u32)]),
     "mf_decode_plan_ctas": (u32, [vp]),
+    "mf_decode_plan_cluster": (u32, [vp]),
     "mf_decode_plan_items": (u32, [vp]),
     "mf_decode_plan_tiles": (u64, [vp]),
     "mf_paged_decode": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv), C.POINTER(MfPagedDecodeArgs)]),
@@ -631,6 +632,10 @@ class DecodePlan:
     @property
     def ctas(self):
         return int(lib.mf_decode_plan_ctas(self._h))
+
+    @property
+    def cluster(self):
+        return int(lib.mf_decode_plan_cluster(self._h))
 
     @property
     def items(self):

@@ -88,7 +88,7 @@ mf_status decode_contiguous(MfContext *ctx, const void *q, const void *k, const 
     const uint64_t total = (uint64_t)U * T;
     if (total > 0xFFFFFFFFull) return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "FlashDecode: too many tiles");
     const uint32_t want = decode_cta_target((uint32_t)ctx->sm_count, decode_ctas_per_sm(ctx, D, group), total);
-    const UniformSplit split = uniform_split(U, T, n_splits, want);
+    const UniformSplit split = uniform_split(U, T, n_splits, want, decode_max_cluster(ctx, D, group));
     const uint32_t span = split.span, n_ctas = split.n_ctas;
 
     const uint64_t slot_bytes = partial_slot_bytes(group, D);
@@ -119,6 +119,7 @@ mf_status decode_contiguous(MfContext *ctx, const void *q, const void *k, const 
     p.uniform_tiles = T;
     p.uniform_span = span;
     p.uniform_parts = split.parts;
+    p.cluster_size = split.cluster;
     p.uniform_total = split.parts ? n_ctas * span : (uint32_t)total;  // the cursor turns flat / span into the CTA index
     p.q_stride_b = s->q_stride_b;
     p.q_stride_h = s->q_stride_h;
@@ -497,7 +498,7 @@ mf_status mf_flash_attention(MfContext *ctx, const MfTensor *q, const MfTensor *
 static mf_status plan_upload(MfContext *ctx, MfDecodePlan *pl)
 {
     pl->n_items = (uint32_t)pl->h_items.size();
-    pl->n_ctas = (uint32_t)pl->h_cta_begin.size() - 1;
+    pl->n_ctas = ((uint32_t)pl->h_cta_begin.size() - 1) * (pl->cluster > 1 ? pl->cluster : 1);  // cluster form: one entry per cluster
     if (pl->n_items > pl->item_capacity)
         return fail(ctx, MF_ERR_INVALID_OPERATION, "decode plan: %u items exceed capacity %u", pl->n_items, pl->item_capacity);
     if (pl->n_items == 0) return MF_OK;
@@ -542,6 +543,7 @@ mf_status mf_decode_plan_create(MfContext *ctx, const uint32_t *kv_lens_host, ui
     pl->auto_ctas = auto_ctas;
     pl->ctas_per_sm = decode_ctas_per_sm(ctx, head_dim, n_heads / n_kv_heads);
     pl->sm_count = (uint32_t)ctx->sm_count;
+    pl->max_cluster = decode_max_cluster(ctx, head_dim, n_heads / n_kv_heads);
     pl->n_units = batch * n_kv_heads;
     pl->item_capacity = pl->n_units + max_ctas;
     pl->heads_padded = heads_padded(n_heads / n_kv_heads);
@@ -583,8 +585,11 @@ mf_status mf_decode_plan_update(MfContext *ctx, MfDecodePlan *pl, const uint32_t
         for (uint32_t b = 0; b < pl->batch; ++b) total += (uint64_t)((kv_lens_host[b] + kTileKeys - 1) / kTileKeys) * pl->n_kv_heads;
         ctas = decode_cta_target(pl->sm_count, pl->ctas_per_sm, total);
     }
+    // the cluster form only for plans whose CTA count the library chooses (an explicit count is a request for
+    // exactly that many spans)
+    pl->cluster = pl->auto_ctas ? pl->max_cluster : 0;
     build_decode_plan(kv_lens_host, pl->batch, pl->n_kv_heads, ctas, pl->h_items, pl->h_cta_begin, &pl->n_units,
-                      &pl->total_tiles);
+                      &pl->total_tiles, &pl->cluster);
     return plan_upload(ctx, pl);
 }
 
@@ -625,6 +630,7 @@ uint32_t mf_decode_plan_build_host(const uint32_t *kv_lens_host, uint32_t batch,
 }
 
 uint32_t mf_decode_plan_ctas(const MfDecodePlan *pl) { return pl ? pl->n_ctas : 0; }
+uint32_t mf_decode_plan_cluster(const MfDecodePlan *pl) { return pl ? pl->cluster : 0; }
 uint32_t mf_decode_plan_items(const MfDecodePlan *pl) { return pl ? pl->n_items : 0; }
 uint64_t mf_decode_plan_tiles(const MfDecodePlan *pl) { return pl ? pl->total_tiles : 0; }
 
@@ -666,6 +672,7 @@ static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, con
     p.rope_positions = rope_positions;
     p.items = pl->d_items;
     p.cta_item_begin = pl->d_cta_begin;
+    p.cluster_size = pl->cluster;
     p.part_acc = pl->d_part_acc;
     p.part_ml = pl->d_part_ml;
     p.counters = pl->d_counters;

@@ -235,6 +235,7 @@ mf_status mf_context_set_option(MfContext *ctx, uint32_t option, uint32_t value)
         case MF_OPTION_OVERLAP_LAUNCHES: ctx->overlap_launches = value > 2 ? 1u : value; return MF_OK;
         case MF_OPTION_DECODE_STAGES: ctx->decode_stages = value; return MF_OK;
         case MF_OPTION_PREFILL_IMPL: ctx->prefill_impl = value; return MF_OK;
+        case MF_OPTION_DECODE_CLUSTERS: ctx->decode_clusters = value ? 1u : 0u; return MF_OK;
         default: return fail(ctx, MF_ERR_INVALID_OPERATION, "unknown option %u", option);
     }
 }

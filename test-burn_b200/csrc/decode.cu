@@ -68,9 +68,13 @@ struct ItemCursor {
     const DecodeParams &p;
     uint32_t idx, end;       // explicit mode
     uint32_t flat, flat_end; // uniform mode
+    bool cluster_pending;    // cluster form: the one item of this CTA's cluster has not been handed out yet
     __device__ ItemCursor(const DecodeParams &pp, uint32_t cta) : p(pp)
     {
-        if (p.items) {
+        cluster_pending = p.cluster_size > 1;
+        if (cluster_pending) {
+            idx = end = flat = flat_end = 0;
+        } else if (p.items) {
             idx = p.cta_item_begin[cta];
             end = p.cta_item_begin[cta + 1];
             flat = flat_end = 0;
@@ -82,6 +86,29 @@ struct ItemCursor {
     }
     __device__ bool next(WorkItem &it)
     {
+        if (p.cluster_size > 1) {
+            // One item per cluster; this CTA takes an equal share of its tiles (the first `rem` CTAs one more).
+            if (!cluster_pending) return false;
+            cluster_pending = false;
+            const uint32_t C = p.cluster_size, c = blockIdx.x / C, r = cluster_cta_rank();
+            if (p.items) {
+                it = p.items[c];
+            } else {
+                const uint32_t u = c / p.uniform_parts, part = c - u * p.uniform_parts;
+                it.seq = u / p.n_kv_heads;
+                it.kvh = u - it.seq * p.n_kv_heads;
+                it.tile_begin = part * p.uniform_span;
+                it.tile_end = min(p.uniform_tiles, it.tile_begin + p.uniform_span);
+                it.unit = u;
+                it.n_parts = p.uniform_parts;
+                it.first_slot = u * p.uniform_parts;
+                it.slot = it.first_slot + part;
+            }
+            const uint32_t tiles = it.tile_end - it.tile_begin, base = tiles / C, rem = tiles - base * C;
+            it.tile_begin += r * base + min(r, rem);
+            it.tile_end = it.tile_begin + base + (r < rem ? 1u : 0u);
+            return true;
+        }
         if (p.items) {
             if (idx >= end) return false;
             it = p.items[idx++];
@@ -638,6 +665,12 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
         const bool direct = (it.n_parts == 1);
         const bool partial_out = (p.out_acc != nullptr);
+        // Cluster form: this CTA's combined state goes to shared memory where the other CTAs of the cluster
+        // can read it.  The ring is idle by now (one item per CTA, every tile consumed): its first bytes
+        // hold [HP][D] accumulators and [HP] (m, l) pairs, m in the scaled log2 domain.
+        const bool cl = p.cluster_size > 1;
+        float *cl_acc = reinterpret_cast<float *>(smem);
+        float *cl_ml = cl_acc + HP * D;
         // The four warps' accumulators meet in shared memory, one half of the head dimension per
         // pass (the buffer is half-width so that two CTAs fit one SM).
 #pragma unroll
@@ -670,7 +703,13 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                     acc += comb[(w * HP + g) * S::kCombStride + dd];
                 }
                 const uint32_t h = it.kvh * G + g;
-                if (!direct) {
+                if (cl) {
+                    cl_acc[g * D + d] = acc;
+                    if (d == 0) {
+                        cl_ml[g * 2] = m_all;
+                        cl_ml[g * 2 + 1] = l_all;
+                    }
+                } else if (!direct) {
                     p.part_acc[((size_t)it.slot * HP + g) * D + d] = acc;
                     if (d == 0) {
                         p.part_ml[((size_t)it.slot * HP + g) * 2] = m_all * kLn2;
@@ -702,7 +741,86 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             }
             if (hp == 0) named_bar_sync(1, kConsumerThreads);  // pass 1 reuses the buffer
         }
-        if (direct) {
+        if (cl) {
+            // ---- the cluster's CTAs meet: each reduces a share of the (head, column) space over all of them ----
+            const uint32_t C = p.cluster_size, crank = cluster_cta_rank();
+            cluster_arrive_release();
+            cluster_wait_acquire();
+            const uint32_t acc_addr = smem_base, ml_addr = smem_base + HP * D * 4;
+            const uint32_t n4 = G * (D / 4);
+            for (uint32_t i = crank + tid * C; i < n4; i += C * kConsumerThreads) {
+                const uint32_t g = i / (D / 4), d0 = (i - g * (D / 4)) * 4;
+                float2 ml[16];
+                float4 a[16];
+#pragma unroll
+                for (uint32_t r = 0; r < 16; ++r) {
+                    if (r < C) {
+                        ml[r] = ld_cluster_f2(cluster_map_shared(ml_addr + g * 8, r));
+                        a[r] = ld_cluster_f4(cluster_map_shared(acc_addr + (g * D + d0) * 4, r));
+                    } else {
+                        ml[r] = make_float2(kNegSentinel, 0.f);
+                        a[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
+                float mx = kNegSentinel;
+#pragma unroll
+                for (uint32_t r = 0; r < 16; ++r) mx = fmaxf(mx, ml[r].x);
+                float lt = 0.f;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (uint32_t r = 0; r < 16; ++r) {
+                    const float w = fast_exp2(ml[r].x - mx);
+                    lt += ml[r].y * w;
+                    acc.x += a[r].x * w;
+                    acc.y += a[r].y * w;
+                    acc.z += a[r].z * w;
+                    acc.w += a[r].w * w;
+                }
+                const uint32_t h = it.kvh * G + g;
+                if (!direct) {
+                    // the cluster's partial of the unit: the last cluster of the unit merges (ticket below)
+                    *reinterpret_cast<float4 *>(p.part_acc + ((size_t)it.slot * HP + g) * D + d0) = acc;
+                    if (d0 == 0) *reinterpret_cast<float2 *>(p.part_ml + ((size_t)it.slot * HP + g) * 2) = make_float2(mx * kLn2, lt);
+                } else if (p.push_world) {
+                    const size_t rows = (size_t)p.batch * p.n_heads, rowi = (size_t)it.seq * p.n_heads + h;
+                    for (uint32_t r = 0; r < p.push_world; ++r) {
+                        *reinterpret_cast<float4 *>(p.push_dst[r] + rowi * D + d0) = acc;
+                        if (d0 == 0) {
+                            p.push_dst[r][rows * D + rowi] = mx * kLn2;
+                            p.push_dst[r][rows * D + rows + rowi] = lt;
+                        }
+                    }
+                } else if (partial_out) {
+                    *reinterpret_cast<float4 *>(p.out_acc + ((size_t)it.seq * p.n_heads + h) * D + d0) = acc;
+                    if (d0 == 0) {
+                        p.out_m[(size_t)it.seq * p.n_heads + h] = mx * kLn2;
+                        p.out_l[(size_t)it.seq * p.n_heads + h] = lt;
+                    }
+                } else {
+                    const bool ok = (fabsf(lt) <= 3.0e38f) && fabsf(lt) > 1e-6f;
+                    const float inv = ok ? 1.0f / lt : 1.0f;  // decode rule: the sum itself when l is tiny
+                    float r4[4] = {acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv};
+                    __half *dst = p.out + (size_t)it.seq * p.out_stride_b + (size_t)h * p.out_stride_h + d0;
+#pragma unroll
+                    for (uint32_t e = 0; e < 4; ++e) {
+                        if (!(fabsf(r4[e]) <= 3.0e38f)) r4[e] = 0.f;
+                        dst[e] = __float2half_rn(r4[e]);
+                    }
+                }
+            }
+            // What this CTA stored for others (a partial slot, a peer's receive block) must be visible before
+            // the cluster's first CTA announces it; and nobody leaves while its shared memory is still read.
+            if (!direct) __threadfence();
+            else if (p.push_world) __threadfence_system();
+            __syncwarp();
+            cluster_arrive_release();
+            cluster_wait_acquire();
+            if (crank != 0) continue;
+            if (direct) {
+                if (p.push_world) push_signal_and_merge<D>(p, it, tid, flags);
+                continue;
+            }
+        } else if (direct) {
             if (p.push_world) push_signal_and_merge<D>(p, it, tid, flags);
             continue;
         }
@@ -814,37 +932,90 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     }
 }
 
+// Per device and instantiation, once: the dynamic shared memory limit, and the largest cluster the kernel can
+// be launched with (16 needs the non-portable opt-in; 8 is portable; 0 if not even that is schedulable).
+template <int D, int NT, int STAGES, int MINB>
+mf_status configure_one(MfContext *ctx, uint32_t *max_cluster_out)
+{
+    using S = Smem<D, NT, STAGES>;
+    static_assert(MINB * (S::kDynamic + 1024) <= 228 * 1024, "CTAs per SM do not fit shared memory");
+    static bool configured[64] = {};
+    static uint32_t max_cluster[64] = {};
+    auto kern = decode_kernel<D, NT, STAGES, MINB>;
+    const int dev = ctx->device;
+    if (dev < 0 || dev >= 64) return fail(ctx, MF_ERR_INVALID_OPERATION, "device index %d", dev);
+    if (!configured[dev]) {
+        mf_status st = check_cuda(
+            ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic),
+            "cudaFuncSetAttribute(decode)");
+        if (st != MF_OK) return st;
+        uint32_t best = 0;
+        const bool wide = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        for (uint32_t c : {16u, 8u}) {
+            if (c == 16 && !wide) continue;
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3(c);
+            cfg.blockDim = dim3(kThreads);
+            cfg.dynamicSmemBytes = S::kDynamic;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = c;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n >= 1) {
+                best = c;
+                break;
+            }
+        }
+        (void)cudaGetLastError();  // a refused query is an answer, not an error of this call
+        max_cluster[dev] = best;
+        configured[dev] = true;
+    }
+    if (max_cluster_out) *max_cluster_out = max_cluster[dev];
+    return MF_OK;
+}
+
 template <int D, int NT, int STAGES, int MINB>
 mf_status launch_one(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap &tm_v,
                      DecodeParams &p, uint32_t n_ctas, const void *writes_k, const void *writes_v)
 {
     using S = Smem<D, NT, STAGES>;
-    static_assert(MINB * (S::kDynamic + 1024) <= 228 * 1024, "CTAs per SM do not fit shared memory");
-    static bool configured[64] = {};
     auto kern = decode_kernel<D, NT, STAGES, MINB>;
-    if (ctx->device < 64 && !configured[ctx->device]) {
-        mf_status st = check_cuda(
-            ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic),
-            "cudaFuncSetAttribute(decode)");
-        if (st != MF_OK) return st;
-        configured[ctx->device] = true;
-    }
-    if (ctx->overlap_launches) {
-        p.strict_release = ctx->next_launch_strict() ? 1u : 0u;
+    mf_status st = configure_one<D, NT, STAGES, MINB>(ctx, nullptr);
+    if (st != MF_OK) return st;
+    if (p.cluster_size > 1 && n_ctas % p.cluster_size != 0)
+        return fail(ctx, MF_ERR_INVALID_OPERATION, "decode: %u CTAs in clusters of %u", n_ctas, p.cluster_size);
+    if (ctx->overlap_launches || p.cluster_size > 1) {
+        const bool programmatic = ctx->overlap_launches != 0;
+        p.strict_release = (programmatic && ctx->next_launch_strict()) ? 1u : 0u;
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(n_ctas);
         cfg.blockDim = dim3(kThreads);
         cfg.dynamicSmemBytes = S::kDynamic;
         cfg.stream = ctx->stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cudaLaunchAttribute attr[2];
+        unsigned n_attr = 0;
+        if (programmatic) {
+            attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+            ++n_attr;
+        }
+        if (p.cluster_size > 1) {
+            attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+            attr[n_attr].val.clusterDim.x = p.cluster_size;
+            attr[n_attr].val.clusterDim.y = 1;
+            attr[n_attr].val.clusterDim.z = 1;
+            ++n_attr;
+        }
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = n_attr;
         cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tm_k, tm_v, p);
         if (e != cudaSuccess) return fail(ctx, MF_ERR_CUDA, "launch decode_kernel: %s", cudaGetErrorString(e));
         ++ctx->launches;
-        ctx->note_programmatic_launch(p.strict_release != 0, writes_k, writes_v);
+        if (programmatic) ctx->note_programmatic_launch(p.strict_release != 0, writes_k, writes_v);
         return MF_OK;
     }
     kern<<<n_ctas, kThreads, S::kDynamic, ctx->stream>>>(tm_k, tm_v, p);
@@ -852,7 +1023,6 @@ mf_status launch_one(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap 
 }
 
 }  // namespace
-
 
 uint32_t decode_ctas_per_sm(const MfContext *ctx, uint32_t head_dim, uint32_t group)
 {
@@ -871,7 +1041,45 @@ uint32_t decode_ctas_per_sm(const MfContext *ctx, uint32_t head_dim, uint32_t gr
 constexpr uint32_t kAlignMaxSpan = 32;   // tiles per CTA up to which units are cut separately
 constexpr uint32_t kAlignMinParts = 4;   // ... given at least this many CTAs per unit
 
-UniformSplit uniform_split(uint32_t units, uint32_t tiles_per_unit, uint32_t n_splits, uint32_t want_ctas)
+uint32_t decode_max_cluster(MfContext *ctx, uint32_t head_dim, uint32_t group)
+{
+    if (!ctx || ctx->decode_clusters == 1) return 0;
+    const uint32_t nt = (group + 7) / 8;
+    uint32_t c = 0;
+    mf_status st = MF_ERR_OPERATION_NOT_SUPPORTED;
+    if (head_dim == 128 && nt == 1 && ctx->decode_stages == 6) st = configure_one<128, 1, 6, 1>(ctx, &c);
+    else if (head_dim == 128 && nt == 1) st = configure_one<128, 1, 3, 2>(ctx, &c);
+    else if (head_dim == 128 && nt == 2) st = configure_one<128, 2, 5, 1>(ctx, &c);
+    else if (head_dim == 64 && nt == 1) st = configure_one<64, 1, 6, 2>(ctx, &c);
+    else if (head_dim == 64 && nt == 2) st = configure_one<64, 2, 8, 1>(ctx, &c);
+    return st == MF_OK ? c : 0;
+}
+
+// Cluster form of a short launch: the `per_unit` CTAs a unit can have are arranged as k clusters of c CTAs, c a
+// power of two up to max_cluster.  A large c leaves few partials to merge through memory (none when k == 1);
+// a small c wastes fewer CTAs when per_unit is not a multiple.  The largest c that keeps at least 85 % of the
+// CTAs the best choice would use is taken.
+void cluster_shape(uint32_t per_unit, uint32_t tiles_per_unit, uint32_t max_cluster, uint32_t *c_out, uint32_t *k_out)
+{
+    *c_out = *k_out = 0;
+    uint32_t best = 0;
+    for (uint32_t c = 2; c <= max_cluster; c *= 2) {
+        const uint32_t k = std::min(per_unit / c, tiles_per_unit / c);
+        best = std::max(best, k * c);
+    }
+    if (!best) return;
+    for (uint32_t c = max_cluster; c >= 2; c /= 2) {
+        const uint32_t k = std::min(per_unit / c, tiles_per_unit / c);
+        if (k && k * c * 100 >= best * 85) {
+            *c_out = c;
+            *k_out = k;
+            return;
+        }
+    }
+}
+
+UniformSplit uniform_split(uint32_t units, uint32_t tiles_per_unit, uint32_t n_splits, uint32_t want_ctas,
+                           uint32_t max_cluster)
 {
     UniformSplit r{};
     const uint32_t T = tiles_per_unit;
@@ -883,6 +1091,17 @@ UniformSplit uniform_split(uint32_t units, uint32_t tiles_per_unit, uint32_t n_s
         return r;
     }
     const uint32_t flat_span = std::max<uint32_t>(1, (uint32_t)((total + want_ctas - 1) / want_ctas));
+    if (max_cluster >= 2 && want_ctas >= kAlignMinParts * units && flat_span <= kAlignMaxSpan) {
+        uint32_t c = 0, k = 0;
+        cluster_shape(want_ctas / units, T, max_cluster, &c, &k);
+        if (c) {
+            r.cluster = c;
+            r.span = (T + k - 1) / k;
+            r.parts = (T + r.span - 1) / r.span;  // ranges (clusters) per unit
+            r.n_ctas = units * r.parts * c;
+            return r;
+        }
+    }
     if (want_ctas >= kAlignMinParts * units && flat_span <= kAlignMaxSpan) {
         const uint32_t parts = std::min(want_ctas / units, T);
         r.span = (T + parts - 1) / parts;
@@ -928,8 +1147,11 @@ mf_status launch_decode(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorM
 
 void build_decode_plan(const uint32_t *kv_lens, uint32_t batch, uint32_t n_kv_heads,
                        uint32_t max_ctas, std::vector<WorkItem> &items,
-                       std::vector<uint32_t> &cta_begin, uint32_t *n_units, uint64_t *total_tiles)
+                       std::vector<uint32_t> &cta_begin, uint32_t *n_units, uint64_t *total_tiles,
+                       uint32_t *cluster_out)
 {
+    const uint32_t max_cluster = cluster_out ? *cluster_out : 0;
+    if (cluster_out) *cluster_out = 0;
     items.clear();
     cta_begin.clear();
     uint64_t total = 0;
@@ -945,6 +1167,44 @@ void build_decode_plan(const uint32_t *kv_lens, uint32_t batch, uint32_t n_kv_he
     uint32_t live_units = 0;
     for (uint32_t b = 0; b < batch; ++b) live_units += kv_lens[b] ? n_kv_heads : 0;
     if (n_ctas >= kAlignMinParts * live_units && (total + n_ctas - 1) / n_ctas <= kAlignMaxSpan) {
+        // Cluster form, when every live sequence has the same number of tiles (one sequence, or equal lengths):
+        // each unit is cut into k ranges, one item and one cluster of c CTAs per range.
+        uint32_t same_tiles = 0;
+        bool same = max_cluster >= 2;
+        for (uint32_t b = 0; b < batch && same; ++b) {
+            const uint32_t tiles = (kv_lens[b] + kTileKeys - 1) / kTileKeys;
+            if (!tiles) continue;
+            if (same_tiles && tiles != same_tiles) same = false;
+            same_tiles = tiles;
+        }
+        uint32_t c = 0, k = 0;
+        if (same && same_tiles) cluster_shape(n_ctas / live_units, same_tiles, max_cluster, &c, &k);
+        if (c) {
+            const uint32_t span = (same_tiles + k - 1) / k, ranges = (same_tiles + span - 1) / span;
+            uint32_t slot = 0;
+            for (uint32_t b = 0; b < batch; ++b) {
+                if (!kv_lens[b]) continue;
+                for (uint32_t kh = 0; kh < n_kv_heads; ++kh) {
+                    const uint32_t first_slot = slot;
+                    for (uint32_t ri = 0; ri < ranges; ++ri) {
+                        WorkItem it{};
+                        it.seq = b;
+                        it.kvh = kh;
+                        it.tile_begin = ri * span;
+                        it.tile_end = std::min(same_tiles, it.tile_begin + span);
+                        it.slot = slot++;
+                        it.unit = b * n_kv_heads + kh;
+                        it.first_slot = first_slot;
+                        it.n_parts = ranges;
+                        cta_begin.push_back((uint32_t)items.size());
+                        items.push_back(it);
+                    }
+                }
+            }
+            cta_begin.push_back((uint32_t)items.size());
+            *cluster_out = c;
+            return;
+        }
         // CTAs per unit in proportion to its tiles, at least one, never more than its tiles
         std::vector<uint32_t> parts(batch, 0);  // per sequence: the same for each of its kv heads
         uint64_t used = 0;

@@ -67,6 +67,12 @@ struct DecodeParams {
     uint32_t k_rows_b, k_rows_h, v_rows_b, v_rows_h;  // contiguous: row strides
     uint32_t uniform_kv_len, uniform_tiles, uniform_span, uniform_total;
     uint32_t uniform_parts;  // > 0: every unit is cut into this many ranges of uniform_span tiles, one CTA each
+    // Cluster form (short launches): a work item is processed by a thread-block cluster of `cluster_size`
+    // CTAs, each taking an equal share of the item's tiles; the cluster combines its CTAs' states through
+    // distributed shared memory and behaves as one CTA towards the rest (output, partial slot, ticket).
+    // Item of cluster c: items[c] (explicit plan) or, for equal lengths, range c % uniform_parts of unit
+    // c / uniform_parts.  0 or 1 = off.
+    uint32_t cluster_size;
     uint32_t rope, rope_mode, append;
     uint32_t rope_position;  // contiguous mode: position of the query token
     uint32_t q_stride_b, q_stride_h, out_stride_b, out_stride_h;
@@ -180,12 +186,14 @@ struct MfContext {
         }
     }
     uint32_t decode_stages = 0;     // MF_OPTION_DECODE_STAGES (0 = default)
+    uint32_t decode_clusters = 0;   // MF_OPTION_DECODE_CLUSTERS: 0 = the library decides, 1 = never
     uint32_t prefill_impl = 0;      // MF_OPTION_PREFILL_IMPL: 0 auto, 1 mma.sync, 2 tcgen05 only
 };
 
 struct MfDecodePlan {
     uint32_t batch = 0, n_heads = 0, n_kv_heads = 0, head_dim = 0, page_size = 0;
     uint32_t max_ctas = 0, n_ctas = 0, n_items = 0, n_units = 0;
+    uint32_t cluster = 0, max_cluster = 0;  // cluster form of the current plan (0 = off) / what the device allows
     bool auto_ctas = false;           // the library picks the CTA count from the step's tile total
     uint32_t ctas_per_sm = 1, sm_count = 0;
     uint64_t total_tiles = 0;
@@ -229,10 +237,12 @@ mf_status get_tensor_map(MfContext *ctx, const void *base, uint64_t rows, uint32
 mf_status ensure_scratch(MfContext *ctx, uint64_t bytes);
 
 // Host planner: cut the tiles of all (sequence, kv head) units into n_ctas equal spans.
+// cluster_out (optional): in: the largest cluster allowed; out: the cluster size of the plan (0 = plain
+// form).  In the cluster form there is one item per cluster and cta_begin is not used by the kernel.
 void build_decode_plan(const uint32_t *kv_lens, uint32_t batch, uint32_t n_kv_heads,
                        uint32_t max_ctas, std::vector<WorkItem> &items,
                        std::vector<uint32_t> &cta_begin, uint32_t *n_units,
-                       uint64_t *total_tiles);
+                       uint64_t *total_tiles, uint32_t *cluster_out = nullptr);
 
 // Resident decode CTAs per SM for a head_dim / GQA group size (decode.cu).
 uint32_t decode_ctas_per_sm(const MfContext *ctx, uint32_t head_dim, uint32_t group);
@@ -241,8 +251,14 @@ uint32_t decode_ctas_per_sm(const MfContext *ctx, uint32_t head_dim, uint32_t gr
 // spans over the flat tile list.
 struct UniformSplit {
     uint32_t span, n_ctas, parts;
+    uint32_t cluster;  // > 1: cluster form, `parts` ranges per unit, each processed by a cluster of this many CTAs
 };
-UniformSplit uniform_split(uint32_t units, uint32_t tiles_per_unit, uint32_t n_splits, uint32_t want_ctas);
+// max_cluster: largest cluster the launch may use (0 or 1: no cluster form).
+UniformSplit uniform_split(uint32_t units, uint32_t tiles_per_unit, uint32_t n_splits, uint32_t want_ctas,
+                           uint32_t max_cluster = 0);
+// Largest cluster size (16, 8 or 0) the decode kernel for this head_dim / group can be launched with on the
+// context's device; 0 when clusters are switched off.
+uint32_t decode_max_cluster(MfContext *ctx, uint32_t head_dim, uint32_t group);
 uint32_t decode_cta_target(uint32_t sm_count, uint32_t ctas_per_sm, uint64_t total_tiles);
 
 // Launchers (decode.cu, prefill.cu, kv_append.cu).

@@ -187,6 +187,43 @@ __device__ __forceinline__ void grid_launch_dependents()
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// ------------------------------------------------------- thread-block clusters ---
+// Rank of this CTA inside its cluster, the cluster barrier in its split (arrive / wait) form, and loads
+// from another CTA's shared memory (distributed shared memory): `local` is a shared-memory address of
+// this CTA, the load reads the same offset in CTA `rank` of the cluster.  Plain loads only.
+__device__ __forceinline__ uint32_t cluster_cta_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_arrive_release()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_acquire()
+{
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_map_shared(uint32_t local, uint32_t rank)
+{
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr)
+{
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float2 ld_cluster_f2(uint32_t addr)
+{
+    float2 v;
+    asm volatile("ld.shared::cluster.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+
 // Named barrier over `count` threads (count a multiple of 32), id 1..15.
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t count)
 {

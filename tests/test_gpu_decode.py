@@ -198,3 +198,50 @@ def test_repeated_launches_are_stable(mfk, foundry):
         assert torch.equal(o, outs[0])
     ref, _ = oracle_decode(case, q_rot, kc, vc)
     assert max_abs(host(outs[0]), ref) <= TOL
+
+
+# shapes for which a short launch takes the cluster form: several CTAs per (sequence, kv head) unit, few tiles each
+CLUSTER_SHAPES = [
+    (24, 8, 128, 8191, 8192),   # configuration 2: 8 units x 16 CTAs, one cluster per unit
+    (16, 2, 128, 8191, 8192),   # 2 units: several clusters per unit, their partials merged through memory
+    (14, 2, 64, 511, 512),      # configuration 1: clusters of 8 with one tile each
+    (32, 2, 128, 3000, 3072),   # G = 16 (two 8-head tiles)
+    (24, 8, 128, 1100, 2048),   # uneven shares: 18 tiles over a cluster
+    (8, 1, 128, 4097, 5000),    # a single unit
+]
+
+
+@pytest.mark.parametrize("shape", CLUSTER_SHAPES)
+@pytest.mark.parametrize("clusters_off", [0, 1])
+@pytest.mark.parametrize("overlap", [0, 1])
+def test_decode_cluster_form_and_plain_form(mfk, foundry, shape, clusters_off, overlap):
+    """The CTAs of a unit combined through distributed shared memory (cluster form) or through partials in
+    global memory and a ticket (plain form): both within tolerance of the oracle and the fp64 gold, with the
+    fused append (caches bit-exact) and without."""
+    import torch
+
+    hq, hkv, d, cached, cap = shape
+    case = ContigCase(n_heads=hq, n_kv_heads=hkv, head_dim=d, cached=cached, capacity=cap, poison=True)
+    q_rot, kc, vc = case.oracle_append()
+    ref, gold = oracle_decode(case, q_rot, kc, vc)
+    foundry.set_option(mfk.OPTION_DECODE_CLUSTERS, clusters_off)
+    foundry.set_option(mfk.OPTION_OVERLAP_LAUNCHES, overlap)
+    try:
+        got = gpu_decode(mfk, foundry, case, q_rot, kc, vc)
+        # one launch: q rotated, the new row appended and attended over
+        kc1, vc1 = dev(case.k_cache), dev(case.v_cache)
+        out1 = torch.full((1, hq * d), float("nan"), dtype=torch.float16, device="cuda")
+        q_rot1 = torch.full((1, hq * d), float("nan"), dtype=torch.float16, device="cuda")
+        p = mfk.KvPrepFusedParamsResolved(hq * d, hkv * d, d, hq, hkv, hq // hkv, 1, cached, cap, hq * d, 0, 0, 0)
+        for _ in range(2):  # twice: the second launch follows a launch that wrote the same cache
+            foundry.kv_prep_flash_decode(dev(case.q), dev(case.k), dev(case.v), q_rot1, kc1, vc1, dev(case.cos), dev(case.sin),
+                                         out1, p)
+        foundry.synchronize()
+    finally:
+        foundry.set_option(mfk.OPTION_DECODE_CLUSTERS, 0)
+        foundry.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 0)
+    assert max_abs(got, ref) <= TOL and max_abs(got, gold.ravel()) <= TOL
+    assert np.array_equal(host(kc1), kc) and np.array_equal(host(vc1), vc)
+    assert np.array_equal(host(q_rot1).ravel(), q_rot)
+    assert max_abs(host(out1).ravel(), ref) <= TOL and max_abs(host(out1).ravel(), gold.ravel()) <= TOL
+    assert np.array_equal(host(out1).ravel(), got)  # same kernel, same cut: the fused form gives the same bits

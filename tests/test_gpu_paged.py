@@ -463,3 +463,27 @@ def test_append_skips_an_empty_sequence_and_a_length_past_the_table(mfk, foundry
             want_k[page, :, t % case.P] = ref[1][page, :, t % case.P]
             want_v[page, :, t % case.P] = ref[2][page, :, t % case.P]
         assert np.array_equal(host(k_pool), want_k) and np.array_equal(host(v_pool), want_v)
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(batch=1, n_heads=24, n_kv_heads=8, head_dim=128, page_size=64, cached=[8191]),
+    dict(batch=1, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[5000]),
+    dict(batch=3, n_heads=14, n_kv_heads=2, head_dim=64, page_size=16, cached=[1023, 1023, 1023]),
+])
+def test_paged_decode_cluster_form(mfk, foundry, cfg):
+    """One sequence (or equal lengths) on pages: the plan takes the cluster form; the same step in the plain
+    form must agree with the oracle just the same."""
+    case = PagedCase(**cfg)
+    ref = case.oracle_step()
+    plan = foundry.decode_plan(case.kv_lens, n_heads=case.Hq, n_kv_heads=case.Hkv, head_dim=case.D, page_size=case.P)
+    assert plan.cluster in (8, 16) and plan.ctas % plan.cluster == 0
+    plan.close()
+    check(case, run_fused(mfk, foundry, case), ref)
+    foundry.set_option(mfk.OPTION_DECODE_CLUSTERS, 1)
+    try:
+        plan = foundry.decode_plan(case.kv_lens, n_heads=case.Hq, n_kv_heads=case.Hkv, head_dim=case.D, page_size=case.P)
+        assert plan.cluster == 0
+        plan.close()
+        check(case, run_fused(mfk, foundry, case), ref)
+    finally:
+        foundry.set_option(mfk.OPTION_DECODE_CLUSTERS, 0)
