@@ -177,11 +177,7 @@ def run_ours(args, w):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world > 1:
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    else:
-        torch.cuda.set_device(0)
+    rank, world, local = rank_setup()
     dev = torch.device("cuda", torch.cuda.current_device())
     mfk = importlib.import_module("test-burn_b200")  # raises if the CUDA library is missing
 
@@ -375,10 +371,8 @@ def run_ours(args, w):
     result["self_check"] = "ok" if ok else "FAILED"
     plan.close()
     f.close()
-    if world > 1:
-        dist.destroy_process_group()
     if rank == 0:
-        print(json.dumps(result))
+        emit(result)
     return 0 if ok else 1
 
 
@@ -390,9 +384,7 @@ def run_long_context(args, w):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local if world > 1 else 0)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank, world, local = rank_setup()
     dev = torch.device("cuda", torch.cuda.current_device())
     mfk = importlib.import_module("test-burn_b200")
     sharding = importlib.import_module("test-burn_b200.sharding")
@@ -553,16 +545,14 @@ def run_long_context(args, w):
         barrier()  # nobody unmaps while a peer may still store
         f.peer_exchange_destroy(px)
     f.close()
-    if world > 1:
-        dist.destroy_process_group()
     if rank == 0:
-        print(json.dumps(result))
+        emit(result)
     return 0 if ok else 1
 
 
 def rank_setup():
-    """(rank, world, device index): one process per GPU under torchrun (NCCL only for the barrier and the
-    max over ranks), a single process otherwise."""
+    """(rank, world, device index): one process per GPU under torchrun (NCCL only for the barrier, the max over
+    ranks and the baseline exchange), a single process otherwise.  The process group is made once per process."""
     import torch
     import torch.distributed as dist
 
@@ -570,9 +560,28 @@ def rank_setup():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0")) if world > 1 else 0
     torch.cuda.set_device(local)
-    if world > 1:
+    if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     return rank, world, local
+
+
+def rank_teardown():
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# Result lines go through emit(): printed, or collected when a run gathers several workloads into one line.
+_COLLECT = None
+
+
+def emit(result):
+    if _COLLECT is not None:
+        _COLLECT.append(result)
+    else:
+        print(json.dumps(result))
 
 
 def rank_reduce(value, world, op="max"):
@@ -669,18 +678,13 @@ def run_prefill(args):
     pairs = sum(cached + i + 1 for i in range(m))
     flops = 4 * d * pairs * hq_all  # the whole job; every GPU's tensor pipe is the roofline of its own share
     ok = rank_reduce(float(bool(torch.isfinite(out.float()).all())), world, "min") > 0.5
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.barrier()
-        dist.destroy_process_group()
     if rank != 0:
         f.close()
         return 0
     peak_path = ROOT / "MEASURED_PEAKS.json"
     peak = json.loads(peak_path.read_text())["bf16_tflops"] if peak_path.exists() else 1590.0
     achieved = flops / (t_attn * 1e-3) / 1e12
-    print(json.dumps({
+    emit({
         "metric": "prefill_attention_tflops", "value": achieved, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": t_append + t_attn, "higher_is_better": True,
         "scaling": "weak" if world == 1 else "strong",
@@ -695,7 +699,7 @@ def run_prefill(args):
         "roofline": {"bound": "tensor", "achieved": achieved / world, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / world / peak, "peak_kind": "measured" if peak_path.exists() else "fallback",
                      "traffic": None, "note": "per GPU"},
-        "gpu_launches": launches, "clocks": clocks, "self_check": "ok" if ok else "FAILED"}))
+        "gpu_launches": launches, "clocks": clocks, "self_check": "ok" if ok else "FAILED"})
     f.close()
     return 0 if ok else 1
 
@@ -833,11 +837,6 @@ def run_contiguous_decode(args, w):
     med = rank_reduce(med, world)
     eager_med = rank_reduce(eager_med, world)
     ok = rank_reduce(float(bool(torch.isfinite(out.float()).all())), world, "min") > 0.5
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.barrier()
-        dist.destroy_process_group()
     if rank != 0:
         f.close()
         return 0
@@ -848,7 +847,7 @@ def run_contiguous_decode(args, w):
     achieved = bytes_layer * layers / (med * 1e-6) / 1e9
     l2_note = ("L2-resident by construction (0.27 MB): latency only, not a bandwidth figure" if layers == 1 else
                "inputs larger than L2 (caches %.2f GB)" % (2 * layers * hkv * cap * d * 2 / 1e9))
-    print(json.dumps({
+    emit({
         "metric": METRIC, "value": 1e6 / med, "unit": "tokens/s", "n_gpus": world, "steps": iters * trials,
         "warmup": max(args.warmup, 3), "ms_per_step": med * 1e-3, "us_per_step": med, "higher_is_better": True,
         "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
@@ -868,9 +867,145 @@ def run_contiguous_decode(args, w):
                      "algorithmic_bytes_per_launch": bytes_layer,
                      "note": "launch-bound" if layers == 1 else "per layer: %s + decode_kernel" %
                              ("fused_qkv_kernel" if args.projection else "kv_append_kernel")},
-        "gpu_launches": launches, "clocks": clocks, "self_check": "ok" if ok else "FAILED"}))
+        "gpu_launches": launches, "clocks": clocks, "self_check": "ok" if ok else "FAILED"})
     f.close()
     return 0 if ok else 1
+
+
+def run_batched_strong(args, w):
+    """ONE batch of the workload (the sequences drawn from the seed of rank 0) split over the ranks by
+    sharding.shard_sequences: longest first, dealt out in a snake; every rank owns its sequences' pages, page
+    table and plan, nothing crosses GPUs during a step (strong scaling; at N = 1 this is the headline step)."""
+    import torch
+    import torch.distributed as dist
+
+    rank, world, local = rank_setup()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    mfk = importlib.import_module("test-burn_b200")
+    sharding = importlib.import_module("test-burn_b200.sharding")
+    layers, hq, hkv, d, P = w["layers"], w["n_heads"], w["n_kv_heads"], w["head_dim"], w["page_size"]
+    _, all_lens = make_lengths(w, SEED)
+    mine = sharding.shard_sequences(all_lens, world, rank)
+    kv_lens = np.ascontiguousarray(all_lens[mine])
+    B = len(mine)
+    wl = dict(w, batch=B)
+    table, n_pages = make_page_table(wl, kv_lens, SEED + rank)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(SEED + rank)
+    pool_elems = n_pages * hkv * P * d
+    k_pools = [torch.empty(pool_elems, dtype=torch.float16, device=dev).normal_(generator=gen) for _ in range(layers)]
+    v_pools = [torch.empty(pool_elems, dtype=torch.float16, device=dev).normal_(generator=gen) for _ in range(layers)]
+    d_table = torch.from_numpy(table.view(np.int32)).to(dev)
+    d_lens = torch.from_numpy(kv_lens.view(np.int32)).to(dev)
+    cos_np, sin_np = mfk.rope_tables(w["theta"], d, int(all_lens.max()))
+    d_cos = torch.from_numpy(cos_np.view(np.float16)).to(dev)
+    d_sin = torch.from_numpy(sin_np.view(np.float16)).to(dev)
+    d_q = torch.empty((layers, B, hq * d), dtype=torch.float16, device=dev).normal_(generator=gen)
+    d_k = torch.empty((layers, B, hkv * d), dtype=torch.float16, device=dev).normal_(generator=gen)
+    d_v = torch.empty((layers, B, hkv * d), dtype=torch.float16, device=dev).normal_(generator=gen)
+    d_out = torch.empty((layers, B, hq * d), dtype=torch.float16, device=dev)
+    stream = torch.cuda.Stream(device=dev)
+    f = mfk.Foundry(dev.index, stream.cuda_stream)
+    if not args.no_overlap:
+        f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 1)
+    plan = f.decode_plan(kv_lens, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P)
+    descs = [mfk.paged_kv(k_pools[i].view(n_pages, hkv, P, d), v_pools[i].view(n_pages, hkv, P, d), d_table, d_lens,
+                          n_kv_heads=hkv, page_size=P, head_dim=d) for i in range(layers)]
+    scale = 1.0 / math.sqrt(d)
+
+    def step():
+        with torch.cuda.stream(stream):
+            for i in range(layers):
+                f.paged_decode(plan, descs[i], d_q[i], d_out[i], n_heads=hq, k=d_k[i], v=d_v[i], cos=d_cos, sin=d_sin,
+                               rope=True, rope_mode=w["rope_mode"], append=True, scale=scale)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    f.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = f.launch_count
+    barrier()
+    start.record(stream)
+    for _ in range(args.steps):
+        step()
+    stop.record(stream)
+    barrier()
+    ms = rank_reduce(start.elapsed_time(stop), world)
+    launches = f.launch_count - launches0
+    f.synchronize()
+    ms_step = ms / args.steps
+    bytes_layer = algorithmic_bytes_per_layer(wl, kv_lens)  # this rank's share
+    launch_us = ms_step * 1e3 / layers
+    achieved = bytes_layer / (launch_us * 1e-6) / 1e9
+    peak, peak_kind = measured_peak_gbs()
+    worst = rank_reduce(achieved, world, "min")
+    ok = rank_reduce(float(bool(torch.isfinite(d_out[-1].float()).all())), world, "min") > 0.5
+    result = {
+        "metric": METRIC, "value": w["batch"] / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "us_per_step": ms_step * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
+        "config": {"workload": w["name"] + "; ONE batch of %d sequences split over the GPUs by length (snake order), "
+                               "no exchange" % w["batch"], "sequences_on_rank_0": B, "seed": SEED,
+                   "l2": "inputs larger than L2"},
+        "roofline": {"bound": "hbm", "achieved": worst, "peak": peak, "unit": "GB/s", "frac": worst / peak,
+                     "peak_kind": peak_kind, "per": "GPU (the rank with the smallest share, max-over-ranks time)",
+                     "launch_us": launch_us, "traffic": None},
+        "gpu_launches": launches * world, "self_check": "ok" if ok else "FAILED"}
+    plan.close()
+    f.close()
+    if rank == 0:
+        emit(result)
+    return 0 if ok else 1
+
+
+def other_workloads(args):
+    """The workloads beside the headline one, measured in the same run so that they land in the same record:
+    at every N the sequence-sharded long context (C5, strong scaling, exchange and merge inside the decode
+    kernel) and ONE batch of the headline workload split over the ranks (strong scaling); at N = 1 also the
+    batch-1 step on contiguous caches (C2, one launch per layer, CUDA-graph replay) and the prefill chunk (C4).
+    Returns {name: short record}; every rank must call it (the sub-runs synchronise)."""
+    import copy
+
+    import torch
+
+    global _COLLECT
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    jobs = [("c5", lambda a: run_long_context(a, LONG_CONTEXT["c5"]), dict(steps=20, exchange="fused")),
+            ("c3_strong", lambda a: run_batched_strong(a, dict(WORKLOADS["c3"])), dict(steps=20))]
+    if world == 1:
+        jobs += [("c2", lambda a: run_contiguous_decode(a, CONTIGUOUS["c2"]), dict(one_launch=True, projection=False)),
+                 ("c4", run_prefill, dict(steps=20, page_size=0))]
+    out = {}
+    for name, fn, over in jobs:
+        a = copy.copy(args)
+        for k, v in over.items():
+            setattr(a, k, v)
+        torch.cuda.empty_cache()
+        _COLLECT = []
+        try:
+            rc = fn(a)
+            rec = _COLLECT[0] if _COLLECT else None
+        except Exception as e:  # a side workload must not take the headline down
+            rc, rec = 1, {"error": "%s: %s" % (type(e).__name__, str(e)[:200])}
+        finally:
+            _COLLECT = None
+        if rec is not None:
+            keep = {k: rec[k] for k in ("metric", "value", "unit", "us_per_step", "ms_per_step", "scaling", "n_gpus", "steps",
+                                        "self_check", "gpu_launches", "error", "append_us", "attention_us") if k in rec}
+            if "roofline" in rec:
+                keep["roofline"] = {k: rec["roofline"].get(k) for k in ("bound", "achieved", "peak", "unit", "frac", "per", "launch_us")}
+            if "config" in rec:
+                keep["workload"] = rec["config"].get("workload")
+            if "latency_us_cuda_graph" in rec:
+                keep["timing"] = "CUDA-graph replay" if "median" in rec["latency_us_cuda_graph"] else "eager"
+            keep["rc"] = rc
+            out[name] = keep
+    return out
 
 
 # ---------------------------------------------------------------------- CPU arms ---
@@ -967,6 +1102,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + sorted(LONG_CONTEXT) + sorted(CONTIGUOUS) + ["c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-other-workloads", action="store_true",
+                    help="c3: only the headline workload (by default the line also carries c5, c3_strong and, at one "
+                         "GPU, c2 and c4 under `other_workloads`)")
     ap.add_argument("--e2e-group", type=int, default=6, help="layers per host<->device transfer in the end-to-end step")
     ap.add_argument("--exchange", default="fused", choices=["fused", "push", "nccl"],
                     help="long-context workloads: partials exchanged and merged inside the decode kernel (fused), "
@@ -984,16 +1122,34 @@ def main():
         sys.stderr.write("--impl reference times the batched paged decode workloads (%s) only; %s has no CPU arm\n"
                          % (", ".join(sorted(WORKLOADS)), args.workload))
         return 2
-    if args.workload == "c4":
-        return run_prefill(args)
-    if args.workload in CONTIGUOUS:
-        return run_contiguous_decode(args, CONTIGUOUS[args.workload])
-    if args.workload in LONG_CONTEXT:
-        return run_long_context(args, LONG_CONTEXT[args.workload])
+    if args.workload == "c4" or args.workload in CONTIGUOUS or args.workload in LONG_CONTEXT:
+        if args.workload == "c4":
+            rc = run_prefill(args)
+        elif args.workload in CONTIGUOUS:
+            rc = run_contiguous_decode(args, CONTIGUOUS[args.workload])
+        else:
+            rc = run_long_context(args, LONG_CONTEXT[args.workload])
+        rank_teardown()
+        return rc
     w = dict(WORKLOADS[args.workload])
     if args.impl == "reference":
         return run_reference(args, w)
-    return run_ours(args, w)
+    if args.workload != "c3" or args.no_other_workloads:
+        rc = run_ours(args, w)
+        rank_teardown()
+        return rc
+    # the headline line, with the other workloads of this run attached
+    global _COLLECT
+    _COLLECT = []
+    rc = run_ours(args, w)
+    headline = _COLLECT[0] if _COLLECT else None
+    _COLLECT = None
+    others = other_workloads(args)
+    rank_teardown()
+    if headline is not None:
+        headline["other_workloads"] = others
+        print(json.dumps(headline))
+    return rc
 
 
 if __name__ == "__main__":

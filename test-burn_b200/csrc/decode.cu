@@ -40,7 +40,7 @@ constexpr uint32_t kMergeFlight = 20;  // partials whose loads are in flight tog
 constexpr uint32_t kMergeFlightFew = 8;                // ... for units cut in at most this many parts
 
 
-template <int D, int NT, int STAGES>
+template <int D, int NT, int STAGES, bool CL = false>
 struct Smem {
     static constexpr uint32_t kHP = 8 * NT;                    // padded heads per group
     static constexpr uint32_t kTileBytes = kTileKeys * D * 2;  // one K or V tile
@@ -55,7 +55,13 @@ struct Smem {
     static constexpr uint32_t kMlBytes = kConsumerWarps * kHP * 2 * 4;
     static constexpr uint32_t kOffMerge = kOffMl + kMlBytes;
     static constexpr uint32_t kMergeBytes = kHP * 2 * 4;
-    static constexpr uint32_t kOffBar = kOffMerge + kMergeBytes;
+    // Cluster form: what the other CTAs of the cluster store here for this CTA to reduce.  [source CTA][the
+    // D / C dims this CTA owns][HP heads] accumulators (D * HP floats whatever the cluster size C) and
+    // [source CTA (up to 16)][HP] (m, l) pairs.  Dedicated: a fast CTA stores while a slow one still streams tiles.
+    static constexpr uint32_t kOffRecv = kOffMerge + kMergeBytes;
+    static constexpr uint32_t kRecvAccBytes = kHP * D * 4;
+    static constexpr uint32_t kRecvBytes = CL ? kRecvAccBytes + 16 * kHP * 2 * 4 : 0;  // only the cluster form has it
+    static constexpr uint32_t kOffBar = kOffRecv + kRecvBytes;
     static constexpr uint32_t kBarBytes = 2 * STAGES * 8;
     static constexpr uint32_t kOffFlags = kOffBar + kBarBytes;
     static constexpr uint32_t kTotal = kOffFlags + 16;
@@ -64,6 +70,7 @@ struct Smem {
 
 // Iterates the work items of one CTA, from the explicit plan or, for uniform
 // lengths, computed from the CTA index.
+template <bool CL>
 struct ItemCursor {
     const DecodeParams &p;
     uint32_t idx, end;       // explicit mode
@@ -71,8 +78,8 @@ struct ItemCursor {
     bool cluster_pending;    // cluster form: the one item of this CTA's cluster has not been handed out yet
     __device__ ItemCursor(const DecodeParams &pp, uint32_t cta) : p(pp)
     {
-        cluster_pending = p.cluster_size > 1;
-        if (cluster_pending) {
+        cluster_pending = CL;
+        if (CL) {
             idx = end = flat = flat_end = 0;
         } else if (p.items) {
             idx = p.cta_item_begin[cta];
@@ -86,7 +93,7 @@ struct ItemCursor {
     }
     __device__ bool next(WorkItem &it)
     {
-        if (p.cluster_size > 1) {
+        if (CL) {
             // One item per cluster; this CTA takes an equal share of its tiles (the first `rem` CTAs one more).
             if (!cluster_pending) return false;
             cluster_pending = false;
@@ -277,12 +284,12 @@ __device__ __forceinline__ void push_signal_and_merge(const DecodeParams &p, con
     }
 }
 
-template <int D, int NT, int STAGES, int MINB>
+template <int D, int NT, int STAGES, int MINB, bool CL = false>
 __global__ void __launch_bounds__(kThreads, MINB)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
               const DecodeParams p)
 {
-    using S = Smem<D, NT, STAGES>;
+    using S = Smem<D, NT, STAGES, CL>;
     constexpr uint32_t HP = S::kHP;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -324,7 +331,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         // appended with a separate kernel right before must the stream of tiles wait for it.
         if (!p.early_stream) grid_dependency_wait();
         const uint64_t policy = l2_policy_evict_first();
-        ItemCursor cur(p, blockIdx.x);
+        ItemCursor<CL> cur(p, blockIdx.x);
         WorkItem it;
         uint32_t stage = 0, phase = 0, issued = 0;
         while (cur.next(it)) {
@@ -412,7 +419,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     const uint32_t G = p.group;
     const uint32_t half_d = D / 2;
 
-    ItemCursor cur(p, blockIdx.x);
+    ItemCursor<CL> cur(p, blockIdx.x);
     WorkItem it;
     uint32_t stage = 0, phase = 0;
     while (cur.next(it)) {
@@ -665,16 +672,67 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
         const bool direct = (it.n_parts == 1);
         const bool partial_out = (p.out_acc != nullptr);
-        // Cluster form: this CTA's combined state goes to shared memory where the other CTAs of the cluster
-        // can read it.  The ring is idle by now (one item per CTA, every tile consumed): its first bytes
-        // hold [HP][D] accumulators and [HP] (m, l) pairs, m in the scaled log2 domain.
-        const bool cl = p.cluster_size > 1;
-        float *cl_acc = reinterpret_cast<float *>(smem);
-        float *cl_ml = cl_acc + HP * D;
+        // Cluster form: CTA r of the cluster owns the dims [r * D / C, (r + 1) * D / C) of every head.  Each CTA
+        // stores its combined accumulators straight into the owners' shared memory (and its (m, l) pairs into
+        // everybody's), m in the scaled log2 domain; after one cluster barrier every owner reduces locally.
+        constexpr bool cl = CL;  // a separate instantiation: the plain form carries none of this
+        const uint32_t C = cl ? p.cluster_size : 1u, crank = cl ? cluster_cta_rank() : 0u;
+        const uint32_t own_dims = D / C;  // C is a power of two up to 16
+        const uint32_t recv_acc_addr = smem_base + S::kOffRecv, recv_ml_addr = recv_acc_addr + S::kRecvAccBytes;
+        if (cl) {
+            // One item per CTA in this form, so the ring is idle by now: its first bytes take the four warps'
+            // accumulators at full width, in one pass.
+            constexpr uint32_t kFS = D + 4;  // floats per head row
+            float *cf = reinterpret_cast<float *>(smem);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint32_t h0 = nt * 8 + 2 * (lane & 3);
+                float *c0 = cf + (warp * HP + h0) * kFS;
+                float *c1 = c0 + kFS;
+#pragma unroll
+                for (int mt = 0; mt < D / 16; ++mt) {
+                    const uint32_t d0 = mt * 16 + (lane >> 2);
+                    c0[d0] = o[nt][mt][0] * fac[nt][0];
+                    c1[d0] = o[nt][mt][1] * fac[nt][1];
+                    c0[d0 + 8] = o[nt][mt][2] * fac[nt][0];
+                    c1[d0 + 8] = o[nt][mt][3] * fac[nt][1];
+                }
+            }
+            named_bar_sync(2, kConsumerThreads);
+            // this CTA's (m, l) of every head to every CTA of the cluster
+            for (uint32_t idx = tid; idx < C * HP; idx += kConsumerThreads) {
+                const uint32_t r = idx / HP, g = idx - r * HP;
+                float m_all = kNegSentinel;
+#pragma unroll
+                for (uint32_t w = 0; w < kConsumerWarps; ++w) m_all = fmaxf(m_all, ml_s[(w * HP + g) * 2]);
+                float l_all = 0.f;
+#pragma unroll
+                for (uint32_t w = 0; w < kConsumerWarps; ++w)
+                    l_all += ml_s[(w * HP + g) * 2 + 1] * fast_exp2(ml_s[(w * HP + g) * 2] - m_all);
+                st_cluster_f2(cluster_map_shared(recv_ml_addr + (crank * HP + g) * 8, r), m_all, l_all);
+            }
+            // four heads of one dim per thread: one 16-byte store into the owner's shared memory
+            for (uint32_t e = tid; e < (HP / 4) * D; e += kConsumerThreads) {
+                const uint32_t gq = e / D, d = e - gq * D;
+                if (gq * 4 >= G) continue;  // padded heads are never read
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (uint32_t w = 0; w < kConsumerWarps; ++w) {
+                    const float *c4 = cf + (w * HP + gq * 4) * kFS + d;
+                    acc.x += c4[0];
+                    acc.y += c4[kFS];
+                    acc.z += c4[2 * kFS];
+                    acc.w += c4[3 * kFS];
+                }
+                const uint32_t owner = d / own_dims, dl = d - owner * own_dims;
+                st_cluster_f4(cluster_map_shared(recv_acc_addr + ((crank * own_dims + dl) * HP + gq * 4) * 4, owner), acc);
+            }
+        }
         // The four warps' accumulators meet in shared memory, one half of the head dimension per
         // pass (the buffer is half-width so that two CTAs fit one SM).
 #pragma unroll
         for (int hp = 0; hp < 2; ++hp) {
+            if (cl) break;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 const uint32_t h0 = nt * 8 + 2 * (lane & 3);
@@ -703,13 +761,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                     acc += comb[(w * HP + g) * S::kCombStride + dd];
                 }
                 const uint32_t h = it.kvh * G + g;
-                if (cl) {
-                    cl_acc[g * D + d] = acc;
-                    if (d == 0) {
-                        cl_ml[g * 2] = m_all;
-                        cl_ml[g * 2 + 1] = l_all;
-                    }
-                } else if (!direct) {
+                if (!direct) {
                     p.part_acc[((size_t)it.slot * HP + g) * D + d] = acc;
                     if (d == 0) {
                         p.part_ml[((size_t)it.slot * HP + g) * 2] = m_all * kLn2;
@@ -742,84 +794,64 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             if (hp == 0) named_bar_sync(1, kConsumerThreads);  // pass 1 reuses the buffer
         }
         if (cl) {
-            // ---- the cluster's CTAs meet: each reduces a share of the (head, column) space over all of them ----
-            const uint32_t C = p.cluster_size, crank = cluster_cta_rank();
+            // ---- the cluster's CTAs meet: every store above has landed once all of them have arrived ----
+            __syncwarp();
             cluster_arrive_release();
             cluster_wait_acquire();
-            const uint32_t acc_addr = smem_base, ml_addr = smem_base + HP * D * 4;
-            const uint32_t n4 = G * (D / 4);
-            for (uint32_t i = crank + tid * C; i < n4; i += C * kConsumerThreads) {
-                const uint32_t g = i / (D / 4), d0 = (i - g * (D / 4)) * 4;
-                float2 ml[16];
-                float4 a[16];
-#pragma unroll
-                for (uint32_t r = 0; r < 16; ++r) {
-                    if (r < C) {
-                        ml[r] = ld_cluster_f2(cluster_map_shared(ml_addr + g * 8, r));
-                        a[r] = ld_cluster_f4(cluster_map_shared(acc_addr + (g * D + d0) * 4, r));
-                    } else {
-                        ml[r] = make_float2(kNegSentinel, 0.f);
-                        a[r] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
-                }
+            const float *racc = reinterpret_cast<const float *>(smem + S::kOffRecv);
+            const float2 *rml = reinterpret_cast<const float2 *>(smem + S::kOffRecv + S::kRecvAccBytes);
+            for (uint32_t col = tid; col < own_dims * HP; col += kConsumerThreads) {  // (dim, head) columns this CTA owns
+                const uint32_t g = col % HP, dl = col / HP, d = crank * own_dims + dl;
+                if (g >= G) continue;
                 float mx = kNegSentinel;
-#pragma unroll
-                for (uint32_t r = 0; r < 16; ++r) mx = fmaxf(mx, ml[r].x);
-                float lt = 0.f;
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (uint32_t r = 0; r < 16; ++r) {
-                    const float w = fast_exp2(ml[r].x - mx);
-                    lt += ml[r].y * w;
-                    acc.x += a[r].x * w;
-                    acc.y += a[r].y * w;
-                    acc.z += a[r].z * w;
-                    acc.w += a[r].w * w;
+#pragma unroll 4
+                for (uint32_t r = 0; r < C; ++r) mx = fmaxf(mx, rml[r * HP + g].x);
+                float lt = 0.f, acc = 0.f;
+#pragma unroll 4
+                for (uint32_t r = 0; r < C; ++r) {
+                    const float2 ml = rml[r * HP + g];
+                    const float w = fast_exp2(ml.x - mx);
+                    lt += ml.y * w;
+                    acc += racc[(r * own_dims + dl) * HP + g] * w;
                 }
                 const uint32_t h = it.kvh * G + g;
                 if (!direct) {
-                    // the cluster's partial of the unit: the last cluster of the unit merges (ticket below)
-                    *reinterpret_cast<float4 *>(p.part_acc + ((size_t)it.slot * HP + g) * D + d0) = acc;
-                    if (d0 == 0) *reinterpret_cast<float2 *>(p.part_ml + ((size_t)it.slot * HP + g) * 2) = make_float2(mx * kLn2, lt);
+                    // the cluster's partial of the unit; the CTA that completes the unit merges (ticket below)
+                    p.part_acc[((size_t)it.slot * HP + g) * D + d] = acc;
+                    if (d == 0) *reinterpret_cast<float2 *>(p.part_ml + ((size_t)it.slot * HP + g) * 2) = make_float2(mx * kLn2, lt);
                 } else if (p.push_world) {
                     const size_t rows = (size_t)p.batch * p.n_heads, rowi = (size_t)it.seq * p.n_heads + h;
                     for (uint32_t r = 0; r < p.push_world; ++r) {
-                        *reinterpret_cast<float4 *>(p.push_dst[r] + rowi * D + d0) = acc;
-                        if (d0 == 0) {
+                        p.push_dst[r][rowi * D + d] = acc;
+                        if (d == 0) {
                             p.push_dst[r][rows * D + rowi] = mx * kLn2;
                             p.push_dst[r][rows * D + rows + rowi] = lt;
                         }
                     }
                 } else if (partial_out) {
-                    *reinterpret_cast<float4 *>(p.out_acc + ((size_t)it.seq * p.n_heads + h) * D + d0) = acc;
-                    if (d0 == 0) {
+                    p.out_acc[((size_t)it.seq * p.n_heads + h) * D + d] = acc;
+                    if (d == 0) {
                         p.out_m[(size_t)it.seq * p.n_heads + h] = mx * kLn2;
                         p.out_l[(size_t)it.seq * p.n_heads + h] = lt;
                     }
                 } else {
                     const bool ok = (fabsf(lt) <= 3.0e38f) && fabsf(lt) > 1e-6f;
-                    const float inv = ok ? 1.0f / lt : 1.0f;  // decode rule: the sum itself when l is tiny
-                    float r4[4] = {acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv};
-                    __half *dst = p.out + (size_t)it.seq * p.out_stride_b + (size_t)h * p.out_stride_h + d0;
-#pragma unroll
-                    for (uint32_t e = 0; e < 4; ++e) {
-                        if (!(fabsf(r4[e]) <= 3.0e38f)) r4[e] = 0.f;
-                        dst[e] = __float2half_rn(r4[e]);
-                    }
+                    float r1 = ok ? acc / lt : acc;  // decode rule: the sum itself when l is tiny
+                    if (!(fabsf(r1) <= 3.0e38f)) r1 = 0.f;
+                    p.out[(size_t)it.seq * p.out_stride_b + (size_t)h * p.out_stride_h + d] = __float2half_rn(r1);
                 }
             }
-            // What this CTA stored for others (a partial slot, a peer's receive block) must be visible before
-            // the cluster's first CTA announces it; and nobody leaves while its shared memory is still read.
-            if (!direct) __threadfence();
-            else if (p.push_world) __threadfence_system();
-            __syncwarp();
-            cluster_arrive_release();
-            cluster_wait_acquire();
-            if (crank != 0) continue;
             if (direct) {
-                if (p.push_world) push_signal_and_merge<D>(p, it, tid, flags);
+                if (!p.push_world) continue;  // nobody reads another CTA's shared memory after the barrier: done
+                // every CTA's share of the unit must be in the peers' receive blocks before the first CTA announces it
+                __threadfence_system();
+                __syncwarp();
+                cluster_arrive_release();
+                cluster_wait_acquire();
+                if (crank == 0) push_signal_and_merge<D>(p, it, tid, flags);
                 continue;
             }
+            // not direct: every CTA of every cluster of the unit takes a ticket below; the last one merges
         } else if (direct) {
             if (p.push_world) push_signal_and_merge<D>(p, it, tid, flags);
             continue;
@@ -830,7 +862,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         named_bar_sync(1, kConsumerThreads);
         if (tid == 0) {
             const uint32_t old = atomicAdd(p.counters + it.unit, 1u);
-            const uint32_t last = (old + 1 == it.n_parts) ? 1u : 0u;
+            // cluster form: every CTA of the unit's clusters arrives with its own share of a partial
+            const uint32_t last = (old + 1 == it.n_parts * C) ? 1u : 0u;
             if (last) p.counters[it.unit] = 0;  // ready for the next launch
             flags[1] = last;
         }
@@ -937,11 +970,13 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 template <int D, int NT, int STAGES, int MINB>
 mf_status configure_one(MfContext *ctx, uint32_t *max_cluster_out)
 {
-    using S = Smem<D, NT, STAGES>;
-    static_assert(MINB * (S::kDynamic + 1024) <= 228 * 1024, "CTAs per SM do not fit shared memory");
+    using S = Smem<D, NT, STAGES, false>;
+    using SC = Smem<D, NT, STAGES, true>;
+    static_assert(MINB * (SC::kDynamic + 1024) <= 228 * 1024, "CTAs per SM do not fit shared memory");
     static bool configured[64] = {};
     static uint32_t max_cluster[64] = {};
-    auto kern = decode_kernel<D, NT, STAGES, MINB>;
+    auto kern = decode_kernel<D, NT, STAGES, MINB, false>;
+    auto kern_cl = decode_kernel<D, NT, STAGES, MINB, true>;
     const int dev = ctx->device;
     if (dev < 0 || dev >= 64) return fail(ctx, MF_ERR_INVALID_OPERATION, "device index %d", dev);
     if (!configured[dev]) {
@@ -949,14 +984,23 @@ mf_status configure_one(MfContext *ctx, uint32_t *max_cluster_out)
             ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic),
             "cudaFuncSetAttribute(decode)");
         if (st != MF_OK) return st;
+        st = check_cuda(ctx, cudaFuncSetAttribute(kern_cl, cudaFuncAttributeMaxDynamicSharedMemorySize, SC::kDynamic),
+                        "cudaFuncSetAttribute(decode, cluster form)");
+        if (st != MF_OK) return st;
+        int resident = 0, resident_cl = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kern, (int)kThreads, S::kDynamic) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident_cl, kern_cl, (int)kThreads, SC::kDynamic) != cudaSuccess ||
+            resident < MINB || resident_cl < MINB)
+            return fail(ctx, MF_ERR_CUDA, "decode kernel: %d / %d CTAs per SM fit, the variant is built for %d", resident,
+                        resident_cl, MINB);
         uint32_t best = 0;
-        const bool wide = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        const bool wide = cudaFuncSetAttribute(kern_cl, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
         for (uint32_t c : {16u, 8u}) {
             if (c == 16 && !wide) continue;
             cudaLaunchConfig_t cfg{};
             cfg.gridDim = dim3(c);
             cfg.blockDim = dim3(kThreads);
-            cfg.dynamicSmemBytes = S::kDynamic;
+            cfg.dynamicSmemBytes = SC::kDynamic;
             cudaLaunchAttribute attr[1];
             attr[0].id = cudaLaunchAttributeClusterDimension;
             attr[0].val.clusterDim.x = c;
@@ -965,7 +1009,7 @@ mf_status configure_one(MfContext *ctx, uint32_t *max_cluster_out)
             cfg.attrs = attr;
             cfg.numAttrs = 1;
             int n = 0;
-            if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n >= 1) {
+            if (cudaOccupancyMaxActiveClusters(&n, kern_cl, &cfg) == cudaSuccess && n >= 1) {
                 best = c;
                 break;
             }
@@ -982,8 +1026,9 @@ template <int D, int NT, int STAGES, int MINB>
 mf_status launch_one(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap &tm_v,
                      DecodeParams &p, uint32_t n_ctas, const void *writes_k, const void *writes_v)
 {
-    using S = Smem<D, NT, STAGES>;
-    auto kern = decode_kernel<D, NT, STAGES, MINB>;
+    const bool clustered = p.cluster_size > 1;
+    auto kern = clustered ? decode_kernel<D, NT, STAGES, MINB, true> : decode_kernel<D, NT, STAGES, MINB, false>;
+    const uint32_t smem_bytes = clustered ? Smem<D, NT, STAGES, true>::kDynamic : Smem<D, NT, STAGES, false>::kDynamic;
     mf_status st = configure_one<D, NT, STAGES, MINB>(ctx, nullptr);
     if (st != MF_OK) return st;
     if (p.cluster_size > 1 && n_ctas % p.cluster_size != 0)
@@ -994,7 +1039,7 @@ mf_status launch_one(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap 
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(n_ctas);
         cfg.blockDim = dim3(kThreads);
-        cfg.dynamicSmemBytes = S::kDynamic;
+        cfg.dynamicSmemBytes = smem_bytes;
         cfg.stream = ctx->stream;
         cudaLaunchAttribute attr[2];
         unsigned n_attr = 0;
@@ -1018,11 +1063,12 @@ mf_status launch_one(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap 
         if (programmatic) ctx->note_programmatic_launch(p.strict_release != 0, writes_k, writes_v);
         return MF_OK;
     }
-    kern<<<n_ctas, kThreads, S::kDynamic, ctx->stream>>>(tm_k, tm_v, p);
+    kern<<<n_ctas, kThreads, smem_bytes, ctx->stream>>>(tm_k, tm_v, p);
     return check_launch(ctx, "decode_kernel");
 }
 
 }  // namespace
+
 
 uint32_t decode_ctas_per_sm(const MfContext *ctx, uint32_t head_dim, uint32_t group)
 {

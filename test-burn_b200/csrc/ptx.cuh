@@ -188,9 +188,9 @@ __device__ __forceinline__ void grid_launch_dependents()
 }
 
 // ------------------------------------------------------- thread-block clusters ---
-// Rank of this CTA inside its cluster, the cluster barrier in its split (arrive / wait) form, and loads
-// from another CTA's shared memory (distributed shared memory): `local` is a shared-memory address of
-// this CTA, the load reads the same offset in CTA `rank` of the cluster.  Plain loads only.
+// Rank of this CTA inside its cluster, the cluster barrier in its split (arrive / wait) form, and plain
+// stores to / loads from another CTA's shared memory (distributed shared memory): `local` is a
+// shared-memory address of this CTA, cluster_map_shared gives the same offset in CTA `rank` of the cluster.
 __device__ __forceinline__ uint32_t cluster_cta_rank()
 {
     uint32_t r;
@@ -210,6 +210,18 @@ __device__ __forceinline__ uint32_t cluster_map_shared(uint32_t local, uint32_t 
     uint32_t remote;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
     return remote;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v)
+{
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void st_cluster_f4(uint32_t addr, float4 v)
+{
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void st_cluster_f2(uint32_t addr, float a, float b)
+{
+    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
 }
 __device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr)
 {
