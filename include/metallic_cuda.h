@@ -665,6 +665,46 @@ MF_API mf_status mf_prefix_cache_lookup(MfPrefixCache *cache, const uint32_t *pr
 MF_API mf_status mf_paged_copy_pages(MfContext *ctx, const MfPagedKv *cache, const uint32_t *src_ids,
                                      const uint32_t *dst_ids, uint32_t n);
 
+/* ---- 8-bit K/V cache (FP8 E4M3, one f32 scale per cached row) ------------------------
+ * The reference has only a roadmap for a quantised cache (docs/FLASH.md:121-186,
+ * docs/SAGE.md:1-60); the format here is this project's.  Pools [n_pages, n_kv_heads,
+ * page_size, 128] bytes for K and for V, every byte an OCP FP8 E4M3 value, and scale pools
+ * [n_pages, n_kv_heads, page_size] f32: for a row x (K after RoPE and f16 rounding, V as
+ * given) amax = max |x_i|, scale = amax / 448 (1 for an all-zero row), byte_i =
+ * e4m3 round-to-nearest-even, saturating, of x_i / scale; the cached value is byte * scale.
+ * head_dim 128 only, page_size a power of two in 8..64, GQA groups of up to 8 heads.
+ * Attention over it keeps the reference's contract with K := decoded bytes * row scale and
+ * V := dequantised rows; half the bytes of the f16 cache cross HBM per key. */
+typedef struct MfPagedKv8 {
+    void *k_pool;                /* device, bytes */
+    void *v_pool;
+    float *k_scales;             /* device, f32 */
+    float *v_scales;
+    const uint32_t *page_table;  /* device, [batch, page_table_stride] */
+    const uint32_t *kv_lens;     /* device, [batch] */
+    uint32_t n_pages;
+    uint32_t n_kv_heads;
+    uint32_t page_size;
+    uint32_t head_dim;           /* 128 */
+    uint32_t page_table_stride;
+    uint32_t batch;
+} MfPagedKv8;
+/* mf_paged_decode over the 8-bit cache: optional append (RoPE of k, row quantiser, pool and scale
+ * written) + RoPE of q + GQA flash-decode in one launch.  The plan must be in the plain form
+ * (created with an explicit CTA count or under MF_OPTION_DECODE_CLUSTERS = 1). */
+MF_API mf_status mf_paged_decode_kv8(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv8 *cache,
+                                     const MfPagedDecodeArgs *args);
+/* mf_paged_kv_append for the 8-bit cache (same arguments and q_rot layouts): seq == 0xFFFFFFFF
+ * appends one token per sequence at kv_lens[b] - 1, otherwise seq_len rows of sequence `seq`
+ * at position_offset (a prefill chunk). */
+MF_API mf_status mf_paged_kv8_append(MfContext *ctx, const MfPagedKv8 *cache, const void *q, const void *k,
+                                     const void *v, void *q_rot, const void *cos, const void *sin, uint32_t n_heads,
+                                     uint32_t rope_mode, uint32_t apply_rope, uint32_t seq, uint32_t position_offset,
+                                     uint32_t seq_len);
+/* The first `len` rows of one sequence, dequantised, as a contiguous [n_kv_heads, len, 128] f16 cache. */
+MF_API mf_status mf_paged_kv8_gather(MfContext *ctx, const MfPagedKv8 *cache, uint32_t use_v, uint32_t seq,
+                                     uint32_t len, void *out);
+
 /* ---- sequence-sharded decode with the exchange fused into the kernels ---------------
  * No counterpart in the reference.  Instead of all-gathering (acc, m, l) with a
  * library collective, the decode kernel of every rank stores each finished unit's

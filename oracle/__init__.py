@@ -38,6 +38,7 @@ u32p = np.ctypeslib.ndpointer(dtype=np.uint32, flags="C_CONTIGUOUS")
 f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
 f64p = np.ctypeslib.ndpointer(dtype=np.float64, flags="C_CONTIGUOUS")
 u32 = C.c_uint32
+u8p = np.ctypeslib.ndpointer(dtype=np.uint8, flags="C_CONTIGUOUS")
 
 _FAST_SRC = _HERE / "mf_oracle_fast.c"
 _FAST_LIB = None
@@ -141,6 +142,14 @@ def lib() -> C.CDLL:
                                    f64p]
     L.mfo_splitk_tile_range.argtypes = [u32, u32, u32, C.POINTER(u32), C.POINTER(u32)]
     L.mfo_merge_partials.argtypes = [f32p, f32p, f32p, u32, u32, u32, u16p]
+    L.mfo_e4m3_to_f32.argtypes = [C.c_uint8]
+    L.mfo_e4m3_to_f32.restype = C.c_float
+    L.mfo_f32_to_e4m3.argtypes = [C.c_float]
+    L.mfo_f32_to_e4m3.restype = C.c_uint8
+    L.mfo_quantize_row_e4m3.argtypes = [u16p, u32, u8p, C.POINTER(C.c_float)]
+    L.mfo_paged_kv8_append.argtypes = [u16p, u16p, u16p, u16p, u8p, u8p, f32p, f32p, u16p, u16p, u32p, u32, u32p, u32, u32,
+                                       u32, u32, u32, u32, C.c_int]
+    L.mfo_decode_kv8.argtypes = [u16p, u8p, u8p, f32p, f32p, u32p, u32, u32, u32, u32, u32, C.c_float, u16p, C.c_void_p]
     L.mfo_sdpa_materialized.argtypes = [u16p, u16p, u16p, u32, u32, u32, u32, u32, u32, C.c_uint64, C.c_uint64,
                                         C.c_uint64, C.c_uint64, C.c_int, u32, C.c_float, u16p]
     L.mfo_paged_decode_layer.argtypes = [u16p, u16p, u16p, u16p, u16p, u16p, u16p, u32p, u32, u32p,

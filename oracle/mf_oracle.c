@@ -752,6 +752,156 @@ void mfo_merge_partials(const float *acc, const float *m, const float *l, uint32
     }
 }
 
+/* ------------------------------------------------- 8-bit K/V cache (e4m3) ---
+ * Not in the reference, which only has a roadmap for a quantised cache (docs/FLASH.md:121-186,
+ * docs/SAGE.md:1-60).  Format defined by this project: K and V rows are stored as OCP FP8 E4M3
+ * ("e4m3fn": 4 exponent bits, bias 7, 3 mantissa bits, largest finite 448, no infinity, NaN =
+ * 0x7F) with one f32 scale per (page, kv head, row):
+ *     amax  = max_i |x_i|            (x = the f16 row: K after RoPE and f16 rounding, V as given)
+ *     scale = amax / 448  (1 when the row is all zeros)
+ *     q_i   = e4m3_rne_satfinite(x_i / scale)           (IEEE f32 division)
+ *     dequantised value = e4m3(q_i) * scale
+ * Attention over such a cache follows the reference's contract with K := the decoded bytes
+ * (products of the f16 q with the exactly-representable e4m3 values, f32 accumulation), the
+ * row's scale applied to the score in f32, and V := dequantised rows. */
+
+float mfo_e4m3_to_f32(uint8_t b)
+{
+    const uint32_t sign = b & 0x80u, exp = (b >> 3) & 0xFu, man = b & 7u;
+    float v;
+    if (exp == 0xFu && man == 7u) return NAN;
+    if (exp == 0) v = ldexpf((float)man, -9);               /* subnormal: man * 2^-3 * 2^-6 */
+    else v = ldexpf((float)(8u + man), (int)exp - 10);      /* (1 + man/8) * 2^(exp-7) */
+    return sign ? -v : v;
+}
+
+/* f32 -> e4m3, round to nearest even, finite inputs saturate at +-448, NaN -> 0x7F
+ * (the behaviour of cvt.rn.satfinite.e4m3x2.f32). */
+uint8_t mfo_f32_to_e4m3(float x)
+{
+    if (isnan(x)) return 0x7F;
+    const uint8_t sign = signbit(x) ? 0x80u : 0u;
+    float a = fabsf(x);
+    if (a >= 448.0f) return (uint8_t)(sign | 0x7E);
+    if (a < ldexpf(1.0f, -10)) return sign; /* below half of the smallest subnormal (2^-9): 0 (ties to even -> 0) */
+    int e;
+    (void)frexpf(a, &e);                     /* a = f * 2^e, f in [0.5, 1) */
+    int exp = e - 1;                         /* a = 1.xxx * 2^exp */
+    if (exp < -6) exp = -6;                  /* subnormal range shares the exponent -6 */
+    const float ulp = ldexpf(1.0f, exp - 3);
+    float q = a / ulp;                       /* exact: power-of-two division */
+    float r = rintf(q);                      /* current rounding mode: nearest even */
+    float v = r * ulp;
+    if (v >= 448.0f) return (uint8_t)(sign | 0x7E);
+    /* encode v */
+    if (v < ldexpf(1.0f, -6)) return (uint8_t)(sign | (uint8_t)(v / ldexpf(1.0f, -9)));
+    (void)frexpf(v, &e);
+    exp = e - 1;
+    const uint32_t man = (uint32_t)(v / ldexpf(1.0f, exp - 3)) - 8u;
+    return (uint8_t)(sign | ((uint32_t)(exp + 7) << 3) | man);
+}
+
+void mfo_quantize_row_e4m3(const uint16_t *x, uint32_t n, uint8_t *q, float *scale_out)
+{
+    h2f_init();
+    float amax = 0.0f;
+    for (uint32_t i = 0; i < n; ++i) {
+        const float a = fabsf(H2F(x[i]));
+        if (a > amax) amax = a;
+    }
+    const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
+    for (uint32_t i = 0; i < n; ++i) q[i] = mfo_f32_to_e4m3(H2F(x[i]) / scale);
+    *scale_out = scale;
+}
+
+/* One new token per sequence appended to 8-bit pools [n_pages, Hkv, P, D] (bytes) with scale pools
+ * [n_pages, Hkv, P] (f32): RoPE of q and k exactly as mfo_paged_kv_append, then the row quantiser. */
+void mfo_paged_kv8_append(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t *q_rot,
+                          uint8_t *k_pool, uint8_t *v_pool, float *k_scales, float *v_scales,
+                          const uint16_t *cos_t, const uint16_t *sin_t, const uint32_t *page_table,
+                          uint32_t pt_stride, const uint32_t *positions, uint32_t batch, uint32_t n_heads,
+                          uint32_t n_kv_heads, uint32_t head_dim, uint32_t page_size, uint32_t rope_mode,
+                          int apply_rope)
+{
+    h2f_init();
+    const uint32_t D = head_dim, half = D >> 1;
+    uint16_t row[512];
+    for (uint32_t b = 0; b < batch; ++b) {
+        const uint32_t pos = positions[b];
+        const uint16_t *c_row = cos_t + (size_t)pos * half, *s_row = sin_t + (size_t)pos * half;
+        for (uint32_t h = 0; h < n_heads; ++h) {
+            const uint16_t *src = q + ((size_t)b * n_heads + h) * D;
+            for (uint32_t hd = 0; hd < D; ++hd)
+                q_rot[((size_t)b * n_heads + h) * D + hd] = apply_rope ? rope_elem(src, c_row, s_row, hd, D, rope_mode) : src[hd];
+        }
+        const uint32_t page = page_table[(size_t)b * pt_stride + pos / page_size];
+        for (uint32_t kh = 0; kh < n_kv_heads; ++kh) {
+            const size_t r = ((size_t)page * n_kv_heads + kh) * page_size + pos % page_size;
+            const uint16_t *ks = k + ((size_t)b * n_kv_heads + kh) * D, *vs = v + ((size_t)b * n_kv_heads + kh) * D;
+            for (uint32_t hd = 0; hd < D; ++hd) row[hd] = apply_rope ? rope_elem(ks, c_row, s_row, hd, D, rope_mode) : ks[hd];
+            mfo_quantize_row_e4m3(row, D, k_pool + r * D, k_scales + r);
+            mfo_quantize_row_e4m3(vs, D, v_pool + r * D, v_scales + r);
+        }
+    }
+}
+
+/* Decode attention of one sequence over an 8-bit paged cache: per-key online softmax in the order of
+ * mfo_decode_online.  out is [Hq, D] f16 bits; gold (optional) the same in two-pass fp64 over the same
+ * quantised data, [Hq, D] doubles. */
+void mfo_decode_kv8(const uint16_t *q_rot, const uint8_t *k_pool, const uint8_t *v_pool, const float *k_scales,
+                    const float *v_scales, const uint32_t *page_table_row, uint32_t kv_len, uint32_t n_heads,
+                    uint32_t n_kv_heads, uint32_t head_dim, uint32_t page_size, float scale, uint16_t *out,
+                    double *gold)
+{
+    h2f_init();
+    const uint32_t D = head_dim, G = n_heads / n_kv_heads;
+    double *sc = gold ? (double *)malloc(sizeof(double) * (kv_len ? kv_len : 1)) : NULL;
+    for (uint32_t h = 0; h < n_heads; ++h) {
+        const uint32_t kh = h / G;
+        const uint16_t *qh = q_rot + (size_t)h * D;
+        float m = MFO_NEG_SENTINEL, l = 0.0f, acc[512];
+        for (uint32_t d = 0; d < D; ++d) acc[d] = 0.0f;
+        double gmax = -1e300;
+        for (uint32_t t = 0; t < kv_len; ++t) {
+            const size_t r = ((size_t)page_table_row[t / page_size] * n_kv_heads + kh) * page_size + t % page_size;
+            float dot = 0.0f;
+            double gdot = 0.0;
+            for (uint32_t d = 0; d < D; ++d) {
+                const float kd = mfo_e4m3_to_f32(k_pool[r * D + d]);
+                dot += H2F(qh[d]) * kd;
+                gdot += (double)H2F(qh[d]) * (double)kd;
+            }
+            float score = (dot * k_scales[r]) * scale;
+            if (!isfinite(score)) score = MFO_NEG_SENTINEL;
+            if (gold) {
+                sc[t] = gdot * (double)k_scales[r] * (double)scale;
+                if (sc[t] > gmax) gmax = sc[t];
+            }
+            /* online step (streaming.metal:20-52) with the dequantised V row */
+            const float mn = score > m ? score : m;
+            const float alpha = expf(m - mn), w = expf(score - mn);
+            l = l * alpha + w;
+            for (uint32_t d = 0; d < D; ++d)
+                acc[d] = acc[d] * alpha + w * (mfo_e4m3_to_f32(v_pool[r * D + d]) * v_scales[r]);
+            m = mn;
+        }
+        finish_decode_row(acc, l, D, out + (size_t)h * D);
+        if (gold) {
+            double lsum = 0.0;
+            for (uint32_t d = 0; d < D; ++d) gold[(size_t)h * D + d] = 0.0;
+            for (uint32_t t = 0; t < kv_len; ++t) {
+                const size_t r = ((size_t)page_table_row[t / page_size] * n_kv_heads + kh) * page_size + t % page_size;
+                const double w = exp(sc[t] - gmax);
+                lsum += w;
+                for (uint32_t d = 0; d < D; ++d)
+                    gold[(size_t)h * D + d] += w * (double)mfo_e4m3_to_f32(v_pool[r * D + d]) * (double)v_scales[r];
+            }
+            for (uint32_t d = 0; d < D; ++d) gold[(size_t)h * D + d] = lsum > 0.0 ? gold[(size_t)h * D + d] / lsum : 0.0;
+        }
+    }
+    if (sc) free(sc);
+}
+
 /* ------------------------------------------------- materialised attention ---
  * SdpaReferenceStep / execute_sdpa_reference (src/metals/sdpa/step.rs:558-779) with the
  * rounding points of its three dispatches:

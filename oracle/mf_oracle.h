@@ -213,6 +213,24 @@ void mfo_merge_partials(const float *acc, const float *m, const float *l,
                         uint32_t n_splits, uint32_t rows, uint32_t head_dim,
                         uint16_t *out);
 
+/* ---- 8-bit K/V cache (FP8 E4M3 with one f32 scale per cached row) --------------------
+ * Not in the reference (roadmap only: docs/FLASH.md:121-186).  Format and arithmetic are
+ * defined in mf_oracle.c above mfo_quantize_row_e4m3: scale = amax/448, q = rne_satfinite(x/scale),
+ * value = e4m3(q) * scale; scores = (q . decoded bytes) * row scale * softmax scale in f32. */
+float mfo_e4m3_to_f32(uint8_t b);
+uint8_t mfo_f32_to_e4m3(float x);
+void mfo_quantize_row_e4m3(const uint16_t *x, uint32_t n, uint8_t *q, float *scale_out);
+void mfo_paged_kv8_append(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t *q_rot,
+                          uint8_t *k_pool, uint8_t *v_pool, float *k_scales, float *v_scales,
+                          const uint16_t *cos_t, const uint16_t *sin_t, const uint32_t *page_table,
+                          uint32_t pt_stride, const uint32_t *positions, uint32_t batch, uint32_t n_heads,
+                          uint32_t n_kv_heads, uint32_t head_dim, uint32_t page_size, uint32_t rope_mode,
+                          int apply_rope);
+void mfo_decode_kv8(const uint16_t *q_rot, const uint8_t *k_pool, const uint8_t *v_pool, const float *k_scales,
+                    const float *v_scales, const uint32_t *page_table_row, uint32_t kv_len, uint32_t n_heads,
+                    uint32_t n_kv_heads, uint32_t head_dim, uint32_t page_size, float scale, uint16_t *out,
+                    double *gold);
+
 /* ---- materialised attention (src/metals/sdpa/step.rs:558-779,
  *      src/metals/softmax/softmax_sdpa_batched.metal:14-115) --------------------
  * The reference's fallback path with its own rounding points: S = scale*QK^T stored as

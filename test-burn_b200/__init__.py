@@ -106,6 +106,12 @@ class MfPagedKv(C.Structure):
                 ("batch", u32)]
 
 
+class MfPagedKv8(C.Structure):
+    _fields_ = [("k_pool", vp), ("v_pool", vp), ("k_scales", vp), ("v_scales", vp), ("page_table", vp), ("kv_lens", vp),
+                ("n_pages", u32), ("n_kv_heads", u32), ("page_size", u32), ("head_dim", u32), ("page_table_stride", u32),
+                ("batch", u32)]
+
+
 class KvRearrangeParamsResolved(C.Structure):
     _fields_ = [(n, u32) for n in ("kv_dim", "row_stride", "kv_head_dim", "n_heads", "n_kv_heads", "head_dim", "seq",
                                    "total_elements")]
@@ -197,6 +203,9 @@ _SIGNATURES = {
     "mf_decode_plan_items": (u32, [vp]),
     "mf_decode_plan_tiles": (u64, [vp]),
     "mf_paged_decode": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv), C.POINTER(MfPagedDecodeArgs)]),
+    "mf_paged_decode_kv8": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv8), C.POINTER(MfPagedDecodeArgs)]),
+    "mf_paged_kv8_append": (C.c_int32, [vp, C.POINTER(MfPagedKv8), vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32]),
+    "mf_paged_kv8_gather": (C.c_int32, [vp, C.POINTER(MfPagedKv8), u32, u32, u32, vp]),
     "mf_paged_kv_append": (C.c_int32, [vp, C.POINTER(MfPagedKv), vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32,
                                        u32]),
     "mf_paged_gather": (C.c_int32, [vp, C.POINTER(MfPagedKv), u32, u32, u32, vp]),
@@ -514,6 +523,23 @@ class Foundry:
     def paged_gather(self, cache: MfPagedKv, use_v: bool, seq: int, length: int, out):
         self.check(lib.mf_paged_gather(self._h, C.byref(cache), int(use_v), seq, length, _ptr(out)))
 
+    # -- 8-bit (FP8 E4M3) paged cache ------------------------------------------------------
+
+    def paged_decode_kv8(self, plan: "DecodePlan", cache: "MfPagedKv8", q, out, *, n_heads, scale=None, k=None, v=None,
+                         cos=None, sin=None, rope=False, rope_mode=ROPE_MODE_NEOX, append=False, q_rot=None):
+        scale = 1.0 / math.sqrt(cache.head_dim) if scale is None else scale
+        a = MfPagedDecodeArgs(_ptr(q), _ptr(k), _ptr(v), _ptr(q_rot), _ptr(out), _ptr(cos), _ptr(sin), n_heads,
+                              int(rope), rope_mode, int(append), scale)
+        self.check(lib.mf_paged_decode_kv8(self._h, plan._h, C.byref(cache), C.byref(a)))
+
+    def paged_kv8_append(self, cache: "MfPagedKv8", q, k, v, q_rot, cos, sin, *, n_heads, rope_mode=ROPE_MODE_NEOX,
+                         apply_rope=True, seq=ALL_SEQUENCES, position_offset=0, seq_len=0):
+        self.check(lib.mf_paged_kv8_append(self._h, C.byref(cache), _ptr(q), _ptr(k), _ptr(v), _ptr(q_rot), _ptr(cos),
+                                           _ptr(sin), n_heads, rope_mode, int(apply_rope), seq, position_offset, seq_len))
+
+    def paged_kv8_gather(self, cache: "MfPagedKv8", use_v: bool, seq: int, length: int, out):
+        self.check(lib.mf_paged_kv8_gather(self._h, C.byref(cache), int(use_v), seq, length, _ptr(out)))
+
 
 def flash_decode_static_scratch(stream, q, k, v, output, strides: MfFlashDecodeStrides, params: SdpaParams, n_heads,
                                 batch=1):
@@ -663,6 +689,15 @@ def paged_kv(k_pool, v_pool, page_table, kv_lens, *, n_kv_heads, page_size, head
     desc = MfPagedKv(k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(), kv_lens.data_ptr(), n_pages,
                      n_kv_heads, page_size, head_dim, page_table.shape[1], page_table.shape[0])
     desc._keep = (k_pool, v_pool, page_table, kv_lens)  # the descriptor holds raw pointers: keep their owners alive
+    return desc
+
+
+def paged_kv8(k_pool, v_pool, k_scales, v_scales, page_table, kv_lens, *, n_kv_heads, page_size) -> MfPagedKv8:
+    """Describe torch-owned 8-bit pools [n_pages, Hkv, P, 128] (uint8), their scale pools [n_pages, Hkv, P] (f32)
+    and a [batch, stride] page table."""
+    desc = MfPagedKv8(k_pool.data_ptr(), v_pool.data_ptr(), k_scales.data_ptr(), v_scales.data_ptr(), page_table.data_ptr(),
+                      kv_lens.data_ptr(), k_pool.shape[0], n_kv_heads, page_size, 128, page_table.shape[1], page_table.shape[0])
+    desc._keep = (k_pool, v_pool, k_scales, v_scales, page_table, kv_lens)
     return desc
 
 

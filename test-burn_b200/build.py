@@ -21,6 +21,7 @@ SOURCES = [
     HERE / "csrc" / "context.cu",
     HERE / "csrc" / "kv_append.cu",
     HERE / "csrc" / "decode.cu",
+    HERE / "csrc" / "decode_kv8.cu",
     HERE / "csrc" / "prefill.cu",
     HERE / "csrc" / "prefill_tc.cu",
     HERE / "csrc" / "attention_api.cu",

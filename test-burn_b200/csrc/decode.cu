@@ -731,8 +731,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         // The four warps' accumulators meet in shared memory, one half of the head dimension per
         // pass (the buffer is half-width so that two CTAs fit one SM).
 #pragma unroll
-        for (int hp = 0; hp < 2; ++hp) {
-            if (cl) break;
+        for (int hp = 0; hp < (cl ? 0 : 2); ++hp) {
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 const uint32_t h0 = nt * 8 + 2 * (lane & 3);

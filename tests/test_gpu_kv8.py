@@ -1,0 +1,202 @@
+"""GPU parity: the 8-bit (FP8 E4M3, one f32 scale per cached row) paged K/V cache.
+
+The reference has no quantised cache (a roadmap only: docs/FLASH.md:121-186); format and arithmetic are this
+project's and are restated in the oracle (oracle/mf_oracle.c, mfo_quantize_row_e4m3 and below).  Bars:
+  * the quantiser is bit-exact with the oracle: pool bytes and row scales after an append are equal;
+  * attention over a given quantised cache is within 2e-3 of the oracle's f32 online softmax and of the fp64
+    gold computed over the SAME quantised data (the error of the kernel, not of the format);
+  * the cost of the format itself - the 8-bit result against the f16-cache result on the same inputs - is
+    measured and bounded at 3e-2 for N(0,1) inputs (three mantissa bits per element: relative 2^-4 per value,
+    averaged over the keys a softmax mixes).
+"""
+import numpy as np
+import pytest
+
+import oracle
+from kvcases import PagedCase, dev, dev_u32, host, max_abs
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+FORMAT_TOL = 3e-2
+
+
+def quantised_pools(case):
+    """The case's f16 pools quantised row by row with the oracle: (k8, v8, ks, vs)."""
+    L = oracle.lib()
+    import ctypes as C
+
+    n_rows = case.n_pages * case.Hkv * case.P
+    out = []
+    for pool in (case.k_pool, case.v_pool):
+        q8 = np.zeros((n_rows, case.D), np.uint8)
+        sc = np.zeros(n_rows, np.float32)
+        rows = pool.reshape(n_rows, case.D)
+        for r in range(n_rows):
+            s = C.c_float()
+            L.mfo_quantize_row_e4m3(np.ascontiguousarray(rows[r]), case.D, q8[r], C.byref(s))
+            sc[r] = s.value
+        out.append((q8.reshape(case.n_pages, case.Hkv, case.P, case.D), sc.reshape(case.n_pages, case.Hkv, case.P)))
+    return out[0][0], out[1][0], out[0][1], out[1][1]
+
+
+def oracle_step(case, k8, v8, ks, vs):
+    """Append + attend with the oracle on the quantised cache.  Returns (q_rot, k8', v8', ks', vs', out, gold)."""
+    L = oracle.lib()
+    k8, v8, ks, vs = k8.copy(), v8.copy(), ks.copy(), vs.copy()
+    q_rot = np.empty_like(case.q)
+    L.mfo_paged_kv8_append(case.q, case.k, case.v, q_rot, k8.reshape(-1), v8.reshape(-1), ks.reshape(-1), vs.reshape(-1),
+                           case.cos, case.sin, case.page_table, case.pt_stride, case.cached, case.B, case.Hq, case.Hkv, case.D,
+                           case.P, case.rope_mode, 1)
+    out = np.empty((case.B, case.Hq * case.D), np.uint16)
+    gold = np.empty((case.B, case.Hq * case.D), np.float64)
+    for b in range(case.B):
+        L.mfo_decode_kv8(q_rot[b], k8.reshape(-1), v8.reshape(-1), ks.reshape(-1), vs.reshape(-1), case.page_table[b],
+                         int(case.kv_lens[b]), case.Hq, case.Hkv, case.D, case.P, float(case.scale), out[b],
+                         gold[b].ctypes.data)
+    return q_rot, k8, v8, ks, vs, out, gold
+
+
+CASES = [
+    dict(batch=6, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[0, 14, 15, 16, 63, 64]),
+    dict(batch=5, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[511, 1000, 2049, 3, 4095]),
+    dict(batch=4, n_heads=24, n_kv_heads=8, head_dim=128, page_size=64, cached=[0, 63, 64, 1337]),
+    dict(batch=2, n_heads=4, n_kv_heads=4, head_dim=128, page_size=8, cached=[77, 130]),
+    dict(batch=3, n_heads=8, n_kv_heads=1, head_dim=128, page_size=32, cached=[300, 127, 31]),
+]
+
+
+@pytest.mark.parametrize("cfg", CASES)
+@pytest.mark.parametrize("rope_mode", [0, 1])
+@pytest.mark.parametrize("max_ctas", [3, 296])
+def test_fused_append_decode_on_the_8bit_cache(mfk, foundry, cfg, rope_mode, max_ctas):
+    import torch
+
+    case = PagedCase(rope_mode=rope_mode, poison=False, **cfg)
+    k8, v8, ks, vs = quantised_pools(case)
+    # rows that were never written: NaN scales and 0xFF bytes (an E4M3 NaN), to prove they are never used
+    written = np.zeros((case.n_pages, case.P), bool)
+    for b in range(case.B):
+        for t in range(int(case.cached[b])):
+            written[case.page_table[b, t // case.P], t % case.P] = True
+    k8[~written[:, None, :].repeat(case.Hkv, 1)] = 0xFF
+    v8[~written[:, None, :].repeat(case.Hkv, 1)] = 0xFF
+    ks[~written[:, None, :].repeat(case.Hkv, 1)] = np.nan
+    vs[~written[:, None, :].repeat(case.Hkv, 1)] = np.nan
+    q_ref, k8_ref, v8_ref, ks_ref, vs_ref, out_ref, gold = oracle_step(case, k8, v8, ks, vs)
+    d_k8, d_v8 = torch.from_numpy(k8).cuda(), torch.from_numpy(v8).cuda()
+    d_ks, d_vs = torch.from_numpy(ks).cuda(), torch.from_numpy(vs).cuda()
+    pt, lens = dev_u32(case.page_table), dev_u32(case.kv_lens)
+    desc = mfk.paged_kv8(d_k8, d_v8, d_ks, d_vs, pt, lens, n_kv_heads=case.Hkv, page_size=case.P)
+    plan = foundry.decode_plan(case.kv_lens, n_heads=case.Hq, n_kv_heads=case.Hkv, head_dim=case.D, page_size=case.P,
+                               max_ctas=max_ctas)
+    out = torch.full((case.B, case.Hq * case.D), float("nan"), dtype=torch.float16, device="cuda")
+    q_rot = torch.full_like(out, float("nan"))
+    foundry.paged_decode_kv8(plan, desc, dev(case.q), out, n_heads=case.Hq, k=dev(case.k), v=dev(case.v), cos=dev(case.cos),
+                             sin=dev(case.sin), rope=True, rope_mode=rope_mode, append=True, q_rot=q_rot, scale=float(case.scale))
+    foundry.synchronize()
+    plan.close()
+    assert np.array_equal(host(q_rot), q_ref)
+    # the appended rows, bit-exact, and nothing else touched (NaN != NaN: compare the bit patterns of the scales)
+    assert np.array_equal(d_k8.cpu().numpy(), k8_ref) and np.array_equal(d_v8.cpu().numpy(), v8_ref)
+    assert np.array_equal(d_ks.cpu().numpy().view(np.uint32), ks_ref.view(np.uint32))
+    assert np.array_equal(d_vs.cpu().numpy().view(np.uint32), vs_ref.view(np.uint32))
+    assert max_abs(host(out), out_ref) <= TOL
+    assert max_abs(host(out), gold.ravel()) <= TOL
+
+
+def test_8bit_append_kernel_and_gather(mfk, foundry):
+    """The standalone quantising append (one token per sequence, and a chunk of rows of one sequence) against
+    the oracle's quantiser, bit for bit; the dequantising gather against e4m3 * scale rounded to f16."""
+    import torch
+
+    case = PagedCase(batch=3, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[100, 31, 700], poison=False)
+    k8, v8, ks, vs = quantised_pools(case)
+    q_ref, k8_ref, v8_ref, ks_ref, vs_ref, _, _ = oracle_step(case, k8, v8, ks, vs)
+    d = [torch.from_numpy(x).cuda() for x in (k8, v8, ks, vs)]
+    pt, lens = dev_u32(case.page_table), dev_u32(case.kv_lens)
+    desc = mfk.paged_kv8(*d, pt, lens, n_kv_heads=case.Hkv, page_size=case.P)
+    q_rot = torch.zeros((case.B, case.Hq * case.D), dtype=torch.float16, device="cuda")
+    for rope_mode in (0,):
+        foundry.paged_kv8_append(desc, dev(case.q), dev(case.k), dev(case.v), q_rot, dev(case.cos), dev(case.sin), n_heads=case.Hq,
+                                 rope_mode=rope_mode)
+    foundry.synchronize()
+    assert np.array_equal(host(q_rot), q_ref)
+    assert np.array_equal(d[0].cpu().numpy(), k8_ref) and np.array_equal(d[1].cpu().numpy(), v8_ref)
+    assert np.array_equal(d[2].cpu().numpy(), ks_ref) and np.array_equal(d[3].cpu().numpy(), vs_ref)
+    # gather: the dequantised rows of sequence 2
+    n = int(case.kv_lens[2])
+    got = torch.zeros((case.Hkv, n, case.D), dtype=torch.float16, device="cuda")
+    foundry.paged_kv8_gather(desc, False, 2, n, got)
+    foundry.synchronize()
+    L = oracle.lib()
+    lut = np.array([L.mfo_e4m3_to_f32(b) for b in range(256)], np.float32)
+    want = np.zeros((case.Hkv, n, case.D), np.float16)
+    for t in range(n):
+        page = case.page_table[2, t // case.P]
+        for h in range(case.Hkv):
+            want[h, t] = (lut[k8_ref[page, h, t % case.P]] * ks_ref[page, h, t % case.P]).astype(np.float16)
+    assert np.array_equal(host(got), want.view(np.uint16))
+    # a chunk of 40 rows of sequence 1 at position 32 (a prefill chunk), both RoPE modes
+    for rope_mode in (0, 1):
+        chunk = PagedCase(batch=2, n_heads=8, n_kv_heads=2, head_dim=128, page_size=16, cached=[10, 71], poison=False,
+                          rope_mode=rope_mode)
+        m, off = 40, 32
+        from kvcases import normal
+        qc = normal(901, m * 8 * 128).reshape(m, -1)
+        kc = normal(902, m * 2 * 128).reshape(m, -1)
+        vc = normal(903, m * 2 * 128).reshape(m, -1)
+        c8 = [np.zeros((chunk.n_pages, 2, 16, 128), np.uint8), np.zeros((chunk.n_pages, 2, 16, 128), np.uint8),
+              np.zeros((chunk.n_pages, 2, 16), np.float32), np.zeros((chunk.n_pages, 2, 16), np.float32)]
+        ref = [x.copy() for x in c8]
+        q_rows = np.zeros((m, 8 * 128), np.uint16)
+        # the oracle appends one token per "sequence": call it row by row for sequence 1
+        for s in range(m):
+            table = np.ascontiguousarray(chunk.page_table[1:2])
+            one_q = np.zeros((1, 8 * 128), np.uint16)
+            L.mfo_paged_kv8_append(qc[s:s + 1].copy(), kc[s:s + 1].copy(), vc[s:s + 1].copy(), one_q, ref[0].reshape(-1),
+                                   ref[1].reshape(-1), ref[2].reshape(-1), ref[3].reshape(-1), chunk.cos, chunk.sin, table,
+                                   chunk.pt_stride, np.array([off + s], np.uint32), 1, 8, 2, 128, 16, rope_mode, 1)
+            q_rows[s] = one_q[0]
+        dd = [torch.from_numpy(x).cuda() for x in c8]
+        desc2 = mfk.paged_kv8(*dd, dev_u32(chunk.page_table), dev_u32(chunk.kv_lens), n_kv_heads=2, page_size=16)
+        q_rot2 = torch.zeros((8, m, 128), dtype=torch.float16, device="cuda")
+        foundry.paged_kv8_append(desc2, dev(qc), dev(kc), dev(vc), q_rot2, dev(chunk.cos), dev(chunk.sin), n_heads=8,
+                                 rope_mode=rope_mode, seq=1, position_offset=off, seq_len=m)
+        foundry.synchronize()
+        for got8, want8 in zip(dd, ref):
+            assert np.array_equal(got8.cpu().numpy(), want8)
+        assert np.array_equal(host(q_rot2), q_rows.reshape(m, 8, 128).transpose(1, 0, 2))
+
+
+def test_cost_of_the_8bit_format(mfk, foundry):
+    """The same step on the f16 cache and on its 8-bit quantisation: the difference is the format's cost."""
+    import torch
+
+    case = PagedCase(batch=4, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[4095, 800, 12000, 300], poison=False)
+    ref16 = case.oracle_step()
+    k8, v8, ks, vs = quantised_pools(case)
+    d = [torch.from_numpy(x).cuda() for x in (k8, v8, ks, vs)]
+    desc = mfk.paged_kv8(*d, dev_u32(case.page_table), dev_u32(case.kv_lens), n_kv_heads=case.Hkv, page_size=case.P)
+    plan = foundry.decode_plan(case.kv_lens, n_heads=case.Hq, n_kv_heads=case.Hkv, head_dim=case.D, page_size=case.P, max_ctas=296)
+    out = torch.zeros((case.B, case.Hq * case.D), dtype=torch.float16, device="cuda")
+    foundry.paged_decode_kv8(plan, desc, dev(case.q), out, n_heads=case.Hq, k=dev(case.k), v=dev(case.v), cos=dev(case.cos),
+                             sin=dev(case.sin), rope=True, rope_mode=0, append=True, scale=float(case.scale))
+    foundry.synchronize()
+    plan.close()
+    err = max_abs(host(out), ref16[4].ravel())  # against the fp64 gold over the UNquantised cache
+    assert err <= FORMAT_TOL, err
+
+
+def test_8bit_cache_refuses_what_it_does_not_support(mfk, foundry):
+    import torch
+
+    z8 = torch.zeros((4, 2, 16, 128), dtype=torch.uint8, device="cuda")
+    zs = torch.zeros((4, 2, 16), dtype=torch.float32, device="cuda")
+    pt, lens = dev_u32(np.zeros((1, 4), np.uint32)), dev_u32(np.array([5], np.uint32))
+    desc = mfk.paged_kv8(z8, z8, zs, zs, pt, lens, n_kv_heads=2, page_size=16)
+    desc.head_dim = 64
+    q = torch.zeros((1, 16 * 64), dtype=torch.float16, device="cuda")
+    with pytest.raises(mfk.MetalError) as e:
+        foundry.paged_kv8_gather(desc, False, 0, 5, q)
+    assert e.value.kind == "OperationNotSupported"
+    foundry.synchronize()
