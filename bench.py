@@ -44,6 +44,11 @@ WORKLOADS = {
                theta=1e6, rope_mode=0,
                name="batched paged decode, Qwen2.5-3B shape: 36 layers, 16q/2kv heads, D128, batch 64, "
                     "ctx U[512,16384], page 16, fused rope+append+decode"),
+    "c3-kv8": dict(layers=36, n_heads=16, n_kv_heads=2, head_dim=128, batch=64, lo=512, hi=16384, page_size=16,
+                   theta=1e6, rope_mode=0, kv8=True,
+                   name="batched paged decode on the 8-bit cache (FP8 E4M3 + one f32 scale per row), Qwen2.5-3B shape: "
+                        "36 layers, 16q/2kv heads, D128, batch 64, ctx U[512,16384], page 16, fused rope+quantising "
+                        "append+decode"),
     "c3-small": dict(layers=4, n_heads=16, n_kv_heads=2, head_dim=128, batch=64, lo=512, hi=16384, page_size=16,
                      theta=1e6, rope_mode=0, name="c3 with 4 layers (profiling case)"),
     "c2-paged": dict(layers=28, n_heads=24, n_kv_heads=8, head_dim=128, batch=1, lo=8191, hi=8191, page_size=64,
@@ -104,9 +109,10 @@ def algorithmic_bytes_per_layer(w, kv_lens):
     """K and V read once per KV head (incl. the new row) + new k,v read + cache row write + q read,
     out write + cos/sin row + page ids."""
     hq, hkv, d, P = w["n_heads"], w["n_kv_heads"], w["head_dim"], w["page_size"]
+    row = d + 4 if w.get("kv8") else d * 2  # bytes of a cached row: e4m3 bytes + its f32 scale, or f16
     total = 0
     for L in kv_lens.astype(np.int64):
-        total += 2 * hkv * L * d * 2 + 2 * hkv * d * 2 + 2 * hkv * d * 2 + 2 * hq * d * 2 + 2 * (d // 2) * 2
+        total += 2 * hkv * L * row + 2 * hkv * d * 2 + 2 * hkv * row + 2 * hq * d * 2 + 2 * (d // 2) * 2
         total += 4 * ((L + P - 1) // P)
     return int(total)
 
@@ -117,7 +123,7 @@ def config_of(w):
     cached, kv_lens = make_lengths(w, SEED)
     P = w["page_size"]
     n_pages = int(((kv_lens + P - 1) // P).sum())
-    pool_gb = 2 * w["layers"] * n_pages * w["n_kv_heads"] * P * w["head_dim"] * 2 / 1e9
+    pool_gb = 2 * w["layers"] * n_pages * w["n_kv_heads"] * P * (w["head_dim"] + 4 if w.get("kv8") else w["head_dim"] * 2) / 1e9
     return {"workload": w["name"], "layers": w["layers"], "batch_per_gpu": w["batch"],
             "tokens_cached_per_gpu": int(cached.sum()), "pages_per_layer": n_pages, "seed": SEED,
             "seed_rule": "rank r uses seed + r", "l2": "inputs larger than L2 (KV pools %.1f GB per GPU)" % pool_gb}
@@ -188,8 +194,20 @@ def run_ours(args, w):
     gen = torch.Generator(device=dev)
     gen.manual_seed(seed)
     pool_elems = n_pages * hkv * P * d
-    k_pools = [torch.empty(pool_elems, dtype=torch.float16, device=dev).normal_(generator=gen) for _ in range(layers)]
-    v_pools = [torch.empty(pool_elems, dtype=torch.float16, device=dev).normal_(generator=gen) for _ in range(layers)]
+    kv8 = bool(w.get("kv8"))
+    if kv8:
+        # bytes of finite E4M3 values (exponent field below 15) with random signs; scales of N(0,1) rows (amax / 448)
+        def fp8_pool():
+            t = torch.randint(0, 0x78, (pool_elems,), dtype=torch.uint8, device=dev, generator=gen)
+            return t | (torch.randint(0, 2, (pool_elems,), dtype=torch.uint8, device=dev, generator=gen) << 7)
+
+        k_pools = [fp8_pool() for _ in range(layers)]
+        v_pools = [fp8_pool() for _ in range(layers)]
+        k_scales = [torch.full((pool_elems // d,), 3.5 / 448, dtype=torch.float32, device=dev) for _ in range(layers)]
+        v_scales = [torch.full((pool_elems // d,), 3.5 / 448, dtype=torch.float32, device=dev) for _ in range(layers)]
+    else:
+        k_pools = [torch.empty(pool_elems, dtype=torch.float16, device=dev).normal_(generator=gen) for _ in range(layers)]
+        v_pools = [torch.empty(pool_elems, dtype=torch.float16, device=dev).normal_(generator=gen) for _ in range(layers)]
     d_table = torch.from_numpy(table.view(np.int32)).to(dev)
     d_lens = torch.from_numpy(kv_lens.view(np.int32)).to(dev)
     cos_np, sin_np = mfk.rope_tables(w["theta"], d, int(kv_lens.max()))
@@ -211,14 +229,23 @@ def run_ours(args, w):
     f = mfk.Foundry(dev.index, stream.cuda_stream)
     if not args.no_overlap:
         f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 1)
-    plan = f.decode_plan(kv_lens, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P)
-    descs = [mfk.paged_kv(k_pools[i].view(n_pages, hkv, P, d), v_pools[i].view(n_pages, hkv, P, d), d_table, d_lens,
-                          n_kv_heads=hkv, page_size=P, head_dim=d) for i in range(layers)]
+    if kv8:
+        plan = f.decode_plan(kv_lens, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P,
+                             max_ctas=2 * torch.cuda.get_device_properties(dev).multi_processor_count)
+        descs = [mfk.paged_kv8(k_pools[i].view(n_pages, hkv, P, d), v_pools[i].view(n_pages, hkv, P, d),
+                               k_scales[i].view(n_pages, hkv, P), v_scales[i].view(n_pages, hkv, P), d_table, d_lens,
+                               n_kv_heads=hkv, page_size=P) for i in range(layers)]
+        decode = f.paged_decode_kv8
+    else:
+        plan = f.decode_plan(kv_lens, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P)
+        descs = [mfk.paged_kv(k_pools[i].view(n_pages, hkv, P, d), v_pools[i].view(n_pages, hkv, P, d), d_table, d_lens,
+                              n_kv_heads=hkv, page_size=P, head_dim=d) for i in range(layers)]
+        decode = f.paged_decode
     scale = 1.0 / math.sqrt(d)
 
     def device_step():
         for i in range(layers):
-            f.paged_decode(plan, descs[i], d_q[i], d_out[i], n_heads=hq, k=d_k[i], v=d_v[i], cos=d_cos, sin=d_sin,
+            decode(plan, descs[i], d_q[i], d_out[i], n_heads=hq, k=d_k[i], v=d_v[i], cos=d_cos, sin=d_sin,
                            rope=True, rope_mode=w["rope_mode"], append=True, scale=scale)
 
     # End-to-end step: host inputs -> device -> host results, through the same C-ABI calls.  The page
@@ -273,7 +300,7 @@ def run_ours(args, w):
             stream.wait_event(ev_out_free[s])
             for i in range(l0, l1):
                 j = i - l0
-                f.paged_decode(plan, descs[i], e2e_q[s][j], e2e_out[s, j], n_heads=hq, k=e2e_k[s][j], v=e2e_v[s][j],
+                decode(plan, descs[i], e2e_q[s][j], e2e_out[s, j], n_heads=hq, k=e2e_k[s][j], v=e2e_v[s][j],
                                cos=d_cos, sin=d_sin, rope=True, rope_mode=w["rope_mode"], append=True, scale=scale)
             ev_done[s].record(stream)
             with torch.cuda.stream(copy_out):
@@ -346,16 +373,17 @@ def run_ours(args, w):
     result = {
         "metric": METRIC, "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "us_per_step": ms_step * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 storage, f32 accumulate" if kv8 else "f16 storage, f32 accumulate",
         "data": "synthetic",
         "config": config_of(w),
         "plan": {"ctas": plan.ctas, "work_items": plan.items},
         "hbm_tb_s": achieved / 1e3,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": peak_kind, "kernel": "decode_kernel<128,1,3,2>", "launch_us": launch_us,
+                     "peak_kind": peak_kind, "kernel": "decode_kv8_kernel" if kv8 else "decode_kernel<128,1,3,2>",
+                     "launch_us": launch_us,
                      "algorithmic_bytes_per_launch": bytes_layer,
                      "traffic": (bytes_layer * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE
-                                 if NCU_TRAFFIC_PER_ALGORITHMIC_BYTE else None)},
+                                 if NCU_TRAFFIC_PER_ALGORITHMIC_BYTE and not kv8 else None)},
         "e2e": {"value": B * world / (ms_step_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_step_e2e,
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
         "gpu_launches": int(launches),
@@ -363,7 +391,7 @@ def run_ours(args, w):
         "step_spread_ms": {"n": n_stat, "min": float(per_step.min()), "median": float(np.median(per_step)),
                            "mean": float(per_step.mean()), "sd": float(per_step.std())},
     }
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not kv8:  # the CPU arm is the f16 cache's
         result["cpu_baseline"] = cpu_baseline(w, steps=3)
     # Sanity on the timed buffers: the last layer's output is finite and the end-to-end output equals it.
     torch.cuda.synchronize()

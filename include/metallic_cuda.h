@@ -761,6 +761,22 @@ MF_API mf_status mf_paged_decode_partial_push(MfContext *ctx, const MfDecodePlan
 MF_API mf_status mf_paged_decode_push_merge(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv *cache,
                                             const MfPagedDecodeArgs *args, const uint32_t *rope_positions,
                                             const MfPeerExchange *px, uint32_t step, uint32_t pusher_mask);
+/* The same exchange through a library collective (the baseline the fused route is measured against,
+ * and the route for hosts that already run NCCL): every rank passes its own block `mine` =
+ * [acc rows*head_dim | m rows | l rows] f32 (what mf_paged_decode_partial wrote, laid out in one
+ * buffer), the blocks of all ranks are all-gathered into `gathered` (world blocks) on the context's
+ * stream with ncclAllGather on the caller's communicator `comm` (an ncclComm_t), and the log-sum-exp
+ * merge of flash_prefill.metal:843-888 writes out [rows, head_dim] f16 on every rank.  The library
+ * does not link NCCL: the symbol is taken from the process (or libnccl.so.2 is loaded) at first use;
+ * MF_ERR_NCCL when it is not there or the collective returns an error. */
+MF_API mf_status mf_allgather_merge(MfContext *ctx, void *comm, const float *mine, float *gathered, uint32_t world,
+                                    uint32_t rows, uint32_t head_dim, void *out);
+/* Replaces ncclAllGather in mf_allgather_merge by the caller's function (another collective library, a
+ * statically linked NCCL, a test double): it gathers count_floats f32 per rank from send into recv on
+ * `stream` and returns 0 on success.  NULL restores the default. */
+typedef int (*MfAllGatherFn)(const void *send, void *recv, uint64_t count_floats, void *comm, void *stream);
+MF_API mf_status mf_context_set_allgather(MfContext *ctx, MfAllGatherFn fn);
+
 /* units_per_rank[r]: (batch x kv head) units rank r pushes per step (0 for a rank that
  * holds no keys); rows = batch * n_heads; out is [rows, head_dim] f16. */
 MF_API mf_status mf_merge_pushed(MfContext *ctx, const MfPeerExchange *px, const uint32_t *units_per_rank,

@@ -42,6 +42,9 @@ OPTION_OVERLAP_LAUNCHES, OPTION_DECODE_STAGES, OPTION_PREFILL_IMPL, OPTION_DECOD
 KV_LAYOUT_EXPANDED_HEADS, KV_LAYOUT_COMPACT_KV_HEADS = 0, 1
 
 
+ALLGATHER_FN = C.CFUNCTYPE(C.c_int, vp, vp, u64, vp, vp)
+
+
 class MetalError(RuntimeError):
     """Raised for any non-zero mf_status; `.kind` is the MetalError variant name."""
 
@@ -237,6 +240,8 @@ _SIGNATURES = {
     "mf_peer_exchange_destroy": (C.c_int32, [vp, C.POINTER(MfPeerExchange)]),
     "mf_paged_decode_push_merge": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv), C.POINTER(MfPagedDecodeArgs), vp,
                                                C.POINTER(MfPeerExchange), u32, u32]),
+    "mf_allgather_merge": (C.c_int32, [vp, vp, vp, vp, u32, u32, u32, vp]),
+    "mf_context_set_allgather": (C.c_int32, [vp, vp]),
     "mf_merge_pushed": (C.c_int32, [vp, C.POINTER(MfPeerExchange), vp, u32, u32, u32, vp]),
     "mf_paged_decode_partial": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv), C.POINTER(MfPagedDecodeArgs), vp, vp, vp,
                                             vp]),
@@ -468,6 +473,14 @@ class Foundry:
                               rope_mode, int(append), scale)
         self.check(lib.mf_paged_decode_push_merge(self._h, plan._h, C.byref(cache), C.byref(a), _ptr(rope_positions),
                                                   C.byref(px), step, pusher_mask))
+
+    def allgather_merge(self, comm, mine, gathered, rows, head_dim, out):
+        """mf_allgather_merge: `mine` [rows*(head_dim+2)] f32, `gathered` [world, rows*(head_dim+2)] f32."""
+        self.check(lib.mf_allgather_merge(self._h, comm, _ptr(mine), _ptr(gathered), gathered.shape[0], rows, head_dim, _ptr(out)))
+
+    def set_allgather(self, fn):
+        """fn: a ctypes callback ALLGATHER_FN (kept alive by the caller) or None."""
+        self.check(lib.mf_context_set_allgather(self._h, C.cast(fn, vp) if fn is not None else None))
 
     def merge_pushed(self, px: MfPeerExchange, units_per_rank, step: int, rows: int, head_dim: int, out):
         arr = (u32 * 8)(*list(units_per_rank) + [0] * (8 - len(units_per_rank)))

@@ -186,6 +186,7 @@ struct MfContext {
         }
     }
     uint32_t decode_stages = 0;     // MF_OPTION_DECODE_STAGES (0 = default)
+    void *allgather_fn = nullptr;   // mf_context_set_allgather: replaces ncclAllGather in mf_allgather_merge
     uint32_t decode_clusters = 0;   // MF_OPTION_DECODE_CLUSTERS: 0 = the library decides, 1 = never
     uint32_t prefill_impl = 0;      // MF_OPTION_PREFILL_IMPL: 0 auto, 1 mma.sync, 2 tcgen05 only
 };

@@ -2,6 +2,7 @@
 // kernel stores its partials into (over NVLink, through CUDA IPC mappings), and the merge
 // kernel that waits for them.  No counterpart in the reference, whose engine is one GPU.
 #include <cuda_fp16.h>
+#include <dlfcn.h>
 
 #include "internal.hpp"
 #include "ptx.cuh"
@@ -155,6 +156,51 @@ mf_status mf_peer_exchange_destroy(MfContext *ctx, MfPeerExchange *px)
     }
     memset(px, 0, sizeof(*px));
     return MF_OK;
+}
+
+// ---- the library-collective route: ncclAllGather of every rank's [acc | m | l] block, then the merge ----
+
+mf_status mf_context_set_allgather(MfContext *ctx, MfAllGatherFn fn)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    ctx->allgather_fn = reinterpret_cast<void *>(fn);
+    return MF_OK;
+}
+
+// ncclAllGather of the NCCL library this process already uses (or can load), bound at first use: the library
+// itself does not link NCCL.
+static int nccl_all_gather(const void *send, void *recv, uint64_t count_floats, void *comm, void *stream)
+{
+    typedef int (*Fn)(const void *, void *, size_t, int, void *, cudaStream_t);
+    static Fn fn = nullptr;
+    static bool looked = false;
+    if (!looked) {
+        looked = true;
+        void *sym = dlsym(RTLD_DEFAULT, "ncclAllGather");
+        if (!sym) {
+            if (void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL)) sym = dlsym(h, "ncclAllGather");
+        }
+        fn = reinterpret_cast<Fn>(sym);
+    }
+    if (!fn) return -1;
+    return fn(send, recv, (size_t)count_floats, 7 /* ncclFloat32 */, comm, static_cast<cudaStream_t>(stream));
+}
+
+mf_status mf_allgather_merge(MfContext *ctx, void *comm, const float *mine, float *gathered, uint32_t world, uint32_t rows,
+                             uint32_t head_dim, void *out)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!mine || !gathered || !out) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "all-gather merge: null buffer");
+    if (world == 0 || rows == 0 || head_dim == 0) return fail(ctx, MF_ERR_INVALID_OPERATION, "all-gather merge: world %u, rows %u", world, rows);
+    const uint64_t block = (uint64_t)rows * (head_dim + 2);
+    MfAllGatherFn fn = ctx->allgather_fn ? reinterpret_cast<MfAllGatherFn>(ctx->allgather_fn) : nccl_all_gather;
+    if (!ctx->allgather_fn && !comm) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "all-gather merge: communicator");
+    const int rc = fn(mine, gathered, block, comm, ctx->stream);
+    if (rc != 0)
+        return fail(ctx, MF_ERR_NCCL, rc == -1 && !ctx->allgather_fn ? "all-gather merge: ncclAllGather is not available in this process"
+                                                                      : "all-gather merge: the all-gather failed (code %d)", rc);
+    return mf_merge_partials_strided(ctx, gathered, gathered + (uint64_t)rows * head_dim, gathered + (uint64_t)rows * head_dim + rows,
+                                     world, rows, head_dim, block, out);
 }
 
 mf_status mf_merge_pushed(MfContext *ctx, const MfPeerExchange *px, const uint32_t *units_per_rank, uint32_t step,

@@ -157,6 +157,21 @@ def _two_gpu_worker(rank, world, port, ret):
                                           scale=float(full.scale))
             f.synchronize()
             ok = ok and max_abs(host(out), out_ref) <= TOL and max_abs(host(out), gold.ravel()) <= TOL
+        # the library-collective route on the same shards: partial blocks, ncclAllGather, merge
+        lib = _nccl()
+        if lib is not None:
+            ids = [_nccl_comm(lib, -1, 0) if rank == 0 else None]
+            dist.broadcast_object_list(ids, src=0)
+            comm = _nccl_comm(lib, world, rank, ids[0])
+            block = Hq * (D + 2)
+            mine = torch.zeros(block, dtype=torch.float32, device="cuda")
+            gathered = torch.zeros((world, block), dtype=torch.float32, device="cuda")
+            out = torch.full((Hq, D), float("nan"), dtype=torch.float16, device="cuda")
+            f.paged_decode_partial(plan, desc, q_rot, mine[:Hq * D].view(1, Hq, D), mine[Hq * D:Hq * D + Hq], mine[Hq * D + Hq:],
+                                   n_heads=Hq, scale=float(full.scale))
+            f.allgather_merge(comm, mine, gathered, Hq, D, out)
+            f.synchronize()
+            ok = ok and max_abs(host(out), out_ref) <= TOL and max_abs(host(out), gold.ravel()) <= TOL
         plan.close()
         dist.barrier()  # nobody unmaps while a peer may still store
         f.peer_exchange_destroy(px)
@@ -226,3 +241,111 @@ def test_a_rank_that_only_merges_holds_the_pushers_back(mfk, foundry):
         o = 1 - r
         pxs[r].recv[o] = pxs[r].counters[o] = None
         foundry.peer_exchange_destroy(pxs[r])
+
+
+def _nccl():
+    """The NCCL library of this Python environment through ctypes (None if it cannot be found), loaded globally
+    so that the product library's lookup of ncclAllGather finds the same instance."""
+    import ctypes as C
+    import glob
+
+    try:
+        import nvidia.nccl as pkg
+
+        paths = glob.glob(os.path.join(list(pkg.__path__)[0], "lib", "libnccl.so*"))
+    except Exception:
+        paths = []
+    for path in paths + ["libnccl.so.2"]:
+        try:
+            return C.CDLL(path, mode=C.RTLD_GLOBAL)
+        except OSError:
+            continue
+    return None
+
+
+def _nccl_comm(lib, world, rank, unique_id=None):
+    import ctypes as C
+
+    class UniqueId(C.Structure):
+        _fields_ = [("internal", C.c_char * 128)]
+
+    uid = UniqueId()
+    if unique_id is None:
+        assert lib.ncclGetUniqueId(C.byref(uid)) == 0
+    else:
+        C.memmove(C.byref(uid), unique_id, 128)
+    if world < 0:
+        return bytes(uid.internal)
+    comm = C.c_void_p()
+    lib.ncclCommInitRank.argtypes = [C.POINTER(C.c_void_p), C.c_int, UniqueId, C.c_int]
+    assert lib.ncclCommInitRank(C.byref(comm), world, uid, rank) == 0
+    return comm
+
+
+def test_allgather_merge_route(mfk, foundry):
+    """The library-collective route on one GPU: two shards' partial blocks, an all-gather and the merge.  The
+    all-gather is (1) a test double installed with mf_context_set_allgather, which also lets the failure of
+    the collective be produced on the host (an error code from the fake: NcclError, nothing written), and
+    (2) the real ncclAllGather on a communicator of one rank."""
+    import ctypes as C
+
+    import torch
+
+    Hq, Hkv, D, P, L = 24, 8, 128, 64, 3000
+    full = PagedCase(batch=1, n_heads=Hq, n_kv_heads=Hkv, head_dim=D, page_size=P, cached=[L - 1], poison=False)
+    q_ref, kp, vp, out_ref, gold = full.oracle_step()
+    dk, dv, q_rot = dev(kp), dev(vp), dev(q_ref)
+    n_pages = full.page_table.shape[1]
+    cut = n_pages // 2
+    block = Hq * (D + 2)
+    blocks = torch.zeros((2, block), dtype=torch.float32, device="cuda")
+    keep = []
+    for r, (p0, p1) in enumerate([(0, cut), (cut, n_pages)]):
+        desc, plan, k = _shard_inputs(mfk, foundry, full, dk, dv, p0, p1, L)
+        keep.append((desc, plan, k))
+        b = blocks[r]
+        foundry.paged_decode_partial(plan, desc, q_rot, b[:Hq * D].view(1, Hq, D), b[Hq * D:Hq * D + Hq], b[Hq * D + Hq:],
+                                     n_heads=Hq, scale=float(full.scale))
+    foundry.synchronize()
+    gathered = torch.zeros((2, block), dtype=torch.float32, device="cuda")
+    out = torch.full((Hq, D), float("nan"), dtype=torch.float16, device="cuda")
+    calls = []
+
+    def fake(send, recv, count, comm, stream):
+        calls.append((count, comm))
+        assert send == blocks[0].data_ptr() and recv == gathered.data_ptr()
+        gathered.copy_(blocks)  # what an all-gather over the two ranks delivers
+        return 0
+
+    cb = mfk.ALLGATHER_FN(fake)
+    foundry.set_allgather(cb)
+    foundry.allgather_merge(0x1234, blocks[0], gathered, Hq, D, out)
+    foundry.synchronize()
+    assert calls == [(block, 0x1234)]
+    assert max_abs(host(out), out_ref) <= TOL and max_abs(host(out), gold.ravel()) <= TOL
+    # the collective fails: the status names it, the output is not touched
+    bad = mfk.ALLGATHER_FN(lambda send, recv, count, comm, stream: 5)
+    foundry.set_allgather(bad)
+    out.fill_(3.0)
+    with pytest.raises(mfk.MetalError) as e:
+        foundry.allgather_merge(0x1234, blocks[0], gathered, Hq, D, out)
+    assert e.value.kind == "NcclError" and "code 5" in str(e.value)
+    foundry.synchronize()
+    assert bool((out == 3.0).all())
+    foundry.set_allgather(None)
+    # the real thing, one rank: gathering one block and merging it normalises that block
+    lib = _nccl()
+    if lib is not None:
+        comm = _nccl_comm(lib, 1, 0)
+        one = torch.zeros((1, block), dtype=torch.float32, device="cuda")
+        foundry.allgather_merge(comm, blocks[1], one, Hq, D, out)
+        foundry.synchronize()
+        want = torch.empty((Hq, D), dtype=torch.float16, device="cuda")
+        b = blocks[1]
+        foundry.merge_partials(b[:Hq * D].view(1, Hq, D), b[Hq * D:Hq * D + Hq].view(1, Hq), b[Hq * D + Hq:].view(1, Hq), want)
+        foundry.synchronize()
+        assert torch.equal(one[0], blocks[1]) and np.array_equal(host(out), host(want))
+        lib.ncclCommDestroy.argtypes = [C.c_void_p]
+        lib.ncclCommDestroy(comm)
+    for _, plan, _ in keep:
+        plan.close()
