@@ -49,6 +49,8 @@ WORKLOADS = {
                    name="batched paged decode on the 8-bit cache (FP8 E4M3 + one f32 scale per row), Qwen2.5-3B shape: "
                         "36 layers, 16q/2kv heads, D128, batch 64, ctx U[512,16384], page 16, fused rope+quantising "
                         "append+decode"),
+    "c3-kv8-small": dict(layers=4, n_heads=16, n_kv_heads=2, head_dim=128, batch=64, lo=512, hi=16384, page_size=16,
+                         theta=1e6, rope_mode=0, kv8=True, name="c3-kv8 with 4 layers (profiling case)"),
     "c3-small": dict(layers=4, n_heads=16, n_kv_heads=2, head_dim=128, batch=64, lo=512, hi=16384, page_size=16,
                      theta=1e6, rope_mode=0, name="c3 with 4 layers (profiling case)"),
     "c2-paged": dict(layers=28, n_heads=24, n_kv_heads=8, head_dim=128, batch=1, lo=8191, hi=8191, page_size=64,

@@ -88,7 +88,9 @@ mf_status decode_contiguous(MfContext *ctx, const void *q, const void *k, const 
     const uint64_t total = (uint64_t)U * T;
     if (total > 0xFFFFFFFFull) return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "FlashDecode: too many tiles");
     const uint32_t want = decode_cta_target((uint32_t)ctx->sm_count, decode_ctas_per_sm(ctx, D, group), total);
-    const UniformSplit split = uniform_split(U, T, n_splits, want, decode_max_cluster(ctx, D, group));
+    // The cluster form only for launches of at most one CTA per SM: larger ones fill the GPU on their own, and
+    // clusters, which must be placed sixteen CTAs at a time, then delay the launch behind them.
+    const UniformSplit split = uniform_split(U, T, n_splits, want, want <= (uint32_t)ctx->sm_count ? decode_max_cluster(ctx, D, group) : 0u);
     const uint32_t span = split.span, n_ctas = split.n_ctas;
 
     const uint64_t slot_bytes = partial_slot_bytes(group, D);
@@ -587,7 +589,9 @@ mf_status mf_decode_plan_update(MfContext *ctx, MfDecodePlan *pl, const uint32_t
     }
     // the cluster form only for plans whose CTA count the library chooses (an explicit count is a request for
     // exactly that many spans)
-    pl->cluster = pl->auto_ctas ? pl->max_cluster : 0;
+    // ... and for launches of at most one CTA per SM: larger ones fill the GPU on their own, and clusters, which
+    // must be placed sixteen CTAs at a time, then delay the launch behind them
+    pl->cluster = (pl->auto_ctas && ctas <= pl->sm_count) ? pl->max_cluster : 0;
     build_decode_plan(kv_lens_host, pl->batch, pl->n_kv_heads, ctas, pl->h_items, pl->h_cta_begin, &pl->n_units,
                       &pl->total_tiles, &pl->cluster);
     return plan_upload(ctx, pl);

@@ -24,8 +24,10 @@
 //    the same way for the q fragment; for V the transposing ldmatrix delivers (key, key+1) x (dim,
 //    dim+1) blocks, a byte permute separates the two dims, and the MMA's row order is permuted
 //    (row r <-> dim 2r, row r+8 <-> dim 2r+1 of a 16-dim chunk), which the epilogue undoes;
-//  * K's row scale multiplies the f32 score; V's row scale multiplies the converted f16 values (a
-//    product of an e4m3 value and its scale is at most the row's amax: no range problem in f16).
+//  * K's row scale multiplies the f32 score; V's row scale multiplies the softmax weight of its key,
+//    relative to the largest scale among the warp's 16 keys (so the f16 weight stays in normal range),
+//    and the accumulator is kept in units of that largest scale, switched inside the online-softmax
+//    rescale.
 #include <cuda_fp8.h>
 
 #include "internal.hpp"
@@ -78,13 +80,6 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_bytes)
 {
     const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(two_bytes), __NV_E4M3);
     return (uint32_t)h.x | ((uint32_t)h.y << 16);
-}
-
-__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b)
-{
-    uint32_t d;
-    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
 }
 
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src)
@@ -253,6 +248,7 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
             }
         }
         float m_run[2] = {kNegSentinel, kNegSentinel}, l_run[2] = {0.f, 0.f};
+        float sigma = 1.f;  // the accumulators are in units of this V scale
         float o[kD / 16][4];
 #pragma unroll
         for (int mt = 0; mt < (int)kD / 16; ++mt) o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f;
@@ -336,7 +332,7 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
             const uint32_t wkey0 = key0 + warp * 16;
             if (wkey0 < L) {
                 // ---- S^T (16 keys x 8 heads) = K_tile Q^T ------------------------------------------------
-                float sc[4] = {0.f, 0.f, 0.f, 0.f};
+                float sc[4] = {0.f, 0.f, 0.f, 0.f}, sc2[4] = {0.f, 0.f, 0.f, 0.f};  // two chains: half the MMA latency exposed
                 const uint32_t row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
                 for (int kq = 0; kq < (int)kD / 32; ++kq) {
@@ -351,8 +347,10 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                     a[1] = e4m3x2_to_f16x2(r[3] & 0xFFFFu);
                     a[2] = e4m3x2_to_f16x2(r[2] >> 16);
                     a[3] = e4m3x2_to_f16x2(r[3] >> 16);
-                    mma_m16n8k16(sc, a, bq[2 * kq + 1][0], bq[2 * kq + 1][1]);
+                    mma_m16n8k16(sc2, a, bq[2 * kq + 1][0], bq[2 * kq + 1][1]);
                 }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) sc[i] += sc2[i];
                 // ---- the rows' scales, then the online softmax over this warp's 16 keys ---------------------
                 const uint32_t kr0 = wkey0 + g;
                 const bool dead0 = kr0 >= L, dead1 = kr0 + 8 >= L;
@@ -376,31 +374,40 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                 const float p2 = dead1 ? 0.f : fast_exp2(s2 - mn0), p3 = dead1 ? 0.f : fast_exp2(s3 - mn1);
                 l_run[0] = l_run[0] * a0 + (p0 + p2);
                 l_run[1] = l_run[1] * a1 + (p1 + p3);
+                // V's row scales ride on the weights: weight * (scale of its key / the largest scale of these 16
+                // keys) stays in f16's normal range whatever the rows' magnitudes, and the accumulator is kept in
+                // units of that largest scale (sigma), switched together with the softmax rescale at no extra cost.
+                const float vsa = vsc[warp * 16 + g], vsb = vsc[warp * 16 + g + 8];  // rows past L were set to 0
+                float vmax = fmaxf(vsa, vsb);
+#pragma unroll
+                for (int off = 4; off <= 16; off <<= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, off));
+                if (!(vmax > 0.f)) vmax = 1.f;
+                const float inv = __frcp_rn(vmax), ra = vsa * inv, rb = vsb * inv, rs = sigma * inv;
+                sigma = vmax;
+                const float f0o = a0 * rs, f1o = a1 * rs;
 #pragma unroll
                 for (int mt = 0; mt < (int)kD / 16; ++mt) {
-                    o[mt][0] *= a0;
-                    o[mt][1] *= a1;
-                    o[mt][2] *= a0;
-                    o[mt][3] *= a1;
+                    o[mt][0] *= f0o;
+                    o[mt][1] *= f1o;
+                    o[mt][2] *= f0o;
+                    o[mt][3] *= f1o;
                 }
-                const uint32_t bp0 = movmatrix_trans(pack_f16x2(p0, p1)), bp1 = movmatrix_trans(pack_f16x2(p2, p3));
-                // ---- O^T (dims x heads) += V_tile^T P^T, V dequantised on the way --------------------------
-                const uint32_t vs01 = pack_f16x2(vsc[warp * 16 + 2 * c], vsc[warp * 16 + 2 * c + 1]);
-                const uint32_t vs89 = pack_f16x2(vsc[warp * 16 + 2 * c + 8], vsc[warp * 16 + 2 * c + 9]);
+                const uint32_t bp0 = movmatrix_trans(pack_f16x2(p0 * ra, p1 * ra)), bp1 = movmatrix_trans(pack_f16x2(p2 * rb, p3 * rb));
+                // ---- O^T (dims x heads) += V_tile^T P^T: the bytes of V converted, nothing else ------------------
 #pragma unroll
                 for (int mp = 0; mp < (int)kD / 32; ++mp) {
                     uint32_t r[4], a[4];
                     ldmatrix_x4_trans(r, v_addr + tile_off8(row, 2 * mp + (lane >> 4)));
                     // a register: (key 2c, dims 2g, 2g+1), (key 2c+1, dims 2g, 2g+1); MMA row g <-> dim 2g, row g+8 <-> dim 2g+1
-                    a[0] = hmul2_u32(e4m3x2_to_f16x2(__byte_perm(r[0], 0, 0x4420)), vs01);
-                    a[1] = hmul2_u32(e4m3x2_to_f16x2(__byte_perm(r[0], 0, 0x4431)), vs01);
-                    a[2] = hmul2_u32(e4m3x2_to_f16x2(__byte_perm(r[1], 0, 0x4420)), vs89);
-                    a[3] = hmul2_u32(e4m3x2_to_f16x2(__byte_perm(r[1], 0, 0x4431)), vs89);
+                    a[0] = e4m3x2_to_f16x2(__byte_perm(r[0], 0, 0x4420));
+                    a[1] = e4m3x2_to_f16x2(__byte_perm(r[0], 0, 0x4431));
+                    a[2] = e4m3x2_to_f16x2(__byte_perm(r[1], 0, 0x4420));
+                    a[3] = e4m3x2_to_f16x2(__byte_perm(r[1], 0, 0x4431));
                     mma_m16n8k16(o[2 * mp], a, bp0, bp1);
-                    a[0] = hmul2_u32(e4m3x2_to_f16x2(__byte_perm(r[2], 0, 0x4420)), vs01);
-                    a[1] = hmul2_u32(e4m3x2_to_f16x2(__byte_perm(r[2], 0, 0x4431)), vs01);
-                    a[2] = hmul2_u32(e4m3x2_to_f16x2(__byte_perm(r[3], 0, 0x4420)), vs89);
-                    a[3] = hmul2_u32(e4m3x2_to_f16x2(__byte_perm(r[3], 0, 0x4431)), vs89);
+                    a[0] = e4m3x2_to_f16x2(__byte_perm(r[2], 0, 0x4420));
+                    a[1] = e4m3x2_to_f16x2(__byte_perm(r[2], 0, 0x4431));
+                    a[2] = e4m3x2_to_f16x2(__byte_perm(r[3], 0, 0x4420));
+                    a[3] = e4m3x2_to_f16x2(__byte_perm(r[3], 0, 0x4431));
                     mma_m16n8k16(o[2 * mp + 1], a, bp0, bp1);
                 }
             }
@@ -435,8 +442,8 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                 ma0 = fmaxf(ma0, ml_s[(w * kHP + h0) * 2]);
                 ma1 = fmaxf(ma1, ml_s[(w * kHP + h0 + 1) * 2]);
             }
-            fac[0] = fast_exp2(m_run[0] - ma0);
-            fac[1] = fast_exp2(m_run[1] - ma1);
+            fac[0] = fast_exp2(m_run[0] - ma0) * sigma;
+            fac[1] = fast_exp2(m_run[1] - ma1) * sigma;
         }
         const bool direct = it.n_parts == 1;
 #pragma unroll

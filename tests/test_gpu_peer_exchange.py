@@ -267,7 +267,7 @@ def _nccl_comm(lib, world, rank, unique_id=None):
     import ctypes as C
 
     class UniqueId(C.Structure):
-        _fields_ = [("internal", C.c_char * 128)]
+        _fields_ = [("internal", C.c_ubyte * 128)]
 
     uid = UniqueId()
     if unique_id is None:
@@ -275,7 +275,7 @@ def _nccl_comm(lib, world, rank, unique_id=None):
     else:
         C.memmove(C.byref(uid), unique_id, 128)
     if world < 0:
-        return bytes(uid.internal)
+        return C.string_at(C.byref(uid), 128)
     comm = C.c_void_p()
     lib.ncclCommInitRank.argtypes = [C.POINTER(C.c_void_p), C.c_int, UniqueId, C.c_int]
     assert lib.ncclCommInitRank(C.byref(comm), world, uid, rank) == 0
