@@ -41,7 +41,8 @@ constexpr uint32_t kHP = 8;  // heads per group, padded
 constexpr uint32_t kStages = 6;
 constexpr uint32_t kConsumerWarps = 4;
 constexpr uint32_t kConsumerThreads = kConsumerWarps * 32;
-constexpr uint32_t kThreads = kConsumerThreads + 32;
+constexpr uint32_t kProducerWarps = 2;  // one streams K and its scales, the other V and its scales
+constexpr uint32_t kThreads = kConsumerThreads + 32 * kProducerWarps;
 constexpr float kNegSentinel = -1e30f;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -112,7 +113,8 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
 
     if (tid == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
-            mbar_init(bar_full + s * 8, 1 + 32);  // the producer's expect-tx arrival + one per lane for its scale copies
+            // per producer warp: its expect-tx arrival + one arrival per lane for the scale copies
+            mbar_init(bar_full + s * 8, kProducerWarps * (1 + 32));
             mbar_init(bar_empty + s * 8, kConsumerWarps);
         }
         flags[0] = 0;
@@ -131,12 +133,14 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         return (page * p.n_kv_heads + kvh) * P + tok % P;
     };
 
-    if (warp == kConsumerWarps) {
-        // ------------------------------------------------------------ producer ---
-        if (lane == 0) {
-            tma_prefetch_desc(&tm_k);
-            tma_prefetch_desc(&tm_v);
-        }
+    if (warp >= kConsumerWarps) {
+        // ------------------------------------------------------- two producer warps ---
+        // With 2 KB per TMA box (a 16-row page of one kv head) the issue rate of the copies, not their bytes,
+        // limits a producer: K and V are streamed by a warp each.
+        const bool is_v = warp > kConsumerWarps;
+        const CUtensorMap *tm = is_v ? &tm_v : &tm_k;
+        const float *scales = is_v ? kp.v_scales : kp.k_scales;
+        if (lane == 0) tma_prefetch_desc(tm);
         if (!p.early_stream) grid_dependency_wait();
         const uint64_t policy = l2_policy_evict_first();
         uint32_t idx = p.cta_item_begin[blockIdx.x];
@@ -150,8 +154,8 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                 const uint32_t tok_box = t * kTileKeys + lane * P;
                 const bool valid = lane < boxes_per_tile && tok_box < L;
                 const int32_t row_box = valid ? (int32_t)row_of(it.seq, it.kvh, tok_box) : 0;
-                const uint32_t chunk = lane & 15, tok_sc = t * kTileKeys + 4 * chunk;  // four scales per 16-byte copy
-                const bool sc_valid = tok_sc < L;
+                const uint32_t tok_sc = t * kTileKeys + 4 * lane;  // four scales per 16-byte copy, lanes 0..15
+                const bool sc_valid = lane < 16 && tok_sc < L;
                 const uint32_t row_sc = sc_valid ? row_of(it.seq, it.kvh, tok_sc) : 0;
                 if (!flags[0] && !mbar_wait_bounded(bar_empty + stage * 8, phase ^ 1, kWaitLimitNs)) {
                     flags[0] = 1;
@@ -159,17 +163,12 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                 }
                 const uint32_t n_valid = __popc(__ballot_sync(0xffffffffu, valid));
                 const uint32_t full = bar_full + stage * 8;
-                if (lane == 0) mbar_arrive_expect_tx(full, n_valid * P * kD * 2);
+                if (lane == 0) mbar_arrive_expect_tx(full, n_valid * P * kD);
                 __syncwarp();
-                if (valid) {
-                    const uint32_t dst_k = smem_base + stage * kStageBytes + lane * P * kD;
-                    tma_load_2d_hint(dst_k, &tm_k, 0, row_box, full, policy);
-                    tma_load_2d_hint(dst_k + kTileBytes, &tm_v, 0, row_box, full, policy);
-                }
-                if (sc_valid) {
-                    const float *src = (lane < 16 ? kp.k_scales : kp.v_scales) + row_sc;
-                    cp_async_16(smem_base + kOffScales + stage * kScaleStage + (lane >> 4) * (kTileKeys * 4) + chunk * 16, src);
-                }
+                if (valid)
+                    tma_load_2d_hint(smem_base + stage * kStageBytes + (is_v ? kTileBytes : 0u) + lane * P * kD, tm, 0, row_box, full, policy);
+                if (sc_valid)
+                    cp_async_16(smem_base + kOffScales + stage * kScaleStage + (is_v ? kTileKeys * 4 : 0u) + lane * 16, scales + row_sc);
                 cp_async_arrive_noinc(full);
                 ++issued;
                 if (++stage == kStages) {

@@ -9,7 +9,6 @@ arrival counter; the merge kernel waits for the counters and merges.  Cases:
 """
 import importlib
 import os
-import socket
 import sys
 from pathlib import Path
 
@@ -112,12 +111,6 @@ def test_merge_wait_runs_out_with_a_status(mfk, foundry):
     foundry.peer_exchange_destroy(silent)
 
 
-def _free_port():
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
-
-
 def _two_gpu_worker(rank, world, port, ret):
     sys.path.insert(0, str(ROOT))
     sys.path.insert(0, str(ROOT / "tests"))
@@ -126,9 +119,8 @@ def _two_gpu_worker(rank, world, port, ret):
 
     mfk = importlib.import_module("test-burn_b200")
     sharding = importlib.import_module("test-burn_b200.sharding")
-    os.environ["MASTER_ADDR"] = "127.0.0.1"
-    os.environ["MASTER_PORT"] = str(port)
-    dist.init_process_group("gloo", rank=rank, world_size=world)  # host plumbing only
+    # host plumbing only; a file store: no port to collide with anything else on the box
+    dist.init_process_group("gloo", init_method="file://" + port, rank=rank, world_size=world)
     torch.cuda.set_device(rank)
     try:
         Hq, Hkv, D, P, L = 24, 8, 128, 64, 6000
@@ -186,7 +178,9 @@ def test_pushed_partials_two_gpus():
 
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    world, port = 2, _free_port()
+    import tempfile
+
+    world, port = 2, os.path.join(tempfile.mkdtemp(prefix="mf_rdzv_"), "store")
     with mp.Manager() as mgr:
         ret = mgr.dict()
         mp.spawn(_two_gpu_worker, args=(world, port, ret), nprocs=world, join=True)
