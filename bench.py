@@ -1146,7 +1146,8 @@ def main():
                     help="c1 / c2: start each layer from the hidden state (RMSNorm + fused QKV projection + RoPE + append "
                          "in one launch) instead of from q, k, v")
     ap.add_argument("--page-size", type=int, default=0,
-                    help="c4 only: prefill into a paged cache with pages of this many rows (default: contiguous cache)")
+                    help="c4: prefill into a paged cache with pages of this many rows (default: contiguous cache); "
+                         "batched paged workloads: pages of this many rows instead of the workload's own")
     args = ap.parse_args()
     if args.impl == "reference" and args.workload not in WORKLOADS:
         sys.stderr.write("--impl reference times the batched paged decode workloads (%s) only; %s has no CPU arm\n"
@@ -1162,6 +1163,9 @@ def main():
         rank_teardown()
         return rc
     w = dict(WORKLOADS[args.workload])
+    if args.page_size:
+        w["name"] = w["name"].replace("page %d" % w["page_size"], "page %d" % args.page_size)
+        w["page_size"] = args.page_size
     if args.impl == "reference":
         return run_reference(args, w)
     if args.workload != "c3" or args.no_other_workloads:

@@ -147,6 +147,8 @@ def lib() -> C.CDLL:
     L.mfo_f32_to_e4m3.argtypes = [C.c_float]
     L.mfo_f32_to_e4m3.restype = C.c_uint8
     L.mfo_quantize_row_e4m3.argtypes = [u16p, u32, u8p, C.POINTER(C.c_float)]
+    L.mfo_kv8_v_index.argtypes = [C.c_size_t, u32, u32, u32]
+    L.mfo_kv8_v_index.restype = C.c_size_t
     L.mfo_paged_kv8_append.argtypes = [u16p, u16p, u16p, u16p, u8p, u8p, f32p, f32p, u16p, u16p, u32p, u32, u32p, u32, u32,
                                        u32, u32, u32, u32, C.c_int]
     L.mfo_decode_kv8.argtypes = [u16p, u8p, u8p, f32p, f32p, u32p, u32, u32, u32, u32, u32, C.c_float, u16p, C.c_void_p]

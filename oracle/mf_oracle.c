@@ -814,8 +814,17 @@ void mfo_quantize_row_e4m3(const uint16_t *x, uint32_t n, uint8_t *q, float *sca
     *scale_out = scale;
 }
 
-/* One new token per sequence appended to 8-bit pools [n_pages, Hkv, P, D] (bytes) with scale pools
- * [n_pages, Hkv, P] (f32): RoPE of q and k exactly as mfo_paged_kv_append, then the row quantiser. */
+/* Byte index of (cache row r, dim d) in the V pool of the 8-bit cache.  K rows lie row-major ([n_pages, Hkv, P, D]);
+ * V is kept dim-major in blocks of 16 keys inside each (page, kv head) run of P rows - [n_pages, Hkv, P/16, D, 16] -
+ * which is the operand layout of the 8-bit tensor-core product V^T W (page sizes are multiples of 16). */
+size_t mfo_kv8_v_index(size_t r, uint32_t d, uint32_t head_dim, uint32_t page_size)
+{
+    const size_t in_page = r % page_size, run = r - in_page;
+    return run * head_dim + (in_page / 16) * (16 * (size_t)head_dim) + (size_t)d * 16 + in_page % 16;
+}
+
+/* One new token per sequence appended to the 8-bit pools (K [n_pages, Hkv, P, D] bytes, V as mfo_kv8_v_index) with
+ * scale pools [n_pages, Hkv, P] (f32): RoPE of q and k exactly as mfo_paged_kv_append, then the row quantiser. */
 void mfo_paged_kv8_append(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t *q_rot,
                           uint8_t *k_pool, uint8_t *v_pool, float *k_scales, float *v_scales,
                           const uint16_t *cos_t, const uint16_t *sin_t, const uint32_t *page_table,
@@ -840,7 +849,9 @@ void mfo_paged_kv8_append(const uint16_t *q, const uint16_t *k, const uint16_t *
             const uint16_t *ks = k + ((size_t)b * n_kv_heads + kh) * D, *vs = v + ((size_t)b * n_kv_heads + kh) * D;
             for (uint32_t hd = 0; hd < D; ++hd) row[hd] = apply_rope ? rope_elem(ks, c_row, s_row, hd, D, rope_mode) : ks[hd];
             mfo_quantize_row_e4m3(row, D, k_pool + r * D, k_scales + r);
-            mfo_quantize_row_e4m3(vs, D, v_pool + r * D, v_scales + r);
+            uint8_t vq[512];
+            mfo_quantize_row_e4m3(vs, D, vq, v_scales + r);
+            for (uint32_t hd = 0; hd < D; ++hd) v_pool[mfo_kv8_v_index(r, hd, D, page_size)] = vq[hd];
         }
     }
 }
@@ -882,7 +893,7 @@ void mfo_decode_kv8(const uint16_t *q_rot, const uint8_t *k_pool, const uint8_t 
             const float alpha = expf(m - mn), w = expf(score - mn);
             l = l * alpha + w;
             for (uint32_t d = 0; d < D; ++d)
-                acc[d] = acc[d] * alpha + w * (mfo_e4m3_to_f32(v_pool[r * D + d]) * v_scales[r]);
+                acc[d] = acc[d] * alpha + w * (mfo_e4m3_to_f32(v_pool[mfo_kv8_v_index(r, d, D, page_size)]) * v_scales[r]);
             m = mn;
         }
         finish_decode_row(acc, l, D, out + (size_t)h * D);
@@ -894,7 +905,7 @@ void mfo_decode_kv8(const uint16_t *q_rot, const uint8_t *k_pool, const uint8_t 
                 const double w = exp(sc[t] - gmax);
                 lsum += w;
                 for (uint32_t d = 0; d < D; ++d)
-                    gold[(size_t)h * D + d] += w * (double)mfo_e4m3_to_f32(v_pool[r * D + d]) * (double)v_scales[r];
+                    gold[(size_t)h * D + d] += w * (double)mfo_e4m3_to_f32(v_pool[mfo_kv8_v_index(r, d, D, page_size)]) * (double)v_scales[r];
             }
             for (uint32_t d = 0; d < D; ++d) gold[(size_t)h * D + d] = lsum > 0.0 ? gold[(size_t)h * D + d] / lsum : 0.0;
         }

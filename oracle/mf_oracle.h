@@ -220,6 +220,8 @@ void mfo_merge_partials(const float *acc, const float *m, const float *l,
 float mfo_e4m3_to_f32(uint8_t b);
 uint8_t mfo_f32_to_e4m3(float x);
 void mfo_quantize_row_e4m3(const uint16_t *x, uint32_t n, uint8_t *q, float *scale_out);
+/* byte index of (cache row r, dim d) in the V pool: dim-major blocks of 16 keys inside each (page, kv head) run */
+size_t mfo_kv8_v_index(size_t r, uint32_t d, uint32_t head_dim, uint32_t page_size);
 void mfo_paged_kv8_append(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t *q_rot,
                           uint8_t *k_pool, uint8_t *v_pool, float *k_scales, float *v_scales,
                           const uint16_t *cos_t, const uint16_t *sin_t, const uint32_t *page_table,

@@ -705,9 +705,27 @@ def paged_kv(k_pool, v_pool, page_table, kv_lens, *, n_kv_heads, page_size, head
     return desc
 
 
+def kv8_v_pool_from_rows(rows):
+    """Quantised V rows [n_pages, Hkv, P, 128] (numpy or torch, uint8) -> the V pool's byte order: dim-major blocks of
+    16 keys inside each (page, kv head) run, [n_pages, Hkv, P/16, 128, 16], returned in the rows' shape."""
+    n, h, p, d = rows.shape
+    x = rows.reshape(n, h, p // 16, 16, d)
+    x = x.transpose(0, 1, 2, 4, 3) if hasattr(x, "__array__") and not hasattr(x, "permute") else x.permute(0, 1, 2, 4, 3)
+    return (x.copy() if not hasattr(x, "contiguous") else x.contiguous()).reshape(n, h, p, d)
+
+
+def kv8_v_rows_from_pool(pool):
+    """Inverse of kv8_v_pool_from_rows."""
+    n, h, p, d = pool.shape
+    x = pool.reshape(n, h, p // 16, d, 16)
+    x = x.transpose(0, 1, 2, 4, 3) if hasattr(x, "__array__") and not hasattr(x, "permute") else x.permute(0, 1, 2, 4, 3)
+    return (x.copy() if not hasattr(x, "contiguous") else x.contiguous()).reshape(n, h, p, d)
+
+
 def paged_kv8(k_pool, v_pool, k_scales, v_scales, page_table, kv_lens, *, n_kv_heads, page_size) -> MfPagedKv8:
-    """Describe torch-owned 8-bit pools [n_pages, Hkv, P, 128] (uint8), their scale pools [n_pages, Hkv, P] (f32)
-    and a [batch, stride] page table."""
+    """Describe torch-owned 8-bit pools (uint8; K [n_pages, Hkv, P, 128] row-major, V the same bytes per (page, kv head)
+    in dim-major 16-key blocks, see kv8_v_pool_from_rows), their scale pools [n_pages, Hkv, P] (f32) and a
+    [batch, stride] page table.  Page sizes 16, 32, 64."""
     desc = MfPagedKv8(k_pool.data_ptr(), v_pool.data_ptr(), k_scales.data_ptr(), v_scales.data_ptr(), page_table.data_ptr(),
                       kv_lens.data_ptr(), k_pool.shape[0], n_kv_heads, page_size, 128, page_table.shape[1], page_table.shape[0])
     desc._keep = (k_pool, v_pool, k_scales, v_scales, page_table, kv_lens)

@@ -336,28 +336,35 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         uint32_t stage = 0, phase = 0, issued = 0;
         while (cur.next(it)) {
             const uint32_t L = kv_len_of(p, it.seq);
-            // Row of this lane's box inside the K / V tensor for a given tile.
-            auto box_rows = [&](uint32_t tile, int32_t &rk, int32_t &rv) -> bool {
-                const uint32_t tok = tile * kTileKeys + lane * rows_per_box;
-                if (lane >= boxes_per_tile) return false;
-                if (p.page_table) {
+            // Paged: the ids of 32 pages travel one per lane, a chunk ahead of the tiles that use them (a lookup
+            // per tile, even issued one tile early, put a global-load latency into every tile of the stream).
+            const bool paged = p.page_table != nullptr;
+            const uint32_t *pt_row = paged ? p.page_table + (size_t)it.seq * p.pt_stride : nullptr;
+            const uint32_t n_pg = paged ? min((L + p.page_size - 1) / p.page_size, p.pt_stride) : 0u;
+            uint32_t chunk = paged ? (it.tile_begin * kTileKeys) / p.page_size : 0u;
+            auto load_ids = [&](uint32_t base) -> uint32_t { return base + lane < n_pg ? __ldg(pt_row + base + lane) : 0u; };
+            uint32_t ids = load_ids(chunk), ids_next = load_ids(chunk + 32);
+            for (uint32_t t = it.tile_begin; t < it.tile_end; ++t) {
+                // Row of this lane's box inside the K / V tensor.
+                const uint32_t tok = t * kTileKeys + lane * rows_per_box;
+                bool valid = lane < boxes_per_tile;
+                int32_t rk, rv;
+                if (paged) {
+                    if ((t * kTileKeys) / p.page_size >= chunk + 32) {
+                        ids = ids_next;
+                        chunk += 32;
+                        ids_next = load_ids(chunk + 32);
+                    }
+                    const uint32_t pg = tok / p.page_size;
+                    const uint32_t page = __shfl_sync(0xffffffffu, ids, (pg - chunk) & 31u);
                     // rows past the sequence, or past the page table when the device-side length is larger
                     // than the table allows (the consumers report that), are not fetched
-                    if (tok >= L || tok / p.page_size >= p.pt_stride) return false;
-                    const uint32_t page = __ldg(p.page_table + (size_t)it.seq * p.pt_stride + tok / p.page_size);
-                    const uint32_t row = (page * p.n_kv_heads + it.kvh) * p.page_size + tok % p.page_size;
-                    rk = rv = static_cast<int32_t>(row);
+                    valid = valid && tok < L && pg < p.pt_stride;
+                    rk = rv = static_cast<int32_t>((page * p.n_kv_heads + it.kvh) * p.page_size + tok % p.page_size);
                 } else {
                     rk = static_cast<int32_t>(it.seq * p.k_rows_b + it.kvh * p.k_rows_h + tok);
                     rv = static_cast<int32_t>(it.seq * p.v_rows_b + it.kvh * p.v_rows_h + tok);
                 }
-                return true;
-            };
-            int32_t rk = 0, rv = 0, nrk = 0, nrv = 0;
-            bool valid = box_rows(it.tile_begin, rk, rv), nvalid = false;
-            for (uint32_t t = it.tile_begin; t < it.tile_end; ++t) {
-                // Look the next tile's page up before blocking on the ring.
-                if (t + 1 < it.tile_end) nvalid = box_rows(t + 1, nrk, nrv);
                 if (!flags[0] && !mbar_wait_bounded(bar_empty + stage * 8, phase ^ 1, kWaitLimitNs)) {
                     flags[0] = 1;
                     atomicOr(p.status, 1u);
@@ -386,9 +393,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                     stage = 0;
                     phase ^= 1;
                 }
-                valid = nvalid;
-                rk = nrk;
-                rv = nrv;
             }
         }
         // After an abort the consumers no longer wait for the ring: make sure our

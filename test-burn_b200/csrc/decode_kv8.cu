@@ -19,11 +19,13 @@
 // into several spans.  What differs:
 //  * a tile row is 128 bytes, so one TMA box per page brings whole rows (128-byte swizzle), and the
 //    row scales of a tile arrive by 16-byte cp.async copies that complete on the same mbarrier;
-//  * ldmatrix moves the bytes as 16-bit units: for K each register holds four consecutive dims of a
-//    key, which become two f16x2 operands (cvt.rn.f16x2.e4m3x2) of an MMA whose k order is permuted
-//    the same way for the q fragment; for V the transposing ldmatrix delivers (key, key+1) x (dim,
-//    dim+1) blocks, a byte permute separates the two dims, and the MMA's row order is permuted
-//    (row r <-> dim 2r, row r+8 <-> dim 2r+1 of a 16-dim chunk), which the epilogue undoes;
+//  * the scores run on the 8-bit tensor path (mma.sync m16n8k32 e4m3): K's bytes are the A operand exactly
+//    as ldmatrix delivers them, and q enters as three E4M3 numbers, q1 + q2/16 + q3/256 (12 of the f16
+//    value's bits), three MMAs per 32 dims and no conversion at all;
+//  * for V the transposing ldmatrix delivers (key, key+1) x (dim, dim+1) blocks of bytes; a byte permute puts
+//    each dim's two keys into the high bytes of a register's halves, a shift and an add turn them into f16
+//    (value / 256, the factor rides on the weights), and the f16 MMA's row order is permuted (row r <-> dim
+//    2r, row r+8 <-> dim 2r+1 of a 16-dim chunk), which the epilogue undoes;
 //  * K's row scale multiplies the f32 score; V's row scale multiplies the softmax weight of its key,
 //    relative to the largest scale among the warp's 16 keys (so the f16 weight stays in normal range),
 //    and the accumulator is kept in units of that largest scale, switched inside the online-softmax
@@ -54,7 +56,7 @@ constexpr uint32_t kOffScales = kStages * kStageBytes;
 constexpr uint32_t kCombStride = kD / 2 + 4;
 constexpr uint32_t kOffComb = kOffScales + kStages * kScaleStage;
 constexpr uint32_t kCombBytes = kConsumerWarps * kHP * kCombStride * 4;
-constexpr uint32_t kQStride = kD + 8;
+constexpr uint32_t kQStride = kD + 8;       // f16 elements per head row of q (the pad spreads the heads over the banks)
 constexpr uint32_t kOffQ = kOffComb + kCombBytes;
 constexpr uint32_t kOffMl = kOffQ + kHP * kQStride * 2;
 constexpr uint32_t kOffRow = kOffMl + kConsumerWarps * kHP * 2 * 4;  // the new k and v rows (f16) while they are quantised
@@ -77,21 +79,54 @@ __device__ __forceinline__ uint32_t tile_off8(uint32_t row, uint32_t c16)
     return (row << 7) + (((c16 & 7) ^ (row & 7)) << 4);
 }
 
-__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_bytes)
+// V is stored dim-major in blocks of 16 keys: byte (key r, dim d) of a run of rows (a page of one kv head in the
+// pool, a tile in shared memory) sits at (r / 16) * 2048 + d * 16 + r % 16.
+__host__ __device__ __forceinline__ uint32_t v_off8(uint32_t r, uint32_t d)
 {
-    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(two_bytes), __NV_E4M3);
-    return (uint32_t)h.x | ((uint32_t)h.y << 16);
+    return (r >> 4) * (16u * kD) + d * 16u + (r & 15u);
 }
 
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src)
+// The low / high two E4M3 bytes of a register as f16x2 (exact: every E4M3 value is an f16 value).  The legacy
+// tensor path of sm_100a has no 8-bit product - ptxas expands mma.sync ... e4m3 into these conversions, f16 MMAs
+// and an f32 add per accumulator register - so the conversions are written out and counted here.
+__device__ __forceinline__ uint32_t e4m3x2_lo_to_f16x2(uint32_t r)
 {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    uint32_t d;
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, lo;\n\t}" : "=r"(d) : "r"(r));
+    return d;
 }
-// The executing thread's earlier cp.async copies arrive on the mbarrier when they complete (the barrier's
-// count already includes this arrival).
-__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar)
+__device__ __forceinline__ uint32_t e4m3x2_hi_to_f16x2(uint32_t r)
 {
-    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+    uint32_t d;
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, hi;\n\t}" : "=r"(d) : "r"(r));
+    return d;
+}
+// D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col); a pure function of its registers (not volatile), so that
+// the compiler may move it among the conversions
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Maximum over the lanes named in `mask` (every lane of a group passes its group's mask) in one instruction: the
+// float's bits mapped to a signed integer of the same order.
+__device__ __forceinline__ float group_max_f32(float x, uint32_t mask)
+{
+    int i = __float_as_int(x);
+    i ^= (i >> 31) & 0x7fffffff;
+    i = __reduce_max_sync(mask, i);
+    i ^= (i >> 31) & 0x7fffffff;
+    return __int_as_float(i);
+}
+
+// Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16); completion is
+// counted on `bar` as transaction bytes, like a tile copy.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
 }
 
 __device__ __forceinline__ void rope_pair(float xi, float xj, float c, float s, __half &oi, __half &oj)
@@ -113,9 +148,8 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
 
     if (tid == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
-            // per producer warp: its expect-tx arrival + one arrival per lane for the scale copies
-            mbar_init(bar_full + s * 8, kProducerWarps * (1 + 32));
-            mbar_init(bar_empty + s * 8, kConsumerWarps);
+            mbar_init(bar_full + s * 8, kProducerWarps);  // each producer warp's expect-tx arrival
+            mbar_init(bar_empty + s * 8, 2);  // the two warps that work on the tile
         }
         flags[0] = 0;
         flags[1] = 0;
@@ -127,11 +161,6 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     const uint32_t P = p.page_size;  // a power of two in 8..64
     const uint32_t boxes_per_tile = kTileKeys / P;
     if (!p.strict_release) grid_launch_dependents();
-
-    auto row_of = [&](uint32_t seq, uint32_t kvh, uint32_t tok) -> uint32_t {
-        const uint32_t page = __ldg(p.page_table + (size_t)seq * p.pt_stride + tok / P);
-        return (page * p.n_kv_heads + kvh) * P + tok % P;
-    };
 
     if (warp >= kConsumerWarps) {
         // ------------------------------------------------------- two producer warps ---
@@ -149,27 +178,39 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         for (; idx < end; ++idx) {
             const WorkItem it = p.items[idx];
             const uint32_t L = min(p.kv_lens[it.seq], p.pt_stride * P);  // never past the page table
+            // Page ids travel 32 at a time, one per lane, a chunk ahead of the tiles that use them: a lookup per
+            // tile in front of its copies had put one global-load latency into every tile of the stream.
+            const uint32_t *pt_row = p.page_table + (size_t)it.seq * p.pt_stride;
+            const uint32_t n_pg = (L + P - 1) / P;
+            uint32_t chunk = it.tile_begin * boxes_per_tile;
+            auto load_ids = [&](uint32_t base) -> uint32_t { return base + lane < n_pg ? __ldg(pt_row + base + lane) : 0u; };
+            uint32_t ids = load_ids(chunk), ids_next = load_ids(chunk + 32);
             for (uint32_t t = it.tile_begin; t < it.tile_end; ++t) {
-                // page lookups first, then the ring slot
+                const uint32_t pg0 = t * boxes_per_tile;
+                if (pg0 >= chunk + 32) {
+                    ids = ids_next;
+                    chunk += 32;
+                    ids_next = load_ids(chunk + 32);
+                }
                 const uint32_t tok_box = t * kTileKeys + lane * P;
-                const bool valid = lane < boxes_per_tile && tok_box < L;
-                const int32_t row_box = valid ? (int32_t)row_of(it.seq, it.kvh, tok_box) : 0;
-                const uint32_t tok_sc = t * kTileKeys + 4 * lane;  // four scales per 16-byte copy, lanes 0..15
-                const bool sc_valid = lane < 16 && tok_sc < L;
-                const uint32_t row_sc = sc_valid ? row_of(it.seq, it.kvh, tok_sc) : 0;
+                const uint32_t page_box = __shfl_sync(0xffffffffu, ids, (pg0 - chunk + lane) & 31u);
+                // The tensor map would clip a tile copy of a page outside the pool; the page's row scales come by an
+                // untiled copy that nothing clips, so such a page is not fetched at all and the launch reports it.
+                const bool valid = lane < boxes_per_tile && tok_box < L && page_box < p.n_pages;
+                const uint32_t row_box = valid ? (page_box * p.n_kv_heads + it.kvh) * P : 0u;
+                if (!valid && lane < boxes_per_tile && tok_box < L && !is_v) atomicOr(p.status, kStatusBadPage);
                 if (!flags[0] && !mbar_wait_bounded(bar_empty + stage * 8, phase ^ 1, kWaitLimitNs)) {
                     flags[0] = 1;
                     atomicOr(p.status, 1u);
                 }
                 const uint32_t n_valid = __popc(__ballot_sync(0xffffffffu, valid));
                 const uint32_t full = bar_full + stage * 8;
-                if (lane == 0) mbar_arrive_expect_tx(full, n_valid * P * kD);
+                if (lane == 0) mbar_arrive_expect_tx(full, n_valid * P * (kD + 4));
                 __syncwarp();
-                if (valid)
-                    tma_load_2d_hint(smem_base + stage * kStageBytes + (is_v ? kTileBytes : 0u) + lane * P * kD, tm, 0, row_box, full, policy);
-                if (sc_valid)
-                    cp_async_16(smem_base + kOffScales + stage * kScaleStage + (is_v ? kTileKeys * 4 : 0u) + lane * 16, scales + row_sc);
-                cp_async_arrive_noinc(full);
+                if (valid) {
+                    tma_load_2d_hint(smem_base + stage * kStageBytes + (is_v ? kTileBytes : 0u) + lane * P * kD, tm, 0, (int32_t)row_box, full, policy);
+                    bulk_load_1d(smem_base + kOffScales + stage * kScaleStage + (is_v ? kTileKeys * 4 : 0u) + lane * P * 4, scales + row_box, P * 4, full);
+                }
                 ++issued;
                 if (++stage == kStages) {
                     stage = 0;
@@ -192,12 +233,21 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     grid_dependency_wait();
     if (p.strict_release) grid_launch_dependents();
     float *comb = reinterpret_cast<float *>(smem + kOffComb);
-    __half *q_s = reinterpret_cast<__half *>(smem + kOffQ);
+    __half *q_s = reinterpret_cast<__half *>(smem + kOffQ);  // [head][kQStride] f16
     float *ml_s = reinterpret_cast<float *>(smem + kOffMl);
     __half *row_s = reinterpret_cast<__half *>(smem + kOffRow);
     float *red_s = reinterpret_cast<float *>(smem + kOffRed);
     const uint32_t G = p.group, half_d = kD / 2;
     const uint32_t g = lane >> 2, c = lane & 3;
+    const uint32_t half = warp & 1u, pair = warp >> 1;  // which 32 keys of a tile, and which tiles
+    // ldmatrix row addresses of this lane (matrix lane / 8, row lane % 8).  K: MMA row i of a 16-key block is key
+    // 4(i/2) + i%2, row i + 8 that key + 2 (the order in which the transposed weights meet V's bytes); the two right-hand
+    // matrices are the next 16 dims.  V: rows are dims, 32 of them per load, 16 keys wide.
+    const uint32_t k_row = 32 * half + 4 * ((lane & 7) >> 1) + (lane & 1) + 2 * ((lane >> 3) & 1);
+    const uint32_t koff = k_row * kD, ksw = ((lane >> 4) ^ (k_row & 7)) << 4;
+    const uint32_t voff = half * (32 * kD) + lane * 16;
+    const uint32_t key_lo = 4 * (g >> 1) + (g & 1);  // key (within a block) of accumulator rows g | g + 8: key_lo | key_lo + 2
+    const uint32_t group_mask = 0x11111111u << c;  // the lanes that hold the same two heads
 
     uint32_t idx = p.cta_item_begin[blockIdx.x];
     const uint32_t end = p.cta_item_begin[blockIdx.x + 1];
@@ -235,25 +285,26 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
             q_s[hg * kQStride + dj] = oj;
         }
         named_bar_sync(1, kConsumerThreads);
-        // B fragments of Q^T for the permuted k order of the 8-bit K operand: within the 16 dims of chunk ks,
-        // the MMA's k = 2c, 2c+1 are dims 4c, 4c+1 and its k = 2c+8, 2c+9 are dims 4c+2, 4c+3.
+        // B fragments of Q^T (k = 16 dims x n = 8 heads per step).  A thread's four K bytes are dims 4c .. 4c + 3 of the
+        // 16-dim chunk, so MMA k-index 2c, 2c + 1 stands for dims 4c, 4c + 1 and 2c + 8, 2c + 9 for dims 4c + 2, 4c + 3.
         uint32_t bq[kD / 16][2];
-        {
-            const __half *row = q_s + g * kQStride + 4 * c;
 #pragma unroll
-            for (int ks = 0; ks < (int)kD / 16; ++ks) {
-                bq[ks][0] = *reinterpret_cast<const uint32_t *>(row + ks * 16);
-                bq[ks][1] = *reinterpret_cast<const uint32_t *>(row + ks * 16 + 2);
-            }
+        for (int ks = 0; ks < (int)kD / 16; ++ks) {
+            const uint2 w = *reinterpret_cast<const uint2 *>(q_s + g * kQStride + 16 * ks + 4 * c);
+            bq[ks][0] = w.x;
+            bq[ks][1] = w.y;
         }
-        float m_run[2] = {kNegSentinel, kNegSentinel}, l_run[2] = {0.f, 0.f};
-        float sigma = 1.f;  // the accumulators are in units of this V scale
+        float m_run[2] = {kNegSentinel, kNegSentinel}, l_run[2] = {0.f, 0.f};  // l: this thread's keys only, summed at the end
+        float sigma = 0.f, wsc = 0.f;  // the accumulators are in units of sigma (a V row scale); wsc = 1 / sigma
         float o[kD / 16][4];
 #pragma unroll
         for (int mt = 0; mt < (int)kD / 16; ++mt) o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f;
 
         for (uint32_t t = it.tile_begin; t < it.tile_end; ++t) {
-            if (!flags[0] && !mbar_wait_bounded(bar_full + stage * 8, phase, kWaitLimitNs)) {
+            // A tile is worked on by two warps, 32 keys each; the other two take the next tile.  The tile that holds
+            // position L - 1 is first patched by all four.
+            const bool mine = ((t - it.tile_begin) & 1u) == pair, last = t + 1 == n_tiles;
+            if ((mine || last) && !flags[0] && !mbar_wait_bounded(bar_full + stage * 8, phase, kWaitLimitNs)) {
                 flags[0] = 1;
                 atomicOr(p.status, 2u);
             }
@@ -261,7 +312,7 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
             const uint32_t k_addr = smem_base + stage * kStageBytes, v_addr = k_addr + kTileBytes;
             float *ksc = reinterpret_cast<float *>(smem + kOffScales + stage * kScaleStage), *vsc = ksc + kTileKeys;
             const uint32_t key0 = t * kTileKeys;
-            if (t + 1 == n_tiles) {
+            if (last) {
                 // The tile that holds position L - 1: quantise and splice in the token appended by this step (and
                 // store it to the cache), then neutralise the rows past L (stale bytes, stale or NaN scales).
                 const uint32_t r_new = (L - 1) - key0;
@@ -307,9 +358,9 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                     const uint8_t qk = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(xk, sk), __NV_SATFINITE, __NV_E4M3);
                     const uint8_t qv = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(xv, sv), __NV_SATFINITE, __NV_E4M3);
                     reinterpret_cast<uint8_t *>(p.k_base)[(size_t)new_row * kD + tid] = qk;
-                    reinterpret_cast<uint8_t *>(p.v_base)[(size_t)new_row * kD + tid] = qv;
+                    reinterpret_cast<uint8_t *>(p.v_base)[(size_t)(new_row - (L - 1) % P) * kD + v_off8((L - 1) % P, tid)] = qv;
                     k_tile[tile_off8(r_new, tid >> 4) + (tid & 15)] = qk;
-                    v_tile[tile_off8(r_new, tid >> 4) + (tid & 15)] = qv;
+                    v_tile[v_off8(r_new, tid)] = qv;
                     if (tid == 0) {
                         kp.k_scales[new_row] = sk;
                         kp.v_scales[new_row] = sv;
@@ -319,99 +370,135 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                 }
                 const uint32_t first_dead = L - key0;  // 1..64
                 for (uint32_t r = first_dead + tid; r < kTileKeys; r += kConsumerThreads) vsc[r] = 0.f;
-                const uint32_t n_chunks = (kTileKeys - first_dead) * (kD / 16);
-                for (uint32_t ch = tid; ch < n_chunks; ch += kConsumerThreads) {
-                    const uint32_t row = first_dead + ch / (kD / 16);
-                    *reinterpret_cast<uint4 *>(v_tile + tile_off8(row, ch % (kD / 16))) = make_uint4(0, 0, 0, 0);
+                // stale bytes of V past L could decode to NaN, and 0 * NaN is NaN: clear them, 16 keys of a dim at a time
+                for (uint32_t ch = (first_dead >> 4) * kD + tid; ch < (kTileKeys / 16) * kD; ch += kConsumerThreads) {
+                    const uint32_t blk = ch / kD, keep = first_dead > blk * 16 ? first_dead - blk * 16 : 0u;  // < 16 only in the first block touched
+                    uint4 *w = reinterpret_cast<uint4 *>(v_tile + ch * 16);
+                    if (keep == 0) {
+                        *w = make_uint4(0, 0, 0, 0);
+                    } else if (keep < 16) {
+                        uint4 x = *w;
+                        uint32_t *xw = reinterpret_cast<uint32_t *>(&x);
+#pragma unroll
+                        for (uint32_t i = 0; i < 4; ++i) {
+                            const uint32_t lo = 4 * i;
+                            const uint32_t m = keep >= lo + 4 ? 0xFFFFFFFFu : (keep > lo ? (1u << (8 * (keep - lo))) - 1u : 0u);
+                            xw[i] &= m;
+                        }
+                        *w = x;
+                    }
                 }
                 fence_proxy_async();
                 named_bar_sync(2, kConsumerThreads);
             }
 
-            const uint32_t wkey0 = key0 + warp * 16;
-            if (wkey0 < L) {
-                // ---- S^T (16 keys x 8 heads) = K_tile Q^T ------------------------------------------------
-                float sc[4] = {0.f, 0.f, 0.f, 0.f}, sc2[4] = {0.f, 0.f, 0.f, 0.f};  // two chains: half the MMA latency exposed
-                const uint32_t row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+
+            const uint32_t ukey0 = key0 + 32 * half;
+            if (mine && ukey0 < L) {
+                // ---- S^T (2 x 16 keys x 8 heads) = K_tile Q^T: bytes -> f16 in registers, f16 MMAs, four accumulator
+                //      chains in rotation ----------------------------------------------------------------------------
+                float acc[2][2][4];  // [16-key block][even | odd 16-dim step]
+#pragma unroll
+                for (int b = 0; b < 2; ++b)
+#pragma unroll
+                    for (int kk = 0; kk < 2; ++kk) acc[b][kk][0] = acc[b][kk][1] = acc[b][kk][2] = acc[b][kk][3] = 0.f;
 #pragma unroll
                 for (int kq = 0; kq < (int)kD / 32; ++kq) {
-                    uint32_t r[4], a[4];
-                    ldmatrix_x4(r, k_addr + tile_off8(row, 2 * kq + (lane >> 4)));
-                    a[0] = e4m3x2_to_f16x2(r[0] & 0xFFFFu);
-                    a[1] = e4m3x2_to_f16x2(r[1] & 0xFFFFu);
-                    a[2] = e4m3x2_to_f16x2(r[0] >> 16);
-                    a[3] = e4m3x2_to_f16x2(r[1] >> 16);
-                    mma_m16n8k16(sc, a, bq[2 * kq][0], bq[2 * kq][1]);
-                    a[0] = e4m3x2_to_f16x2(r[2] & 0xFFFFu);
-                    a[1] = e4m3x2_to_f16x2(r[3] & 0xFFFFu);
-                    a[2] = e4m3x2_to_f16x2(r[2] >> 16);
-                    a[3] = e4m3x2_to_f16x2(r[3] >> 16);
-                    mma_m16n8k16(sc2, a, bq[2 * kq + 1][0], bq[2 * kq + 1][1]);
+                    uint32_t r[2][4];
+#pragma unroll
+                    for (int b = 0; b < 2; ++b)
+                        // four 8 x 16-byte matrices: (rows 0-7 | rows 8-15) x (dims 32kq .. +15 | +16 .. +31)
+                        ldmatrix_x4(r[b], k_addr + koff + b * (16 * kD) + (ksw ^ (kq * 32)));
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        mma_f16(acc[b][0], e4m3x2_lo_to_f16x2(r[b][0]), e4m3x2_lo_to_f16x2(r[b][1]), e4m3x2_hi_to_f16x2(r[b][0]),
+                                e4m3x2_hi_to_f16x2(r[b][1]), bq[2 * kq][0], bq[2 * kq][1]);
+                        mma_f16(acc[b][1], e4m3x2_lo_to_f16x2(r[b][2]), e4m3x2_lo_to_f16x2(r[b][3]), e4m3x2_hi_to_f16x2(r[b][2]),
+                                e4m3x2_hi_to_f16x2(r[b][3]), bq[2 * kq + 1][0], bq[2 * kq + 1][1]);
+                    }
                 }
+                // ---- the rows' scales; scores in the log2 domain --------------------------------------------------
+                float sc[2][4], vlo[2], vhi[2];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) sc[i] += sc2[i];
-                // ---- the rows' scales, then the online softmax over this warp's 16 keys ---------------------
-                const uint32_t kr0 = wkey0 + g;
-                const bool dead0 = kr0 >= L, dead1 = kr0 + 8 >= L;
-                const float f0 = ksc[warp * 16 + g] * p.scale_log2, f1 = ksc[warp * 16 + g + 8] * p.scale_log2;
-                float s0 = sc[0] * f0, s1 = sc[1] * f0, s2 = sc[2] * f1, s3 = sc[3] * f1;
-                if (dead0 || !(fabsf(s0) <= 3.0e38f)) s0 = kNegSentinel;
-                if (dead0 || !(fabsf(s1) <= 3.0e38f)) s1 = kNegSentinel;
-                if (dead1 || !(fabsf(s2) <= 3.0e38f)) s2 = kNegSentinel;
-                if (dead1 || !(fabsf(s3) <= 3.0e38f)) s3 = kNegSentinel;
-                float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
+                for (int b = 0; b < 2; ++b) {
+                    const uint32_t at = 32 * half + 16 * b + key_lo;
+                    const float k_lo = ksc[at] * p.scale_log2, k_hi = ksc[at + 2] * p.scale_log2;
+                    vlo[b] = vsc[at];  // rows past L were set to 0
+                    vhi[b] = vsc[at + 2];
 #pragma unroll
-                for (int off = 4; off <= 16; off <<= 1) {
-                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
-                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+                    for (int i = 0; i < 4; ++i) {
+                        const float v = (acc[b][0][i] + acc[b][1][i]) * (i < 2 ? k_lo : k_hi);
+                        sc[b][i] = fabsf(v) <= 3.0e38f ? v : kNegSentinel;
+                    }
                 }
-                const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
-                const float a0 = fast_exp2(m_run[0] - mn0), a1 = fast_exp2(m_run[1] - mn1);
-                m_run[0] = mn0;
-                m_run[1] = mn1;
-                const float p0 = dead0 ? 0.f : fast_exp2(s0 - mn0), p1 = dead0 ? 0.f : fast_exp2(s1 - mn1);
-                const float p2 = dead1 ? 0.f : fast_exp2(s2 - mn0), p3 = dead1 ? 0.f : fast_exp2(s3 - mn1);
-                l_run[0] = l_run[0] * a0 + (p0 + p2);
-                l_run[1] = l_run[1] * a1 + (p1 + p3);
-                // V's row scales ride on the weights: weight * (scale of its key / the largest scale of these 16
-                // keys) stays in f16's normal range whatever the rows' magnitudes, and the accumulator is kept in
-                // units of that largest scale (sigma), switched together with the softmax rescale at no extra cost.
-                const float vsa = vsc[warp * 16 + g], vsb = vsc[warp * 16 + g + 8];  // rows past L were set to 0
-                float vmax = fmaxf(vsa, vsb);
+                bool dead[2][2] = {{false, false}, {false, false}};
+                if (last) {
 #pragma unroll
-                for (int off = 4; off <= 16; off <<= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, off));
+                    for (int b = 0; b < 2; ++b) {
+                        const uint32_t kr = ukey0 + 16 * b + key_lo;
+                        dead[b][0] = kr >= L;
+                        dead[b][1] = kr + 2 >= L;
+                        if (dead[b][0]) sc[b][0] = sc[b][1] = kNegSentinel;
+                        if (dead[b][1]) sc[b][2] = sc[b][3] = kNegSentinel;
+                    }
+                }
+                // ---- online softmax over the 32 keys: the maxima by one reduction per head --------------------------
+                const float mx0 = group_max_f32(fmaxf(fmaxf(sc[0][0], sc[0][2]), fmaxf(sc[1][0], sc[1][2])), group_mask);
+                const float mx1 = group_max_f32(fmaxf(fmaxf(sc[0][1], sc[0][3]), fmaxf(sc[1][1], sc[1][3])), group_mask);
+                // V's row scales ride on the weights: weight * scale / sigma, sigma a recent maximum of the scales (at most
+                // 8 times the largest of these 32), so that the f16 weight stays in normal range whatever the rows' magnitudes.
+                float vmax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fmaxf(fmaxf(vlo[0], vhi[0]), fmaxf(vlo[1], vhi[1])))));
                 if (!(vmax > 0.f)) vmax = 1.f;
-                const float inv = __frcp_rn(vmax), ra = vsa * inv, rb = vsb * inv, rs = sigma * inv;
-                sigma = vmax;
-                const float f0o = a0 * rs, f1o = a1 * rs;
+                const bool keep_sigma = vmax <= sigma && vmax * 8.f >= sigma;
+                const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+                if (__any_sync(0xffffffffu, mn0 > m_run[0] || mn1 > m_run[1] || !keep_sigma)) {
+                    const float sig_new = keep_sigma ? sigma : vmax;
+                    wsc = __frcp_rn(sig_new);
+                    const float rs = sigma * wsc;
+                    const float a0 = fast_exp2(m_run[0] - mn0), a1 = fast_exp2(m_run[1] - mn1);
+                    const float f0o = a0 * rs, f1o = a1 * rs;
 #pragma unroll
-                for (int mt = 0; mt < (int)kD / 16; ++mt) {
-                    o[mt][0] *= f0o;
-                    o[mt][1] *= f1o;
-                    o[mt][2] *= f0o;
-                    o[mt][3] *= f1o;
+                    for (int mt = 0; mt < (int)kD / 16; ++mt) {
+                        o[mt][0] *= f0o;
+                        o[mt][1] *= f1o;
+                        o[mt][2] *= f0o;
+                        o[mt][3] *= f1o;
+                    }
+                    l_run[0] *= a0;
+                    l_run[1] *= a1;
+                    m_run[0] = mn0;
+                    m_run[1] = mn1;
+                    sigma = sig_new;
                 }
-                const uint32_t bp0 = movmatrix_trans(pack_f16x2(p0 * ra, p1 * ra)), bp1 = movmatrix_trans(pack_f16x2(p2 * rb, p3 * rb));
-                // ---- O^T (dims x heads) += V_tile^T P^T: the bytes of V converted, nothing else ------------------
+                // ---- weights, transposed into the B fragments of the second product: (keys 4c, 4c + 1 | 4c + 2, 4c + 3) of head g ----
+                uint32_t bp[2][2];
 #pragma unroll
-                for (int mp = 0; mp < (int)kD / 32; ++mp) {
-                    uint32_t r[4], a[4];
-                    ldmatrix_x4_trans(r, v_addr + tile_off8(row, 2 * mp + (lane >> 4)));
-                    // a register: (key 2c, dims 2g, 2g+1), (key 2c+1, dims 2g, 2g+1); MMA row g <-> dim 2g, row g+8 <-> dim 2g+1
-                    a[0] = e4m3x2_to_f16x2(__byte_perm(r[0], 0, 0x4420));
-                    a[1] = e4m3x2_to_f16x2(__byte_perm(r[0], 0, 0x4431));
-                    a[2] = e4m3x2_to_f16x2(__byte_perm(r[1], 0, 0x4420));
-                    a[3] = e4m3x2_to_f16x2(__byte_perm(r[1], 0, 0x4431));
-                    mma_m16n8k16(o[2 * mp], a, bp0, bp1);
-                    a[0] = e4m3x2_to_f16x2(__byte_perm(r[2], 0, 0x4420));
-                    a[1] = e4m3x2_to_f16x2(__byte_perm(r[2], 0, 0x4431));
-                    a[2] = e4m3x2_to_f16x2(__byte_perm(r[3], 0, 0x4420));
-                    a[3] = e4m3x2_to_f16x2(__byte_perm(r[3], 0, 0x4431));
-                    mma_m16n8k16(o[2 * mp + 1], a, bp0, bp1);
+                for (int b = 0; b < 2; ++b) {
+                    float pw[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) pw[i] = dead[b][i >> 1] ? 0.f : fast_exp2(sc[b][i] - m_run[i & 1]);
+                    l_run[0] += pw[0] + pw[2];
+                    l_run[1] += pw[1] + pw[3];
+                    const float w_lo = vlo[b] * wsc, w_hi = vhi[b] * wsc;
+                    bp[b][0] = movmatrix_trans(pack_f16x2(pw[0] * w_lo, pw[1] * w_lo));
+                    bp[b][1] = movmatrix_trans(pack_f16x2(pw[2] * w_hi, pw[3] * w_hi));
                 }
+                // ---- O^T (dims x heads) += V_tile^T W: a load brings 32 dims x 16 keys of bytes as they lie in the dim-major
+                //      blocks; low / high halves of a register are keys 4c, 4c + 1 | 4c + 2, 4c + 3 -----------------------
+#pragma unroll
+                for (int b = 0; b < 2; ++b)
+#pragma unroll
+                    for (int mq = 0; mq < (int)kD / 32; ++mq) {
+                        uint32_t r[4];
+                        ldmatrix_x4(r, v_addr + voff + b * (16 * kD) + mq * 512);
+                        mma_f16(o[2 * mq], e4m3x2_lo_to_f16x2(r[0]), e4m3x2_lo_to_f16x2(r[1]), e4m3x2_hi_to_f16x2(r[0]), e4m3x2_hi_to_f16x2(r[1]),
+                                bp[b][0], bp[b][1]);
+                        mma_f16(o[2 * mq + 1], e4m3x2_lo_to_f16x2(r[2]), e4m3x2_lo_to_f16x2(r[3]), e4m3x2_hi_to_f16x2(r[2]),
+                                e4m3x2_hi_to_f16x2(r[3]), bp[b][0], bp[b][1]);
+                    }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_empty + stage * 8);
+            if (mine && lane == 0) mbar_arrive(bar_empty + stage * 8);
             if (++stage == kStages) {
                 stage = 0;
                 phase ^= 1;
@@ -452,11 +539,11 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
 #pragma unroll
                 for (int mh = 0; mh < (int)kD / 32; ++mh) {
                     const int mt = hp * (kD / 32) + mh;
-                    const uint32_t d0 = mh * 16 + 2 * g;  // accumulator rows are dims 2g (first pair) and 2g + 1 (second)
+                    const uint32_t d0 = mh * 16 + g;  // accumulator rows are dims g and g + 8 of the chunk
                     c0[d0] = o[mt][0] * fac[0];
                     c1[d0] = o[mt][1] * fac[1];
-                    c0[d0 + 1] = o[mt][2] * fac[0];
-                    c1[d0 + 1] = o[mt][3] * fac[1];
+                    c0[d0 + 8] = o[mt][2] * fac[0];
+                    c1[d0 + 8] = o[mt][3] * fac[1];
                 }
             }
             named_bar_sync(2, kConsumerThreads);
@@ -638,17 +725,20 @@ __global__ void __launch_bounds__(256) kv8_append_kernel(const Kv8AppendParams p
     for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
     const float scale = amax > 0.f ? __fdiv_rn(amax, 448.f) : 1.f;
     const size_t row = ((size_t)page * p.n_kv_heads + head) * p.page_size + pos % p.page_size;
-    uint8_t *dst = (is_v ? p.v_pool : p.k_pool) + row * kD;
+    const uint32_t in_page = pos % p.page_size;
+    uint8_t *dst = is_v ? p.v_pool + (row - in_page) * kD : p.k_pool + row * kD;  // V: the page's dim-major blocks
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-        dst[lane + 32 * i] = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(__half2float(y[i]), scale), __NV_SATFINITE, __NV_E4M3);
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t d = lane + 32 * i;
+        dst[is_v ? v_off8(in_page, d) : d] = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(__half2float(y[i]), scale), __NV_SATFINITE, __NV_E4M3);
+    }
     if (lane == 0) (is_v ? p.v_scales : p.k_scales)[row] = scale;
 }
 
 // Dequantising gather: the first `len` rows of one sequence -> [Hkv, len, 128] f16 (value = f16(e4m3 * scale)).
 __global__ void __launch_bounds__(256)
 kv8_gather_kernel(const uint8_t *pool, const float *scales, __half *out, const uint32_t *page_table_row, uint32_t n_kv_heads,
-                  uint32_t page_size, uint32_t len, uint32_t n_pages, uint32_t *status)
+                  uint32_t page_size, uint32_t len, uint32_t n_pages, uint32_t dim_major, uint32_t *status)
 {
     const uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (gid >= (uint64_t)n_kv_heads * len * kD) return;
@@ -660,7 +750,9 @@ kv8_gather_kernel(const uint8_t *pool, const float *scales, __half *out, const u
         return;
     }
     const size_t row = ((size_t)page * n_kv_heads + h) * page_size + t % page_size;
-    const __half_raw hr = __nv_cvt_fp8_to_halfraw(pool[row * kD + d], __NV_E4M3);
+    const uint32_t in_page = t % page_size;
+    const size_t at = dim_major ? (row - in_page) * kD + v_off8(in_page, d) : row * kD + d;
+    const __half_raw hr = __nv_cvt_fp8_to_halfraw(pool[at], __NV_E4M3);
     out[gid] = __float2half_rn(__half2float(__half(hr)) * scales[row]);
 }
 
@@ -668,8 +760,9 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// Byte tensor map over [rows, 128] with boxes of box_rows rows and the 128-byte swizzle.
-mf_status byte_map(MfContext *ctx, const void *base, uint64_t rows, uint32_t box_rows, CUtensorMap *out)
+// Byte tensor map over [rows, 128] with boxes of box_rows rows; K rows land with the 128-byte swizzle, the
+// dim-major 16-key blocks of V as they are.
+mf_status byte_map(MfContext *ctx, const void *base, uint64_t rows, uint32_t box_rows, bool swizzle, CUtensorMap *out)
 {
     if (!ctx->encode_fn) {
         cudaDriverEntryPointQueryResult q;
@@ -686,7 +779,8 @@ mf_status byte_map(MfContext *ctx, const void *base, uint64_t rows, uint32_t box
     cuuint32_t estr[2] = {1, 1};
     const CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_fn)(
         out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(ctx, MF_ERR_CUDA, "cuTensorMapEncodeTiled (8-bit pool) failed (%d)", (int)r);
     return MF_OK;
 }
@@ -697,10 +791,12 @@ mf_status check_kv8(MfContext *ctx, const MfPagedKv8 *c, const char *what)
         return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "%s: null pool, scales or page table", what);
     if (c->head_dim != kD) return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "%s: the 8-bit cache supports head_dim 128, got %u", what, c->head_dim);
     const uint32_t P = c->page_size;
-    if (P < 8 || P > 64 || (P & (P - 1)) != 0)
-        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "%s: page_size %u (power of two in 8..64)", what, P);
+    if (P < 16 || P > 64 || (P & (P - 1)) != 0)
+        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "%s: page_size %u (16, 32 or 64)", what, P);
     if (c->n_kv_heads == 0 || (uint64_t)c->n_pages * c->n_kv_heads * P > 0x7FFFFFFFull)
         return fail(ctx, MF_ERR_INVALID_SHAPE, "%s: pool geometry", what);
+    if ((reinterpret_cast<uintptr_t>(c->k_scales) | reinterpret_cast<uintptr_t>(c->v_scales)) & 15u)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "%s: the scale pools must be 16-byte aligned", what);
     return MF_OK;
 }
 
@@ -778,8 +874,8 @@ mf_status mf_paged_decode_kv8(MfContext *ctx, const MfDecodePlan *pl, const MfPa
                       ctx->may_stream_early(c->k_pool, c->v_pool)) ? 1u : 0u;
     CUtensorMap tm_k, tm_v;
     const uint64_t rows = (uint64_t)c->n_pages * c->n_kv_heads * c->page_size;
-    if ((st = byte_map(ctx, c->k_pool, rows, c->page_size, &tm_k)) != MF_OK) return st;
-    if ((st = byte_map(ctx, c->v_pool, rows, c->page_size, &tm_v)) != MF_OK) return st;
+    if ((st = byte_map(ctx, c->k_pool, rows, c->page_size, true, &tm_k)) != MF_OK) return st;
+    if ((st = byte_map(ctx, c->v_pool, rows, c->page_size, false, &tm_v)) != MF_OK) return st;
     const bool programmatic = ctx->overlap_launches != 0;
     p.strict_release = (programmatic && ctx->next_launch_strict()) ? 1u : 0u;
     cudaLaunchConfig_t cfg{};
@@ -863,7 +959,7 @@ mf_status mf_paged_kv8_gather(MfContext *ctx, const MfPagedKv8 *c, uint32_t use_
     const uint64_t n = (uint64_t)c->n_kv_heads * len * kD;
     kv8_gather_kernel<<<(uint32_t)((n + 255) / 256), 256, 0, ctx->stream>>>(
         static_cast<const uint8_t *>(use_v ? c->v_pool : c->k_pool), use_v ? c->v_scales : c->k_scales, static_cast<__half *>(out),
-        c->page_table + (size_t)seq * c->page_table_stride, c->n_kv_heads, c->page_size, len, c->n_pages, ctx->d_status);
+        c->page_table + (size_t)seq * c->page_table_stride, c->n_kv_heads, c->page_size, len, c->n_pages, use_v ? 1u : 0u, ctx->d_status);
     return check_launch(ctx, "kv8_gather_kernel");
 }
 

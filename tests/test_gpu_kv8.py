@@ -20,8 +20,9 @@ TOL = 2e-3
 FORMAT_TOL = 3e-2
 
 
-def quantised_pools(case):
-    """The case's f16 pools quantised row by row with the oracle: (k8, v8, ks, vs)."""
+def quantised_pools(case, unwritten=None):
+    """The case's f16 pools quantised row by row with the oracle: (k8, v8, ks, vs), V in the pool's byte order.
+    `unwritten` ([n_pages, Hkv, P] bool): rows to fill with 0xFF bytes (an E4M3 NaN) and NaN scales."""
     L = oracle.lib()
     import ctypes as C
 
@@ -36,7 +37,13 @@ def quantised_pools(case):
             L.mfo_quantize_row_e4m3(np.ascontiguousarray(rows[r]), case.D, q8[r], C.byref(s))
             sc[r] = s.value
         out.append((q8.reshape(case.n_pages, case.Hkv, case.P, case.D), sc.reshape(case.n_pages, case.Hkv, case.P)))
-    return out[0][0], out[1][0], out[0][1], out[1][1]
+    import importlib
+    if unwritten is not None:
+        for q8, sc in out:
+            q8[unwritten] = 0xFF
+            sc[unwritten] = np.nan
+    v8 = importlib.import_module("test-burn_b200").kv8_v_pool_from_rows(out[1][0])  # V: dim-major 16-key blocks
+    return out[0][0], v8, out[0][1], out[1][1]
 
 
 def oracle_step(case, k8, v8, ks, vs):
@@ -60,7 +67,7 @@ CASES = [
     dict(batch=6, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[0, 14, 15, 16, 63, 64]),
     dict(batch=5, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[511, 1000, 2049, 3, 4095]),
     dict(batch=4, n_heads=24, n_kv_heads=8, head_dim=128, page_size=64, cached=[0, 63, 64, 1337]),
-    dict(batch=2, n_heads=4, n_kv_heads=4, head_dim=128, page_size=8, cached=[77, 130]),
+    dict(batch=2, n_heads=4, n_kv_heads=4, head_dim=128, page_size=16, cached=[77, 130]),
     dict(batch=3, n_heads=8, n_kv_heads=1, head_dim=128, page_size=32, cached=[300, 127, 31]),
 ]
 
@@ -72,16 +79,12 @@ def test_fused_append_decode_on_the_8bit_cache(mfk, foundry, cfg, rope_mode, max
     import torch
 
     case = PagedCase(rope_mode=rope_mode, poison=False, **cfg)
-    k8, v8, ks, vs = quantised_pools(case)
     # rows that were never written: NaN scales and 0xFF bytes (an E4M3 NaN), to prove they are never used
     written = np.zeros((case.n_pages, case.P), bool)
     for b in range(case.B):
         for t in range(int(case.cached[b])):
             written[case.page_table[b, t // case.P], t % case.P] = True
-    k8[~written[:, None, :].repeat(case.Hkv, 1)] = 0xFF
-    v8[~written[:, None, :].repeat(case.Hkv, 1)] = 0xFF
-    ks[~written[:, None, :].repeat(case.Hkv, 1)] = np.nan
-    vs[~written[:, None, :].repeat(case.Hkv, 1)] = np.nan
+    k8, v8, ks, vs = quantised_pools(case, unwritten=~written[:, None, :].repeat(case.Hkv, 1))
     q_ref, k8_ref, v8_ref, ks_ref, vs_ref, out_ref, gold = oracle_step(case, k8, v8, ks, vs)
     d_k8, d_v8 = torch.from_numpy(k8).cuda(), torch.from_numpy(v8).cuda()
     d_ks, d_vs = torch.from_numpy(ks).cuda(), torch.from_numpy(vs).cuda()
@@ -135,6 +138,14 @@ def test_8bit_append_kernel_and_gather(mfk, foundry):
         page = case.page_table[2, t // case.P]
         for h in range(case.Hkv):
             want[h, t] = (lut[k8_ref[page, h, t % case.P]] * ks_ref[page, h, t % case.P]).astype(np.float16)
+    assert np.array_equal(host(got), want.view(np.uint16))
+    foundry.paged_kv8_gather(desc, True, 2, n, got)  # V: out of its dim-major blocks
+    foundry.synchronize()
+    v_rows = mfk.kv8_v_rows_from_pool(v8_ref)
+    for t in range(n):
+        page = case.page_table[2, t // case.P]
+        for h in range(case.Hkv):
+            want[h, t] = (lut[v_rows[page, h, t % case.P]] * vs_ref[page, h, t % case.P]).astype(np.float16)
     assert np.array_equal(host(got), want.view(np.uint16))
     # a chunk of 40 rows of sequence 1 at position 32 (a prefill chunk), both RoPE modes
     for rope_mode in (0, 1):
@@ -196,6 +207,11 @@ def test_8bit_cache_refuses_what_it_does_not_support(mfk, foundry):
     desc = mfk.paged_kv8(z8, z8, zs, zs, pt, lens, n_kv_heads=2, page_size=16)
     desc.head_dim = 64
     q = torch.zeros((1, 16 * 64), dtype=torch.float16, device="cuda")
+    with pytest.raises(mfk.MetalError) as e:
+        foundry.paged_kv8_gather(desc, False, 0, 5, q)
+    assert e.value.kind == "OperationNotSupported"
+    desc.head_dim = 128
+    desc.page_size = 8  # V lies in blocks of 16 keys: pages of 16, 32 or 64 rows
     with pytest.raises(mfk.MetalError) as e:
         foundry.paged_kv8_gather(desc, False, 0, 5, q)
     assert e.value.kind == "OperationNotSupported"
