@@ -667,12 +667,16 @@ MF_API mf_status mf_paged_copy_pages(MfContext *ctx, const MfPagedKv *cache, con
 
 /* ---- 8-bit K/V cache (FP8 E4M3, one f32 scale per cached row) ------------------------
  * The reference has only a roadmap for a quantised cache (docs/FLASH.md:121-186,
- * docs/SAGE.md:1-60); the format here is this project's.  Pools [n_pages, n_kv_heads,
- * page_size, 128] bytes for K and for V, every byte an OCP FP8 E4M3 value, and scale pools
+ * docs/SAGE.md:1-60); the format here is this project's.  Byte pools of n_pages * n_kv_heads *
+ * page_size * 128 bytes for K and for V, every byte an OCP FP8 E4M3 value, and scale pools
  * [n_pages, n_kv_heads, page_size] f32: for a row x (K after RoPE and f16 rounding, V as
  * given) amax = max |x_i|, scale = amax / 448 (1 for an all-zero row), byte_i =
  * e4m3 round-to-nearest-even, saturating, of x_i / scale; the cached value is byte * scale.
- * head_dim 128 only, page_size a power of two in 8..64, GQA groups of up to 8 heads.
+ * K is row-major, [n_pages, n_kv_heads, page_size, 128].  V is dim-major in blocks of 16 keys
+ * inside each (page, kv head) run, [n_pages, n_kv_heads, page_size / 16, 128, 16]: byte (row r
+ * of the page, dim d) at (r / 16) * 2048 + d * 16 + r % 16 - the operand layout of V^T W on the
+ * tensor cores, so that V's bytes need no transposition on their way into the product.
+ * head_dim 128 only, page_size 16, 32 or 64, GQA groups of up to 8 heads.
  * Attention over it keeps the reference's contract with K := decoded bytes * row scale and
  * V := dequantised rows; half the bytes of the f16 cache cross HBM per key. */
 typedef struct MfPagedKv8 {

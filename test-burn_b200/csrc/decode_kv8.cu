@@ -7,29 +7,31 @@
 // `scale`, running max from -1e30, non-finite scores count as -1e30, acc / l, one rounding to f16)
 // with K := the decoded bytes times the row's scale and V := the dequantised rows.
 //
-// Cache format (defined by this project): pools [n_pages, Hkv, P, 128] bytes for K and for V, each
-// byte an OCP FP8 E4M3 value, and scale pools [n_pages, Hkv, P] f32, one scale per cached row:
+// Cache format (defined by this project): byte pools for K and for V, each byte an OCP FP8 E4M3 value, and scale
+// pools [n_pages, Hkv, P] f32, one scale per cached row:
 //     amax = max |x_i| over the row (K after RoPE and f16 rounding, V as given),
 //     scale = amax / 448 (1 for an all-zero row), byte_i = e4m3_rne_satfinite(x_i / scale).
-// Half the bytes of the f16 cache cross HBM per key.
+// K rows lie row-major, [n_pages, Hkv, P, 128]; V lies dim-major in blocks of 16 keys inside each (page, kv head)
+// run, [n_pages, Hkv, P / 16, 128, 16] (v_off8 below).  Half the bytes of the f16 cache cross HBM per key.
 //
-// Kernel shape: that of decode_kernel (decode.cu) - a TMA producer warp filling a ring of 64-key K/V
-// tiles, four consumer warps of 16 keys each on mma.sync m16n8k16 with the query group on the 8-wide N
-// side, equal spans of tiles per CTA from the host's plan, partials and an atomic ticket for units cut
-// into several spans.  What differs:
-//  * a tile row is 128 bytes, so one TMA box per page brings whole rows (128-byte swizzle), and the
-//    row scales of a tile arrive by 16-byte cp.async copies that complete on the same mbarrier;
-//  * the scores run on the 8-bit tensor path (mma.sync m16n8k32 e4m3): K's bytes are the A operand exactly
-//    as ldmatrix delivers them, and q enters as three E4M3 numbers, q1 + q2/16 + q3/256 (12 of the f16
-//    value's bits), three MMAs per 32 dims and no conversion at all;
-//  * for V the transposing ldmatrix delivers (key, key+1) x (dim, dim+1) blocks of bytes; a byte permute puts
-//    each dim's two keys into the high bytes of a register's halves, a shift and an add turn them into f16
-//    (value / 256, the factor rides on the weights), and the f16 MMA's row order is permuted (row r <-> dim
-//    2r, row r+8 <-> dim 2r+1 of a 16-dim chunk), which the epilogue undoes;
-//  * K's row scale multiplies the f32 score; V's row scale multiplies the softmax weight of its key,
-//    relative to the largest scale among the warp's 16 keys (so the f16 weight stays in normal range),
-//    and the accumulator is kept in units of that largest scale, switched inside the online-softmax
-//    rescale.
+// Kernel shape: that of decode_kernel (decode.cu) - TMA producers filling a ring of 64-key K/V tiles, four consumer
+// warps on mma.sync with the query group on the 8-wide N side, equal spans of tiles per CTA from the host's plan,
+// partials and an atomic ticket for units cut into several spans.  What differs:
+//  * a tile row is 128 bytes: one TMA box per page and tensor (K with the 128-byte swizzle, V's blocks as they lie),
+//    and the page's row scales by an untiled bulk copy counted on the same mbarrier; K and V have a producer warp
+//    each, which read the page table 32 ids at a time, a chunk ahead of the tiles that use them;
+//  * a tile is worked on by TWO warps, 32 keys each, while the other two take the next tile: per key the softmax
+//    bookkeeping (maxima by redux.sync, rescale skipped by a vote when no maximum moved) is amortised over twice the
+//    keys, and the accumulators are rescaled half as often;
+//  * sm_100a's legacy tensor path has no 8-bit product (ptxas expands mma.sync ... e4m3 into conversions, f16 MMAs and
+//    f32 adds, measured: 2 HMMA + 4 FADD + up to 12 F2FP per instruction), so the bytes are converted here, two per
+//    cvt.rn.f16x2.e4m3x2 (exact), straight from the registers ldmatrix delivers, and meet f16 MMAs whose k order is
+//    permuted to match: a thread's four K bytes are dims 4c .. 4c + 3 of a 16-dim chunk (q's fragment is loaded in the
+//    same order), its four V bytes keys 4c .. 4c + 3 of a 16-key block (the score MMA's rows are laid out so that the
+//    transposed weights arrive in that order).  Nothing is permuted or transposed in registers;
+//  * K's row scale multiplies the f32 score; V's row scale multiplies the softmax weight of its key, relative to
+//    sigma, a recent maximum of the scales (so the f16 weight stays in normal range), and the accumulator is kept in
+//    units of sigma, switched inside the online-softmax rescale.
 #include <cuda_fp8.h>
 
 #include "internal.hpp"
@@ -46,6 +48,7 @@ constexpr uint32_t kConsumerThreads = kConsumerWarps * 32;
 constexpr uint32_t kProducerWarps = 2;  // one streams K and its scales, the other V and its scales
 constexpr uint32_t kThreads = kConsumerThreads + 32 * kProducerWarps;
 constexpr float kNegSentinel = -1e30f;
+constexpr float kMaxSlack = 8.f;  // log2: how far a score may exceed the running reference before it moves
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -109,17 +112,6 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1,
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-// Maximum over the lanes named in `mask` (every lane of a group passes its group's mask) in one instruction: the
-// float's bits mapped to a signed integer of the same order.
-__device__ __forceinline__ float group_max_f32(float x, uint32_t mask)
-{
-    int i = __float_as_int(x);
-    i ^= (i >> 31) & 0x7fffffff;
-    i = __reduce_max_sync(mask, i);
-    i ^= (i >> 31) & 0x7fffffff;
-    return __int_as_float(i);
-}
-
 // Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16); completion is
 // counted on `bar` as transaction bytes, like a tile copy.
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
@@ -247,7 +239,6 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     const uint32_t koff = k_row * kD, ksw = ((lane >> 4) ^ (k_row & 7)) << 4;
     const uint32_t voff = half * (32 * kD) + lane * 16;
     const uint32_t key_lo = 4 * (g >> 1) + (g & 1);  // key (within a block) of accumulator rows g | g + 8: key_lo | key_lo + 2
-    const uint32_t group_mask = 0x11111111u << c;  // the lanes that hold the same two heads
 
     uint32_t idx = p.cta_item_begin[blockIdx.x];
     const uint32_t end = p.cta_item_begin[blockIdx.x + 1];
@@ -425,11 +416,9 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                     const float k_lo = ksc[at] * p.scale_log2, k_hi = ksc[at + 2] * p.scale_log2;
                     vlo[b] = vsc[at];  // rows past L were set to 0
                     vhi[b] = vsc[at + 2];
+                    // non-finite scores count as -1e30: fmaxf maps NaN and -inf there; +inf shows in the maxima below
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float v = (acc[b][0][i] + acc[b][1][i]) * (i < 2 ? k_lo : k_hi);
-                        sc[b][i] = fabsf(v) <= 3.0e38f ? v : kNegSentinel;
-                    }
+                    for (int i = 0; i < 4; ++i) sc[b][i] = fmaxf((acc[b][0][i] + acc[b][1][i]) * (i < 2 ? k_lo : k_hi), kNegSentinel);
                 }
                 bool dead[2][2] = {{false, false}, {false, false}};
                 if (last) {
@@ -442,16 +431,38 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                         if (dead[b][1]) sc[b][2] = sc[b][3] = kNegSentinel;
                     }
                 }
-                // ---- online softmax over the 32 keys: the maxima by one reduction per head --------------------------
-                const float mx0 = group_max_f32(fmaxf(fmaxf(sc[0][0], sc[0][2]), fmaxf(sc[1][0], sc[1][2])), group_mask);
-                const float mx1 = group_max_f32(fmaxf(fmaxf(sc[0][1], sc[0][3]), fmaxf(sc[1][1], sc[1][3])), group_mask);
+                // ---- online softmax over the 32 keys.  The running maximum is only a reference point: it moves when a
+                //      score exceeds it by more than 8 (log2), so weights stay below 2^8 and the accumulators are rescaled
+                //      a few times per span instead of whenever one of eight heads sees a new record ------------------------
+                float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][2]), fmaxf(sc[1][0], sc[1][2]));
+                float mx1 = fmaxf(fmaxf(sc[0][1], sc[0][3]), fmaxf(sc[1][1], sc[1][3]));
+#pragma unroll
+                for (int off = 4; off <= 16; off <<= 1) {
+                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+                }
+                if (__any_sync(0xffffffffu, !(mx0 <= 3.0e38f) || !(mx1 <= 3.0e38f))) {  // an infinite score somewhere: once more without it
+#pragma unroll
+                    for (int b = 0; b < 2; ++b)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            if (!(sc[b][i] <= 3.0e38f)) sc[b][i] = kNegSentinel;
+                    mx0 = fmaxf(fmaxf(sc[0][0], sc[0][2]), fmaxf(sc[1][0], sc[1][2]));
+                    mx1 = fmaxf(fmaxf(sc[0][1], sc[0][3]), fmaxf(sc[1][1], sc[1][3]));
+#pragma unroll
+                    for (int off = 4; off <= 16; off <<= 1) {
+                        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+                        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+                    }
+                }
                 // V's row scales ride on the weights: weight * scale / sigma, sigma a recent maximum of the scales (at most
                 // 8 times the largest of these 32), so that the f16 weight stays in normal range whatever the rows' magnitudes.
                 float vmax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fmaxf(fmaxf(vlo[0], vhi[0]), fmaxf(vlo[1], vhi[1])))));
                 if (!(vmax > 0.f)) vmax = 1.f;
                 const bool keep_sigma = vmax <= sigma && vmax * 8.f >= sigma;
-                const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
-                if (__any_sync(0xffffffffu, mn0 > m_run[0] || mn1 > m_run[1] || !keep_sigma)) {
+                const bool up0 = mx0 > m_run[0] + kMaxSlack, up1 = mx1 > m_run[1] + kMaxSlack;
+                if (__any_sync(0xffffffffu, up0 || up1 || !keep_sigma)) {
+                    const float mn0 = up0 ? mx0 : m_run[0], mn1 = up1 ? mx1 : m_run[1];
                     const float sig_new = keep_sigma ? sigma : vmax;
                     wsc = __frcp_rn(sig_new);
                     const float rs = sigma * wsc;
