@@ -192,6 +192,7 @@ void mf_context_destroy(MfContext *ctx)
     cudaSetDevice(ctx->device);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch && ctx->scratch_owned) cudaFree(ctx->scratch);
+    if (ctx->qkv_xn) cudaFree(ctx->qkv_xn);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
@@ -235,6 +236,7 @@ mf_status mf_context_set_option(MfContext *ctx, uint32_t option, uint32_t value)
         case MF_OPTION_OVERLAP_LAUNCHES: ctx->overlap_launches = value > 2 ? 1u : value; return MF_OK;
         case MF_OPTION_DECODE_STAGES: ctx->decode_stages = value; return MF_OK;
         case MF_OPTION_PREFILL_IMPL: ctx->prefill_impl = value; return MF_OK;
+        case MF_OPTION_QKV_IMPL: ctx->qkv_impl = value; return MF_OK;
         case MF_OPTION_DECODE_CLUSTERS: ctx->decode_clusters = value ? 1u : 0u; return MF_OK;
         default: return fail(ctx, MF_ERR_INVALID_OPERATION, "unknown option %u", option);
     }

@@ -240,3 +240,89 @@ def test_projection_and_paged_append_more_rows_than_one_pass(mfk, foundry):
     for a, b in zip(*res):
         assert np.array_equal(a, b)
     assert not np.array_equal(res[0][1], case.k_pool)  # rows were written
+
+
+# ---- the tensor-core (tcgen05) projection: 16 input rows or more -------------------------------------------------
+# (m, k_dim, n_dim, n_kv, gamma, bias, blocked)
+TC_SHAPES = [
+    (16, 2048, 2048, 256, True, True, True),     # Qwen2.5-3B layer, the smallest batch that takes this path
+    (64, 3072, 3072, 1024, True, False, True),   # Llama-3.2-3B layer at C3's batch
+    (70, 896, 896, 128, True, True, True),       # two row tiles, the second partial; 7 k stages over a cluster of 7
+    (33, 1024, 1024, 128, True, True, False),    # row-major weights (128-byte swizzle)
+    (64, 256, 128, 128, False, False, True),     # no norm; two k stages
+    (130, 128, 128, 128, True, True, False),     # one k stage: no split, three row tiles
+]
+
+
+@pytest.mark.parametrize("shape", TC_SHAPES)
+def test_fused_qkv_tensor_core_kernel_against_oracle(mfk, foundry, shape):
+    m, k_dim, n_dim, n_kv, gamma, bias, blocked = shape
+    pj = Proj(m=m, k_dim=k_dim, n_dim=n_dim, n_kv=n_kv, gamma=bool(gamma), bias=bias, blocked=blocked)
+    ref = pj.oracle()
+    foundry.set_option(mfk.OPTION_QKV_IMPL, 2)  # fail rather than fall back
+    try:
+        got = _run_plain(foundry, pj)
+    finally:
+        foundry.set_option(mfk.OPTION_QKV_IMPL, 0)
+    for g, r in zip(got, ref):
+        assert _close(g, r)
+    # the mma.sync kernel on the same rows: same contract, other order of the f32 sums
+    foundry.set_option(mfk.OPTION_QKV_IMPL, 1)
+    try:
+        old = _run_plain(foundry, pj)
+    finally:
+        foundry.set_option(mfk.OPTION_QKV_IMPL, 0)
+    for g, o in zip(got, old):
+        assert _close(g, o)
+
+
+def test_fused_qkv_tensor_core_rows_do_not_depend_on_their_company(mfk, foundry):
+    """A row's bits are the same whether 16, 40 or 64 rows are projected with it (same tile columns or not)."""
+    pj = Proj(m=64, k_dim=1024, n_dim=256, n_kv=128, gamma=True, bias=True, blocked=True)
+    foundry.set_option(mfk.OPTION_QKV_IMPL, 2)
+    try:
+        full = _run_plain(foundry, pj)
+        x = dev(pj.x).reshape(64, 1024)
+        part = _run_plain(foundry, pj, m=16, x=x[24:40].contiguous())
+        one = _run_plain(foundry, pj, m=1, x=x[63].contiguous())
+    finally:
+        foundry.set_option(mfk.OPTION_QKV_IMPL, 0)
+    for a, b, c, n in zip(full, part, one, (256, 128, 128)):
+        assert np.array_equal(a.reshape(64, n)[24:40].ravel(), b)
+        assert np.array_equal(a.reshape(64, n)[63], c)
+
+
+@pytest.mark.parametrize("rope_mode", [0, 1])
+@pytest.mark.parametrize("shape", [(40, 100, 256, 16, 2, 128, 2048), (64, 0, 64, 14, 2, 64, 896)])
+def test_tensor_core_projection_and_append_in_one_launch(mfk, foundry, shape, rope_mode):
+    """Projection + RoPE + append by the tensor-core kernel against its own plain outputs pushed through KvPrepFused."""
+    import torch
+
+    m, off, cap, hq, hkv, d, k_dim = shape
+    if (hq * d) % 128 or (hkv * d) % 128:
+        pytest.skip("shape outside the tensor-core kernel's envelope")
+    case = ContigCase(n_heads=hq, n_kv_heads=hkv, head_dim=d, cached=off, m=m, capacity=cap, theta=1e4, rope_mode=rope_mode)
+    pj = Proj(m=m, k_dim=k_dim, n_dim=hq * d, n_kv=hkv * d, gamma=True, bias=True, blocked=True)
+    p = mfk.KvPrepFusedParamsResolved(hq * d, hkv * d, d, hq, hkv, hq // hkv, m, off, cap, hq * m * d, rope_mode, 0, 0)
+    cos, sin = dev(case.cos), dev(case.sin)
+    foundry.set_option(mfk.OPTION_QKV_IMPL, 2)
+    try:
+        q_bits, k_bits, v_bits = _run_plain(foundry, pj)
+        kc1, vc1 = dev(case.k_cache), dev(case.v_cache)
+        q_rot1 = torch.full((hq * m * d,), float("nan"), dtype=torch.float16, device="cuda")
+        out = tuple(torch.full((m * n,), float("nan"), dtype=torch.float16, device="cuda") for n in (hq * d, hkv * d, hkv * d))
+        foundry.fused_qkv_kv_prep(pj.args(foundry, out=out), q_rot1, kc1, vc1, cos, sin, p)
+    finally:
+        foundry.set_option(mfk.OPTION_QKV_IMPL, 0)
+    kc2, vc2 = dev(case.k_cache), dev(case.v_cache)
+    q_rot2 = torch.full((hq * m * d,), float("nan"), dtype=torch.float16, device="cuda")
+    foundry.kv_prep_fused(dev(q_bits.reshape(m, hq * d)), dev(k_bits.reshape(m, hkv * d)), dev(v_bits.reshape(m, hkv * d)),
+                          q_rot2, kc2, vc2, cos, sin, p)
+    foundry.synchronize()
+    assert np.array_equal(host(q_rot1), host(q_rot2))
+    assert np.array_equal(host(kc1), host(kc2)) and np.array_equal(host(vc1), host(vc2))
+    for o, bits in zip(out, (q_bits, k_bits, v_bits)):
+        assert np.array_equal(host(o).ravel(), bits)
+    ref = pj.oracle()
+    for g, r in zip((q_bits, k_bits, v_bits), ref):
+        assert _close(g, r)
