@@ -14,7 +14,7 @@
 // 64 x 5120 x 3072 x 2 FLOP = 2 GFLOP).  The weight rows are the 128-row M side of the MMA, 64
 // input rows its N side, the accumulator a 128 x 64 f32 tile in TMEM.  A layer has only 20-40 such
 // tiles, so each tile's k range is cut over a thread-block cluster of up to eight CTAs (one CTA per
-// SM pulling weights through a 3-stage TMA ring, 144 KB in flight per SM); the partial tiles meet
+// SM pulling weights through a TMA ring of 3 to 5 stages, up to 180 KB in flight per SM); the partial tiles meet
 // through distributed shared memory: CTA r of the cluster owns input rows [r * c, (r + 1) * c) of
 // the tile, every CTA stores its partial sums of those rows into r's receive buffer (plain
 // st.shared::cluster, coalesced over the 128 output features), one cluster barrier, and each CTA
@@ -38,12 +38,11 @@ namespace mf {
 namespace {
 
 constexpr uint32_t kTM = 128;       // output features per tile (M of the MMA)
-constexpr uint32_t kTN = 64;        // input rows per tile (N of the MMA)
+constexpr uint32_t kTN = 64;        // input rows per tile at most (N of the MMA: 16, 32, 48 or 64)
 constexpr uint32_t kStageK = 128;   // k elements per pipeline stage
-constexpr uint32_t kStages = 3;
+constexpr uint32_t kMaxStages = 5;
 constexpr uint32_t kWBytes = kTM * kStageK * 2;  // 32 KB of weights per stage
-constexpr uint32_t kXBytes = kTN * kStageK * 2;  // 16 KB of input rows per stage
-constexpr uint32_t kStageBytes = kWBytes + kXBytes;
+constexpr uint32_t kRingBytes = 184 * 1024;  // 5 stages at N = 16, 4 at 32 and 48, 3 at 64
 constexpr uint32_t kMaxSplit = 8;   // portable cluster size
 constexpr uint32_t kTcThreads = 192;
 constexpr uint64_t kWaitNs = 2000000000ull;
@@ -51,7 +50,7 @@ constexpr uint64_t kWaitNs = 2000000000ull;
 // shared memory: the ring, the receive buffer [rank][column][128 features] f32 (columns of all ranks:
 // at most kTN + kMaxSplit - 1), barriers
 constexpr uint32_t kRecvCols = kTN + kMaxSplit;
-constexpr uint32_t kOffRecv = kStages * kStageBytes;
+constexpr uint32_t kOffRecv = kRingBytes;
 constexpr uint32_t kOffBars = kOffRecv + kRecvCols * kTM * 4;
 constexpr uint32_t kTcSmem = kOffBars + 128;
 constexpr uint32_t kTcDynamic = kTcSmem + 1024;  // the ring is aligned to 1 KB by hand
@@ -61,6 +60,8 @@ struct QkvTcParams {
     uint32_t split;       // CTAs per output tile along k = cluster size
     uint32_t kb_bytes;    // bytes of a row inside one TMA box = swizzle span: 64 (blocked weights) or 128
     uint32_t n_stages;    // k_dim / kStageK
+    uint32_t tn;          // N of the MMA = rows of an input box: the row count of a tile rounded up to 16
+    uint32_t ring;        // stages of the ring: what fits into kRingBytes at this N, at most kMaxStages
     uint32_t *status;
 };
 
@@ -117,8 +118,10 @@ fused_qkv_tc_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_cons
     uint8_t *smem = tc_smem_raw + (smem_base - smem_u32(tc_smem_raw));
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t bars = smem_base + kOffBars;
-    const uint32_t bar_full = bars, bar_empty = bars + kStages * 8, bar_acc = bars + 2 * kStages * 8;
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + kOffBars + 64);
+    const uint32_t bar_full = bars, bar_empty = bars + kMaxStages * 8, bar_acc = bars + 2 * kMaxStages * 8;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + kOffBars + 96);
+    const uint32_t kStages = tp.ring, tn = tp.tn;
+    const uint32_t kXBytes = tn * kStageK * 2, kStageBytes = kWBytes + kXBytes;
     volatile uint32_t *abort_flag = tmem_slot + 1;
 
     // which tile, which k range
@@ -179,7 +182,7 @@ fused_qkv_tc_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_cons
                 const uint32_t stage = i % kStages, dst = smem_base + stage * kStageBytes + kWBytes, full = bar_full + stage * 8;
                 const uint32_t k0 = (st0 + i) * kStageK;
                 for (uint32_t sb = 0; sb < n_sub; ++sb)
-                    tma_load_2d(dst + sb * (kTN * kb), &tm_x, (int32_t)(k0 + (kb / 2) * sb), (int32_t)mrow0, full);
+                    tma_load_2d(dst + sb * (tn * kb), &tm_x, (int32_t)(k0 + (kb / 2) * sb), (int32_t)mrow0, full);
             };
             // the weights of the first stages travel while the kernel in front (the normalisation) still runs
             const uint32_t pre = min(n_local, kStages);
@@ -204,7 +207,7 @@ fused_qkv_tc_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_cons
     } else if (warp == 5) {
         // ------------------------------------------------------------------- MMA issuer ---
         if (lane == 0) {
-            constexpr uint32_t kIdesc = instr_desc_f16(kTM, kTN, 0);
+            const uint32_t kIdesc = instr_desc_f16(kTM, tn, 0);
             const uint32_t layout = kb == 64 ? 4u : 2u, sbo = 8u * kb;
             for (uint32_t i = 0; i < n_local; ++i) {
                 const uint32_t stage = i % kStages;
@@ -214,7 +217,7 @@ fused_qkv_tc_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_cons
                 const uint32_t w_addr = smem_base + stage * kStageBytes, x_addr = w_addr + kWBytes;
                 for (uint32_t sb = 0; sb < n_sub; ++sb) {
                     const uint64_t a_desc = smem_desc_layout(w_addr + sb * (kTM * kb), 16, sbo, layout);
-                    const uint64_t b_desc = smem_desc_layout(x_addr + sb * (kTN * kb), 16, sbo, layout);
+                    const uint64_t b_desc = smem_desc_layout(x_addr + sb * (tn * kb), 16, sbo, layout);
                     for (uint32_t ks = 0; ks < k_steps; ++ks)
                         tc_mma_ss(tmem, a_desc + 2 * ks, b_desc + 2 * ks, kIdesc, (i | sb | ks) != 0);  // + 32 bytes per k step
                 }
@@ -231,25 +234,30 @@ fused_qkv_tc_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_cons
         wait(bar_acc, 0, 256u);
         tc_fence_after();
         grid_dependency_wait();  // (has returned long ago in the producer; orders this thread's own accesses too)
+        // The partial tile goes through this CTA's own ring (idle now: every product that read it has completed)
+        // as [column][128 features], so that a warp hands a column to its owner with one 16-byte store per lane:
+        // scalar remote stores, one per lane and column, had cost several microseconds.
+        float *stage = reinterpret_cast<float *>(smem);
         if (!*abort_flag) {
             const uint32_t f = warp * 32 + lane;  // this thread's output feature = TMEM lane
-            uint32_t owner = 0, cl = 0;
 #pragma unroll
             for (uint32_t half = 0; half < kTN / 32; ++half) {
-                uint32_t v[32];
-                tmem_ld32(tmem + ((warp * 32) << 16) + half * 32, v);
-                tc_wait_ld();
+                if (half * 32 < tn) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem + ((warp * 32) << 16) + half * 32, v);
+                    tc_wait_ld();
 #pragma unroll
-                for (uint32_t c = 0; c < 32; ++c) {
-                    if (half * 32 + c < mt) {
-                        // [source rank][column of the owner][feature]: 32 lanes store 128 consecutive bytes
-                        st_cluster_f32(cluster_map_shared(recv + ((rank * cpr + cl) * kTM + f) * 4, owner), __uint_as_float(v[c]));
-                        if (++cl == cpr) {
-                            cl = 0;
-                            ++owner;
-                        }
-                    }
+                    for (uint32_t c = 0; c < 32; ++c)
+                        if (half * 32 + c < mt) stage[(half * 32 + c) * kTM + f] = __uint_as_float(v[c]);
                 }
+            }
+        }
+        named_bar_sync(1, 128);
+        if (!*abort_flag) {
+            for (uint32_t c = warp; c < mt; c += 4) {
+                const uint32_t owner = c / cpr, cl = c - owner * cpr;
+                const float4 v4 = *reinterpret_cast<const float4 *>(stage + c * kTM + 4 * lane);
+                st_cluster_f4(cluster_map_shared(recv + ((rank * cpr + cl) * kTM + 4 * lane) * 4, owner), v4);
             }
         }
         tc_fence_before();
@@ -400,27 +408,55 @@ mf_status launch_fused_qkv_tc(MfContext *ctx, QkvParams &qp, const AppendParams 
     tp.n_stages = qp.k_dim / kStageK;
     tp.status = ctx->d_status;
     const uint32_t tiles = (qp.n_dim + 2 * qp.n_kv) / kTM, m_tiles = (qp.m + kTN - 1) / kTN;
-    uint32_t split = std::max(1u, (uint32_t)ctx->sm_count / (tiles * m_tiles));
-    split = std::min(std::min(split, kMaxSplit), tp.n_stages);
+    tp.tn = m_tiles > 1 ? kTN : ((qp.m + 15u) / 16u) * 16u;
+    tp.ring = std::min(kMaxStages, kRingBytes / (kWBytes + tp.tn * kStageK * 2));
+    static bool configured[64] = {};
+    static int max_clusters[64][kMaxSplit + 1] = {};
+    mf_status st;
+    if (ctx->device < 64 && !configured[ctx->device]) {
+        st = check_cuda(ctx, cudaFuncSetAttribute(fused_qkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcDynamic),
+                        "cudaFuncSetAttribute(fused_qkv_tc_kernel)");
+        if (st != MF_OK) return st;
+        // how many clusters of each size the device holds at once (a cluster needs its SMs inside one GPC)
+        for (uint32_t c = 2; c <= kMaxSplit; ++c) {
+            cudaLaunchConfig_t qc{};
+            qc.gridDim = dim3(c);
+            qc.blockDim = dim3(kTcThreads);
+            qc.dynamicSmemBytes = kTcDynamic;
+            cudaLaunchAttribute qa[1];
+            qa[0].id = cudaLaunchAttributeClusterDimension;
+            qa[0].val.clusterDim.x = c;
+            qa[0].val.clusterDim.y = 1;
+            qa[0].val.clusterDim.z = 1;
+            qc.attrs = qa;
+            qc.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, fused_qkv_tc_kernel, &qc) != cudaSuccess) n = 0;
+            max_clusters[ctx->device][c] = n;
+        }
+        (void)cudaGetLastError();  // a refused query is an answer, not an error of this call
+        configured[ctx->device] = true;
+    }
+    // The k range of a tile is cut over as many CTAs as keeps every cluster of the launch resident at once.
+    uint32_t split = 1;
+    for (uint32_t c = std::min(kMaxSplit, tp.n_stages); c >= 2; --c) {
+        const int fit = ctx->device < 64 ? max_clusters[ctx->device][c] : 0;
+        if ((uint32_t)fit >= tiles * m_tiles) {
+            split = c;
+            break;
+        }
+    }
     tp.split = split;
 
     CUtensorMap tm_wq, tm_wk, tm_wv, tm_x;
-    mf_status st;
     if ((st = weight_map(ctx, &tm_wq, qp.w_q, qp.n_dim, qp.k_dim, qp.blocked != 0, what)) != MF_OK) return st;
     if ((st = weight_map(ctx, &tm_wk, qp.w_k, qp.n_kv, qp.k_dim, qp.blocked != 0, what)) != MF_OK) return st;
     if ((st = weight_map(ctx, &tm_wv, qp.w_v, qp.n_kv, qp.k_dim, qp.blocked != 0, what)) != MF_OK) return st;
     {
         const cuuint64_t dims[2] = {qp.k_dim, qp.m};
         const cuuint64_t strides[1] = {(cuuint64_t)qp.k_dim * 2};
-        const cuuint32_t box[2] = {tp.kb_bytes / 2, kTN};
+        const cuuint32_t box[2] = {tp.kb_bytes / 2, tp.tn};
         if ((st = encode_f16(ctx, &tm_x, x_in, 2, dims, strides, box, qp.blocked != 0, what)) != MF_OK) return st;
-    }
-    static bool configured[64] = {};
-    if (ctx->device < 64 && !configured[ctx->device]) {
-        st = check_cuda(ctx, cudaFuncSetAttribute(fused_qkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcDynamic),
-                        "cudaFuncSetAttribute(fused_qkv_tc_kernel)");
-        if (st != MF_OK) return st;
-        configured[ctx->device] = true;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(tiles * split, m_tiles);
