@@ -52,7 +52,8 @@ constexpr uint64_t kWaitNs = 2000000000ull;
 constexpr uint32_t kRecvCols = kTN + kMaxSplit;
 constexpr uint32_t kOffRecv = kRingBytes;
 constexpr uint32_t kOffBars = kOffRecv + kRecvCols * kTM * 4;
-constexpr uint32_t kTcSmem = kOffBars + 128;
+constexpr uint32_t kOffBias = kOffBars + 128;  // the tile's 128 bias values as f32
+constexpr uint32_t kTcSmem = kOffBias + kTM * 4;
 constexpr uint32_t kTcDynamic = kTcSmem + 1024;  // the ring is aligned to 1 KB by hand
 
 struct QkvTcParams {
@@ -230,7 +231,12 @@ fused_qkv_tc_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_cons
     // ---------------------------------------------------------------- reduce-scatter over the cluster ---
     const uint32_t cpr = (mt + S - 1) / S;  // input rows (tile columns) owned by a rank
     const uint32_t recv = smem_base + kOffRecv;
+    float *bias_s = reinterpret_cast<float *>(smem + kOffBias);
     if (warp < 4) {
+        {  // the tile's bias (a constant of the stream, like the weights) while the products run
+            const __half *bias = mtx == 0 ? qp.b_q : (mtx == 1 ? qp.b_k : qp.b_v);
+            bias_s[tid] = bias ? __half2float(bias[row0 + tid]) : 0.f;
+        }
         wait(bar_acc, 0, 256u);
         tc_fence_after();
         grid_dependency_wait();  // (has returned long ago in the producer; orders this thread's own accesses too)
@@ -279,7 +285,6 @@ fused_qkv_tc_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_cons
     // ------------------------------------------------- this rank's rows: sum, bias, f16, RoPE, stores ---
     const uint32_t my_first = rank * cpr, my_cols = my_first < mt ? min(cpr, mt - my_first) : 0u;
     const uint32_t hd = qp.head_dim, pairs_per_slot = hd / 16, pairs = kTM / 16;
-    const __half *bias = mtx == 0 ? qp.b_q : (mtx == 1 ? qp.b_k : qp.b_v);
     __half *plain = mtx == 0 ? qp.out_q : (mtx == 1 ? qp.out_k : qp.out_v);
     const uint32_t n_out = mtx == 0 ? qp.n_dim : qp.n_kv;
     const uint32_t slot0 = (mtx == 0 ? 0u : (mtx == 1 ? qp.q_slots : qp.q_slots + qp.kv_slots)) + row0 / hd;
@@ -288,20 +293,29 @@ fused_qkv_tc_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_cons
         const uint32_t cl = item / pairs, pr = item % pairs;
         const uint32_t sl = pr / pairs_per_slot, j = pr % pairs_per_slot;
         const uint32_t fa = sl * hd + 8 * j, fc = fa + hd / 2;  // features of the pair's two chunks inside the tile
+        float4 acc[4] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f),
+                         make_float4(0.f, 0.f, 0.f, 0.f)};
+        for (uint32_t r = 0; r < S; ++r) {  // the ranks' k ranges, in order
+            const float *src = rv + (r * cpr + cl) * kTM;
+            const float4 v[4] = {*reinterpret_cast<const float4 *>(src + fa), *reinterpret_cast<const float4 *>(src + fa + 4),
+                                 *reinterpret_cast<const float4 *>(src + fc), *reinterpret_cast<const float4 *>(src + fc + 4)};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                acc[q].x += v[q].x;
+                acc[q].y += v[q].y;
+                acc[q].z += v[q].z;
+                acc[q].w += v[q].w;
+            }
+        }
         Chunk a, c;
 #pragma unroll
-        for (uint32_t e = 0; e < 8; ++e) {
-            float sa = 0.f, sc = 0.f;
-            for (uint32_t r = 0; r < S; ++r) {  // the ranks' k ranges, in order
-                sa += rv[(r * cpr + cl) * kTM + fa + e];
-                sc += rv[(r * cpr + cl) * kTM + fc + e];
-            }
-            if (bias) {
-                sa += __half2float(bias[row0 + fa + e]);
-                sc += __half2float(bias[row0 + fc + e]);
-            }
-            a.h[e] = __float2half_rn(sa);
-            c.h[e] = __float2half_rn(sc);
+        for (int q = 0; q < 4; ++q) {
+            const float4 bv = *reinterpret_cast<const float4 *>(bias_s + (q < 2 ? fa : fc) + 4 * (q & 1));
+            Chunk &dst = q < 2 ? a : c;
+            dst.h[4 * (q & 1) + 0] = __float2half_rn(acc[q].x + bv.x);
+            dst.h[4 * (q & 1) + 1] = __float2half_rn(acc[q].y + bv.y);
+            dst.h[4 * (q & 1) + 2] = __float2half_rn(acc[q].z + bv.z);
+            dst.h[4 * (q & 1) + 3] = __float2half_rn(acc[q].w + bv.w);
         }
         const uint32_t s = mrow0 + my_first + cl;  // input row
         if (plain) {
