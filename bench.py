@@ -997,7 +997,8 @@ def other_workloads(args):
     """The workloads beside the headline one, measured in the same run so that they land in the same record:
     at every N the sequence-sharded long context (C5, strong scaling, exchange and merge inside the decode
     kernel) and ONE batch of the headline workload split over the ranks (strong scaling); at N = 1 also the
-    batch-1 step on contiguous caches (C2, one launch per layer, CUDA-graph replay) and the prefill chunk (C4).
+    batch-1 step on contiguous caches (C2, one launch per layer, CUDA-graph replay), the prefill chunk (C4) and the
+    headline workload on the 8-bit cache (FP8 E4M3 pages + one f32 scale per row).
     Returns {name: short record}; every rank must call it (the sub-runs synchronise)."""
     import copy
 
@@ -1009,7 +1010,8 @@ def other_workloads(args):
             ("c3_strong", lambda a: run_batched_strong(a, dict(WORKLOADS["c3"])), dict(steps=20))]
     if world == 1:
         jobs += [("c2", lambda a: run_contiguous_decode(a, CONTIGUOUS["c2"]), dict(one_launch=True, projection=False)),
-                 ("c4", run_prefill, dict(steps=20, page_size=0))]
+                 ("c4", run_prefill, dict(steps=20, page_size=0)),
+                 ("c3_kv8", lambda a: run_ours(a, dict(WORKLOADS["c3-kv8"])), dict(steps=20, no_cpu_baseline=True))]
     out = {}
     for name, fn, over in jobs:
         a = copy.copy(args)

@@ -254,7 +254,7 @@ MF_API uint64_t mf_launch_count(const MfContext *ctx);
  * its states through distributed shared memory; 1 = never (every span writes a partial and
  * the last one merges, as long launches do).
  * MF_OPTION_QKV_IMPL: which kernel projects Q/K/V (mf_fused_qkv and its append forms): 0 = the
- * tcgen05 kernel from 16 input rows when the shape allows (k_dim a multiple of 128, n_dim and
+ * tcgen05 kernel from 8 input rows when the shape allows (k_dim a multiple of 128, n_dim and
  * n_kv of 128), else the mma.sync kernel; 1 = mma.sync kernel only; 2 = the tcgen05 kernel at
  * any row count the shape allows. */
 enum {

@@ -155,7 +155,7 @@ struct QkvParams {
     uint32_t strict_release;  // 1: dependents are released after the dependency wait, not at the start
 };
 
-// Projection of 16 input rows or more on the tcgen05 tensor cores (fused_qkv_tc.cu).  Returns
+// Projection of eight input rows or more on the tcgen05 tensor cores (fused_qkv_tc.cu).  Returns
 // MF_ERR_OPERATION_NOT_SUPPORTED without launching anything when the shape is outside what it takes.
 bool fused_qkv_tc_eligible(const MfContext *ctx, const QkvParams &qp);
 mf_status launch_fused_qkv_tc(MfContext *ctx, QkvParams &qp, const AppendParams &ap, const char *what);

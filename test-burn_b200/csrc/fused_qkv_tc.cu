@@ -1,4 +1,4 @@
-// RMSNorm -> Q/K/V projection (+bias) -> RoPE -> append for 16 input rows or more, on the
+// RMSNorm -> Q/K/V projection (+bias) -> RoPE -> append for eight input rows or more, on the
 // 5th-generation tensor cores (tcgen05 + TMEM).
 //
 // Same contract as fused_qkv_kernel (kv_append.cu; the reference's qkv_project.metal:4-272 computes
@@ -7,7 +7,7 @@
 // added in f32, one rounding to f16, then RoPE and the stores of rope_and_store.  What differs from
 // the mma.sync kernel is only the order of the f32 additions inside a dot product (the tensor core's
 // own order inside a k range, the k ranges of a tile added in rank order), so a row projected with
-// 16 rows or more need not have the bits it has when projected alone; within this kernel the
+// eight rows or more need not have the bits it has when projected alone; within this kernel the
 // result of a row does not depend on how many rows travel with it.
 //
 // Shape of the work: a batch-sized projection is bound by the weights (31 MB for a 3B layer against
@@ -376,7 +376,7 @@ mf_status weight_map(MfContext *ctx, CUtensorMap *out, const void *w, uint32_t n
 bool fused_qkv_tc_eligible(const MfContext *ctx, const QkvParams &qp)
 {
     if (ctx->qkv_impl == 1) return false;
-    if (qp.m < 16 && ctx->qkv_impl != 2) return false;
+    if (qp.m < 8 && ctx->qkv_impl != 2) return false;  // below eight rows the mma.sync kernel's single launch is faster
     if (qp.k_dim % kStageK || qp.n_dim % kTM || qp.n_kv % kTM) return false;
     if (qp.head_dim < 16 || kTM % qp.head_dim) return false;
     return true;

@@ -189,7 +189,7 @@ struct MfContext {
     void *allgather_fn = nullptr;   // mf_context_set_allgather: replaces ncclAllGather in mf_allgather_merge
     uint32_t decode_clusters = 0;   // MF_OPTION_DECODE_CLUSTERS: 0 = the library decides, 1 = never
     uint32_t prefill_impl = 0;      // MF_OPTION_PREFILL_IMPL: 0 auto, 1 mma.sync, 2 tcgen05 only
-    uint32_t qkv_impl = 0;          // MF_OPTION_QKV_IMPL: 0 auto (tcgen05 from 16 input rows), 1 mma.sync, 2 tcgen05 whenever the shape allows
+    uint32_t qkv_impl = 0;          // MF_OPTION_QKV_IMPL: 0 auto (tcgen05 from 8 input rows), 1 mma.sync, 2 tcgen05 whenever the shape allows
     void *qkv_xn = nullptr;         // normalised input rows of the tcgen05 projection
     size_t qkv_xn_bytes = 0;
 };

@@ -589,7 +589,7 @@ static mf_status launch_fused_qkv(MfContext *ctx, const MfFusedQkvArgs *a, uint3
     qp.append = ap != nullptr;
     const AppendParams none{};
     const AppendParams &app = ap ? *ap : none;
-    // 16 input rows or more: the tensor-core kernel (fused_qkv_tc.cu), when the shape is one it takes
+    // eight input rows or more: the tensor-core kernel (fused_qkv_tc.cu), when the shape is one it takes
     if (fused_qkv_tc_eligible(ctx, qp)) return launch_fused_qkv_tc(ctx, qp, app, what);
     // input rows per CTA: eight, fewer when the staged rows would not fit in shared memory
     const size_t row_bytes = ((size_t)a->k_dim + kQkvPad) * sizeof(__half), budget = 200 * 1024;

@@ -242,7 +242,7 @@ def test_projection_and_paged_append_more_rows_than_one_pass(mfk, foundry):
     assert not np.array_equal(res[0][1], case.k_pool)  # rows were written
 
 
-# ---- the tensor-core (tcgen05) projection: 16 input rows or more -------------------------------------------------
+# ---- the tensor-core (tcgen05) projection: eight input rows or more (automatic choice) ----------------------------------------------
 # (m, k_dim, n_dim, n_kv, gamma, bias, blocked)
 TC_SHAPES = [
     (16, 2048, 2048, 256, True, True, True),     # Qwen2.5-3B layer, the smallest batch that takes this path
