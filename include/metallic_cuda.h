@@ -256,13 +256,17 @@ MF_API uint64_t mf_launch_count(const MfContext *ctx);
  * MF_OPTION_QKV_IMPL: which kernel projects Q/K/V (mf_fused_qkv and its append forms): 0 = the
  * tcgen05 kernel from 8 input rows when the shape allows (k_dim a multiple of 128, n_dim and
  * n_kv of 128), else the mma.sync kernel; 1 = mma.sync kernel only; 2 = the tcgen05 kernel at
- * any row count the shape allows. */
+ * any row count the shape allows.
+ * MF_OPTION_PLAN_ITEM_COST = n: what the step planner charges a CTA for every piece of a (sequence,
+ * kv head) unit it takes, in 64-key tiles (0 = the default, 6): long launches give every CTA the
+ * same tiles + n * pieces, not the same number of tiles. */
 enum {
     MF_OPTION_OVERLAP_LAUNCHES = 1,
     MF_OPTION_DECODE_STAGES = 2,
     MF_OPTION_PREFILL_IMPL = 3,
     MF_OPTION_DECODE_CLUSTERS = 4,
-    MF_OPTION_QKV_IMPL = 5
+    MF_OPTION_QKV_IMPL = 5,
+    MF_OPTION_PLAN_ITEM_COST = 6
 };
 MF_API mf_status mf_context_set_option(MfContext *ctx, uint32_t option, uint32_t value);
 /* Caller-provided scratch (device); when absent the context allocates its own

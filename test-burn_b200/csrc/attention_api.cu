@@ -593,7 +593,7 @@ mf_status mf_decode_plan_update(MfContext *ctx, MfDecodePlan *pl, const uint32_t
     // must be placed sixteen CTAs at a time, then delay the launch behind them
     pl->cluster = (pl->auto_ctas && ctas <= pl->sm_count) ? pl->max_cluster : 0;
     build_decode_plan(kv_lens_host, pl->batch, pl->n_kv_heads, ctas, pl->h_items, pl->h_cta_begin, &pl->n_units,
-                      &pl->total_tiles, &pl->cluster);
+                      &pl->total_tiles, &pl->cluster, ctx->plan_item_cost);
     return plan_upload(ctx, pl);
 }
 

@@ -1197,7 +1197,7 @@ mf_status launch_decode(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorM
 void build_decode_plan(const uint32_t *kv_lens, uint32_t batch, uint32_t n_kv_heads,
                        uint32_t max_ctas, std::vector<WorkItem> &items,
                        std::vector<uint32_t> &cta_begin, uint32_t *n_units, uint64_t *total_tiles,
-                       uint32_t *cluster_out)
+                       uint32_t *cluster_out, uint32_t item_cost)
 {
     const uint32_t max_cluster = cluster_out ? *cluster_out : 0;
     if (cluster_out) *cluster_out = 0;
@@ -1309,42 +1309,63 @@ void build_decode_plan(const uint32_t *kv_lens, uint32_t batch, uint32_t n_kv_he
         cta_begin.push_back((uint32_t)items.size());
         return;
     }
-    const uint64_t base = total / n_ctas, rem = total % n_ctas;
-    uint32_t cta = 0;
-    uint64_t room = base + (0 < rem ? 1 : 0);  // tiles the current CTA can still take
-    uint32_t slot = 0;
-    cta_begin.push_back(0);
-    for (uint32_t b = 0; b < batch; ++b) {
-        const uint32_t tiles = (kv_lens[b] + kTileKeys - 1) / kTileKeys;
-        if (tiles == 0) continue;
-        for (uint32_t kh = 0; kh < n_kv_heads; ++kh) {
-            const uint32_t unit = b * n_kv_heads + kh;
-            const uint32_t first_slot = slot;
-            const size_t first_item = items.size();
-            uint32_t t = 0;
-            while (t < tiles) {
-                if (room == 0) {
-                    ++cta;
-                    cta_begin.push_back((uint32_t)items.size());
-                    room = base + (cta < rem ? 1 : 0);
+    // Long launch: CTAs take consecutive tiles across unit boundaries.  What is equal from CTA to CTA is not the
+    // number of tiles but tiles + item_cost * items: every piece of a unit costs a CTA the staging of q, the combine
+    // of its warps, a partial and a ticket (5-6 us, the time of `item_cost` tiles), and the launch behind this one
+    // cannot start its arithmetic before the slowest CTA has ended.  With equal tile counts the few CTAs that cover
+    // three or four short sequences ended 15-20 us after the median one (batch 64, lengths 512-16384).
+    const uint64_t c = item_cost;
+    auto pieces_fit = [&](uint64_t budget, bool emit) -> uint64_t {
+        uint64_t ctas = 0, room = 0;
+        uint32_t slot = 0;
+        for (uint32_t b = 0; b < batch; ++b) {
+            const uint32_t tiles = (kv_lens[b] + kTileKeys - 1) / kTileKeys;
+            if (tiles == 0) continue;
+            for (uint32_t kh = 0; kh < n_kv_heads; ++kh) {
+                const uint32_t first_slot = slot;
+                const size_t first_item = items.size();
+                uint32_t t = 0;
+                while (t < tiles) {
+                    // a piece shorter than a few tiles is not worth its fixed cost: rather leave the room unused
+                    const uint64_t least = std::min<uint64_t>(kMinPieceTiles, tiles - t);
+                    if (room < c + least) {
+                        ++ctas;
+                        room = budget;
+                        if (emit) cta_begin.push_back((uint32_t)items.size());
+                    }
+                    const uint32_t take = (uint32_t)std::min<uint64_t>(tiles - t, room - c);
+                    if (emit) {
+                        WorkItem it{};
+                        it.seq = b;
+                        it.kvh = kh;
+                        it.tile_begin = t;
+                        it.tile_end = t + take;
+                        it.slot = slot;
+                        it.unit = b * n_kv_heads + kh;
+                        it.first_slot = first_slot;
+                        items.push_back(it);
+                    }
+                    ++slot;
+                    t += take;
+                    room -= take + c;
                 }
-                const uint32_t take = (uint32_t)((uint64_t)(tiles - t) < room ? (tiles - t) : room);
-                WorkItem it{};
-                it.seq = b;
-                it.kvh = kh;
-                it.tile_begin = t;
-                it.tile_end = t + take;
-                it.slot = slot++;
-                it.unit = unit;
-                it.first_slot = first_slot;
-                items.push_back(it);
-                t += take;
-                room -= take;
+                if (emit) {
+                    const uint32_t parts = (uint32_t)(items.size() - first_item);
+                    for (size_t i = first_item; i < items.size(); ++i) items[i].n_parts = parts;
+                }
             }
-            const uint32_t parts = (uint32_t)(items.size() - first_item);
-            for (size_t i = first_item; i < items.size(); ++i) items[i].n_parts = parts;
         }
+        return ctas;
+    };
+    // smallest budget with which the pieces fit into n_ctas CTAs
+    uint64_t lo = c + 1, hi = total + c * (uint64_t)(*n_units) + c + kMinPieceTiles;
+    while (lo < hi) {
+        const uint64_t mid = (lo + hi) / 2;
+        if (pieces_fit(mid, false) <= n_ctas) hi = mid;
+        else lo = mid + 1;
     }
+    while (pieces_fit(lo, false) > n_ctas) ++lo;  // (the count is not strictly monotonic in the budget)
+    (void)pieces_fit(lo, true);
     while (cta_begin.size() < (size_t)n_ctas + 1) cta_begin.push_back((uint32_t)items.size());
 }
 

@@ -101,6 +101,11 @@ struct DecodeParams {
     float scale_log2;
 };
 
+// What a piece of a (sequence, kv head) unit costs the CTA that takes it, in tiles (q staging, combine, partial,
+// ticket: 5-6 us against 0.7-1.5 us per tile), and the shortest piece worth that cost.  MF_OPTION_PLAN_ITEM_COST.
+constexpr uint32_t kPlanItemCost = 6;
+constexpr uint32_t kMinPieceTiles = 4;
+
 struct TensorMapKey {
     const void *base;
     uint64_t rows;
@@ -189,6 +194,7 @@ struct MfContext {
     void *allgather_fn = nullptr;   // mf_context_set_allgather: replaces ncclAllGather in mf_allgather_merge
     uint32_t decode_clusters = 0;   // MF_OPTION_DECODE_CLUSTERS: 0 = the library decides, 1 = never
     uint32_t prefill_impl = 0;      // MF_OPTION_PREFILL_IMPL: 0 auto, 1 mma.sync, 2 tcgen05 only
+    uint32_t plan_item_cost = mf::kPlanItemCost;  // MF_OPTION_PLAN_ITEM_COST
     uint32_t qkv_impl = 0;          // MF_OPTION_QKV_IMPL: 0 auto (tcgen05 from 8 input rows), 1 mma.sync, 2 tcgen05 whenever the shape allows
     void *qkv_xn = nullptr;         // normalised input rows of the tcgen05 projection
     size_t qkv_xn_bytes = 0;
@@ -246,7 +252,7 @@ mf_status ensure_scratch(MfContext *ctx, uint64_t bytes);
 void build_decode_plan(const uint32_t *kv_lens, uint32_t batch, uint32_t n_kv_heads,
                        uint32_t max_ctas, std::vector<WorkItem> &items,
                        std::vector<uint32_t> &cta_begin, uint32_t *n_units,
-                       uint64_t *total_tiles, uint32_t *cluster_out = nullptr);
+                       uint64_t *total_tiles, uint32_t *cluster_out = nullptr, uint32_t item_cost = kPlanItemCost);
 
 // Resident decode CTAs per SM for a head_dim / GQA group size (decode.cu).
 uint32_t decode_ctas_per_sm(const MfContext *ctx, uint32_t head_dim, uint32_t group);
