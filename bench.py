@@ -229,6 +229,8 @@ def run_ours(args, w):
     stream = torch.cuda.Stream(device=dev)
     copy_in, copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
     f = mfk.Foundry(dev.index, stream.cuda_stream)
+    if getattr(args, "plan_item_cost", 0):
+        f.set_option(mfk.OPTION_PLAN_ITEM_COST, args.plan_item_cost)
     if not args.no_overlap:
         f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 1)
     if kv8:
@@ -1134,6 +1136,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + sorted(LONG_CONTEXT) + sorted(CONTIGUOUS) + ["c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--plan-item-cost", type=int, default=0,
+                    help="batched paged workloads: what the step planner charges a CTA per piece of a (sequence, kv head) "
+                         "unit, in tiles (MF_OPTION_PLAN_ITEM_COST; default 20)")
     ap.add_argument("--no-other-workloads", action="store_true",
                     help="c3: only the headline workload (by default the line also carries c5, c3_strong and, at one "
                          "GPU, c2 and c4 under `other_workloads`)")

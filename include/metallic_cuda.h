@@ -258,7 +258,7 @@ MF_API uint64_t mf_launch_count(const MfContext *ctx);
  * n_kv of 128), else the mma.sync kernel; 1 = mma.sync kernel only; 2 = the tcgen05 kernel at
  * any row count the shape allows.
  * MF_OPTION_PLAN_ITEM_COST = n: what the step planner charges a CTA for every piece of a (sequence,
- * kv head) unit it takes, in 64-key tiles (0 = the default, 6): long launches give every CTA the
+ * kv head) unit it takes, in 64-key tiles (0 = the default, 20): long launches give every CTA the
  * same tiles + n * pieces, not the same number of tiles. */
 enum {
     MF_OPTION_OVERLAP_LAUNCHES = 1,

@@ -1311,7 +1311,7 @@ void build_decode_plan(const uint32_t *kv_lens, uint32_t batch, uint32_t n_kv_he
     }
     // Long launch: CTAs take consecutive tiles across unit boundaries.  What is equal from CTA to CTA is not the
     // number of tiles but tiles + item_cost * items: every piece of a unit costs a CTA the staging of q, the combine
-    // of its warps, a partial and a ticket (5-6 us, the time of `item_cost` tiles), and the launch behind this one
+    // of its warps, a partial and a ticket, for one piece of a unit its merge (5-10 us, the time of `item_cost` tiles), and the launch behind this one
     // cannot start its arithmetic before the slowest CTA has ended.  With equal tile counts the few CTAs that cover
     // three or four short sequences ended 15-20 us after the median one (batch 64, lengths 512-16384).
     const uint64_t c = item_cost;

@@ -102,8 +102,9 @@ struct DecodeParams {
 };
 
 // What a piece of a (sequence, kv head) unit costs the CTA that takes it, in tiles (q staging, combine, partial,
-// ticket: 5-6 us against 0.7-1.5 us per tile), and the shortest piece worth that cost.  MF_OPTION_PLAN_ITEM_COST.
-constexpr uint32_t kPlanItemCost = 6;
+// ticket, and for one piece of a unit its merge: 5-10 us against 0.5-1.4 us per tile; 20 measured best for the f16 and
+// the 8-bit cache alike), and the shortest piece worth that cost.  MF_OPTION_PLAN_ITEM_COST.
+constexpr uint32_t kPlanItemCost = 20;
 constexpr uint32_t kMinPieceTiles = 4;
 
 struct TensorMapKey {

@@ -109,7 +109,7 @@ def check_plan(items, cta_begin, kv_lens, n_kv_heads, max_ctas):
     if not one_item_per_cta:
         # long launches: what is equal is tiles + ITEM_COST * pieces (a piece of a unit costs its CTA the staging of q,
         # a combine, a partial and a ticket); no CTA is more than one piece and a minimum piece above the mean
-        ITEM_COST, MIN_PIECE = 6, 4
+        ITEM_COST, MIN_PIECE = 20, 4
         cost = np.array([t + ITEM_COST * (cta_begin[c + 1] - cta_begin[c]) for c, t in enumerate(per_cta)])
         assert cost.max() <= cost.sum() / n_ctas + ITEM_COST + MIN_PIECE + 1
         assert cost.max() <= np.median(cost) + ITEM_COST + MIN_PIECE + 1
