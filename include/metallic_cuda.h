@@ -507,7 +507,8 @@ MF_API mf_status mf_merge_partials_strided(MfContext *ctx, const float *acc, con
 
 /* ------------------------------------------------------ paged batched decode ---
  * No counterpart in the reference (contiguous cache, batch 1).  A plan cuts the
- * step's KV tiles into equal spans, one per resident CTA; it depends only on
+ * step's KV tiles into spans of equal cost (tiles + a charge per piece of a
+ * (sequence, kv head) unit), one per resident CTA; it depends only on
  * kv_lens (host copy), geometry and the device, and is reused by every layer of
  * the step. */
 MF_API mf_status mf_decode_plan_create(MfContext *ctx, const uint32_t *kv_lens_host, uint32_t batch,

@@ -15,7 +15,7 @@
 // run, [n_pages, Hkv, P / 16, 128, 16] (v_off8 below).  Half the bytes of the f16 cache cross HBM per key.
 //
 // Kernel shape: that of decode_kernel (decode.cu) - TMA producers filling a ring of 64-key K/V tiles, four consumer
-// warps on mma.sync with the query group on the 8-wide N side, equal spans of tiles per CTA from the host's plan,
+// warps on mma.sync with the query group on the 8-wide N side, consecutive tiles per CTA from the host's plan,
 // partials and an atomic ticket for units cut into several spans.  What differs:
 //  * a tile row is 128 bytes: one TMA box per page and tensor (K with the 128-byte swizzle, V's blocks as they lie),
 //    and the page's row scales by an untiled bulk copy counted on the same mbarrier; K and V have a producer warp
