@@ -178,6 +178,14 @@ class ClockSampler:
 
 # --------------------------------------------------------------------------- ours ---
 
+def apply_options(mfk, f, args):
+    """Library options that a run may override from the command line."""
+    if getattr(args, "plan_item_cost", 0):
+        f.set_option(mfk.OPTION_PLAN_ITEM_COST, args.plan_item_cost)
+    if getattr(args, "decode_stages", 0):
+        f.set_option(mfk.OPTION_DECODE_STAGES, args.decode_stages)
+
+
 def run_ours(args, w):
     import torch
     import torch.distributed as dist
@@ -229,8 +237,7 @@ def run_ours(args, w):
     stream = torch.cuda.Stream(device=dev)
     copy_in, copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
     f = mfk.Foundry(dev.index, stream.cuda_stream)
-    if getattr(args, "plan_item_cost", 0):
-        f.set_option(mfk.OPTION_PLAN_ITEM_COST, args.plan_item_cost)
+    apply_options(mfk, f, args)
     if not args.no_overlap:
         f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 1)
     if kv8:
@@ -656,6 +663,7 @@ def run_prefill(args):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     stream = torch.cuda.Stream(device=dev)
     f = mfk.Foundry(local, stream.cuda_stream)
+    apply_options(mfk, f, args)
     p = mfk.KvPrepFusedParamsResolved(hq * d, hkv * d, d, hq, hkv, hq // hkv, m, cached, cap, hq * m * d, 1, 0, 0)
     desc = None
     if args.page_size:
@@ -781,6 +789,7 @@ def run_contiguous_decode(args, w):
     out = torch.empty((layers, 1, hq * d), dtype=torch.float16, device=dev)
     stream = torch.cuda.Stream(device=dev)
     f = mfk.Foundry(local, stream.cuda_stream)
+    apply_options(mfk, f, args)
     if not args.no_overlap:
         f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 1)
     p = mfk.KvPrepFusedParamsResolved(hq * d, hkv * d, d, hq, hkv, hq // hkv, 1, cached, cap, hq * d, w["rope_mode"], 0, 0)
@@ -1136,6 +1145,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + sorted(LONG_CONTEXT) + sorted(CONTIGUOUS) + ["c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--decode-stages", type=int, default=0,
+                    help="depth of the decode kernel's K/V ring (MF_OPTION_DECODE_STAGES; 6 = one CTA per SM with a 192 KB ring)")
     ap.add_argument("--plan-item-cost", type=int, default=0,
                     help="batched paged workloads: what the step planner charges a CTA per piece of a (sequence, kv head) "
                          "unit, in tiles (MF_OPTION_PLAN_ITEM_COST; default 20)")

@@ -996,7 +996,10 @@ mf_status configure_one(MfContext *ctx, uint32_t *max_cluster_out)
             resident < MINB || resident_cl < MINB)
             return fail(ctx, MF_ERR_CUDA, "decode kernel: %d / %d CTAs per SM fit, the variant is built for %d", resident,
                         resident_cl, MINB);
-        uint32_t best = 0;
+        // The largest cluster size the device takes, and how many clusters of 16 and of 8 CTAs it holds at once
+        // (packed into the value: bits 0-7 the size, 8-15 the count for 16, 16-23 the count for 8): a launch whose
+        // clusters are not all resident runs them in waves.
+        uint32_t best = 0, fit16 = 0, fit8 = 0;
         const bool wide = cudaFuncSetAttribute(kern_cl, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
         for (uint32_t c : {16u, 8u}) {
             if (c == 16 && !wide) continue;
@@ -1013,12 +1016,12 @@ mf_status configure_one(MfContext *ctx, uint32_t *max_cluster_out)
             cfg.numAttrs = 1;
             int n = 0;
             if (cudaOccupancyMaxActiveClusters(&n, kern_cl, &cfg) == cudaSuccess && n >= 1) {
-                best = c;
-                break;
+                if (!best) best = c;
+                (c == 16 ? fit16 : fit8) = (uint32_t)std::min(n, 255);
             }
         }
         (void)cudaGetLastError();  // a refused query is an answer, not an error of this call
-        max_cluster[dev] = best;
+        max_cluster[dev] = best | (fit16 << 8) | (fit8 << 16);
         configured[dev] = true;
     }
     if (max_cluster_out) *max_cluster_out = max_cluster[dev];
@@ -1108,18 +1111,26 @@ uint32_t decode_max_cluster(MfContext *ctx, uint32_t head_dim, uint32_t group)
 // power of two up to max_cluster.  A large c leaves few partials to merge through memory (none when k == 1);
 // a small c wastes fewer CTAs when per_unit is not a multiple.  The largest c that keeps at least 85 % of the
 // CTAs the best choice would use is taken.
-void cluster_shape(uint32_t per_unit, uint32_t tiles_per_unit, uint32_t max_cluster, uint32_t *c_out, uint32_t *k_out)
+void cluster_shape(uint32_t per_unit, uint32_t tiles_per_unit, uint32_t units, uint32_t max_cluster_packed, uint32_t *c_out,
+                   uint32_t *k_out)
 {
     *c_out = *k_out = 0;
+    const uint32_t max_cluster = max_cluster_packed & 0xFFu, fit16 = (max_cluster_packed >> 8) & 0xFFu,
+                   fit8 = (max_cluster_packed >> 16) & 0xFFu;
+    // all clusters of the launch resident at once (sizes below 8 always are, for the launches this form is used for)
+    auto resident = [&](uint32_t c, uint32_t k) {
+        const uint32_t fit = c == 16 ? fit16 : (c == 8 ? fit8 : 0xFFFFu);
+        return fit == 0 || (uint64_t)k * units <= fit;
+    };
     uint32_t best = 0;
     for (uint32_t c = 2; c <= max_cluster; c *= 2) {
         const uint32_t k = std::min(per_unit / c, tiles_per_unit / c);
-        best = std::max(best, k * c);
+        if (resident(c, k)) best = std::max(best, k * c);
     }
     if (!best) return;
     for (uint32_t c = max_cluster; c >= 2; c /= 2) {
         const uint32_t k = std::min(per_unit / c, tiles_per_unit / c);
-        if (k && k * c * 100 >= best * 85) {
+        if (k && resident(c, k) && k * c * 100 >= best * 85) {
             *c_out = c;
             *k_out = k;
             return;
@@ -1142,7 +1153,7 @@ UniformSplit uniform_split(uint32_t units, uint32_t tiles_per_unit, uint32_t n_s
     const uint32_t flat_span = std::max<uint32_t>(1, (uint32_t)((total + want_ctas - 1) / want_ctas));
     if (max_cluster >= 2 && want_ctas >= kAlignMinParts * units && flat_span <= kAlignMaxSpan) {
         uint32_t c = 0, k = 0;
-        cluster_shape(want_ctas / units, T, max_cluster, &c, &k);
+        cluster_shape(want_ctas / units, T, units, max_cluster, &c, &k);
         if (c) {
             r.cluster = c;
             r.span = (T + k - 1) / k;
@@ -1227,7 +1238,7 @@ void build_decode_plan(const uint32_t *kv_lens, uint32_t batch, uint32_t n_kv_he
             same_tiles = tiles;
         }
         uint32_t c = 0, k = 0;
-        if (same && same_tiles) cluster_shape(n_ctas / live_units, same_tiles, max_cluster, &c, &k);
+        if (same && same_tiles) cluster_shape(n_ctas / live_units, same_tiles, live_units, max_cluster, &c, &k);
         if (c) {
             const uint32_t span = (same_tiles + k - 1) / k, ranges = (same_tiles + span - 1) / span;
             uint32_t slot = 0;
