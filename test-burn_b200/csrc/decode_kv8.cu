@@ -167,16 +167,28 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         uint32_t idx = p.cta_item_begin[blockIdx.x];
         const uint32_t end = p.cta_item_begin[blockIdx.x + 1];
         uint32_t stage = 0, phase = 0, issued = 0;
+        // Page ids travel 32 at a time, one per lane, a chunk ahead of the tiles that use them: a lookup per tile in
+        // front of its copies had put one global-load latency into every tile of the stream.  The same goes for the
+        // items: the next item, its length and its first ids are fetched while this item's tiles are issued.
+        auto ids_of = [&](const WorkItem &w, uint32_t len, uint32_t base) -> uint32_t {
+            return base + lane < (len + P - 1) / P ? __ldg(p.page_table + (size_t)w.seq * p.pt_stride + base + lane) : 0u;
+        };
+        WorkItem it_next{};
+        uint32_t L_next = 0, ids_a = 0, ids_b = 0;
+        auto fetch_item = [&](uint32_t i) {
+            it_next = p.items[i];
+            L_next = min(p.kv_lens[it_next.seq], p.pt_stride * P);  // never past the page table
+            ids_a = ids_of(it_next, L_next, it_next.tile_begin * boxes_per_tile);
+            ids_b = ids_of(it_next, L_next, it_next.tile_begin * boxes_per_tile + 32);
+        };
+        if (idx < end) fetch_item(idx);
         for (; idx < end; ++idx) {
-            const WorkItem it = p.items[idx];
-            const uint32_t L = min(p.kv_lens[it.seq], p.pt_stride * P);  // never past the page table
-            // Page ids travel 32 at a time, one per lane, a chunk ahead of the tiles that use them: a lookup per
-            // tile in front of its copies had put one global-load latency into every tile of the stream.
-            const uint32_t *pt_row = p.page_table + (size_t)it.seq * p.pt_stride;
-            const uint32_t n_pg = (L + P - 1) / P;
+            const WorkItem it = it_next;
+            const uint32_t L = L_next;
             uint32_t chunk = it.tile_begin * boxes_per_tile;
-            auto load_ids = [&](uint32_t base) -> uint32_t { return base + lane < n_pg ? __ldg(pt_row + base + lane) : 0u; };
-            uint32_t ids = load_ids(chunk), ids_next = load_ids(chunk + 32);
+            auto load_ids = [&](uint32_t base) -> uint32_t { return ids_of(it, L, base); };
+            uint32_t ids = ids_a, ids_next = ids_b;
+            if (idx + 1 < end) fetch_item(idx + 1);
             for (uint32_t t = it.tile_begin; t < it.tile_end; ++t) {
                 const uint32_t pg0 = t * boxes_per_tile;
                 if (pg0 >= chunk + 32) {
@@ -243,13 +255,27 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     uint32_t idx = p.cta_item_begin[blockIdx.x];
     const uint32_t end = p.cta_item_begin[blockIdx.x + 1];
     uint32_t stage = 0, phase = 0;
+    // The next item and its length are fetched while this item's tiles stream: two dependent loads less between
+    // the last tile of one item and the first of the next (what an item costs is what the step planner charges).
+    WorkItem it_next{};
+    uint32_t L_next = 0, pos_next = 0;
+    if (idx < end) {
+        it_next = p.items[idx];
+        L_next = p.kv_lens[it_next.seq];
+        pos_next = p.rope_positions ? p.rope_positions[it_next.seq] : 0u;
+    }
     for (; idx < end; ++idx) {
-        const WorkItem it = p.items[idx];
-        const uint32_t L_dev = p.kv_lens[it.seq];
+        const WorkItem it = it_next;
+        const uint32_t L_dev = L_next, pos_dev = pos_next;
+        if (idx + 1 < end) {
+            it_next = p.items[idx + 1];
+            L_next = p.kv_lens[it_next.seq];
+            pos_next = p.rope_positions ? p.rope_positions[it_next.seq] : 0u;
+        }
         const uint32_t L = min(L_dev, p.pt_stride * P);
         if (L_dev != L && tid == 0) atomicOr(p.status, kStatusBadPage);  // a length the page table has no entries for
         const uint32_t n_tiles = (L + kTileKeys - 1) / kTileKeys;
-        const uint32_t pos = p.rope_positions ? p.rope_positions[it.seq] : (L ? L - 1 : 0);
+        const uint32_t pos = p.rope_positions ? pos_dev : (L ? L - 1 : 0);
         const __half *cos_row = p.cos_t + (size_t)pos * half_d, *sin_row = p.sin_t + (size_t)pos * half_d;
 
         // ---- q (optionally roped, rounded to f16) -> shared memory --------------------------------------
