@@ -66,6 +66,11 @@ LONG_CONTEXT = {
                     "131072 cached tokens, page 64, sequence-sharded with (O,m,l) all-gather + merge"),
     "c5-small": dict(layers=4, n_heads=24, n_kv_heads=8, head_dim=128, kv_len=131072, page_size=64, theta=5e5,
                      rope_mode=1, name="c5 with 4 layers (test case)"),
+    # the per-GPU shape of c5 at 8 GPUs (16384 tokens per rank: short launches, cluster form) on 2 and on 4 GPUs
+    "c5-32k": dict(layers=28, n_heads=24, n_kv_heads=8, head_dim=128, kv_len=32768, page_size=64, theta=5e5, rope_mode=1,
+                   name="long-context single-sequence decode, Llama-3.2-3B shape, 32768 cached tokens, page 64, sequence-sharded"),
+    "c5-64k": dict(layers=28, n_heads=24, n_kv_heads=8, head_dim=128, kv_len=65536, page_size=64, theta=5e5, rope_mode=1,
+                   name="long-context single-sequence decode, Llama-3.2-3B shape, 65536 cached tokens, page 64, sequence-sharded"),
 }
 SEED = 0x5EED
 METRIC = "kv_append_decode_attn_tokens_per_s"

@@ -70,21 +70,41 @@ struct Smem {
 
 // Iterates the work items of one CTA, from the explicit plan or, for uniform
 // lengths, computed from the CTA index.
+__device__ __forceinline__ uint32_t kv_len_of(const DecodeParams &p, uint32_t seq)
+{
+    return p.kv_lens ? p.kv_lens[seq] : p.uniform_kv_len;
+}
+
 template <bool CL>
 struct ItemCursor {
     const DecodeParams &p;
     uint32_t idx, end;       // explicit mode
     uint32_t flat, flat_end; // uniform mode
     bool cluster_pending;    // cluster form: the one item of this CTA's cluster has not been handed out yet
+    uint32_t len;            // kv length of the item next() handed out last
+    // explicit mode: the item after the current one and its length, fetched while the current item's tiles stream
+    // (two dependent loads less between the last tile of one item and the first of the next)
+    WorkItem ahead;
+    uint32_t ahead_len;
+    __device__ void fetch_ahead()
+    {
+        if (idx < end) {
+            ahead = p.items[idx];
+            ahead_len = kv_len_of(p, ahead.seq);
+        }
+    }
     __device__ ItemCursor(const DecodeParams &pp, uint32_t cta) : p(pp)
     {
         cluster_pending = CL;
+        len = ahead_len = 0;
+        ahead = WorkItem{};
         if (CL) {
             idx = end = flat = flat_end = 0;
         } else if (p.items) {
             idx = p.cta_item_begin[cta];
             end = p.cta_item_begin[cta + 1];
             flat = flat_end = 0;
+            fetch_ahead();
         } else {
             idx = end = 0;
             flat = cta * p.uniform_span;
@@ -114,11 +134,15 @@ struct ItemCursor {
             const uint32_t tiles = it.tile_end - it.tile_begin, base = tiles / C, rem = tiles - base * C;
             it.tile_begin += r * base + min(r, rem);
             it.tile_end = it.tile_begin + base + (r < rem ? 1u : 0u);
+            len = kv_len_of(p, it.seq);
             return true;
         }
         if (p.items) {
             if (idx >= end) return false;
-            it = p.items[idx++];
+            it = ahead;
+            len = ahead_len;
+            ++idx;
+            fetch_ahead();
             return true;
         }
         if (flat >= flat_end) return false;
@@ -136,6 +160,7 @@ struct ItemCursor {
             it.first_slot = u * p.uniform_parts;
             it.slot = it.first_slot + part;
             flat = flat_end;
+            len = kv_len_of(p, it.seq);
             return true;
         }
         const uint32_t u = flat / T;
@@ -152,14 +177,10 @@ struct ItemCursor {
         it.first_slot = u + c_first;
         it.slot = u + flat / p.uniform_span;
         flat += te - tb;
+        len = kv_len_of(p, it.seq);
         return true;
     }
 };
-
-__device__ __forceinline__ uint32_t kv_len_of(const DecodeParams &p, uint32_t seq)
-{
-    return p.kv_lens ? p.kv_lens[seq] : p.uniform_kv_len;
-}
 
 // Byte offset of (row, 16-byte chunk `c16` of the D*2-byte row) inside a K or V tile.
 // A tile is a sequence of TMA boxes of 2^rpb_log2 rows (one page, or 64 rows); each box
@@ -335,7 +356,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         WorkItem it;
         uint32_t stage = 0, phase = 0, issued = 0;
         while (cur.next(it)) {
-            const uint32_t L = kv_len_of(p, it.seq);
+            const uint32_t L = cur.len;
             // Paged: the ids of 32 pages travel one per lane, a chunk ahead of the tiles that use them (a lookup
             // per tile, even issued one tile early, put a global-load latency into every tile of the stream).
             const bool paged = p.page_table != nullptr;
@@ -427,7 +448,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     WorkItem it;
     uint32_t stage = 0, phase = 0;
     while (cur.next(it)) {
-        const uint32_t L = kv_len_of(p, it.seq);
+        const uint32_t L = cur.len;
         const uint32_t n_tiles = (L + kTileKeys - 1) / kTileKeys;
         const uint32_t pos = p.rope_positions ? p.rope_positions[it.seq]
                                               : (p.kv_lens ? (L ? L - 1 : 0) : p.rope_position);

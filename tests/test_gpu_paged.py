@@ -79,6 +79,21 @@ def test_any_cta_count_gives_the_same_answer(mfk, foundry, max_ctas):
     check(case, run_fused(mfk, foundry, case, max_ctas=max_ctas), case.oracle_step())
 
 
+@pytest.mark.parametrize("item_cost", [1, 6, 64])
+@pytest.mark.parametrize("max_ctas", [7, 40])
+def test_any_item_cost_gives_the_same_answer(mfk, foundry, item_cost, max_ctas):
+    """What the planner charges per piece of a unit moves the span boundaries (and leaves some CTAs without work);
+    parity must not move."""
+    case = PagedCase(batch=9, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16,
+                     cached=[511, 40, 1000, 2049, 3, 4095, 70, 64, 900])
+    foundry.set_option(mfk.OPTION_PLAN_ITEM_COST, item_cost)
+    try:
+        got = run_fused(mfk, foundry, case, max_ctas=max_ctas)
+    finally:
+        foundry.set_option(mfk.OPTION_PLAN_ITEM_COST, 0)
+    check(case, got, case.oracle_step())
+
+
 def test_fused_step_is_idempotent(mfk, foundry):
     """Running the same step again rewrites the same row and gives the same output."""
     case = PagedCase(batch=4, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[100, 2000, 17, 900])
