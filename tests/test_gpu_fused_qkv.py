@@ -326,3 +326,16 @@ def test_tensor_core_projection_and_append_in_one_launch(mfk, foundry, shape, ro
     ref = pj.oracle()
     for g, r in zip((q_bits, k_bits, v_bits), ref):
         assert _close(g, r)
+
+
+@pytest.mark.parametrize("m", [8, 9, 17, 31, 48, 63, 65, 127, 129])
+def test_fused_qkv_tensor_core_kernel_row_counts(mfk, foundry, m):
+    """Row counts around the tile edges (N of the MMA = 16, 32, 48, 64; one, two and three 64-row tiles; the last rank
+    of the cluster owning fewer rows or none), automatic kernel choice."""
+    pj = Proj(m=m, k_dim=512, n_dim=256, n_kv=128, gamma=True, bias=True, blocked=(m % 2 == 1))
+    ref = pj.oracle()
+    before = foundry.launch_count
+    got = _run_plain(foundry, pj)
+    assert foundry.launch_count - before == 2  # the normalisation and the tensor-core projection
+    for g, r in zip(got, ref):
+        assert _close(g, r)
