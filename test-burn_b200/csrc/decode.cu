@@ -235,10 +235,12 @@ template <int D>
 __device__ __forceinline__ void push_signal_and_merge(const DecodeParams &p, const WorkItem &it, uint32_t tid,
                                                       volatile uint32_t *flags)
 {
-    // every peer sees this unit's block before its counters move
-    __threadfence_system();
+    // Every peer sees this unit's block before its counters move: the CTA's (and, in the cluster form, the
+    // cluster's) stores happen before this barrier, the barrier before the signalling threads' system-scope fence,
+    // and fences are cumulative.  Only those threads execute one: it costs microseconds, whatever is outstanding.
     named_bar_sync(1, kConsumerThreads);
     if (tid < p.push_world) {
+        __threadfence_system();
         atomicAdd_system(p.push_cnt[tid], 1u);
         atomicAdd_system(p.push_unit_cnt[tid] + it.unit, 1u);
     }
@@ -867,8 +869,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             }
             if (direct) {
                 if (!p.push_world) continue;  // nobody reads another CTA's shared memory after the barrier: done
-                // every CTA's share of the unit must be in the peers' receive blocks before the first CTA announces it
-                __threadfence_system();
+                // Every CTA's share of the unit must be in the peers' receive blocks before the first CTA announces
+                // it.  The owners' stores happen before this barrier, the barrier before the system-scope fence that
+                // the announcing CTA executes in front of its counter updates (push_signal_and_merge): fences are
+                // cumulative, so one fence orders all sixteen CTAs' stores - and a system-scope fence costs about
+                // 5 us here whatever is outstanding, which is why the owners do not each execute one of their own.
                 __syncwarp();
                 cluster_arrive_release();
                 cluster_wait_acquire();
