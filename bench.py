@@ -573,10 +573,12 @@ def run_long_context(args, w):
         "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
         "config": {"workload": w["name"], "layers": layers, "kv_len": L, "pages_per_rank": e - b,
                    "l2": "inputs larger than L2 (KV pools %.1f GB per GPU)" % (2 * layers * pool_elems * 2 / 1e9),
-                   "ctas": plan.ctas, "collective": ("none: decode kernels store %d bytes per layer into every rank's receive block "
-                                  "(peer stores + arrival counters), " % (block * 4)
-                                  + ("and merge them themselves once every rank has delivered: one launch per layer"
-                                     if args.exchange == "fused" and all_push else "merge kernel waits on the counters"))
+                   "ctas": plan.ctas, "collective": ("none: decode kernels store %d values per layer into every rank's receive block "
+                                  % block
+                                  + ("(peer stores of tagged 8-byte words: value + step tag) and merge them themselves as soon as "
+                                     "every word carries the tag: one launch per layer"
+                                     if args.exchange == "fused" and all_push else
+                                     "(peer stores, a system-scope fence, arrival counters); the merge kernel waits on the counters"))
                    if px is not None else "ncclAllGather of %d bytes per rank per layer" % (block * 4)},
         "hbm_tb_s_per_gpu": achieved / 1e3,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

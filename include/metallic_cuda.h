@@ -259,14 +259,20 @@ MF_API uint64_t mf_launch_count(const MfContext *ctx);
  * any row count the shape allows.
  * MF_OPTION_PLAN_ITEM_COST = n: what the step planner charges a CTA for every piece of a (sequence,
  * kv head) unit it takes, in 64-key tiles (0 = the default, 20): long launches give every CTA the
- * same tiles + n * pieces, not the same number of tiles. */
+ * same tiles + n * pieces, not the same number of tiles.
+ * MF_OPTION_PUSH_TAGGED: 1 (default) = mf_paged_decode_push_merge sends every float of a partial
+ * together with the step's tag in one 8-byte store and the merging side trusts a word as soon as
+ * it carries the tag, step + 1 (no system-scope fence, and nothing waits on the arrival counters,
+ * which still advance so that steps of both forms may alternate; used when no rank is in
+ * merge_only_mask); 0 = data, fence, arrival counters. */
 enum {
     MF_OPTION_OVERLAP_LAUNCHES = 1,
     MF_OPTION_DECODE_STAGES = 2,
     MF_OPTION_PREFILL_IMPL = 3,
     MF_OPTION_DECODE_CLUSTERS = 4,
     MF_OPTION_QKV_IMPL = 5,
-    MF_OPTION_PLAN_ITEM_COST = 6
+    MF_OPTION_PLAN_ITEM_COST = 6,
+    MF_OPTION_PUSH_TAGGED = 7
 };
 MF_API mf_status mf_context_set_option(MfContext *ctx, uint32_t option, uint32_t value);
 /* Caller-provided scratch (device); when absent the context allocates its own
@@ -727,7 +733,8 @@ MF_API mf_status mf_paged_kv8_gather(MfContext *ctx, const MfPagedKv8 *cache, ui
  * MF_ERR_TIMEOUT at mf_synchronize) until every rank's counter has reached the step's
  * expected value and merges out of its own memory.
  *   recv[r]     rank r's receive buffer, 2 * world * rows * (head_dim + 2) floats
- *               ([step parity][source rank][acc | m | l]), mapped in this process
+ *               ([step parity][source rank][acc | m | l]), followed by the same blocks as 8-byte
+ *               {tag, float} words (MF_OPTION_PUSH_TAGGED), mapped in this process
  *   counters[r] rank r's counters (8 per-source totals, 8 "merged by rank" counts, then one per
  *               unit), zero before the first step
  * Steps are numbered from 0 and must be issued in the same order on every rank, and a rank

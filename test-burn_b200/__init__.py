@@ -40,6 +40,7 @@ DTYPE_F16, DTYPE_F32, DTYPE_U32 = 0, 1, 2
 ALL_SEQUENCES = 0xFFFFFFFF
 OPTION_OVERLAP_LAUNCHES, OPTION_DECODE_STAGES, OPTION_PREFILL_IMPL, OPTION_DECODE_CLUSTERS, OPTION_QKV_IMPL = 1, 2, 3, 4, 5
 OPTION_PLAN_ITEM_COST = 6
+OPTION_PUSH_TAGGED = 7
 KV_LAYOUT_EXPANDED_HEADS, KV_LAYOUT_COMPACT_KV_HEADS = 0, 1
 
 

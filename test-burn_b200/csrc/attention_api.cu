@@ -737,6 +737,16 @@ static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, con
             p.push_expected = (uint32_t)__builtin_popcount(merge_mask) * (step + 1);
             p.push_local = px->recv[px->rank] + (uint64_t)(step & 1) * px->world * block;
             p.push_local_cnt = px->counters[px->rank] + kPeerUnitCounters;
+            if (ctx->push_tagged && px->merge_only_mask == 0) {
+                // tagged words: the same blocks, eight bytes per value, in a region of their own behind the plain
+                // floats (a float left by a step in the counted form can then never be read as a tag)
+                p.push_tagged = 1;
+                p.push_tag = step + 1;
+                const uint64_t tagged_base = (uint64_t)2 * px->world * block;
+                for (uint32_t r = 0; r < px->world; ++r)
+                    p.push_dst[r] = px->recv[r] + tagged_base + 2 * (((uint64_t)(step & 1) * px->world + px->rank) * block);
+                p.push_local = px->recv[px->rank] + tagged_base + 2 * ((uint64_t)(step & 1) * px->world * block);
+            }
         }
     }
     CUtensorMap tm_k, tm_v;

@@ -237,6 +237,7 @@ mf_status mf_context_set_option(MfContext *ctx, uint32_t option, uint32_t value)
         case MF_OPTION_DECODE_STAGES: ctx->decode_stages = value; return MF_OK;
         case MF_OPTION_PREFILL_IMPL: ctx->prefill_impl = value; return MF_OK;
         case MF_OPTION_QKV_IMPL: ctx->qkv_impl = value; return MF_OK;
+        case MF_OPTION_PUSH_TAGGED: ctx->push_tagged = value ? 1u : 0u; return MF_OK;
         case MF_OPTION_PLAN_ITEM_COST: ctx->plan_item_cost = value ? value : mf::kPlanItemCost; return MF_OK;
         case MF_OPTION_DECODE_CLUSTERS: ctx->decode_clusters = value ? 1u : 0u; return MF_OK;
         default: return fail(ctx, MF_ERR_INVALID_OPERATION, "unknown option %u", option);

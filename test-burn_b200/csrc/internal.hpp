@@ -87,6 +87,9 @@ struct DecodeParams {
     uint32_t *push_cnt[8];   // rank r's arrival counter for THIS rank
     uint32_t *push_unit_cnt[8];  // rank r's per-unit arrival counters
     // Merge inside the kernel: after pushing a unit, wait for the ranks of push_mask and write `out`.
+    // Tagged words: every float travels with the step's tag in one 8-byte store, so a reader trusts a word as soon as
+    // it carries the tag: no system-scope fence, no arrival counters (only with push_merge and no merge-only ranks).
+    uint32_t push_tagged, push_tag;
     uint32_t push_merge;     // 0 = the caller merges with a second kernel
     uint32_t push_mask;      // ranks that push in this step
     uint32_t push_expected;  // value the unit counter reaches when all of them have
@@ -196,6 +199,7 @@ struct MfContext {
     uint32_t decode_clusters = 0;   // MF_OPTION_DECODE_CLUSTERS: 0 = the library decides, 1 = never
     uint32_t prefill_impl = 0;      // MF_OPTION_PREFILL_IMPL: 0 auto, 1 mma.sync, 2 tcgen05 only
     uint32_t plan_item_cost = mf::kPlanItemCost;  // MF_OPTION_PLAN_ITEM_COST
+    uint32_t push_tagged = 1;       // MF_OPTION_PUSH_TAGGED: 1 = tagged words in the fused exchange, 0 = fence + counters
     uint32_t qkv_impl = 0;          // MF_OPTION_QKV_IMPL: 0 auto (tcgen05 from 8 input rows), 1 mma.sync, 2 tcgen05 whenever the shape allows
     void *qkv_xn = nullptr;         // normalised input rows of the tcgen05 projection
     size_t qkv_xn_bytes = 0;

@@ -102,7 +102,9 @@ mf_status mf_peer_exchange_create(MfContext *ctx, uint32_t world, uint32_t rank,
     if (world == 0 || world > 8 || rank >= world || rows == 0 || head_dim == 0)
         return fail(ctx, MF_ERR_INVALID_OPERATION, "peer exchange: rank %u of %u, %u rows x %u", rank, world, rows, head_dim);
     memset(px, 0, sizeof(*px));
-    const size_t bytes = counter_bytes(rows) + (size_t)2 * world * rows * (head_dim + 2) * sizeof(float);
+    // two step parities x world blocks of rows x (head_dim + 2) values, twice: as plain floats (the counted form), and
+    // behind them as 8-byte words of a float and its tag (the tagged form)
+    const size_t bytes = counter_bytes(rows) + (size_t)2 * world * rows * (head_dim + 2) * 3 * sizeof(float);
     void *base = nullptr;
     mf_status st = check_cuda(ctx, cudaMalloc(&base, bytes), "peer exchange: cudaMalloc");
     if (st != MF_OK) return st;

@@ -140,6 +140,7 @@ def _two_gpu_worker(rank, world, port, ret):
         ok = True
         for step in range(6):
             f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, step // 3)
+            f.set_option(mfk.OPTION_PUSH_TAGGED, 1 if step < 4 else 0)  # steps 1, 3: tagged words; step 5: counters
             out = torch.full((Hq, D), float("nan"), dtype=torch.float16, device="cuda")
             if step % 2 == 0:  # two launches: push, then the waiting merge kernel
                 f.paged_decode_partial_push(plan, desc, q_rot, px, step, n_heads=Hq, scale=float(full.scale))
