@@ -427,7 +427,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
     // Relaxed launches let the next launch of the stream be scheduled right away (it sets up, and its
     // producer may stream its own K/V, while this grid works); strict ones do so only after their wait.
-    if (!p.strict_release) grid_launch_dependents();
+    // Cluster-form launches release theirs when their own last tile has been requested: the next launch then
+    // fills its ring while this one combines and writes, not while it still streams (its requests would queue in
+    // front of tiles this launch is waiting for).
+    if (!p.strict_release && !p.release_late) grid_launch_dependents();
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------ producer ---
         if (lane == 0) {
@@ -502,6 +505,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                 }
             }
         }
+        if (p.release_late) grid_launch_dependents();
         // After an abort the consumers no longer wait for the ring: make sure our
         // own copies have landed before the CTA gives its shared memory back.
         if (flags[0]) {
@@ -1163,6 +1167,7 @@ mf_status launch_one(MfContext *ctx, const CUtensorMap &tm_k, const CUtensorMap 
     if (ctx->overlap_launches || p.cluster_size > 1) {
         const bool programmatic = ctx->overlap_launches != 0;
         p.strict_release = (programmatic && ctx->next_launch_strict()) ? 1u : 0u;
+        p.release_late = (clustered && !p.strict_release) ? 1u : 0u;
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(n_ctas);
         cfg.blockDim = dim3(kThreads);

@@ -80,6 +80,7 @@ struct DecodeParams {
     uint32_t whole_rows;     // 1: one TMA box per page fetches both halves (3-D tensor map)
     uint32_t early_stream;   // 1: the producer may stream K/V before the previous kernel has finished
     uint32_t strict_release; // 1: dependents are released after this grid's own dependency wait, not at its start
+    uint32_t release_late;   // 1: dependents are released when the producer has requested its last tile
     // Push mode (sequence-sharded decode): the finished (acc, m, l) of every unit is stored straight
     // into each rank's receive block over NVLink and announced on that rank's arrival counter.
     uint32_t push_world;     // 0 = off
