@@ -546,30 +546,62 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         const __half *sin_row = p.sin_t + (size_t)pos * half_d;
 
         // ---- q (optionally roped, rounded to f16) -> shared memory -----------------
+        // Every global load of this prologue is issued before the first one is used: q of the group's heads, the
+        // position's cos / sin pair, and - in the CTA that will meet the sequence's last tile - the new k and v row
+        // and the id of the page they go to.  One memory latency instead of one per pass and one more at the last tile.
         named_bar_sync(1, kConsumerThreads);  // previous item is done with q_s / comb
-        for (uint32_t e = tid; e < HP * half_d; e += kConsumerThreads) {
-            const uint32_t g = e / half_d;
-            const uint32_t pr = e - g * half_d;
-            uint32_t di, dj;
-            if (p.rope_mode == MF_ROPE_MODE_NORMAL) {
-                di = 2 * pr;
-                dj = di + 1;
-            } else {
-                di = pr;
-                dj = pr + half_d;
-            }
-            __half oi = __float2half_rn(0.f), oj = oi;
+        constexpr uint32_t kQPasses = (HP * (D / 2)) / kConsumerThreads;
+        static_assert((HP * (D / 2)) % kConsumerThreads == 0 && kConsumerThreads % (D / 2) == 0, "q staging");
+        const uint32_t pr = tid % half_d;  // the same pair of dims in every pass
+        const uint32_t di = p.rope_mode == MF_ROPE_MODE_NORMAL ? 2 * pr : pr;
+        const uint32_t dj = p.rope_mode == MF_ROPE_MODE_NORMAL ? di + 1 : pr + half_d;
+        __half qi[kQPasses], qj[kQPasses];
+#pragma unroll
+        for (uint32_t j = 0; j < kQPasses; ++j) {
+            const uint32_t g = (tid + j * kConsumerThreads) / half_d;
+            qi[j] = qj[j] = __float2half_rn(0.f);
             if (g < G) {
-                const uint32_t h = it.kvh * G + g;
-                const __half *src = p.q + (size_t)it.seq * p.q_stride_b + (size_t)h * p.q_stride_h;
-                oi = src[di];
-                oj = src[dj];
-                if (p.rope) {
-                    rope_pair(__half2float(oi), __half2float(oj), __half2float(cos_row[pr]),
-                              __half2float(sin_row[pr]), oi, oj);
+                const __half *src = p.q + (size_t)it.seq * p.q_stride_b + (size_t)(it.kvh * G + g) * p.q_stride_h;
+                qi[j] = src[di];
+                qj[j] = src[dj];
+            }
+        }
+        float cs = 1.f, sn = 0.f;
+        if (p.rope) {
+            cs = __half2float(cos_row[pr]);
+            sn = __half2float(sin_row[pr]);
+        }
+        // the row this step appends, if this CTA's span ends the sequence
+        const bool ends_seq = p.append && it.tile_begin < n_tiles && it.tile_end >= n_tiles;
+        __half kn_i = __float2half_rn(0.f), kn_j = kn_i, vn = kn_i;
+        uint32_t new_page = 0;
+        bool store_ok = true;
+        if (ends_seq) {
+            if (tid < half_d) {
+                const __half *ks = p.k_new + (size_t)it.seq * p.knew_stride_b + (size_t)it.kvh * D;
+                kn_i = ks[di];
+                kn_j = ks[dj];
+            }
+            if (tid < (uint32_t)D) vn = p.v_new[(size_t)it.seq * p.knew_stride_b + (size_t)it.kvh * D + tid];
+            if (p.page_table) {
+                // The page id of the new row comes from the caller's device-side table: one that is not a page
+                // of this pool (or a length the table has no entry for) skips the store and the splice and
+                // raises the status bit; the output of that sequence is then not meaningful.
+                store_ok = (L - 1) / p.page_size < p.pt_stride;
+                if (store_ok) {
+                    new_page = p.page_table[(size_t)it.seq * p.pt_stride + (L - 1) / p.page_size];
+                    store_ok = new_page < p.n_pages;
                 }
+            }
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < kQPasses; ++j) {
+            const uint32_t g = (tid + j * kConsumerThreads) / half_d;
+            __half oi = qi[j], oj = qj[j];
+            if (g < G) {
+                if (p.rope) rope_pair(__half2float(oi), __half2float(oj), cs, sn, oi, oj);
                 if (p.q_rot && it.tile_begin == 0) {
-                    __half *dst = p.q_rot + (size_t)it.seq * p.q_stride_b + (size_t)h * p.q_stride_h;
+                    __half *dst = p.q_rot + (size_t)it.seq * p.q_stride_b + (size_t)(it.kvh * G + g) * p.q_stride_h;
                     dst[di] = oi;
                     dst[dj] = oj;
                 }
@@ -577,6 +609,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             q_s[g * S::kQStride + di] = oi;
             q_s[g * S::kQStride + dj] = oj;
         }
+        if (ends_seq && p.rope) rope_pair(__half2float(kn_i), __half2float(kn_j), cs, sn, kn_i, kn_j);
         named_bar_sync(1, kConsumerThreads);
 
         // B fragments of Q^T: [k = 16 dims][n = 8 heads] per k-step and n-tile.
@@ -618,53 +651,24 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                 // this step (and store it to the cache), then clear V rows past L so
                 // that stale or never-written rows cannot leak NaNs through 0 * NaN.
                 const uint32_t r_new = (L - 1) - key0;
-                // The page id of the new row comes from the caller's device-side table: one that is not a
-                // page of this pool (or a length the table has no entry for) skips the store and the splice
-                // and raises the status bit; the output of that sequence is then not meaningful.
-                bool store_ok = true;
-                uint32_t new_page = 0;
-                if (p.append && p.page_table) {
-                    store_ok = (L - 1) / p.page_size < p.pt_stride;
-                    if (store_ok) {
-                        new_page = p.page_table[(size_t)it.seq * p.pt_stride + (L - 1) / p.page_size];
-                        store_ok = new_page < p.n_pages;
-                    }
-                    if (!store_ok && tid == 0) atomicOr(p.status, kStatusBadPage);
-                }
+                if (p.append && !store_ok && tid == 0) atomicOr(p.status, kStatusBadPage);
                 if (p.append && store_ok) {
                     size_t krow, vrow;
                     if (p.page_table) {
-                        const uint32_t page = new_page;
-                        krow = vrow = ((size_t)page * p.n_kv_heads + it.kvh) * p.page_size + (L - 1) % p.page_size;
+                        krow = vrow = ((size_t)new_page * p.n_kv_heads + it.kvh) * p.page_size + (L - 1) % p.page_size;
                     } else {
                         krow = (size_t)it.seq * p.k_rows_b + (size_t)it.kvh * p.k_rows_h + (L - 1);
                         vrow = (size_t)it.seq * p.v_rows_b + (size_t)it.kvh * p.v_rows_h + (L - 1);
                     }
-                    const __half *ks = p.k_new + (size_t)it.seq * p.knew_stride_b + (size_t)it.kvh * D;
-                    const __half *vs = p.v_new + (size_t)it.seq * p.knew_stride_b + (size_t)it.kvh * D;
-                    for (uint32_t pr = tid; pr < half_d; pr += kConsumerThreads) {
-                        uint32_t di, dj;
-                        if (p.rope_mode == MF_ROPE_MODE_NORMAL) {
-                            di = 2 * pr;
-                            dj = di + 1;
-                        } else {
-                            di = pr;
-                            dj = pr + half_d;
-                        }
-                        __half oi = ks[di], oj = ks[dj];
-                        if (p.rope) {
-                            rope_pair(__half2float(oi), __half2float(oj), __half2float(cos_row[pr]),
-                                      __half2float(sin_row[pr]), oi, oj);
-                        }
-                        p.k_base[krow * D + di] = oi;
-                        p.k_base[krow * D + dj] = oj;
-                        *reinterpret_cast<__half *>(k_tile + tile_off<D>(r_new, di >> 3, rpb_log2) + (di & 7) * 2) = oi;
-                        *reinterpret_cast<__half *>(k_tile + tile_off<D>(r_new, dj >> 3, rpb_log2) + (dj & 7) * 2) = oj;
+                    if (tid < half_d) {  // the pair this thread roped in the prologue
+                        p.k_base[krow * D + di] = kn_i;
+                        p.k_base[krow * D + dj] = kn_j;
+                        *reinterpret_cast<__half *>(k_tile + tile_off<D>(r_new, di >> 3, rpb_log2) + (di & 7) * 2) = kn_i;
+                        *reinterpret_cast<__half *>(k_tile + tile_off<D>(r_new, dj >> 3, rpb_log2) + (dj & 7) * 2) = kn_j;
                     }
-                    for (uint32_t d = tid; d < (uint32_t)D; d += kConsumerThreads) {
-                        const __half x = vs[d];
-                        p.v_base[vrow * D + d] = x;
-                        *reinterpret_cast<__half *>(v_tile + tile_off<D>(r_new, d >> 3, rpb_log2) + (d & 7) * 2) = x;
+                    if (tid < (uint32_t)D) {
+                        p.v_base[vrow * D + tid] = vn;
+                        *reinterpret_cast<__half *>(v_tile + tile_off<D>(r_new, tid >> 3, rpb_log2) + (tid & 7) * 2) = vn;
                     }
                 }
                 const uint32_t first_dead = L - key0;  // 1..64
