@@ -279,21 +279,51 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         const __half *cos_row = p.cos_t + (size_t)pos * half_d, *sin_row = p.sin_t + (size_t)pos * half_d;
 
         // ---- q (optionally roped, rounded to f16) -> shared memory --------------------------------------
+        // Every global load of this prologue is issued before the first one is used: q of the group's heads, the
+        // position's cos / sin pair, and - in the CTA that will meet the sequence's last tile - the new k and v
+        // row and the id of the page they go to.
         named_bar_sync(1, kConsumerThreads);
-        for (uint32_t e = tid; e < kHP * half_d; e += kConsumerThreads) {
-            const uint32_t hg = e / half_d, pr = e - hg * half_d;
-            const uint32_t di = p.rope_mode == MF_ROPE_MODE_NORMAL ? 2 * pr : pr;
-            const uint32_t dj = p.rope_mode == MF_ROPE_MODE_NORMAL ? di + 1 : pr + half_d;
-            __half oi = __float2half_rn(0.f), oj = oi;
+        constexpr uint32_t kQPasses = (kHP * (kD / 2)) / kConsumerThreads;
+        static_assert((kHP * (kD / 2)) % kConsumerThreads == 0 && kConsumerThreads % (kD / 2) == 0, "q staging");
+        const uint32_t pr = tid % half_d;  // the same pair of dims in every pass
+        const uint32_t di = p.rope_mode == MF_ROPE_MODE_NORMAL ? 2 * pr : pr;
+        const uint32_t dj = p.rope_mode == MF_ROPE_MODE_NORMAL ? di + 1 : pr + half_d;
+        __half qi[kQPasses], qj[kQPasses];
+#pragma unroll
+        for (uint32_t j = 0; j < kQPasses; ++j) {
+            const uint32_t hg = (tid + j * kConsumerThreads) / half_d;
+            qi[j] = qj[j] = __float2half_rn(0.f);
             if (hg < G) {
-                const uint32_t h = it.kvh * G + hg;
-                const __half *src = p.q + (size_t)it.seq * p.q_stride_b + (size_t)h * p.q_stride_h;
-                oi = src[di];
-                oj = src[dj];
-                if (p.rope)
-                    rope_pair(__half2float(oi), __half2float(oj), __half2float(cos_row[pr]), __half2float(sin_row[pr]), oi, oj);
+                const __half *src = p.q + (size_t)it.seq * p.q_stride_b + (size_t)(it.kvh * G + hg) * p.q_stride_h;
+                qi[j] = src[di];
+                qj[j] = src[dj];
+            }
+        }
+        float cs = 1.f, sn = 0.f;
+        if (p.rope) {
+            cs = __half2float(cos_row[pr]);
+            sn = __half2float(sin_row[pr]);
+        }
+        const bool ends_seq = p.append && it.tile_begin < n_tiles && it.tile_end >= n_tiles;
+        __half kn_i = __float2half_rn(0.f), kn_j = kn_i, vn = kn_i;
+        uint32_t new_page = 0;
+        if (ends_seq) {
+            if (tid < half_d) {
+                const __half *ks = p.k_new + (size_t)it.seq * p.knew_stride_b + (size_t)it.kvh * kD;
+                kn_i = ks[di];
+                kn_j = ks[dj];
+            }
+            vn = p.v_new[(size_t)it.seq * p.knew_stride_b + (size_t)it.kvh * kD + tid];
+            new_page = p.page_table[(size_t)it.seq * p.pt_stride + (L - 1) / P];
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < kQPasses; ++j) {
+            const uint32_t hg = (tid + j * kConsumerThreads) / half_d;
+            __half oi = qi[j], oj = qj[j];
+            if (hg < G) {
+                if (p.rope) rope_pair(__half2float(oi), __half2float(oj), cs, sn, oi, oj);
                 if (p.q_rot && it.tile_begin == 0) {
-                    __half *dst = p.q_rot + (size_t)it.seq * p.q_stride_b + (size_t)h * p.q_stride_h;
+                    __half *dst = p.q_rot + (size_t)it.seq * p.q_stride_b + (size_t)(it.kvh * G + hg) * p.q_stride_h;
                     dst[di] = oi;
                     dst[dj] = oj;
                 }
@@ -301,6 +331,7 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
             q_s[hg * kQStride + di] = oi;
             q_s[hg * kQStride + dj] = oj;
         }
+        if (ends_seq && p.rope) rope_pair(__half2float(kn_i), __half2float(kn_j), cs, sn, kn_i, kn_j);
         named_bar_sync(1, kConsumerThreads);
         // B fragments of Q^T (k = 16 dims x n = 8 heads per step).  A thread's four K bytes are dims 4c .. 4c + 3 of the
         // 16-dim chunk, so MMA k-index 2c, 2c + 1 stands for dims 4c, 4c + 1 and 2c + 8, 2c + 9 for dims 4c + 2, 4c + 3.
@@ -336,25 +367,17 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                 bool store_ok = p.append != 0;
                 uint32_t new_row = 0;
                 if (p.append) {
-                    const uint32_t page = p.page_table[(size_t)it.seq * p.pt_stride + (L - 1) / P];
+                    const uint32_t page = new_page;  // read in the prologue
                     store_ok = page < p.n_pages;
                     if (!store_ok && tid == 0) atomicOr(p.status, kStatusBadPage);
                     new_row = (page * p.n_kv_heads + it.kvh) * P + (L - 1) % P;
                 }
                 if (store_ok) {
-                    const __half *ks = p.k_new + (size_t)it.seq * p.knew_stride_b + (size_t)it.kvh * kD;
-                    const __half *vs = p.v_new + (size_t)it.seq * p.knew_stride_b + (size_t)it.kvh * kD;
-                    if (tid < half_d) {
-                        const uint32_t pr = tid;
-                        const uint32_t di = p.rope_mode == MF_ROPE_MODE_NORMAL ? 2 * pr : pr;
-                        const uint32_t dj = p.rope_mode == MF_ROPE_MODE_NORMAL ? di + 1 : pr + half_d;
-                        __half oi = ks[di], oj = ks[dj];
-                        if (p.rope)
-                            rope_pair(__half2float(oi), __half2float(oj), __half2float(cos_row[pr]), __half2float(sin_row[pr]), oi, oj);
-                        row_s[di] = oi;
-                        row_s[dj] = oj;
+                    if (tid < half_d) {  // the pair this thread roped in the prologue
+                        row_s[di] = kn_i;
+                        row_s[dj] = kn_j;
                     }
-                    row_s[kD + tid] = vs[tid];
+                    row_s[kD + tid] = vn;
                     named_bar_sync(2, kConsumerThreads);
                     // one element of each row per thread: row maxima by warp shuffles and four words of shared memory
                     const float xk = __half2float(row_s[tid]), xv = __half2float(row_s[kD + tid]);
