@@ -685,9 +685,14 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             const uint32_t wkey0 = key0 + warp * 16;
             if (wkey0 < L) {
                 // ---- S^T (16 keys x 8*NT heads) = K_tile Q^T ---------------------------
-                float c[NT][4];
+                // two accumulators per n-tile (even and odd k-steps): the products of a tile form two dependent
+                // chains of D / 32 instead of one of D / 16
+                float c[NT][4], c_odd[NT][4];
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.f;
+                for (int nt = 0; nt < NT; ++nt) {
+                    c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.f;
+                    c_odd[nt][0] = c_odd[nt][1] = c_odd[nt][2] = c_odd[nt][3] = 0.f;
+                }
                 {
                     const uint32_t row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
@@ -695,8 +700,15 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                         uint32_t a[4];
                         ldmatrix_x4(a, k_addr + tile_off<D>(row, 2 * ks + (lane >> 4), rpb_log2));
 #pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) mma_m16n8k16(c[nt], a, bq[nt][ks][0], bq[nt][ks][1]);
+                        for (int nt = 0; nt < NT; ++nt) mma_m16n8k16((ks & 1) ? c_odd[nt] : c[nt], a, bq[nt][ks][0], bq[nt][ks][1]);
                     }
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    c[nt][0] += c_odd[nt][0];
+                    c[nt][1] += c_odd[nt][1];
+                    c[nt][2] += c_odd[nt][2];
+                    c[nt][3] += c_odd[nt][3];
                 }
                 // ---- online softmax over this warp's 16 keys ---------------------------
                 const uint32_t kr0 = wkey0 + (lane >> 2);
