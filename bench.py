@@ -64,6 +64,12 @@ LONG_CONTEXT = {
     "c5": dict(layers=28, n_heads=24, n_kv_heads=8, head_dim=128, kv_len=131072, page_size=64, theta=5e5, rope_mode=1,
                name="long-context single-sequence decode, Llama-3.2-3B shape: 28 layers, 24q/8kv heads, D128, "
                     "131072 cached tokens, page 64, sequence-sharded with (O,m,l) all-gather + merge"),
+    # c5 on the 8-bit cache: every rank's shard through mf_paged_decode_kv8_partial, then all-gather + merge
+    "c5-kv8": dict(layers=28, n_heads=24, n_kv_heads=8, head_dim=128, kv_len=131072, page_size=64, theta=5e5, rope_mode=1,
+                   kv8=True,
+                   name="long-context single-sequence decode on the 8-bit cache (FP8 E4M3 + one f32 scale per row), "
+                        "Llama-3.2-3B shape: 28 layers, 24q/8kv heads, D128, 131072 cached tokens, page 64, "
+                        "sequence-sharded with (O,m,l) all-gather + merge"),
     "c5-small": dict(layers=4, n_heads=24, n_kv_heads=8, head_dim=128, kv_len=131072, page_size=64, theta=5e5,
                      rope_mode=1, name="c5 with 4 layers (test case)"),
     # the per-GPU shape of c5 at 8 GPUs (16384 tokens per rank: short launches, cluster form) on 2 and on 4 GPUs
@@ -440,8 +446,20 @@ def run_long_context(args, w):
     gen = torch.Generator(device=dev)
     gen.manual_seed(SEED + rank)
     pool_elems = (e - b) * hkv * P * d
-    k_pools = [torch.empty(pool_elems, dtype=torch.float16, device=dev).normal_(generator=gen) for _ in range(layers)]
-    v_pools = [torch.empty(pool_elems, dtype=torch.float16, device=dev).normal_(generator=gen) for _ in range(layers)]
+    kv8 = bool(w.get("kv8"))
+    if kv8:
+        # bytes of finite E4M3 values (exponent field below 15) with random signs; scales of N(0,1) rows (amax / 448)
+        def fp8_pool():
+            t = torch.randint(0, 0x78, (pool_elems,), dtype=torch.uint8, device=dev, generator=gen)
+            return t | (torch.randint(0, 2, (pool_elems,), dtype=torch.uint8, device=dev, generator=gen) << 7)
+
+        k_pools = [fp8_pool() for _ in range(layers)]
+        v_pools = [fp8_pool() for _ in range(layers)]
+        k_scales = [torch.full((pool_elems // d,), 3.5 / 448, dtype=torch.float32, device=dev) for _ in range(layers)]
+        v_scales = [torch.full((pool_elems // d,), 3.5 / 448, dtype=torch.float32, device=dev) for _ in range(layers)]
+    else:
+        k_pools = [torch.empty(pool_elems, dtype=torch.float16, device=dev).normal_(generator=gen) for _ in range(layers)]
+        v_pools = [torch.empty(pool_elems, dtype=torch.float16, device=dev).normal_(generator=gen) for _ in range(layers)]
     table = torch.arange(e - b, dtype=torch.int32, device=dev).view(1, -1)
     lens_host = np.array([n_local], np.uint32)
     d_lens = torch.from_numpy(lens_host.view(np.int32)).to(dev)
@@ -460,9 +478,18 @@ def run_long_context(args, w):
         # 2: the pools of a layer are written by nothing but that layer's own fused append, so every rank
         # (not only the one that appends) may stream K/V before the previous launch has ended
         f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 2)
-    plan = f.decode_plan(lens_host, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P)
-    descs = [mfk.paged_kv(k_pools[i].view(e - b, hkv, P, d), v_pools[i].view(e - b, hkv, P, d), table, d_lens,
-                          n_kv_heads=hkv, page_size=P, head_dim=d) for i in range(layers)]
+    if kv8:
+        # the 8-bit kernel takes the plain form of the plan (an explicit CTA count) and the partial + gather route
+        plan = f.decode_plan(lens_host, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P,
+                             max_ctas=2 * torch.cuda.get_device_properties(dev).multi_processor_count)
+        descs = [mfk.paged_kv8(k_pools[i].view(e - b, hkv, P, d), v_pools[i].view(e - b, hkv, P, d),
+                               k_scales[i].view(e - b, hkv, P), v_scales[i].view(e - b, hkv, P), table, d_lens,
+                               n_kv_heads=hkv, page_size=P) for i in range(layers)]
+        args.exchange = "nccl"
+    else:
+        plan = f.decode_plan(lens_host, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P)
+        descs = [mfk.paged_kv(k_pools[i].view(e - b, hkv, P, d), v_pools[i].view(e - b, hkv, P, d), table, d_lens,
+                              n_kv_heads=hkv, page_size=P, head_dim=d) for i in range(layers)]
     block = hq * (d + 2)
     mine = torch.zeros(block, dtype=torch.float32, device=dev)
     mine[hq * d:hq * d + hq] = -1e30  # a shard without keys contributes nothing
@@ -515,7 +542,11 @@ def run_long_context(args, w):
             return step_push()
         with torch.cuda.stream(stream):
             for i in range(layers):
-                if n_local:
+                if n_local and kv8:
+                    f.paged_decode_kv8_partial(plan, descs[i], q[i], d_pos, acc, m, l, n_heads=hq, scale=scale,
+                                               k=k[i] if append_here else None, v=v[i] if append_here else None,
+                                               cos=d_cos, sin=d_sin, rope=True, rope_mode=w["rope_mode"], append=append_here)
+                elif n_local:
                     f.paged_decode_partial(plan, descs[i], q[i], acc, m, l, n_heads=hq, rope_positions=d_pos,
                                            scale=scale, k=k[i] if append_here else None,
                                            v=v[i] if append_here else None, cos=d_cos, sin=d_sin, rope=True,
@@ -557,7 +588,7 @@ def run_long_context(args, w):
     f.synchronize()
     clocks = sampler.stop(t0, t1)
     ms_step = ms / args.steps
-    bytes_layer_rank = 2 * hkv * (L // world) * d * 2
+    bytes_layer_rank = 2 * hkv * (L // world) * ((d + 4) if kv8 else d * 2)
     launch_us = ms_step * 1e3 / layers
     achieved = bytes_layer_rank / (launch_us * 1e-6) / 1e9
     peak, peak_kind = measured_peak_gbs()
@@ -570,9 +601,10 @@ def run_long_context(args, w):
     result = {
         "metric": METRIC, "value": 1.0 / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "us_per_step": ms_step * 1e3, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None,
+        "dtype": "e4m3 storage, f32 accumulate" if kv8 else "f16 storage, f32 accumulate", "data": "synthetic",
         "config": {"workload": w["name"], "layers": layers, "kv_len": L, "pages_per_rank": e - b,
-                   "l2": "inputs larger than L2 (KV pools %.1f GB per GPU)" % (2 * layers * pool_elems * 2 / 1e9),
+                   "l2": "inputs larger than L2 (KV pools %.1f GB per GPU)" % (2 * layers * pool_elems * (1 if kv8 else 2) / 1e9),
                    "ctas": plan.ctas, "collective": ("none: decode kernels store %d values per layer into every rank's receive block "
                                   % block
                                   + ("(peer stores of tagged 8-byte words: value + step tag) and merge them themselves as soon as "
@@ -582,7 +614,8 @@ def run_long_context(args, w):
                    if px is not None else "ncclAllGather of %d bytes per rank per layer" % (block * 4)},
         "hbm_tb_s_per_gpu": achieved / 1e3,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": peak_kind, "kernel": "decode_kernel<128,1,3,2> + exchange + merge per layer",
+                     "peak_kind": peak_kind,
+                     "kernel": ("decode_kv8_kernel" if kv8 else "decode_kernel<128,1,3,2>") + " + exchange + merge per layer",
                      "launch_us": launch_us, "algorithmic_bytes_per_launch": bytes_layer_rank, "traffic": None},
         "gpu_launches": launches, "clocks": clocks, "self_check": "ok" if ok else "FAILED",
     }

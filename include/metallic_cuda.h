@@ -714,6 +714,14 @@ typedef struct MfPagedKv8 {
  * (created with an explicit CTA count or under MF_OPTION_DECODE_CLUSTERS = 1). */
 MF_API mf_status mf_paged_decode_kv8(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv8 *cache,
                                      const MfPagedDecodeArgs *args);
+/* mf_paged_decode_partial over the 8-bit cache: this shard attends over its own keys only and emits
+ * unnormalised f32 partials (acc [batch, Hq, D] 16-byte aligned, m and l [batch, Hq]) for mf_merge_partials,
+ * mf_allgather_merge or any other gather; kv_lens in `cache` are the shard-local lengths, RoPE positions come
+ * from rope_positions (device, [batch]; may be null when args->rope and args->append are 0); args->out is not
+ * written.  No counterpart in the reference. */
+MF_API mf_status mf_paged_decode_kv8_partial(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv8 *cache,
+                                             const MfPagedDecodeArgs *args, const uint32_t *rope_positions, float *acc,
+                                             float *m, float *l);
 /* mf_paged_kv_append for the 8-bit cache (same arguments and q_rot layouts): seq == 0xFFFFFFFF
  * appends one token per sequence at kv_lens[b] - 1, otherwise seq_len rows of sequence `seq`
  * at position_offset (a prefill chunk). */

@@ -209,6 +209,7 @@ _SIGNATURES = {
     "mf_decode_plan_tiles": (u64, [vp]),
     "mf_paged_decode": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv), C.POINTER(MfPagedDecodeArgs)]),
     "mf_paged_decode_kv8": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv8), C.POINTER(MfPagedDecodeArgs)]),
+    "mf_paged_decode_kv8_partial": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv8), C.POINTER(MfPagedDecodeArgs), vp, vp, vp, vp]),
     "mf_paged_kv8_append": (C.c_int32, [vp, C.POINTER(MfPagedKv8), vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32]),
     "mf_paged_kv8_gather": (C.c_int32, [vp, C.POINTER(MfPagedKv8), u32, u32, u32, vp]),
     "mf_paged_kv_append": (C.c_int32, [vp, C.POINTER(MfPagedKv), vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32,
@@ -546,6 +547,16 @@ class Foundry:
         a = MfPagedDecodeArgs(_ptr(q), _ptr(k), _ptr(v), _ptr(q_rot), _ptr(out), _ptr(cos), _ptr(sin), n_heads,
                               int(rope), rope_mode, int(append), scale)
         self.check(lib.mf_paged_decode_kv8(self._h, plan._h, C.byref(cache), C.byref(a)))
+
+    def paged_decode_kv8_partial(self, plan: "DecodePlan", cache: "MfPagedKv8", q, rope_positions, acc, m, l, *, n_heads,
+                                 scale=None, k=None, v=None, cos=None, sin=None, rope=False, rope_mode=ROPE_MODE_NEOX,
+                                 append=False, q_rot=None):
+        """mf_paged_decode_kv8_partial: a shard's unnormalised (acc, m, l) over the 8-bit cache."""
+        scale = 1.0 / math.sqrt(cache.head_dim) if scale is None else scale
+        a = MfPagedDecodeArgs(_ptr(q), _ptr(k), _ptr(v), _ptr(q_rot), None, _ptr(cos), _ptr(sin), n_heads,
+                              int(rope), rope_mode, int(append), scale)
+        self.check(lib.mf_paged_decode_kv8_partial(self._h, plan._h, C.byref(cache), C.byref(a), _ptr(rope_positions),
+                                                   _ptr(acc), _ptr(m), _ptr(l)))
 
     def paged_kv8_append(self, cache: "MfPagedKv8", q, k, v, q_rot, cos, sin, *, n_heads, rope_mode=ROPE_MODE_NEOX,
                          apply_rope=True, seq=ALL_SEQUENCES, position_offset=0, seq_len=0):

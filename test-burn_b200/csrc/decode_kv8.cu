@@ -625,11 +625,19 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                         p.part_ml[((size_t)it.slot * kHP + hg) * 2 + 1] = l_all;
                     }
                 } else if (hg < G) {
-                    const bool ok = (fabsf(l_all) <= 3.0e38f) && fabsf(l_all) > 1e-6f;
-                    float r1 = ok ? acc / l_all : acc;
-                    if (!(fabsf(r1) <= 3.0e38f)) r1 = 0.f;
                     const uint32_t h = it.kvh * G + hg;
-                    p.out[(size_t)it.seq * p.out_stride_b + (size_t)h * p.out_stride_h + d] = __float2half_rn(r1);
+                    if (p.out_acc) {  // sequence-sharded: this shard's unnormalised partial
+                        p.out_acc[((size_t)it.seq * p.n_heads + h) * kD + d] = acc;
+                        if (d == 0) {
+                            p.out_m[(size_t)it.seq * p.n_heads + h] = m_all * kLn2;
+                            p.out_l[(size_t)it.seq * p.n_heads + h] = l_all;
+                        }
+                    } else {
+                        const bool ok = (fabsf(l_all) <= 3.0e38f) && fabsf(l_all) > 1e-6f;
+                        float r1 = ok ? acc / l_all : acc;
+                        if (!(fabsf(r1) <= 3.0e38f)) r1 = 0.f;
+                        p.out[(size_t)it.seq * p.out_stride_b + (size_t)h * p.out_stride_h + d] = __float2half_rn(r1);
+                    }
                 }
             }
             if (hp == 0) named_bar_sync(1, kConsumerThreads);
@@ -675,10 +683,18 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                     acc.w += v[j].w * w;
                 }
             }
+            const uint32_t h = it.kvh * G + hg;
+            if (p.out_acc) {
+                *reinterpret_cast<float4 *>(p.out_acc + ((size_t)it.seq * p.n_heads + h) * kD + d0) = acc;
+                if (d0 == 0) {
+                    p.out_m[(size_t)it.seq * p.n_heads + h] = mx;
+                    p.out_l[(size_t)it.seq * p.n_heads + h] = lt;
+                }
+                continue;
+            }
             const bool ok = (fabsf(lt) <= 3.0e38f) && fabsf(lt) > 1e-6f;
             const float inv = ok ? 1.0f / lt : 0.f;  // merge rule: flash_prefill.metal:861
             float r4[4] = {acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv};
-            const uint32_t h = it.kvh * G + hg;
             __half *dst = p.out + (size_t)it.seq * p.out_stride_b + (size_t)h * p.out_stride_h + d0;
 #pragma unroll
             for (uint32_t i = 0; i < 4; ++i) {
@@ -860,20 +876,18 @@ mf_status check_kv8(MfContext *ctx, const MfPagedKv8 *c, const char *what)
     return MF_OK;
 }
 
-}  // namespace
-}  // namespace mf
-
-using namespace mf;
-
-extern "C" {
-
-mf_status mf_paged_decode_kv8(MfContext *ctx, const MfDecodePlan *pl, const MfPagedKv8 *c, const MfPagedDecodeArgs *a)
+// acc / m / l: null for the whole-sequence form (rows go to a->out), else the sequence-sharded form's partials.
+mf_status paged_decode_kv8_common(MfContext *ctx, const MfDecodePlan *pl, const MfPagedKv8 *c, const MfPagedDecodeArgs *a,
+                                  const uint32_t *rope_positions, float *acc, float *m, float *l)
 {
     if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
     if (!pl || !a) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode (8-bit): null argument");
     mf_status st = check_kv8(ctx, c, "paged decode (8-bit)");
     if (st != MF_OK) return st;
-    if (!c->kv_lens || !a->q || !a->out) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode (8-bit): null tensor");
+    if (!c->kv_lens || !a->q || (!a->out && !acc)) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode (8-bit): null tensor");
+    if (acc && (!m || !l || ((a->rope || a->append) && !rope_positions) || (reinterpret_cast<uintptr_t>(acc) & 15u)))
+        return fail(ctx, MF_ERR_INPUT_NOT_FOUND,
+                    "paged decode (8-bit): the partial form needs acc (16-byte aligned), m, l, and rope_positions when it rotates");
     if (a->append && (!a->k || !a->v)) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode (8-bit): k/v of the new token");
     if (a->rope && (!a->cos || !a->sin)) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode (8-bit): cos/sin");
     if (a->rope_mode > 1) return fail(ctx, MF_ERR_INVALID_OPERATION, "paged decode (8-bit): rope_mode %u", a->rope_mode);
@@ -908,6 +922,10 @@ mf_status mf_paged_decode_kv8(MfContext *ctx, const MfDecodePlan *pl, const MfPa
     kp.v_scales = c->v_scales;
     p.page_table = c->page_table;
     p.kv_lens = c->kv_lens;
+    p.rope_positions = rope_positions;
+    p.out_acc = acc;
+    p.out_m = m;
+    p.out_l = l;
     p.items = pl->d_items;
     p.cta_item_begin = pl->d_cta_begin;
     p.part_acc = pl->d_part_acc;
@@ -953,6 +971,25 @@ mf_status mf_paged_decode_kv8(MfContext *ctx, const MfDecodePlan *pl, const MfPa
     ++ctx->launches;
     if (programmatic) ctx->note_programmatic_launch(p.strict_release != 0, a->append ? c->k_pool : nullptr, a->append ? c->v_pool : nullptr);
     return MF_OK;
+}
+
+}  // namespace
+}  // namespace mf
+
+using namespace mf;
+
+extern "C" {
+
+mf_status mf_paged_decode_kv8(MfContext *ctx, const MfDecodePlan *pl, const MfPagedKv8 *c, const MfPagedDecodeArgs *a)
+{
+    return mf::paged_decode_kv8_common(ctx, pl, c, a, nullptr, nullptr, nullptr, nullptr);
+}
+
+mf_status mf_paged_decode_kv8_partial(MfContext *ctx, const MfDecodePlan *pl, const MfPagedKv8 *c, const MfPagedDecodeArgs *a,
+                                      const uint32_t *rope_positions, float *acc, float *m, float *l)
+{
+    if (ctx && (!acc || !m || !l)) return mf::fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode (8-bit), partial: acc / m / l");
+    return mf::paged_decode_kv8_common(ctx, pl, c, a, rope_positions, acc, m, l);
 }
 
 mf_status mf_paged_kv8_append(MfContext *ctx, const MfPagedKv8 *c, const void *q, const void *k, const void *v, void *q_rot,

@@ -107,6 +107,60 @@ def test_fused_append_decode_on_the_8bit_cache(mfk, foundry, cfg, rope_mode, max
     assert max_abs(host(out), gold.ravel()) <= TOL
 
 
+@pytest.mark.parametrize("append_in_shard", [False, True])
+@pytest.mark.parametrize("max_ctas", [296, 5])
+def test_8bit_partials_and_merge_equal_full_decode(mfk, foundry, append_in_shard, max_ctas):
+    """Sequence-sharded decode over the 8-bit cache on one GPU: two shards of one long sequence emit (acc, m, l)
+    with mf_paged_decode_kv8_partial, mf_merge_partials over them equals the oracle's unsharded result.  With
+    append_in_shard the last shard ropes q and k and appends the new row itself (positions from rope_positions);
+    the other shard gets the rotated q, as a rank without the token's keys would."""
+    import torch
+
+    Hq, Hkv, D, P, L = 24, 8, 128, 64, 2048 + 17
+    case = PagedCase(batch=1, n_heads=Hq, n_kv_heads=Hkv, head_dim=D, page_size=P, cached=[L - 1], poison=False, rope_mode=1)
+    k8, v8, ks, vs = quantised_pools(case)
+    q_ref, k8_ref, v8_ref, ks_ref, vs_ref, out_ref, gold = oracle_step(case, k8, v8, ks, vs)
+    start = (k8, v8, ks, vs) if append_in_shard else (k8_ref, v8_ref, ks_ref, vs_ref)
+    d_k8, d_v8, d_ks, d_vs = (torch.from_numpy(np.ascontiguousarray(x)).cuda() for x in start)
+    n_pages = case.page_table.shape[1]
+    cut = n_pages // 2
+    pos = dev_u32(np.array([L - 1], np.uint32))
+    accs, ms, ls = [], [], []
+    keep = []
+    for (p0, p1) in [(0, cut), (cut, n_pages)]:
+        pt = np.ascontiguousarray(case.page_table[:, p0:p1])
+        lens = np.array([min(L, p1 * P) - p0 * P], np.uint32)
+        d_pt, d_len = dev_u32(pt), dev_u32(lens)
+        keep += [d_pt, d_len]
+        desc = mfk.paged_kv8(d_k8, d_v8, d_ks, d_vs, d_pt, d_len, n_kv_heads=Hkv, page_size=P)
+        plan = foundry.decode_plan(lens, n_heads=Hq, n_kv_heads=Hkv, head_dim=D, page_size=P,
+                                   max_ctas=max_ctas)
+        acc = torch.zeros((1, Hq, D), dtype=torch.float32, device="cuda")
+        m = torch.full((1, Hq), -1e30, dtype=torch.float32, device="cuda")
+        l = torch.zeros((1, Hq), dtype=torch.float32, device="cuda")
+        if append_in_shard and p1 == n_pages:
+            foundry.paged_decode_kv8_partial(plan, desc, dev(case.q), pos, acc, m, l, n_heads=Hq, k=dev(case.k), v=dev(case.v),
+                                             cos=dev(case.cos), sin=dev(case.sin), rope=True, rope_mode=1, append=True,
+                                             scale=float(case.scale))
+        else:
+            foundry.paged_decode_kv8_partial(plan, desc, dev(q_ref), pos, acc, m, l, n_heads=Hq, scale=float(case.scale))
+        foundry.synchronize()
+        plan.close()
+        accs.append(acc.view(Hq, D))
+        ms.append(m.view(Hq))
+        ls.append(l.view(Hq))
+    acc, m, l = torch.stack(accs).contiguous(), torch.stack(ms).contiguous(), torch.stack(ls).contiguous()
+    out = torch.empty((Hq, D), dtype=torch.float16, device="cuda")
+    foundry.merge_partials(acc, m, l, out)
+    foundry.synchronize()
+    assert max_abs(host(out), out_ref) <= TOL
+    assert max_abs(host(out), gold.ravel()) <= TOL
+    if append_in_shard:  # the shard that owns the token wrote the same bytes and scales as the oracle's append
+        assert np.array_equal(d_k8.cpu().numpy(), k8_ref) and np.array_equal(d_v8.cpu().numpy(), v8_ref)
+        assert np.array_equal(d_ks.cpu().numpy().view(np.uint32), ks_ref.view(np.uint32))
+        assert np.array_equal(d_vs.cpu().numpy().view(np.uint32), vs_ref.view(np.uint32))
+
+
 def test_8bit_append_kernel_and_gather(mfk, foundry):
     """The standalone quantising append (one token per sequence, and a chunk of rows of one sequence) against
     the oracle's quantiser, bit for bit; the dequantising gather against e4m3 * scale rounded to f16."""
