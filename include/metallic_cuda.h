@@ -714,6 +714,13 @@ typedef struct MfPagedKv8 {
  * (created with an explicit CTA count or under MF_OPTION_DECODE_CLUSTERS = 1). */
 MF_API mf_status mf_paged_decode_kv8(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv8 *cache,
                                      const MfPagedDecodeArgs *args);
+/* Causal chunked prefill over the 8-bit cache (mf_paged_prefill's arguments): the sequence's first kv_len rows are
+ * dequantised (e4m3 * row scale, rounded to f16) into the caller's workspace as K and V [Hkv, kv_len, D], then the
+ * f16 prefill kernels run on them.  workspace: device memory, 256-byte aligned, at least
+ * mf_paged_prefill_kv8_workspace_bytes(cache, kv_len) bytes; the library allocates nothing. */
+MF_API uint64_t mf_paged_prefill_kv8_workspace_bytes(const MfPagedKv8 *cache, uint32_t kv_len);
+MF_API mf_status mf_paged_prefill_kv8(MfContext *ctx, const MfPagedKv8 *cache, const MfPagedPrefillArgs *args,
+                                      void *workspace, uint64_t workspace_bytes);
 /* mf_paged_decode_partial over the 8-bit cache: this shard attends over its own keys only and emits
  * unnormalised f32 partials (acc [batch, Hq, D] 16-byte aligned, m and l [batch, Hq]) for mf_merge_partials,
  * mf_allgather_merge or any other gather; kv_lens in `cache` are the shard-local lengths, RoPE positions come

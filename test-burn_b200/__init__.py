@@ -209,6 +209,8 @@ _SIGNATURES = {
     "mf_decode_plan_tiles": (u64, [vp]),
     "mf_paged_decode": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv), C.POINTER(MfPagedDecodeArgs)]),
     "mf_paged_decode_kv8": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv8), C.POINTER(MfPagedDecodeArgs)]),
+    "mf_paged_prefill_kv8_workspace_bytes": (C.c_uint64, [C.POINTER(MfPagedKv8), C.c_uint32]),
+    "mf_paged_prefill_kv8": (C.c_int32, [vp, C.POINTER(MfPagedKv8), C.POINTER(MfPagedPrefillArgs), vp, C.c_uint64]),
     "mf_paged_decode_kv8_partial": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv8), C.POINTER(MfPagedDecodeArgs), vp, vp, vp, vp]),
     "mf_paged_kv8_append": (C.c_int32, [vp, C.POINTER(MfPagedKv8), vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32]),
     "mf_paged_kv8_gather": (C.c_int32, [vp, C.POINTER(MfPagedKv8), u32, u32, u32, vp]),
@@ -548,6 +550,17 @@ class Foundry:
                               int(rope), rope_mode, int(append), scale)
         self.check(lib.mf_paged_decode_kv8(self._h, plan._h, C.byref(cache), C.byref(a)))
 
+    def paged_prefill_kv8(self, cache: "MfPagedKv8", q, out, workspace, *, seq, q_len, kv_len, query_offset, n_heads,
+                          scale=None):
+        """mf_paged_prefill_kv8: causal prefill over the 8-bit pages of one sequence; q head-major [Hq, M, D], out
+        token-major [M, Hq*D]; `workspace`: a device tensor of at least paged_prefill_kv8_workspace_bytes bytes."""
+        d = cache.head_dim
+        scale = 1.0 / math.sqrt(d) if scale is None else scale
+        a = MfPagedPrefillArgs(_ptr(q), _ptr(out), seq, q_len, kv_len, query_offset, n_heads, q_len * d, d, d, n_heads * d,
+                               scale)
+        self.check(lib.mf_paged_prefill_kv8(self._h, C.byref(cache), C.byref(a), _ptr(workspace),
+                                            workspace.numel() * workspace.element_size()))
+
     def paged_decode_kv8_partial(self, plan: "DecodePlan", cache: "MfPagedKv8", q, rope_positions, acc, m, l, *, n_heads,
                                  scale=None, k=None, v=None, cos=None, sin=None, rope=False, rope_mode=ROPE_MODE_NEOX,
                                  append=False, q_rot=None):
@@ -565,6 +578,10 @@ class Foundry:
 
     def paged_kv8_gather(self, cache: "MfPagedKv8", use_v: bool, seq: int, length: int, out):
         self.check(lib.mf_paged_kv8_gather(self._h, C.byref(cache), int(use_v), seq, length, _ptr(out)))
+
+
+def paged_prefill_kv8_workspace_bytes(cache: "MfPagedKv8", kv_len: int) -> int:
+    return int(lib.mf_paged_prefill_kv8_workspace_bytes(C.byref(cache), kv_len))
 
 
 def flash_decode_static_scratch(stream, q, k, v, output, strides: MfFlashDecodeStrides, params: SdpaParams, n_heads,

@@ -797,6 +797,54 @@ mf_status mf_paged_prefill(MfContext *ctx, const MfPagedKv *cache, const MfPaged
     return launch_prefill(ctx, a->q, nullptr, nullptr, a->out, pp, cache, a->seq);
 }
 
+uint64_t mf_paged_prefill_kv8_workspace_bytes(const MfPagedKv8 *cache, uint32_t kv_len)
+{
+    if (!cache) return 0;
+    // K and V of one sequence as f16 [Hkv, kv_len, D], each rounded up to 256 bytes
+    const uint64_t one = ((uint64_t)cache->n_kv_heads * kv_len * cache->head_dim * 2 + 255) & ~(uint64_t)255;
+    return 2 * one;
+}
+
+mf_status mf_paged_prefill_kv8(MfContext *ctx, const MfPagedKv8 *cache, const MfPagedPrefillArgs *a, void *workspace,
+                               uint64_t workspace_bytes)
+{
+    if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
+    if (!cache || !a || !a->q || !a->out) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged prefill (8-bit): null input");
+    if (a->q_len == 0 || a->kv_len == 0) return MF_OK;
+    if (a->n_heads == 0 || cache->n_kv_heads == 0 || a->n_heads % cache->n_kv_heads != 0)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "paged prefill (8-bit): n_heads %u, n_kv_heads %u", a->n_heads, cache->n_kv_heads);
+    const uint64_t need = mf_paged_prefill_kv8_workspace_bytes(cache, a->kv_len);
+    if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return fail(ctx, MF_ERR_INVALID_OPERATION, "paged prefill (8-bit): workspace of %llu bytes, 256-byte aligned, needed",
+                    (unsigned long long)need);
+    // The sequence's rows, dequantised (e4m3 * row scale, rounded to f16), as a contiguous cache; then the f16 kernels.
+    __half *kf = static_cast<__half *>(workspace);
+    __half *vf = reinterpret_cast<__half *>(static_cast<char *>(workspace) + need / 2);
+    mf_status st = mf_paged_kv8_gather(ctx, cache, 0, a->seq, a->kv_len, kf);
+    if (st != MF_OK) return st;
+    if ((st = mf_paged_kv8_gather(ctx, cache, 1, a->seq, a->kv_len, vf)) != MF_OK) return st;
+    SdpaPrefillSplitKParams pp{};
+    SdpaPrefillParams &b = pp.base;
+    const uint32_t D = cache->head_dim;
+    b.kv_len = a->kv_len;
+    b.head_dim = D;
+    b.scale = a->scale;
+    b.stride_k_s = D;
+    b.stride_v_s = D;
+    b.k_stride_h = a->kv_len * D;
+    b.v_stride_h = a->kv_len * D;
+    b.query_offset = a->query_offset;
+    b.q_stride_h = a->q_stride_h;
+    b.q_stride_m = a->q_stride_m;
+    b.out_stride_h = a->out_stride_h;
+    b.out_stride_m = a->out_stride_m;
+    b.group_size = a->n_heads / cache->n_kv_heads;
+    b.q_len = a->q_len;
+    pp.n_heads = a->n_heads;
+    pp.split_k = effective_prefill_split_k(ctx, a->kv_len, a->q_len, a->n_heads);
+    return launch_prefill(ctx, a->q, kf, vf, a->out, pp);
+}
+
 mf_status mf_paged_decode_partial_push(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv *cache,
                                        const MfPagedDecodeArgs *args, const uint32_t *rope_positions,
                                        const MfPeerExchange *px, uint32_t step)

@@ -233,6 +233,62 @@ def test_8bit_append_kernel_and_gather(mfk, foundry):
         assert np.array_equal(host(q_rot2), q_rows.reshape(m, 8, 128).transpose(1, 0, 2))
 
 
+@pytest.mark.parametrize("shape", [(8, 2, 16, 100, 40), (24, 8, 64, 512, 256), (16, 2, 32, 0, 130)])
+def test_chunked_prefill_over_the_8bit_cache(mfk, foundry, shape):
+    """A prefill chunk on the 8-bit cache: mf_paged_kv8_append of the chunk's rows, then mf_paged_prefill_kv8 =
+    causal attention of the chunk's queries over the dequantised rows.  Checked against the oracle's f32 causal
+    prefill and fp64 gold over the SAME dequantised cache (e4m3 * scale rounded to f16, the oracle's table)."""
+    import torch
+
+    from kvcases import normal
+
+    hq, hkv, P, cached, m = shape
+    d, L = 128, cached + m
+    n_seq_pages = (L + P - 1) // P
+    n_pages = n_seq_pages + 3
+    rng = np.random.default_rng(cached * 7 + m)
+    pages = rng.permutation(n_pages)[:n_seq_pages].astype(np.uint32)
+    table = np.full((2, n_seq_pages), 0x7FFFFFF0, np.uint32)
+    table[1] = pages
+    lens = np.array([1, L], np.uint32)
+    d_table, d_lens = dev_u32(table), dev_u32(lens)
+    pools = [torch.zeros((n_pages, hkv, P, d), dtype=torch.uint8, device="cuda"), torch.zeros((n_pages, hkv, P, d), dtype=torch.uint8, device="cuda"),
+             torch.full((n_pages, hkv, P), float("nan"), dtype=torch.float32, device="cuda"),
+             torch.full((n_pages, hkv, P), float("nan"), dtype=torch.float32, device="cuda")]
+    desc = mfk.paged_kv8(*pools, d_table, d_lens, n_kv_heads=hkv, page_size=P)
+    cos, sin = oracle.rope_tables(1e6, d, L)
+    # the cached rows arrive the way a model would have written them: earlier chunks through the same append
+    q_rot = None
+    for (off, rows, seed) in ([(0, cached, 50)] if cached else []) + [(cached, m, 60)]:
+        qc, kc, vc = (normal(seed + i, rows * h * d).reshape(rows, h * d) for i, h in enumerate((hq, hkv, hkv)))
+        q_rot = torch.full((hq, rows, d), float("nan"), dtype=torch.float16, device="cuda")
+        foundry.paged_kv8_append(desc, dev(qc), dev(kc), dev(vc), q_rot, dev(cos), dev(sin), n_heads=hq, rope_mode=0, seq=1,
+                                 position_offset=off, seq_len=rows)
+    ws = torch.empty(mfk.paged_prefill_kv8_workspace_bytes(desc, L), dtype=torch.uint8, device="cuda")
+    out = torch.full((m, hq * d), float("nan"), dtype=torch.float16, device="cuda")
+    scale = np.float32(1.0) / np.sqrt(np.float32(d))
+    foundry.paged_prefill_kv8(desc, q_rot, out, ws, seq=1, q_len=m, kv_len=L, query_offset=cached, n_heads=hq, scale=float(scale))
+    foundry.synchronize()
+    # the dequantised cache, restated on the host from the pool bytes and scales the append left
+    lut = np.array([oracle.lib().mfo_e4m3_to_f32(b) for b in range(256)], np.float32)
+    k8, ks, vs = pools[0].cpu().numpy(), pools[2].cpu().numpy(), pools[3].cpu().numpy()
+    v_rows = mfk.kv8_v_rows_from_pool(pools[1].cpu().numpy())
+    kc_f, vc_f = np.zeros((hkv, L, d), np.float16), np.zeros((hkv, L, d), np.float16)
+    for t in range(L):
+        pg, r = pages[t // P], t % P
+        kc_f[:, t] = (lut[k8[pg, :, r]] * ks[pg, :, r, None]).astype(np.float16)
+        vc_f[:, t] = (lut[v_rows[pg, :, r]] * vs[pg, :, r, None]).astype(np.float16)
+    args = dict(n_heads=hq, cache_heads=hkv, head_dim=d, capacity=L, q_len=m, kv_len=L, query_offset=cached, scale=scale)
+    q_host = host(q_rot).ravel()
+    want = oracle.prefill_causal(q_host, kc_f.view(np.uint16).ravel(), vc_f.view(np.uint16).ravel(), **args)
+    gold = oracle.prefill_gold(q_host, kc_f.view(np.uint16).ravel(), vc_f.view(np.uint16).ravel(), **args)
+    assert max_abs(host(out), want) <= TOL
+    assert max_abs(host(out), gold) <= TOL
+    with pytest.raises(mfk.MetalError) as e:  # a workspace that is too small is refused, nothing is allocated behind the caller
+        foundry.paged_prefill_kv8(desc, q_rot, out, ws[:256], seq=1, q_len=m, kv_len=L, query_offset=cached, n_heads=hq)
+    assert e.value.kind == "InvalidOperation"
+
+
 def test_cost_of_the_8bit_format(mfk, foundry):
     """The same step on the f16 cache and on its 8-bit quantisation: the difference is the format's cost."""
     import torch
