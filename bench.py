@@ -82,7 +82,7 @@ SEED = 0x5EED
 METRIC = "kv_append_decode_attn_tokens_per_s"
 # DRAM bytes moved by the decode kernel per algorithmic byte: dram__bytes_read.sum + dram__bytes_write.sum of
 # one ncu capture of a 4-layer C3 step over the algorithmic bytes of the same launch.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0072
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0099
 
 
 def measured_peak_gbs():
