@@ -34,6 +34,8 @@
 //    units of sigma, switched inside the online-softmax rescale.
 #include <cuda_fp8.h>
 
+#include <type_traits>
+
 #include "internal.hpp"
 #include "ptx.cuh"
 
@@ -656,33 +658,68 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         named_bar_sync(2, kConsumerThreads);
         if (!flags[1]) continue;
         __threadfence();
+        // Merge (flash_prefill.metal:843-888), arranged so that the loads of one round trip are all in flight
+        // together: this runs at the end of a CTA's work, where latency is not hidden.  Pass 1: the parts' (m, l)
+        // over all threads (a head per eight threads), maxima cached in shared memory.
+        constexpr uint32_t kMergeCap = 64;                    // parts whose m is cached in shared memory
+        constexpr uint32_t kPerHead = kConsumerThreads / kHP; // threads per head in pass 1
+        constexpr uint32_t kFlight = 20, kFlightFew = 8;      // partials in flight together in pass 2
+        static_assert((kMergeCap * kHP + kConsumerThreads * 2) * 4 <= kConsumerWarps * kHP * kCombStride * 4, "merge scratch");
+        float *msv = comb;                                    // [kMergeCap][kHP]
+        float *red = comb + kMergeCap * kHP;                  // [threads][2]
+        {
+            const uint32_t g1 = tid % kHP;
+            float m_loc = kNegSentinel, l_loc = 0.f;
+            for (uint32_t sp = tid / kHP; sp < it.n_parts; sp += kPerHead) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2 *>(p.part_ml) + (size_t)(it.first_slot + sp) * kHP + g1);
+                if (sp < kMergeCap) msv[sp * kHP + g1] = ml.x;
+                const float mn = fmaxf(m_loc, ml.x);
+                l_loc = l_loc * __expf(m_loc - mn) + (ml.y > 0.f ? ml.y * __expf(ml.x - mn) : 0.f);
+                m_loc = mn;
+            }
+            red[tid * 2] = m_loc;
+            red[tid * 2 + 1] = l_loc;
+        }
+        named_bar_sync(1, kConsumerThreads);
+        // Pass 2: one float4 column of one real head per thread and round.
         for (uint32_t c4 = tid; c4 < G * (kD / 4); c4 += kConsumerThreads) {
             const uint32_t hg = c4 / (kD / 4), d0 = (c4 % (kD / 4)) * 4;
-            float mx = kNegSentinel;
-            for (uint32_t sp = 0; sp < it.n_parts; ++sp)
-                mx = fmaxf(mx, __ldcg(p.part_ml + ((size_t)(it.first_slot + sp) * kHP + hg) * 2));
-            float lt = 0.f;
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (uint32_t s0 = 0; s0 < it.n_parts; s0 += 8) {
-                float4 v[8];
-                float2 ml[8];
+            float mx = kNegSentinel, lt = 0.f;
 #pragma unroll
-                for (uint32_t j = 0; j < 8; ++j) {
-                    const size_t sl = it.first_slot + min(s0 + j, it.n_parts - 1);
-                    v[j] = __ldcg(reinterpret_cast<const float4 *>(p.part_acc + (sl * kHP + hg) * kD + d0));
-                    ml[j] = __ldcg(reinterpret_cast<const float2 *>(p.part_ml + (sl * kHP + hg) * 2));
-                }
+            for (uint32_t j = 0; j < kPerHead; ++j) mx = fmaxf(mx, red[(j * kHP + hg) * 2]);
 #pragma unroll
-                for (uint32_t j = 0; j < 8; ++j) {
-                    if (s0 + j >= it.n_parts) continue;
-                    const float w = __expf(ml[j].x - mx);
-                    if (ml[j].y > 0.f) lt += ml[j].y * w;
-                    acc.x += v[j].x * w;
-                    acc.y += v[j].y * w;
-                    acc.z += v[j].z * w;
-                    acc.w += v[j].w * w;
+            for (uint32_t j = 0; j < kPerHead; ++j) lt += red[(j * kHP + hg) * 2 + 1] * __expf(red[(j * kHP + hg) * 2] - mx);
+            auto accumulate = [&](auto flight) {
+                constexpr uint32_t F = decltype(flight)::value;
+                float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (uint32_t s0 = 0; s0 < it.n_parts; s0 += F) {
+                    float4 v[F];
+                    float w[F];
+#pragma unroll
+                    for (uint32_t j = 0; j < F; ++j) {
+                        const uint32_t sp = s0 + j;
+                        if (sp < it.n_parts) {
+                            const size_t sl = it.first_slot + sp;
+                            v[j] = __ldcg(reinterpret_cast<const float4 *>(p.part_acc + (sl * kHP + hg) * kD + d0));
+                            const float ms = sp < kMergeCap ? msv[sp * kHP + hg] : __ldcg(p.part_ml + (sl * kHP + hg) * 2);
+                            w[j] = __expf(ms - mx);
+                        } else {
+                            v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            w[j] = 0.f;
+                        }
+                    }
+#pragma unroll
+                    for (uint32_t j = 0; j < F; ++j) {
+                        a4.x += v[j].x * w[j];
+                        a4.y += v[j].y * w[j];
+                        a4.z += v[j].z * w[j];
+                        a4.w += v[j].w * w[j];
+                    }
                 }
-            }
+                return a4;
+            };
+            const float4 acc = it.n_parts <= kFlightFew ? accumulate(std::integral_constant<uint32_t, kFlightFew>{})
+                                                        : accumulate(std::integral_constant<uint32_t, kFlight>{});
             const uint32_t h = it.kvh * G + hg;
             if (p.out_acc) {
                 *reinterpret_cast<float4 *>(p.out_acc + ((size_t)it.seq * p.n_heads + h) * kD + d0) = acc;
