@@ -797,6 +797,17 @@ MF_API mf_status mf_paged_decode_partial_push(MfContext *ctx, const MfDecodePlan
 MF_API mf_status mf_paged_decode_push_merge(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv *cache,
                                             const MfPagedDecodeArgs *args, const uint32_t *rope_positions,
                                             const MfPeerExchange *px, uint32_t step, uint32_t pusher_mask);
+/* mf_paged_decode_partial_push over the 8-bit cache: the two-launch form (mf_merge_pushed merges, as for the f16
+ * cache; the exchange object does not know which cache the partials came from). */
+MF_API mf_status mf_paged_decode_kv8_partial_push(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv8 *cache,
+                                                  const MfPagedDecodeArgs *args, const uint32_t *rope_positions,
+                                                  const MfPeerExchange *px, uint32_t step);
+/* mf_paged_decode_push_merge over the 8-bit cache (same exchange object, step numbering, pusher mask and wire
+ * forms): one launch appends (quantising), attends over this shard's 8-bit pages, stores the unit's partial into
+ * every rank's receive block and merges all ranks' partials into args->out.  No counterpart in the reference. */
+MF_API mf_status mf_paged_decode_kv8_push_merge(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv8 *cache,
+                                                const MfPagedDecodeArgs *args, const uint32_t *rope_positions,
+                                                const MfPeerExchange *px, uint32_t step, uint32_t pusher_mask);
 /* The same exchange through a library collective (the baseline the fused route is measured against,
  * and the route for hosts that already run NCCL): every rank passes its own block `mine` =
  * [acc rows*head_dim | m rows | l rows] f32 (what mf_paged_decode_partial wrote, laid out in one

@@ -211,6 +211,10 @@ _SIGNATURES = {
     "mf_paged_decode_kv8": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv8), C.POINTER(MfPagedDecodeArgs)]),
     "mf_paged_prefill_kv8_workspace_bytes": (C.c_uint64, [C.POINTER(MfPagedKv8), C.c_uint32]),
     "mf_paged_prefill_kv8": (C.c_int32, [vp, C.POINTER(MfPagedKv8), C.POINTER(MfPagedPrefillArgs), vp, C.c_uint64]),
+    "mf_paged_decode_kv8_partial_push": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv8), C.POINTER(MfPagedDecodeArgs), vp,
+                                                     C.POINTER(MfPeerExchange), C.c_uint32]),
+    "mf_paged_decode_kv8_push_merge": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv8), C.POINTER(MfPagedDecodeArgs), vp,
+                                                   C.POINTER(MfPeerExchange), C.c_uint32, C.c_uint32]),
     "mf_paged_decode_kv8_partial": (C.c_int32, [vp, vp, C.POINTER(MfPagedKv8), C.POINTER(MfPagedDecodeArgs), vp, vp, vp, vp]),
     "mf_paged_kv8_append": (C.c_int32, [vp, C.POINTER(MfPagedKv8), vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32]),
     "mf_paged_kv8_gather": (C.c_int32, [vp, C.POINTER(MfPagedKv8), u32, u32, u32, vp]),
@@ -560,6 +564,25 @@ class Foundry:
                                scale)
         self.check(lib.mf_paged_prefill_kv8(self._h, C.byref(cache), C.byref(a), _ptr(workspace),
                                             workspace.numel() * workspace.element_size()))
+
+    def paged_decode_kv8_partial_push(self, plan: "DecodePlan", cache: "MfPagedKv8", q, px: MfPeerExchange, step: int, *,
+                                      n_heads, rope_positions=None, scale=None, k=None, v=None, cos=None, sin=None,
+                                      rope=False, rope_mode=ROPE_MODE_NEOX, append=False):
+        scale = 1.0 / math.sqrt(cache.head_dim) if scale is None else scale
+        a = MfPagedDecodeArgs(_ptr(q), _ptr(k), _ptr(v), None, None, _ptr(cos), _ptr(sin), n_heads, int(rope), rope_mode,
+                              int(append), scale)
+        self.check(lib.mf_paged_decode_kv8_partial_push(self._h, plan._h, C.byref(cache), C.byref(a), _ptr(rope_positions),
+                                                        C.byref(px), step))
+
+    def paged_decode_kv8_push_merge(self, plan: "DecodePlan", cache: "MfPagedKv8", q, out, px: MfPeerExchange, step: int,
+                                    pusher_mask: int, *, n_heads, rope_positions=None, scale=None, k=None, v=None, cos=None,
+                                    sin=None, rope=False, rope_mode=ROPE_MODE_NEOX, append=False):
+        """mf_paged_decode_kv8_push_merge: the fused sequence-sharded step over the 8-bit cache."""
+        scale = 1.0 / math.sqrt(cache.head_dim) if scale is None else scale
+        a = MfPagedDecodeArgs(_ptr(q), _ptr(k), _ptr(v), None, _ptr(out), _ptr(cos), _ptr(sin), n_heads, int(rope),
+                              rope_mode, int(append), scale)
+        self.check(lib.mf_paged_decode_kv8_push_merge(self._h, plan._h, C.byref(cache), C.byref(a), _ptr(rope_positions),
+                                                      C.byref(px), step, pusher_mask))
 
     def paged_decode_kv8_partial(self, plan: "DecodePlan", cache: "MfPagedKv8", q, rope_positions, acc, m, l, *, n_heads,
                                  scale=None, k=None, v=None, cos=None, sin=None, rope=False, rope_mode=ROPE_MODE_NEOX,

@@ -30,7 +30,7 @@ SOURCES = [
     HERE / "host" / "host_logic.cpp",
     HERE / "host" / "prefix_cache.cpp",
 ]
-HEADERS = [HERE / "csrc" / "internal.hpp", HERE / "csrc" / "ptx.cuh", HERE / "csrc" / "tcgen05.cuh", HERE / "csrc" / "append.cuh", ROOT / "include" / "metallic_cuda.h"]
+HEADERS = [HERE / "csrc" / "internal.hpp", HERE / "csrc" / "ptx.cuh", HERE / "csrc" / "tcgen05.cuh", HERE / "csrc" / "append.cuh", HERE / "csrc" / "push.cuh", ROOT / "include" / "metallic_cuda.h"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 EXTRA = os.environ.get("MF_EXTRA_NVCC_FLAGS", "").split()
 FLAGS = EXTRA + ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -638,6 +638,63 @@ uint32_t mf_decode_plan_cluster(const MfDecodePlan *pl) { return pl ? pl->cluste
 uint32_t mf_decode_plan_items(const MfDecodePlan *pl) { return pl ? pl->n_items : 0; }
 uint64_t mf_decode_plan_tiles(const MfDecodePlan *pl) { return pl ? pl->total_tiles : 0; }
 
+}  // extern "C"
+
+namespace mf {
+
+// Sequence-sharded decode: where this call's partials go in every rank's receive block, what it counts, waits for
+// and merges (step parity, counted or tagged form).  Shared by the f16 and the 8-bit launchers.
+mf_status setup_push(MfContext *ctx, const MfPeerExchange *px, uint32_t step, uint32_t merge_mask, uint64_t rows_in_call,
+                     uint32_t D, DecodeParams &p)
+{
+    if (px->world == 0 || px->world > 8 || px->rank >= px->world)
+        return fail(ctx, MF_ERR_INVALID_OPERATION, "peer exchange: rank %u of %u", px->rank, px->world);
+    const uint64_t block = rows_in_call * (D + 2);
+    p.push_world = px->world;
+    for (uint32_t r = 0; r < px->world; ++r) {
+        if (!px->recv[r] || !px->counters[r]) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "peer exchange: rank %u buffers", r);
+        p.push_dst[r] = px->recv[r] + ((uint64_t)(step & 1) * px->world + px->rank) * block;
+        p.push_cnt[r] = px->counters[r] + px->rank;
+        p.push_unit_cnt[r] = px->counters[r] + kPeerUnitCounters;
+    }
+    // ranks that only merge: their merge of step - 2 read the parity block this step overwrites
+    if (px->merge_only_mask >> px->rank & 1u)
+        return fail(ctx, MF_ERR_INVALID_OPERATION, "peer exchange: rank %u is in merge_only_mask and cannot push", px->rank);
+    if (px->merge_only_mask && step >= 2) {
+        p.push_wait_mask = px->merge_only_mask & ((1u << px->world) - 1u);
+        p.push_wait_expected = px->rows * (step - 1);
+        p.push_merged_local = px->counters[px->rank] + kPeerMergedBy;
+    }
+    if (rows_in_call != px->rows || D != px->head_dim)
+        return fail(ctx, MF_ERR_INVALID_SHAPE, "peer exchange was created for %u rows x %u, this call has %llu x %u",
+                    px->rows, px->head_dim, (unsigned long long)rows_in_call, D);
+    if (merge_mask) {
+        if (!(merge_mask >> px->rank & 1u) || (merge_mask >> px->world))
+            return fail(ctx, MF_ERR_INVALID_OPERATION, "pusher mask 0x%x does not fit rank %u of %u", merge_mask, px->rank,
+                        px->world);
+        p.push_merge = 1;
+        p.push_mask = merge_mask;
+        p.push_expected = (uint32_t)__builtin_popcount(merge_mask) * (step + 1);
+        p.push_local = px->recv[px->rank] + (uint64_t)(step & 1) * px->world * block;
+        p.push_local_cnt = px->counters[px->rank] + kPeerUnitCounters;
+        if (ctx->push_tagged && px->merge_only_mask == 0) {
+            // tagged words: the same blocks, eight bytes per value, in a region of their own behind the plain
+            // floats (a float left by a step in the counted form can then never be read as a tag)
+            p.push_tagged = 1;
+            p.push_tag = step + 1;
+            const uint64_t tagged_base = (uint64_t)2 * px->world * block;
+            for (uint32_t r = 0; r < px->world; ++r)
+                p.push_dst[r] = px->recv[r] + tagged_base + 2 * (((uint64_t)(step & 1) * px->world + px->rank) * block);
+            p.push_local = px->recv[px->rank] + tagged_base + 2 * ((uint64_t)(step & 1) * px->world * block);
+        }
+    }
+    return MF_OK;
+}
+
+}  // namespace mf
+
+extern "C" {
+
 static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, const MfPagedKv *c,
                                      const MfPagedDecodeArgs *a, const uint32_t *rope_positions, float *acc, float *m,
                                      float *l, const MfPeerExchange *px = nullptr, uint32_t step = 0,
@@ -707,47 +764,8 @@ static mf_status paged_decode_common(MfContext *ctx, const MfDecodePlan *pl, con
     p.early_stream = (((ctx->overlap_launches && a->append) || ctx->overlap_launches == 2) &&
                       ctx->may_stream_early(c->k_pool, c->v_pool)) ? 1u : 0u;
     if (px) {
-        if (px->world == 0 || px->world > 8 || px->rank >= px->world)
-            return fail(ctx, MF_ERR_INVALID_OPERATION, "peer exchange: rank %u of %u", px->rank, px->world);
-        const uint64_t block = (uint64_t)c->batch * a->n_heads * (D + 2);
-        p.push_world = px->world;
-        for (uint32_t r = 0; r < px->world; ++r) {
-            if (!px->recv[r] || !px->counters[r]) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "peer exchange: rank %u buffers", r);
-            p.push_dst[r] = px->recv[r] + ((uint64_t)(step & 1) * px->world + px->rank) * block;
-            p.push_cnt[r] = px->counters[r] + px->rank;
-            p.push_unit_cnt[r] = px->counters[r] + kPeerUnitCounters;
-        }
-        // ranks that only merge: their merge of step - 2 read the parity block this step overwrites
-        if (px->merge_only_mask >> px->rank & 1u)
-            return fail(ctx, MF_ERR_INVALID_OPERATION, "peer exchange: rank %u is in merge_only_mask and cannot push", px->rank);
-        if (px->merge_only_mask && step >= 2) {
-            p.push_wait_mask = px->merge_only_mask & ((1u << px->world) - 1u);
-            p.push_wait_expected = px->rows * (step - 1);
-            p.push_merged_local = px->counters[px->rank] + kPeerMergedBy;
-        }
-        if ((uint64_t)c->batch * a->n_heads != px->rows || D != px->head_dim)
-            return fail(ctx, MF_ERR_INVALID_SHAPE, "peer exchange was created for %u rows x %u, this call has %llu x %u",
-                        px->rows, px->head_dim, (unsigned long long)c->batch * a->n_heads, D);
-        if (merge_mask) {
-            if (!(merge_mask >> px->rank & 1u) || (merge_mask >> px->world))
-                return fail(ctx, MF_ERR_INVALID_OPERATION, "pusher mask 0x%x does not fit rank %u of %u", merge_mask, px->rank,
-                            px->world);
-            p.push_merge = 1;
-            p.push_mask = merge_mask;
-            p.push_expected = (uint32_t)__builtin_popcount(merge_mask) * (step + 1);
-            p.push_local = px->recv[px->rank] + (uint64_t)(step & 1) * px->world * block;
-            p.push_local_cnt = px->counters[px->rank] + kPeerUnitCounters;
-            if (ctx->push_tagged && px->merge_only_mask == 0) {
-                // tagged words: the same blocks, eight bytes per value, in a region of their own behind the plain
-                // floats (a float left by a step in the counted form can then never be read as a tag)
-                p.push_tagged = 1;
-                p.push_tag = step + 1;
-                const uint64_t tagged_base = (uint64_t)2 * px->world * block;
-                for (uint32_t r = 0; r < px->world; ++r)
-                    p.push_dst[r] = px->recv[r] + tagged_base + 2 * (((uint64_t)(step & 1) * px->world + px->rank) * block);
-                p.push_local = px->recv[px->rank] + tagged_base + 2 * ((uint64_t)(step & 1) * px->world * block);
-            }
-        }
+        const mf_status pst = setup_push(ctx, px, step, merge_mask, (uint64_t)c->batch * a->n_heads, D, p);
+        if (pst != MF_OK) return pst;
     }
     CUtensorMap tm_k, tm_v;
     const uint64_t rows = (uint64_t)c->n_pages * c->n_kv_heads * P;

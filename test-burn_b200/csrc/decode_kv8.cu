@@ -38,6 +38,7 @@
 
 #include "internal.hpp"
 #include "ptx.cuh"
+#include "push.cuh"
 
 namespace mf {
 namespace {
@@ -238,6 +239,7 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     // ---------------------------------------------------------------- consumers ---
     grid_dependency_wait();
     if (p.strict_release) grid_launch_dependents();
+    if (p.push_wait_mask) push::push_wait_for_mergers(p, tid);
     float *comb = reinterpret_cast<float *>(smem + kOffComb);
     __half *q_s = reinterpret_cast<__half *>(smem + kOffQ);  // [head][kQStride] f16
     float *ml_s = reinterpret_cast<float *>(smem + kOffMl);
@@ -628,7 +630,16 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                     }
                 } else if (hg < G) {
                     const uint32_t h = it.kvh * G + hg;
-                    if (p.out_acc) {  // sequence-sharded: this shard's unnormalised partial
+                    if (p.push_world) {  // sequence-sharded, fused exchange: the partial goes to every rank
+                        const size_t rows = (size_t)p.batch * p.n_heads, rowi = (size_t)it.seq * p.n_heads + h;
+                        for (uint32_t r = 0; r < p.push_world; ++r) {
+                            push::push_store(p, r, rowi * kD + d, acc);
+                            if (d == 0) {
+                                push::push_store(p, r, rows * kD + rowi, m_all * kLn2);
+                                push::push_store(p, r, rows * kD + rows + rowi, l_all);
+                            }
+                        }
+                    } else if (p.out_acc) {  // sequence-sharded: this shard's unnormalised partial
                         p.out_acc[((size_t)it.seq * p.n_heads + h) * kD + d] = acc;
                         if (d == 0) {
                             p.out_m[(size_t)it.seq * p.n_heads + h] = m_all * kLn2;
@@ -644,7 +655,10 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
             }
             if (hp == 0) named_bar_sync(1, kConsumerThreads);
         }
-        if (direct) continue;
+        if (direct) {
+            if (p.push_world) push::push_signal_and_merge<(int)kD>(p, it, tid, flags);
+            continue;
+        }
 
         // ---- ticket: the CTA that completes the unit merges its partials (flash_prefill.metal:843-888) -------
         __threadfence();
@@ -721,6 +735,24 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
             const float4 acc = it.n_parts <= kFlightFew ? accumulate(std::integral_constant<uint32_t, kFlightFew>{})
                                                         : accumulate(std::integral_constant<uint32_t, kFlight>{});
             const uint32_t h = it.kvh * G + hg;
+            if (p.push_world) {
+                const size_t rows = (size_t)p.batch * p.n_heads, rowi = (size_t)it.seq * p.n_heads + h;
+                for (uint32_t r = 0; r < p.push_world; ++r) {
+                    if (p.push_tagged) {
+                        push::push_store(p, r, rowi * kD + d0, acc.x);
+                        push::push_store(p, r, rowi * kD + d0 + 1, acc.y);
+                        push::push_store(p, r, rowi * kD + d0 + 2, acc.z);
+                        push::push_store(p, r, rowi * kD + d0 + 3, acc.w);
+                    } else {
+                        *reinterpret_cast<float4 *>(p.push_dst[r] + rowi * kD + d0) = acc;
+                    }
+                    if (d0 == 0) {
+                        push::push_store(p, r, rows * kD + rowi, mx);
+                        push::push_store(p, r, rows * kD + rows + rowi, lt);
+                    }
+                }
+                continue;
+            }
             if (p.out_acc) {
                 *reinterpret_cast<float4 *>(p.out_acc + ((size_t)it.seq * p.n_heads + h) * kD + d0) = acc;
                 if (d0 == 0) {
@@ -739,6 +771,7 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                 dst[i] = __float2half_rn(r4[i]);
             }
         }
+        if (p.push_world) push::push_signal_and_merge<(int)kD>(p, it, tid, flags);
     }
 }
 
@@ -915,13 +948,17 @@ mf_status check_kv8(MfContext *ctx, const MfPagedKv8 *c, const char *what)
 
 // acc / m / l: null for the whole-sequence form (rows go to a->out), else the sequence-sharded form's partials.
 mf_status paged_decode_kv8_common(MfContext *ctx, const MfDecodePlan *pl, const MfPagedKv8 *c, const MfPagedDecodeArgs *a,
-                                  const uint32_t *rope_positions, float *acc, float *m, float *l)
+                                  const uint32_t *rope_positions, float *acc, float *m, float *l,
+                                  const MfPeerExchange *px = nullptr, uint32_t step = 0, uint32_t merge_mask = 0)
 {
     if (!ctx) return MF_ERR_INPUT_NOT_FOUND;
     if (!pl || !a) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode (8-bit): null argument");
     mf_status st = check_kv8(ctx, c, "paged decode (8-bit)");
     if (st != MF_OK) return st;
-    if (!c->kv_lens || !a->q || (!a->out && !acc)) return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode (8-bit): null tensor");
+    if (!c->kv_lens || !a->q || (!a->out && !acc && !(px && !merge_mask)))
+        return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode (8-bit): null tensor");
+    if (px && (a->rope || a->append) && !rope_positions)
+        return fail(ctx, MF_ERR_INPUT_NOT_FOUND, "paged decode (8-bit): the sharded forms need rope_positions when they rotate");
     if (acc && (!m || !l || ((a->rope || a->append) && !rope_positions) || (reinterpret_cast<uintptr_t>(acc) & 15u)))
         return fail(ctx, MF_ERR_INPUT_NOT_FOUND,
                     "paged decode (8-bit): the partial form needs acc (16-byte aligned), m, l, and rope_positions when it rotates");
@@ -987,6 +1024,7 @@ mf_status paged_decode_kv8_common(MfContext *ctx, const MfDecodePlan *pl, const 
     p.scale_log2 = a->scale * 1.4426950408889634f;
     p.early_stream = (((ctx->overlap_launches && a->append) || ctx->overlap_launches == 2) &&
                       ctx->may_stream_early(c->k_pool, c->v_pool)) ? 1u : 0u;
+    if (px && (st = setup_push(ctx, px, step, merge_mask, (uint64_t)c->batch * a->n_heads, kD, p)) != MF_OK) return st;
     CUtensorMap tm_k, tm_v;
     const uint64_t rows = (uint64_t)c->n_pages * c->n_kv_heads * c->page_size;
     if ((st = byte_map(ctx, c->k_pool, rows, c->page_size, true, &tm_k)) != MF_OK) return st;
@@ -1020,6 +1058,23 @@ extern "C" {
 mf_status mf_paged_decode_kv8(MfContext *ctx, const MfDecodePlan *pl, const MfPagedKv8 *c, const MfPagedDecodeArgs *a)
 {
     return mf::paged_decode_kv8_common(ctx, pl, c, a, nullptr, nullptr, nullptr, nullptr);
+}
+
+mf_status mf_paged_decode_kv8_push_merge(MfContext *ctx, const MfDecodePlan *pl, const MfPagedKv8 *c, const MfPagedDecodeArgs *a,
+                                         const uint32_t *rope_positions, const MfPeerExchange *px, uint32_t step,
+                                         uint32_t pusher_mask)
+{
+    if (ctx && !px) return mf::fail(ctx, MF_ERR_INPUT_NOT_FOUND, "peer exchange");
+    if (ctx && !pusher_mask) return mf::fail(ctx, MF_ERR_INVALID_OPERATION, "empty pusher mask");
+    if (ctx && a && !a->out) return mf::fail(ctx, MF_ERR_INPUT_NOT_FOUND, "push merge: output");
+    return mf::paged_decode_kv8_common(ctx, pl, c, a, rope_positions, nullptr, nullptr, nullptr, px, step, pusher_mask);
+}
+
+mf_status mf_paged_decode_kv8_partial_push(MfContext *ctx, const MfDecodePlan *pl, const MfPagedKv8 *c, const MfPagedDecodeArgs *a,
+                                           const uint32_t *rope_positions, const MfPeerExchange *px, uint32_t step)
+{
+    if (ctx && !px) return mf::fail(ctx, MF_ERR_INPUT_NOT_FOUND, "peer exchange");
+    return mf::paged_decode_kv8_common(ctx, pl, c, a, rope_positions, nullptr, nullptr, nullptr, px, step, 0);
 }
 
 mf_status mf_paged_decode_kv8_partial(MfContext *ctx, const MfDecodePlan *pl, const MfPagedKv8 *c, const MfPagedDecodeArgs *a,

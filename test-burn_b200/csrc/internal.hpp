@@ -275,6 +275,9 @@ UniformSplit uniform_split(uint32_t units, uint32_t tiles_per_unit, uint32_t n_s
 // Largest cluster size (16, 8 or 0) the decode kernel for this head_dim / group can be launched with on the
 // context's device; 0 when clusters are switched off.
 uint32_t decode_max_cluster(MfContext *ctx, uint32_t head_dim, uint32_t group);
+// Sequence-sharded decode: fills the exchange fields of a launch's parameters (attention_api.cu).
+mf_status setup_push(MfContext *ctx, const MfPeerExchange *px, uint32_t step, uint32_t merge_mask, uint64_t rows_in_call,
+                     uint32_t D, DecodeParams &p);
 uint32_t decode_cta_target(uint32_t sm_count, uint32_t ctas_per_sm, uint64_t total_tiles);
 
 // Launchers (decode.cu, prefill.cu, kv_append.cu).

@@ -161,6 +161,146 @@ def test_8bit_partials_and_merge_equal_full_decode(mfk, foundry, append_in_shard
         assert np.array_equal(d_vs.cpu().numpy().view(np.uint32), vs_ref.view(np.uint32))
 
 
+def _kv8_shards(mfk, foundry, case, pools, L, cuts, max_ctas=296):
+    """Shard descriptors over one set of 8-bit pools: [(desc, plan, keep-alive)] for the page ranges in `cuts`."""
+    out = []
+    for (p0, p1) in cuts:
+        pt = np.ascontiguousarray(case.page_table[:, p0:p1])
+        lens = np.array([max(0, min(L, p1 * case.P) - p0 * case.P)], np.uint32)
+        d_pt, d_len = dev_u32(pt), dev_u32(lens)
+        desc = mfk.paged_kv8(*pools, d_pt, d_len, n_kv_heads=case.Hkv, page_size=case.P)
+        plan = foundry.decode_plan(lens, n_heads=case.Hq, n_kv_heads=case.Hkv, head_dim=case.D, page_size=case.P, max_ctas=max_ctas)
+        out.append((desc, plan, (d_pt, d_len)))
+    return out
+
+
+def test_8bit_pushed_partials_two_shards_one_gpu(mfk, foundry):
+    """The kernels' own exchange over the 8-bit cache, both shards on one GPU: two-launch form (both shards push,
+    then each "rank" merges) against mf_paged_decode_kv8_partial + mf_merge_partials bit for bit and against the
+    oracle's unsharded result; the one-launch form with a single pusher (a second rank's kernel could not run
+    beside it on this one GPU) gives that shard's own normalised partial."""
+    import torch
+
+    Hq, Hkv, D, P, L = 24, 8, 128, 64, 2048 + 17
+    case = PagedCase(batch=1, n_heads=Hq, n_kv_heads=Hkv, head_dim=D, page_size=P, cached=[L - 1], poison=False, rope_mode=1)
+    k8, v8, ks, vs = quantised_pools(case)
+    q_ref, k8_ref, v8_ref, ks_ref, vs_ref, out_ref, gold = oracle_step(case, k8, v8, ks, vs)
+    pools = [torch.from_numpy(np.ascontiguousarray(x)).cuda() for x in (k8_ref, v8_ref, ks_ref, vs_ref)]
+    n_pages = case.page_table.shape[1]
+    cut = n_pages // 3
+    parts = _kv8_shards(mfk, foundry, case, pools, L, [(0, cut), (cut, n_pages)])
+    q_rot = dev(q_ref)
+    pxs = [foundry.peer_exchange_create(2, r, Hq, D)[0] for r in range(2)]
+    for r in range(2):  # same process: the "peer" buffers are plain local pointers
+        o = 1 - r
+        pxs[r].recv[o], pxs[r].counters[o] = pxs[o].recv[o], pxs[o].counters[o]
+    accs = torch.zeros((2, Hq, D), dtype=torch.float32, device="cuda")
+    ms = torch.full((2, Hq), -1e30, dtype=torch.float32, device="cuda")
+    ls = torch.zeros((2, Hq), dtype=torch.float32, device="cuda")
+    for r, (desc, plan, _) in enumerate(parts):
+        foundry.paged_decode_kv8_partial(plan, desc, q_rot, None, accs[r:r + 1], ms[r:r + 1], ls[r:r + 1], n_heads=Hq,
+                                         scale=float(case.scale))
+    want = torch.empty((Hq, D), dtype=torch.float16, device="cuda")
+    foundry.merge_partials(accs, ms, ls, want)
+    foundry.synchronize()
+    assert max_abs(host(want), out_ref) <= TOL and max_abs(host(want), gold.ravel()) <= TOL
+    for step in range(3):
+        outs = [torch.full((Hq, D), float("nan"), dtype=torch.float16, device="cuda") for _ in range(2)]
+        for r, (desc, plan, _) in enumerate(parts):
+            foundry.paged_decode_kv8_partial_push(plan, desc, q_rot, pxs[r], step, n_heads=Hq, scale=float(case.scale))
+        for r in range(2):
+            foundry.merge_pushed(pxs[r], [Hkv, Hkv], step, Hq, D, outs[r])
+        foundry.synchronize()
+        for o in outs:
+            assert np.array_equal(host(o), host(want))
+    for r, (desc, plan, _) in enumerate(parts):
+        solo = torch.full((Hq, D), float("nan"), dtype=torch.float16, device="cuda")
+        foundry.paged_decode_kv8_push_merge(plan, desc, q_rot, solo, pxs[r], 3, 1 << r, n_heads=Hq, scale=float(case.scale))
+        foundry.synchronize()
+        one = torch.empty((Hq, D), dtype=torch.float16, device="cuda")
+        foundry.merge_partials(accs[r:r + 1], ms[r:r + 1], ls[r:r + 1], one)
+        foundry.synchronize()
+        assert np.array_equal(host(solo), host(one))
+    for (_, plan, _) in parts:
+        plan.close()
+    for r in range(2):  # borrowed pointers are not this exchange's to release
+        o = 1 - r
+        pxs[r].recv[o] = pxs[r].counters[o] = None
+        foundry.peer_exchange_destroy(pxs[r])
+
+
+def _kv8_two_gpu_worker(rank, world, port, ret):
+    import importlib
+    import os
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    sys.path.insert(0, str(root))
+    sys.path.insert(0, str(root / "tests"))
+    import torch
+    import torch.distributed as dist
+
+    mfk = importlib.import_module("test-burn_b200")
+    sharding = importlib.import_module("test-burn_b200.sharding")
+    dist.init_process_group("gloo", init_method="file://" + port, rank=rank, world_size=world)
+    torch.cuda.set_device(rank)
+    try:
+        Hq, Hkv, D, P, L = 24, 8, 128, 64, 6000
+        case = PagedCase(batch=1, n_heads=Hq, n_kv_heads=Hkv, head_dim=D, page_size=P, cached=[L - 1], poison=False, rope_mode=1)
+        k8, v8, ks, vs = quantised_pools(case)
+        q_ref, k8_ref, v8_ref, ks_ref, vs_ref, out_ref, gold = oracle_step(case, k8, v8, ks, vs)
+        f = mfk.Foundry(rank)
+        pools = [torch.from_numpy(np.ascontiguousarray(x)).cuda() for x in (k8_ref, v8_ref, ks_ref, vs_ref)]
+        n_pages = case.page_table.shape[1]
+        b, e = sharding.shard_pages(n_pages, world, rank)
+        (desc, plan, keep), = _kv8_shards(mfk, f, case, pools, L, [(b, e)])
+        px, handle = f.peer_exchange_create(world, rank, Hq, D)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle)
+        for r in range(world):
+            if r != rank:
+                f.peer_exchange_attach(px, r, handles[r])
+        ok = True
+        q_rot = dev(q_ref)
+        for step in range(6):
+            f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, step // 3)
+            f.set_option(mfk.OPTION_PUSH_TAGGED, 1 if step < 4 else 0)  # steps 1, 3: tagged words; step 5: counters
+            out = torch.full((Hq, D), float("nan"), dtype=torch.float16, device="cuda")
+            if step % 2 == 0:  # two launches: push, then the waiting merge kernel
+                f.paged_decode_kv8_partial_push(plan, desc, q_rot, px, step, n_heads=Hq, scale=float(case.scale))
+                f.merge_pushed(px, [Hkv] * world, step, Hq, D, out)
+            else:              # one launch: the decode kernel also waits for the peers and merges
+                f.paged_decode_kv8_push_merge(plan, desc, q_rot, out, px, step, (1 << world) - 1, n_heads=Hq,
+                                              scale=float(case.scale))
+            f.synchronize()
+            ok = ok and max_abs(host(out), out_ref) <= TOL and max_abs(host(out), gold.ravel()) <= TOL
+        plan.close()
+        dist.barrier()  # nobody unmaps while a peer may still store
+        f.peer_exchange_destroy(px)
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_8bit_pushed_partials_two_gpus():
+    """One process per GPU: the 8-bit decode kernels exchange their partials over NVLink, two-launch and fused forms,
+    tagged words and counters, against the oracle's unsharded result."""
+    import os
+    import tempfile
+
+    import torch
+    import torch.multiprocessing as mp
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world, port = 2, os.path.join(tempfile.mkdtemp(prefix="mf_rdzv_"), "store")
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_kv8_two_gpu_worker, args=(world, port, ret), nprocs=world, join=True)
+        assert dict(ret) == {0: True, 1: True}
+
+
 def test_8bit_append_kernel_and_gather(mfk, foundry):
     """The standalone quantising append (one token per sequence, and a chunk of rows of one sequence) against
     the oracle's quantiser, bit for bit; the dequantising gather against e4m3 * scale rounded to f16."""
