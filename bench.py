@@ -64,7 +64,7 @@ LONG_CONTEXT = {
     "c5": dict(layers=28, n_heads=24, n_kv_heads=8, head_dim=128, kv_len=131072, page_size=64, theta=5e5, rope_mode=1,
                name="long-context single-sequence decode, Llama-3.2-3B shape: 28 layers, 24q/8kv heads, D128, "
                     "131072 cached tokens, page 64, sequence-sharded with (O,m,l) all-gather + merge"),
-    # c5 on the 8-bit cache: every rank's shard through mf_paged_decode_kv8_partial, then all-gather + merge
+    # c5 on the 8-bit cache (the same three exchange routes)
     "c5-kv8": dict(layers=28, n_heads=24, n_kv_heads=8, head_dim=128, kv_len=131072, page_size=64, theta=5e5, rope_mode=1,
                    kv8=True,
                    name="long-context single-sequence decode on the 8-bit cache (FP8 E4M3 + one f32 scale per row), "
@@ -479,13 +479,12 @@ def run_long_context(args, w):
         # (not only the one that appends) may stream K/V before the previous launch has ended
         f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 2)
     if kv8:
-        # the 8-bit kernel takes the plain form of the plan (an explicit CTA count) and the partial + gather route
+        # the 8-bit kernel takes the plain form of the plan (an explicit CTA count)
         plan = f.decode_plan(lens_host, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P,
                              max_ctas=2 * torch.cuda.get_device_properties(dev).multi_processor_count)
         descs = [mfk.paged_kv8(k_pools[i].view(e - b, hkv, P, d), v_pools[i].view(e - b, hkv, P, d),
                                k_scales[i].view(e - b, hkv, P), v_scales[i].view(e - b, hkv, P), table, d_lens,
                                n_kv_heads=hkv, page_size=P) for i in range(layers)]
-        args.exchange = "nccl"
     else:
         plan = f.decode_plan(lens_host, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P)
         descs = [mfk.paged_kv(k_pools[i].view(e - b, hkv, P, d), v_pools[i].view(e - b, hkv, P, d), table, d_lens,
@@ -512,11 +511,14 @@ def run_long_context(args, w):
             rb, re_ = sharding.shard_pages(n_pages, world, r)
             units.append(hkv if sharding.shard_local_len(L, P, rb, re_) else 0)
 
+    partial_push = f.paged_decode_kv8_partial_push if kv8 else f.paged_decode_partial_push
+    push_merge = f.paged_decode_kv8_push_merge if kv8 else f.paged_decode_push_merge
+
     def step_push():
         with torch.cuda.stream(stream):
             for i in range(layers):
                 if n_local:
-                    f.paged_decode_partial_push(plan, descs[i], q[i], px, step_no[0], n_heads=hq, rope_positions=d_pos,
+                    partial_push(plan, descs[i], q[i], px, step_no[0], n_heads=hq, rope_positions=d_pos,
                                                 scale=scale, k=k[i] if append_here else None,
                                                 v=v[i] if append_here else None, cos=d_cos, sin=d_sin, rope=True,
                                                 rope_mode=w["rope_mode"], append=append_here)
@@ -529,7 +531,7 @@ def run_long_context(args, w):
     def step_fused():
         with torch.cuda.stream(stream):
             for i in range(layers):
-                f.paged_decode_push_merge(plan, descs[i], q[i], out[i], px, step_no[0], pusher_mask, n_heads=hq,
+                push_merge(plan, descs[i], q[i], out[i], px, step_no[0], pusher_mask, n_heads=hq,
                                           rope_positions=d_pos, scale=scale, k=k[i] if append_here else None,
                                           v=v[i] if append_here else None, cos=d_cos, sin=d_sin, rope=True,
                                           rope_mode=w["rope_mode"], append=append_here)

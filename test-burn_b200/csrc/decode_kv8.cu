@@ -130,6 +130,9 @@ __device__ __forceinline__ void rope_pair(float xi, float xj, float c, float s, 
     oj = __float2half_rn(__fadd_rn(__fmul_rn(xj, c), __fmul_rn(xi, s)));
 }
 
+// PUSH: the sequence-sharded forms that hand the partials to the other ranks themselves (a separate instantiation, so
+// that the plain form carries none of that code: merely present, it cost the batched step 7 %).
+template <bool PUSH>
 __global__ void __launch_bounds__(kThreads, 2)
 decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const Kv8Params kp)
 {
@@ -239,7 +242,7 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     // ---------------------------------------------------------------- consumers ---
     grid_dependency_wait();
     if (p.strict_release) grid_launch_dependents();
-    if (p.push_wait_mask) push::push_wait_for_mergers(p, tid);
+    if (PUSH && p.push_wait_mask) push::push_wait_for_mergers(p, tid);
     float *comb = reinterpret_cast<float *>(smem + kOffComb);
     __half *q_s = reinterpret_cast<__half *>(smem + kOffQ);  // [head][kQStride] f16
     float *ml_s = reinterpret_cast<float *>(smem + kOffMl);
@@ -630,7 +633,7 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                     }
                 } else if (hg < G) {
                     const uint32_t h = it.kvh * G + hg;
-                    if (p.push_world) {  // sequence-sharded, fused exchange: the partial goes to every rank
+                    if (PUSH && p.push_world) {  // sequence-sharded, fused exchange: the partial goes to every rank
                         const size_t rows = (size_t)p.batch * p.n_heads, rowi = (size_t)it.seq * p.n_heads + h;
                         for (uint32_t r = 0; r < p.push_world; ++r) {
                             push::push_store(p, r, rowi * kD + d, acc);
@@ -656,7 +659,7 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
             if (hp == 0) named_bar_sync(1, kConsumerThreads);
         }
         if (direct) {
-            if (p.push_world) push::push_signal_and_merge<(int)kD>(p, it, tid, flags);
+            if (PUSH && p.push_world) push::push_signal_and_merge<(int)kD>(p, it, tid, flags);
             continue;
         }
 
@@ -735,7 +738,7 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
             const float4 acc = it.n_parts <= kFlightFew ? accumulate(std::integral_constant<uint32_t, kFlightFew>{})
                                                         : accumulate(std::integral_constant<uint32_t, kFlight>{});
             const uint32_t h = it.kvh * G + hg;
-            if (p.push_world) {
+            if (PUSH && p.push_world) {
                 const size_t rows = (size_t)p.batch * p.n_heads, rowi = (size_t)it.seq * p.n_heads + h;
                 for (uint32_t r = 0; r < p.push_world; ++r) {
                     if (p.push_tagged) {
@@ -771,7 +774,7 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                 dst[i] = __float2half_rn(r4[i]);
             }
         }
-        if (p.push_world) push::push_signal_and_merge<(int)kD>(p, it, tid, flags);
+        if (PUSH && p.push_world) push::push_signal_and_merge<(int)kD>(p, it, tid, flags);
     }
 }
 
@@ -976,8 +979,11 @@ mf_status paged_decode_kv8_common(MfContext *ctx, const MfDecodePlan *pl, const 
     if (pl->n_items == 0) return MF_OK;
     static bool configured[64] = {};
     if (ctx->device < 64 && !configured[ctx->device]) {
-        st = check_cuda(ctx, cudaFuncSetAttribute(decode_kv8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynamic),
+        st = check_cuda(ctx, cudaFuncSetAttribute(decode_kv8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynamic),
                         "cudaFuncSetAttribute(decode, 8-bit)");
+        if (st != MF_OK) return st;
+        st = check_cuda(ctx, cudaFuncSetAttribute(decode_kv8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynamic),
+                        "cudaFuncSetAttribute(decode, 8-bit, exchange)");
         if (st != MF_OK) return st;
         configured[ctx->device] = true;
     }
@@ -1041,7 +1047,8 @@ mf_status paged_decode_kv8_common(MfContext *ctx, const MfDecodePlan *pl, const 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = programmatic ? 1 : 0;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, decode_kv8_kernel, tm_k, tm_v, kp);
+    const cudaError_t e = px ? cudaLaunchKernelEx(&cfg, decode_kv8_kernel<true>, tm_k, tm_v, kp)
+                             : cudaLaunchKernelEx(&cfg, decode_kv8_kernel<false>, tm_k, tm_v, kp);
     if (e != cudaSuccess) return fail(ctx, MF_ERR_CUDA, "launch decode_kv8_kernel: %s", cudaGetErrorString(e));
     ++ctx->launches;
     if (programmatic) ctx->note_programmatic_launch(p.strict_release != 0, a->append ? c->k_pool : nullptr, a->append ? c->v_pool : nullptr);
