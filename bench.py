@@ -1060,7 +1060,8 @@ def other_workloads(args):
     global _COLLECT
     world = int(os.environ.get("WORLD_SIZE", "1"))
     jobs = [("c5", lambda a: run_long_context(a, LONG_CONTEXT["c5"]), dict(steps=20, exchange="fused")),
-            ("c3_strong", lambda a: run_batched_strong(a, dict(WORKLOADS["c3"])), dict(steps=20))]
+            ("c3_strong", lambda a: run_batched_strong(a, dict(WORKLOADS["c3"])), dict(steps=20)),
+            ("c5_kv8", lambda a: run_long_context(a, LONG_CONTEXT["c5-kv8"]), dict(steps=20, exchange="fused"))]
     if world == 1:
         jobs += [("c2", lambda a: run_contiguous_decode(a, CONTIGUOUS["c2"]), dict(one_launch=True, projection=False)),
                  ("c4", run_prefill, dict(steps=20, page_size=0)),
