@@ -532,6 +532,15 @@ MF_API void mf_decode_plan_destroy(MfContext *ctx, MfDecodePlan *plan);
 MF_API uint32_t mf_decode_plan_build_host(const uint32_t *kv_lens_host, uint32_t batch, uint32_t n_kv_heads,
                                           uint32_t max_ctas, uint32_t *items_out, uint32_t item_capacity,
                                           uint32_t *cta_begin_out, uint32_t *n_ctas_out);
+/* The same for launches the library may run in the cluster form (at most one CTA per SM): max_cluster is the
+ * largest cluster size allowed (a power of two up to 16, 0 = none), clusters_of_16 / clusters_of_8 how many
+ * clusters of those sizes the device holds at once (0 = no limit).  *cluster_out: the cluster size chosen, 0 =
+ * plain form (then the result is mf_decode_plan_build_host's); in the cluster form every item is one range of
+ * one unit and one cluster, *n_ranges_out their number (CTAs = ranges * cluster size). */
+MF_API uint32_t mf_decode_plan_build_host_clusters(const uint32_t *kv_lens_host, uint32_t batch, uint32_t n_kv_heads,
+                                                   uint32_t max_ctas, uint32_t max_cluster, uint32_t clusters_of_16,
+                                                   uint32_t clusters_of_8, uint32_t *items_out, uint32_t item_capacity,
+                                                   uint32_t *n_ranges_out, uint32_t *cluster_out);
 MF_API uint32_t mf_decode_plan_ctas(const MfDecodePlan *plan);
 /* CTAs per thread-block cluster of the plan's launches (0: the plain form, see MF_OPTION_DECODE_CLUSTERS). */
 MF_API uint32_t mf_decode_plan_cluster(const MfDecodePlan *plan);

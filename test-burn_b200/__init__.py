@@ -203,6 +203,7 @@ _SIGNATURES = {
     "mf_decode_plan_update": (C.c_int32, [vp, vp, vp]),
     "mf_decode_plan_destroy": (None, [vp, vp]),
     "mf_decode_plan_build_host": (u32, [vp, u32, u32, u32, vp, u32, vp, C.POINTER(u32)]),
+    "mf_decode_plan_build_host_clusters": (u32, [vp, u32, u32, u32, u32, u32, u32, vp, u32, C.POINTER(u32), C.POINTER(u32)]),
     "mf_decode_plan_ctas": (u32, [vp]),
     "mf_decode_plan_cluster": (u32, [vp]),
     "mf_decode_plan_items": (u32, [vp]),
@@ -812,6 +813,22 @@ def build_decode_plan_host(kv_lens, n_kv_heads: int, max_ctas: int):
     n = lib.mf_decode_plan_build_host(lens.ctypes.data, lens.shape[0], n_kv_heads, max_ctas, items.ctypes.data, cap,
                                       cta_begin.ctypes.data, C.byref(n_ctas))
     return items[:n].copy(), cta_begin[:n_ctas.value + 1].copy()
+
+
+def build_decode_plan_host_clusters(kv_lens, n_kv_heads: int, max_ctas: int, max_cluster: int = 16, clusters_of_16: int = 0,
+                                    clusters_of_8: int = 0):
+    """The step planner for a launch that may take the cluster form.  Returns (items [n, 8] uint32, cluster size);
+    cluster size 0: the plain form was chosen (items as build_decode_plan_host gives them)."""
+    import numpy as np
+
+    lens = np.ascontiguousarray(kv_lens, dtype=np.uint32)
+    cap = lens.shape[0] * n_kv_heads + max_ctas
+    items = np.zeros((cap, 8), np.uint32)
+    n_ranges, cluster = u32(0), u32(0)
+    n = lib.mf_decode_plan_build_host_clusters(lens.ctypes.data, lens.shape[0], n_kv_heads, max_ctas, max_cluster,
+                                               clusters_of_16, clusters_of_8, items.ctypes.data, cap, C.byref(n_ranges),
+                                               C.byref(cluster))
+    return items[:n].copy(), int(cluster.value)
 
 
 def align_capacity(n: int) -> int:

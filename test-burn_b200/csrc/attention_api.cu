@@ -510,11 +510,12 @@ static mf_status plan_upload(MfContext *ctx, MfDecodePlan *pl)
     mf_status st = check_cuda(ctx, cudaEventSynchronize(pl->staged[s]), "cudaEventSynchronize(plan staging)");
     if (st != MF_OK) return st;
     std::memcpy(pl->pinned_items[s], pl->h_items.data(), sizeof(WorkItem) * pl->n_items);
-    std::memcpy(pl->pinned_cta_begin[s], pl->h_cta_begin.data(), 4 * (pl->n_ctas + 1));
+    const size_t begin_bytes = 4 * pl->h_cta_begin.size();  // cluster form: one entry per cluster, not per CTA
+    std::memcpy(pl->pinned_cta_begin[s], pl->h_cta_begin.data(), begin_bytes);
     st = check_cuda(ctx, cudaMemcpyAsync(pl->d_items, pl->pinned_items[s], sizeof(WorkItem) * pl->n_items,
                                          cudaMemcpyHostToDevice, ctx->stream), "plan upload");
     if (st != MF_OK) return st;
-    st = check_cuda(ctx, cudaMemcpyAsync(pl->d_cta_begin, pl->pinned_cta_begin[s], 4 * (pl->n_ctas + 1),
+    st = check_cuda(ctx, cudaMemcpyAsync(pl->d_cta_begin, pl->pinned_cta_begin[s], begin_bytes,
                                          cudaMemcpyHostToDevice, ctx->stream), "plan upload");
     if (st != MF_OK) return st;
     return check_cuda(ctx, cudaEventRecord(pl->staged[s], ctx->stream), "cudaEventRecord(plan staging)");
@@ -630,6 +631,23 @@ uint32_t mf_decode_plan_build_host(const uint32_t *kv_lens_host, uint32_t batch,
         if (!items.empty()) std::memcpy(items_out, items.data(), items.size() * sizeof(WorkItem));
         std::memcpy(cta_begin_out, cta_begin.data(), cta_begin.size() * 4);
     }
+    return (uint32_t)items.size();
+}
+
+uint32_t mf_decode_plan_build_host_clusters(const uint32_t *kv_lens_host, uint32_t batch, uint32_t n_kv_heads,
+                                            uint32_t max_ctas, uint32_t max_cluster, uint32_t clusters_of_16,
+                                            uint32_t clusters_of_8, uint32_t *items_out, uint32_t item_capacity,
+                                            uint32_t *n_ranges_out, uint32_t *cluster_out)
+{
+    if (!kv_lens_host || max_ctas == 0 || n_kv_heads == 0) return 0;
+    std::vector<WorkItem> items;
+    std::vector<uint32_t> cta_begin;
+    uint32_t n_units = 0, cluster = (max_cluster & 0xFFu) | ((clusters_of_16 & 0xFFu) << 8) | ((clusters_of_8 & 0xFFu) << 16);
+    uint64_t total = 0;
+    build_decode_plan(kv_lens_host, batch, n_kv_heads, max_ctas, items, cta_begin, &n_units, &total, &cluster);
+    if (n_ranges_out) *n_ranges_out = (uint32_t)cta_begin.size() - 1;
+    if (cluster_out) *cluster_out = cluster;
+    if (items.size() <= item_capacity && items_out && !items.empty()) std::memcpy(items_out, items.data(), items.size() * sizeof(WorkItem));
     return (uint32_t)items.size();
 }
 

@@ -502,3 +502,22 @@ def test_paged_decode_cluster_form(mfk, foundry, cfg):
         check(case, run_fused(mfk, foundry, case), ref)
     finally:
         foundry.set_option(mfk.OPTION_DECODE_CLUSTERS, 0)
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(batch=4, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[5567, 2751, 11455, 16255]),
+    dict(batch=8, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16,
+         cached=[5567, 2751, 11455, 16255, 12095, 4095, 6335, 10559]),
+    dict(batch=2, n_heads=24, n_kv_heads=8, head_dim=128, page_size=64, cached=[700, 3000]),
+    dict(batch=3, n_heads=14, n_kv_heads=2, head_dim=64, page_size=16, cached=[1500, 520, 4000]),
+])
+def test_short_batches_of_different_lengths_take_the_cluster_form(mfk, foundry, cfg):
+    """A few sequences of different lengths (what a rank holds when one batch is split over eight GPUs): every unit is
+    cut into ranges of about equal length, one cluster per range; same bits in the pools and in q_rot, same answer."""
+    case = PagedCase(**cfg)
+    ref = case.oracle_step()
+    plan = foundry.decode_plan(case.kv_lens, n_heads=case.Hq, n_kv_heads=case.Hkv, head_dim=case.D, page_size=case.P)
+    assert plan.cluster in (2, 4, 8) and plan.ctas % plan.cluster == 0
+    plan.close()
+    check(case, run_fused(mfk, foundry, case), ref)
+    check(case, run_fused(mfk, foundry, case, repeats=2), ref)  # the step again on the same pools: idempotent

@@ -127,6 +127,57 @@ def check_plan(items, cta_begin, kv_lens, n_kv_heads, max_ctas):
     assert len(seen) == int((tiles > 0).sum()) * n_kv_heads
 
 
+@pytest.mark.parametrize("seed", range(8))
+def test_cluster_plans_for_sequences_of_different_lengths(mfk, seed):
+    """Short launches (at most one CTA per SM) over sequences of different lengths: clusters of one size, every unit cut
+    into ranges of about equal length, one cluster per range.  Every range has at least one tile per CTA of its
+    cluster, the ranges of a unit cover it in order, the CTAs fit the launch, and clusters of 16 are only used when
+    no unit needs a second range."""
+    rng = np.random.default_rng(100 + seed)
+    batch = int(rng.integers(1, 10))
+    n_kv_heads = int(rng.choice([1, 2, 8]))
+    lens = rng.integers(512, 16385, size=batch).astype(np.uint32)
+    if seed == 0:
+        lens[:] = 8192                      # equal lengths: the uniform cluster plan
+    if seed == 1:
+        lens[0] = 0                         # a sequence without keys has no unit
+    max_ctas = 148
+    fit16, fit8 = (14, 36) if seed % 2 else (0, 0)
+    items, cluster = mfk.build_decode_plan_host_clusters(lens, n_kv_heads, max_ctas, 16, fit16, fit8)
+    tiles = (lens.astype(np.int64) + 63) // 64
+    total = int(tiles.sum()) * n_kv_heads
+    if cluster == 0:                        # plain form: the other planner's invariants
+        plain, cta_begin = mfk.build_decode_plan_host(lens, n_kv_heads, max_ctas)
+        assert np.array_equal(items, plain)
+        check_plan(plain, cta_begin, lens, n_kv_heads, max_ctas)
+        return
+    assert cluster in (2, 4, 8, 16) and len(items) * cluster <= max_ctas
+    if cluster == 16 and fit16:
+        assert len(items) <= fit16
+    if cluster == 8 and fit8:
+        assert len(items) <= fit8
+    uniform = len(set(int(t) for t in tiles if t)) == 1   # equal lengths: ranges of ceil(T / k) tiles, the last one shorter
+    seen = {}
+    for i, (seq, kvh, tb, te, slot, unit, n_parts, first_slot) in enumerate(items.tolist()):
+        assert te - tb >= (1 if uniform else cluster) and unit == seq * n_kv_heads + kvh and slot == i
+        cov = seen.setdefault(unit, [])
+        assert tb == (cov[-1][1] if cov else 0)
+        cov.append((tb, te))
+        assert first_slot == slot - (len(cov) - 1)
+    for unit, cov in seen.items():
+        assert cov[-1][1] == tiles[unit // n_kv_heads]
+        assert all(items[i, 6] == len(cov) for i in range(len(items)) if items[i, 5] == unit)
+        spans = [e - b for b, e in cov]
+        if uniform:
+            assert all(x == spans[0] for x in spans[:-1]) and spans[-1] <= spans[0]
+        else:
+            assert max(spans) - min(spans) <= 1       # ranges of equal length
+            if cluster == 16:
+                assert len(cov) == 1
+    assert len(seen) == int((tiles > 0).sum()) * n_kv_heads
+    assert sum(e - b for cov in seen.values() for b, e in cov) == total
+
+
 @pytest.mark.parametrize("seed", range(6))
 def test_decode_plan_invariants(mfk, seed):
     rng = np.random.default_rng(seed)
