@@ -971,9 +971,6 @@ mf_status paged_decode_kv8_common(MfContext *ctx, const MfDecodePlan *pl, const 
     if (c->batch != pl->batch || c->n_kv_heads != pl->n_kv_heads || c->head_dim != pl->head_dim || a->n_heads != pl->n_heads ||
         c->page_size != pl->page_size)
         return fail(ctx, MF_ERR_INVALID_SHAPE, "paged decode (8-bit): cache geometry differs from the plan");
-    if (pl->cluster > 1)
-        return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "paged decode (8-bit): the plan is in the cluster form; create it with "
-                                                         "MF_OPTION_DECODE_CLUSTERS = 1 or an explicit CTA count");
     if (a->n_heads / c->n_kv_heads > 8)
         return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "paged decode (8-bit): group size %u > 8", a->n_heads / c->n_kv_heads);
     if (pl->n_items == 0) return MF_OK;
@@ -1038,7 +1035,10 @@ mf_status paged_decode_kv8_common(MfContext *ctx, const MfDecodePlan *pl, const 
     const bool programmatic = ctx->overlap_launches != 0;
     p.strict_release = (programmatic && ctx->next_launch_strict()) ? 1u : 0u;
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(pl->n_ctas);
+    // A plan in the cluster form lists one range of one unit per cluster; this kernel has no cluster form and runs
+    // every range as one CTA's item (correct, with fewer CTAs than the plan was made for: a plan with an explicit CTA
+    // count, or made under MF_OPTION_DECODE_CLUSTERS = 1, uses the whole GPU).
+    cfg.gridDim = dim3(pl->cluster > 1 ? pl->n_ctas / pl->cluster : pl->n_ctas);
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = kDynamic;
     cfg.stream = ctx->stream;

@@ -107,6 +107,29 @@ def test_fused_append_decode_on_the_8bit_cache(mfk, foundry, cfg, rope_mode, max
     assert max_abs(host(out), gold.ravel()) <= TOL
 
 
+@pytest.mark.parametrize("cached", [[4999], [1500, 520, 4000]])
+def test_8bit_decode_on_a_plan_in_the_cluster_form(mfk, foundry, cached):
+    """A plan made under the library's own CTA count for a short launch is in the cluster form (one range of a unit per
+    cluster); the 8-bit kernel has no cluster form and runs every range as one CTA's item: same answer."""
+    import torch
+
+    case = PagedCase(batch=len(cached), n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=cached, poison=False)
+    k8, v8, ks, vs = quantised_pools(case)
+    q_ref, k8_ref, v8_ref, ks_ref, vs_ref, out_ref, gold = oracle_step(case, k8, v8, ks, vs)
+    pools = [torch.from_numpy(x).cuda() for x in (k8, v8, ks, vs)]
+    pt, lens = dev_u32(case.page_table), dev_u32(case.kv_lens)
+    desc = mfk.paged_kv8(*pools, pt, lens, n_kv_heads=case.Hkv, page_size=case.P)
+    plan = foundry.decode_plan(case.kv_lens, n_heads=case.Hq, n_kv_heads=case.Hkv, head_dim=case.D, page_size=case.P)
+    assert plan.cluster > 1
+    out = torch.full((case.B, case.Hq * case.D), float("nan"), dtype=torch.float16, device="cuda")
+    foundry.paged_decode_kv8(plan, desc, dev(case.q), out, n_heads=case.Hq, k=dev(case.k), v=dev(case.v), cos=dev(case.cos),
+                             sin=dev(case.sin), rope=True, rope_mode=case.rope_mode, append=True, scale=float(case.scale))
+    foundry.synchronize()
+    plan.close()
+    assert np.array_equal(pools[0].cpu().numpy(), k8_ref) and np.array_equal(pools[1].cpu().numpy(), v8_ref)
+    assert max_abs(host(out), out_ref) <= TOL and max_abs(host(out), gold.ravel()) <= TOL
+
+
 @pytest.mark.parametrize("append_in_shard", [False, True])
 @pytest.mark.parametrize("max_ctas", [296, 5])
 def test_8bit_partials_and_merge_equal_full_decode(mfk, foundry, append_in_shard, max_ctas):
