@@ -70,6 +70,8 @@ LONG_CONTEXT = {
                    name="long-context single-sequence decode on the 8-bit cache (FP8 E4M3 + one f32 scale per row), "
                         "Llama-3.2-3B shape: 28 layers, 24q/8kv heads, D128, 131072 cached tokens, page 64, "
                         "sequence-sharded with (O,m,l) all-gather + merge"),
+    "c5-kv8-32k": dict(layers=28, n_heads=24, n_kv_heads=8, head_dim=128, kv_len=32768, page_size=64, theta=5e5, rope_mode=1,
+                       kv8=True, name="c5-32k on the 8-bit cache (the per-GPU shape of c5-kv8 at 8 GPUs, on 2)"),
     "c5-small": dict(layers=4, n_heads=24, n_kv_heads=8, head_dim=128, kv_len=131072, page_size=64, theta=5e5,
                      rope_mode=1, name="c5 with 4 layers (test case)"),
     # the per-GPU shape of c5 at 8 GPUs (16384 tokens per rank: short launches, cluster form) on 2 and on 4 GPUs
@@ -479,9 +481,7 @@ def run_long_context(args, w):
         # (not only the one that appends) may stream K/V before the previous launch has ended
         f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 2)
     if kv8:
-        # the 8-bit kernel takes the plain form of the plan (an explicit CTA count)
-        plan = f.decode_plan(lens_host, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P,
-                             max_ctas=2 * torch.cuda.get_device_properties(dev).multi_processor_count)
+        plan = f.decode_plan(lens_host, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P)
         descs = [mfk.paged_kv8(k_pools[i].view(e - b, hkv, P, d), v_pools[i].view(e - b, hkv, P, d),
                                k_scales[i].view(e - b, hkv, P), v_scales[i].view(e - b, hkv, P), table, d_lens,
                                n_kv_heads=hkv, page_size=P) for i in range(layers)]

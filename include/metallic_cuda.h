@@ -719,9 +719,8 @@ typedef struct MfPagedKv8 {
     uint32_t batch;
 } MfPagedKv8;
 /* mf_paged_decode over the 8-bit cache: optional append (RoPE of k, row quantiser, pool and scale
- * written) + RoPE of q + GQA flash-decode in one launch.  The kernel has no cluster form: a plan in
- * that form (short launches under the library's own CTA count) is run with one CTA per range; create
- * the plan with an explicit CTA count or under MF_OPTION_DECODE_CLUSTERS = 1 to use the whole GPU. */
+ * written) + RoPE of q + GQA flash-decode in one launch.  Plans in the plain and in the cluster form are
+ * taken (where the device refuses the plan's cluster size every range runs as one CTA's item). */
 MF_API mf_status mf_paged_decode_kv8(MfContext *ctx, const MfDecodePlan *plan, const MfPagedKv8 *cache,
                                      const MfPagedDecodeArgs *args);
 /* Causal chunked prefill over the 8-bit cache (mf_paged_prefill's arguments): the sequence's first kv_len rows are

@@ -132,7 +132,26 @@ __device__ __forceinline__ void rope_pair(float xi, float xj, float c, float s, 
 
 // PUSH: the sequence-sharded forms that hand the partials to the other ranks themselves (a separate instantiation, so
 // that the plain form carries none of that code: merely present, it cost the batched step 7 %).
-template <bool PUSH>
+// Item i of the plan; in the cluster form (CL) item i belongs to cluster i and this CTA takes an equal share of its
+// tiles (the first `rem` CTAs one more).
+template <bool CL>
+__device__ __forceinline__ WorkItem load_item(const DecodeParams &p, uint32_t i)
+{
+    WorkItem it = p.items[i];
+    if (CL) {
+        const uint32_t C = p.cluster_size, r = cluster_cta_rank();
+        const uint32_t tiles = it.tile_end - it.tile_begin, base = tiles / C, rem = tiles - base * C;
+        it.tile_begin += r * base + min(r, rem);
+        it.tile_end = it.tile_begin + base + (r < rem ? 1u : 0u);
+    }
+    return it;
+}
+
+// CL: the cluster form of decode_kernel (decode.cu) - the CTAs of a unit (or of one range of it) form a thread-block
+// cluster, every CTA owns head_dim / C dims of every head, the CTAs' combined accumulators meet in the owners' shared
+// memory (in the area the plain form's combine uses: nothing else touches it while tiles stream) and one cluster
+// barrier later every owner reduces its columns.  A separate instantiation, like PUSH.
+template <bool PUSH, bool CL>
 __global__ void __launch_bounds__(kThreads, 2)
 decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const Kv8Params kp)
 {
@@ -170,8 +189,8 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         if (lane == 0) tma_prefetch_desc(tm);
         if (!p.early_stream) grid_dependency_wait();
         const uint64_t policy = l2_policy_evict_first();
-        uint32_t idx = p.cta_item_begin[blockIdx.x];
-        const uint32_t end = p.cta_item_begin[blockIdx.x + 1];
+        uint32_t idx = CL ? blockIdx.x / p.cluster_size : p.cta_item_begin[blockIdx.x];
+        const uint32_t end = CL ? idx + 1 : p.cta_item_begin[blockIdx.x + 1];
         uint32_t stage = 0, phase = 0, issued = 0;
         // Page ids travel 32 at a time, one per lane, a chunk ahead of the tiles that use them: a lookup per tile in
         // front of its copies had put one global-load latency into every tile of the stream.  The same goes for the
@@ -182,7 +201,7 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         WorkItem it_next{};
         uint32_t L_next = 0, ids_a = 0, ids_b = 0;
         auto fetch_item = [&](uint32_t i) {
-            it_next = p.items[i];
+            it_next = load_item<CL>(p, i);
             L_next = min(p.kv_lens[it_next.seq], p.pt_stride * P);  // never past the page table
             ids_a = ids_of(it_next, L_next, it_next.tile_begin * boxes_per_tile);
             ids_b = ids_of(it_next, L_next, it_next.tile_begin * boxes_per_tile + 32);
@@ -259,15 +278,15 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
     const uint32_t voff = half * (32 * kD) + lane * 16;
     const uint32_t key_lo = 4 * (g >> 1) + (g & 1);  // key (within a block) of accumulator rows g | g + 8: key_lo | key_lo + 2
 
-    uint32_t idx = p.cta_item_begin[blockIdx.x];
-    const uint32_t end = p.cta_item_begin[blockIdx.x + 1];
+    uint32_t idx = CL ? blockIdx.x / p.cluster_size : p.cta_item_begin[blockIdx.x];
+    const uint32_t end = CL ? idx + 1 : p.cta_item_begin[blockIdx.x + 1];
     uint32_t stage = 0, phase = 0;
     // The next item and its length are fetched while this item's tiles stream: two dependent loads less between
     // the last tile of one item and the first of the next (what an item costs is what the step planner charges).
     WorkItem it_next{};
     uint32_t L_next = 0, pos_next = 0;
     if (idx < end) {
-        it_next = p.items[idx];
+        it_next = load_item<CL>(p, idx);
         L_next = p.kv_lens[it_next.seq];
         pos_next = p.rope_positions ? p.rope_positions[it_next.seq] : 0u;
     }
@@ -275,7 +294,7 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         const WorkItem it = it_next;
         const uint32_t L_dev = L_next, pos_dev = pos_next;
         if (idx + 1 < end) {
-            it_next = p.items[idx + 1];
+            it_next = load_item<CL>(p, idx + 1);
             L_next = p.kv_lens[it_next.seq];
             pos_next = p.rope_positions ? p.rope_positions[it_next.seq] : 0u;
         }
@@ -599,8 +618,118 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
             fac[1] = fast_exp2(m_run[1] - ma1) * sigma;
         }
         const bool direct = it.n_parts == 1;
+        const uint32_t C = CL ? p.cluster_size : 1u;
+        if (CL) {
+            const uint32_t crank = cluster_cta_rank(), own_dims = kD / C;  // C is a power of two up to 16
+            const uint32_t recv_acc_addr = smem_base + kOffComb, recv_ml_addr = recv_acc_addr + kHP * kD * 4;
+            static_assert(kHP * kD * 4 + 16 * kHP * 2 * 4 <= kCombBytes, "the receive area takes the combine area's place");
+            // One item per CTA in this form, so the ring is idle by now: its first bytes take the four warps'
+            // accumulators at full width, in one pass.
+            constexpr uint32_t kFS = kD + 4;  // floats per head row
+            float *cf = reinterpret_cast<float *>(smem);
+            {
+                float *c0 = cf + (warp * kHP + 2 * c) * kFS, *c1 = c0 + kFS;
 #pragma unroll
-        for (int hp = 0; hp < 2; ++hp) {
+                for (int mt = 0; mt < (int)kD / 16; ++mt) {
+                    const uint32_t d0 = mt * 16 + g;  // accumulator rows are dims g and g + 8 of the chunk
+                    c0[d0] = o[mt][0] * fac[0];
+                    c1[d0] = o[mt][1] * fac[1];
+                    c0[d0 + 8] = o[mt][2] * fac[0];
+                    c1[d0 + 8] = o[mt][3] * fac[1];
+                }
+            }
+            named_bar_sync(2, kConsumerThreads);
+            // this CTA's (m, l) of every head to every CTA of the cluster
+            for (uint32_t i2 = tid; i2 < C * kHP; i2 += kConsumerThreads) {
+                const uint32_t r = i2 / kHP, hg = i2 - r * kHP;
+                float m_all = kNegSentinel;
+#pragma unroll
+                for (uint32_t w = 0; w < kConsumerWarps; ++w) m_all = fmaxf(m_all, ml_s[(w * kHP + hg) * 2]);
+                float l_all = 0.f;
+#pragma unroll
+                for (uint32_t w = 0; w < kConsumerWarps; ++w)
+                    l_all += ml_s[(w * kHP + hg) * 2 + 1] * fast_exp2(ml_s[(w * kHP + hg) * 2] - m_all);
+                st_cluster_f2(cluster_map_shared(recv_ml_addr + (crank * kHP + hg) * 8, r), m_all, l_all);
+            }
+            // four heads of one dim per thread: one 16-byte store into the owner's shared memory
+            for (uint32_t e = tid; e < (kHP / 4) * kD; e += kConsumerThreads) {
+                const uint32_t gq = e / kD, d = e - gq * kD;
+                if (gq * 4 >= G) continue;  // padded heads are never read
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (uint32_t w = 0; w < kConsumerWarps; ++w) {
+                    const float *c4 = cf + (w * kHP + gq * 4) * kFS + d;
+                    acc.x += c4[0];
+                    acc.y += c4[kFS];
+                    acc.z += c4[2 * kFS];
+                    acc.w += c4[3 * kFS];
+                }
+                const uint32_t owner = d / own_dims, dl = d - owner * own_dims;
+                st_cluster_f4(cluster_map_shared(recv_acc_addr + ((crank * own_dims + dl) * kHP + gq * 4) * 4, owner), acc);
+            }
+            // ---- the cluster's CTAs meet: every store above has landed once all of them have arrived ----
+            __syncwarp();
+            cluster_arrive_release();
+            cluster_wait_acquire();
+            const float *racc = reinterpret_cast<const float *>(smem + kOffComb);
+            const float2 *rml = reinterpret_cast<const float2 *>(smem + kOffComb + kHP * kD * 4);
+            for (uint32_t col = tid; col < own_dims * kHP; col += kConsumerThreads) {  // (dim, head) columns this CTA owns
+                const uint32_t hg = col % kHP, dl = col / kHP, d = crank * own_dims + dl;
+                if (hg >= G) continue;
+                float mx = kNegSentinel;
+#pragma unroll 4
+                for (uint32_t r = 0; r < C; ++r) mx = fmaxf(mx, rml[r * kHP + hg].x);
+                float lt = 0.f, acc = 0.f;
+#pragma unroll 4
+                for (uint32_t r = 0; r < C; ++r) {
+                    const float2 ml = rml[r * kHP + hg];
+                    const float w = fast_exp2(ml.x - mx);
+                    lt += ml.y * w;
+                    acc += racc[(r * own_dims + dl) * kHP + hg] * w;
+                }
+                const uint32_t h = it.kvh * G + hg;
+                if (!direct) {
+                    // the cluster's partial of the unit; the CTA that completes the unit merges (ticket below)
+                    p.part_acc[((size_t)it.slot * kHP + hg) * kD + d] = acc;
+                    if (d == 0) *reinterpret_cast<float2 *>(p.part_ml + ((size_t)it.slot * kHP + hg) * 2) = make_float2(mx * kLn2, lt);
+                } else if (PUSH && p.push_world) {
+                    const size_t rows = (size_t)p.batch * p.n_heads, rowi = (size_t)it.seq * p.n_heads + h;
+                    for (uint32_t r = 0; r < p.push_world; ++r) {
+                        push::push_store(p, r, rowi * kD + d, acc);
+                        if (d == 0) {
+                            push::push_store(p, r, rows * kD + rowi, mx * kLn2);
+                            push::push_store(p, r, rows * kD + rows + rowi, lt);
+                        }
+                    }
+                } else if (p.out_acc) {
+                    p.out_acc[((size_t)it.seq * p.n_heads + h) * kD + d] = acc;
+                    if (d == 0) {
+                        p.out_m[(size_t)it.seq * p.n_heads + h] = mx * kLn2;
+                        p.out_l[(size_t)it.seq * p.n_heads + h] = lt;
+                    }
+                } else {
+                    const bool ok = (fabsf(lt) <= 3.0e38f) && fabsf(lt) > 1e-6f;
+                    float r1 = ok ? acc / lt : acc;  // decode rule: the sum itself when l is tiny
+                    if (!(fabsf(r1) <= 3.0e38f)) r1 = 0.f;
+                    p.out[(size_t)it.seq * p.out_stride_b + (size_t)h * p.out_stride_h + d] = __float2half_rn(r1);
+                }
+            }
+            if (direct) {
+                if (!PUSH || !p.push_world) continue;  // nobody reads another CTA's shared memory after the barrier: done
+                // counted form: every CTA's share must be in the peers' blocks before the first CTA announces it (one
+                // cumulative fence by the announcing threads, after this barrier); tagged words need neither
+                if (!p.push_tagged) {
+                    __syncwarp();
+                    cluster_arrive_release();
+                    cluster_wait_acquire();
+                }
+                if (crank == 0) push::push_signal_and_merge<(int)kD>(p, it, tid, flags);
+                continue;
+            }
+            // not direct: every CTA of every cluster of the unit takes a ticket below; the last one merges
+        }
+#pragma unroll
+        for (int hp = 0; hp < (CL ? 0 : 2); ++hp) {
             {
                 float *c0 = comb + (warp * kHP + 2 * c) * kCombStride, *c1 = c0 + kCombStride;
 #pragma unroll
@@ -658,7 +787,7 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
             }
             if (hp == 0) named_bar_sync(1, kConsumerThreads);
         }
-        if (direct) {
+        if (!CL && direct) {
             if (PUSH && p.push_world) push::push_signal_and_merge<(int)kD>(p, it, tid, flags);
             continue;
         }
@@ -668,7 +797,7 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
         named_bar_sync(1, kConsumerThreads);
         if (tid == 0) {
             const uint32_t old = atomicAdd(p.counters + it.unit, 1u);
-            const uint32_t last = (old + 1 == it.n_parts) ? 1u : 0u;
+            const uint32_t last = (old + 1 == it.n_parts * C) ? 1u : 0u;  // cluster form: every CTA of the unit's clusters arrives
             if (last) p.counters[it.unit] = 0;
             flags[1] = last;
         }
@@ -974,14 +1103,20 @@ mf_status paged_decode_kv8_common(MfContext *ctx, const MfDecodePlan *pl, const 
     if (a->n_heads / c->n_kv_heads > 8)
         return fail(ctx, MF_ERR_OPERATION_NOT_SUPPORTED, "paged decode (8-bit): group size %u > 8", a->n_heads / c->n_kv_heads);
     if (pl->n_items == 0) return MF_OK;
+    typedef void (*Kv8Kernel)(const CUtensorMap, const CUtensorMap, const Kv8Params);
+    static const Kv8Kernel kernels[4] = {decode_kv8_kernel<false, false>, decode_kv8_kernel<true, false>,
+                                         decode_kv8_kernel<false, true>, decode_kv8_kernel<true, true>};
     static bool configured[64] = {};
+    static bool wide_clusters[64] = {};  // the cluster forms may run clusters of 16 (the non-portable size)
     if (ctx->device < 64 && !configured[ctx->device]) {
-        st = check_cuda(ctx, cudaFuncSetAttribute(decode_kv8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynamic),
-                        "cudaFuncSetAttribute(decode, 8-bit)");
-        if (st != MF_OK) return st;
-        st = check_cuda(ctx, cudaFuncSetAttribute(decode_kv8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynamic),
-                        "cudaFuncSetAttribute(decode, 8-bit, exchange)");
-        if (st != MF_OK) return st;
+        for (int i = 0; i < 4; ++i) {
+            st = check_cuda(ctx, cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, kDynamic),
+                            "cudaFuncSetAttribute(decode, 8-bit)");
+            if (st != MF_OK) return st;
+        }
+        wide_clusters[ctx->device] = cudaFuncSetAttribute(kernels[2], cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess &&
+                                     cudaFuncSetAttribute(kernels[3], cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        (void)cudaGetLastError();
         configured[ctx->device] = true;
     }
     Kv8Params kp{};
@@ -1034,21 +1169,33 @@ mf_status paged_decode_kv8_common(MfContext *ctx, const MfDecodePlan *pl, const 
     if ((st = byte_map(ctx, c->v_pool, rows, c->page_size, false, &tm_v)) != MF_OK) return st;
     const bool programmatic = ctx->overlap_launches != 0;
     p.strict_release = (programmatic && ctx->next_launch_strict()) ? 1u : 0u;
+    // A plan in the cluster form lists one range of one unit per cluster: the cluster instantiation runs it as such;
+    // where the device does not take clusters of that size, every range runs as one CTA's item in the plain form
+    // (correct, with fewer CTAs than the plan was made for).
+    const bool clustered = pl->cluster > 1 && (pl->cluster <= 8 || (ctx->device < 64 && wide_clusters[ctx->device]));
+    p.cluster_size = clustered ? pl->cluster : 1;
     cudaLaunchConfig_t cfg{};
-    // A plan in the cluster form lists one range of one unit per cluster; this kernel has no cluster form and runs
-    // every range as one CTA's item (correct, with fewer CTAs than the plan was made for: a plan with an explicit CTA
-    // count, or made under MF_OPTION_DECODE_CLUSTERS = 1, uses the whole GPU).
-    cfg.gridDim = dim3(pl->cluster > 1 ? pl->n_ctas / pl->cluster : pl->n_ctas);
+    cfg.gridDim = dim3(pl->cluster > 1 && !clustered ? pl->n_ctas / pl->cluster : pl->n_ctas);
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = kDynamic;
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    unsigned n_attr = 0;
+    if (programmatic) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    if (clustered) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = pl->cluster;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = programmatic ? 1 : 0;
-    const cudaError_t e = px ? cudaLaunchKernelEx(&cfg, decode_kv8_kernel<true>, tm_k, tm_v, kp)
-                             : cudaLaunchKernelEx(&cfg, decode_kv8_kernel<false>, tm_k, tm_v, kp);
+    cfg.numAttrs = n_attr;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernels[(px ? 1 : 0) + (clustered ? 2 : 0)], tm_k, tm_v, kp);
     if (e != cudaSuccess) return fail(ctx, MF_ERR_CUDA, "launch decode_kv8_kernel: %s", cudaGetErrorString(e));
     ++ctx->launches;
     if (programmatic) ctx->note_programmatic_launch(p.strict_release != 0, a->append ? c->k_pool : nullptr, a->append ? c->v_pool : nullptr);

@@ -131,7 +131,7 @@ def test_8bit_decode_on_a_plan_in_the_cluster_form(mfk, foundry, cached):
 
 
 @pytest.mark.parametrize("append_in_shard", [False, True])
-@pytest.mark.parametrize("max_ctas", [296, 5])
+@pytest.mark.parametrize("max_ctas", [296, 5, 0])
 def test_8bit_partials_and_merge_equal_full_decode(mfk, foundry, append_in_shard, max_ctas):
     """Sequence-sharded decode over the 8-bit cache on one GPU: two shards of one long sequence emit (acc, m, l)
     with mf_paged_decode_kv8_partial, mf_merge_partials over them equals the oracle's unsharded result.  With
@@ -197,7 +197,8 @@ def _kv8_shards(mfk, foundry, case, pools, L, cuts, max_ctas=296):
     return out
 
 
-def test_8bit_pushed_partials_two_shards_one_gpu(mfk, foundry):
+@pytest.mark.parametrize("max_ctas", [296, 0])  # 0: the library's own count, which gives these shards the cluster form
+def test_8bit_pushed_partials_two_shards_one_gpu(mfk, foundry, max_ctas):
     """The kernels' own exchange over the 8-bit cache, both shards on one GPU: two-launch form (both shards push,
     then each "rank" merges) against mf_paged_decode_kv8_partial + mf_merge_partials bit for bit and against the
     oracle's unsharded result; the one-launch form with a single pusher (a second rank's kernel could not run
@@ -211,7 +212,8 @@ def test_8bit_pushed_partials_two_shards_one_gpu(mfk, foundry):
     pools = [torch.from_numpy(np.ascontiguousarray(x)).cuda() for x in (k8_ref, v8_ref, ks_ref, vs_ref)]
     n_pages = case.page_table.shape[1]
     cut = n_pages // 3
-    parts = _kv8_shards(mfk, foundry, case, pools, L, [(0, cut), (cut, n_pages)])
+    parts = _kv8_shards(mfk, foundry, case, pools, L, [(0, cut), (cut, n_pages)], max_ctas=max_ctas)
+    assert all((plan.cluster > 1) == (max_ctas == 0) for (_, plan, _) in parts)
     q_rot = dev(q_ref)
     pxs = [foundry.peer_exchange_create(2, r, Hq, D)[0] for r in range(2)]
     for r in range(2):  # same process: the "peer" buffers are plain local pointers
@@ -252,7 +254,7 @@ def test_8bit_pushed_partials_two_shards_one_gpu(mfk, foundry):
         foundry.peer_exchange_destroy(pxs[r])
 
 
-def _kv8_two_gpu_worker(rank, world, port, ret):
+def _kv8_two_gpu_worker(rank, world, port, ret, max_ctas):
     import importlib
     import os
     import sys
@@ -277,7 +279,7 @@ def _kv8_two_gpu_worker(rank, world, port, ret):
         pools = [torch.from_numpy(np.ascontiguousarray(x)).cuda() for x in (k8_ref, v8_ref, ks_ref, vs_ref)]
         n_pages = case.page_table.shape[1]
         b, e = sharding.shard_pages(n_pages, world, rank)
-        (desc, plan, keep), = _kv8_shards(mfk, f, case, pools, L, [(b, e)])
+        (desc, plan, keep), = _kv8_shards(mfk, f, case, pools, L, [(b, e)], max_ctas=max_ctas)
         px, handle = f.peer_exchange_create(world, rank, Hq, D)
         handles = [None] * world
         dist.all_gather_object(handles, handle)
@@ -306,7 +308,8 @@ def _kv8_two_gpu_worker(rank, world, port, ret):
         dist.destroy_process_group()
 
 
-def test_8bit_pushed_partials_two_gpus():
+@pytest.mark.parametrize("max_ctas", [296, 0])  # 0: the cluster form
+def test_8bit_pushed_partials_two_gpus(max_ctas):
     """One process per GPU: the 8-bit decode kernels exchange their partials over NVLink, two-launch and fused forms,
     tagged words and counters, against the oracle's unsharded result."""
     import os
@@ -320,7 +323,7 @@ def test_8bit_pushed_partials_two_gpus():
     world, port = 2, os.path.join(tempfile.mkdtemp(prefix="mf_rdzv_"), "store")
     with mp.Manager() as mgr:
         ret = mgr.dict()
-        mp.spawn(_kv8_two_gpu_worker, args=(world, port, ret), nprocs=world, join=True)
+        mp.spawn(_kv8_two_gpu_worker, args=(world, port, ret, max_ctas), nprocs=world, join=True)
         assert dict(ret) == {0: True, 1: True}
 
 
