@@ -177,7 +177,8 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
 
     const uint32_t P = p.page_size;  // a power of two in 8..64
     const uint32_t boxes_per_tile = kTileKeys / P;
-    if (!p.strict_release) grid_launch_dependents();
+    // (cluster form: dependents are released when the V producer has requested its last tile, as in decode_kernel)
+    if (!p.strict_release && !p.release_late) grid_launch_dependents();
 
     if (warp >= kConsumerWarps) {
         // ------------------------------------------------------- two producer warps ---
@@ -247,6 +248,7 @@ decode_kv8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
                 }
             }
         }
+        if (p.release_late && is_v) grid_launch_dependents();
         if (flags[0]) {  // after an abort nobody waits for the ring: let our own copies land before the CTA ends
             const uint32_t n = issued < kStages ? issued : kStages;
             for (uint32_t i = 0; i < n; ++i) {
@@ -1174,6 +1176,7 @@ mf_status paged_decode_kv8_common(MfContext *ctx, const MfDecodePlan *pl, const 
     // (correct, with fewer CTAs than the plan was made for).
     const bool clustered = pl->cluster > 1 && (pl->cluster <= 8 || (ctx->device < 64 && wide_clusters[ctx->device]));
     p.cluster_size = clustered ? pl->cluster : 1;
+    p.release_late = (clustered && !p.strict_release) ? 1u : 0u;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(pl->cluster > 1 && !clustered ? pl->n_ctas / pl->cluster : pl->n_ctas);
     cfg.blockDim = dim3(kThreads);
