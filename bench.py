@@ -57,6 +57,12 @@ WORKLOADS = {
                      theta=5e5, rope_mode=1,
                      name="Llama-3.2-3B shape decode step: 28 layers, 24q/8kv heads, D128, batch 1, ctx 8192, "
                           "cache as 64-token pages in order, one fused launch per layer"),
+    # the batch-1 step on the 8-bit cache: pages in order, the library's own plan (cluster form), CUDA-graph replay
+    "c2-kv8": dict(layers=28, n_heads=24, n_kv_heads=8, head_dim=128, batch=1, lo=8191, hi=8191, page_size=64,
+                   theta=5e5, rope_mode=1, kv8=True, auto_plan=True, graph=True,
+                   name="Llama-3.2-3B shape decode step on the 8-bit cache (FP8 E4M3 + one f32 scale per row): 28 layers, "
+                        "24q/8kv heads, D128, batch 1, ctx 8192, 64-token pages in order, one fused launch per layer, "
+                        "CUDA-graph replay"),
 }
 LONG_CONTEXT = {
     # sequence-sharded single-sequence decode (strong scaling): pages of ONE sequence are cut into
@@ -255,7 +261,7 @@ def run_ours(args, w):
         f.set_option(mfk.OPTION_OVERLAP_LAUNCHES, 1)
     if kv8:
         plan = f.decode_plan(kv_lens, n_heads=hq, n_kv_heads=hkv, head_dim=d, page_size=P,
-                             max_ctas=2 * torch.cuda.get_device_properties(dev).multi_processor_count)
+                             max_ctas=0 if w.get("auto_plan") else 2 * torch.cuda.get_device_properties(dev).multi_processor_count)
         descs = [mfk.paged_kv8(k_pools[i].view(n_pages, hkv, P, d), v_pools[i].view(n_pages, hkv, P, d),
                                k_scales[i].view(n_pages, hkv, P), v_scales[i].view(n_pages, hkv, P), d_table, d_lens,
                                n_kv_heads=hkv, page_size=P) for i in range(layers)]
@@ -363,8 +369,25 @@ def run_ours(args, w):
     sampler.start()
     time.sleep(0.3)
     launches0 = f.launch_count
-    ms, t0, t1 = timed(device_step, args.steps)
-    launches = f.launch_count - launches0
+    if w.get("graph"):
+        # batch-1 steps are host-bound call by call: the same launches replayed from a CUDA graph (the step is
+        # idempotent: same rows, same values)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+            device_step()
+
+        def replay():
+            with torch.cuda.stream(stream):
+                graph.replay()
+
+        for _ in range(3):
+            replay()
+        torch.cuda.synchronize()
+        ms, t0, t1 = timed(replay, args.steps)
+        launches = layers * args.steps
+    else:
+        ms, t0, t1 = timed(device_step, args.steps)
+        launches = f.launch_count - launches0
     f.synchronize()  # also reads the device status word: a timed-out barrier wait would raise here
     for _ in range(2):
         e2e_step()
@@ -1065,7 +1088,8 @@ def other_workloads(args):
     if world == 1:
         jobs += [("c2", lambda a: run_contiguous_decode(a, CONTIGUOUS["c2"]), dict(one_launch=True, projection=False)),
                  ("c4", run_prefill, dict(steps=20, page_size=0)),
-                 ("c3_kv8", lambda a: run_ours(a, dict(WORKLOADS["c3-kv8"])), dict(steps=20, no_cpu_baseline=True))]
+                 ("c3_kv8", lambda a: run_ours(a, dict(WORKLOADS["c3-kv8"])), dict(steps=20, no_cpu_baseline=True)),
+                 ("c2_kv8", lambda a: run_ours(a, dict(WORKLOADS["c2-kv8"])), dict(steps=100, no_cpu_baseline=True))]
     out = {}
     for name, fn, over in jobs:
         a = copy.copy(args)
