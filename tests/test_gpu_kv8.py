@@ -107,7 +107,7 @@ def test_fused_append_decode_on_the_8bit_cache(mfk, foundry, cfg, rope_mode, max
     assert max_abs(host(out), gold.ravel()) <= TOL
 
 
-@pytest.mark.parametrize("cached", [[4999], [1500, 520, 4000]])
+@pytest.mark.parametrize("cached", [[4999], [1500, 520, 4000], [4159]])  # 4159: two CTAs of the last cluster get no tile
 def test_8bit_decode_on_a_plan_in_the_cluster_form(mfk, foundry, cached):
     """A plan made under the library's own CTA count for a short launch is in the cluster form (one range of a unit per
     cluster); the 8-bit kernel has no cluster form and runs every range as one CTA's item: same answer."""

@@ -484,6 +484,8 @@ def test_append_skips_an_empty_sequence_and_a_length_past_the_table(mfk, foundry
     dict(batch=1, n_heads=24, n_kv_heads=8, head_dim=128, page_size=64, cached=[8191]),
     dict(batch=1, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[5000]),
     dict(batch=3, n_heads=14, n_kv_heads=2, head_dim=64, page_size=16, cached=[1023, 1023, 1023]),
+    # 65 tiles per unit in 4 ranges of 17, 17, 17, 14 tiles for clusters of 16: two CTAs of the last cluster get no tile
+    dict(batch=1, n_heads=16, n_kv_heads=2, head_dim=128, page_size=16, cached=[4159]),
 ])
 def test_paged_decode_cluster_form(mfk, foundry, cfg):
     """One sequence (or equal lengths) on pages: the plan takes the cluster form; the same step in the plain
