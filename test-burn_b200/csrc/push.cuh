@@ -13,15 +13,15 @@ namespace push {
 constexpr uint32_t kConsumerThreads = 128;
 constexpr float kNegSentinel = -1e30f;
 
-// One value of a partial into rank r's receive block.  Tagged form: value and step tag in ONE 8-byte store, which
+// One value of a partial into rank r's receive block.  Tagged form: value and step tag in ONE 64-bit store, which
 // the reader sees whole or not at all; it trusts the word once it carries this step's tag, so neither a fence nor a
 // counter stands between the stores and the merge (a system-scope fence costs about 5 us on this machine).
 __device__ __forceinline__ void push_store(const DecodeParams &p, uint32_t r, size_t e, float v)
 {
     if (p.push_tagged) {
-        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(reinterpret_cast<uint2 *>(p.push_dst[r]) + e), "r"(p.push_tag),
-                     "r"(__float_as_uint(v))
-                     : "memory");
+        // one scalar 64-bit store (tag in the low word): single-copy atomic by the memory model, not only in practice
+        const unsigned long long word = ((unsigned long long)__float_as_uint(v) << 32) | p.push_tag;
+        asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(reinterpret_cast<unsigned long long *>(p.push_dst[r]) + e), "l"(word) : "memory");
     } else {
         p.push_dst[r][e] = v;
     }
@@ -29,10 +29,10 @@ __device__ __forceinline__ void push_store(const DecodeParams &p, uint32_t r, si
 // A tagged word of this rank's receive blocks; false while it does not carry the tag yet.
 __device__ __forceinline__ bool tagged_load(const float *base, size_t e, uint32_t tag, float &v)
 {
-    uint32_t t, x;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(t), "=r"(x) : "l"(reinterpret_cast<const uint2 *>(base) + e) : "memory");
-    v = __uint_as_float(x);
-    return t == tag;
+    unsigned long long word;
+    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(word) : "l"(reinterpret_cast<const unsigned long long *>(base) + e) : "memory");
+    v = __uint_as_float((uint32_t)(word >> 32));
+    return (uint32_t)word == tag;
 }
 
 // Sequence-sharded decode, end of a unit: announce the block this CTA has just stored into every
