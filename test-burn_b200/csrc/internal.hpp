@@ -150,6 +150,10 @@ struct MfContext {
     uint64_t launches = 0;
     std::unordered_map<mf::TensorMapKey, CUtensorMap, mf::TensorMapKeyHash> tmaps;
     void *encode_fn = nullptr;
+    // prefill_tc: the order in which the CTAs of the last launch shape take their (query tile, head) items
+    uint32_t tc_order_key[6] = {0, 0, 0, 0, 0, 0};
+    uint16_t tc_order[512];
+    uint32_t tc_order_n = 0;
     uint32_t overlap_launches = 0;  // MF_OPTION_OVERLAP_LAUNCHES
     // Early K/V streaming under programmatic dependent launches, and what bounds it.
     //

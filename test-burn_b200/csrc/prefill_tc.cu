@@ -26,6 +26,9 @@
 //
 // TMEM columns (512): S_0/P_0 [0,128)  S_1/P_1 [128,256)  S_2/P_2 [256,384)  O [384,512).
 #include <algorithm>
+#include <cstring>
+#include <queue>
+#include <vector>
 
 #include "internal.hpp"
 #include "ptx.cuh"
@@ -54,6 +57,9 @@ struct TcParams {
     __half *out;
     uint32_t *status;
     uint32_t q_len, kv_len, query_offset, group, n_heads, n_q_tiles;
+    // The (query tile << 8 | head) item of every CTA, in launch order (use_order; else the arithmetic longest-first order)
+    uint32_t use_order;
+    uint16_t order[512];
     uint32_t out_stride_h, out_stride_m;
     float scale_log2;
     // paged cache: K/V tiles are gathered page by page through the sequence's page-table row
@@ -174,10 +180,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     auto bar = [&](uint32_t i) { return bars + i * 8; };
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // CTAs are handed out in blockIdx order: all heads of the last (longest) query tile first, so the
-    // short tiles fill the tail of the grid.
-    const uint32_t q_tile = p.n_q_tiles - 1 - blockIdx.x / p.n_heads;
-    const uint32_t head = blockIdx.x % p.n_heads;
+    // CTAs are handed out in blockIdx order.  Small grids come with the host's list (tc_item_order); else all heads
+    // of the last (longest) query tile first, so that the short tiles fill the tail of the grid.
+    const uint32_t q_tile = p.use_order ? p.order[blockIdx.x] >> 8 : p.n_q_tiles - 1 - blockIdx.x / p.n_heads;
+    const uint32_t head = p.use_order ? p.order[blockIdx.x] & 0xFFu : blockIdx.x % p.n_heads;
     const uint32_t kvh = head / p.group;
     const uint32_t row0 = q_tile * kBM;
     const uint32_t last_row = min(p.q_len, row0 + kBM) - 1;
@@ -604,6 +610,103 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
 }
 
+// The order in which a grid's CTAs take their (query tile, head) items.  The hardware hands CTAs to the SMs in
+// blockIdx order, one per SM here, so a launch is list scheduling of n_items jobs of (key tiles + a fixed cost) on
+// the SMs, and with 2-3 jobs per SM the longest-first list ends 10-14 % above the mean (measured on the C4 shape: the
+// list below is 3-5 % faster).  Assignment: longest first onto the least loaded SM, then moves and swaps off the most
+// loaded SM while they lower it; list: all jobs by their start time in that assignment, which list scheduling then
+// reproduces.  Heads of a query tile are interchangeable and are numbered as they come.
+constexpr float kTcItemFixedCost = 7.3f;  // what a CTA costs beyond its key tiles, in key tiles (fill, drain, launch)
+
+void tc_item_order(const TcParams &p, uint32_t n_sms, uint16_t *order)
+{
+    const uint32_t nq = p.n_q_tiles, H = p.n_heads, n = nq * H, m = std::min(n_sms, n);
+    std::vector<float> size(nq);
+    for (uint32_t i = 0; i < nq; ++i) {
+        const uint32_t last_row = std::min(p.q_len, (i + 1) * kBM) - 1;
+        const uint32_t key_end = std::min(p.kv_len, last_row + p.query_offset + 1);
+        size[i] = (float)((key_end + kBN - 1) / kBN) + kTcItemFixedCost;
+    }
+    std::vector<uint32_t> cls(nq);  // query tiles, longest first
+    for (uint32_t i = 0; i < nq; ++i) cls[i] = i;
+    std::stable_sort(cls.begin(), cls.end(), [&](uint32_t a, uint32_t b) { return size[a] > size[b]; });
+    std::vector<std::vector<uint32_t>> on(m);  // query tile of every job of an SM
+    std::vector<float> load(m, 0.f);
+    {
+        typedef std::pair<float, uint32_t> Slot;
+        std::priority_queue<Slot, std::vector<Slot>, std::greater<Slot>> free_at;
+        for (uint32_t s = 0; s < m; ++s) free_at.push(Slot(0.f, s));
+        for (uint32_t ci = 0; ci < nq; ++ci)
+            for (uint32_t h = 0; h < H; ++h) {
+                const Slot s = free_at.top();
+                free_at.pop();
+                on[s.second].push_back(cls[ci]);
+                load[s.second] = s.first + size[cls[ci]];
+                free_at.push(Slot(load[s.second], s.second));
+            }
+    }
+    for (uint32_t round = 0; round < 512; ++round) {
+        const uint32_t A = (uint32_t)(std::max_element(load.begin(), load.end()) - load.begin());
+        const float LA = load[A];
+        float best = LA - 1e-3f;
+        int best_a = -1, best_b = -1;
+        uint32_t best_B = 0;
+        for (uint32_t ia = 0; ia < on[A].size(); ++ia) {
+            const float a = size[on[A][ia]];
+            for (uint32_t B = 0; B < m; ++B) {
+                if (B == A) continue;
+                const float moved = std::max(LA - a, load[B] + a);
+                if (moved < best) {
+                    best = moved;
+                    best_a = (int)ia, best_b = -1, best_B = B;
+                }
+                for (uint32_t ib = 0; ib < on[B].size(); ++ib) {
+                    const float b = size[on[B][ib]];
+                    if (b >= a) continue;
+                    const float swapped = std::max(LA - a + b, load[B] + a - b);
+                    if (swapped < best) {
+                        best = swapped;
+                        best_a = (int)ia, best_b = (int)ib, best_B = B;
+                    }
+                }
+            }
+        }
+        if (best_a < 0) break;
+        const uint32_t qa = on[A][best_a];
+        if (best_b >= 0) {
+            const uint32_t qb = on[best_B][best_b];
+            on[A][best_a] = qb;
+            on[best_B][best_b] = qa;
+            load[A] += size[qb] - size[qa];
+            load[best_B] += size[qa] - size[qb];
+        } else {
+            on[A].erase(on[A].begin() + best_a);
+            on[best_B].push_back(qa);
+            load[A] -= size[qa];
+            load[best_B] += size[qa];
+        }
+    }
+    struct Job {
+        float start;
+        uint32_t q_tile;
+    };
+    std::vector<Job> jobs;
+    jobs.reserve(n);
+    for (uint32_t s = 0; s < m; ++s) {
+        std::sort(on[s].begin(), on[s].end(), [&](uint32_t a, uint32_t b) { return size[a] > size[b]; });
+        float t = 0.f;
+        for (uint32_t q : on[s]) {
+            jobs.push_back(Job{t, q});
+            t += size[q];
+        }
+    }
+    std::stable_sort(jobs.begin(), jobs.end(), [&](const Job &a, const Job &b) {
+        return a.start != b.start ? a.start < b.start : size[a.q_tile] > size[b.q_tile];
+    });
+    std::vector<uint32_t> next_head(nq, 0);
+    for (uint32_t i = 0; i < n; ++i) order[i] = (uint16_t)((jobs[i].q_tile << 8) | next_head[jobs[i].q_tile]++);
+}
+
 }  // namespace
 
 // Returns MF_ERR_OPERATION_NOT_SUPPORTED (without touching last_error semantics) when the
@@ -706,7 +809,19 @@ mf_status launch_prefill_tc(MfContext *ctx, const void *q, const void *k, const 
     }
     p.n_heads = sp.n_heads;
     p.n_q_tiles = (b.q_len + kBM - 1) / kBM;
-    dim3 grid(p.n_q_tiles * sp.n_heads);
+    const uint32_t n_items = p.n_q_tiles * sp.n_heads;
+    if (n_items <= 512 && p.n_q_tiles <= 256 && sp.n_heads <= 256 && n_items > (uint32_t)std::max(1, ctx->sm_count)) {
+        // the list of the last shape is kept: the layers of a model launch the same shape one after another
+        const uint32_t key[6] = {p.q_len, p.kv_len, p.query_offset, sp.n_heads, (uint32_t)ctx->sm_count, 1u};
+        if (memcmp(key, ctx->tc_order_key, sizeof(key)) != 0 || ctx->tc_order_n != n_items) {
+            tc_item_order(p, (uint32_t)ctx->sm_count, ctx->tc_order);
+            memcpy(ctx->tc_order_key, key, sizeof(key));
+            ctx->tc_order_n = n_items;
+        }
+        memcpy(p.order, ctx->tc_order, n_items * sizeof(uint16_t));
+        p.use_order = 1;
+    }
+    dim3 grid(n_items);
     kern<<<grid, kTcThreads, smem_bytes, ctx->stream>>>(tm_q, tm_k, tm_v, p);
     *handled = true;
     return check_launch(ctx, "prefill_tc_kernel");
